@@ -1,0 +1,279 @@
+"""CPU restatement of the memorax sequence-mixing path (TEST INFRASTRUCTURE ONLY).
+
+Two layers, both plain CPU code:
+
+* ``prefix_scan`` / ``memoroid_scan``: the reference's formulation -- an
+  inclusive prefix over ``[carry, z_1 .. z_T]`` under a reset-aware wrapper of a
+  cell's binary operator (memorax/networks/sequence_models/memoroid.py:60-91),
+  with the per-cell operators of lru.py:92-95, s5.py:133-136,
+  min_gru.py:67-74, linear_attention.py:82-86 and the multiplicative-reset
+  linear form of memoroid.py:119-123.  NumPy, any bracketing.
+* ``*_seq`` functions: the closed-form sequential recurrences those scans
+  equal, written in torch so that fp64 autograd gives the gradient oracle.
+  ``tests/test_oracle.py`` proves layer 2 == layer 1, and
+  ``tests/golden`` pins both against the reference's own source.
+
+Shapes follow the reference: batch-major, time second, features last;
+``done[b, t] = 1`` means step t starts a new episode, i.e. the state before
+step t is discarded (memoroid.py:67-85).
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+# --------------------------------------------------------------------------
+# Layer 1: the reference formulation (generic prefix scan + wrapped operator)
+# --------------------------------------------------------------------------
+
+
+def _tmap(fn, *trees):
+    """Map over tuples-of-arrays pytrees (the only pytrees on this path)."""
+    if isinstance(trees[0], (tuple, list)):
+        return tuple(_tmap(fn, *parts) for parts in zip(*trees))
+    return fn(*trees)
+
+
+def prefix_scan(op, elems, bracketing="tree"):
+    """Inclusive prefix of ``elems`` along axis 1 under associative ``op``.
+
+    ``bracketing='tree'`` combines in the odd/even recursive-doubling order of
+    a work-efficient parallel scan (the order jax.lax.associative_scan, the
+    call at memoroid.py:87, uses); ``'left'`` folds left to right.  Both must
+    agree up to rounding for an associative operator.
+    """
+    n = _leaves(elems)[0].shape[1]
+    if bracketing == "left":
+        acc = _tmap(lambda x: x[:, :1], elems)
+        outs = [acc]
+        for t in range(1, n):
+            acc = op(acc, _tmap(lambda x: x[:, t:t + 1], elems))
+            outs.append(acc)
+        return _tmap(lambda *xs: np.concatenate(xs, axis=1), *outs)
+    if n < 2:
+        return elems
+    # Pairwise-reduce neighbours, scan the half-length sequence, then fill the
+    # even positions from the odd prefixes.
+    even = _tmap(lambda x: x[:, 0:n - 1:2], elems)
+    odd = _tmap(lambda x: x[:, 1:n:2], elems)
+    odd_prefix = prefix_scan(op, op(even, odd), "tree")
+    if n % 2 == 0:
+        rest = op(_tmap(lambda x: x[:, :-1], odd_prefix),
+                  _tmap(lambda x: x[:, 2::2], elems))
+    else:
+        rest = op(odd_prefix, _tmap(lambda x: x[:, 2::2], elems))
+    first = _tmap(lambda x: x[:, :1], elems)
+    even_prefix = _tmap(lambda f, r: np.concatenate([f, r], axis=1), first, rest)
+
+    def interleave(e, o):
+        out = np.empty((e.shape[0], n) + e.shape[2:], dtype=e.dtype)
+        out[:, 0::2] = e
+        out[:, 1::2] = o
+        return out
+
+    return _tmap(interleave, even_prefix, odd_prefix)
+
+
+def _leaves(tree):
+    if isinstance(tree, (tuple, list)):
+        out = []
+        for part in tree:
+            out.extend(_leaves(part))
+        return out
+    return [tree]
+
+
+def _expand_like(flag, leaf):
+    while flag.ndim < leaf.ndim:
+        flag = flag[..., None]
+    return flag
+
+
+def memoroid_scan(cell_op, z, initial_carry, done, bracketing="tree"):
+    """Restates ``Memoroid.scan_fn`` (memoroid.py:60-91).
+
+    The carry is prepended at time 0 with reset flag 0, ``done`` supplies the
+    flags of the T real steps, and two prefix elements combine as
+    ``where(rhs_reset, rhs, cell_op(lhs, rhs))`` with the flags OR-ed.
+    Returns ``(h, next_carry)``: all T prefixes and the last one (time axis
+    kept, as memoroid.py:89-90 does).
+    """
+    elems = _tmap(lambda c, e: np.concatenate([c, e], axis=1), initial_carry, z)
+    done = np.asarray(done, dtype=np.float64)
+    flags = np.concatenate([np.zeros((done.shape[0], 1)), done], axis=1)
+
+    def wrapped(lhs, rhs):
+        lhs_c, lhs_f = lhs
+        rhs_c, rhs_f = rhs
+        merged = cell_op(lhs_c, rhs_c)
+        out = _tmap(lambda r, m: np.where(_expand_like(rhs_f, r) > 0, r, m), rhs_c, merged)
+        return out, np.maximum(lhs_f, rhs_f)
+
+    h, _ = prefix_scan(wrapped, (elems, flags), bracketing)
+    next_carry = _tmap(lambda x: x[:, -1:], h)
+    h = _tmap(lambda x: x[:, 1:], h)
+    return h, next_carry
+
+
+def op_linear(lhs, rhs):
+    """(state, decay) operator of LRU / S5 / the RTRL sensitivity scan
+    (lru.py:92-95, s5.py:133-136, memoroid.py:119-123)."""
+    s_i, a_i = lhs
+    s_j, a_j = rhs
+    return (a_j * s_i + s_j, a_j * a_i)
+
+
+def op_log_linear(lhs, rhs):
+    """MinGRU's log-space operator (min_gru.py:67-74)."""
+    x_i, d_i = lhs
+    x_j, d_j = rhs
+    return (np.logaddexp(d_j + x_i, x_j), d_i + d_j)
+
+
+def op_additive(lhs, rhs):
+    """Linear attention's additive operator (linear_attention.py:82-86)."""
+    return tuple(p + q for p, q in zip(lhs, rhs))
+
+
+def op_gated_delta(lhs, rhs):
+    """Gated delta rule as a monoid over (M, U): state maps compose on the
+    right, ``S -> S M + U`` with S of shape (d_v, d_k).  Not in the reference."""
+    m_i, u_i = lhs
+    m_j, u_j = rhs
+    return (m_i @ m_j, u_i @ m_j + u_j)
+
+
+def elu_plus_one(x):
+    """Feature map of linear_attention.py:58-60 (works on numpy and torch)."""
+    if isinstance(x, torch.Tensor):
+        return torch.where(x > 0, x + 1.0, torch.exp(torch.clamp(x, max=0.0)))
+    return np.where(x > 0, x + 1.0, np.exp(np.minimum(x, 0.0)))
+
+
+# --------------------------------------------------------------------------
+# Layer 2: closed-form sequential recurrences (torch; fp64 autograd oracle)
+# --------------------------------------------------------------------------
+
+
+def _keep(done, t, like):
+    """1 - done[:, t] broadcast against ``like`` (real dtype)."""
+    m = 1.0 - done[:, t].to(like.real.dtype if like.is_complex() else like.dtype)
+    while m.ndim < like.ndim:
+        m = m[..., None]
+    return m
+
+
+def linrec_seq(a, b, h0, done, a0=None):
+    """h_t = done_t ? b_t : a_t h_{t-1} + b_t ;  A_t = done_t ? a_t : a_t A_{t-1}.
+
+    ``a`` is (B,T,D) or time-invariant (D,) (lru.py:86); real or complex.
+    Returns ``h`` (B,T,D) and the decay leaf of the next carry ``A_T`` (B,D).
+    Equals ``memoroid_scan(op_linear, ...)``.
+    """
+    bsz, steps, _ = b.shape
+    if a.ndim == 1:
+        a = a.expand(bsz, steps, -1)
+    h = h0
+    acc = torch.ones_like(h0) if a0 is None else a0
+    out = []
+    for t in range(steps):
+        m = _keep(done, t, h)
+        h = a[:, t] * (m * h) + b[:, t]
+        acc = torch.where(m > 0, a[:, t] * acc, a[:, t] + 0 * acc)
+        out.append(h)
+    return torch.stack(out, dim=1), acc
+
+
+def mingru_seq(log_state, decay, x0, done, a0=None):
+    """x_t = done_t ? ls_t : logaddexp(d_t + x_{t-1}, ls_t); A_t likewise with
+    sums (min_gru.py:67-74 under the reset wrapper).  ``x0`` may be -inf."""
+    bsz, steps, _ = log_state.shape
+    x = x0
+    acc = torch.zeros_like(x0) if a0 is None else a0
+    out = []
+    for t in range(steps):
+        m = _keep(done, t, x) > 0
+        prev = torch.where(m, decay[:, t] + x, torch.full_like(x, -float("inf")))
+        x = torch.logaddexp(prev, log_state[:, t])
+        acc = torch.where(m, decay[:, t] + acc, decay[:, t])
+        out.append(x)
+    return torch.stack(out, dim=1), acc
+
+
+def linattn_seq(q, k, v, s0, z0, done, eps=1e-6, feature_map=True):
+    """Causal linear attention with carried (S, z) (linear_attention.py:62-112).
+
+    q,k (B,T,H,dk), v (B,T,H,dv); S (B,H,dv,dk) = sum v (x) phi(k), z (B,H,dk).
+    o_t = S_t phi(q_t) / max(phi(q_t).z_t, eps).  Returns (o, S_T, z_T).
+    """
+    if feature_map:
+        q, k = elu_plus_one(q), elu_plus_one(k)
+    s, z = s0, z0
+    out = []
+    for t in range(q.shape[1]):
+        m = _keep(done, t, z)
+        s = m[..., None] * s + v[:, t, :, :, None] * k[:, t, :, None, :]
+        z = m * z + k[:, t]
+        num = torch.einsum("bhvk,bhk->bhv", s, q[:, t])
+        den = torch.clamp((q[:, t] * z).sum(-1, keepdim=True), min=eps)
+        out.append(num / den)
+    return torch.stack(out, dim=1), s, z
+
+
+def gdelta_seq(q, k, v, alpha, beta, s0, done):
+    """Gated delta rule: S_t = a_t S'_{t-1} (I - b_t k_t k_t^T) + b_t v_t k_t^T,
+    o_t = S_t q_t, with S' = 0 where done_t.  S is (B,H,dv,dk); alpha, beta are
+    (B,T,H).  Equals ``memoroid_scan(op_gated_delta, ...)`` on the elements
+    ``(alpha (I - beta k k^T), beta v k^T)`` with carry ``(I, S_0)``."""
+    s = s0
+    out = []
+    for t in range(q.shape[1]):
+        m = _keep(done, t, alpha[:, t])
+        s = (m * alpha[:, t])[..., None, None] * s
+        sk = torch.einsum("bhvk,bhk->bhv", s, k[:, t])
+        bt = beta[:, t][..., None]
+        s = s + (bt * (v[:, t] - sk))[..., None] * k[:, t, :, None, :]
+        out.append(torch.einsum("bhvk,bhk->bhv", s, q[:, t]))
+    return torch.stack(out, dim=1), s
+
+
+def jax_cotangent(grad):
+    """torch.autograd's gradient of a real loss w.r.t. a complex tensor is the
+    conjugate of what JAX's reverse mode (and hence the reference) returns."""
+    return grad.conj() if grad.is_complex() else grad
+
+
+# --------------------------------------------------------------------------
+# fp32 multi-threaded port timed as the CPU baseline of the benchmark
+# --------------------------------------------------------------------------
+
+
+def linattn_reference_form(q, k, v, s0, z0, done, eps=1e-6):
+    """The reference's own O(T d^2) formulation, vectorised: materialise every
+    per-step outer product (linear_attention.py:78), take the reset-aware
+    inclusive prefix over time (memoroid.py:60-91; here segment-wise cumsum,
+    which an additive operator's prefix scan equals), then read
+    (linear_attention.py:100-109).  Differentiable; used for timing."""
+    bsz, steps, heads, _ = q.shape
+    fq, fk = elu_plus_one(q), elu_plus_one(k)
+    outer = torch.einsum("bthi,bthj->bthij", v, fk)
+    outer = torch.cat([s0[:, None], outer], dim=1)
+    keys = torch.cat([z0[:, None], fk], dim=1)
+    flags = torch.cat([torch.zeros_like(done[:, :1]), done], dim=1)
+    seg = torch.cumsum(flags, dim=1)
+    cs = torch.cumsum(outer, dim=1)
+    cz = torch.cumsum(keys, dim=1)
+    # subtract the prefix that ended just before the last reset
+    idx = torch.arange(steps + 1, device=q.device)[None].expand(bsz, -1)
+    start = torch.where(flags > 0, idx, torch.zeros_like(idx))
+    start = torch.cummax(start, dim=1).values
+    prev = torch.clamp(start - 1, min=0)
+    gate = (start > 0).to(q.dtype)
+    base_s = torch.gather(cs, 1, prev[:, :, None, None, None].expand_as(cs))
+    base_z = torch.gather(cz, 1, prev[:, :, None, None].expand_as(cz))
+    s_all = cs - gate[:, :, None, None, None] * base_s
+    z_all = cz - gate[:, :, None, None] * base_z
+    del seg
+    num = torch.einsum("bthij,bthj->bthi", s_all[:, 1:], fq)
+    den = torch.clamp(torch.einsum("bthi,bthi->bth", fq, z_all[:, 1:]), min=eps)
+    return num / den[..., None], s_all[:, -1], z_all[:, -1]

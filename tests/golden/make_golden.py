@@ -1,0 +1,294 @@
+"""Generate tests/golden/memoroid_golden.npz by executing the reference's own
+source files for the sequence-mixing path.
+
+The reference (memorax 1.0.1) is pure Python on top of JAX/Flax, neither of
+which can be installed in the build image.  This script therefore loads the
+reference's files *unmodified* from a checkout (``--reference DIR``; nothing is
+copied) under a minimal NumPy stand-in for the JAX/Flax symbols those files
+touch: ``jax.numpy`` is NumPy, ``jax.vmap`` maps over axis 0 with a Python
+loop, ``jax.tree.map`` maps over tuples, ``flax.linen.Module`` is a plain
+attribute bag, and ``jax.lax.associative_scan`` is a left-to-right fold (any
+bracketing of an associative operator gives the same prefix).  Everything is
+evaluated in float64, so the vectors pin the reference's *semantics* --
+operators, reset rule, carry layout, read-outs -- not XLA's rounding.
+
+Files executed: memorax/utils/axes.py,
+memorax/networks/sequence_models/{sequence_model,memoroid,lru,min_gru,
+linear_attention}.py.
+
+Run (only where the reference checkout exists):
+    python tests/golden/make_golden.py --reference /path/to/memorax
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import os
+import sys
+import types
+import zlib
+
+import numpy as np
+
+F64 = np.float64
+
+
+# ----------------------------------------------------------------------------
+# stand-ins
+# ----------------------------------------------------------------------------
+def _tree_map(fn, *trees):
+    first = trees[0]
+    if isinstance(first, (tuple, list)):
+        return tuple(_tree_map(fn, *parts) for parts in zip(*trees))
+    if isinstance(first, dict):
+        return {k: _tree_map(fn, *(t[k] for t in trees)) for k in first}
+    return fn(*trees)
+
+
+def _vmap(fn):
+    def mapped(*args):
+        n = None
+
+        def probe(x):
+            nonlocal n
+            n = x.shape[0]
+            return x
+
+        _tree_map(probe, args)
+        outs = [fn(*_tree_map(lambda x: x[i], args)) for i in range(n)]
+        return _tree_map(lambda *xs: np.stack(xs, axis=0), *outs)
+
+    return mapped
+
+
+def _fold_scan(fn, elems, axis=0):
+    take = lambda x, t: np.take(x, [t], axis=axis)
+    n = None
+
+    def probe(x):
+        nonlocal n
+        n = x.shape[axis]
+        return x
+
+    _tree_map(probe, elems)
+    acc = _tree_map(lambda x: take(x, 0), elems)
+    outs = [acc]
+    for t in range(1, n):
+        acc = fn(acc, _tree_map(lambda x: take(x, t), elems))
+        outs.append(acc)
+    return _tree_map(lambda *xs: np.concatenate(xs, axis=axis), *outs)
+
+
+def _softplus(x):
+    return np.logaddexp(x, 0.0)
+
+
+class _Module:
+    """Attribute bag with the few Flax hooks the reference's cells call."""
+
+    def __init__(self, **fields):
+        for name, value in fields.items():
+            setattr(self, name, value)
+        self._params = {}
+        if hasattr(self, "setup"):
+            self.setup()
+
+    def param(self, name, init_fn, *args):
+        rng = np.random.default_rng(zlib.crc32(name.encode()))
+        shape = next((a for a in args if isinstance(a, tuple) and all(isinstance(i, int) for i in a)), None)
+        if shape is None:  # gamma_log style: derived from other params
+            value = init_fn(None, *args)
+        else:
+            value = rng.normal(size=shape).astype(F64) * 0.5
+        self._params[name] = value
+        return value
+
+    def sow(self, *a, **k):
+        return None
+
+
+class _Dense(_Module):
+    """Bias-free projection with lazily drawn float64 weights."""
+
+    def __init__(self, features=None, name="dense", **_):
+        self.features = features if isinstance(features, tuple) else (features,)
+        self.name = name
+        self.kernel = None
+
+    def __call__(self, x):
+        if self.kernel is None:
+            rng = np.random.default_rng(zlib.crc32(self.name.encode()))
+            self.kernel = rng.normal(size=(x.shape[-1],) + self.features).astype(F64) / np.sqrt(x.shape[-1])
+        return np.tensordot(x, self.kernel, axes=([-1], [0]))
+
+
+class _Identity(_Module):
+    def __init__(self, *a, **k):
+        pass
+
+    def __call__(self, x):
+        return x
+
+
+def install_stand_ins(reference_dir):
+    jnp = types.ModuleType("jax.numpy")
+    jnp.__dict__.update({k: getattr(np, k) for k in dir(np) if not k.startswith("_")})
+    jnp.zeros = lambda shape, dtype=None: np.zeros(shape, dtype=np.complex128 if dtype == np.complex64 else F64)
+    jnp.ones = lambda shape, dtype=None: np.ones(shape, dtype=np.complex128 if dtype == np.complex64 else F64)
+    jnp.full = lambda shape, v, dtype=None: np.full(shape, v, dtype=F64)
+
+    lax = types.ModuleType("jax.lax")
+    lax.associative_scan = _fold_scan
+    lax.complex = lambda re, im: re + 1j * im
+    lax.stop_gradient = lambda x: x
+
+    tree = types.ModuleType("jax.tree")
+    tree.map = _tree_map
+
+    rnd = types.ModuleType("jax.random")
+    rnd.key = lambda seed: seed
+
+    jax = types.ModuleType("jax")
+    jax.numpy, jax.lax, jax.tree, jax.random = jnp, lax, tree, rnd
+    jax.vmap = _vmap
+    jax.Array = np.ndarray
+
+    nn = types.ModuleType("flax.linen")
+    nn.Module = _Module
+    nn.compact = lambda f: f
+    nn.elu = lambda x: np.where(x > 0, x, np.expm1(np.minimum(x, 0)))
+    nn.relu = lambda x: np.maximum(x, 0)
+    nn.softplus = _softplus
+    nn.Dense = _Dense
+    nn.DenseGeneral = _Dense
+    nn.RMSNorm = _Identity
+    inits = types.ModuleType("flax.linen.initializers")
+    inits.lecun_normal = lambda *a, **k: None
+    inits.zeros_init = lambda *a, **k: None
+    nn.initializers = inits
+    flax = types.ModuleType("flax")
+    flax.linen = nn
+    ftyping = types.ModuleType("flax.typing")
+    ftyping.Dtype = ftyping.Initializer = object
+
+    mods = {"jax": jax, "jax.numpy": jnp, "jax.lax": lax, "jax.tree": tree, "jax.random": rnd,
+            "flax": flax, "flax.linen": nn, "flax.linen.initializers": inits, "flax.typing": ftyping}
+
+    # Bare packages whose __path__ points into the checkout, so that the
+    # reference's modules import each other without running the package
+    # __init__ files (which pull in the whole library).
+    root = os.path.join(reference_dir, "memorax")
+    for name, rel in [("memorax", ""), ("memorax.utils", "utils"), ("memorax.networks", "networks"),
+                      ("memorax.networks.sequence_models", "networks/sequence_models")]:
+        pkg = types.ModuleType(name)
+        pkg.__path__ = [os.path.join(root, rel)]
+        mods[name] = pkg
+    typing_stub = types.ModuleType("memorax.utils.typing")
+    typing_stub.Array = typing_stub.Carry = typing_stub.Key = object
+    mods["memorax.utils.typing"] = typing_stub
+    sys.modules.update(mods)
+
+
+# ----------------------------------------------------------------------------
+# cases
+# ----------------------------------------------------------------------------
+def done_patterns(rng, bsz, steps):
+    done = (rng.random((bsz, steps)) < 0.25).astype(F64)
+    done[0, 0] = 1.0                      # reset at the very first step
+    if steps > 4:
+        done[1, 2:4] = 1.0                # consecutive resets
+        done[-1, :] = 0.0                 # a row with no reset at all
+    return done
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--out", default=os.path.join(os.path.dirname(__file__), "memoroid_golden.npz"))
+    args = ap.parse_args()
+    install_stand_ins(args.reference)
+
+    sm = "memorax.networks.sequence_models."
+    memoroid = importlib.import_module(sm + "memoroid")
+    lru = importlib.import_module(sm + "lru")
+    min_gru = importlib.import_module(sm + "min_gru")
+    linattn = importlib.import_module(sm + "linear_attention")
+
+    rng = np.random.default_rng(20240611)
+    out = {}
+
+    # ---- LRU (complex diagonal, time-invariant decay) through Memoroid ----
+    bsz, steps, feat, hid = 3, 9, 5, 4
+    cell = lru.LRUCell(features=feat, hidden_dim=hid)
+    # keep |lambda| < 1 and the phase moderate
+    cell.nu_log = np.log(rng.uniform(0.05, 0.6, hid))
+    cell.theta_log = np.log(rng.uniform(0.05, 0.6, hid))
+    model = memoroid.Memoroid(cell=cell)
+    x = rng.normal(size=(bsz, steps, feat))
+    done = done_patterns(rng, bsz, steps)
+    carry = (rng.normal(size=(bsz, 1, hid)) + 1j * rng.normal(size=(bsz, 1, hid)),
+             rng.normal(size=(bsz, 1, hid)) * 0.3 + 1j * rng.normal(size=(bsz, 1, hid)) * 0.3)
+    z = cell(x)
+    h, nxt = model.scan_fn(z, carry, done)
+    nxt2, y = model(x, done, carry)
+    assert all(np.array_equal(p, q) for p, q in zip(nxt, nxt2))
+    out.update(lru_x=x, lru_done=done, lru_c_state=carry[0], lru_c_decay=carry[1],
+               lru_z_state=z[0], lru_z_decay=z[1], lru_h_state=h[0], lru_h_decay=h[1],
+               lru_n_state=nxt[0], lru_n_decay=nxt[1], lru_y=y,
+               lru_C=cell.C_real + 1j * cell.C_imag, lru_D=cell.D)
+    # default carry (initialize_carry) path
+    nxt0, y0 = model(x, done, None)
+    out.update(lru_default_n_state=nxt0[0], lru_default_n_decay=nxt0[1], lru_default_y=y0)
+
+    # ---- MinGRU (log space, -inf initial carry) --------------------------
+    bsz, steps, feat = 3, 8, 6
+    cell = min_gru.MinGRUCell(features=feat)
+    cell.dtype, cell.param_dtype = None, F64
+    model = memoroid.Memoroid(cell=cell)
+    x = rng.normal(size=(bsz, steps, 4)) * 2.0
+    done = done_patterns(rng, bsz, steps)
+    z = cell(x)
+    carry0 = cell.initialize_carry(0, (bsz, feat))
+    assert np.all(np.isneginf(carry0[0]))
+    with np.errstate(invalid="ignore"):
+        h, nxt = model.scan_fn(z, carry0, done)
+        _, y = model(x, done, None)
+    carry1 = (rng.normal(size=(bsz, 1, feat)), -np.abs(rng.normal(size=(bsz, 1, feat))))
+    h1, nxt1 = model.scan_fn(z, carry1, done)
+    out.update(gru_done=done, gru_z_state=z[0], gru_z_decay=z[1],
+               gru_h_state=h[0], gru_h_decay=h[1], gru_n_state=nxt[0], gru_n_decay=nxt[1], gru_y=y,
+               gru_c1_state=carry1[0], gru_c1_decay=carry1[1],
+               gru_h1_state=h1[0], gru_n1_state=nxt1[0], gru_n1_decay=nxt1[1])
+
+    # ---- Linear attention (ELU+1, carried S and z) ------------------------
+    bsz, steps, heads, hd, feat = 2, 11, 2, 4, 6
+    cell = linattn.LinearAttentionCell(features=feat, head_dim=hd, num_heads=heads)
+    cell.output_projection = _Identity()   # kernel boundary = before RMSNorm / output Dense
+    model = memoroid.Memoroid(cell=cell)
+    x = rng.normal(size=(bsz, steps, feat))
+    done = done_patterns(rng, bsz, steps)
+    carry = (rng.normal(size=(bsz, 1, heads, hd, hd)) * 0.3, np.abs(rng.normal(size=(bsz, 1, heads, hd))) * 0.3)
+    nxt, y = model(x, done, carry)
+    out.update(la_done=done, la_q=cell.query(x), la_k=cell.key(x), la_v=cell.value(x),
+               la_c_S=carry[0], la_c_z=carry[1], la_n_S=nxt[0], la_n_z=nxt[1],
+               la_y=y.reshape(bsz, steps, heads, hd))
+    # clamp branch: a state that drives the denominator below eps
+    carry_neg = (carry[0], -np.abs(carry[1]) * 50.0)
+    nxt, y = model(x, done, carry_neg)
+    out.update(la_neg_c_z=carry_neg[1], la_neg_n_z=nxt[1], la_neg_y=y.reshape(bsz, steps, heads, hd))
+
+    # ---- multiplicative-reset linear scan (RTRL sensitivities) ------------
+    bsz, steps, hid, psize = 3, 10, 4, 3
+    decay = rng.uniform(0.2, 0.95, size=(bsz, steps, hid))
+    jac = {"w": rng.normal(size=(bsz, steps, hid, psize))}
+    sens = {"w": rng.normal(size=(bsz, 1, hid, psize))}
+    done = done_patterns(rng, bsz, steps)
+    nxt = memoroid.Memoroid._propagate_sensitivities(None, decay, jac, sens, done)
+    out.update(rt_decay=decay, rt_jac=jac["w"], rt_sens=sens["w"], rt_done=done, rt_next=nxt["w"])
+
+    np.savez_compressed(args.out, **out)
+    print("wrote", args.out, "with", len(out), "arrays")
+
+
+if __name__ == "__main__":
+    main()

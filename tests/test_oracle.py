@@ -1,0 +1,180 @@
+"""CPU checks of the oracle itself: against the golden vectors produced by the
+reference's own source, and layer 2 (sequential closed forms) against layer 1
+(the reference's prefix-scan formulation)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import memoroid_oracle as mo
+
+T64 = lambda x: torch.from_numpy(np.ascontiguousarray(x))
+TOL = dict(rtol=1e-11, atol=1e-11)
+
+
+# ---------------------------------------------------------------- golden pins
+def test_golden_lru_scan_and_read(golden):
+    g = golden
+    h, a_last = mo.linrec_seq(T64(g["lru_z_decay"]), T64(g["lru_z_state"]), T64(g["lru_c_state"][:, 0]),
+                              T64(g["lru_done"]), T64(g["lru_c_decay"][:, 0]))
+    np.testing.assert_allclose(h.numpy(), g["lru_h_state"], **TOL)
+    np.testing.assert_allclose(h[:, -1:].numpy(), g["lru_n_state"], **TOL)
+    np.testing.assert_allclose(a_last[:, None].numpy(), g["lru_n_decay"], **TOL)
+    # read-out of lru.py:97-102 on top of the scanned state
+    y = np.einsum("fh,bth->btf", g["lru_C"], h.numpy()).real + g["lru_D"] * g["lru_x"]
+    np.testing.assert_allclose(y, g["lru_y"], **TOL)
+
+
+def test_golden_lru_time_invariant_decay_and_default_carry(golden):
+    g = golden
+    lam = T64(g["lru_z_decay"][0, 0])
+    assert np.all(g["lru_z_decay"] == g["lru_z_decay"][0, 0])  # lru.py:86 broadcasts one lambda
+    bsz, _, hid = g["lru_z_state"].shape
+    h0 = torch.zeros(bsz, hid, dtype=torch.complex128)
+    h, a_last = mo.linrec_seq(lam, T64(g["lru_z_state"]), h0, T64(g["lru_done"]))
+    np.testing.assert_allclose(h[:, -1:].numpy(), g["lru_default_n_state"], **TOL)
+    np.testing.assert_allclose(a_last[:, None].numpy(), g["lru_default_n_decay"], **TOL)
+
+
+def test_golden_mingru(golden):
+    g = golden
+    bsz, _, feat = g["gru_z_state"].shape
+    x0 = torch.full((bsz, feat), -float("inf"), dtype=torch.float64)
+    x, a_last = mo.mingru_seq(T64(g["gru_z_state"]), T64(g["gru_z_decay"]), x0, T64(g["gru_done"]))
+    assert not torch.isnan(x).any()
+    np.testing.assert_allclose(x.numpy(), g["gru_h_state"], **TOL)
+    np.testing.assert_allclose(torch.exp(x).numpy(), g["gru_y"], **TOL)
+    np.testing.assert_allclose(a_last[:, None].numpy(), g["gru_n_decay"], **TOL)
+    x, a_last = mo.mingru_seq(T64(g["gru_z_state"]), T64(g["gru_z_decay"]), T64(g["gru_c1_state"][:, 0]),
+                              T64(g["gru_done"]), T64(g["gru_c1_decay"][:, 0]))
+    np.testing.assert_allclose(x.numpy(), g["gru_h1_state"], **TOL)
+    np.testing.assert_allclose(a_last[:, None].numpy(), g["gru_n1_decay"], **TOL)
+
+
+@pytest.mark.parametrize("variant", ["", "neg_"])
+def test_golden_linear_attention(golden, variant):
+    g = golden
+    z0 = g["la_c_z"] if variant == "" else g["la_neg_c_z"]
+    o, s_last, z_last = mo.linattn_seq(T64(g["la_q"]), T64(g["la_k"]), T64(g["la_v"]), T64(g["la_c_S"][:, 0]),
+                                       T64(z0[:, 0]), T64(g["la_done"]))
+    np.testing.assert_allclose(o.numpy(), g["la_y"] if variant == "" else g["la_neg_y"], rtol=1e-9, atol=1e-9)
+    if variant == "":
+        np.testing.assert_allclose(s_last[:, None].numpy(), g["la_n_S"], **TOL)
+        np.testing.assert_allclose(z_last[:, None].numpy(), g["la_n_z"], **TOL)
+    o2, s2, z2 = mo.linattn_reference_form(T64(g["la_q"]), T64(g["la_k"]), T64(g["la_v"]), T64(g["la_c_S"][:, 0]),
+                                           T64(z0[:, 0]), T64(g["la_done"]))
+    np.testing.assert_allclose(o2.numpy(), o.numpy(), rtol=1e-8, atol=1e-8)
+    np.testing.assert_allclose(s2.numpy(), s_last.numpy(), rtol=1e-9, atol=1e-9)
+    np.testing.assert_allclose(z2.numpy(), z_last.numpy(), rtol=1e-9, atol=1e-9)
+
+
+def test_golden_rtrl_multiplicative_reset(golden):
+    g = golden
+    bsz, steps, hid, psz = g["rt_jac"].shape
+    a = np.repeat(g["rt_decay"], psz, axis=-1)
+    h, _ = mo.linrec_seq(T64(a), T64(g["rt_jac"].reshape(bsz, steps, -1)), T64(g["rt_sens"].reshape(bsz, -1)),
+                         T64(g["rt_done"]))
+    np.testing.assert_allclose(h[:, -1].numpy().reshape(bsz, 1, hid, psz), g["rt_next"], **TOL)
+
+
+# ------------------------------------------------- layer 1 == layer 2, any bracketing
+def _done(rng, bsz, steps, p=0.2):
+    d = (rng.random((bsz, steps)) < p).astype(np.float64)
+    d[0, 0] = 1
+    if steps > 3:
+        d[-1, 1:3] = 1
+    return d
+
+
+@pytest.mark.parametrize("steps", [1, 2, 7, 16, 33])
+@pytest.mark.parametrize("cplx", [False, True])
+def test_linear_operator_scan_equals_recurrence(steps, cplx):
+    rng = np.random.default_rng(steps)
+    bsz, dim = 3, 5
+    mk = (lambda *s: rng.normal(size=s) + 1j * rng.normal(size=s)) if cplx else (lambda *s: rng.normal(size=s))
+    a, b = mk(bsz, steps, dim) * 0.7, mk(bsz, steps, dim)
+    h0, a0 = mk(bsz, 1, dim), mk(bsz, 1, dim)
+    done = _done(rng, bsz, steps)
+    for br in ("tree", "left"):
+        (h, acc), (hn, an) = mo.memoroid_scan(mo.op_linear, (b, a), (h0, a0), done, br)
+        h_seq, a_last = mo.linrec_seq(T64(a), T64(b), T64(h0[:, 0]), T64(done), T64(a0[:, 0]))
+        np.testing.assert_allclose(h, h_seq.numpy(), rtol=1e-10, atol=1e-10)
+        np.testing.assert_allclose(an[:, 0], a_last.numpy(), rtol=1e-10, atol=1e-10)
+        np.testing.assert_allclose(hn, h[:, -1:], rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("steps", [1, 5, 32])
+def test_log_operator_scan_equals_recurrence(steps):
+    rng = np.random.default_rng(steps + 100)
+    bsz, dim = 2, 4
+    ls, d = rng.normal(size=(bsz, steps, dim)), -np.abs(rng.normal(size=(bsz, steps, dim)))
+    x0 = np.full((bsz, 1, dim), -np.inf)
+    d0 = np.zeros((bsz, 1, dim))
+    done = _done(rng, bsz, steps)
+    (x, _), (_, dn) = mo.memoroid_scan(mo.op_log_linear, (ls, d), (x0, d0), done)
+    x_seq, d_last = mo.mingru_seq(T64(ls), T64(d), T64(x0[:, 0]), T64(done))
+    np.testing.assert_allclose(x, x_seq.numpy(), rtol=1e-10, atol=1e-10)
+    np.testing.assert_allclose(dn[:, 0], d_last.numpy(), rtol=1e-10, atol=1e-10)
+
+
+@pytest.mark.parametrize("steps", [1, 6, 19])
+def test_additive_operator_scan_equals_linear_attention(steps):
+    rng = np.random.default_rng(steps + 200)
+    bsz, heads, dk, dv = 2, 2, 3, 4
+    q, k = rng.normal(size=(bsz, steps, heads, dk)), rng.normal(size=(bsz, steps, heads, dk))
+    v = rng.normal(size=(bsz, steps, heads, dv))
+    s0, z0 = rng.normal(size=(bsz, 1, heads, dv, dk)), np.abs(rng.normal(size=(bsz, 1, heads, dk)))
+    done = _done(rng, bsz, steps)
+    fk = mo.elu_plus_one(k)
+    elems = (np.einsum("bthi,bthj->bthij", v, fk), fk)
+    (s_all, z_all), (sn, zn) = mo.memoroid_scan(mo.op_additive, elems, (s0, z0), done)
+    fq = mo.elu_plus_one(q)
+    o = np.einsum("bthij,bthj->bthi", s_all, fq) / np.maximum(np.einsum("bthi,bthi->bth", fq, z_all), 1e-6)[..., None]
+    o_seq, s_last, z_last = mo.linattn_seq(T64(q), T64(k), T64(v), T64(s0[:, 0]), T64(z0[:, 0]), T64(done))
+    np.testing.assert_allclose(o, o_seq.numpy(), rtol=1e-9, atol=1e-9)
+    np.testing.assert_allclose(sn[:, 0], s_last.numpy(), rtol=1e-10, atol=1e-10)
+    np.testing.assert_allclose(zn[:, 0], z_last.numpy(), rtol=1e-10, atol=1e-10)
+
+
+@pytest.mark.parametrize("steps", [1, 6, 19])
+def test_gated_delta_monoid_equals_recurrence(steps):
+    rng = np.random.default_rng(steps + 300)
+    bsz, heads, dk, dv = 2, 2, 4, 3
+    q = rng.normal(size=(bsz, steps, heads, dk))
+    k = rng.normal(size=(bsz, steps, heads, dk))
+    k /= np.linalg.norm(k, axis=-1, keepdims=True)
+    v = rng.normal(size=(bsz, steps, heads, dv))
+    alpha = rng.uniform(0.5, 1.0, size=(bsz, steps, heads))
+    beta = rng.uniform(0.1, 0.9, size=(bsz, steps, heads))
+    s0 = rng.normal(size=(bsz, 1, heads, dv, dk))
+    done = _done(rng, bsz, steps)
+    eye = np.broadcast_to(np.eye(dk), (bsz, steps, heads, dk, dk))
+    m = alpha[..., None, None] * (eye - beta[..., None, None] * k[..., :, None] * k[..., None, :])
+    u = beta[..., None, None] * v[..., :, None] * k[..., None, :]
+    carry = (np.broadcast_to(np.eye(dk), (bsz, 1, heads, dk, dk)).copy(), s0)
+    # With the carry's map set to the identity the U leaf of the prefix is the state.
+    (_, s_all), _ = mo.memoroid_scan(mo.op_gated_delta, (m, u), carry, done)
+    # A reset replaces the whole element by (M_t, U_t), i.e. S_t = U_t: the
+    # previous state is dropped, exactly the recurrence with S' = 0.
+    o = np.einsum("bthvk,bthk->bthv", s_all, q)
+    o_seq, s_last = mo.gdelta_seq(T64(q), T64(k), T64(v), T64(alpha), T64(beta), T64(s0[:, 0]), T64(done))
+    np.testing.assert_allclose(o, o_seq.numpy(), rtol=1e-9, atol=1e-9)
+    np.testing.assert_allclose(s_all[:, -1], s_last.numpy(), rtol=1e-9, atol=1e-9)
+
+
+# ------------------------------------------------------------ structural properties
+def test_carry_split_invariance_and_reset_equivalence():
+    rng = np.random.default_rng(7)
+    bsz, steps, dim = 2, 12, 3
+    a = T64(rng.uniform(0.1, 0.9, size=(bsz, steps, dim)))
+    b = T64(rng.normal(size=(bsz, steps, dim)))
+    h0 = T64(rng.normal(size=(bsz, dim)))
+    done = torch.zeros(bsz, steps, dtype=torch.float64)
+    done[:, 5] = 1
+    h, acc = mo.linrec_seq(a, b, h0, done)
+    h1, acc1 = mo.linrec_seq(a[:, :4], b[:, :4], h0, done[:, :4])
+    h2, acc2 = mo.linrec_seq(a[:, 4:], b[:, 4:], h1[:, -1], done[:, 4:], acc1)
+    np.testing.assert_allclose(torch.cat([h1, h2], 1).numpy(), h.numpy(), rtol=1e-12, atol=1e-12)
+    np.testing.assert_allclose(acc2.numpy(), acc.numpy(), rtol=1e-12)
+    # a reset at t=5 == an independent sequence starting at t=5 from a zero state
+    h_tail, _ = mo.linrec_seq(a[:, 5:], b[:, 5:], torch.zeros_like(h0), torch.zeros(bsz, steps - 5, dtype=torch.float64))
+    np.testing.assert_allclose(h[:, 5:].numpy(), h_tail.numpy(), rtol=1e-12, atol=1e-12)
