@@ -1,0 +1,126 @@
+/*
+ * mxk -- sequence-mixing kernels for NVIDIA B200 (sm_100a) behind a plain C ABI.
+ *
+ * Every function below replaces one computation that memorax performs with
+ * jax.lax.associative_scan inside Memoroid.scan_fn
+ * (memorax/networks/sequence_models/memoroid.py:60-91) plus the cell-specific
+ * operator / read-out named in its comment.  The reference has no FFI of its
+ * own; these are the entry points an XLA custom call (jax.ffi) or any other
+ * host would bind.
+ *
+ * Conventions
+ *   - Launch-only: each call validates its arguments on the host, enqueues
+ *     kernels on `stream` and returns.  No host synchronisation, no allocation,
+ *     no retained pointers.  All buffers, outputs and workspaces included, are
+ *     device memory owned by the caller.
+ *   - Layout: batch-major, time second, features last, C-contiguous --
+ *     (B, T, D) or (B, T, H, d); `done` is (B, T) bytes, non-zero = "step t is
+ *     the first step of a new episode", i.e. the state before step t is
+ *     discarded (memoroid.py:67-85).  `done` may be NULL (no resets).
+ *   - Carries are passed without the reference's singleton time axis:
+ *     (B, D) or (B, H, dv, dk).
+ *   - Complex tensors are interleaved (re, im) float pairs.  Complex
+ *     cotangents follow JAX's convention (no conjugation anywhere), which is
+ *     the conjugate of torch.autograd's.
+ *   - Return value: 0 = enqueued; negative = argument rejected before any
+ *     launch (MXK_ERR_*); positive = cudaError_t reported by the launch.
+ */
+#ifndef MXK_H_
+#define MXK_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* mxk_stream_t; /* a cudaStream_t / CUstream */
+
+enum {
+  MXK_OK = 0,
+  MXK_ERR_NULL = -1,        /* a required pointer is NULL */
+  MXK_ERR_DIMS = -2,        /* a dimension is non-positive or too large */
+  MXK_ERR_ALIGN = -3,       /* a pointer is not 16-byte aligned */
+  MXK_ERR_UNSUPPORTED = -4, /* head dim / chunk size outside the compiled set */
+  MXK_ERR_WORKSPACE = -5    /* workspace missing or too small */
+};
+
+/* Human-readable text for a status returned by any function below. */
+const char* mxk_status_string(int status);
+/* ABI version of the loaded library (bumped on signature changes). */
+int mxk_abi_version(void);
+
+/* ---------------------------------------------------------------------------
+ * Diagonal linear recurrence  h_t = done_t ? b_t : a_t * h_{t-1} + b_t
+ * with the decay leaf          A_t = done_t ? a_t : a_t * A_{t-1}.
+ *
+ * Replaces Memoroid.scan_fn over the (state, decay) operator of
+ * lru.py:92-95 / s5.py:133-136 and the multiplicative-reset scan of
+ * memoroid.py:114-141.
+ *
+ *   a       (B,T,D), or (D) when a_time_invariant != 0 (lru.py:86)
+ *   b       (B,T,D)
+ *   h0      (B,D) carried state, NULL = zeros (lru.py:104-108)
+ *   a0      (B,D) carried decay leaf, NULL = ones; read only if a_last != NULL
+ *   h       (B,T,D) out: every state (next carry's state is h[:, T-1])
+ *   a_last  (B,D) out, optional: decay leaf of the next carry (memoroid.py:89)
+ * f32: real floats.  c64: complex64, D counts complex elements.
+ * ------------------------------------------------------------------------- */
+int mxk_linrec_f32_fwd(const float* a, int a_time_invariant, const float* b, const float* h0,
+                       const float* a0, const uint8_t* done, float* h, float* a_last,
+                       int B, int T, int D, mxk_stream_t stream);
+int mxk_linrec_c64_fwd(const float* a, int a_time_invariant, const float* b, const float* h0,
+                       const float* a0, const uint8_t* done, float* h, float* a_last,
+                       int B, int T, int D, mxk_stream_t stream);
+
+/* Reverse-mode of the above (what jax.grad derives from the scan; the
+ * reference has no hand-written rule).  With m_t = !done_t and
+ * g_t = gh_t + a_{t+1} m_{t+1} g_{t+1}   (gh_last is added to gh_{T-1}):
+ *   gb_t = g_t;  ga_t = m_t h_{t-1} g_t;  gh0 = a_1 m_1 g_1.
+ *
+ *   h        (B,T,D) states saved by the forward call;  h0 as in forward
+ *   gh       (B,T,D) cotangent of h;  gh_last (B,D) cotangent of the carried
+ *            state, NULL = zeros
+ *   gb       (B,T,D) out
+ *   ga       out, optional: (B,T,D), or (D) summed over batch and time when
+ *            a_time_invariant (needs `workspace`)
+ *   gh0      (B,D) out, optional
+ *   workspace  scratch of mxk_linrec_bwd_workspace_bytes(...) bytes, only for
+ *            the time-invariant ga reduction; contents undefined afterwards.
+ * The decay leaf a_last has no cotangent (every read-out ignores it). */
+size_t mxk_linrec_bwd_workspace_bytes(int is_complex, int a_time_invariant, int B, int T, int D);
+int mxk_linrec_f32_bwd(const float* a, int a_time_invariant, const float* h, const float* h0,
+                       const uint8_t* done, const float* gh, const float* gh_last, float* gb,
+                       float* ga, float* gh0, void* workspace, size_t workspace_bytes,
+                       int B, int T, int D, mxk_stream_t stream);
+/* c64 only: `conjugate` != 0 runs the same recurrences with conj(a) and
+ * conj(h), which maps torch.autograd-convention cotangents in to
+ * torch-convention cotangents out without separate conjugation passes;
+ * 0 = JAX convention. */
+int mxk_linrec_c64_bwd(const float* a, int a_time_invariant, const float* h, const float* h0,
+                       const uint8_t* done, const float* gh, const float* gh_last, float* gb,
+                       float* ga, float* gh0, void* workspace, size_t workspace_bytes,
+                       int B, int T, int D, int conjugate, mxk_stream_t stream);
+
+/* ---------------------------------------------------------------------------
+ * Log-space recurrence (MinGRU, min_gru.py:67-78):
+ *   x_t = done_t ? ls_t : logaddexp(d_t + x_{t-1}, ls_t)
+ *   A_t = done_t ? d_t  : d_t + A_{t-1}
+ * x0 may hold -inf (min_gru.py:80-90); NULL = -inf.  a0 NULL = zeros.
+ *   x  (B,T,D) out: log states;  y (B,T,D) out, optional: exp(x), the read-out.
+ * Backward: gx is the cotangent of x, gy (optional) that of y; with
+ * w_t = m_t exp(d_t + x_{t-1} - x_t) and G_t = gx_t + gy_t y_t + w_{t+1} G_{t+1}:
+ *   gls_t = (1 - w_t) G_t;  gd_t = w_t G_t;  gx0 = w_1 G_1.
+ * ------------------------------------------------------------------------- */
+int mxk_loglinrec_f32_fwd(const float* ls, const float* d, const float* x0, const float* a0,
+                          const uint8_t* done, float* x, float* y, float* a_last,
+                          int B, int T, int D, mxk_stream_t stream);
+int mxk_loglinrec_f32_bwd(const float* d, const float* x, const float* x0, const uint8_t* done,
+                          const float* gx, const float* gy, const float* gx_last, float* gls,
+                          float* gd, float* gx0, int B, int T, int D, mxk_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MXK_H_ */

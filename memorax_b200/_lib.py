@@ -1,0 +1,66 @@
+"""ctypes binding of ``libmxk.so`` (the C-ABI declared in ``include/mxk.h``).
+
+There is no CPU or PyTorch fallback: if the shared library is missing the
+import of this module raises, and every wrapper raises on a non-zero status.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libmxk.so")
+
+_p = ctypes.c_void_p
+_i = ctypes.c_int
+_z = ctypes.c_size_t
+_f = ctypes.c_float
+
+# name -> (restype, argtypes); mirrors include/mxk.h one to one.
+SIGNATURES = {
+    "mxk_status_string": (ctypes.c_char_p, [_i]),
+    "mxk_abi_version": (_i, []),
+    "mxk_linrec_f32_fwd": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
+    "mxk_linrec_c64_fwd": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
+    "mxk_linrec_bwd_workspace_bytes": (_z, [_i, _i, _i, _i, _i]),
+    "mxk_linrec_f32_bwd": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _i, _i, _i, _p]),
+    "mxk_linrec_c64_bwd": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _i, _i, _i, _i, _p]),
+    "mxk_loglinrec_f32_fwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
+    "mxk_loglinrec_f32_bwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
+}
+
+
+class MxkError(RuntimeError):
+    def __init__(self, fn, status, text):
+        super().__init__(f"{fn} failed with status {status}: {text}")
+        self.status = status
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m memorax_b200.build` "
+            "(nvcc, sm_100a). memorax_b200 has no fallback path.")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+lib = _load()
+
+
+def status_string(status: int) -> str:
+    return lib.mxk_status_string(int(status)).decode()
+
+
+def check(fn_name: str, status: int) -> None:
+    if status != 0:
+        raise MxkError(fn_name, status, status_string(status))
+
+
+def call(fn_name: str, *args) -> None:
+    """Invoke a status-returning entry point and raise MxkError on failure."""
+    check(fn_name, getattr(lib, fn_name)(*args))

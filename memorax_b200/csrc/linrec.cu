@@ -1,0 +1,548 @@
+// Diagonal linear recurrences over time with carried state and episode resets:
+// real fp32, complex64 and MinGRU's log-space form, forward and backward.
+//
+// All of these are bandwidth-bound: one pass over the (B,T,D) operands.  A
+// thread owns 16 bytes of channels of one batch row and walks time
+// sequentially, so a warp touches 512 contiguous bytes per step and a 256-
+// thread block streams whole rows; loads for several time steps are issued
+// before the dependent arithmetic so that enough bytes are in flight to cover
+// HBM latency.  When B*D is too small to fill 148 SMs that way, each thread
+// owns a single element instead (more, narrower threads).
+#include "mxk_common.cuh"
+
+namespace mxk {
+namespace {
+
+constexpr int kBlock = 256;
+constexpr int kUnroll = 4;  // time steps whose loads are in flight together
+
+template <int W> struct VecOf;
+template <> struct VecOf<4> { using type = float4; };
+template <> struct VecOf<2> { using type = float2; };
+template <> struct VecOf<1> { using type = float; };
+
+template <int W>
+struct Pack {
+  float v[W];
+};
+
+template <int W>
+__device__ __forceinline__ Pack<W> load_pack(const float* p) {
+  using V = typename VecOf<W>::type;
+  V raw = ld_stream(reinterpret_cast<const V*>(p));
+  Pack<W> out;
+  const float* f = reinterpret_cast<const float*>(&raw);
+#pragma unroll
+  for (int i = 0; i < W; ++i) out.v[i] = f[i];
+  return out;
+}
+
+template <int W>
+__device__ __forceinline__ Pack<W> load_pack_cached(const float* p) {
+  using V = typename VecOf<W>::type;
+  V raw = *reinterpret_cast<const V*>(p);
+  Pack<W> out;
+  const float* f = reinterpret_cast<const float*>(&raw);
+#pragma unroll
+  for (int i = 0; i < W; ++i) out.v[i] = f[i];
+  return out;
+}
+
+template <int W>
+__device__ __forceinline__ void store_pack(float* p, const Pack<W>& x) {
+  using V = typename VecOf<W>::type;
+  V raw;
+  float* f = reinterpret_cast<float*>(&raw);
+#pragma unroll
+  for (int i = 0; i < W; ++i) f[i] = x.v[i];
+  st_stream(reinterpret_cast<V*>(p), raw);
+}
+
+template <int W>
+__device__ __forceinline__ Pack<W> fill_pack(float re, float im, bool cplx) {
+  Pack<W> out;
+#pragma unroll
+  for (int i = 0; i < W; ++i) out.v[i] = (cplx && (i & 1)) ? im : re;
+  return out;
+}
+
+// out = x * y (+ z), elementwise over the pack; complex packs hold (re, im) pairs.
+template <bool CPLX, int W>
+__device__ __forceinline__ Pack<W> mul(const Pack<W>& x, const Pack<W>& y) {
+  Pack<W> o;
+  if constexpr (CPLX) {
+#pragma unroll
+    for (int i = 0; i < W; i += 2) {
+      o.v[i] = x.v[i] * y.v[i] - x.v[i + 1] * y.v[i + 1];
+      o.v[i + 1] = x.v[i] * y.v[i + 1] + x.v[i + 1] * y.v[i];
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < W; ++i) o.v[i] = x.v[i] * y.v[i];
+  }
+  return o;
+}
+
+template <bool CPLX, int W>
+__device__ __forceinline__ Pack<W> mul_add(const Pack<W>& x, const Pack<W>& y, const Pack<W>& z) {
+  Pack<W> o;
+  if constexpr (CPLX) {
+#pragma unroll
+    for (int i = 0; i < W; i += 2) {
+      o.v[i] = fmaf(x.v[i], y.v[i], fmaf(-x.v[i + 1], y.v[i + 1], z.v[i]));
+      o.v[i + 1] = fmaf(x.v[i], y.v[i + 1], fmaf(x.v[i + 1], y.v[i], z.v[i + 1]));
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < W; ++i) o.v[i] = fmaf(x.v[i], y.v[i], z.v[i]);
+  }
+  return o;
+}
+
+// Complex conjugate of every (re, im) pair when `on` (no-op for real packs).
+template <bool CPLX, int W>
+__device__ __forceinline__ Pack<W> conj_if(Pack<W> x, int on) {
+  if constexpr (CPLX) {
+    if (on) {
+#pragma unroll
+      for (int i = 1; i < W; i += 2) x.v[i] = -x.v[i];
+    }
+  }
+  return x;
+}
+
+template <int W>
+__device__ __forceinline__ Pack<W> add(const Pack<W>& x, const Pack<W>& y) {
+  Pack<W> o;
+#pragma unroll
+  for (int i = 0; i < W; ++i) o.v[i] = x.v[i] + y.v[i];
+  return o;
+}
+
+// ------------------------------------------------------------------ forward
+// Row stride is `row` floats (D for real, 2D for complex); a thread's W floats
+// start at column `col`.
+template <bool CPLX, int W>
+__global__ void __launch_bounds__(kBlock)
+linrec_fwd_kernel(const float* __restrict__ a, int a_tinv, const float* __restrict__ b,
+                  const float* __restrict__ h0, const float* __restrict__ a0,
+                  const uint8_t* __restrict__ done, float* __restrict__ h,
+                  float* __restrict__ a_last, int B, int T, int row) {
+  const int per_row = row / W;
+  const long long gid = static_cast<long long>(blockIdx.x) * kBlock + threadIdx.x;
+  if (gid >= static_cast<long long>(B) * per_row) return;
+  const int bi = static_cast<int>(gid / per_row);
+  const int col = static_cast<int>(gid % per_row) * W;
+  const size_t seq = static_cast<size_t>(bi) * T * row + col;
+  const uint8_t* drow = done ? done + static_cast<size_t>(bi) * T : nullptr;
+
+  Pack<W> cur = h0 ? load_pack_cached<W>(h0 + static_cast<size_t>(bi) * row + col) : fill_pack<W>(0.f, 0.f, CPLX);
+  const bool want_decay = a_last != nullptr;
+  Pack<W> acc = (want_decay && a0) ? load_pack_cached<W>(a0 + static_cast<size_t>(bi) * row + col)
+                                   : fill_pack<W>(1.f, 0.f, CPLX);
+  Pack<W> a_fix = fill_pack<W>(0.f, 0.f, CPLX);
+  if (a_tinv) a_fix = load_pack_cached<W>(a + col);
+
+  for (int t0 = 0; t0 < T; t0 += kUnroll) {
+    Pack<W> av[kUnroll], bv[kUnroll];
+    bool rs[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int t = t0 + u;
+      if (t < T) {
+        const size_t off = seq + static_cast<size_t>(t) * row;
+        bv[u] = load_pack<W>(b + off);
+        if (!a_tinv) av[u] = load_pack<W>(a + off);
+        rs[u] = drow ? (drow[t] != 0) : false;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int t = t0 + u;
+      if (t < T) {
+        const Pack<W>& at = a_tinv ? a_fix : av[u];
+        cur = rs[u] ? bv[u] : mul_add<CPLX, W>(at, cur, bv[u]);
+        if (want_decay) acc = rs[u] ? at : mul<CPLX, W>(at, acc);
+        store_pack<W>(h + seq + static_cast<size_t>(t) * row, cur);
+      }
+    }
+  }
+  if (want_decay) {
+    float* dst = a_last + static_cast<size_t>(bi) * row + col;
+#pragma unroll
+    for (int i = 0; i < W; ++i) dst[i] = acc.v[i];
+  }
+}
+
+// ----------------------------------------------------------------- backward
+// Walks time right to left carrying c = a_{t+1} m_{t+1} g_{t+1}.
+template <bool CPLX, int W>
+__global__ void __launch_bounds__(kBlock)
+linrec_bwd_kernel(const float* __restrict__ a, int a_tinv, const float* __restrict__ h,
+                  const float* __restrict__ h0, const uint8_t* __restrict__ done,
+                  const float* __restrict__ gh, const float* __restrict__ gh_last,
+                  float* __restrict__ gb, float* __restrict__ ga, float* __restrict__ ga_partial,
+                  float* __restrict__ gh0, int B, int T, int row, int conj_ops) {
+  const int per_row = row / W;
+  const long long gid = static_cast<long long>(blockIdx.x) * kBlock + threadIdx.x;
+  if (gid >= static_cast<long long>(B) * per_row) return;
+  const int bi = static_cast<int>(gid / per_row);
+  const int col = static_cast<int>(gid % per_row) * W;
+  const size_t seq = static_cast<size_t>(bi) * T * row + col;
+  const size_t crow = static_cast<size_t>(bi) * row + col;
+  const uint8_t* drow = done ? done + static_cast<size_t>(bi) * T : nullptr;
+
+  Pack<W> carry = gh_last ? load_pack_cached<W>(gh_last + crow) : fill_pack<W>(0.f, 0.f, CPLX);
+  Pack<W> a_fix = fill_pack<W>(0.f, 0.f, CPLX);
+  if (a_tinv) a_fix = conj_if<CPLX, W>(load_pack_cached<W>(a + col), conj_ops);
+  Pack<W> ga_acc = fill_pack<W>(0.f, 0.f, CPLX);
+  const bool want_ga = (ga != nullptr) || (ga_partial != nullptr);
+
+  for (int t0 = T - 1; t0 >= 0; t0 -= kUnroll) {
+    Pack<W> av[kUnroll], gv[kUnroll], hp[kUnroll];
+    bool rs[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int t = t0 - u;
+      if (t >= 0) {
+        const size_t off = seq + static_cast<size_t>(t) * row;
+        gv[u] = load_pack<W>(gh + off);
+        if (!a_tinv) av[u] = conj_if<CPLX, W>(load_pack<W>(a + off), conj_ops);
+        rs[u] = drow ? (drow[t] != 0) : false;
+        if (want_ga && !rs[u]) {
+          if (t > 0) hp[u] = load_pack<W>(h + off - row);
+          else hp[u] = h0 ? load_pack_cached<W>(h0 + crow) : fill_pack<W>(0.f, 0.f, CPLX);
+          hp[u] = conj_if<CPLX, W>(hp[u], conj_ops);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int t = t0 - u;
+      if (t >= 0) {
+        const Pack<W>& at = a_tinv ? a_fix : av[u];
+        const Pack<W> g = add<W>(gv[u], carry);
+        const size_t off = seq + static_cast<size_t>(t) * row;
+        store_pack<W>(gb + off, g);
+        if (rs[u]) {
+          carry = fill_pack<W>(0.f, 0.f, CPLX);
+          if (want_ga && !a_tinv) store_pack<W>(ga + off, carry);
+        } else {
+          carry = mul<CPLX, W>(at, g);
+          if (want_ga) {
+            if (a_tinv) ga_acc = mul_add<CPLX, W>(hp[u], g, ga_acc);
+            else store_pack<W>(ga + off, mul<CPLX, W>(hp[u], g));
+          }
+        }
+      }
+    }
+  }
+  if (gh0) {
+#pragma unroll
+    for (int i = 0; i < W; ++i) gh0[crow + i] = carry.v[i];
+  }
+  if (a_tinv && ga_partial) {
+#pragma unroll
+    for (int i = 0; i < W; ++i) ga_partial[crow + i] = ga_acc.v[i];
+  }
+}
+
+// Sums the (B, row) per-sequence partials of the time-invariant decay gradient
+// over the batch in a fixed order (deterministic; no atomics).
+__global__ void __launch_bounds__(kBlock)
+reduce_rows_kernel(const float* __restrict__ partial, float* __restrict__ out, int B, int row) {
+  const int col = blockIdx.x * kBlock + threadIdx.x;
+  if (col >= row) return;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  int bi = 0;
+  for (; bi + 3 < B; bi += 4) {
+    s0 += partial[static_cast<size_t>(bi) * row + col];
+    s1 += partial[static_cast<size_t>(bi + 1) * row + col];
+    s2 += partial[static_cast<size_t>(bi + 2) * row + col];
+    s3 += partial[static_cast<size_t>(bi + 3) * row + col];
+  }
+  for (; bi < B; ++bi) s0 += partial[static_cast<size_t>(bi) * row + col];
+  out[col] = (s0 + s1) + (s2 + s3);
+}
+
+// ------------------------------------------------------------ log-space form
+__device__ __forceinline__ float log_add_exp(float p, float q) {
+  const float hi = fmaxf(p, q), lo = fminf(p, q);
+  if (hi == -INFINITY) return -INFINITY;
+  return hi + log1pf(expf(lo - hi));
+}
+
+template <int W>
+__global__ void __launch_bounds__(kBlock)
+loglinrec_fwd_kernel(const float* __restrict__ ls, const float* __restrict__ d,
+                     const float* __restrict__ x0, const float* __restrict__ a0,
+                     const uint8_t* __restrict__ done, float* __restrict__ x, float* __restrict__ y,
+                     float* __restrict__ a_last, int B, int T, int row) {
+  const int per_row = row / W;
+  const long long gid = static_cast<long long>(blockIdx.x) * kBlock + threadIdx.x;
+  if (gid >= static_cast<long long>(B) * per_row) return;
+  const int bi = static_cast<int>(gid / per_row);
+  const int col = static_cast<int>(gid % per_row) * W;
+  const size_t seq = static_cast<size_t>(bi) * T * row + col;
+  const size_t crow = static_cast<size_t>(bi) * row + col;
+  const uint8_t* drow = done ? done + static_cast<size_t>(bi) * T : nullptr;
+
+  Pack<W> cur = x0 ? load_pack_cached<W>(x0 + crow) : fill_pack<W>(-INFINITY, 0.f, false);
+  Pack<W> acc = (a_last && a0) ? load_pack_cached<W>(a0 + crow) : fill_pack<W>(0.f, 0.f, false);
+
+  for (int t0 = 0; t0 < T; t0 += kUnroll) {
+    Pack<W> lv[kUnroll], dv[kUnroll];
+    bool rs[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int t = t0 + u;
+      if (t < T) {
+        const size_t off = seq + static_cast<size_t>(t) * row;
+        lv[u] = load_pack<W>(ls + off);
+        dv[u] = load_pack<W>(d + off);
+        rs[u] = drow ? (drow[t] != 0) : false;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int t = t0 + u;
+      if (t < T) {
+        Pack<W> yo;
+#pragma unroll
+        for (int i = 0; i < W; ++i) {
+          cur.v[i] = rs[u] ? lv[u].v[i] : log_add_exp(dv[u].v[i] + cur.v[i], lv[u].v[i]);
+          acc.v[i] = rs[u] ? dv[u].v[i] : dv[u].v[i] + acc.v[i];
+          yo.v[i] = expf(cur.v[i]);
+        }
+        const size_t off = seq + static_cast<size_t>(t) * row;
+        store_pack<W>(x + off, cur);
+        if (y) store_pack<W>(y + off, yo);
+      }
+    }
+  }
+  if (a_last) {
+#pragma unroll
+    for (int i = 0; i < W; ++i) a_last[crow + i] = acc.v[i];
+  }
+}
+
+template <int W>
+__global__ void __launch_bounds__(kBlock)
+loglinrec_bwd_kernel(const float* __restrict__ d, const float* __restrict__ x,
+                     const float* __restrict__ x0, const uint8_t* __restrict__ done,
+                     const float* __restrict__ gx, const float* __restrict__ gy,
+                     const float* __restrict__ gx_last, float* __restrict__ gls,
+                     float* __restrict__ gd, float* __restrict__ gx0, int B, int T, int row) {
+  const int per_row = row / W;
+  const long long gid = static_cast<long long>(blockIdx.x) * kBlock + threadIdx.x;
+  if (gid >= static_cast<long long>(B) * per_row) return;
+  const int bi = static_cast<int>(gid / per_row);
+  const int col = static_cast<int>(gid % per_row) * W;
+  const size_t seq = static_cast<size_t>(bi) * T * row + col;
+  const size_t crow = static_cast<size_t>(bi) * row + col;
+  const uint8_t* drow = done ? done + static_cast<size_t>(bi) * T : nullptr;
+
+  // carry = w_{t+1} G_{t+1}
+  Pack<W> carry = gx_last ? load_pack_cached<W>(gx_last + crow) : fill_pack<W>(0.f, 0.f, false);
+
+  for (int t0 = T - 1; t0 >= 0; t0 -= kUnroll) {
+    Pack<W> dv[kUnroll], xv[kUnroll], xp[kUnroll], gxv[kUnroll], gyv[kUnroll];
+    bool rs[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int t = t0 - u;
+      if (t >= 0) {
+        const size_t off = seq + static_cast<size_t>(t) * row;
+        rs[u] = drow ? (drow[t] != 0) : false;
+        xv[u] = load_pack<W>(x + off);
+        gxv[u] = gx ? load_pack<W>(gx + off) : fill_pack<W>(0.f, 0.f, false);
+        if (gy) gyv[u] = load_pack<W>(gy + off);
+        if (!rs[u]) {
+          dv[u] = load_pack<W>(d + off);
+          if (t > 0) xp[u] = load_pack<W>(x + off - row);
+          else xp[u] = x0 ? load_pack_cached<W>(x0 + crow) : fill_pack<W>(-INFINITY, 0.f, false);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int t = t0 - u;
+      if (t >= 0) {
+        Pack<W> ols, od;
+#pragma unroll
+        for (int i = 0; i < W; ++i) {
+          float g = gxv[u].v[i] + carry.v[i];
+          if (gy) g = fmaf(gyv[u].v[i], expf(xv[u].v[i]), g);
+          float w = 0.f;
+          if (!rs[u]) {
+            const float p = dv[u].v[i] + xp[u].v[i];
+            w = (p == -INFINITY) ? 0.f : expf(p - xv[u].v[i]);
+          }
+          od.v[i] = w * g;
+          ols.v[i] = (1.f - w) * g;
+          carry.v[i] = od.v[i];
+        }
+        const size_t off = seq + static_cast<size_t>(t) * row;
+        store_pack<W>(gls + off, ols);
+        store_pack<W>(gd + off, od);
+      }
+    }
+  }
+  if (gx0) {
+#pragma unroll
+    for (int i = 0; i < W; ++i) gx0[crow + i] = carry.v[i];
+  }
+}
+
+// ------------------------------------------------------------- host helpers
+// Wide packs when they give every SM at least two full blocks, else one
+// element per thread (more, narrower threads keep more SMs busy on small B*D).
+inline int pick_width(long long floats_total, int row, bool cplx, std::initializer_list<const void*> ptrs) {
+  const int narrow = cplx ? 2 : 1;
+  if (row % 4 != 0) return narrow;
+  for (const void* p : ptrs)
+    if (p && !aligned16(p)) return narrow;
+  if (floats_total / 4 < 2LL * kNumSMs * kBlock) return narrow;
+  return 4;
+}
+
+inline unsigned blocks_for(long long threads) {
+  return static_cast<unsigned>((threads + kBlock - 1) / kBlock);
+}
+
+inline int check_dims(int B, int T, int D) {
+  if (B <= 0 || T <= 0 || D <= 0) return MXK_ERR_DIMS;
+  if (static_cast<long long>(B) * D > (1LL << 40)) return MXK_ERR_DIMS;
+  return MXK_OK;
+}
+
+template <bool CPLX>
+int linrec_fwd(const float* a, int a_tinv, const float* b, const float* h0, const float* a0,
+               const uint8_t* done, float* h, float* a_last, int B, int T, int D, mxk_stream_t stream) {
+  if (!a || !b || !h) return MXK_ERR_NULL;
+  if (int st = check_dims(B, T, D)) return st;
+  const int row = CPLX ? 2 * D : D;
+  const int min_align = CPLX ? 8 : 4;
+  for (const void* p : {(const void*)a, (const void*)b, (const void*)h0, (const void*)a0, (const void*)h, (const void*)a_last})
+    if (p && (reinterpret_cast<uintptr_t>(p) % min_align)) return MXK_ERR_ALIGN;
+  const long long total = static_cast<long long>(B) * row;
+  const int w = pick_width(total, row, CPLX, {a, b, h0, a0, h, a_last});
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (w == 4)
+    linrec_fwd_kernel<CPLX, 4><<<blocks_for(total / 4), kBlock, 0, s>>>(a, a_tinv, b, h0, a0, done, h, a_last, B, T, row);
+  else
+    linrec_fwd_kernel<CPLX, CPLX ? 2 : 1><<<blocks_for(total / (CPLX ? 2 : 1)), kBlock, 0, s>>>(a, a_tinv, b, h0, a0, done, h, a_last, B, T, row);
+  return launch_status();
+}
+
+template <bool CPLX>
+int linrec_bwd(const float* a, int a_tinv, const float* h, const float* h0, const uint8_t* done,
+               const float* gh, const float* gh_last, float* gb, float* ga, float* gh0,
+               void* workspace, size_t workspace_bytes, int B, int T, int D, int conj_ops,
+               mxk_stream_t stream) {
+  if (!a || !h || !gh || !gb) return MXK_ERR_NULL;
+  if (int st = check_dims(B, T, D)) return st;
+  const int row = CPLX ? 2 * D : D;
+  const int min_align = CPLX ? 8 : 4;
+  for (const void* p : {(const void*)a, (const void*)h, (const void*)h0, (const void*)gh, (const void*)gh_last,
+                        (const void*)gb, (const void*)ga, (const void*)gh0, (const void*)workspace})
+    if (p && (reinterpret_cast<uintptr_t>(p) % min_align)) return MXK_ERR_ALIGN;
+  float* partial = nullptr;
+  if (ga && a_tinv) {
+    const size_t need = mxk_linrec_bwd_workspace_bytes(CPLX, 1, B, T, D);
+    if (!workspace || workspace_bytes < need) return MXK_ERR_WORKSPACE;
+    partial = static_cast<float*>(workspace);
+  }
+  const long long total = static_cast<long long>(B) * row;
+  const int w = pick_width(total, row, CPLX, {a, h, h0, gh, gh_last, gb, ga, gh0, workspace});
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* ga_full = a_tinv ? nullptr : ga;
+  if (w == 4)
+    linrec_bwd_kernel<CPLX, 4><<<blocks_for(total / 4), kBlock, 0, s>>>(a, a_tinv, h, h0, done, gh, gh_last, gb, ga_full, partial, gh0, B, T, row, conj_ops);
+  else
+    linrec_bwd_kernel<CPLX, CPLX ? 2 : 1><<<blocks_for(total / (CPLX ? 2 : 1)), kBlock, 0, s>>>(a, a_tinv, h, h0, done, gh, gh_last, gb, ga_full, partial, gh0, B, T, row, conj_ops);
+  if (int st = launch_status()) return st;
+  if (partial) {
+    reduce_rows_kernel<<<(row + kBlock - 1) / kBlock, kBlock, 0, s>>>(partial, ga, B, row);
+    return launch_status();
+  }
+  return MXK_OK;
+}
+
+}  // namespace
+}  // namespace mxk
+
+extern "C" {
+
+int mxk_linrec_f32_fwd(const float* a, int a_time_invariant, const float* b, const float* h0,
+                       const float* a0, const uint8_t* done, float* h, float* a_last,
+                       int B, int T, int D, mxk_stream_t stream) {
+  return mxk::linrec_fwd<false>(a, a_time_invariant, b, h0, a0, done, h, a_last, B, T, D, stream);
+}
+
+int mxk_linrec_c64_fwd(const float* a, int a_time_invariant, const float* b, const float* h0,
+                       const float* a0, const uint8_t* done, float* h, float* a_last,
+                       int B, int T, int D, mxk_stream_t stream) {
+  return mxk::linrec_fwd<true>(a, a_time_invariant, b, h0, a0, done, h, a_last, B, T, D, stream);
+}
+
+size_t mxk_linrec_bwd_workspace_bytes(int is_complex, int a_time_invariant, int B, int T, int D) {
+  (void)T;
+  if (!a_time_invariant || B <= 0 || D <= 0) return 0;
+  return static_cast<size_t>(B) * D * (is_complex ? 2 : 1) * sizeof(float);
+}
+
+int mxk_linrec_f32_bwd(const float* a, int a_time_invariant, const float* h, const float* h0,
+                       const uint8_t* done, const float* gh, const float* gh_last, float* gb,
+                       float* ga, float* gh0, void* workspace, size_t workspace_bytes,
+                       int B, int T, int D, mxk_stream_t stream) {
+  return mxk::linrec_bwd<false>(a, a_time_invariant, h, h0, done, gh, gh_last, gb, ga, gh0, workspace,
+                                workspace_bytes, B, T, D, 0, stream);
+}
+
+int mxk_linrec_c64_bwd(const float* a, int a_time_invariant, const float* h, const float* h0,
+                       const uint8_t* done, const float* gh, const float* gh_last, float* gb,
+                       float* ga, float* gh0, void* workspace, size_t workspace_bytes,
+                       int B, int T, int D, int conjugate, mxk_stream_t stream) {
+  return mxk::linrec_bwd<true>(a, a_time_invariant, h, h0, done, gh, gh_last, gb, ga, gh0, workspace,
+                               workspace_bytes, B, T, D, conjugate, stream);
+}
+
+int mxk_loglinrec_f32_fwd(const float* ls, const float* d, const float* x0, const float* a0,
+                          const uint8_t* done, float* x, float* y, float* a_last,
+                          int B, int T, int D, mxk_stream_t stream) {
+  using namespace mxk;
+  if (!ls || !d || !x) return MXK_ERR_NULL;
+  if (int st = check_dims(B, T, D)) return st;
+  for (const void* p : {(const void*)ls, (const void*)d, (const void*)x0, (const void*)a0, (const void*)x, (const void*)y, (const void*)a_last})
+    if (p && (reinterpret_cast<uintptr_t>(p) % 4)) return MXK_ERR_ALIGN;
+  const long long total = static_cast<long long>(B) * D;
+  const int w = pick_width(total, D, false, {ls, d, x0, a0, x, y, a_last});
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (w == 4)
+    loglinrec_fwd_kernel<4><<<blocks_for(total / 4), kBlock, 0, s>>>(ls, d, x0, a0, done, x, y, a_last, B, T, D);
+  else
+    loglinrec_fwd_kernel<1><<<blocks_for(total), kBlock, 0, s>>>(ls, d, x0, a0, done, x, y, a_last, B, T, D);
+  return launch_status();
+}
+
+int mxk_loglinrec_f32_bwd(const float* d, const float* x, const float* x0, const uint8_t* done,
+                          const float* gx, const float* gy, const float* gx_last, float* gls,
+                          float* gd, float* gx0, int B, int T, int D, mxk_stream_t stream) {
+  using namespace mxk;
+  if (!d || !x || !gls || !gd || (!gx && !gy)) return MXK_ERR_NULL;
+  if (int st = check_dims(B, T, D)) return st;
+  for (const void* p : {(const void*)d, (const void*)x, (const void*)x0, (const void*)gx, (const void*)gy,
+                        (const void*)gx_last, (const void*)gls, (const void*)gd, (const void*)gx0})
+    if (p && (reinterpret_cast<uintptr_t>(p) % 4)) return MXK_ERR_ALIGN;
+  const long long total = static_cast<long long>(B) * D;
+  const int w = pick_width(total, D, false, {d, x, x0, gx, gy, gx_last, gls, gd, gx0});
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (w == 4)
+    loglinrec_bwd_kernel<4><<<blocks_for(total / 4), kBlock, 0, s>>>(d, x, x0, done, gx, gy, gx_last, gls, gd, gx0, B, T, D);
+  else
+    loglinrec_bwd_kernel<1><<<blocks_for(total), kBlock, 0, s>>>(d, x, x0, done, gx, gy, gx_last, gls, gd, gx0, B, T, D);
+  return launch_status();
+}
+
+}  // extern "C"

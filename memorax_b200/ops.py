@@ -1,0 +1,159 @@
+"""PyTorch-facing wrappers of the mxk C-ABI: raw launches on device tensors and
+``torch.autograd.Function`` classes that mirror a ``custom_vjp`` split (the
+forward returns residuals, the backward consumes cotangents).
+
+PyTorch is plumbing only (device memory, streams).  Every function here ends
+in a call through ``include/mxk.h``; nothing falls back to PyTorch math.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+
+# ------------------------------------------------------------------ helpers
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dev(t, dtype, name):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (memorax_b200 has no CPU path)")
+    if t.dtype != dtype:
+        t = t.to(dtype)
+    return t.contiguous()
+
+
+def _done_bytes(done):
+    """(B,T) flags of any dtype -> contiguous uint8 on the device (bool is reinterpreted)."""
+    if done is None:
+        return None
+    if not done.is_cuda:
+        raise ValueError("done must be a CUDA tensor")
+    if done.dtype == torch.bool:
+        return done.contiguous().view(torch.uint8)
+    if done.dtype == torch.uint8:
+        return done.contiguous()
+    return (done != 0).contiguous().view(torch.uint8)
+
+
+# ------------------------------------------------- diagonal linear recurrence
+def linrec_fwd(a, b, h0=None, a0=None, done=None, want_decay=True):
+    """h_t = done_t ? b_t : a_t h_{t-1} + b_t over (B,T,D); ``a`` is (B,T,D) or a
+    time-invariant (D,).  Returns ``(h, a_last)`` (a_last None unless wanted).
+    float32 or complex64, chosen by ``b.dtype``."""
+    cplx = b.is_complex()
+    dt = torch.complex64 if cplx else torch.float32
+    b = _dev(b, dt, "b")
+    a = _dev(a, dt, "a")
+    h0, a0 = _dev(h0, dt, "h0"), _dev(a0, dt, "a0")
+    bsz, steps, dim = b.shape
+    tinv = a.dim() == 1
+    if tinv:
+        assert a.shape == (dim,)
+    else:
+        assert a.shape == b.shape
+    h = torch.empty_like(b)
+    a_last = torch.empty(bsz, dim, dtype=dt, device=b.device) if want_decay else None
+    fn = "mxk_linrec_c64_fwd" if cplx else "mxk_linrec_f32_fwd"
+    _lib.call(fn, _ptr(a), int(tinv), _ptr(b), _ptr(h0), _ptr(a0), _ptr(_done_bytes(done)), _ptr(h),
+              _ptr(a_last), bsz, steps, dim, _stream())
+    return h, a_last
+
+
+def linrec_bwd(a, h, h0, done, gh, gh_last=None, need_ga=True, need_gh0=True, conjugate=False):
+    """Cotangents ``(gb, ga, gh0)`` of :func:`linrec_fwd`.  For complex inputs the
+    cotangents are in JAX's convention unless ``conjugate`` (torch's)."""
+    cplx = h.is_complex()
+    dt = torch.complex64 if cplx else torch.float32
+    a, h, gh = _dev(a, dt, "a"), _dev(h, dt, "h"), _dev(gh, dt, "gh")
+    h0, gh_last = _dev(h0, dt, "h0"), _dev(gh_last, dt, "gh_last")
+    bsz, steps, dim = h.shape
+    tinv = a.dim() == 1
+    gb = torch.empty_like(h)
+    ga = (torch.empty_like(a) if need_ga else None)
+    gh0 = torch.empty(bsz, dim, dtype=dt, device=h.device) if need_gh0 else None
+    ws, ws_bytes = None, 0
+    if need_ga and tinv:
+        ws_bytes = _lib.lib.mxk_linrec_bwd_workspace_bytes(int(cplx), 1, bsz, steps, dim)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=h.device)
+    args = [_ptr(a), int(tinv), _ptr(h), _ptr(h0), _ptr(_done_bytes(done)), _ptr(gh), _ptr(gh_last), _ptr(gb),
+            _ptr(ga), _ptr(gh0), _ptr(ws), ws_bytes, bsz, steps, dim]
+    if cplx:
+        _lib.call("mxk_linrec_c64_bwd", *args, int(conjugate), _stream())
+    else:
+        _lib.call("mxk_linrec_f32_bwd", *args, _stream())
+    return gb, ga, gh0
+
+
+class LinRec(torch.autograd.Function):
+    """(a, b, h0, a0, done) -> (h, a_last).  ``a_last`` (the decay leaf of the
+    next carry) is returned for state parity with memoroid.py:89 but carries no
+    gradient: no read-out in the reference consumes it."""
+
+    @staticmethod
+    def forward(ctx, a, b, h0, a0, done):
+        h, a_last = linrec_fwd(a, b, h0, a0, done, want_decay=True)
+        ctx.save_for_backward(a, h, h0, done)
+        ctx.mark_non_differentiable(a_last)
+        return h, a_last
+
+    @staticmethod
+    def backward(ctx, gh, _ga_last):
+        a, h, h0, done = ctx.saved_tensors
+        need_a, need_b, need_h0 = ctx.needs_input_grad[0], ctx.needs_input_grad[1], ctx.needs_input_grad[2]
+        gb, ga, gh0 = linrec_bwd(a, h, h0, done, gh.contiguous(), None, need_ga=need_a,
+                                 need_gh0=need_h0 and h0 is not None, conjugate=True)
+        return ga, (gb if need_b else None), gh0, None, None
+
+
+# --------------------------------------------------------- log-space (MinGRU)
+def loglinrec_fwd(ls, d, x0=None, a0=None, done=None, want_y=True, want_decay=True):
+    ls, d = _dev(ls, torch.float32, "ls"), _dev(d, torch.float32, "d")
+    x0, a0 = _dev(x0, torch.float32, "x0"), _dev(a0, torch.float32, "a0")
+    bsz, steps, dim = ls.shape
+    x = torch.empty_like(ls)
+    y = torch.empty_like(ls) if want_y else None
+    a_last = torch.empty(bsz, dim, dtype=torch.float32, device=ls.device) if want_decay else None
+    _lib.call("mxk_loglinrec_f32_fwd", _ptr(ls), _ptr(d), _ptr(x0), _ptr(a0), _ptr(_done_bytes(done)), _ptr(x),
+              _ptr(y), _ptr(a_last), bsz, steps, dim, _stream())
+    return x, y, a_last
+
+
+def loglinrec_bwd(d, x, x0, done, gx=None, gy=None, gx_last=None, need_gx0=True):
+    d, x = _dev(d, torch.float32, "d"), _dev(x, torch.float32, "x")
+    x0, gx, gy = _dev(x0, torch.float32, "x0"), _dev(gx, torch.float32, "gx"), _dev(gy, torch.float32, "gy")
+    gx_last = _dev(gx_last, torch.float32, "gx_last")
+    bsz, steps, dim = x.shape
+    gls, gd = torch.empty_like(x), torch.empty_like(x)
+    gx0 = torch.empty(bsz, dim, dtype=torch.float32, device=x.device) if need_gx0 else None
+    _lib.call("mxk_loglinrec_f32_bwd", _ptr(d), _ptr(x), _ptr(x0), _ptr(_done_bytes(done)), _ptr(gx), _ptr(gy),
+              _ptr(gx_last), _ptr(gls), _ptr(gd), _ptr(gx0), bsz, steps, dim, _stream())
+    return gls, gd, gx0
+
+
+class LogLinRec(torch.autograd.Function):
+    """(ls, d, x0, a0, done) -> (x, y = exp(x), a_last)."""
+
+    @staticmethod
+    def forward(ctx, ls, d, x0, a0, done):
+        x, y, a_last = loglinrec_fwd(ls, d, x0, a0, done)
+        ctx.save_for_backward(d, x, x0, done)
+        ctx.mark_non_differentiable(a_last)
+        return x, y, a_last
+
+    @staticmethod
+    def backward(ctx, gx, gy, _ga_last):
+        d, x, x0, done = ctx.saved_tensors
+        gls, gd, gx0 = loglinrec_bwd(d, x, x0, done, gx.contiguous(), gy.contiguous(), None,
+                                     need_gx0=x0 is not None and ctx.needs_input_grad[2])
+        return gls, gd, gx0, None, None
