@@ -120,6 +120,30 @@ int mxk_loglinrec_f32_bwd(const float* d, const float* x, const float* x0, const
                           const float* gx, const float* gy, const float* gx_last, float* gls,
                           float* gd, float* gx0, int B, int T, int D, mxk_stream_t stream);
 
+/* ---------------------------------------------------------------------------
+ * Chunked causal linear attention with carried state (linear_attention.py:58-124
+ * under Memoroid.scan_fn): per head, S_t = [!done_t] S_{t-1} + v_t phi(k_t)^T,
+ * z_t = [!done_t] z_{t-1} + phi(k_t), o_t = S_t phi(q_t) / max(phi(q_t).z_t, eps),
+ * phi = elu + 1 when feature_map != 0 (else q, k are used as given).
+ * The reference materialises every S_t; here the state is carried chunk to
+ * chunk (64 tokens) in fp32 and only (B,H,d,d) ever touches memory.
+ *
+ *   q, k, v   (B,T,H,d) bf16, contiguous;  d = 64
+ *   s0        (B,H,d_v,d_k) fp32 carried S, NULL = zeros;  z0 (B,H,d_k), NULL = zeros
+ *   o         (B,T,H,d) bf16 out
+ *   s_last, z_last   next carry, optional
+ *   chunk_states  optional residual for the backward call,
+ *             mxk_linattn_chunk_states_bytes(...) bytes: the bf16 state entering
+ *             every chunk in tensor-core operand order
+ *   status    optional device int, set non-zero if a bounded device-side wait
+ *             gave up (results are then undefined)
+ * ------------------------------------------------------------------------- */
+size_t mxk_linattn_chunk_states_bytes(int B, int T, int H, int d);
+int mxk_linattn_bf16_fwd(const void* q, const void* k, const void* v, const float* s0, const float* z0,
+                         const uint8_t* done, void* o, float* s_last, float* z_last, void* chunk_states,
+                         int* status, int B, int T, int H, int d, float eps, int feature_map,
+                         mxk_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

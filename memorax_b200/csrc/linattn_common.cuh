@@ -1,0 +1,48 @@
+// Constants and mask helpers shared by the linear-attention forward and
+// backward kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "mxk_common.cuh"
+#include "umma.cuh"
+
+namespace mxk {
+namespace linattn {
+
+constexpr int kC = 64;        // tokens per chunk
+constexpr int kD = 64;        // head dimension (d_k = d_v)
+constexpr int kDX = kD + 8;   // value columns + the normaliser column block
+constexpr int kThreads = 128;
+constexpr int kPanels = kD / 8;
+constexpr int kPanelsX = kDX / 8;
+constexpr uint32_t kOneBf16 = 0x3F80u;
+
+__device__ __forceinline__ float phi(float x) { return x > 0.f ? x + 1.f : __expf(x); }
+
+// 64 done flags of the chunk starting at t0 as a bit mask (bit i = token t0+i).
+__device__ __forceinline__ uint64_t chunk_done_mask(const uint8_t* drow, int t0, int T, int lane) {
+  if (!drow) return 0ull;
+  const int ta = t0 + lane, tb = t0 + 32 + lane;
+  const unsigned lo = __ballot_sync(0xffffffffu, ta < T && drow[ta] != 0);
+  const unsigned hi = __ballot_sync(0xffffffffu, tb < T && drow[tb] != 0);
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+__device__ __forceinline__ bool row_live(uint64_t dm, int i) { return (dm & ((2ull << i) - 1ull)) == 0ull; }
+__device__ __forceinline__ bool row_keep(uint64_t dm, int j) { return j >= 63 || (dm >> (j + 1)) == 0ull; }
+__device__ __forceinline__ int row_first_key(uint64_t dm, int i) {
+  const uint64_t m = dm & ((2ull << i) - 1ull);
+  return m ? 63 - __clzll(static_cast<long long>(m)) : 0;
+}
+
+// Vector `vid` (0..511) of a 64 x 64 bf16 tile: eight consecutive lanes take
+// eight different rows (conflict-free 16-byte shared stores) while a warp still
+// covers 64 contiguous bytes of every row it touches.
+__device__ __forceinline__ void tile_vec(int vid, int& row, int& seg) {
+  row = (vid & 7) + 8 * (vid >> 6);
+  seg = (vid >> 3) & 7;
+}
+
+
+}  // namespace linattn
+}  // namespace mxk

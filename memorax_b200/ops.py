@@ -157,3 +157,37 @@ class LogLinRec(torch.autograd.Function):
         gls, gd, gx0 = loglinrec_bwd(d, x, x0, done, gx.contiguous(), gy.contiguous(), None,
                                      need_gx0=x0 is not None and ctx.needs_input_grad[2])
         return gls, gd, gx0, None, None
+
+
+# ------------------------------------------------------- linear attention
+def _status_word(device):
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def _check_status(word, what):
+    if int(word.item()) != 0:
+        raise _lib.MxkError(what, int(word.item()), "a bounded device-side wait gave up")
+
+
+def linattn_fwd(q, k, v, s0=None, z0=None, done=None, eps=1e-6, feature_map=True, save_states=False,
+                check=False):
+    """Chunked causal linear attention; q, k, v are (B,T,H,64) bf16.  Returns
+    ``(o, s_last, z_last, chunk_states)`` (chunk_states None unless asked for)."""
+    q, k, v = (_dev(t, torch.bfloat16, n) for t, n in ((q, "q"), (k, "k"), (v, "v")))
+    s0, z0 = _dev(s0, torch.float32, "s0"), _dev(z0, torch.float32, "z0")
+    bsz, steps, heads, dim = q.shape
+    assert k.shape == q.shape and v.shape == q.shape
+    o = torch.empty_like(q)
+    s_last = torch.empty(bsz, heads, dim, dim, dtype=torch.float32, device=q.device)
+    z_last = torch.empty(bsz, heads, dim, dtype=torch.float32, device=q.device)
+    states = None
+    if save_states:
+        nbytes = _lib.lib.mxk_linattn_chunk_states_bytes(bsz, steps, heads, dim)
+        states = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    status = _status_word(q.device) if check else None
+    _lib.call("mxk_linattn_bf16_fwd", _ptr(q), _ptr(k), _ptr(v), _ptr(s0), _ptr(z0), _ptr(_done_bytes(done)),
+              _ptr(o), _ptr(s_last), _ptr(z_last), _ptr(states), _ptr(status), bsz, steps, heads, dim,
+              float(eps), int(feature_map), _stream())
+    if check:
+        _check_status(status, "mxk_linattn_bf16_fwd")
+    return o, s_last, z_last, states
