@@ -144,6 +144,18 @@ int mxk_linattn_bf16_fwd(const void* q, const void* k, const void* v, const floa
                          int* status, int B, int T, int H, int d, float eps, int feature_map,
                          mxk_stream_t stream);
 
+/* Reverse mode of mxk_linattn_bf16_fwd (what jax.grad derives from the scan and
+ * read-out; the clamp max(den, eps) passes no gradient where it is active).
+ *   d_o       (B,T,H,d) bf16 cotangent of o
+ *   chunk_states  the residual written by the forward call on the same inputs
+ *   ds_last, dz_last  cotangents of the next carry, NULL = zeros
+ *   dq, dk, dv  (B,T,H,d) bf16 out;  ds0 (B,H,d,d), dz0 (B,H,d) fp32 out, optional
+ * `done` has no cotangent. */
+int mxk_linattn_bf16_bwd(const void* q, const void* k, const void* v, const void* d_o, const void* chunk_states,
+                         const uint8_t* done, const float* ds_last, const float* dz_last, void* dq, void* dk,
+                         void* dv, float* ds0, float* dz0, int* status, int B, int T, int H, int d, float eps,
+                         int feature_map, mxk_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,382 @@
+// Backward of chunked causal linear attention on the sm_100a tensor cores.
+//
+// One CTA owns one (batch, head) sequence and walks its 64-token chunks right
+// to left, carrying G^T = (dL/dS)^T with gz = dL/dz as one extra column in
+// tensor memory (fp32).  The state entering each chunk comes from the forward
+// call's residual (bf16, already in operand order).  Per chunk, with
+// D_i = max(den_i, eps), c_i = [den_i > eps]:
+//   phase 1 (independent MMAs):  P = phi(Q) phi(K)^T,  dA = dO V^T,  R = dO S_in
+//   epilogue 1 (one thread per query row):
+//     den_i  = sum_j M_ij P_ij + live_i phi(q_i).z_in
+//     don_i  = sum_j M_ij P_ij dA_ij + live_i phi(q_i).R_i          (= do_i . num_i)
+//     dden_i = -c_i don_i / D_i^2
+//     Pn_ij  = M_ij P_ij / D_i          dP_ij = M_ij (dA_ij / D_i + dden_i)
+//     dOs_i  = live_i [do_i / D_i | dden_i]
+//   phase 2:  dphiQ = dP phi(K) + dOs [S_in | z_in]
+//             dphiK = dP^T phi(Q) + keep [V | 1] [G | gz]^T
+//             dV    = Pn^T dO + keep phi(K) G^T
+//             [G|gz]^T = [no reset] [G|gz]^T + phi(Q)^T dOs
+//   epilogue 2: dq = dphiQ * phi'(q), dk = dphiK * phi'(k), dv; refresh the
+//   bf16 operand copy of G.
+#include <cuda_bf16.h>
+
+#include "linattn_common.cuh"
+#include "mxk_common.cuh"
+
+namespace mxk {
+namespace {
+
+using namespace umma;
+using namespace linattn;
+
+constexpr int kPanelsK = kPanels + 2;  // 80 columns: a K = 80 contraction needs whole K=16 steps
+
+struct BwdParams {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  const __nv_bfloat16* d_o;
+  const uint4* chunk_states;
+  const uint8_t* done;
+  const float* ds_last;
+  const float* dz_last;
+  __nv_bfloat16* dq;
+  __nv_bfloat16* dk;
+  __nv_bfloat16* dv;
+  float* ds0;
+  float* dz0;
+  int* status;
+  int B, T, H;
+  float eps;
+  int feature_map;
+};
+
+struct BwdSmem {
+  uint4 q[kPanels * kC];      // phi(Q)                 [k/8][i]
+  uint4 k[kPanels * kC];      // phi(K)                 [k/8][j]
+  uint4 kk[kPanels * kC];     // keep rows of phi(K)
+  uint4 v[kPanels * kC];      // V                      [v/8][j]
+  uint4 vk[kPanelsK * kC];    // keep rows of V | 1 | 0 [v/8][j]
+  uint4 d_o[kPanels * kC];    // dO                     [v/8][i]
+  uint4 dos[kPanelsK * kC];   // live rows of dO/D | dden | 0
+  uint4 s[kPanelsK * kD];     // S_in^T | z_in | 0      [v/8][k]
+  uint4 g[kPanelsK * kD];     // G^T | gz | 0           [v/8][k]
+  uint4 pn[kPanels * kC];     // P / D                  [j/8][i]
+  uint4 dp[kPanels * kC];     // dP                     [j/8][i]
+  uint64_t bar[2];
+  uint32_t tmem;
+};
+
+constexpr uint32_t kBwdTmemCols = 512;
+constexpr uint32_t kColP = 0, kColA = 64, kColR = 128, kColDQ = 192, kColDK = 256, kColDV = 320, kColG = 384;
+
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+
+__global__ void __launch_bounds__(kThreads) linattn_bwd_kernel(const BwdParams p) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  BwdSmem& sm = *reinterpret_cast<BwdSmem*>(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
+  const int row = warp * 16 + (lane & 15);
+  const bool row_active = lane < 16;
+  const int nchunks = (p.T + kC - 1) / kC;
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
+
+  if (tid == 0) {
+    mbar_init(&sm.bar[0], 1);
+    mbar_init(&sm.bar[1], 1);
+    mbar_init_fence();
+  }
+  if (warp == 0) tmem_alloc(&sm.tmem, kBwdTmemCols);
+  // zero padding panels that never change (columns 72..79 of the 80-wide operands)
+  if (tid < kC) {
+    sm.vk[(kPanelsK - 1) * kC + tid] = zero4;
+    sm.dos[(kPanelsK - 1) * kC + tid] = zero4;
+    sm.s[(kPanelsK - 1) * kD + tid] = zero4;
+    sm.g[(kPanelsK - 1) * kD + tid] = zero4;
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = sm.tmem;
+  const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+
+  // Cotangent of the next carry -> TMEM and its bf16 operand copy (thread `row`
+  // owns G^T[row][.] = dS[.][row]).
+  {
+    const float* gs = p.ds_last ? p.ds_last + static_cast<size_t>(bh) * kD * kD : nullptr;
+    const float* gz = p.dz_last ? p.dz_last + static_cast<size_t>(bh) * kD : nullptr;
+#pragma unroll
+    for (int pn = 0; pn < kPanelsX; ++pn) {
+      float vals[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int vcol = pn * 8 + e;
+        float x = 0.f;
+        if (row_active) {
+          if (vcol < kD) x = gs ? gs[vcol * kD + row] : 0.f;
+          else if (vcol == kD) x = gz ? gz[row] : 0.f;
+        }
+        vals[e] = x;
+      }
+      tmem_st8(lane_base + kColG + pn * 8, vals);
+      if (row_active) sm.g[pn * kD + row] = pack8_bf16(vals);
+    }
+    tmem_st_wait();
+  }
+
+  const size_t stride_t = static_cast<size_t>(p.H) * kD;
+  const size_t seq_base = (static_cast<size_t>(b) * p.T * p.H + h) * kD;
+  const uint8_t* drow = p.done ? p.done + static_cast<size_t>(b) * p.T : nullptr;
+  const uint32_t id_kk = idesc_bf16(kC, kC, false, false);   // A, B contract over columns
+  const uint32_t id_km = idesc_bf16(kC, kC, false, true);    // B contracts over rows
+  const uint32_t id_mm = idesc_bf16(kC, kC, true, true);
+  const uint32_t id_g = idesc_bf16(kD, kDX, true, true);
+  bool timed_out = false;
+
+  for (int it = 0; it < nchunks; ++it) {
+    const int c = nchunks - 1 - it;
+    const int t0 = c * kC;
+    const int valid = min(kC, p.T - t0);
+    const uint64_t dm = chunk_done_mask(drow, t0, p.T, lane);
+    const bool has_reset = dm != 0ull;
+
+    // ---- stage phi(Q), phi(K), V, dO, S_in ----
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      int trow, seg;
+      tile_vec(r * kThreads + tid, trow, seg);
+      const size_t g = seq_base + static_cast<size_t>(t0 + trow) * stride_t + seg * 8;
+      uint4 qv = zero4, kv = zero4, vv = zero4, gv = zero4;
+      if (trow < valid) {
+        qv = __ldg(reinterpret_cast<const uint4*>(p.q + g));
+        kv = __ldg(reinterpret_cast<const uint4*>(p.k + g));
+        vv = __ldg(reinterpret_cast<const uint4*>(p.v + g));
+        gv = __ldg(reinterpret_cast<const uint4*>(p.d_o + g));
+        if (p.feature_map) {
+          float f[8];
+          unpack8_bf16(qv, f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = phi(f[e]);
+          qv = pack8_bf16(f);
+          unpack8_bf16(kv, f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = phi(f[e]);
+          kv = pack8_bf16(f);
+        }
+      }
+      const int slot = seg * kC + trow;
+      const bool keep = row_keep(dm, trow);
+      sm.q[slot] = qv;
+      sm.k[slot] = kv;
+      sm.kk[slot] = keep ? kv : zero4;
+      sm.v[slot] = vv;
+      sm.vk[slot] = keep ? vv : zero4;
+      sm.d_o[slot] = gv;
+    }
+    if (tid < kC) sm.vk[kPanels * kC + tid] = make_uint4((tid < valid && row_keep(dm, tid)) ? kOneBf16 : 0u, 0, 0, 0);
+    {
+      const uint4* src = p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * (kPanelsX * kD);
+      for (int i = tid; i < kPanelsX * kD; i += kThreads) sm.s[i] = __ldg(src + i);
+    }
+    fence_smem_to_async();
+    fence_before_sync();
+    __syncthreads();
+
+    if (tid == 0) {
+      fence_after_sync();
+      const Operand aq{smem_u32(sm.q), kC, false}, bk{smem_u32(sm.k), kC, false};
+      const Operand ado{smem_u32(sm.d_o), kC, false}, bv{smem_u32(sm.v), kC, false};
+      const Operand bs{smem_u32(sm.s), kD, false};
+      gemm(tmem + kColP, aq, bk, id_kk, kD / 16, false);
+      gemm(tmem + kColA, ado, bv, id_kk, kD / 16, false);
+      gemm(tmem + kColR, ado, bs, id_kk, kD / 16, false);
+      commit(&sm.bar[0]);
+    }
+    if (!mbar_wait(&sm.bar[0], it & 1)) timed_out = true;
+    fence_after_sync();
+
+    // ---- epilogue 1: row statistics, dP, P/D, scaled dO ----
+    {
+      const bool live = row_live(dm, row);
+      float s_dot = 0.f, z_dot = 0.f;
+      {
+        float rrow[kD];
+        tmem_ld_row<kD>(lane_base + kColR, rrow);
+#pragma unroll
+        for (int pn = 0; pn < kPanels; ++pn) {
+          float fq[8];
+          unpack8_bf16(sm.q[pn * kC + row], fq);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int kk = pn * 8 + e;
+            s_dot = fmaf(fq[e], rrow[kk], s_dot);
+            z_dot = fmaf(fq[e], bf16_lo(sm.s[kPanels * kD + kk].x), z_dot);
+          }
+        }
+      }
+      float prow[kC], arow[kC];
+      tmem_ld_row<kC>(lane_base + kColP, prow);
+      tmem_ld_row<kC>(lane_base + kColA, arow);
+      const int lo = row_first_key(dm, row);
+      float den = live ? z_dot : 0.f, don = live ? s_dot : 0.f;
+#pragma unroll
+      for (int j = 0; j < kC; ++j) {
+        const bool m = (j >= lo && j <= row);
+        prow[j] = m ? prow[j] : 0.f;
+        den += prow[j];
+        don = fmaf(prow[j], arow[j], don);
+      }
+      const float dcl = fmaxf(den, p.eps);
+      const float inv = 1.f / dcl;
+      const float dden = den > p.eps ? -don * inv * inv : 0.f;
+      if (row_active) {
+#pragma unroll
+        for (int jp = 0; jp < kPanels; ++jp) {
+          float a[8], bq[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int j = jp * 8 + e;
+            const bool m = (j >= lo && j <= row);
+            a[e] = prow[j] * inv;
+            bq[e] = m ? fmaf(arow[j], inv, dden) : 0.f;
+          }
+          sm.pn[jp * kC + row] = pack8_bf16(a);
+          sm.dp[jp * kC + row] = pack8_bf16(bq);
+        }
+        const float sc = live ? inv : 0.f;
+#pragma unroll
+        for (int pn = 0; pn < kPanels; ++pn) {
+          float f[8];
+          unpack8_bf16(sm.d_o[pn * kC + row], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] *= sc;
+          sm.dos[pn * kC + row] = pack8_bf16(f);
+        }
+        sm.dos[kPanels * kC + row] = make_uint4(pack_bf16(live ? dden : 0.f, 0.f), 0, 0, 0);
+      }
+    }
+    fence_smem_to_async();
+    fence_before_sync();
+    __syncthreads();
+
+    if (tid == 0) {
+      fence_after_sync();
+      // dphiQ = dP phi(K) + dOs [S|z]
+      gemm(tmem + kColDQ, Operand{smem_u32(sm.dp), kC, false}, Operand{smem_u32(sm.k), kC, true}, id_km, kC / 16, false);
+      gemm(tmem + kColDQ, Operand{smem_u32(sm.dos), kC, false}, Operand{smem_u32(sm.s), kD, false}, id_kk, 5, true);
+      // dphiK = dP^T phi(Q) + keep[V|1] [G|gz]^T
+      gemm(tmem + kColDK, Operand{smem_u32(sm.dp), kC, true}, Operand{smem_u32(sm.q), kC, true}, id_mm, kC / 16, false);
+      gemm(tmem + kColDK, Operand{smem_u32(sm.vk), kC, false}, Operand{smem_u32(sm.g), kD, false}, id_kk, 5, true);
+      // dV = (P/D)^T dO + keep phi(K) G^T
+      gemm(tmem + kColDV, Operand{smem_u32(sm.pn), kC, true}, Operand{smem_u32(sm.d_o), kC, true}, id_mm, kC / 16, false);
+      gemm(tmem + kColDV, Operand{smem_u32(sm.kk), kC, false}, Operand{smem_u32(sm.g), kD, true}, id_km, kD / 16, true);
+      // [G|gz]^T = [no reset][G|gz]^T + phi(Q)^T dOs
+      gemm(tmem + kColG, Operand{smem_u32(sm.q), kC, true}, Operand{smem_u32(sm.dos), kC, true}, id_g, kC / 16, !has_reset);
+      commit(&sm.bar[1]);
+    }
+    if (!mbar_wait(&sm.bar[1], it & 1)) timed_out = true;
+    fence_after_sync();
+
+    // ---- epilogue 2: chain through phi', store, refresh the operand copy of G ----
+    {
+      const bool store = row_active && row < valid;
+      const size_t g = seq_base + static_cast<size_t>(t0 + row) * stride_t;
+      float acc[kD];
+      tmem_ld_row<kD>(lane_base + kColDQ, acc);
+      if (store) {
+        uint4* dst = reinterpret_cast<uint4*>(p.dq + g);
+#pragma unroll
+        for (int pn = 0; pn < kPanels; ++pn) {
+          float f[8];
+          unpack8_bf16(sm.q[pn * kC + row], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = acc[pn * 8 + e] * ((p.feature_map && f[e] <= 1.f) ? f[e] : 1.f);
+          dst[pn] = pack8_bf16(f);
+        }
+      }
+      tmem_ld_row<kD>(lane_base + kColDK, acc);
+      if (store) {
+        uint4* dst = reinterpret_cast<uint4*>(p.dk + g);
+#pragma unroll
+        for (int pn = 0; pn < kPanels; ++pn) {
+          float f[8];
+          unpack8_bf16(sm.k[pn * kC + row], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = acc[pn * 8 + e] * ((p.feature_map && f[e] <= 1.f) ? f[e] : 1.f);
+          dst[pn] = pack8_bf16(f);
+        }
+      }
+      tmem_ld_row<kD>(lane_base + kColDV, acc);
+      if (store) {
+        uint4* dst = reinterpret_cast<uint4*>(p.dv + g);
+#pragma unroll
+        for (int pn = 0; pn < kPanels; ++pn) dst[pn] = pack8_bf16(acc + pn * 8);
+      }
+      float grow[kDX];
+      tmem_ld_row<kDX>(lane_base + kColG, grow);
+      if (row_active) {
+#pragma unroll
+        for (int pn = 0; pn < kPanelsX; ++pn) sm.g[pn * kD + row] = pack8_bf16(grow + pn * 8);
+        if (c == 0) {
+          if (p.ds0) {
+            float* dst = p.ds0 + static_cast<size_t>(bh) * kD * kD;
+#pragma unroll
+            for (int vcol = 0; vcol < kD; ++vcol) dst[vcol * kD + row] = grow[vcol];
+          }
+          if (p.dz0) p.dz0[static_cast<size_t>(bh) * kD + row] = grow[kD];
+        }
+      }
+    }
+  }
+
+  if (timed_out && p.status) atomicExch(p.status, 1);
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kBwdTmemCols);
+}
+
+}  // namespace
+}  // namespace mxk
+
+extern "C" {
+
+int mxk_linattn_bf16_bwd(const void* q, const void* k, const void* v, const void* d_o, const void* chunk_states,
+                         const uint8_t* done, const float* ds_last, const float* dz_last, void* dq, void* dk,
+                         void* dv, float* ds0, float* dz0, int* status, int B, int T, int H, int d, float eps,
+                         int feature_map, mxk_stream_t stream) {
+  using namespace mxk;
+  using namespace mxk::linattn;
+  if (!q || !k || !v || !d_o || !chunk_states || !dq || !dk || !dv) return MXK_ERR_NULL;
+  if (B <= 0 || T <= 0 || H <= 0 || static_cast<long long>(B) * H > 0x7fffffffLL) return MXK_ERR_DIMS;
+  if (d != kD) return MXK_ERR_UNSUPPORTED;
+  for (const void* ptr : {q, k, v, d_o, chunk_states, (const void*)dq, (const void*)dk, (const void*)dv})
+    if (!aligned16(ptr)) return MXK_ERR_ALIGN;
+  for (const void* ptr : {(const void*)ds_last, (const void*)dz_last, (const void*)ds0, (const void*)dz0})
+    if (ptr && (reinterpret_cast<uintptr_t>(ptr) & 3u)) return MXK_ERR_ALIGN;
+  BwdParams prm;
+  prm.q = static_cast<const __nv_bfloat16*>(q);
+  prm.k = static_cast<const __nv_bfloat16*>(k);
+  prm.v = static_cast<const __nv_bfloat16*>(v);
+  prm.d_o = static_cast<const __nv_bfloat16*>(d_o);
+  prm.chunk_states = static_cast<const uint4*>(chunk_states);
+  prm.done = done;
+  prm.ds_last = ds_last;
+  prm.dz_last = dz_last;
+  prm.dq = static_cast<__nv_bfloat16*>(dq);
+  prm.dk = static_cast<__nv_bfloat16*>(dk);
+  prm.dv = static_cast<__nv_bfloat16*>(dv);
+  prm.ds0 = ds0;
+  prm.dz0 = dz0;
+  prm.status = status;
+  prm.B = B; prm.T = T; prm.H = H;
+  prm.eps = eps;
+  prm.feature_map = feature_map;
+  cudaError_t e = cudaFuncSetAttribute(linattn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(sizeof(BwdSmem)));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  linattn_bwd_kernel<<<B * H, kThreads, sizeof(BwdSmem), static_cast<cudaStream_t>(stream)>>>(prm);
+  return launch_status();
+}
+
+}  // extern "C"

@@ -1,0 +1,217 @@
+"""Host-side mirror of memorax's sequence-model interface for the scan path.
+
+Same names, call signatures and carry pytrees as
+``memorax/networks/sequence_models/{sequence_model,memoroid,lru,min_gru,
+linear_attention}.py``; the time-axis scan that the reference runs with
+``jax.lax.associative_scan`` is one fused CUDA launch through the C-ABI here.
+
+* ``SequenceModel.__call__(inputs, done, initial_carry=None) -> (next_carry, y)``
+  and ``initialize_carry(key, input_shape)`` (sequence_model.py:8-19);
+* ``MemoroidCellBase``: ``__call__(x) -> z``, ``binary_operator(a, b)``,
+  ``read(h, x) -> y``, ``initialize_carry`` (memoroid.py:20-54);
+* ``Memoroid(cell)`` (memoroid.py:57-112): ``z = cell(x)``; scan; ``y = read``.
+
+Carries keep the reference's singleton time axis: ``(B, 1, ...)``.
+
+Two deliberate differences, both forced by not materialising O(T d^2) data:
+the linear-attention and delta-rule cells emit *factored* elements (k, v, ...)
+instead of per-step outer products, and their ``scan`` returns the read-out
+together with the last state (the reference's ``read`` over every S_t is
+fused into the kernel).  ``binary_operator`` is kept on every cell as the
+algebraic definition (used by the tests); the product path never calls it.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+from torch import nn
+
+from . import ops
+
+
+def get_input_shape(inputs):
+    """(B, T, F) -> (B, F)   (utils/axes.py:46-49)."""
+    return inputs.shape[:1] + inputs.shape[2:]
+
+
+class SequenceModel(nn.Module):
+    def forward(self, inputs, done, initial_carry=None, **kwargs):
+        raise NotImplementedError
+
+    def initialize_carry(self, key, input_shape):
+        raise NotImplementedError
+
+
+class MemoroidCellBase(nn.Module):
+    """Plugin protocol of a cell (memoroid.py:20-54) plus ``scan``, the fused
+    replacement of ``Memoroid.scan_fn`` + ``read`` for this cell."""
+
+    def forward(self, x, **kwargs):
+        raise NotImplementedError
+
+    def binary_operator(self, a, b):
+        raise NotImplementedError
+
+    def read(self, h, x, **kwargs):
+        raise NotImplementedError
+
+    def initialize_carry(self, key, input_shape):
+        raise NotImplementedError
+
+    def scan(self, z, initial_carry, done, inputs):
+        """-> (next_carry, y)"""
+        raise NotImplementedError
+
+
+class Memoroid(SequenceModel):
+    def __init__(self, cell: MemoroidCellBase):
+        super().__init__()
+        self.cell = cell
+
+    def forward(self, inputs, done, initial_carry=None, **kwargs):
+        if initial_carry is None:
+            initial_carry = self.cell.initialize_carry(None, get_input_shape(inputs))
+            initial_carry = tuple(c.to(inputs.device) for c in initial_carry)
+        z = self.cell(inputs, **kwargs)
+        next_carry, y = self.cell.scan(z, initial_carry, done, inputs)
+        return next_carry, y
+
+    def initialize_carry(self, key, input_shape):
+        return self.cell.initialize_carry(key, input_shape)
+
+
+# ---------------------------------------------------------------------- LRU
+class LRUCell(MemoroidCellBase):
+    """Complex diagonal linear recurrence with time-invariant decay (lru.py:32-108)."""
+
+    def __init__(self, features, hidden_dim, r_min=0.0, r_max=1.0, max_phase=6.28):
+        super().__init__()
+        self.features, self.hidden_dim = features, hidden_dim
+        u1, u2 = torch.rand(hidden_dim), torch.rand(hidden_dim)
+        self.nu_log = nn.Parameter(torch.log(-0.5 * torch.log(u1 * (r_max ** 2 - r_min ** 2) + r_min ** 2)))
+        self.theta_log = nn.Parameter(torch.log(max_phase * u2))
+        lam_abs = torch.exp(-torch.exp(self.nu_log.detach()))
+        self.gamma_log = nn.Parameter(torch.log(torch.sqrt(1 - lam_abs ** 2)))
+        self.B_real = nn.Parameter(torch.randn(hidden_dim, features) / math.sqrt(2 * features))
+        self.B_imag = nn.Parameter(torch.randn(hidden_dim, features) / math.sqrt(2 * features))
+        self.C_real = nn.Parameter(torch.randn(features, hidden_dim) / math.sqrt(hidden_dim))
+        self.C_imag = nn.Parameter(torch.randn(features, hidden_dim) / math.sqrt(hidden_dim))
+        self.D = nn.Parameter(torch.randn(features))
+
+    def diag_lambda(self):
+        return torch.exp(torch.complex(-torch.exp(self.nu_log), torch.exp(self.theta_log)))
+
+    def forward(self, x, **kwargs):
+        """-> (state (B,T,H) complex64, decay (H,)): the decay is one lambda for
+        every (b, t) (lru.py:86), so it is passed un-broadcast."""
+        b_norm = torch.complex(self.B_real, self.B_imag) * torch.exp(self.gamma_log)[:, None]
+        state = torch.matmul(x.to(torch.complex64), b_norm.t())
+        return state, self.diag_lambda()
+
+    def binary_operator(self, a, b):
+        s_i, a_i = a
+        s_j, a_j = b
+        return a_j * s_i + s_j, a_j * a_i
+
+    def read(self, h, x, **kwargs):
+        state, _ = h
+        c = torch.complex(self.C_real, self.C_imag)
+        return torch.matmul(state, c.t()).real + self.D * x
+
+    def initialize_carry(self, key, input_shape):
+        *batch, _ = input_shape
+        return (torch.zeros(*batch, 1, self.hidden_dim, dtype=torch.complex64),
+                torch.ones(*batch, 1, self.hidden_dim, dtype=torch.complex64))
+
+    def scan(self, z, initial_carry, done, inputs):
+        state, lam = z
+        h0, a0 = initial_carry
+        h, a_last = ops.LinRec.apply(lam, state.contiguous(), h0[:, 0].contiguous(), a0[:, 0].contiguous(), done)
+        y = self.read((h, None), inputs)
+        return (h[:, -1:], a_last[:, None]), y
+
+
+# ------------------------------------------------------------------- MinGRU
+class MinGRUCell(MemoroidCellBase):
+    """Log-space minimal GRU (min_gru.py:14-90)."""
+
+    def __init__(self, features, in_features=None):
+        super().__init__()
+        self.features = features
+        in_features = in_features or features
+        self.z = nn.Linear(in_features, features, bias=False)
+        self.h = nn.Linear(in_features, features, bias=False)
+
+    def forward(self, x, **kwargs):
+        z, h_tilde = self.z(x), self.h(x)
+        log_z = -torch.nn.functional.softplus(-z)
+        log_h = torch.where(h_tilde >= 0, torch.log(torch.relu(h_tilde) + 0.5),
+                            -torch.nn.functional.softplus(-h_tilde))
+        return log_z + log_h, -torch.nn.functional.softplus(z)
+
+    def binary_operator(self, a, b):
+        x_i, d_i = a
+        x_j, d_j = b
+        return torch.logaddexp(d_j + x_i, x_j), d_i + d_j
+
+    def read(self, h, x, **kwargs):
+        return torch.exp(h[0])
+
+    def initialize_carry(self, key, input_shape):
+        *batch, _ = input_shape
+        return (torch.full((*batch, 1, self.features), -float("inf")), torch.zeros(*batch, 1, self.features))
+
+    def scan(self, z, initial_carry, done, inputs):
+        log_state, decay = z
+        x0, a0 = initial_carry
+        x, y, a_last = ops.LogLinRec.apply(log_state.contiguous(), decay.contiguous(), x0[:, 0].contiguous(),
+                                           a0[:, 0].contiguous(), done)
+        return (x[:, -1:], a_last[:, None]), y
+
+
+# --------------------------------------------------------- linear attention
+class LinearAttentionCell(MemoroidCellBase):
+    """ELU+1 linear attention (linear_attention.py:14-124).  ``head_dim`` must be 64."""
+
+    def __init__(self, features, head_dim, num_heads, eps=1e-6, in_features=None):
+        super().__init__()
+        self.features, self.head_dim, self.num_heads, self.eps = features, head_dim, num_heads, eps
+        in_features = in_features or features
+        hidden = num_heads * head_dim
+        self.key = nn.Linear(in_features, hidden, bias=False)
+        self.value = nn.Linear(in_features, hidden, bias=False)
+        self.query = nn.Linear(in_features, hidden, bias=False)
+        self.norm = nn.RMSNorm(hidden)
+        self.output_projection = nn.Linear(hidden, features)
+
+    def _heads(self, t):
+        return t.view(*t.shape[:2], self.num_heads, self.head_dim)
+
+    def forward(self, x, **kwargs):
+        """-> factored elements (k, v) with k, v (B,T,H,hd): S_t = v_t (x) phi(k_t)
+        and z_t = phi(k_t) (linear_attention.py:75-80) are never materialised;
+        the feature map is applied inside the kernel."""
+        return self._heads(self.key(x)), self._heads(self.value(x))
+
+    def binary_operator(self, a, b):
+        return tuple(p + q for p, q in zip(a, b))
+
+    def read(self, h, x, **kwargs):
+        raise RuntimeError("the read-out over every S_t is fused into scan(); see the module docstring")
+
+    def initialize_carry(self, key, input_shape):
+        *batch, _ = input_shape
+        return (torch.zeros(*batch, 1, self.num_heads, self.head_dim, self.head_dim),
+                torch.zeros(*batch, 1, self.num_heads, self.head_dim))
+
+    def scan(self, z, initial_carry, done, inputs):
+        k, v = z
+        q = self._heads(self.query(inputs))
+        s0, z0 = initial_carry
+        bf = torch.bfloat16
+        o, s_last, z_last = ops.LinAttn.apply(q.to(bf), k.to(bf), v.to(bf), s0[:, 0].contiguous(),
+                                              z0[:, 0].contiguous(), done, self.eps, True)
+        o = o.reshape(*o.shape[:2], -1).to(inputs.dtype)
+        y = self.output_projection(self.norm(o))
+        return (s_last[:, None], z_last[:, None]), y

@@ -191,3 +191,41 @@ def linattn_fwd(q, k, v, s0=None, z0=None, done=None, eps=1e-6, feature_map=True
     if check:
         _check_status(status, "mxk_linattn_bf16_fwd")
     return o, s_last, z_last, states
+
+
+def linattn_bwd(q, k, v, d_o, chunk_states, done=None, ds_last=None, dz_last=None, eps=1e-6, feature_map=True,
+                check=False):
+    """Cotangents ``(dq, dk, dv, ds0, dz0)`` of :func:`linattn_fwd`."""
+    q, k, v, d_o = (_dev(t, torch.bfloat16, n) for t, n in ((q, "q"), (k, "k"), (v, "v"), (d_o, "d_o")))
+    ds_last, dz_last = _dev(ds_last, torch.float32, "ds_last"), _dev(dz_last, torch.float32, "dz_last")
+    bsz, steps, heads, dim = q.shape
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    ds0 = torch.empty(bsz, heads, dim, dim, dtype=torch.float32, device=q.device)
+    dz0 = torch.empty(bsz, heads, dim, dtype=torch.float32, device=q.device)
+    status = _status_word(q.device) if check else None
+    _lib.call("mxk_linattn_bf16_bwd", _ptr(q), _ptr(k), _ptr(v), _ptr(d_o), _ptr(chunk_states),
+              _ptr(_done_bytes(done)), _ptr(ds_last), _ptr(dz_last), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(ds0),
+              _ptr(dz0), _ptr(status), bsz, steps, heads, dim, float(eps), int(feature_map), _stream())
+    if check:
+        _check_status(status, "mxk_linattn_bf16_bwd")
+    return dq, dk, dv, ds0, dz0
+
+
+class LinAttn(torch.autograd.Function):
+    """(q, k, v, s0, z0, done) -> (o, s_last, z_last); the forward keeps the
+    per-chunk states as its residual."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, s0, z0, done, eps, feature_map):
+        o, s_last, z_last, states = linattn_fwd(q, k, v, s0, z0, done, eps, feature_map, save_states=True)
+        ctx.save_for_backward(q, k, v, states, done)
+        ctx.eps, ctx.feature_map = eps, feature_map
+        ctx.has_state = (s0 is not None, z0 is not None)
+        return o, s_last, z_last
+
+    @staticmethod
+    def backward(ctx, d_o, ds_last, dz_last):
+        q, k, v, states, done = ctx.saved_tensors
+        dq, dk, dv, ds0, dz0 = linattn_bwd(q, k, v, d_o, states, done, ds_last, dz_last, ctx.eps, ctx.feature_map)
+        return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), ds0 if ctx.has_state[0] else None,
+                dz0 if ctx.has_state[1] else None, None, None, None)

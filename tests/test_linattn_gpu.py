@@ -74,3 +74,41 @@ def test_linattn_split_sequence_matches_single_call():
     o2, s2, z2, _ = ops.linattn_fwd(cu(q[:, 128:]), cu(k[:, 128:]), cu(v[:, 128:]), s1, z1, cu(done[:, 128:]))
     assert torch.equal(torch.cat([o1, o2], 1), o)   # chunk-aligned split: identical arithmetic
     assert torch.equal(s2, s_last) and torch.equal(z2, z_last)
+
+
+@pytest.mark.parametrize("shape,p_done", [((2, 64, 2, 64), 0.0), ((2, 64, 2, 64), 0.05), ((2, 256, 4, 64), 0.01),
+                                          ((2, 1, 1, 64), 0.0), ((2, 7, 3, 64), 0.3), ((2, 65, 2, 64), 0.05),
+                                          ((1, 200, 2, 64), 0.02), ((2, 128, 1, 64), 1.0)])
+def test_linattn_bwd(shape, p_done):
+    from memorax_b200 import ops
+    q, k, v, s0, z0, done = make_case(sum(shape) + 1, *shape, p_done)
+    gen = torch.Generator().manual_seed(99)
+    d_o = torch.randn(*shape, generator=gen).bfloat16()
+    ds_last = torch.randn(*s0.shape, generator=gen) * 0.1
+    dz_last = torch.randn(*z0.shape, generator=gen) * 0.1
+    leaves = [t.double().requires_grad_() for t in (q, k, v, s0, z0)]
+    o_ref, s_ref, z_ref = mo.linattn_seq(*leaves, done.double())
+    ((o_ref * d_o.double()).sum() + (s_ref * ds_last.double()).sum() + (z_ref * dz_last.double()).sum()).backward()
+    cu = lambda t: t.cuda()
+    _, _, _, states = ops.linattn_fwd(cu(q), cu(k), cu(v), cu(s0), cu(z0), cu(done), save_states=True, check=True)
+    outs = ops.linattn_bwd(cu(q), cu(k), cu(v), cu(d_o), states, cu(done), cu(ds_last), cu(dz_last), check=True)
+    for got, leaf, name in zip(outs, leaves, ["dq", "dk", "dv", "ds0", "dz0"]):
+        ref = leaf.grad
+        tol = ATOL if name in ("dq", "dk", "dv") else 1e-2 * max(1.0, float(ref.abs().max()))
+        err = max_abs(got.float(), ref)
+        assert err <= tol, f"{name}: {err:.4f} > {tol:.4f} (ref max {float(ref.abs().max()):.3f})"
+
+
+def test_linattn_autograd_function():
+    from memorax_b200 import ops
+    q, k, v, s0, z0, done = make_case(5, 2, 96, 2, 64, 0.03)
+    w = torch.randn(2, 96, 2, 64, generator=torch.Generator().manual_seed(1))
+    leaves = [t.double().requires_grad_() for t in (q, k, v, s0, z0)]
+    o_ref, _, _ = mo.linattn_seq(*leaves, done.double())
+    (o_ref * w.double()).sum().backward()
+    dev = [t.cuda().requires_grad_() for t in (q, k, v, s0, z0)]
+    o, _, _ = ops.LinAttn.apply(*dev, done.cuda(), 1e-6, True)
+    (o.float() * w.cuda()).sum().backward()
+    for got, leaf in zip(dev, leaves):
+        tol = ATOL if got.dtype == torch.bfloat16 else 1e-2 * max(1.0, float(leaf.grad.abs().max()))
+        assert max_abs(got.grad.float(), leaf.grad) <= tol
