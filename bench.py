@@ -1,0 +1,430 @@
+#!/usr/bin/env python
+"""Benchmark of the sequence-mixing hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c4|c1]
+    python bench.py --impl reference ...      # CPU arm: the oracle port, host cores
+
+A step is one pass of the hot path over one batch of seeded synthetic input:
+forward + backward of the op for c2 / c4, forward only for c1 (the shapes and
+value distributions of the reference's headline configurations; the reference
+names no dataset).  One process per GPU; every rank owns a full batch of
+independent sequences (weak scaling, no data-path collective).  Rank 0 prints
+ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_HBM_GBS = 6650.0
+NSETS = 4  # input sets rotated between steps so that no step finds its inputs in L2
+
+
+def measured_hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+# ----------------------------------------------------------------- workloads
+class LinAttnC2:
+    """Causal linear attention fwd+bwd: B=256, H=4, T=256, d=64, bf16 in, fp32
+    state, chunk 64, done ~ Bernoulli(0.01), initial state ~ N(0, 0.1)."""
+    name = "c2_linear_attention_fwd_bwd"
+    dtype = "bf16"
+    B, H, T, D = 256, 4, 256, 64
+    p_done = 0.01
+    seed = 1234 + 2
+    # bytes of q,k,v,o (fwd) and q,k,v,do,dq,dk,dv (bwd) per token-head, bf16
+    fwd_bytes_per_token_head = 4 * 64 * 2
+    bwd_bytes_per_token_head = 7 * 64 * 2
+    dominant = "linattn_bwd_kernel"
+    launches_per_step = 2
+    # dram__bytes_read.sum + dram__bytes_write.sum of one linattn_bwd_kernel launch at
+    # this size; see profiles/linattn_c2.md
+    dominant_traffic_bytes = None
+
+    def __init__(self, batch=None):
+        self.B = batch or self.B
+
+    def tokens(self):
+        return self.B * self.T
+
+    def host_inputs(self, seed_offset=0):
+        g = torch.Generator().manual_seed(self.seed + seed_offset)
+        shp = (self.B, self.T, self.H, self.D)
+        mk = lambda *s: torch.randn(*s, generator=g)
+        return dict(
+            q=(mk(*shp) / 8).bfloat16(), k=(mk(*shp) / 8).bfloat16(), v=(mk(*shp) / 8).bfloat16(),
+            d_o=mk(*shp).bfloat16(),
+            s0=mk(self.B, self.H, self.D, self.D) * 0.1, z0=mk(self.B, self.H, self.D).abs() * 0.1,
+            done=(torch.rand(self.B, self.T, generator=g) < self.p_done).to(torch.uint8))
+
+    def state_bytes(self):
+        return self.B * self.H * (self.D * self.D + self.D) * 4
+
+    def algorithmic_bytes(self):
+        th = self.B * self.T * self.H
+        fwd = th * self.fwd_bytes_per_token_head + 2 * self.state_bytes()
+        bwd = th * self.bwd_bytes_per_token_head + 2 * self.state_bytes()
+        return {"linattn_fwd_kernel": fwd, "linattn_bwd_kernel": bwd}
+
+    def step(self, x, ops, mark=None):
+        o, s_last, z_last, states = ops.linattn_fwd(x["q"], x["k"], x["v"], x["s0"], x["z0"], x["done"],
+                                                    save_states=True)
+        if mark:
+            mark[0].record()
+        dq, dk, dv, ds0, dz0 = ops.linattn_bwd(x["q"], x["k"], x["v"], x["d_o"], states, x["done"])
+        if mark:
+            mark[1].record()
+        return (o, s_last, z_last, dq, dk, dv, ds0, dz0)
+
+    def cpu_step(self, x):
+        """The reference's own formulation (every S_t materialised, prefix over
+        time, read-out; autograd backward) in fp32 on the host cores."""
+        from oracle import memoroid_oracle as mo
+        q, k, v = (x[n].float().requires_grad_() for n in ("q", "k", "v"))
+        o, s_last, z_last = mo.linattn_reference_form(q, k, v, x["s0"], x["z0"], x["done"].float())
+        (o * x["d_o"].float()).sum().backward()
+        return o
+
+    cpu_sample_batch = 64
+
+
+class LruC4:
+    """Complex diagonal LRU recurrence fwd+bwd, complex64, time-invariant lambda:
+    B=1024, T=1024, D=512, |lambda|~U[0.9,0.999], phase~U[0,pi/10], done~Bern(0.002)."""
+    name = "c4_complex_lru_fwd_bwd"
+    dtype = "c64"
+    B, T, D = 1024, 1024, 512
+    p_done = 0.002
+    seed = 1234 + 4
+    dominant = "linrec_bwd_kernel"
+    launches_per_step = 3
+    dominant_traffic_bytes = None
+    cpu_sample_batch = 64
+
+    def __init__(self, batch=None):
+        self.B = batch or self.B
+
+    def tokens(self):
+        return self.B * self.T
+
+    def host_inputs(self, seed_offset=0):
+        g = torch.Generator().manual_seed(self.seed + seed_offset)
+        mag = 0.9 + 0.099 * torch.rand(self.D, generator=g)
+        ph = torch.rand(self.D, generator=g) * math.pi / 10
+        shp = (self.B, self.T, self.D)
+        return dict(lam=torch.polar(mag, ph).to(torch.complex64),
+                    bu=torch.complex(torch.randn(*shp, generator=g), torch.randn(*shp, generator=g)),
+                    gh=torch.complex(torch.randn(*shp, generator=g), torch.randn(*shp, generator=g)),
+                    done=(torch.rand(self.B, self.T, generator=g) < self.p_done).to(torch.uint8))
+
+    def algorithmic_bytes(self):
+        n = self.B * self.T * self.D
+        return {"linrec_fwd_kernel": 16 * n, "linrec_bwd_kernel": 24 * n}
+
+    def step(self, x, ops, mark=None):
+        h, _ = ops.linrec_fwd(x["lam"], x["bu"], None, None, x["done"], want_decay=False)
+        if mark:
+            mark[0].record()
+        gb, ga, _ = ops.linrec_bwd(x["lam"], h, None, x["done"], x["gh"], None, need_ga=True, need_gh0=False)
+        if mark:
+            mark[1].record()
+        return (h[:, -1], gb, ga)
+
+    def cpu_step(self, x):
+        from oracle import memoroid_oracle as mo
+        lam, bu = x["lam"].clone().requires_grad_(), x["bu"].clone().requires_grad_()
+        h0 = torch.zeros(bu.shape[0], bu.shape[2], dtype=bu.dtype)
+        h, _ = mo.linrec_seq(lam, bu, h0, x["done"].float())
+        (h * x["gh"]).sum().real.backward()
+        return h
+
+
+class LinRecC1:
+    """Real diagonal recurrence, forward only, fp32: B=64, T=128, D=256,
+    a = sigmoid(N(0,1)), done ~ Bernoulli(0.01), carried h0."""
+    name = "c1_real_linrec_fwd"
+    dtype = "f32"
+    B, T, D = 64, 128, 256
+    p_done = 0.01
+    seed = 1234 + 1
+    dominant = "linrec_fwd_kernel"
+    launches_per_step = 1
+    dominant_traffic_bytes = None
+    cpu_sample_batch = 64
+
+    def __init__(self, batch=None):
+        self.B = batch or self.B
+
+    def tokens(self):
+        return self.B * self.T
+
+    def host_inputs(self, seed_offset=0):
+        g = torch.Generator().manual_seed(self.seed + seed_offset)
+        shp = (self.B, self.T, self.D)
+        return dict(a=torch.sigmoid(torch.randn(*shp, generator=g)), b=torch.randn(*shp, generator=g),
+                    h0=torch.randn(self.B, self.D, generator=g),
+                    done=(torch.rand(self.B, self.T, generator=g) < self.p_done).to(torch.uint8))
+
+    def algorithmic_bytes(self):
+        return {"linrec_fwd_kernel": 12 * self.B * self.T * self.D}
+
+    def step(self, x, ops, mark=None):
+        if mark:
+            mark[0].record()
+        h, _ = ops.linrec_fwd(x["a"], x["b"], x["h0"], None, x["done"], want_decay=False)
+        if mark:
+            mark[1].record()
+        return (h,)
+
+    def cpu_step(self, x):
+        from oracle import memoroid_oracle as mo
+        with torch.no_grad():
+            return mo.linrec_seq(x["a"], x["b"], x["h0"], x["done"].float())[0]
+
+
+WORKLOADS = {"c2": LinAttnC2, "c4": LruC4, "c1": LinRecC1}
+
+
+# ------------------------------------------------------------ clock sampling
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only)
+    from a background thread while the timed region runs."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.handle, self.nv.NVML_CLOCK_SM))
+                mask = self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def __enter__(self):
+        if self.nv:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+# ------------------------------------------------------------------ CPU arm
+def time_cpu(workload_cls, steps, warmup, batch=None):
+    """Times the oracle port on the host cores over a bounded sample of the
+    workload (fewer sequences, same T / heads / widths)."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    w = workload_cls(batch=batch or workload_cls.cpu_sample_batch)
+    x = w.host_inputs()
+    for _ in range(warmup):
+        w.cpu_step(x)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        w.cpu_step(x)
+    dt = (time.perf_counter() - t0) / steps
+    return w, dt
+
+
+def bounded_cpu_batch(workload_cls, passes, budget_s=90.0):
+    """Largest sample (in sequences) for which `passes` passes fit the budget,
+    from one calibration pass on a few sequences."""
+    probe = min(4, workload_cls.cpu_sample_batch)
+    _, dt = time_cpu(workload_cls, steps=1, warmup=1, batch=probe)
+    per_seq = dt / probe
+    return int(max(1, min(workload_cls.cpu_sample_batch, budget_s / (per_seq * max(passes, 1)))))
+
+
+def cpu_baseline(workload_cls):
+    w, dt = time_cpu(workload_cls, steps=2, warmup=1)
+    return {"value": w.tokens() / dt, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{w.B} of {workload_cls.B} sequences of the same workload, fp32 torch-CPU oracle port, "
+                      f"{dt:.3f} s per pass"}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cls = WORKLOADS[args.workload]
+    batch = bounded_cpu_batch(cls, args.steps + args.warmup)
+    w, dt = time_cpu(cls, steps=args.steps, warmup=args.warmup, batch=batch)
+    val = w.tokens() / dt
+    base = {"value": val, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{w.B} of {cls.B} sequences per step, fp32 torch-CPU oracle port (reference formulation)"}
+    print(json.dumps({
+        "impl": "reference", "metric": "tokens/s", "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": cls.name, "sample_batch": w.B, "note": "jax is not installable here; the timed code "
+                   "is the CPU restatement of the reference's algorithm"},
+        "cpu_baseline": base,
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+# ------------------------------------------------------------------ GPU arm
+def to_device(x, dev):
+    return {k: v.to(dev, non_blocking=True) for k, v in x.items()}
+
+
+def run_gpu_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: memorax_b200 has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    from memorax_b200 import ops  # raises if libmxk.so is missing
+
+    cls = WORKLOADS[args.workload]
+    w = cls(batch=args.batch)
+    host = w.host_inputs(seed_offset=1000 * rank)
+    in_bytes = sum(v.numel() * v.element_size() for v in host.values())
+    # enough distinct input sets that a step never finds its inputs in the 126 MB L2
+    nsets = 1 if in_bytes > (1 << 30) else min(64, max(NSETS, -(-(512 << 20) // in_bytes)))
+    sets = [to_device(host if i == 0 else w.host_inputs(seed_offset=1000 * rank + i), dev) for i in range(nsets)]
+    torch.cuda.synchronize()
+
+    def barrier():
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        w.step(sets[i % nsets], ops)
+    barrier()
+
+    marks = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        t_start.record()
+        for i in range(args.steps):
+            w.step(sets[i % nsets], ops, marks[i])
+        t_stop.record()
+        barrier()
+    elapsed_ms = t_start.elapsed_time(t_stop)
+    dominant_ms = sum(a.elapsed_time(b) for a, b in marks) / args.steps
+    if dist:
+        t = torch.tensor([elapsed_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / args.steps
+    value = world * w.tokens() / (ms_per_step * 1e-3)
+
+    # ---- end to end: host buffers in, host results out, through the same calls ----
+    pinned_in = {k: v.pin_memory() for k, v in host.items()}
+    e2e_steps = max(3, min(args.steps, 20))
+    outs = w.step(to_device(pinned_in, dev), ops)
+    pinned_out = [torch.empty(o.shape, dtype=o.dtype, pin_memory=True) for o in outs]
+    h2d = sum(v.numel() * v.element_size() for v in pinned_in.values())
+    d2h = sum(o.numel() * o.element_size() for o in pinned_out)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        x = to_device(pinned_in, dev)
+        outs = w.step(x, ops)
+        for dst, src in zip(pinned_out, outs):
+            dst.copy_(src, non_blocking=True)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if dist:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = world * w.tokens() / (e2e_ms / e2e_steps * 1e-3)
+
+    if rank == 0:
+        peak, peak_kind = measured_hbm_peak()
+        alg = w.algorithmic_bytes()[w.dominant]
+        achieved = alg / (dominant_ms * 1e-3) / 1e9
+        line = {
+            "metric": "tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
+            "config": {"workload": w.name, "batch_per_gpu": w.B, "T": w.T, "tokens_per_step_per_gpu": w.tokens(),
+                       "l2": f"{nsets} input set(s) rotated, {in_bytes * nsets / 1e6:.0f} MB of inputs > 126 MB L2",
+                       "sharding": "independent sequences per rank, no data-path collective"},
+            "clocks": clocks.summary(),
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps},
+            "gpu_launches": w.launches_per_step * args.steps,
+            "roofline": {"bound": "hbm", "kernel": w.dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": w.dominant_traffic_bytes,
+                         "algorithmic_bytes_per_launch": alg, "ms_per_launch": dominant_ms},
+        }
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline(cls)
+        print(json.dumps(line))
+    if dist:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--batch", type=int, default=None, help="override sequences per GPU (profiling only)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()
