@@ -56,7 +56,7 @@ class LinAttnC2:
     launches_per_step = 2
     # dram__bytes_read.sum + dram__bytes_write.sum of one linattn_bwd_kernel launch at
     # this size; see profiles/linattn_c2.md
-    dominant_traffic_bytes = None
+    dominant_traffic_bytes = 254.0e6
 
     def __init__(self, batch=None):
         self.B = batch or self.B
@@ -400,7 +400,7 @@ def run_gpu_arm(args):
                     "steps": e2e_steps},
             "gpu_launches": w.launches_per_step * args.steps,
             "roofline": {"bound": "hbm", "kernel": w.dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": w.dominant_traffic_bytes,
+                         "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": (w.dominant_traffic_bytes if args.batch is None else None),
                          "algorithmic_bytes_per_launch": alg, "ms_per_launch": dominant_ms},
         }
         if world == 1 and not args.no_cpu:
