@@ -43,7 +43,8 @@ enum {
   MXK_ERR_DIMS = -2,        /* a dimension is non-positive or too large */
   MXK_ERR_ALIGN = -3,       /* a pointer is not 16-byte aligned */
   MXK_ERR_UNSUPPORTED = -4, /* head dim / chunk size outside the compiled set */
-  MXK_ERR_WORKSPACE = -5    /* workspace missing or too small */
+  MXK_ERR_WORKSPACE = -5,   /* workspace missing or too small */
+  MXK_ERR_SCRATCH_LIMIT = -6 /* problem larger than the library's built-in scratch buffer */
 };
 
 /* Human-readable text for a status returned by any function below. */
@@ -102,6 +103,32 @@ int mxk_linrec_c64_bwd(const float* a, int a_time_invariant, const float* h, con
                        const uint8_t* done, const float* gh, const float* gh_last, float* gb,
                        float* ga, float* gh0, void* workspace, size_t workspace_bytes,
                        int B, int T, int D, int conjugate, mxk_stream_t stream);
+
+/* Allocation-free variant of mxk_linrec_c64_bwd for a time-invariant decay
+ * (the LRU / S5 case).  It has no counterpart in the reference; it exists for
+ * hosts that cannot hand this library a workspace.  An XLA custom call is
+ * given exactly the operand and result buffers the compiler planned at trace
+ * time, a CUDA-graph replay cannot grow a buffer, and an acting loop that steps
+ * environments every few hundred microseconds cannot afford cudaMalloc's
+ * device-wide synchronisation -- yet the (D,) decay gradient needs B * D
+ * partial sums somewhere.  Here they go into a fixed 4 MiB array that lives in
+ * the library's device image (every GPU that loads the library holds it until
+ * the process exits), so the caller passes inputs and outputs only.
+ *
+ *   - Limit: B * D <= mxk_linrec_noalloc_max_elements() (524288 complex
+ *     elements); larger problems return MXK_ERR_SCRATCH_LIMIT and launch nothing.
+ *   - The first call on each device looks up the array's device address (one
+ *     cudaGetSymbolAddress, no allocation); make that first call before any
+ *     stream capture begins.
+ *   - All calls on a device share the one array.  Every partial sum is
+ *     overwritten before it is read, so nothing has to be cleared between
+ *     calls, but two calls whose kernels overlap on the GPU (different streams)
+ *     race on it: serialise them.
+ * Arguments as mxk_linrec_c64_bwd with a_time_invariant = 1; `ga` is (D). */
+size_t mxk_linrec_noalloc_max_elements(void);
+int mxk_linrec_c64_bwd_noalloc(const float* a, const float* h, const float* h0, const uint8_t* done,
+                               const float* gh, const float* gh_last, float* gb, float* ga, float* gh0,
+                               int B, int T, int D, int conjugate, mxk_stream_t stream);
 
 /* ---------------------------------------------------------------------------
  * Log-space recurrence (MinGRU, min_gru.py:67-78):

@@ -25,6 +25,8 @@ SIGNATURES = {
     "mxk_linrec_bwd_workspace_bytes": (_z, [_i, _i, _i, _i, _i]),
     "mxk_linrec_f32_bwd": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _i, _i, _i, _p]),
     "mxk_linrec_c64_bwd": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _i, _i, _i, _i, _p]),
+    "mxk_linrec_noalloc_max_elements": (_z, []),
+    "mxk_linrec_c64_bwd_noalloc": (_i, [_p] * 9 + [_i, _i, _i, _i, _p]),
     "mxk_loglinrec_f32_fwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
     "mxk_loglinrec_f32_bwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
     "mxk_linattn_chunk_states_bytes": (_z, [_i, _i, _i, _i]),

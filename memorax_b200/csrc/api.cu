@@ -11,6 +11,7 @@ const char* mxk_status_string(int status) {
     case MXK_ERR_ALIGN: return "a pointer or stride is not sufficiently aligned";
     case MXK_ERR_UNSUPPORTED: return "head dimension or chunk size outside the compiled set";
     case MXK_ERR_WORKSPACE: return "workspace missing or too small";
+    case MXK_ERR_SCRATCH_LIMIT: return "problem exceeds the library's built-in scratch buffer (see mxk_linrec_noalloc_max_elements)";
     default: break;
   }
   if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));

@@ -8,6 +8,8 @@
 // before the dependent arithmetic so that enough bytes are in flight to cover
 // HBM latency.  When B*D is too small to fill 148 SMs that way, each thread
 // owns a single element instead (more, narrower threads).
+#include <mutex>
+
 #include "mxk_common.cuh"
 
 namespace mxk {
@@ -472,6 +474,42 @@ int linrec_bwd(const float* a, int a_tinv, const float* h, const float* h0, cons
 }  // namespace
 }  // namespace mxk
 
+// ---------------------------------------------------------------------------
+// Built-in scratch for mxk_linrec_c64_bwd_noalloc: one fixed array per GPU that
+// loads this library, resident until the process exits.
+// ---------------------------------------------------------------------------
+namespace mxk {
+namespace {
+
+constexpr size_t kNoAllocScratchFloats = 1u << 20;  // 4 MiB: B * D <= 524288 complex elements
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+float* g_noalloc_ptr[kMaxDevices] = {};
+
+// Device address of g_noalloc_scratch on the current device.  In host code the
+// symbol itself is only a handle, so the address is looked up once per device
+// (with that device current) and cached.
+int noalloc_scratch(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDevices) return MXK_ERR_DIMS;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_ptr[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    g_noalloc_ptr[dev] = static_cast<float*>(ptr);
+  }
+  *out = g_noalloc_ptr[dev];
+  return MXK_OK;
+}
+
+}  // namespace
+}  // namespace mxk
+
 extern "C" {
 
 int mxk_linrec_f32_fwd(const float* a, int a_time_invariant, const float* b, const float* h0,
@@ -506,6 +544,19 @@ int mxk_linrec_c64_bwd(const float* a, int a_time_invariant, const float* h, con
                        int B, int T, int D, int conjugate, mxk_stream_t stream) {
   return mxk::linrec_bwd<true>(a, a_time_invariant, h, h0, done, gh, gh_last, gb, ga, gh0, workspace,
                                workspace_bytes, B, T, D, conjugate, stream);
+}
+
+size_t mxk_linrec_noalloc_max_elements(void) { return mxk::kNoAllocScratchFloats / 2; }
+
+int mxk_linrec_c64_bwd_noalloc(const float* a, const float* h, const float* h0, const uint8_t* done,
+                               const float* gh, const float* gh_last, float* gb, float* ga, float* gh0,
+                               int B, int T, int D, int conjugate, mxk_stream_t stream) {
+  if (B <= 0 || T <= 0 || D <= 0) return MXK_ERR_DIMS;
+  if (static_cast<size_t>(B) * static_cast<size_t>(D) > mxk_linrec_noalloc_max_elements()) return MXK_ERR_SCRATCH_LIMIT;
+  float* scratch = nullptr;
+  if (int st = mxk::noalloc_scratch(&scratch)) return st;
+  return mxk::linrec_bwd<true>(a, /*a_tinv=*/1, h, h0, done, gh, gh_last, gb, ga, gh0, scratch,
+                               mxk::kNoAllocScratchFloats * sizeof(float), B, T, D, conjugate, stream);
 }
 
 int mxk_loglinrec_f32_fwd(const float* ls, const float* d, const float* x0, const float* a0,
