@@ -9,7 +9,7 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libmxk.so")
+LIB_PATH = os.environ.get("MXK_LIBRARY") or os.path.join(_HERE, "libmxk.so")
 
 _p = ctypes.c_void_p
 _i = ctypes.c_int

@@ -16,7 +16,25 @@ namespace mxk {
 namespace {
 
 constexpr int kBlock = 256;
-constexpr int kUnroll = 4;  // time steps whose loads are in flight together
+// Time steps whose loads are in flight together and the occupancy the
+// register allocation must allow, per direction (tuned on B200: the one-read
+// forward stream likes deep unrolling, the two-read backward stream likes more
+// resident warps).
+#ifndef MXK_LINREC_UNROLL_F
+#define MXK_LINREC_UNROLL_F 4
+#endif
+#ifndef MXK_LINREC_MINB_F
+#define MXK_LINREC_MINB_F 4
+#endif
+#ifndef MXK_LINREC_UNROLL_B
+#define MXK_LINREC_UNROLL_B 2
+#endif
+#ifndef MXK_LINREC_MINB_B
+#define MXK_LINREC_MINB_B 4
+#endif
+constexpr int kUnroll = 4;  // log-space kernels
+constexpr int kUnrollF = MXK_LINREC_UNROLL_F;
+constexpr int kUnrollB = MXK_LINREC_UNROLL_B;
 
 template <int W> struct VecOf;
 template <> struct VecOf<4> { using type = float4; };
@@ -125,7 +143,7 @@ __device__ __forceinline__ Pack<W> add(const Pack<W>& x, const Pack<W>& y) {
 // Row stride is `row` floats (D for real, 2D for complex); a thread's W floats
 // start at column `col`.
 template <bool CPLX, int W>
-__global__ void __launch_bounds__(kBlock)
+__global__ void __launch_bounds__(kBlock, MXK_LINREC_MINB_F)
 linrec_fwd_kernel(const float* __restrict__ a, int a_tinv, const float* __restrict__ b,
                   const float* __restrict__ h0, const float* __restrict__ a0,
                   const uint8_t* __restrict__ done, float* __restrict__ h,
@@ -145,11 +163,11 @@ linrec_fwd_kernel(const float* __restrict__ a, int a_tinv, const float* __restri
   Pack<W> a_fix = fill_pack<W>(0.f, 0.f, CPLX);
   if (a_tinv) a_fix = load_pack_cached<W>(a + col);
 
-  for (int t0 = 0; t0 < T; t0 += kUnroll) {
-    Pack<W> av[kUnroll], bv[kUnroll];
-    bool rs[kUnroll];
+  for (int t0 = 0; t0 < T; t0 += kUnrollF) {
+    Pack<W> av[kUnrollF], bv[kUnrollF];
+    bool rs[kUnrollF];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
+    for (int u = 0; u < kUnrollF; ++u) {
       const int t = t0 + u;
       if (t < T) {
         const size_t off = seq + static_cast<size_t>(t) * row;
@@ -159,7 +177,7 @@ linrec_fwd_kernel(const float* __restrict__ a, int a_tinv, const float* __restri
       }
     }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
+    for (int u = 0; u < kUnrollF; ++u) {
       const int t = t0 + u;
       if (t < T) {
         const Pack<W>& at = a_tinv ? a_fix : av[u];
@@ -179,7 +197,7 @@ linrec_fwd_kernel(const float* __restrict__ a, int a_tinv, const float* __restri
 // ----------------------------------------------------------------- backward
 // Walks time right to left carrying c = a_{t+1} m_{t+1} g_{t+1}.
 template <bool CPLX, int W>
-__global__ void __launch_bounds__(kBlock)
+__global__ void __launch_bounds__(kBlock, MXK_LINREC_MINB_B)
 linrec_bwd_kernel(const float* __restrict__ a, int a_tinv, const float* __restrict__ h,
                   const float* __restrict__ h0, const uint8_t* __restrict__ done,
                   const float* __restrict__ gh, const float* __restrict__ gh_last,
@@ -200,11 +218,11 @@ linrec_bwd_kernel(const float* __restrict__ a, int a_tinv, const float* __restri
   Pack<W> ga_acc = fill_pack<W>(0.f, 0.f, CPLX);
   const bool want_ga = (ga != nullptr) || (ga_partial != nullptr);
 
-  for (int t0 = T - 1; t0 >= 0; t0 -= kUnroll) {
-    Pack<W> av[kUnroll], gv[kUnroll], hp[kUnroll];
-    bool rs[kUnroll];
+  for (int t0 = T - 1; t0 >= 0; t0 -= kUnrollB) {
+    Pack<W> av[kUnrollB], gv[kUnrollB], hp[kUnrollB];
+    bool rs[kUnrollB];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
+    for (int u = 0; u < kUnrollB; ++u) {
       const int t = t0 - u;
       if (t >= 0) {
         const size_t off = seq + static_cast<size_t>(t) * row;
@@ -219,7 +237,7 @@ linrec_bwd_kernel(const float* __restrict__ a, int a_tinv, const float* __restri
       }
     }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
+    for (int u = 0; u < kUnrollB; ++u) {
       const int t = t0 - u;
       if (t >= 0) {
         const Pack<W>& at = a_tinv ? a_fix : av[u];
