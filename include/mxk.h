@@ -183,6 +183,27 @@ int mxk_linattn_bf16_bwd(const void* q, const void* k, const void* v, const void
                          void* dv, float* ds0, float* dz0, int* status, int B, int T, int H, int d, float eps,
                          int feature_map, mxk_stream_t stream);
 
+/* ---------------------------------------------------------------------------
+ * Gated delta rule (DeltaNet with a scalar forget gate).  The reference has no
+ * such cell; this is the new MemoroidCellBase-shaped mixer, defined per head
+ * (S is d_v x d_k, a_t = done_t ? 0 : alpha_t) by
+ *   S_t = a_t S_{t-1} (I - beta_t k_t k_t^T) + beta_t v_t k_t^T,   o_t = S_t q_t,
+ * i.e. Memoroid.scan_fn (memoroid.py:60-91) over the elements
+ * (alpha (I - beta k k^T), beta v k^T) with the operator (M_i M_j, U_i M_j + U_j).
+ *
+ *   q, k, v   (B,T,H,d) bf16, contiguous, d = 128; k is expected L2-normalised
+ *   alpha     (B,T,H) fp32 in (0, 1];  beta (B,T,H) fp32
+ *   s0        (B,H,d_v,d_k) fp32 carried state, NULL = zeros
+ *   o         (B,T,H,d) bf16 out;  s_last (B,H,d_v,d_k) fp32 out, optional
+ *   chunk_states  optional residual for the backward call,
+ *             mxk_gdelta_chunk_states_bytes(...) bytes
+ *   status    optional device int, set non-zero if a bounded wait gave up
+ * ------------------------------------------------------------------------- */
+size_t mxk_gdelta_chunk_states_bytes(int B, int T, int H, int d);
+int mxk_gdelta_bf16_fwd(const void* q, const void* k, const void* v, const float* alpha, const float* beta,
+                        const float* s0, const uint8_t* done, void* o, float* s_last, void* chunk_states,
+                        int* status, int B, int T, int H, int d, mxk_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,281 @@
+// Gated delta rule, forward, on the sm_100a tensor cores (math in gdelta_common.cuh).
+//
+// One CTA (128 threads) owns one (batch, head) sequence and walks its 64-token
+// chunks in order with the fp32 state S (128 x 128) resident in tensor memory.
+// Per chunk:
+//   MMAs 1: K K^T, Q K^T (64 x 64), Y^T = S_in K^T, OI^T = S_in Q^T (128 x 64)
+//   epilogue 1: row threads build beta L (fp32, shared) and tril(G o QK^T) (bf16);
+//               thread v forms its column of beta (V - g Y) and solves the unit
+//               lower-triangular system by forward substitution in fp32 registers
+//   MMAs 2: OA^T = U^T P^T (128 x 64), dS = (gam U)^T K (128 x 128)
+//   epilogue 2: o = g OI + OA (staged through shared memory for 16-byte stores);
+//               S = g_last S + dS back into TMEM, bf16 operand copy for the next chunk.
+#include "gdelta_common.cuh"
+
+namespace mxk {
+namespace {
+
+using namespace umma;
+using namespace gdelta;
+
+struct FwdParams {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  const float* alpha;
+  const float* beta;
+  const float* s0;
+  const uint8_t* done;
+  __nv_bfloat16* o;
+  float* s_last;
+  uint4* chunk_states;
+  int* status;
+  int B, T, H;
+};
+
+struct FwdSmem {
+  uint4 s[kStateVecs];        // S_in bf16     [k/8][v][8]
+  uint4 k[kPanD * kC];        // K             [k/8][t][8]
+  uint4 q[kPanD * kC];        // Q             [k/8][t][8]
+  uint4 vplain[kC * 16];      // V row-major [t][v]; later the output tile [t][v]
+  uint4 u[kPanC * kD];        // U^T           [j/8][v][8]
+  uint4 ug[kPanC * kD];       // (gam U)^T
+  uint4 p[kPanC * kC];        // tril(G o QK^T) [j/8][t][8]
+  float lt[kC * kC];          // lt[j][t] = beta_t L_tj
+  ChunkDecay cd;
+  uint64_t bar[2];
+  uint32_t tmem;
+};
+
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColS = 0, kColKK = 128, kColOA = 128, kColQK = 192, kColY = 256, kColDS = 192, kColOI = 320;
+
+__global__ void __launch_bounds__(kThreads) gdelta_fwd_kernel(const FwdParams p) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  FwdSmem& sm = *reinterpret_cast<FwdSmem*>(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
+  const int row = warp * 16 + (lane & 15);  // token row owned in M = 64 accumulators
+  const bool row_active = lane < 16;
+  const int nchunks = (p.T + kC - 1) / kC;
+
+  if (tid == 0) {
+    mbar_init(&sm.bar[0], 1);
+    mbar_init(&sm.bar[1], 1);
+    mbar_init_fence();
+  }
+  if (warp == 0) tmem_alloc(&sm.tmem, kTmemCols);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = sm.tmem;
+  const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+
+  // carried state: thread v owns S[v][.]
+  {
+    const float* s0 = p.s0 ? p.s0 + (static_cast<size_t>(bh) * kD + tid) * kD : nullptr;
+#pragma unroll
+    for (int c8 = 0; c8 < kPanD; ++c8) {
+      float vals[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) vals[e] = 0.f;
+      if (s0) {
+        const float4 a = *reinterpret_cast<const float4*>(s0 + c8 * 8);
+        const float4 c = *reinterpret_cast<const float4*>(s0 + c8 * 8 + 4);
+        vals[0] = a.x; vals[1] = a.y; vals[2] = a.z; vals[3] = a.w;
+        vals[4] = c.x; vals[5] = c.y; vals[6] = c.z; vals[7] = c.w;
+      }
+      tmem_st8(lane_base + kColS + c8 * 8, vals);
+      sm.s[c8 * kD + tid] = pack8_bf16(vals);
+    }
+    tmem_st_wait();
+  }
+
+  const size_t stride_t = static_cast<size_t>(p.H) * kD;
+  const size_t seq_base = (static_cast<size_t>(b) * p.T * p.H + h) * kD;
+  const uint8_t* drow = p.done ? p.done + static_cast<size_t>(b) * p.T : nullptr;
+  const uint32_t id_64 = idesc_bf16(kC, kC, false, false);
+  const uint32_t id_128x64 = idesc_bf16(kD, kC, false, false);
+  const uint32_t id_ds = idesc_bf16(kD, kD, false, true);
+  bool timed_out = false;
+
+  for (int c = 0; c < nchunks; ++c) {
+    const int t0 = c * kC;
+    const int valid = min(kC, p.T - t0);
+    const uint64_t dm = chunk_done_mask(drow, t0, p.T, lane);
+    __syncthreads();
+    load_chunk_decay(sm.cd, p.alpha, p.beta, static_cast<size_t>(b) * p.T, p.H, h, t0, p.T, dm, tid);
+
+    stage_panel_tile(sm.k, p.k + seq_base + static_cast<size_t>(t0) * stride_t, stride_t, valid, tid);
+    stage_panel_tile(sm.q, p.q + seq_base + static_cast<size_t>(t0) * stride_t, stride_t, valid, tid);
+    stage_plain_tile(sm.vplain, p.v + seq_base + static_cast<size_t>(t0) * stride_t, stride_t, valid, tid);
+    if (p.chunk_states) {
+      uint4* dst = p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * kStateVecs;
+      for (int i = tid; i < kStateVecs; i += kThreads) dst[i] = sm.s[i];
+    }
+    fence_smem_to_async();
+    fence_before_sync();
+    __syncthreads();
+
+    if (tid == 0) {
+      fence_after_sync();
+      const Operand ak{smem_u32(sm.k), kC, false}, aq{smem_u32(sm.q), kC, false}, as{smem_u32(sm.s), kD, false};
+      gemm(tmem + kColKK, ak, ak, id_64, kD / 16, false);
+      gemm(tmem + kColQK, aq, ak, id_64, kD / 16, false);
+      gemm(tmem + kColY, as, ak, id_128x64, kD / 16, false);
+      gemm(tmem + kColOI, as, aq, id_128x64, kD / 16, false);
+      commit(&sm.bar[0]);
+    }
+    if (!mbar_wait(&sm.bar[0], c & 1)) timed_out = true;
+    fence_after_sync();
+
+    // ---- epilogue 1a: row threads -> beta L (fp32) and masked decayed QK^T (bf16) ----
+    {
+      const int lo = row_first_key(dm, row);
+      const float cum_t = sm.cd.cum[row], beta_t = sm.cd.beta[row];
+#pragma unroll
+      for (int jp = 0; jp < kPanC; ++jp) {
+        float kk[8], qk[8], pm[8];
+        tmem_ld8(lane_base + kColKK + jp * 8, kk);
+        tmem_ld8(lane_base + kColQK + jp * 8, qk);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int j = jp * 8 + e;
+          const bool in = (j >= lo && j <= row);
+          const float gtj = in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
+          pm[e] = gtj * qk[e];
+          if (row_active) sm.lt[j * kC + row] = (j < row) ? beta_t * gtj * kk[e] : 0.f;
+        }
+        if (row_active) sm.p[jp * kC + row] = pack8_bf16(pm);
+      }
+    }
+    __syncthreads();
+
+    // ---- epilogue 1b: thread v solves for its column of U ----
+    {
+      float r[kC];
+      tmem_ld_row<kC>(lane_base + kColY, r);
+#pragma unroll
+      for (int t = 0; t < kC; ++t)
+        r[t] = sm.cd.beta[t] * (bf16_at(sm.vplain, t, tid) - sm.cd.g[t] * r[t]);
+      forward_substitute(r, sm.lt);
+#pragma unroll
+      for (int jp = 0; jp < kPanC; ++jp) {
+        float sc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sc[e] = r[jp * 8 + e] * sm.cd.gam[jp * 8 + e];
+        sm.u[jp * kD + tid] = pack8_bf16(r + jp * 8);
+        sm.ug[jp * kD + tid] = pack8_bf16(sc);
+      }
+    }
+    fence_smem_to_async();
+    fence_before_sync();
+    __syncthreads();
+
+    if (tid == 0) {
+      fence_after_sync();
+      const Operand au{smem_u32(sm.u), kD, false}, aug{smem_u32(sm.ug), kD, false};
+      const Operand bp{smem_u32(sm.p), kC, false}, bk{smem_u32(sm.k), kC, true};
+      gemm(tmem + kColOA, au, bp, id_128x64, kC / 16, false);
+      gemm(tmem + kColDS, aug, bk, id_ds, kC / 16, false);
+      commit(&sm.bar[1]);
+    }
+    if (!mbar_wait(&sm.bar[1], c & 1)) timed_out = true;
+    fence_after_sync();
+
+    // ---- epilogue 2: outputs and state update ----
+    {
+      __nv_bfloat16* otile = reinterpret_cast<__nv_bfloat16*>(sm.vplain);
+#pragma unroll
+      for (int tp = 0; tp < kPanC; ++tp) {
+        float oi[8], oa[8];
+        tmem_ld8(lane_base + kColOI + tp * 8, oi);
+        tmem_ld8(lane_base + kColOA + tp * 8, oa);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int t = tp * 8 + e;
+          otile[t * kD + tid] = __float2bfloat16(fmaf(sm.cd.g[t], oi[e], oa[e]));
+        }
+      }
+      const float g_last = sm.cd.g[kC - 1];
+      const bool last = (c == nchunks - 1);
+      float* sl = (last && p.s_last) ? p.s_last + (static_cast<size_t>(bh) * kD + tid) * kD : nullptr;
+#pragma unroll
+      for (int c8 = 0; c8 < kPanD; ++c8) {
+        float s[8], ds[8];
+        tmem_ld8(lane_base + kColS + c8 * 8, s);
+        tmem_ld8(lane_base + kColDS + c8 * 8, ds);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s[e] = fmaf(g_last, s[e], ds[e]);
+        tmem_st8(lane_base + kColS + c8 * 8, s);
+        sm.s[c8 * kD + tid] = pack8_bf16(s);
+        if (sl) {
+          *reinterpret_cast<float4*>(sl + c8 * 8) = make_float4(s[0], s[1], s[2], s[3]);
+          *reinterpret_cast<float4*>(sl + c8 * 8 + 4) = make_float4(s[4], s[5], s[6], s[7]);
+        }
+      }
+      tmem_st_wait();
+    }
+    __syncthreads();
+    {
+      __nv_bfloat16* obase = p.o + seq_base + static_cast<size_t>(t0) * stride_t;
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const int vid = r * kThreads + tid;
+        const int trow = vid >> 4, seg = vid & 15;
+        if (trow < valid) *reinterpret_cast<uint4*>(obase + trow * stride_t + seg * 8) = sm.vplain[trow * 16 + seg];
+      }
+    }
+  }
+
+  if (timed_out && p.status) atomicExch(p.status, 1);
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+}
+
+}  // namespace
+}  // namespace mxk
+
+extern "C" {
+
+size_t mxk_gdelta_chunk_states_bytes(int B, int T, int H, int d) {
+  if (B <= 0 || T <= 0 || H <= 0 || d != mxk::gdelta::kD) return 0;
+  const size_t nchunks = (static_cast<size_t>(T) + mxk::gdelta::kC - 1) / mxk::gdelta::kC;
+  return static_cast<size_t>(B) * H * nchunks * mxk::gdelta::kStateVecs * sizeof(uint4);
+}
+
+int mxk_gdelta_bf16_fwd(const void* q, const void* k, const void* v, const float* alpha, const float* beta,
+                        const float* s0, const uint8_t* done, void* o, float* s_last, void* chunk_states,
+                        int* status, int B, int T, int H, int d, mxk_stream_t stream) {
+  using namespace mxk;
+  using namespace mxk::gdelta;
+  if (!q || !k || !v || !alpha || !beta || !o) return MXK_ERR_NULL;
+  if (B <= 0 || T <= 0 || H <= 0 || static_cast<long long>(B) * H > 0x7fffffffLL) return MXK_ERR_DIMS;
+  if (d != kD) return MXK_ERR_UNSUPPORTED;
+  for (const void* ptr : {q, k, v, (const void*)o, (const void*)chunk_states, (const void*)s0, (const void*)s_last})
+    if (ptr && !aligned16(ptr)) return MXK_ERR_ALIGN;
+  FwdParams prm;
+  prm.q = static_cast<const __nv_bfloat16*>(q);
+  prm.k = static_cast<const __nv_bfloat16*>(k);
+  prm.v = static_cast<const __nv_bfloat16*>(v);
+  prm.alpha = alpha;
+  prm.beta = beta;
+  prm.s0 = s0;
+  prm.done = done;
+  prm.o = static_cast<__nv_bfloat16*>(o);
+  prm.s_last = s_last;
+  prm.chunk_states = static_cast<uint4*>(chunk_states);
+  prm.status = status;
+  prm.B = B; prm.T = T; prm.H = H;
+  cudaError_t e = cudaFuncSetAttribute(gdelta_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(sizeof(FwdSmem)));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  gdelta_fwd_kernel<<<B * H, kThreads, sizeof(FwdSmem), static_cast<cudaStream_t>(stream)>>>(prm);
+  return launch_status();
+}
+
+}  // extern "C"

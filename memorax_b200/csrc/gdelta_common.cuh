@@ -1,0 +1,124 @@
+// Shared pieces of the gated delta-rule kernels (head dimension 128, 64-token chunks).
+//
+// Recurrence per head (S is d_v x d_k, a_t = done_t ? 0 : alpha_t):
+//   S_t = a_t S_{t-1} (I - beta_t k_t k_t^T) + beta_t v_t k_t^T,   o_t = S_t q_t.
+// Chunk form used by both kernels (rows t, j inside a chunk; cum_t = sum_{i<=t} log alpha_i):
+//   G_tj  = exp(cum_t - cum_j) if no reset in (j, t] else 0           (j <= t)
+//   g_t   = G from the chunk start (0 once a reset has been passed)   ("live" rows)
+//   gam_j = G_{last,j}                                                  ("keep" rows)
+//   L = strict_tril(G o K K^T),  (I + diag(beta) L) U = diag(beta) (V - diag(g) K S_in^T)
+//   O = diag(g) Q S_in^T + tril(G o Q K^T) U,   S_out = g_last S_in + (diag(gam) U)^T K.
+// Accumulators that have d_v on their rows are kept transposed ([v][t]) so that
+// they fill all 128 TMEM lanes and thread v owns one value column of U.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "linattn_common.cuh"
+#include "mxk_common.cuh"
+#include "umma.cuh"
+
+namespace mxk {
+namespace gdelta {
+
+using linattn::chunk_done_mask;
+using linattn::row_first_key;
+using linattn::row_keep;
+using linattn::row_live;
+
+constexpr int kC = 64;
+constexpr int kD = 128;
+constexpr int kThreads = 128;
+constexpr int kPanD = kD / 8;   // panels of a matrix with 128 columns
+constexpr int kPanC = kC / 8;   // panels of a matrix with 64 columns
+constexpr int kStateVecs = kPanD * kD;  // uint4 per bf16 state copy (32 KiB)
+
+struct ChunkDecay {
+  float alpha[kC], beta[kC], cum[kC], g[kC], gam[kC];
+};
+
+// Loads alpha/beta of one chunk, builds cum / g / gam.  Call with all threads;
+// ends with a __syncthreads().  Rows past the end of the sequence get alpha = 1,
+// beta = 0, i.e. they leave the state untouched.
+__device__ __forceinline__ void load_chunk_decay(ChunkDecay& cd, const float* alpha, const float* beta, size_t bt_base,
+                                                 int H, int h, int t0, int T, uint64_t dm, int tid) {
+  if (tid < kC) {
+    const bool in = t0 + tid < T;
+    const size_t idx = (bt_base + t0 + tid) * H + h;
+    cd.alpha[tid] = in ? alpha[idx] : 1.f;
+    cd.beta[tid] = in ? beta[idx] : 0.f;
+  }
+  __syncthreads();
+  if (tid < 32) {
+    const float l0 = __logf(cd.alpha[2 * tid]), l1 = __logf(cd.alpha[2 * tid + 1]);
+    float s = l0 + l1;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const float o = __shfl_up_sync(0xffffffffu, s, off);
+      if (tid >= off) s += o;
+    }
+    cd.cum[2 * tid] = s - l1;
+    cd.cum[2 * tid + 1] = s;
+  }
+  __syncthreads();
+  if (tid < kC) {
+    cd.g[tid] = row_live(dm, tid) ? __expf(cd.cum[tid]) : 0.f;
+    cd.gam[tid] = row_keep(dm, tid) ? __expf(cd.cum[kC - 1] - cd.cum[tid]) : 0.f;
+  }
+  __syncthreads();
+}
+
+// 64 x 128 bf16 tile (rows = tokens) -> panels [c/8][t][8].  Eight consecutive
+// lanes take eight different rows, so the 16-byte shared stores are conflict-free.
+__device__ __forceinline__ void stage_panel_tile(uint4* dst, const __nv_bfloat16* src, size_t stride_t, int valid,
+                                                 int tid) {
+#pragma unroll
+  for (int r = 0; r < 8; ++r) {
+    const int vid = r * kThreads + tid;
+    const int row = (vid & 7) + 8 * (vid >> 7);
+    const int seg = (vid >> 3) & 15;
+    uint4 x = make_uint4(0, 0, 0, 0);
+    if (row < valid) x = __ldg(reinterpret_cast<const uint4*>(src + row * stride_t + seg * 8));
+    dst[seg * kC + row] = x;
+  }
+}
+
+// Same tile -> plain row-major [t][c] (for element-wise transposed reads).
+__device__ __forceinline__ void stage_plain_tile(uint4* dst, const __nv_bfloat16* src, size_t stride_t, int valid,
+                                                 int tid) {
+#pragma unroll
+  for (int r = 0; r < 8; ++r) {
+    const int vid = r * kThreads + tid;
+    const int row = vid >> 4, seg = vid & 15;
+    uint4 x = make_uint4(0, 0, 0, 0);
+    if (row < valid) x = __ldg(reinterpret_cast<const uint4*>(src + row * stride_t + seg * 8));
+    dst[row * 16 + seg] = x;
+  }
+}
+
+__device__ __forceinline__ float bf16_at(const uint4* plain, int t, int c) {
+  const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(plain);
+  return __bfloat162float(p[t * kD + c]);
+}
+
+// r[t] holds the right-hand side on entry and the solution on exit of
+// (I + diag(beta) L) u = r, one independent column per thread;
+// lt[j * 64 + t] = beta_t L_tj (zero for t <= j).
+__device__ __forceinline__ void forward_substitute(float* r, const float* lt) {
+  const float4* lt4 = reinterpret_cast<const float4*>(lt);
+#pragma unroll
+  for (int j = 0; j < kC - 1; ++j) {
+    const float uj = r[j];
+#pragma unroll
+    for (int m = (j + 1) / 4; m < kC / 4; ++m) {
+      const float4 l = lt4[j * (kC / 4) + m];
+      r[4 * m + 0] = fmaf(-l.x, uj, r[4 * m + 0]);
+      r[4 * m + 1] = fmaf(-l.y, uj, r[4 * m + 1]);
+      r[4 * m + 2] = fmaf(-l.z, uj, r[4 * m + 2]);
+      r[4 * m + 3] = fmaf(-l.w, uj, r[4 * m + 3]);
+    }
+  }
+}
+
+}  // namespace gdelta
+}  // namespace mxk

@@ -229,3 +229,27 @@ class LinAttn(torch.autograd.Function):
         dq, dk, dv, ds0, dz0 = linattn_bwd(q, k, v, d_o, states, done, ds_last, dz_last, ctx.eps, ctx.feature_map)
         return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), ds0 if ctx.has_state[0] else None,
                 dz0 if ctx.has_state[1] else None, None, None, None)
+
+
+# --------------------------------------------------------- gated delta rule
+def gdelta_fwd(q, k, v, alpha, beta, s0=None, done=None, save_states=False, check=False):
+    """Gated delta rule; q, k, v (B,T,H,128) bf16, alpha/beta (B,T,H) fp32.
+    Returns ``(o, s_last, chunk_states)``."""
+    q, k, v = (_dev(t, torch.bfloat16, n) for t, n in ((q, "q"), (k, "k"), (v, "v")))
+    alpha, beta = _dev(alpha, torch.float32, "alpha"), _dev(beta, torch.float32, "beta")
+    s0 = _dev(s0, torch.float32, "s0")
+    bsz, steps, heads, dim = q.shape
+    assert alpha.shape == (bsz, steps, heads) and beta.shape == alpha.shape
+    o = torch.empty_like(q)
+    s_last = torch.empty(bsz, heads, dim, dim, dtype=torch.float32, device=q.device)
+    states = None
+    if save_states:
+        states = torch.empty(_lib.lib.mxk_gdelta_chunk_states_bytes(bsz, steps, heads, dim), dtype=torch.uint8,
+                             device=q.device)
+    status = _status_word(q.device) if check else None
+    _lib.call("mxk_gdelta_bf16_fwd", _ptr(q), _ptr(k), _ptr(v), _ptr(alpha), _ptr(beta), _ptr(s0),
+              _ptr(_done_bytes(done)), _ptr(o), _ptr(s_last), _ptr(states), _ptr(status), bsz, steps, heads, dim,
+              _stream())
+    if check:
+        _check_status(status, "mxk_gdelta_bf16_fwd")
+    return o, s_last, states
