@@ -204,6 +204,17 @@ int mxk_gdelta_bf16_fwd(const void* q, const void* k, const void* v, const float
                         const float* s0, const uint8_t* done, void* o, float* s_last, void* chunk_states,
                         int* status, int B, int T, int H, int d, mxk_stream_t stream);
 
+/* Reverse mode of mxk_gdelta_bf16_fwd.
+ *   d_o (B,T,H,d) bf16 cotangent of o;  ds_last (B,H,d,d) fp32 cotangent of the
+ *   next carry, NULL = zeros;  chunk_states from the forward call
+ *   dq, dk, dv (B,T,H,d) bf16 out;  dalpha, dbeta (B,T,H) fp32 out (dalpha is 0
+ *   where done, whose steps ignore alpha);  ds0 (B,H,d,d) fp32 out, optional.
+ * beta must be non-zero wherever its gradient is wanted. */
+int mxk_gdelta_bf16_bwd(const void* q, const void* k, const void* v, const float* alpha, const float* beta,
+                        const void* d_o, const void* chunk_states, const uint8_t* done, const float* ds_last,
+                        void* dq, void* dk, void* dv, float* dalpha, float* dbeta, float* ds0, int* status,
+                        int B, int T, int H, int d, mxk_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

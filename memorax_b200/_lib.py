@@ -34,6 +34,7 @@ SIGNATURES = {
     "mxk_linattn_bf16_bwd": (_i, [_p] * 14 + [_i, _i, _i, _i, _f, _i, _p]),
     "mxk_gdelta_chunk_states_bytes": (_z, [_i, _i, _i, _i]),
     "mxk_gdelta_bf16_fwd": (_i, [_p] * 11 + [_i, _i, _i, _i, _p]),
+    "mxk_gdelta_bf16_bwd": (_i, [_p] * 16 + [_i, _i, _i, _i, _p]),
 }
 
 

@@ -1,0 +1,541 @@
+// Gated delta rule, backward, on the sm_100a tensor cores.
+//
+// One CTA (128 threads) owns one (batch, head) sequence and walks its 64-token
+// chunks right to left with the fp32 cotangent of the state, dS (128 x 128),
+// resident in tensor memory.  S_in of every chunk is the forward call's residual.
+// With the chunk quantities of gdelta_common.cuh (A = I + diag(beta) L, P =
+// tril(G o QK^T), R = V - diag(g) K S_in^T, U = A^-1 diag(beta) R):
+//   dU   = P^T dO + diag(gam) K dS^T            dUt = A^-T dU      (back substitution)
+//   dV   = diag(beta) dUt =: dR                  dbeta_t = (dUt_t . U_t) / beta_t
+//   dP   = tril(dO U^T)                          dL = -diag(beta) stril(dUt U^T)
+//   dQ   = (dP o G) K + diag(g) dO S_in
+//   dK   = (dP o G)^T Q + (dL o G) K + (dL o G)^T K + diag(gam) U dS - diag(g) dR S_in
+//   dS_in = g_last dS + (diag(g) dO)^T Q - (diag(g) dR)^T K
+//   decay: E = (dP o QK^T + dL o KK^T) o G,  dg_t = do_t.(S_in q_t) - dr_t.(S_in k_t),
+//          dgam_j = u_j.(dS k_j),  dg_last += <dS, S_in>;
+//          dcum_t = rowsum_t(E) - colsum_t(E) + dg_t g_t - dgam_t gam_t (+ sum_j dgam_j gam_j at t = last),
+//          dlog(alpha_i) = sum_{t >= i} dcum_t,  dalpha_i = done_i ? 0 : dlog(alpha_i) / alpha_i.
+// Matrices with d_v on their rows are kept transposed ([v][t]) so that thread v
+// owns one value column, as in the forward kernel.
+#include "gdelta_common.cuh"
+
+namespace mxk {
+namespace {
+
+using namespace umma;
+using namespace gdelta;
+
+struct BwdParams {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  const float* alpha;
+  const float* beta;
+  const __nv_bfloat16* d_o;
+  const uint4* chunk_states;
+  const uint8_t* done;
+  const float* ds_last;
+  __nv_bfloat16* dq;
+  __nv_bfloat16* dk;
+  __nv_bfloat16* dv;
+  float* dalpha;
+  float* dbeta;
+  float* ds0;
+  int* status;
+  int B, T, H;
+};
+
+struct BwdSmem {
+  uint4 s[kStateVecs];      // S_in bf16          [k/8][v][8]
+  uint4 ds[kStateVecs];     // dS bf16            [k/8][v][8]
+  uint4 k[kPanD * kC];      // K                  [k/8][t][8]
+  uint4 q[kPanD * kC];      // Q                  [k/8][t][8]
+  uint4 d_o[kPanD * kC];    // dO, later g dO     [v/8][t][8]
+  uint4 r1[kC * 16];        // V [t][v]   -> dUt^T            [t/8][v][8]
+  uint4 r2[kC * 16];        // dO [t][v]  -> -(g dR)^T        [j/8][v][8]
+  uint4 u[kPanC * kD];      // U^T                [j/8][v][8]
+  uint4 ug[kPanC * kD];     // (gam U)^T
+  uint4 p[kPanC * kC];      // tril(G o QK^T)     [j/8][t][8]
+  float l[kC * kC];         // l[t][j] = beta_t L_tj         -> E[t][j]
+  float lt[kC * kC];        // lt[j][t] = beta_t L_tj        -> dV tile -> (dP o G), (dL o G) panels
+  ChunkDecay cd;
+  float dg[kC], dgam[kC], rowsum[kC], colsum[kC], dcum[kC];
+  float dgl[4];
+  uint64_t bar[2];
+  uint32_t tmem;
+};
+static_assert(sizeof(BwdSmem) <= 227 * 1024, "backward shared memory exceeds one SM");
+
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColDS = 0, kColKK = 128, kColQK = 192, kColY = 256, kColOI = 320, kColX1 = 320, kColW = 320,
+                   kColX2 = 384, kColDP = 448, kColDQ = 128, kColDK = 256, kColDelta = 384;
+
+// Sums 64 per-thread values over the 32 lanes of a warp; on return lane l holds
+// the totals of indices 2l and 2l+1 in vals[0], vals[1].
+__device__ __forceinline__ void warp_reduce64(float* vals, int lane) {
+#pragma unroll
+  for (int off = 16, n = kC; off >= 1; off >>= 1, n >>= 1) {
+    const int half = n >> 1;
+    const bool upper = (lane & off) != 0;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if (i < half) {
+        const float send = upper ? vals[i] : vals[i + half];
+        const float keep = upper ? vals[i + half] : vals[i];
+        vals[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+      }
+    }
+  }
+}
+
+// r[t] holds dU on entry and A^-T dU on exit; l[i * 64 + t] = beta_i L_it (zero for t >= i).
+__device__ __forceinline__ void backward_substitute(float* r, const float* l) {
+  const float4* l4 = reinterpret_cast<const float4*>(l);
+#pragma unroll
+  for (int i = kC - 1; i >= 1; --i) {
+    const float xi = r[i];
+#pragma unroll
+    for (int m = 0; m <= (i - 1) / 4; ++m) {
+      const float4 c = l4[i * (kC / 4) + m];
+      r[4 * m + 0] = fmaf(-c.x, xi, r[4 * m + 0]);
+      r[4 * m + 1] = fmaf(-c.y, xi, r[4 * m + 1]);
+      r[4 * m + 2] = fmaf(-c.z, xi, r[4 * m + 2]);
+      r[4 * m + 3] = fmaf(-c.w, xi, r[4 * m + 3]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  BwdSmem& sm = *reinterpret_cast<BwdSmem*>(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
+  const int row = warp * 16 + (lane & 15);
+  const bool row_active = lane < 16;
+  const int nchunks = (p.T + kC - 1) / kC;
+
+  if (tid == 0) {
+    mbar_init(&sm.bar[0], 1);
+    mbar_init(&sm.bar[1], 1);
+    mbar_init_fence();
+  }
+  if (warp == 0) tmem_alloc(&sm.tmem, kTmemCols);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = sm.tmem;
+  const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+
+  // cotangent of the next carry: thread v owns dS[v][.]
+  {
+    const float* g0 = p.ds_last ? p.ds_last + (static_cast<size_t>(bh) * kD + tid) * kD : nullptr;
+#pragma unroll
+    for (int c8 = 0; c8 < kPanD; ++c8) {
+      float vals[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) vals[e] = 0.f;
+      if (g0) {
+        const float4 a = *reinterpret_cast<const float4*>(g0 + c8 * 8);
+        const float4 c = *reinterpret_cast<const float4*>(g0 + c8 * 8 + 4);
+        vals[0] = a.x; vals[1] = a.y; vals[2] = a.z; vals[3] = a.w;
+        vals[4] = c.x; vals[5] = c.y; vals[6] = c.z; vals[7] = c.w;
+      }
+      tmem_st8(lane_base + kColDS + c8 * 8, vals);
+      sm.ds[c8 * kD + tid] = pack8_bf16(vals);
+    }
+    tmem_st_wait();
+  }
+
+  const size_t stride_t = static_cast<size_t>(p.H) * kD;
+  const size_t seq_base = (static_cast<size_t>(b) * p.T * p.H + h) * kD;
+  const uint8_t* drow = p.done ? p.done + static_cast<size_t>(b) * p.T : nullptr;
+  bool timed_out = false;
+
+  for (int it = 0; it < nchunks; ++it) {
+    const int c = nchunks - 1 - it;
+    const int t0 = c * kC;
+    const int valid = min(kC, p.T - t0);
+    const uint64_t dm = chunk_done_mask(drow, t0, p.T, lane);
+    __syncthreads();
+    load_chunk_decay(sm.cd, p.alpha, p.beta, static_cast<size_t>(b) * p.T, p.H, h, t0, p.T, dm, tid);
+    if (tid < kC) sm.dg[tid] = sm.dgam[tid] = 0.f;
+    if (tid < 4) sm.dgl[tid] = 0.f;
+
+    const size_t tile = seq_base + static_cast<size_t>(t0) * stride_t;
+    stage_panel_tile(sm.k, p.k + tile, stride_t, valid, tid);
+    stage_panel_tile(sm.q, p.q + tile, stride_t, valid, tid);
+    stage_panel_tile(sm.d_o, p.d_o + tile, stride_t, valid, tid);
+    stage_plain_tile(sm.r1, p.v + tile, stride_t, valid, tid);
+    stage_plain_tile(sm.r2, p.d_o + tile, stride_t, valid, tid);
+    {
+      const uint4* src = p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * kStateVecs;
+      for (int i = tid; i < kStateVecs; i += kThreads) sm.s[i] = __ldg(src + i);
+    }
+    fence_smem_to_async();
+    fence_before_sync();
+    __syncthreads();
+
+    // ---- MMAs A: K K^T, Q K^T, Y^T = S_in K^T, OI^T = S_in Q^T, X2^T = dS K^T ----
+    if (tid == 0) {
+      fence_after_sync();
+      const Operand ak{smem_u32(sm.k), kC, false}, aq{smem_u32(sm.q), kC, false};
+      const Operand as{smem_u32(sm.s), kD, false}, ads{smem_u32(sm.ds), kD, false};
+      const uint32_t id_64 = idesc_bf16(kC, kC, false, false), id_128 = idesc_bf16(kD, kC, false, false);
+      gemm(tmem + kColKK, ak, ak, id_64, kD / 16, false);
+      gemm(tmem + kColQK, aq, ak, id_64, kD / 16, false);
+      gemm(tmem + kColY, as, ak, id_128, kD / 16, false);
+      gemm(tmem + kColOI, as, aq, id_128, kD / 16, false);
+      gemm(tmem + kColX2, ads, ak, id_128, kD / 16, false);
+      commit(&sm.bar[0]);
+    }
+    if (!mbar_wait(&sm.bar[0], 0)) timed_out = true;
+    fence_after_sync();
+
+    // ---- epilogue A1: row threads -> beta L (both orientations), tril(G o QK^T) ----
+    {
+      const int lo = row_first_key(dm, row);
+      const float cum_t = sm.cd.cum[row], beta_t = sm.cd.beta[row];
+#pragma unroll
+      for (int jp = 0; jp < kPanC; ++jp) {
+        float kk[8], qk[8], pm[8];
+        tmem_ld8(lane_base + kColKK + jp * 8, kk);
+        tmem_ld8(lane_base + kColQK + jp * 8, qk);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int j = jp * 8 + e;
+          const bool in = (j >= lo && j <= row);
+          const float gtj = in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
+          pm[e] = gtj * qk[e];
+          const float bl = (j < row) ? beta_t * gtj * kk[e] : 0.f;
+          if (row_active) {
+            sm.lt[j * kC + row] = bl;
+            sm.l[row * kC + j] = bl;
+          }
+        }
+        if (row_active) sm.p[jp * kC + row] = pack8_bf16(pm);
+      }
+    }
+    __syncthreads();
+
+    // ---- epilogue A2: thread v recomputes its column of U; first dg term ----
+    {
+      float r[kC];
+      tmem_ld_row<kC>(lane_base + kColY, r);
+#pragma unroll
+      for (int t = 0; t < kC; ++t) r[t] = sm.cd.beta[t] * (bf16_at(sm.r1, t, tid) - sm.cd.g[t] * r[t]);
+      forward_substitute(r, sm.lt);
+#pragma unroll
+      for (int jp = 0; jp < kPanC; ++jp) {
+        float sc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sc[e] = r[jp * 8 + e] * sm.cd.gam[jp * 8 + e];
+        sm.u[jp * kD + tid] = pack8_bf16(r + jp * 8);
+        sm.ug[jp * kD + tid] = pack8_bf16(sc);
+      }
+      // dg_t += sum_v dO[t][v] (S_in q_t)[v]
+      tmem_ld_row<kC>(lane_base + kColOI, r);
+#pragma unroll
+      for (int t = 0; t < kC; ++t) r[t] *= bf16_at(sm.r2, t, tid);
+      warp_reduce64(r, lane);
+      atomicAdd(&sm.dg[2 * lane], r[0]);
+      atomicAdd(&sm.dg[2 * lane + 1], r[1]);
+    }
+    fence_smem_to_async();
+    fence_before_sync();
+    __syncthreads();
+
+    // ---- MMAs B: X1^T = dO^T P (128 x 64), DP = dO U^T (64 x 64) ----
+    if (tid == 0) {
+      fence_after_sync();
+      gemm(tmem + kColX1, Operand{smem_u32(sm.d_o), kC, true}, Operand{smem_u32(sm.p), kC, true},
+           idesc_bf16(kD, kC, true, true), kC / 16, false);
+      gemm(tmem + kColDP, Operand{smem_u32(sm.d_o), kC, false}, Operand{smem_u32(sm.u), kD, true},
+           idesc_bf16(kC, kC, false, true), kD / 16, false);
+      commit(&sm.bar[1]);
+    }
+    if (!mbar_wait(&sm.bar[1], 0)) timed_out = true;
+    fence_after_sync();
+
+    // ---- epilogue B: thread v: dU column, back substitution, dV, decay partials ----
+    {
+      float r[kC];
+      float ga[kC];
+      tmem_ld_row<kC>(lane_base + kColX2, ga);   // (dS k_j)[v]
+      tmem_ld_row<kC>(lane_base + kColX1, r);
+#pragma unroll
+      for (int jp = 0; jp < kPanC; ++jp) {
+        float uf[8];
+        unpack8_bf16(sm.u[jp * kD + tid], uf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int j = jp * 8 + e;
+          r[j] = fmaf(sm.cd.gam[j], ga[j], r[j]);   // dU[v][j]
+          ga[j] *= uf[e];                            // u_j[v] (dS k_j)[v]
+        }
+      }
+      warp_reduce64(ga, lane);
+      atomicAdd(&sm.dgam[2 * lane], ga[0]);
+      atomicAdd(&sm.dgam[2 * lane + 1], ga[1]);
+
+      backward_substitute(r, sm.l);                  // r = dUt[v][.]
+
+      // dR = beta dUt: the dV tile (row-major [t][v], staged in `lt`), -(g dR)^T panels,
+      // dUt^T panels, and dg_t -= dr_t . (S_in k_t)
+      tmem_ld_row<kC>(lane_base + kColY, ga);
+      __nv_bfloat16* dvt = reinterpret_cast<__nv_bfloat16*>(sm.lt);
+#pragma unroll
+      for (int tp = 0; tp < kPanC; ++tp) {
+        float ng[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int t = tp * 8 + e;
+          const float dr = sm.cd.beta[t] * r[t];
+          dvt[t * kD + tid] = __float2bfloat16(dr);
+          ng[e] = -sm.cd.g[t] * dr;
+          ga[t] *= -dr;
+        }
+        sm.r1[tp * kD + tid] = pack8_bf16(r + tp * 8);
+        sm.r2[tp * kD + tid] = pack8_bf16(ng);
+      }
+      warp_reduce64(ga, lane);
+      atomicAdd(&sm.dg[2 * lane], ga[0]);
+      atomicAdd(&sm.dg[2 * lane + 1], ga[1]);
+
+      // <dS, S_in> for the g_last gradient
+      float dot = 0.f;
+#pragma unroll
+      for (int c8 = 0; c8 < kPanD; ++c8) {
+        float d8[8], s8[8];
+        tmem_ld8(lane_base + kColDS + c8 * 8, d8);
+        tmem_ld_wait();
+        unpack8_bf16(sm.s[c8 * kD + tid], s8);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dot = fmaf(d8[e], s8[e], dot);
+      }
+#pragma unroll
+      for (int off = 16; off >= 1; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+      if (lane == 0) sm.dgl[warp] = dot;
+    }
+    fence_smem_to_async();
+    fence_before_sync();
+    __syncthreads();
+    {
+      // flush the dV tile
+      __nv_bfloat16* base = p.dv + tile;
+      const uint4* src = reinterpret_cast<const uint4*>(sm.lt);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const int vid = r * kThreads + tid;
+        const int trow = vid >> 4, seg = vid & 15;
+        if (trow < valid) *reinterpret_cast<uint4*>(base + trow * stride_t + seg * 8) = src[trow * 16 + seg];
+      }
+    }
+
+    // ---- MMA C: W = dUt U^T (64 x 64) ----
+    if (tid == 0) {
+      fence_after_sync();
+      gemm(tmem + kColW, Operand{smem_u32(sm.r1), kD, true}, Operand{smem_u32(sm.u), kD, true},
+           idesc_bf16(kC, kC, true, true), kD / 16, false);
+      commit(&sm.bar[0]);
+    }
+    if (!mbar_wait(&sm.bar[0], 1)) timed_out = true;
+    fence_after_sync();
+    __syncthreads();  // every thread has flushed its part of the dV tile before `lt` is reused
+
+    // ---- epilogue C: row threads: (dP o G), (dL o G), E, dbeta; g-scaled dO ----
+    {
+      uint4* dpg = reinterpret_cast<uint4*>(sm.lt);           // [j/8][t][8]
+      uint4* dlg = dpg + kPanC * kC;
+      const int lo = row_first_key(dm, row);
+      const float cum_t = sm.cd.cum[row], beta_t = sm.cd.beta[row];
+      float rs = 0.f, wtt = 0.f;
+#pragma unroll
+      for (int jp = 0; jp < kPanC; ++jp) {
+        float kk[8], qk[8], dp[8], w[8], a8[8], b8[8];
+        tmem_ld8(lane_base + kColKK + jp * 8, kk);
+        tmem_ld8(lane_base + kColQK + jp * 8, qk);
+        tmem_ld8(lane_base + kColDP + jp * 8, dp);
+        tmem_ld8(lane_base + kColW + jp * 8, w);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int j = jp * 8 + e;
+          const bool in = (j >= lo && j <= row);
+          const float gtj = in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
+          const float dl = (j < row) ? -beta_t * w[e] : 0.f;
+          if (j == row) wtt = w[e];
+          a8[e] = dp[e] * gtj;
+          b8[e] = dl * gtj;
+          const float ev = (dp[e] * qk[e] + dl * kk[e]) * gtj;
+          rs += ev;
+          if (row_active) sm.l[row * kC + j] = ev;
+        }
+        if (row_active) {
+          dpg[jp * kC + row] = pack8_bf16(a8);
+          dlg[jp * kC + row] = pack8_bf16(b8);
+        }
+      }
+      if (row_active) {
+        sm.rowsum[row] = rs;
+        if (row < valid) p.dbeta[(static_cast<size_t>(b) * p.T + t0 + row) * p.H + h] = beta_t > 0.f ? wtt / beta_t : 0.f;
+        const float gt = sm.cd.g[row];
+#pragma unroll
+        for (int pn = 0; pn < kPanD; ++pn) {
+          float f[8];
+          unpack8_bf16(sm.d_o[pn * kC + row], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] *= gt;
+          sm.d_o[pn * kC + row] = pack8_bf16(f);
+        }
+      }
+    }
+    fence_smem_to_async();
+    fence_before_sync();
+    __syncthreads();
+
+    // ---- MMAs D: dQ, dK (64 x 128), dS_in increment (128 x 128) ----
+    if (tid == 0) {
+      fence_after_sync();
+      const uint4* dpg_p = reinterpret_cast<const uint4*>(sm.lt);
+      const uint32_t dpg = smem_u32(dpg_p), dlg = smem_u32(dpg_p + kPanC * kC);
+      const Operand bk{smem_u32(sm.k), kC, true}, bq{smem_u32(sm.q), kC, true};
+      const Operand bs{smem_u32(sm.s), kD, true}, bds{smem_u32(sm.ds), kD, true};
+      const uint32_t id_km = idesc_bf16(kC, kD, false, true), id_mm = idesc_bf16(kC, kD, true, true);
+      // dQ = (dP o G) K + (g dO) S_in
+      gemm(tmem + kColDQ, Operand{dpg, kC, false}, bk, id_km, kC / 16, false);
+      gemm(tmem + kColDQ, Operand{smem_u32(sm.d_o), kC, false}, bs, id_km, kD / 16, true);
+      // dK = (dP o G)^T Q + (dL o G) K + (dL o G)^T K + (gam U) dS - (g dR) S_in
+      gemm(tmem + kColDK, Operand{dpg, kC, true}, bq, id_mm, kC / 16, false);
+      gemm(tmem + kColDK, Operand{dlg, kC, false}, bk, id_km, kC / 16, true);
+      gemm(tmem + kColDK, Operand{dlg, kC, true}, bk, id_mm, kC / 16, true);
+      gemm(tmem + kColDK, Operand{smem_u32(sm.ug), kD, true}, bds, id_mm, kD / 16, true);
+      gemm(tmem + kColDK, Operand{smem_u32(sm.r2), kD, true}, bs, id_mm, kD / 16, true);
+      // dS_in - g_last dS = (g dO)^T Q - (g dR)^T K
+      gemm(tmem + kColDelta, Operand{smem_u32(sm.d_o), kC, true}, bq, idesc_bf16(kD, kD, true, true), kC / 16, false);
+      gemm(tmem + kColDelta, Operand{smem_u32(sm.r2), kD, false}, bk, idesc_bf16(kD, kD, false, true), kC / 16, true);
+      commit(&sm.bar[1]);
+    }
+
+    // ---- decay gradients (overlaps the MMAs) ----
+    if (tid < kC) {
+      float cs = 0.f;
+#pragma unroll 8
+      for (int t = 0; t < kC; ++t) cs += sm.l[t * kC + tid];
+      sm.dcum[tid] = sm.rowsum[tid] - cs + sm.dg[tid] * sm.cd.g[tid] - sm.dgam[tid] * sm.cd.gam[tid];
+      sm.colsum[tid] = sm.dgam[tid] * sm.cd.gam[tid];
+    }
+    __syncthreads();
+    if (tid < 32) {
+      float extra = sm.colsum[2 * tid] + sm.colsum[2 * tid + 1];
+#pragma unroll
+      for (int off = 16; off >= 1; off >>= 1) extra += __shfl_xor_sync(0xffffffffu, extra, off);
+      extra += (sm.dgl[0] + sm.dgl[1] + sm.dgl[2] + sm.dgl[3]) * sm.cd.g[kC - 1];
+      float d0 = sm.dcum[2 * tid], d1 = sm.dcum[2 * tid + 1];
+      if (tid == 31) d1 += extra;
+      // suffix sums over the chunk
+      float s = d0 + d1;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const float o = __shfl_down_sync(0xffffffffu, s, off);
+        if (tid + off < 32) s += o;
+      }
+      const float dla0 = s, dla1 = s - d0;
+      const size_t base = (static_cast<size_t>(b) * p.T + t0) * p.H + h;
+      const int i0 = 2 * tid, i1 = 2 * tid + 1;
+      if (i0 < valid) p.dalpha[base + static_cast<size_t>(i0) * p.H] = ((dm >> i0) & 1ull) ? 0.f : dla0 / sm.cd.alpha[i0];
+      if (i1 < valid) p.dalpha[base + static_cast<size_t>(i1) * p.H] = ((dm >> i1) & 1ull) ? 0.f : dla1 / sm.cd.alpha[i1];
+    }
+
+    if (!mbar_wait(&sm.bar[1], 1)) timed_out = true;
+    fence_after_sync();
+
+    // ---- epilogue D: dq, dk rows; dS = g_last dS + increment ----
+    {
+      const bool store = row_active && row < valid;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        __nv_bfloat16* dst = (which == 0 ? p.dq : p.dk) + tile + static_cast<size_t>(row) * stride_t;
+        const uint32_t col = which == 0 ? kColDQ : kColDK;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          float acc[kC];
+          tmem_ld_row<kC>(lane_base + col + half * kC, acc);
+          if (store) {
+#pragma unroll
+            for (int pn = 0; pn < kPanC; ++pn)
+              reinterpret_cast<uint4*>(dst)[half * kPanC + pn] = pack8_bf16(acc + pn * 8);
+          }
+        }
+      }
+      const float g_last = sm.cd.g[kC - 1];
+      float* out0 = (c == 0 && p.ds0) ? p.ds0 + (static_cast<size_t>(bh) * kD + tid) * kD : nullptr;
+#pragma unroll
+      for (int c8 = 0; c8 < kPanD; ++c8) {
+        float s[8], inc[8];
+        tmem_ld8(lane_base + kColDS + c8 * 8, s);
+        tmem_ld8(lane_base + kColDelta + c8 * 8, inc);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s[e] = fmaf(g_last, s[e], inc[e]);
+        tmem_st8(lane_base + kColDS + c8 * 8, s);
+        sm.ds[c8 * kD + tid] = pack8_bf16(s);
+        if (out0) {
+          *reinterpret_cast<float4*>(out0 + c8 * 8) = make_float4(s[0], s[1], s[2], s[3]);
+          *reinterpret_cast<float4*>(out0 + c8 * 8 + 4) = make_float4(s[4], s[5], s[6], s[7]);
+        }
+      }
+      tmem_st_wait();
+    }
+  }
+
+  if (timed_out && p.status) atomicExch(p.status, 1);
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+}
+
+}  // namespace
+}  // namespace mxk
+
+extern "C" {
+
+int mxk_gdelta_bf16_bwd(const void* q, const void* k, const void* v, const float* alpha, const float* beta,
+                        const void* d_o, const void* chunk_states, const uint8_t* done, const float* ds_last,
+                        void* dq, void* dk, void* dv, float* dalpha, float* dbeta, float* ds0, int* status,
+                        int B, int T, int H, int d, mxk_stream_t stream) {
+  using namespace mxk;
+  using namespace mxk::gdelta;
+  if (!q || !k || !v || !alpha || !beta || !d_o || !chunk_states || !dq || !dk || !dv || !dalpha || !dbeta)
+    return MXK_ERR_NULL;
+  if (B <= 0 || T <= 0 || H <= 0 || static_cast<long long>(B) * H > 0x7fffffffLL) return MXK_ERR_DIMS;
+  if (d != kD) return MXK_ERR_UNSUPPORTED;
+  for (const void* ptr : {q, k, v, d_o, chunk_states, (const void*)dq, (const void*)dk, (const void*)dv,
+                          (const void*)ds_last, (const void*)ds0})
+    if (ptr && !aligned16(ptr)) return MXK_ERR_ALIGN;
+  BwdParams prm;
+  prm.q = static_cast<const __nv_bfloat16*>(q);
+  prm.k = static_cast<const __nv_bfloat16*>(k);
+  prm.v = static_cast<const __nv_bfloat16*>(v);
+  prm.alpha = alpha;
+  prm.beta = beta;
+  prm.d_o = static_cast<const __nv_bfloat16*>(d_o);
+  prm.chunk_states = static_cast<const uint4*>(chunk_states);
+  prm.done = done;
+  prm.ds_last = ds_last;
+  prm.dq = static_cast<__nv_bfloat16*>(dq);
+  prm.dk = static_cast<__nv_bfloat16*>(dk);
+  prm.dv = static_cast<__nv_bfloat16*>(dv);
+  prm.dalpha = dalpha;
+  prm.dbeta = dbeta;
+  prm.ds0 = ds0;
+  prm.status = status;
+  prm.B = B; prm.T = T; prm.H = H;
+  cudaError_t e = cudaFuncSetAttribute(gdelta_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(sizeof(BwdSmem)));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  gdelta_bwd_kernel<<<B * H, kThreads, sizeof(BwdSmem), static_cast<cudaStream_t>(stream)>>>(prm);
+  return launch_status();
+}
+
+}  // extern "C"

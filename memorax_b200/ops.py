@@ -253,3 +253,39 @@ def gdelta_fwd(q, k, v, alpha, beta, s0=None, done=None, save_states=False, chec
     if check:
         _check_status(status, "mxk_gdelta_bf16_fwd")
     return o, s_last, states
+
+
+def gdelta_bwd(q, k, v, alpha, beta, d_o, chunk_states, done=None, ds_last=None, check=False):
+    """Cotangents ``(dq, dk, dv, dalpha, dbeta, ds0)`` of :func:`gdelta_fwd`."""
+    q, k, v, d_o = (_dev(t, torch.bfloat16, n) for t, n in ((q, "q"), (k, "k"), (v, "v"), (d_o, "d_o")))
+    alpha, beta = _dev(alpha, torch.float32, "alpha"), _dev(beta, torch.float32, "beta")
+    ds_last = _dev(ds_last, torch.float32, "ds_last")
+    bsz, steps, heads, dim = q.shape
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    dalpha, dbeta = torch.empty_like(alpha), torch.empty_like(beta)
+    ds0 = torch.empty(bsz, heads, dim, dim, dtype=torch.float32, device=q.device)
+    status = _status_word(q.device) if check else None
+    _lib.call("mxk_gdelta_bf16_bwd", _ptr(q), _ptr(k), _ptr(v), _ptr(alpha), _ptr(beta), _ptr(d_o),
+              _ptr(chunk_states), _ptr(_done_bytes(done)), _ptr(ds_last), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dalpha),
+              _ptr(dbeta), _ptr(ds0), _ptr(status), bsz, steps, heads, dim, _stream())
+    if check:
+        _check_status(status, "mxk_gdelta_bf16_bwd")
+    return dq, dk, dv, dalpha, dbeta, ds0
+
+
+class GatedDelta(torch.autograd.Function):
+    """(q, k, v, alpha, beta, s0, done) -> (o, s_last)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, alpha, beta, s0, done):
+        o, s_last, states = gdelta_fwd(q, k, v, alpha, beta, s0, done, save_states=True)
+        ctx.save_for_backward(q, k, v, alpha, beta, states, done)
+        ctx.has_state = s0 is not None
+        return o, s_last
+
+    @staticmethod
+    def backward(ctx, d_o, ds_last):
+        q, k, v, alpha, beta, states, done = ctx.saved_tensors
+        dq, dk, dv, dalpha, dbeta, ds0 = gdelta_bwd(q, k, v, alpha, beta, d_o, states, done, ds_last)
+        return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dalpha.to(alpha.dtype), dbeta.to(beta.dtype),
+                ds0 if ctx.has_state else None, None)

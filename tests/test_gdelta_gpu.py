@@ -56,3 +56,41 @@ def test_gdelta_split_sequence_matches_single_call():
     o1, s1, _ = ops.gdelta_fwd(cu(q[:, a]), cu(k[:, a]), cu(v[:, a]), cu(alpha[:, a]), cu(beta[:, a]), cu(s0), cu(done[:, a]))
     o2, s2, _ = ops.gdelta_fwd(cu(q[:, b]), cu(k[:, b]), cu(v[:, b]), cu(alpha[:, b]), cu(beta[:, b]), s1, cu(done[:, b]))
     assert torch.equal(torch.cat([o1, o2], 1), o) and torch.equal(s2, s_last)
+
+
+@pytest.mark.parametrize("shape,p_done,zero_state", CASES)
+def test_gdelta_bwd(shape, p_done, zero_state):
+    from memorax_b200 import ops
+    q, k, v, alpha, beta, s0, done = make_case(sum(shape) + 7, *shape, p_done, zero_state)
+    gen = torch.Generator().manual_seed(5)
+    d_o = torch.randn(*q.shape, generator=gen).bfloat16()
+    ds_last = torch.randn(*s0.shape, generator=gen) * 0.2
+    leaves = [t.double().requires_grad_() for t in (q, k, v, alpha, beta, s0)]
+    o_ref, s_ref = mo.gdelta_seq(*leaves, done.double())
+    ((o_ref * d_o.double()).sum() + (s_ref * ds_last.double()).sum()).backward()
+    cu = lambda t: t.cuda()
+    _, _, states = ops.gdelta_fwd(cu(q), cu(k), cu(v), cu(alpha), cu(beta), cu(s0), cu(done), save_states=True,
+                                  check=True)
+    outs = ops.gdelta_bwd(cu(q), cu(k), cu(v), cu(alpha), cu(beta), cu(d_o), states, cu(done), cu(ds_last), check=True)
+    for got, leaf, name in zip(outs, leaves, ["dq", "dk", "dv", "dalpha", "dbeta", "ds0"]):
+        ref = leaf.grad
+        if name == "dalpha":   # steps that start an episode ignore alpha
+            assert float(got.cpu()[done[:, :, None].expand_as(got)].abs().max() if done.any() else 0.0) == 0.0
+        # gradients here are O(1..30); 2e-2 max-abs is applied relative to each tensor's scale
+        tol = ATOL * max(1.0, float(ref.abs().max()))
+        err = max_abs(got.float(), ref)
+        assert err <= tol, f"{name}: {err:.4f} > {tol:.4f} (ref max {float(ref.abs().max()):.3f})"
+
+
+def test_gdelta_autograd_function():
+    from memorax_b200 import ops
+    q, k, v, alpha, beta, s0, done = make_case(11, 2, 96, 2, 0.03, False)
+    w = torch.randn(*q.shape, generator=torch.Generator().manual_seed(1))
+    leaves = [t.double().requires_grad_() for t in (q, k, v, alpha, beta, s0)]
+    o_ref, _ = mo.gdelta_seq(*leaves, done.double())
+    (o_ref * w.double()).sum().backward()
+    dev = [t.cuda().requires_grad_() for t in (q, k, v, alpha, beta, s0)]
+    o, _ = ops.GatedDelta.apply(*dev, done.cuda())
+    (o.float() * w.cuda()).sum().backward()
+    for got, leaf in zip(dev, leaves):
+        assert max_abs(got.grad.float(), leaf.grad) <= ATOL * max(1.0, float(leaf.grad.abs().max()))
