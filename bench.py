@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the sequence-mixing hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c4|c1]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c1]
     python bench.py --impl reference ...      # CPU arm: the oracle port, host cores
 
 A step is one pass of the hot path over one batch of seeded synthetic input:
@@ -199,7 +199,63 @@ class LinRecC1:
             return mo.linrec_seq(x["a"], x["b"], x["h0"], x["done"].float())[0]
 
 
-WORKLOADS = {"c2": LinAttnC2, "c4": LruC4, "c1": LinRecC1}
+class GDeltaC3:
+    """Gated delta rule fwd+bwd: B=128, H=8, T=512, d=128, bf16 in, fp32 state
+    (zero-initialised), q,k L2-normalised, beta=sigmoid(N), alpha=exp(-softplus(N)),
+    done ~ Bernoulli(0.005)."""
+    name = "c3_gated_delta_rule_fwd_bwd"
+    dtype = "bf16"
+    B, H, T, D = 128, 8, 512, 128
+    p_done = 0.005
+    seed = 1234 + 3
+    dominant = "gdelta_bwd_kernel"
+    launches_per_step = 2
+    dominant_traffic_bytes = None
+    cpu_sample_batch = 4
+
+    def __init__(self, batch=None):
+        self.B = batch or self.B
+
+    def tokens(self):
+        return self.B * self.T
+
+    def host_inputs(self, seed_offset=0):
+        g = torch.Generator().manual_seed(self.seed + seed_offset)
+        shp = (self.B, self.T, self.H, self.D)
+        mk = lambda *s: torch.randn(*s, generator=g)
+        nrm = lambda x: x / x.norm(dim=-1, keepdim=True)
+        return dict(q=nrm(mk(*shp)).bfloat16(), k=nrm(mk(*shp)).bfloat16(), v=mk(*shp).bfloat16(),
+                    d_o=mk(*shp).bfloat16(), beta=torch.sigmoid(mk(*shp[:3])),
+                    alpha=torch.exp(-torch.nn.functional.softplus(mk(*shp[:3]))),
+                    done=(torch.rand(self.B, self.T, generator=g) < self.p_done).to(torch.uint8))
+
+    def algorithmic_bytes(self):
+        th = self.B * self.T * self.H
+        state = self.B * self.H * self.D * self.D * 4
+        # q,k,v,o bf16 + alpha,beta fp32 | q,k,v,do,dq,dk,dv bf16 + alpha,beta,dalpha,dbeta fp32
+        return {"gdelta_fwd_kernel": th * (4 * 256 + 8) + state, "gdelta_bwd_kernel": th * (7 * 256 + 16) + state}
+
+    def step(self, x, ops, mark=None):
+        o, s_last, states = ops.gdelta_fwd(x["q"], x["k"], x["v"], x["alpha"], x["beta"], None, x["done"],
+                                           save_states=True)
+        if mark:
+            mark[0].record()
+        outs = ops.gdelta_bwd(x["q"], x["k"], x["v"], x["alpha"], x["beta"], x["d_o"], states, x["done"])
+        if mark:
+            mark[1].record()
+        return (o, s_last) + tuple(outs)
+
+    def cpu_step(self, x):
+        """Sequential recurrence (the definition of the op) with autograd, fp32, host cores."""
+        from oracle import memoroid_oracle as mo
+        q, k, v = (x[n].float().requires_grad_() for n in ("q", "k", "v"))
+        s0 = torch.zeros(q.shape[0], self.H, self.D, self.D)
+        o, _ = mo.gdelta_seq(q, k, v, x["alpha"], x["beta"], s0, x["done"].float())
+        (o * x["d_o"].float()).sum().backward()
+        return o
+
+
+WORKLOADS = {"c2": LinAttnC2, "c3": GDeltaC3, "c4": LruC4, "c1": LinRecC1}
 
 
 # ------------------------------------------------------------ clock sampling

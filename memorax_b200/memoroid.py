@@ -215,3 +215,57 @@ class LinearAttentionCell(MemoroidCellBase):
         o = o.reshape(*o.shape[:2], -1).to(inputs.dtype)
         y = self.output_projection(self.norm(o))
         return (s_last[:, None], z_last[:, None]), y
+
+
+# ------------------------------------------------------- gated delta rule
+class DeltaNetCell(MemoroidCellBase):
+    """Gated delta-rule mixer.  The reference has no such cell; this one follows
+    its cell protocol.  As a monoid the element is
+    ``(alpha (I - beta k k^T), beta v k^T)`` with operator
+    ``((M_i, U_i), (M_j, U_j)) -> (M_i M_j, U_i M_j + U_j)``; the carry keeps
+    only the state ``S (B,1,H,d_v,d_k)`` (the map leaf is O(d_k^2) per step and
+    no read-out uses it).  ``head_dim`` must be 128."""
+
+    def __init__(self, features, head_dim, num_heads, in_features=None):
+        super().__init__()
+        self.features, self.head_dim, self.num_heads = features, head_dim, num_heads
+        in_features = in_features or features
+        hidden = num_heads * head_dim
+        self.query = nn.Linear(in_features, hidden, bias=False)
+        self.key = nn.Linear(in_features, hidden, bias=False)
+        self.value = nn.Linear(in_features, hidden, bias=False)
+        self.gate = nn.Linear(in_features, 2 * num_heads)   # -> (beta logits, decay logits)
+        self.norm = nn.RMSNorm(hidden)
+        self.output_projection = nn.Linear(hidden, features)
+
+    def _heads(self, t):
+        return t.view(*t.shape[:2], self.num_heads, self.head_dim)
+
+    def forward(self, x, **kwargs):
+        """-> factored elements (k, v, alpha, beta); k is L2-normalised per head."""
+        k = torch.nn.functional.normalize(self._heads(self.key(x)).float(), dim=-1)
+        v = self._heads(self.value(x))
+        b_logit, a_logit = self.gate(x).float().chunk(2, dim=-1)
+        return k, v, torch.exp(-torch.nn.functional.softplus(a_logit)), torch.sigmoid(b_logit)
+
+    def binary_operator(self, a, b):
+        m_i, u_i = a
+        m_j, u_j = b
+        return m_i @ m_j, u_i @ m_j + u_j
+
+    def read(self, h, x, **kwargs):
+        raise RuntimeError("the read-out o_t = S_t q_t is fused into scan()")
+
+    def initialize_carry(self, key, input_shape):
+        *batch, _ = input_shape
+        return (torch.zeros(*batch, 1, self.num_heads, self.head_dim, self.head_dim),)
+
+    def scan(self, z, initial_carry, done, inputs):
+        k, v, alpha, beta = z
+        q = torch.nn.functional.normalize(self._heads(self.query(inputs)).float(), dim=-1)
+        (s0,) = initial_carry
+        bf = torch.bfloat16
+        o, s_last = ops.GatedDelta.apply(q.to(bf), k.to(bf), v.to(bf), alpha.contiguous(), beta.contiguous(),
+                                         s0[:, 0].contiguous(), done)
+        o = o.reshape(*o.shape[:2], -1).to(inputs.dtype)
+        return (s_last[:, None],), self.output_projection(self.norm(o))

@@ -1,0 +1,68 @@
+"""The host-side mirror of the reference interface: Memoroid(cell)(inputs, done,
+initial_carry) -> (next_carry, y) with the reference's carry pytrees, carry
+threading across calls (memoroid.py:89) and gradients through the CUDA ops."""
+import pytest
+import torch
+
+from oracle import memoroid_oracle as mo
+
+pytestmark = pytest.mark.gpu
+
+
+def _done(bsz, steps, p=0.05, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.rand(bsz, steps, generator=g) < p).cuda()
+
+
+def test_lru_module_matches_oracle_and_threads_carry():
+    from memorax_b200.memoroid import LRUCell, Memoroid
+    torch.manual_seed(0)
+    cell = LRUCell(features=8, hidden_dim=32, r_min=0.5, r_max=0.99, max_phase=0.6).cuda()
+    model = Memoroid(cell)
+    x, done = torch.randn(3, 20, 8, device="cuda"), _done(3, 20)
+    (h_last, a_last), y = model(x, done)
+    assert h_last.shape == (3, 1, 32) and a_last.shape == (3, 1, 32) and h_last.dtype == torch.complex64
+    assert y.shape == (3, 20, 8)
+    # oracle on the same elements
+    state, lam = cell(x)
+    h_ref, a_ref = mo.linrec_seq(lam.detach().cpu().to(torch.complex128), state.detach().cpu().to(torch.complex128),
+                                 torch.zeros(3, 32, dtype=torch.complex128), done.cpu().double())
+    assert float((h_last[:, 0].cpu() - h_ref[:, -1]).abs().max()) <= 1e-5 * float(h_ref.abs().max())
+    assert float((a_last[:, 0].cpu() - a_ref).abs().max()) <= 1e-5
+    # one call == two calls threading the carry
+    c1, y1 = model(x[:, :9], done[:, :9])
+    c2, y2 = model(x[:, 9:], done[:, 9:], c1)
+    assert torch.allclose(torch.cat([y1, y2], 1), y, atol=1e-5)
+    assert torch.allclose(c2[0], h_last, atol=1e-5)
+    # gradients reach every parameter
+    y.square().mean().backward()
+    for name, prm in cell.named_parameters():
+        assert prm.grad is not None and torch.isfinite(prm.grad).all(), name
+
+
+def test_mingru_module_default_carry_is_neg_inf_and_finite():
+    from memorax_b200.memoroid import MinGRUCell, Memoroid
+    torch.manual_seed(1)
+    model = Memoroid(MinGRUCell(features=64, in_features=16)).cuda()
+    carry = model.initialize_carry(None, (4, 16))
+    assert torch.isneginf(carry[0]).all() and carry[0].shape == (4, 1, 64)
+    x, done = torch.randn(4, 33, 16, device="cuda"), _done(4, 33)
+    (x_last, d_last), y = model(x, done)
+    assert torch.isfinite(y).all() and y.shape == (4, 33, 64) and x_last.shape == (4, 1, 64)
+    y.sum().backward()
+    assert all(torch.isfinite(p.grad).all() for p in model.parameters())
+
+
+def test_linear_attention_and_deltanet_modules_run_and_thread_carry():
+    from memorax_b200.memoroid import DeltaNetCell, LinearAttentionCell, Memoroid
+    torch.manual_seed(2)
+    for cell in (LinearAttentionCell(features=32, head_dim=64, num_heads=2), DeltaNetCell(features=32, head_dim=128, num_heads=2)):
+        model = Memoroid(cell).cuda()
+        x, done = torch.randn(2, 128, 32, device="cuda"), _done(2, 128, 0.02)
+        carry, y = model(x, done)
+        assert y.shape == (2, 128, 32) and all(c.shape[1] == 1 for c in carry)
+        c1, y1 = model(x[:, :64], done[:, :64])
+        c2, y2 = model(x[:, 64:], done[:, 64:], c1)
+        assert torch.allclose(torch.cat([y1, y2], 1), y, atol=2e-2)
+        y.square().mean().backward()
+        assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())
