@@ -41,7 +41,7 @@ struct FwdSmem {
   uint4 u[kPanC * kD];        // U^T           [j/8][v][8]
   uint4 ug[kPanC * kD];       // (gam U)^T
   uint4 p[kPanC * kC];        // tril(G o QK^T) [j/8][t][8]
-  float lt[kC * kC];          // lt[j][t] = beta_t L_tj
+  float lt[kC * kC];          // lt[j][t] = -beta_t L_tj
   ChunkDecay cd;
   uint64_t bar[2];
   uint32_t tmem;
@@ -134,32 +134,35 @@ __global__ void __launch_bounds__(kThreads) gdelta_fwd_kernel(const FwdParams p)
       const int lo = row_first_key(dm, row);
       const float cum_t = sm.cd.cum[row], beta_t = sm.cd.beta[row];
 #pragma unroll
-      for (int jp = 0; jp < kPanC; ++jp) {
-        float kk[8], qk[8], pm[8];
-        tmem_ld8(lane_base + kColKK + jp * 8, kk);
-        tmem_ld8(lane_base + kColQK + jp * 8, qk);
-        tmem_ld_wait();
+      for (int half = 0; half < 2; ++half) {
+        float kk[32], qk[32];
+        tmem_ld_row<32>(lane_base + kColKK + half * 32, kk);
+        tmem_ld_row<32>(lane_base + kColQK + half * 32, qk);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int j = jp * 8 + e;
-          const bool in = (j >= lo && j <= row);
-          const float gtj = in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
-          pm[e] = gtj * qk[e];
-          if (row_active) sm.lt[j * kC + row] = (j < row) ? beta_t * gtj * kk[e] : 0.f;
+        for (int jq = 0; jq < 4; ++jq) {
+          float pm[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int j = half * 32 + jq * 8 + e;
+            const bool in = (j >= lo && j <= row);
+            const float gtj = in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
+            pm[e] = gtj * qk[jq * 8 + e];
+            if (row_active) sm.lt[j * kC + row] = (j < row) ? -beta_t * gtj * kk[jq * 8 + e] : 0.f;
+          }
+          if (row_active) sm.p[(half * 4 + jq) * kC + row] = pack8_bf16(pm);
         }
-        if (row_active) sm.p[jp * kC + row] = pack8_bf16(pm);
       }
     }
     __syncthreads();
 
     // ---- epilogue 1b: thread v solves for its column of U ----
     {
-      float r[kC];
+      __align__(8) float r[kC];
       tmem_ld_row<kC>(lane_base + kColY, r);
 #pragma unroll
       for (int t = 0; t < kC; ++t)
         r[t] = sm.cd.beta[t] * (bf16_at(sm.vplain, t, tid) - sm.cd.g[t] * r[t]);
-      forward_substitute(r, sm.lt);
+      forward_substitute(reinterpret_cast<float2*>(r), sm.lt);
 #pragma unroll
       for (int jp = 0; jp < kPanC; ++jp) {
         float sc[8];
@@ -188,14 +191,13 @@ __global__ void __launch_bounds__(kThreads) gdelta_fwd_kernel(const FwdParams p)
     {
       __nv_bfloat16* otile = reinterpret_cast<__nv_bfloat16*>(sm.vplain);
 #pragma unroll
-      for (int tp = 0; tp < kPanC; ++tp) {
-        float oi[8], oa[8];
-        tmem_ld8(lane_base + kColOI + tp * 8, oi);
-        tmem_ld8(lane_base + kColOA + tp * 8, oa);
-        tmem_ld_wait();
+      for (int half = 0; half < 2; ++half) {
+        float oi[32], oa[32];
+        tmem_ld_row<32>(lane_base + kColOI + half * 32, oi);
+        tmem_ld_row<32>(lane_base + kColOA + half * 32, oa);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int t = tp * 8 + e;
+        for (int e = 0; e < 32; ++e) {
+          const int t = half * 32 + e;
           otile[t * kD + tid] = __float2bfloat16(fmaf(sm.cd.g[t], oi[e], oa[e]));
         }
       }
@@ -203,18 +205,20 @@ __global__ void __launch_bounds__(kThreads) gdelta_fwd_kernel(const FwdParams p)
       const bool last = (c == nchunks - 1);
       float* sl = (last && p.s_last) ? p.s_last + (static_cast<size_t>(bh) * kD + tid) * kD : nullptr;
 #pragma unroll
-      for (int c8 = 0; c8 < kPanD; ++c8) {
-        float s[8], ds[8];
-        tmem_ld8(lane_base + kColS + c8 * 8, s);
-        tmem_ld8(lane_base + kColDS + c8 * 8, ds);
-        tmem_ld_wait();
+      for (int q4 = 0; q4 < 4; ++q4) {
+        float s[32], ds[32];
+        tmem_ld_row<32>(lane_base + kColS + q4 * 32, s);
+        tmem_ld_row<32>(lane_base + kColDS + q4 * 32, ds);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) s[e] = fmaf(g_last, s[e], ds[e]);
-        tmem_st8(lane_base + kColS + c8 * 8, s);
-        sm.s[c8 * kD + tid] = pack8_bf16(s);
-        if (sl) {
-          *reinterpret_cast<float4*>(sl + c8 * 8) = make_float4(s[0], s[1], s[2], s[3]);
-          *reinterpret_cast<float4*>(sl + c8 * 8 + 4) = make_float4(s[4], s[5], s[6], s[7]);
+        for (int e = 0; e < 32; ++e) s[e] = fmaf(g_last, s[e], ds[e]);
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) {
+          tmem_st8(lane_base + kColS + q4 * 32 + c8 * 8, s + c8 * 8);
+          sm.s[(q4 * 4 + c8) * kD + tid] = pack8_bf16(s + c8 * 8);
+          if (sl) {
+            *reinterpret_cast<float4*>(sl + q4 * 32 + c8 * 8) = make_float4(s[c8 * 8], s[c8 * 8 + 1], s[c8 * 8 + 2], s[c8 * 8 + 3]);
+            *reinterpret_cast<float4*>(sl + q4 * 32 + c8 * 8 + 4) = make_float4(s[c8 * 8 + 4], s[c8 * 8 + 5], s[c8 * 8 + 6], s[c8 * 8 + 7]);
+          }
         }
       }
       tmem_st_wait();

@@ -56,8 +56,8 @@ struct BwdSmem {
   uint4 u[kPanC * kD];      // U^T                [j/8][v][8]
   uint4 ug[kPanC * kD];     // (gam U)^T
   uint4 p[kPanC * kC];      // tril(G o QK^T)     [j/8][t][8]
-  float l[kC * kC];         // l[t][j] = beta_t L_tj         -> E[t][j]
-  float lt[kC * kC];        // lt[j][t] = beta_t L_tj        -> dV tile -> (dP o G), (dL o G) panels
+  float l[kC * kC];         // l[t][j] = -beta_t L_tj        -> E[t][j]
+  float lt[kC * kC];        // lt[j][t] = -beta_t L_tj       -> dV tile -> (dP o G), (dL o G) panels
   ChunkDecay cd;
   float dg[kC], dgam[kC], rowsum[kC], colsum[kC], dcum[kC];
   float dgl[4];
@@ -84,23 +84,6 @@ __device__ __forceinline__ void warp_reduce64(float* vals, int lane) {
         const float keep = upper ? vals[i + half] : vals[i];
         vals[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
       }
-    }
-  }
-}
-
-// r[t] holds dU on entry and A^-T dU on exit; l[i * 64 + t] = beta_i L_it (zero for t >= i).
-__device__ __forceinline__ void backward_substitute(float* r, const float* l) {
-  const float4* l4 = reinterpret_cast<const float4*>(l);
-#pragma unroll
-  for (int i = kC - 1; i >= 1; --i) {
-    const float xi = r[i];
-#pragma unroll
-    for (int m = 0; m <= (i - 1) / 4; ++m) {
-      const float4 c = l4[i * (kC / 4) + m];
-      r[4 * m + 0] = fmaf(-c.x, xi, r[4 * m + 0]);
-      r[4 * m + 1] = fmaf(-c.y, xi, r[4 * m + 1]);
-      r[4 * m + 2] = fmaf(-c.z, xi, r[4 * m + 2]);
-      r[4 * m + 3] = fmaf(-c.w, xi, r[4 * m + 3]);
     }
   }
 }
@@ -196,35 +179,38 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
       const int lo = row_first_key(dm, row);
       const float cum_t = sm.cd.cum[row], beta_t = sm.cd.beta[row];
 #pragma unroll
-      for (int jp = 0; jp < kPanC; ++jp) {
-        float kk[8], qk[8], pm[8];
-        tmem_ld8(lane_base + kColKK + jp * 8, kk);
-        tmem_ld8(lane_base + kColQK + jp * 8, qk);
-        tmem_ld_wait();
+      for (int half = 0; half < 2; ++half) {
+        float kk[32], qk[32];
+        tmem_ld_row<32>(lane_base + kColKK + half * 32, kk);
+        tmem_ld_row<32>(lane_base + kColQK + half * 32, qk);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int j = jp * 8 + e;
-          const bool in = (j >= lo && j <= row);
-          const float gtj = in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
-          pm[e] = gtj * qk[e];
-          const float bl = (j < row) ? beta_t * gtj * kk[e] : 0.f;
-          if (row_active) {
-            sm.lt[j * kC + row] = bl;
-            sm.l[row * kC + j] = bl;
+        for (int jq = 0; jq < 4; ++jq) {
+          float pm[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int j = half * 32 + jq * 8 + e;
+            const bool in = (j >= lo && j <= row);
+            const float gtj = in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
+            pm[e] = gtj * qk[jq * 8 + e];
+            const float bl = (j < row) ? -beta_t * gtj * kk[jq * 8 + e] : 0.f;
+            if (row_active) {
+              sm.lt[j * kC + row] = bl;
+              sm.l[row * kC + j] = bl;
+            }
           }
+          if (row_active) sm.p[(half * 4 + jq) * kC + row] = pack8_bf16(pm);
         }
-        if (row_active) sm.p[jp * kC + row] = pack8_bf16(pm);
       }
     }
     __syncthreads();
 
     // ---- epilogue A2: thread v recomputes its column of U; first dg term ----
     {
-      float r[kC];
+      __align__(8) float r[kC];
       tmem_ld_row<kC>(lane_base + kColY, r);
 #pragma unroll
       for (int t = 0; t < kC; ++t) r[t] = sm.cd.beta[t] * (bf16_at(sm.r1, t, tid) - sm.cd.g[t] * r[t]);
-      forward_substitute(r, sm.lt);
+      forward_substitute(reinterpret_cast<float2*>(r), sm.lt);
 #pragma unroll
       for (int jp = 0; jp < kPanC; ++jp) {
         float sc[8];
@@ -259,7 +245,7 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
 
     // ---- epilogue B: thread v: dU column, back substitution, dV, decay partials ----
     {
-      float r[kC];
+      __align__(8) float r[kC];
       float ga[kC];
       tmem_ld_row<kC>(lane_base + kColX2, ga);   // (dS k_j)[v]
       tmem_ld_row<kC>(lane_base + kColX1, r);
@@ -278,7 +264,7 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
       atomicAdd(&sm.dgam[2 * lane], ga[0]);
       atomicAdd(&sm.dgam[2 * lane + 1], ga[1]);
 
-      backward_substitute(r, sm.l);                  // r = dUt[v][.]
+      backward_substitute(reinterpret_cast<float2*>(r), sm.l);                  // r = dUt[v][.]
 
       // dR = beta dUt: the dV tile (row-major [t][v], staged in `lt`), -(g dR)^T panels,
       // dUt^T panels, and dg_t -= dr_t . (S_in k_t)
@@ -305,13 +291,16 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
       // <dS, S_in> for the g_last gradient
       float dot = 0.f;
 #pragma unroll
-      for (int c8 = 0; c8 < kPanD; ++c8) {
-        float d8[8], s8[8];
-        tmem_ld8(lane_base + kColDS + c8 * 8, d8);
-        tmem_ld_wait();
-        unpack8_bf16(sm.s[c8 * kD + tid], s8);
+      for (int q4 = 0; q4 < 4; ++q4) {
+        float d32[32];
+        tmem_ld_row<32>(lane_base + kColDS + q4 * 32, d32);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) dot = fmaf(d8[e], s8[e], dot);
+        for (int c8 = 0; c8 < 4; ++c8) {
+          float s8[8];
+          unpack8_bf16(sm.s[(q4 * 4 + c8) * kD + tid], s8);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) dot = fmaf(d32[c8 * 8 + e], s8[e], dot);
+        }
       }
 #pragma unroll
       for (int off = 16; off >= 1; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
@@ -351,29 +340,32 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
       const float cum_t = sm.cd.cum[row], beta_t = sm.cd.beta[row];
       float rs = 0.f, wtt = 0.f;
 #pragma unroll
-      for (int jp = 0; jp < kPanC; ++jp) {
-        float kk[8], qk[8], dp[8], w[8], a8[8], b8[8];
-        tmem_ld8(lane_base + kColKK + jp * 8, kk);
-        tmem_ld8(lane_base + kColQK + jp * 8, qk);
-        tmem_ld8(lane_base + kColDP + jp * 8, dp);
-        tmem_ld8(lane_base + kColW + jp * 8, w);
-        tmem_ld_wait();
+      for (int q4 = 0; q4 < 4; ++q4) {
+        float kk[16], qk[16], dp[16], w[16];
+        tmem_ld_row<16>(lane_base + kColKK + q4 * 16, kk);
+        tmem_ld_row<16>(lane_base + kColQK + q4 * 16, qk);
+        tmem_ld_row<16>(lane_base + kColDP + q4 * 16, dp);
+        tmem_ld_row<16>(lane_base + kColW + q4 * 16, w);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int j = jp * 8 + e;
-          const bool in = (j >= lo && j <= row);
-          const float gtj = in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
-          const float dl = (j < row) ? -beta_t * w[e] : 0.f;
-          if (j == row) wtt = w[e];
-          a8[e] = dp[e] * gtj;
-          b8[e] = dl * gtj;
-          const float ev = (dp[e] * qk[e] + dl * kk[e]) * gtj;
-          rs += ev;
-          if (row_active) sm.l[row * kC + j] = ev;
-        }
-        if (row_active) {
-          dpg[jp * kC + row] = pack8_bf16(a8);
-          dlg[jp * kC + row] = pack8_bf16(b8);
+        for (int jq = 0; jq < 2; ++jq) {
+          float a8[8], b8[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int x = jq * 8 + e, j = q4 * 16 + x;
+            const bool in = (j >= lo && j <= row);
+            const float gtj = in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
+            const float dl = (j < row) ? -beta_t * w[x] : 0.f;
+            if (j == row) wtt = w[x];
+            a8[e] = dp[x] * gtj;
+            b8[e] = dl * gtj;
+            const float ev = (dp[x] * qk[x] + dl * kk[x]) * gtj;
+            rs += ev;
+            if (row_active) sm.l[row * kC + j] = ev;
+          }
+          if (row_active) {
+            dpg[(q4 * 2 + jq) * kC + row] = pack8_bf16(a8);
+            dlg[(q4 * 2 + jq) * kC + row] = pack8_bf16(b8);
+          }
         }
       }
       if (row_active) {
@@ -471,18 +463,20 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
       const float g_last = sm.cd.g[kC - 1];
       float* out0 = (c == 0 && p.ds0) ? p.ds0 + (static_cast<size_t>(bh) * kD + tid) * kD : nullptr;
 #pragma unroll
-      for (int c8 = 0; c8 < kPanD; ++c8) {
-        float s[8], inc[8];
-        tmem_ld8(lane_base + kColDS + c8 * 8, s);
-        tmem_ld8(lane_base + kColDelta + c8 * 8, inc);
-        tmem_ld_wait();
+      for (int q4 = 0; q4 < 4; ++q4) {
+        float s[32], inc[32];
+        tmem_ld_row<32>(lane_base + kColDS + q4 * 32, s);
+        tmem_ld_row<32>(lane_base + kColDelta + q4 * 32, inc);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) s[e] = fmaf(g_last, s[e], inc[e]);
-        tmem_st8(lane_base + kColDS + c8 * 8, s);
-        sm.ds[c8 * kD + tid] = pack8_bf16(s);
-        if (out0) {
-          *reinterpret_cast<float4*>(out0 + c8 * 8) = make_float4(s[0], s[1], s[2], s[3]);
-          *reinterpret_cast<float4*>(out0 + c8 * 8 + 4) = make_float4(s[4], s[5], s[6], s[7]);
+        for (int e = 0; e < 32; ++e) s[e] = fmaf(g_last, s[e], inc[e]);
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) {
+          tmem_st8(lane_base + kColDS + q4 * 32 + c8 * 8, s + c8 * 8);
+          sm.ds[(q4 * 4 + c8) * kD + tid] = pack8_bf16(s + c8 * 8);
+          if (out0) {
+            *reinterpret_cast<float4*>(out0 + q4 * 32 + c8 * 8) = make_float4(s[c8 * 8], s[c8 * 8 + 1], s[c8 * 8 + 2], s[c8 * 8 + 3]);
+            *reinterpret_cast<float4*>(out0 + q4 * 32 + c8 * 8 + 4) = make_float4(s[c8 * 8 + 4], s[c8 * 8 + 5], s[c8 * 8 + 6], s[c8 * 8 + 7]);
+          }
         }
       }
       tmem_st_wait();

@@ -101,21 +101,39 @@ __device__ __forceinline__ float bf16_at(const uint4* plain, int t, int c) {
   return __bfloat162float(p[t * kD + c]);
 }
 
-// r[t] holds the right-hand side on entry and the solution on exit of
-// (I + diag(beta) L) u = r, one independent column per thread;
-// lt[j * 64 + t] = beta_t L_tj (zero for t <= j).
-__device__ __forceinline__ void forward_substitute(float* r, const float* lt) {
-  const float4* lt4 = reinterpret_cast<const float4*>(lt);
+// Unit-triangular solves, one independent column per thread, on packed fp32
+// pairs (fma.rn.f32x2): r2[i] = (r[2i], r[2i+1]).
+//
+// forward_substitute: r holds the right-hand side on entry and the solution of
+// (I + diag(beta) L) u = r on exit; nlt[j * 64 + t] = -beta_t L_tj (zero for t <= j).
+__device__ __forceinline__ void forward_substitute(float2* r2, const float* nlt) {
+  const float4* lt4 = reinterpret_cast<const float4*>(nlt);
 #pragma unroll
   for (int j = 0; j < kC - 1; ++j) {
-    const float uj = r[j];
+    const float uj = (j & 1) ? r2[j >> 1].y : r2[j >> 1].x;
+    const float2 u2 = make_float2(uj, uj);
 #pragma unroll
     for (int m = (j + 1) / 4; m < kC / 4; ++m) {
       const float4 l = lt4[j * (kC / 4) + m];
-      r[4 * m + 0] = fmaf(-l.x, uj, r[4 * m + 0]);
-      r[4 * m + 1] = fmaf(-l.y, uj, r[4 * m + 1]);
-      r[4 * m + 2] = fmaf(-l.z, uj, r[4 * m + 2]);
-      r[4 * m + 3] = fmaf(-l.w, uj, r[4 * m + 3]);
+      r2[2 * m] = __ffma2_rn(make_float2(l.x, l.y), u2, r2[2 * m]);
+      r2[2 * m + 1] = __ffma2_rn(make_float2(l.z, l.w), u2, r2[2 * m + 1]);
+    }
+  }
+}
+
+// backward_substitute: r holds dU on entry and (I + diag(beta) L)^-T dU on exit;
+// nl[i * 64 + t] = -beta_i L_it (zero for t >= i).
+__device__ __forceinline__ void backward_substitute(float2* r2, const float* nl) {
+  const float4* l4 = reinterpret_cast<const float4*>(nl);
+#pragma unroll
+  for (int i = kC - 1; i >= 1; --i) {
+    const float xi = (i & 1) ? r2[i >> 1].y : r2[i >> 1].x;
+    const float2 x2 = make_float2(xi, xi);
+#pragma unroll
+    for (int m = 0; m <= (i - 1) / 4; ++m) {
+      const float4 c = l4[i * (kC / 4) + m];
+      r2[2 * m] = __ffma2_rn(make_float2(c.x, c.y), x2, r2[2 * m]);
+      r2[2 * m + 1] = __ffma2_rn(make_float2(c.z, c.w), x2, r2[2 * m + 1]);
     }
   }
 }
