@@ -44,28 +44,32 @@ struct FwdParams {
 };
 
 struct FwdSmem {
-  uint4 q[kPanels * kC];     // phi(Q)            [k/8][i]
-  uint4 ql[kPanels * kC];    // live rows only
-  uint4 k[kPanels * kC];     // phi(K)            [k/8][j]
-  uint4 v[kPanelsX * kC];    // V | 1             [v/8][j]
-  uint4 vk[kPanelsX * kC];   // keep rows only
-  uint4 p[kPanels * kC];     // masked P          [j/8][i]
-  uint4 s[kPanelsX * kD];    // bf16 S^T | z      [v/8][k]
+  uint4 q[kPanels * kC];        // phi(Q)                      [k/8][i]
+  uint4 k[kPanelsX * kC];       // phi(K) [k/8][j]; after the first MMAs: masked P [j/8][i]
+  uint4 v[kPanelsX * kC];       // V | 1                       [v/8][j]
+  uint4 alt[kPanelsX * kC];     // chunks with a reset: keep rows of V|1, then live rows of phi(Q)
+  uint4 s[2][kPanelsX * kD];    // bf16 S^T | z entering / leaving the chunk   [v/8][k]
   uint64_t bar[2];
   uint32_t tmem;
 };
+static_assert(sizeof(FwdSmem) <= 55 * 1024, "four CTAs per SM");
 
-constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColP = 0, kColO = 64, kColS = 136;
+// 128 TMEM columns per CTA.  M = 64 accumulators occupy 16 of the 32 lanes of a
+// warp's TMEM quarter, so two of them share columns: P and later O in lanes
+// 0..15 ("lower" threads, one query row each), the state S^T|z in lanes 16..31
+// ("upper" threads, one key-feature row each).
+constexpr uint32_t kTmemCols = 128;
+constexpr uint32_t kUpper = 16u << 16;
 
-__global__ void __launch_bounds__(kThreads) linattn_fwd_kernel(const FwdParams p) {
+__global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const FwdParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   FwdSmem& sm = *reinterpret_cast<FwdSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
-  const int row = warp * 16 + (lane & 15);
-  const bool row_active = lane < 16;
+  const bool upper = lane >= 16;
+  const int row = warp * 16 + (lane & 15);   // lower: query row i; upper: state row k
   const int nchunks = (p.T + kC - 1) / kC;
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
 
   if (tid == 0) {
     mbar_init(&sm.bar[0], 1);
@@ -79,9 +83,9 @@ __global__ void __launch_bounds__(kThreads) linattn_fwd_kernel(const FwdParams p
   const uint32_t tmem = sm.tmem;
   const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
 
-  // Carried state -> TMEM (fp32) and its bf16 operand copy.  Thread `row` owns
-  // S^T[row][.] = S[.][row]; global S is (d_v, d_k) row-major, so a fixed v is a
-  // coalesced read across threads.
+  // Carried state -> TMEM (fp32, upper lanes) and its bf16 operand copy.  Upper
+  // thread `row` owns S^T[row][.] = S[.][row]; S is (d_v, d_k) row-major in
+  // memory, so a fixed v is a coalesced read across threads.
   {
     const float* s0 = p.s0 ? p.s0 + static_cast<size_t>(bh) * kD * kD : nullptr;
     const float* z0 = p.z0 ? p.z0 + static_cast<size_t>(bh) * kD : nullptr;
@@ -92,21 +96,16 @@ __global__ void __launch_bounds__(kThreads) linattn_fwd_kernel(const FwdParams p
       for (int e = 0; e < 8; ++e) {
         const int vcol = pn * 8 + e;
         float x = 0.f;
-        if (row_active) {
+        if (upper) {
           if (vcol < kD) x = s0 ? s0[vcol * kD + row] : 0.f;
           else if (vcol == kD) x = z0 ? z0[row] : 0.f;
         }
         vals[e] = x;
       }
-      tmem_st8(lane_base + kColS + pn * 8, vals);
-      if (row_active) sm.s[pn * kD + row] = pack8_bf16(vals);
+      tmem_st8(lane_base + pn * 8, vals);
+      if (upper) sm.s[0][pn * kD + row] = pack8_bf16(vals);
     }
     tmem_st_wait();
-  }
-  __syncthreads();
-  if (p.chunk_states) {
-    uint4* dst = p.chunk_states + static_cast<size_t>(bh) * nchunks * (kPanelsX * kD);
-    for (int i = tid; i < kPanelsX * kD; i += kThreads) dst[i] = sm.s[i];
   }
 
   const size_t stride_t = static_cast<size_t>(p.H) * kD;
@@ -116,6 +115,7 @@ __global__ void __launch_bounds__(kThreads) linattn_fwd_kernel(const FwdParams p
   const uint32_t idesc_o = idesc_bf16(kC, kDX, false, true);
   const uint32_t idesc_s = idesc_bf16(kD, kDX, true, true);
   bool timed_out = false;
+  int cur = 0;
 
   for (int c = 0; c < nchunks; ++c) {
     const int t0 = c * kC;
@@ -123,42 +123,32 @@ __global__ void __launch_bounds__(kThreads) linattn_fwd_kernel(const FwdParams p
     const uint64_t dm = chunk_done_mask(drow, t0, p.T, lane);
     const bool has_reset = dm != 0ull;
 
-    // ---- stage phi(Q), phi(K), V|1 (and their masked copies) ----
+    // ---- stage phi(Q), phi(K), V|1 (keep-masked copy only if the chunk has a reset) ----
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
       int trow, seg;
       tile_vec(r * kThreads + tid, trow, seg);
-      const bool in = trow < valid;
       const size_t g = seq_base + static_cast<size_t>(t0 + trow) * stride_t + seg * 8;
-      uint4 qv = make_uint4(0, 0, 0, 0), kv = qv, vv = qv;
-      if (in) {
+      uint4 qv = zero4, kv = zero4, vv = zero4;
+      if (trow < valid) {
         qv = __ldg(reinterpret_cast<const uint4*>(p.q + g));
         kv = __ldg(reinterpret_cast<const uint4*>(p.k + g));
         vv = __ldg(reinterpret_cast<const uint4*>(p.v + g));
         if (p.feature_map) {
-          float f[8];
-          unpack8_bf16(qv, f);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = phi(f[e]);
-          qv = pack8_bf16(f);
-          unpack8_bf16(kv, f);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = phi(f[e]);
-          kv = pack8_bf16(f);
+          qv = phi8(qv);
+          kv = phi8(kv);
         }
       }
-      const uint4 zero = make_uint4(0, 0, 0, 0);
       const int slot = seg * kC + trow;
       sm.q[slot] = qv;
-      sm.ql[slot] = row_live(dm, trow) ? qv : zero;
       sm.k[slot] = kv;
       sm.v[slot] = vv;
-      sm.vk[slot] = row_keep(dm, trow) ? vv : zero;
+      if (has_reset) sm.alt[slot] = row_keep(dm, trow) ? vv : zero4;
     }
     if (tid < kC) {
       const uint4 one = make_uint4(tid < valid ? kOneBf16 : 0u, 0, 0, 0);
       sm.v[kPanels * kC + tid] = one;
-      sm.vk[kPanels * kC + tid] = row_keep(dm, tid) ? one : make_uint4(0, 0, 0, 0);
+      if (has_reset) sm.alt[kPanels * kC + tid] = row_keep(dm, tid) ? one : zero4;
     }
     fence_smem_to_async();
     fence_before_sync();
@@ -166,45 +156,55 @@ __global__ void __launch_bounds__(kThreads) linattn_fwd_kernel(const FwdParams p
 
     if (tid == 0) {
       fence_after_sync();
-      const Operand aq{smem_u32(sm.q), kC, false}, aql{smem_u32(sm.ql), kC, false};
-      const Operand bk{smem_u32(sm.k), kC, false}, ak{smem_u32(sm.k), kC, true};
-      const Operand bs{smem_u32(sm.s), kD, true}, bvk{smem_u32(sm.vk), kC, true};
-      gemm(tmem + kColP, aq, bk, idesc_p, kD / 16, false);
-      gemm(tmem + kColO, aql, bs, idesc_o, kD / 16, false);
-      gemm(tmem + kColS, ak, bvk, idesc_s, kC / 16, !has_reset);
+      const Operand aq{smem_u32(sm.q), kC, false}, bk{smem_u32(sm.k), kC, false}, ak{smem_u32(sm.k), kC, true};
+      const Operand bvk{smem_u32(has_reset ? sm.alt : sm.v), kC, true};
+      gemm(tmem, aq, bk, idesc_p, kD / 16, false);                           // P        -> lower lanes
+      gemm(tmem + kUpper, ak, bvk, idesc_s, kC / 16, !has_reset);            // S^T | z  -> upper lanes
       commit(&sm.bar[0]);
+    }
+    // residual for the backward pass: the state entering this chunk
+    if (p.chunk_states) {
+      uint4* dst = p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * (kPanelsX * kD);
+      for (int i = tid; i < kPanelsX * kD; i += kThreads) dst[i] = sm.s[cur][i];
     }
     if (!mbar_wait(&sm.bar[0], c & 1)) timed_out = true;
     fence_after_sync();
 
-    // ---- epilogue A: mask P -> bf16 operand; new state -> bf16 operand ----
+    // ---- epilogue A, one instruction stream for both halves: lower rows mask P into
+    //      the bf16 A operand (over phi(K), which is dead now), upper rows convert the
+    //      new state into the next chunk's bf16 B operand ----
     {
-      float prow[kC];
-      tmem_ld_row<kC>(lane_base + kColP, prow);
-      const int lo = row_first_key(dm, row);
+      float vals[kDX];
+      tmem_ld_row<kDX>(lane_base, vals);
+      const int lo = upper ? 0 : row_first_key(dm, row);
+      const int hi = upper ? kDX : row;
+      uint4* dst = upper ? &sm.s[cur ^ 1][row] : &sm.k[row];
 #pragma unroll
-      for (int jp = 0; jp < kPanels; ++jp) {
+      for (int pn = 0; pn < kPanelsX; ++pn) {
         float m[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const int j = jp * 8 + e;
-          m[e] = (j >= lo && j <= row) ? prow[j] : 0.f;
+          const int j = pn * 8 + e;
+          m[e] = (j >= lo && j <= hi) ? vals[j] : 0.f;
         }
-        if (row_active) sm.p[jp * kC + row] = pack8_bf16(m);
+        if (pn < kPanels || upper) dst[pn * kC] = pack8_bf16(m);
       }
-      float srow[kDX];
-      tmem_ld_row<kDX>(lane_base + kColS, srow);
-      if (row_active) {
+      if (upper && c == nchunks - 1) {
+        if (p.s_last) {
+          float* out = p.s_last + static_cast<size_t>(bh) * kD * kD;
 #pragma unroll
-        for (int pn = 0; pn < kPanelsX; ++pn) sm.s[pn * kD + row] = pack8_bf16(srow + pn * 8);
-        if (c == nchunks - 1) {
-          if (p.s_last) {
-            float* dst = p.s_last + static_cast<size_t>(bh) * kD * kD;
-#pragma unroll
-            for (int vcol = 0; vcol < kD; ++vcol) dst[vcol * kD + row] = srow[vcol];
-          }
-          if (p.z_last) p.z_last[static_cast<size_t>(bh) * kD + row] = srow[kD];
+          for (int vcol = 0; vcol < kD; ++vcol) out[vcol * kD + row] = vals[vcol];
         }
+        if (p.z_last) p.z_last[static_cast<size_t>(bh) * kD + row] = vals[kD];
+      }
+    }
+    if (has_reset) {   // live rows of phi(Q) for the inter-chunk product (the keep copy is dead now)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        int trow, seg;
+        tile_vec(r * kThreads + tid, trow, seg);
+        const int slot = seg * kC + trow;
+        sm.alt[slot] = row_live(dm, trow) ? sm.q[slot] : zero4;
       }
     }
     fence_smem_to_async();
@@ -213,22 +213,20 @@ __global__ void __launch_bounds__(kThreads) linattn_fwd_kernel(const FwdParams p
 
     if (tid == 0) {
       fence_after_sync();
-      const Operand ap{smem_u32(sm.p), kC, false}, bv{smem_u32(sm.v), kC, true};
-      gemm(tmem + kColO, ap, bv, idesc_o, kC / 16, true);
+      const Operand aql{smem_u32(has_reset ? sm.alt : sm.q), kC, false}, bs{smem_u32(sm.s[cur]), kD, true};
+      const Operand ap{smem_u32(sm.k), kC, false}, bv{smem_u32(sm.v), kC, true};
+      gemm(tmem, aql, bs, idesc_o, kD / 16, false);     // O  = live(phi(Q)) S_in^T
+      gemm(tmem, ap, bv, idesc_o, kC / 16, true);       // O += mask(P) (V|1)
       commit(&sm.bar[1]);
-    }
-    if (p.chunk_states && c + 1 < nchunks) {
-      uint4* dst = p.chunk_states + (static_cast<size_t>(bh) * nchunks + c + 1) * (kPanelsX * kD);
-      for (int i = tid; i < kPanelsX * kD; i += kThreads) dst[i] = sm.s[i];
     }
     if (!mbar_wait(&sm.bar[1], c & 1)) timed_out = true;
     fence_after_sync();
 
-    // ---- epilogue B: normalise and store ----
+    // ---- epilogue B: lower rows normalise and store ----
     {
       float orow[kDX];
-      tmem_ld_row<kDX>(lane_base + kColO, orow);
-      if (row_active && row < valid) {
+      tmem_ld_row<kDX>(lane_base, orow);
+      if (!upper && row < valid) {
         const float inv = 1.f / fmaxf(orow[kD], p.eps);
         uint4* dst = reinterpret_cast<uint4*>(p.o + seq_base + static_cast<size_t>(t0 + row) * stride_t);
 #pragma unroll
@@ -240,6 +238,7 @@ __global__ void __launch_bounds__(kThreads) linattn_fwd_kernel(const FwdParams p
         }
       }
     }
+    cur ^= 1;
   }
 
   if (timed_out && p.status) atomicExch(p.status, 1);
@@ -286,7 +285,6 @@ int mxk_linattn_bf16_fwd(const void* q, const void* k, const void* v, const floa
   prm.B = B; prm.T = T; prm.H = H;
   prm.eps = eps;
   prm.feature_map = feature_map;
-  static_assert(sizeof(FwdSmem) < 100 * 1024, "two CTAs per SM");
   cudaError_t e = cudaFuncSetAttribute(linattn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(FwdSmem)));
   if (e != cudaSuccess) return static_cast<int>(e);

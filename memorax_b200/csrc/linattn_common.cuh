@@ -20,6 +20,15 @@ constexpr uint32_t kOneBf16 = 0x3F80u;
 
 __device__ __forceinline__ float phi(float x) { return x > 0.f ? x + 1.f : __expf(x); }
 
+// Feature map on eight packed bf16 values.
+__device__ __forceinline__ uint4 phi8(uint4 x) {
+  float f[8];
+  umma::unpack8_bf16(x, f);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) f[e] = phi(f[e]);
+  return umma::pack8_bf16(f);
+}
+
 // 64 done flags of the chunk starting at t0 as a bit mask (bit i = token t0+i).
 __device__ __forceinline__ uint64_t chunk_done_mask(const uint8_t* drow, int t0, int T, int lane) {
   if (!drow) return 0ull;
