@@ -67,18 +67,24 @@ struct BwdSmem {
   uint32_t tmem;
 };
 
-constexpr uint32_t kBwdTmemCols = 512;
-constexpr uint32_t kColP = 0, kColA = 64, kColR = 128, kColDQ = 192, kColDK = 256, kColDV = 320, kColG = 384;
+// 256 TMEM columns per CTA (two CTAs per SM).  M = 64 accumulators use 16 of a
+// warp's 32 TMEM lanes, so lanes 0..15 ("lower" threads) and 16..31 ("upper"
+// threads) hold different matrices in the same columns:
+//   columns   0.. 63   lower: P, later dphiQ      upper: dA, later dphiK
+//   columns  64..135   lower: R, later dV         upper: G^T | gz (persistent)
+constexpr uint32_t kBwdTmemCols = 256;
+constexpr uint32_t kUpper = 16u << 16;
+constexpr uint32_t kColLo = 0, kColHi = 64;
 
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 
-__global__ void __launch_bounds__(kThreads) linattn_bwd_kernel(const BwdParams p) {
+__global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   BwdSmem& sm = *reinterpret_cast<BwdSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
+  const bool upper = lane >= 16;
   const int row = warp * 16 + (lane & 15);
-  const bool row_active = lane < 16;
   const int nchunks = (p.T + kC - 1) / kC;
   const uint4 zero4 = make_uint4(0, 0, 0, 0);
 
@@ -101,8 +107,8 @@ __global__ void __launch_bounds__(kThreads) linattn_bwd_kernel(const BwdParams p
   const uint32_t tmem = sm.tmem;
   const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
 
-  // Cotangent of the next carry -> TMEM and its bf16 operand copy (thread `row`
-  // owns G^T[row][.] = dS[.][row]).
+  // Cotangent of the next carry -> TMEM (upper lanes) and its bf16 operand copy
+  // (upper thread `row` owns G^T[row][.] = dS[.][row]).
   {
     const float* gs = p.ds_last ? p.ds_last + static_cast<size_t>(bh) * kD * kD : nullptr;
     const float* gz = p.dz_last ? p.dz_last + static_cast<size_t>(bh) * kD : nullptr;
@@ -113,14 +119,14 @@ __global__ void __launch_bounds__(kThreads) linattn_bwd_kernel(const BwdParams p
       for (int e = 0; e < 8; ++e) {
         const int vcol = pn * 8 + e;
         float x = 0.f;
-        if (row_active) {
+        if (upper) {
           if (vcol < kD) x = gs ? gs[vcol * kD + row] : 0.f;
           else if (vcol == kD) x = gz ? gz[row] : 0.f;
         }
         vals[e] = x;
       }
-      tmem_st8(lane_base + kColG + pn * 8, vals);
-      if (row_active) sm.g[pn * kD + row] = pack8_bf16(vals);
+      tmem_st8(lane_base + kColHi + pn * 8, vals);
+      if (upper) sm.g[pn * kD + row] = pack8_bf16(vals);
     }
     tmem_st_wait();
   }
@@ -154,15 +160,8 @@ __global__ void __launch_bounds__(kThreads) linattn_bwd_kernel(const BwdParams p
         vv = __ldg(reinterpret_cast<const uint4*>(p.v + g));
         gv = __ldg(reinterpret_cast<const uint4*>(p.d_o + g));
         if (p.feature_map) {
-          float f[8];
-          unpack8_bf16(qv, f);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = phi(f[e]);
-          qv = pack8_bf16(f);
-          unpack8_bf16(kv, f);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = phi(f[e]);
-          kv = pack8_bf16(f);
+          qv = phi8(qv);
+          kv = phi8(kv);
         }
       }
       const int slot = seg * kC + trow;
@@ -188,72 +187,82 @@ __global__ void __launch_bounds__(kThreads) linattn_bwd_kernel(const BwdParams p
       const Operand aq{smem_u32(sm.q), kC, false}, bk{smem_u32(sm.k), kC, false};
       const Operand ado{smem_u32(sm.d_o), kC, false}, bv{smem_u32(sm.v), kC, false};
       const Operand bs{smem_u32(sm.s), kD, false};
-      gemm(tmem + kColP, aq, bk, id_kk, kD / 16, false);
-      gemm(tmem + kColA, ado, bv, id_kk, kD / 16, false);
-      gemm(tmem + kColR, ado, bs, id_kk, kD / 16, false);
+      gemm(tmem + kColLo, aq, bk, id_kk, kD / 16, false);             // P  (lower)
+      gemm(tmem + kUpper + kColLo, ado, bv, id_kk, kD / 16, false);   // dA (upper)
+      gemm(tmem + kColHi, ado, bs, id_kk, kD / 16, false);            // R  (lower)
       commit(&sm.bar[0]);
     }
     if (!mbar_wait(&sm.bar[0], it & 1)) timed_out = true;
     fence_after_sync();
 
-    // ---- epilogue 1: row statistics, dP, P/D, scaled dO ----
+    // ---- epilogue 1 ----
     {
       const bool live = row_live(dm, row);
+      const int lo = row_first_key(dm, row);
+      // lower: s_dot = phi(q_i).R_i, z_dot = phi(q_i).z_in
       float s_dot = 0.f, z_dot = 0.f;
       {
         float rrow[kD];
-        tmem_ld_row<kD>(lane_base + kColR, rrow);
+        tmem_ld_row<kD>(lane_base + kColHi, rrow);   // upper lanes read (and ignore) G
+        if (!upper) {
 #pragma unroll
-        for (int pn = 0; pn < kPanels; ++pn) {
-          float fq[8];
-          unpack8_bf16(sm.q[pn * kC + row], fq);
+          for (int pn = 0; pn < kPanels; ++pn) {
+            float fq[8];
+            unpack8_bf16(sm.q[pn * kC + row], fq);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int kk = pn * 8 + e;
-            s_dot = fmaf(fq[e], rrow[kk], s_dot);
-            z_dot = fmaf(fq[e], bf16_lo(sm.s[kPanels * kD + kk].x), z_dot);
+            for (int e = 0; e < 8; ++e) {
+              const int kk = pn * 8 + e;
+              s_dot = fmaf(fq[e], rrow[kk], s_dot);
+              z_dot = fmaf(fq[e], bf16_lo(sm.s[kPanels * kD + kk].x), z_dot);
+            }
           }
         }
       }
-      float prow[kC], arow[kC];
-      tmem_ld_row<kC>(lane_base + kColP, prow);
-      tmem_ld_row<kC>(lane_base + kColA, arow);
-      const int lo = row_first_key(dm, row);
+      // vals: lower = P row, upper = dA row of the same query
+      float vals[kC];
+      tmem_ld_row<kC>(lane_base + kColLo, vals);
       float den = live ? z_dot : 0.f, don = live ? s_dot : 0.f;
 #pragma unroll
       for (int j = 0; j < kC; ++j) {
         const bool m = (j >= lo && j <= row);
-        prow[j] = m ? prow[j] : 0.f;
-        den += prow[j];
-        don = fmaf(prow[j], arow[j], don);
+        vals[j] = m ? vals[j] : 0.f;
+        const float da = __shfl_sync(0xffffffffu, vals[j], lane | 16);   // dA_ij from the upper partner
+        den += vals[j];
+        don = fmaf(vals[j], da, don);
       }
       const float dcl = fmaxf(den, p.eps);
-      const float inv = 1.f / dcl;
-      const float dden = den > p.eps ? -don * inv * inv : 0.f;
-      if (row_active) {
+      float inv = 1.f / dcl;
+      float dden = den > p.eps ? -don * inv * inv : 0.f;
+      inv = __shfl_sync(0xffffffffu, inv, lane & 15);     // lower row statistics to both halves
+      dden = __shfl_sync(0xffffffffu, dden, lane & 15);
+      // one stream: lower writes P / D, upper writes dP = M (dA / D + dden)
+      {
+        const float add = upper ? dden : 0.f;
+        uint4* dst = upper ? &sm.dp[row] : &sm.pn[row];
 #pragma unroll
         for (int jp = 0; jp < kPanels; ++jp) {
-          float a[8], bq[8];
+          float a[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const int j = jp * 8 + e;
-            const bool m = (j >= lo && j <= row);
-            a[e] = prow[j] * inv;
-            bq[e] = m ? fmaf(arow[j], inv, dden) : 0.f;
+            a[e] = (j >= lo && j <= row) ? fmaf(vals[j], inv, add) : 0.f;
           }
-          sm.pn[jp * kC + row] = pack8_bf16(a);
-          sm.dp[jp * kC + row] = pack8_bf16(bq);
+          dst[jp * kC] = pack8_bf16(a);
         }
+      }
+      // scaled dO rows: two panels per thread pair member (lower: panels 0..3, upper: 4..7 and the extra column)
+      {
         const float sc = live ? inv : 0.f;
+        const int p0 = upper ? 4 : 0;
 #pragma unroll
-        for (int pn = 0; pn < kPanels; ++pn) {
+        for (int pp = 0; pp < 4; ++pp) {
           float f[8];
-          unpack8_bf16(sm.d_o[pn * kC + row], f);
+          unpack8_bf16(sm.d_o[(p0 + pp) * kC + row], f);
 #pragma unroll
           for (int e = 0; e < 8; ++e) f[e] *= sc;
-          sm.dos[pn * kC + row] = pack8_bf16(f);
+          sm.dos[(p0 + pp) * kC + row] = pack8_bf16(f);
         }
-        sm.dos[kPanels * kC + row] = make_uint4(pack_bf16(live ? dden : 0.f, 0.f), 0, 0, 0);
+        if (upper) sm.dos[kPanels * kC + row] = make_uint4(pack_bf16(live ? dden : 0.f, 0.f), 0, 0, 0);
       }
     }
     fence_smem_to_async();
@@ -262,69 +271,61 @@ __global__ void __launch_bounds__(kThreads) linattn_bwd_kernel(const BwdParams p
 
     if (tid == 0) {
       fence_after_sync();
-      // dphiQ = dP phi(K) + dOs [S|z]
-      gemm(tmem + kColDQ, Operand{smem_u32(sm.dp), kC, false}, Operand{smem_u32(sm.k), kC, true}, id_km, kC / 16, false);
-      gemm(tmem + kColDQ, Operand{smem_u32(sm.dos), kC, false}, Operand{smem_u32(sm.s), kD, false}, id_kk, 5, true);
-      // dphiK = dP^T phi(Q) + keep[V|1] [G|gz]^T
-      gemm(tmem + kColDK, Operand{smem_u32(sm.dp), kC, true}, Operand{smem_u32(sm.q), kC, true}, id_mm, kC / 16, false);
-      gemm(tmem + kColDK, Operand{smem_u32(sm.vk), kC, false}, Operand{smem_u32(sm.g), kD, false}, id_kk, 5, true);
-      // dV = (P/D)^T dO + keep phi(K) G^T
-      gemm(tmem + kColDV, Operand{smem_u32(sm.pn), kC, true}, Operand{smem_u32(sm.d_o), kC, true}, id_mm, kC / 16, false);
-      gemm(tmem + kColDV, Operand{smem_u32(sm.kk), kC, false}, Operand{smem_u32(sm.g), kD, true}, id_km, kD / 16, true);
-      // [G|gz]^T = [no reset][G|gz]^T + phi(Q)^T dOs
-      gemm(tmem + kColG, Operand{smem_u32(sm.q), kC, true}, Operand{smem_u32(sm.dos), kC, true}, id_g, kC / 16, !has_reset);
+      // dphiQ = dP phi(K) + dOs [S|z]                      (lower, columns 0..63)
+      gemm(tmem + kColLo, Operand{smem_u32(sm.dp), kC, false}, Operand{smem_u32(sm.k), kC, true}, id_km, kC / 16, false);
+      gemm(tmem + kColLo, Operand{smem_u32(sm.dos), kC, false}, Operand{smem_u32(sm.s), kD, false}, id_kk, 5, true);
+      // dphiK = dP^T phi(Q) + keep[V|1] [G|gz]^T           (upper, columns 0..63)
+      gemm(tmem + kUpper + kColLo, Operand{smem_u32(sm.dp), kC, true}, Operand{smem_u32(sm.q), kC, true}, id_mm, kC / 16, false);
+      gemm(tmem + kUpper + kColLo, Operand{smem_u32(sm.vk), kC, false}, Operand{smem_u32(sm.g), kD, false}, id_kk, 5, true);
+      // dV = (P/D)^T dO + keep phi(K) G^T                  (lower, columns 64..127)
+      gemm(tmem + kColHi, Operand{smem_u32(sm.pn), kC, true}, Operand{smem_u32(sm.d_o), kC, true}, id_mm, kC / 16, false);
+      gemm(tmem + kColHi, Operand{smem_u32(sm.kk), kC, false}, Operand{smem_u32(sm.g), kD, true}, id_km, kD / 16, true);
+      // [G|gz]^T = [no reset][G|gz]^T + phi(Q)^T dOs       (upper, columns 64..135)
+      gemm(tmem + kUpper + kColHi, Operand{smem_u32(sm.q), kC, true}, Operand{smem_u32(sm.dos), kC, true}, id_g, kC / 16, !has_reset);
       commit(&sm.bar[1]);
     }
     if (!mbar_wait(&sm.bar[1], it & 1)) timed_out = true;
     fence_after_sync();
 
-    // ---- epilogue 2: chain through phi', store, refresh the operand copy of G ----
+    // ---- epilogue 2 ----
     {
-      const bool store = row_active && row < valid;
+      const bool store = row < valid;
       const size_t g = seq_base + static_cast<size_t>(t0 + row) * stride_t;
-      float acc[kD];
-      tmem_ld_row<kD>(lane_base + kColDQ, acc);
-      if (store) {
-        uint4* dst = reinterpret_cast<uint4*>(p.dq + g);
+      // one stream: lower chains dphiQ through phi'(q) into dq, upper dphiK through phi'(k) into dk
+      {
+        float acc[kD];
+        tmem_ld_row<kD>(lane_base + kColLo, acc);
+        const uint4* feat = upper ? &sm.k[row] : &sm.q[row];
+        uint4* dst = reinterpret_cast<uint4*>((upper ? p.dk : p.dq) + g);
+        if (store) {
 #pragma unroll
-        for (int pn = 0; pn < kPanels; ++pn) {
-          float f[8];
-          unpack8_bf16(sm.q[pn * kC + row], f);
+          for (int pn = 0; pn < kPanels; ++pn) {
+            float f[8];
+            unpack8_bf16(feat[pn * kC], f);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = acc[pn * 8 + e] * ((p.feature_map && f[e] <= 1.f) ? f[e] : 1.f);
-          dst[pn] = pack8_bf16(f);
-        }
-      }
-      tmem_ld_row<kD>(lane_base + kColDK, acc);
-      if (store) {
-        uint4* dst = reinterpret_cast<uint4*>(p.dk + g);
-#pragma unroll
-        for (int pn = 0; pn < kPanels; ++pn) {
-          float f[8];
-          unpack8_bf16(sm.k[pn * kC + row], f);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = acc[pn * 8 + e] * ((p.feature_map && f[e] <= 1.f) ? f[e] : 1.f);
-          dst[pn] = pack8_bf16(f);
-        }
-      }
-      tmem_ld_row<kD>(lane_base + kColDV, acc);
-      if (store) {
-        uint4* dst = reinterpret_cast<uint4*>(p.dv + g);
-#pragma unroll
-        for (int pn = 0; pn < kPanels; ++pn) dst[pn] = pack8_bf16(acc + pn * 8);
-      }
-      float grow[kDX];
-      tmem_ld_row<kDX>(lane_base + kColG, grow);
-      if (row_active) {
-#pragma unroll
-        for (int pn = 0; pn < kPanelsX; ++pn) sm.g[pn * kD + row] = pack8_bf16(grow + pn * 8);
-        if (c == 0) {
-          if (p.ds0) {
-            float* dst = p.ds0 + static_cast<size_t>(bh) * kD * kD;
-#pragma unroll
-            for (int vcol = 0; vcol < kD; ++vcol) dst[vcol * kD + row] = grow[vcol];
+            for (int e = 0; e < 8; ++e) f[e] = acc[pn * 8 + e] * ((p.feature_map && f[e] <= 1.f) ? f[e] : 1.f);
+            dst[pn] = pack8_bf16(f);
           }
-          if (p.dz0) p.dz0[static_cast<size_t>(bh) * kD + row] = grow[kD];
+        }
+      }
+      // one stream: lower stores dV, upper refreshes the bf16 operand copy of G | gz
+      {
+        float acc[kDX];
+        tmem_ld_row<kDX>(lane_base + kColHi, acc);
+        uint4* dst = upper ? &sm.g[row] : reinterpret_cast<uint4*>(p.dv + g);
+        const int step = upper ? kD : 1;
+        if (upper || store) {
+#pragma unroll
+          for (int pn = 0; pn < kPanelsX; ++pn)
+            if (pn < kPanels || upper) dst[pn * step] = pack8_bf16(acc + pn * 8);
+        }
+        if (upper && c == 0) {
+          if (p.ds0) {
+            float* out = p.ds0 + static_cast<size_t>(bh) * kD * kD;
+#pragma unroll
+            for (int vcol = 0; vcol < kD; ++vcol) out[vcol * kD + row] = acc[vcol];
+          }
+          if (p.dz0) p.dz0[static_cast<size_t>(bh) * kD + row] = acc[kD];
         }
       }
     }
