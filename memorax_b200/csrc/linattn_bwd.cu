@@ -140,6 +140,24 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
   const uint32_t id_g = idesc_bf16(kD, kDX, true, true);
   bool timed_out = false;
 
+  // This thread's 16 vectors (q, k, v, dO of four tile positions) of chunk cc.
+  uint4 pre[16];
+  auto prefetch = [&](int cc) {
+    const int base_t = cc * kC;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      int trow, seg;
+      tile_vec(r * kThreads + tid, trow, seg);
+      const size_t g = seq_base + static_cast<size_t>(base_t + trow) * stride_t + seg * 8;
+      const bool in = base_t + trow < p.T;
+      pre[4 * r] = in ? __ldg(reinterpret_cast<const uint4*>(p.q + g)) : zero4;
+      pre[4 * r + 1] = in ? __ldg(reinterpret_cast<const uint4*>(p.k + g)) : zero4;
+      pre[4 * r + 2] = in ? __ldg(reinterpret_cast<const uint4*>(p.v + g)) : zero4;
+      pre[4 * r + 3] = in ? __ldg(reinterpret_cast<const uint4*>(p.d_o + g)) : zero4;
+    }
+  };
+  prefetch(nchunks - 1);
+
   for (int it = 0; it < nchunks; ++it) {
     const int c = nchunks - 1 - it;
     const int t0 = c * kC;
@@ -147,22 +165,16 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
     const uint64_t dm = chunk_done_mask(drow, t0, p.T, lane);
     const bool has_reset = dm != 0ull;
 
-    // ---- stage phi(Q), phi(K), V, dO, S_in ----
+    // ---- stage phi(Q), phi(K), V, dO (prefetched during the previous chunk), S_in ----
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
       int trow, seg;
       tile_vec(r * kThreads + tid, trow, seg);
-      const size_t g = seq_base + static_cast<size_t>(t0 + trow) * stride_t + seg * 8;
-      uint4 qv = zero4, kv = zero4, vv = zero4, gv = zero4;
-      if (trow < valid) {
-        qv = __ldg(reinterpret_cast<const uint4*>(p.q + g));
-        kv = __ldg(reinterpret_cast<const uint4*>(p.k + g));
-        vv = __ldg(reinterpret_cast<const uint4*>(p.v + g));
-        gv = __ldg(reinterpret_cast<const uint4*>(p.d_o + g));
-        if (p.feature_map) {
-          qv = phi8(qv);
-          kv = phi8(kv);
-        }
+      uint4 qv = pre[4 * r], kv = pre[4 * r + 1];
+      const uint4 vv = pre[4 * r + 2], gv = pre[4 * r + 3];
+      if (p.feature_map && trow < valid) {
+        qv = phi8(qv);
+        kv = phi8(kv);
       }
       const int slot = seg * kC + trow;
       const bool keep = row_keep(dm, trow);
@@ -284,6 +296,7 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
       gemm(tmem + kUpper + kColHi, Operand{smem_u32(sm.q), kC, true}, Operand{smem_u32(sm.dos), kC, true}, id_g, kC / 16, !has_reset);
       commit(&sm.bar[1]);
     }
+    if (c > 0) prefetch(c - 1);   // in flight while the MMAs and the output epilogue run
     if (!mbar_wait(&sm.bar[1], it & 1)) timed_out = true;
     fence_after_sync();
 
