@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the sequence-mixing hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c1]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c1|c5]
     python bench.py --impl reference ...      # CPU arm: the oracle port, host cores
 
 A step is one pass of the hot path over one batch of seeded synthetic input:
@@ -255,7 +255,100 @@ class GDeltaC3:
         return o
 
 
-WORKLOADS = {"c2": LinAttnC2, "c3": GDeltaC3, "c4": LruC4, "c1": LinRecC1}
+class TrainC5:
+    """Training step (fwd + bwd + gradient all-reduce + Adam) of a 4-layer GTrXL-style value
+    network with the delta-rule mixer: d_model 512, MLP 4x, bf16 parameters, fp32 Adam moments,
+    512 sequences x 256 steps of 128-dim observations per GPU (4096 sequences over 8 GPUs),
+    done ~ Bernoulli(0.005).  Deviation from BASELINE.json: the mixer runs 4 heads of 128
+    (the delta-rule kernels are built for head dimension 128), not 8 heads of 64."""
+    name = "c5_gtrxl_deltanet_train_step"
+    dtype = "bf16"
+    B, T, OBS = 512, 256, 128
+    p_done = 0.005
+    seed = 1234 + 5
+    dominant = "train_step"
+    launches_per_step = 4 * 2 + 1   # this library's kernels per step: 4 layers x (gdelta fwd, bwd) + Adam
+    dominant_traffic_bytes = None
+    cpu_sample_batch = 2
+
+    def __init__(self, batch=None):
+        self.B = batch or self.B
+        self.trainer = None
+
+    def tokens(self):
+        return self.B * self.T
+
+    def host_inputs(self, seed_offset=0):
+        g = torch.Generator().manual_seed(self.seed + seed_offset)
+        return dict(obs=torch.randn(self.B, self.T, self.OBS, generator=g).bfloat16(),
+                    target=torch.randn(self.B, self.T, generator=g),
+                    done=(torch.rand(self.B, self.T, generator=g) < self.p_done).to(torch.uint8))
+
+    def _build(self, device):
+        import torch.distributed as dist
+        from memorax_b200.blocks import FlatAdamTrainer, GTrXLStyleValueNet
+        torch.manual_seed(0)   # same initial parameters on every rank
+        model = GTrXLStyleValueNet(obs_dim=self.OBS).to(device=device, dtype=torch.bfloat16)
+        world = dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+        self.trainer = FlatAdamTrainer(model, world_size=world)
+        dense = sum(m.weight.numel() for m in model.modules() if isinstance(m, torch.nn.Linear))
+        # 6 FLOP per dense weight per token (fwd + bwd) + the mixer's own 582 kFLOP per token-head
+        self.flop_per_token = 6.0 * dense + 4 * 4 * 582e3
+
+    def step(self, x, ops, mark=None):
+        if self.trainer is None:
+            self._build(x["obs"].device)
+        if mark:
+            mark[0].record()
+        loss = self.trainer.step(x["obs"], x["done"], x["target"])
+        if mark:
+            mark[1].record()
+        return (loss.reshape(1),)
+
+    def algorithmic_bytes(self):
+        return {"train_step": 0}
+
+    def roofline(self, dominant_ms):
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+                peak, kind = float(json.load(fh)["bf16_tflops_sustained"]), "measured (sustained)"
+        except Exception:
+            peak, kind = 1400.0, "fallback"
+        achieved = self.flop_per_token * self.tokens() / (dominant_ms * 1e-3) / 1e12
+        return {"bound": "tensor", "kernel": "whole training step (library GEMMs + this library's kernels)",
+                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_kind": f"of {kind}",
+                "traffic": None, "flop_per_step": self.flop_per_token * self.tokens(), "ms_per_launch": dominant_ms,
+                "parameters": self.trainer.num_params}
+
+    def cpu_step(self, x):
+        """Same network on the host cores in fp32 with the oracle's sequential delta rule."""
+        from oracle import memoroid_oracle as mo
+        if not hasattr(self, "_cpu"):
+            torch.manual_seed(0)
+            d, H, hd = 512, 4, 128
+            lin = lambda i, o: torch.nn.Linear(i, o)
+            self._cpu = dict(embed=lin(self.OBS, d), head=lin(d, 1), layers=[
+                dict(n1=torch.nn.LayerNorm(d), q=lin(d, d), k=lin(d, d), v=lin(d, d), gate=lin(d, 2 * H), rms=torch.nn.RMSNorm(d),
+                     out=lin(d, d), g1=lin(d, d), n2=torch.nn.LayerNorm(d), up=lin(d, 4 * d), down=lin(4 * d, d), g2=lin(d, d))
+                for _ in range(4)])
+        P, F = self._cpu, torch.nn.functional
+        h = P["embed"](x["obs"].float())
+        B, T, _ = h.shape
+        for L in P["layers"]:
+            y = L["n1"](h)
+            hv = lambda t: t.view(B, T, 4, 128)
+            q, k = F.normalize(hv(L["q"](y)), dim=-1), F.normalize(hv(L["k"](y)), dim=-1)
+            bl, al = L["gate"](y).chunk(2, -1)
+            o, _ = mo.gdelta_seq(q, k, hv(L["v"](y)), torch.exp(-F.softplus(al)), torch.sigmoid(bl),
+                                 torch.zeros(B, 4, 128, 128), x["done"].float())
+            h = h + torch.sigmoid(L["g1"](h)) * L["out"](L["rms"](o.reshape(B, T, -1)))
+            h = h + torch.sigmoid(L["g2"](h)) * L["down"](F.gelu(L["up"](L["n2"](h))))
+        loss = 0.5 * (P["head"](h).squeeze(-1) - x["target"]).square().mean()
+        loss.backward()
+        return loss
+
+
+WORKLOADS = {"c2": LinAttnC2, "c3": GDeltaC3, "c4": LruC4, "c1": LinRecC1, "c5": TrainC5}
 
 
 # ------------------------------------------------------------ clock sampling
@@ -441,9 +534,16 @@ def run_gpu_arm(args):
     e2e_value = world * w.tokens() / (e2e_ms / e2e_steps * 1e-3)
 
     if rank == 0:
-        peak, peak_kind = measured_hbm_peak()
-        alg = w.algorithmic_bytes()[w.dominant]
-        achieved = alg / (dominant_ms * 1e-3) / 1e9
+        if hasattr(w, "roofline"):
+            roof = w.roofline(dominant_ms)
+        else:
+            peak, peak_kind = measured_hbm_peak()
+            alg = w.algorithmic_bytes()[w.dominant]
+            achieved = alg / (dominant_ms * 1e-3) / 1e9
+            roof = {"bound": "hbm", "kernel": w.dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                    "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
+                    "traffic": (w.dominant_traffic_bytes if args.batch is None else None),
+                    "algorithmic_bytes_per_launch": alg, "ms_per_launch": dominant_ms}
         line = {
             "metric": "tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -455,9 +555,7 @@ def run_gpu_arm(args):
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps},
             "gpu_launches": w.launches_per_step * args.steps,
-            "roofline": {"bound": "hbm", "kernel": w.dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": (w.dominant_traffic_bytes if args.batch is None else None),
-                         "algorithmic_bytes_per_launch": alg, "ms_per_launch": dominant_ms},
+            "roofline": roof,
         }
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(cls)

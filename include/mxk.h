@@ -215,6 +215,16 @@ int mxk_gdelta_bf16_bwd(const void* q, const void* k, const void* v, const float
                         void* dq, void* dk, void* dv, float* dalpha, float* dbeta, float* ds0, int* status,
                         int B, int T, int H, int d, mxk_stream_t stream);
 
+/* ---------------------------------------------------------------------------
+ * Fused Adam step for the training-step harness (the reference trains with
+ * optax.adam inside its algorithms, e.g. algorithms/ppo.py:276-279): one flat
+ * buffer of n bf16 parameters (n % 8 == 0) with bf16 gradients and fp32
+ * moments; bias-corrected update for 1-based `step`; every gradient is
+ * multiplied by grad_scale first (1 / world size after a sum all-reduce).
+ * ------------------------------------------------------------------------- */
+int mxk_adam_bf16(void* params, const void* grads, float* m, float* v, long long n, float lr, float beta1,
+                  float beta2, float eps, int step, float grad_scale, mxk_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -35,6 +35,7 @@ SIGNATURES = {
     "mxk_gdelta_chunk_states_bytes": (_z, [_i, _i, _i, _i]),
     "mxk_gdelta_bf16_fwd": (_i, [_p] * 11 + [_i, _i, _i, _i, _p]),
     "mxk_gdelta_bf16_bwd": (_i, [_p] * 16 + [_i, _i, _i, _i, _p]),
+    "mxk_adam_bf16": (_i, [_p, _p, _p, _p, ctypes.c_longlong, _f, _f, _f, _f, _i, _f, _p]),
 }
 
 

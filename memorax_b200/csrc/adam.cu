@@ -1,0 +1,53 @@
+// Fused Adam step over one flat parameter buffer: bf16 parameters and
+// gradients, fp32 moments, bias correction as in optax.adam (the optimiser the
+// reference's algorithms use).  One pass, 16-byte accesses; the gradient is
+// scaled on the fly (1 / world size after a sum all-reduce).
+#include <cuda_bf16.h>
+
+#include "mxk_common.cuh"
+#include "umma.cuh"
+
+namespace mxk {
+namespace {
+
+__global__ void __launch_bounds__(256)
+adam_bf16_kernel(uint4* __restrict__ p, const uint4* __restrict__ g, float4* __restrict__ m, float4* __restrict__ v,
+                 long long n8, float lr, float b1, float b2, float eps, float c1, float c2, float gscale) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  float pf[8], gf[8];
+  umma::unpack8_bf16(p[i], pf);
+  umma::unpack8_bf16(g[i], gf);
+  float4 mm[2] = {m[2 * i], m[2 * i + 1]}, vv[2] = {v[2 * i], v[2 * i + 1]};
+  float* mf = reinterpret_cast<float*>(mm);
+  float* vf = reinterpret_cast<float*>(vv);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float gr = gf[e] * gscale;
+    mf[e] = b1 * mf[e] + (1.f - b1) * gr;
+    vf[e] = b2 * vf[e] + (1.f - b2) * gr * gr;
+    pf[e] -= lr * (mf[e] * c1) / (sqrtf(vf[e] * c2) + eps);
+  }
+  p[i] = umma::pack8_bf16(pf);
+  m[2 * i] = mm[0]; m[2 * i + 1] = mm[1];
+  v[2 * i] = vv[0]; v[2 * i + 1] = vv[1];
+}
+
+}  // namespace
+}  // namespace mxk
+
+extern "C" int mxk_adam_bf16(void* params, const void* grads, float* m, float* v, long long n, float lr, float beta1,
+                             float beta2, float eps, int step, float grad_scale, mxk_stream_t stream) {
+  using namespace mxk;
+  if (!params || !grads || !m || !v) return MXK_ERR_NULL;
+  if (n <= 0 || (n % 8) != 0 || step <= 0) return MXK_ERR_DIMS;
+  for (const void* ptr : {(const void*)params, grads, (const void*)m, (const void*)v})
+    if (!aligned16(ptr)) return MXK_ERR_ALIGN;
+  const float c1 = 1.f / (1.f - powf(beta1, static_cast<float>(step)));
+  const float c2 = 1.f / (1.f - powf(beta2, static_cast<float>(step)));
+  const long long n8 = n / 8;
+  adam_bf16_kernel<<<static_cast<unsigned>((n8 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<uint4*>(params), static_cast<const uint4*>(grads), reinterpret_cast<float4*>(m),
+      reinterpret_cast<float4*>(v), n8, lr, beta1, beta2, eps, c1, c2, grad_scale);
+  return launch_status();
+}

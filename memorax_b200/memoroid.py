@@ -35,6 +35,14 @@ def get_input_shape(inputs):
     return inputs.shape[:1] + inputs.shape[2:]
 
 
+def _squeeze_carry(carry, leaves):
+    """Carry pytree with the reference's singleton time axis -> per-leaf (B, ...)
+    tensors for the C-ABI; ``None`` (default carry) stays ``None`` per leaf."""
+    if carry is None:
+        return (None,) * leaves
+    return tuple(None if c is None else c[:, 0].contiguous() for c in carry)
+
+
 class SequenceModel(nn.Module):
     def forward(self, inputs, done, initial_carry=None, **kwargs):
         raise NotImplementedError
@@ -70,9 +78,8 @@ class Memoroid(SequenceModel):
         self.cell = cell
 
     def forward(self, inputs, done, initial_carry=None, **kwargs):
-        if initial_carry is None:
-            initial_carry = self.cell.initialize_carry(None, get_input_shape(inputs))
-            initial_carry = tuple(c.to(inputs.device) for c in initial_carry)
+        # initial_carry=None means the cell's initialize_carry() value (memoroid.py:101-103);
+        # the kernels take that default as NULL pointers, so it is never materialised.
         z = self.cell(inputs, **kwargs)
         next_carry, y = self.cell.scan(z, initial_carry, done, inputs)
         return next_carry, y
@@ -126,8 +133,8 @@ class LRUCell(MemoroidCellBase):
 
     def scan(self, z, initial_carry, done, inputs):
         state, lam = z
-        h0, a0 = initial_carry
-        h, a_last = ops.LinRec.apply(lam, state.contiguous(), h0[:, 0].contiguous(), a0[:, 0].contiguous(), done)
+        h0, a0 = _squeeze_carry(initial_carry, 2)
+        h, a_last = ops.LinRec.apply(lam, state.contiguous(), h0, a0, done)
         y = self.read((h, None), inputs)
         return (h[:, -1:], a_last[:, None]), y
 
@@ -164,9 +171,8 @@ class MinGRUCell(MemoroidCellBase):
 
     def scan(self, z, initial_carry, done, inputs):
         log_state, decay = z
-        x0, a0 = initial_carry
-        x, y, a_last = ops.LogLinRec.apply(log_state.contiguous(), decay.contiguous(), x0[:, 0].contiguous(),
-                                           a0[:, 0].contiguous(), done)
+        x0, a0 = _squeeze_carry(initial_carry, 2)
+        x, y, a_last = ops.LogLinRec.apply(log_state.contiguous(), decay.contiguous(), x0, a0, done)
         return (x[:, -1:], a_last[:, None]), y
 
 
@@ -208,10 +214,9 @@ class LinearAttentionCell(MemoroidCellBase):
     def scan(self, z, initial_carry, done, inputs):
         k, v = z
         q = self._heads(self.query(inputs))
-        s0, z0 = initial_carry
+        s0, z0 = _squeeze_carry(initial_carry, 2)
         bf = torch.bfloat16
-        o, s_last, z_last = ops.LinAttn.apply(q.to(bf), k.to(bf), v.to(bf), s0[:, 0].contiguous(),
-                                              z0[:, 0].contiguous(), done, self.eps, True)
+        o, s_last, z_last = ops.LinAttn.apply(q.to(bf), k.to(bf), v.to(bf), s0, z0, done, self.eps, True)
         o = o.reshape(*o.shape[:2], -1).to(inputs.dtype)
         y = self.output_projection(self.norm(o))
         return (s_last[:, None], z_last[:, None]), y
@@ -263,9 +268,8 @@ class DeltaNetCell(MemoroidCellBase):
     def scan(self, z, initial_carry, done, inputs):
         k, v, alpha, beta = z
         q = torch.nn.functional.normalize(self._heads(self.query(inputs)).float(), dim=-1)
-        (s0,) = initial_carry
+        (s0,) = _squeeze_carry(initial_carry, 1)
         bf = torch.bfloat16
-        o, s_last = ops.GatedDelta.apply(q.to(bf), k.to(bf), v.to(bf), alpha.contiguous(), beta.contiguous(),
-                                         s0[:, 0].contiguous(), done)
+        o, s_last = ops.GatedDelta.apply(q.to(bf), k.to(bf), v.to(bf), alpha.contiguous(), beta.contiguous(), s0, done)
         o = o.reshape(*o.shape[:2], -1).to(inputs.dtype)
         return (s_last[:, None],), self.output_projection(self.norm(o))

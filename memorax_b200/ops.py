@@ -289,3 +289,12 @@ class GatedDelta(torch.autograd.Function):
         dq, dk, dv, dalpha, dbeta, ds0 = gdelta_bwd(q, k, v, alpha, beta, d_o, states, done, ds_last)
         return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dalpha.to(alpha.dtype), dbeta.to(beta.dtype),
                 ds0 if ctx.has_state else None, None)
+
+
+# ------------------------------------------------------------------- Adam
+def adam_step(params, grads, m, v, step, lr=3e-4, betas=(0.9, 0.999), eps=1e-8, grad_scale=1.0):
+    """In-place fused Adam on flat buffers (bf16 params/grads, fp32 moments)."""
+    assert params.dtype == torch.bfloat16 and grads.dtype == torch.bfloat16
+    assert m.dtype == torch.float32 and v.dtype == torch.float32 and params.is_contiguous() and grads.is_contiguous()
+    _lib.call("mxk_adam_bf16", _ptr(params), _ptr(grads), _ptr(m), _ptr(v), params.numel(), float(lr), float(betas[0]),
+              float(betas[1]), float(eps), int(step), float(grad_scale), _stream())
