@@ -20,14 +20,18 @@ constexpr uint32_t kOneBf16 = 0x3F80u;
 
 __device__ __forceinline__ float phi(float x) { return x > 0.f ? x + 1.f : __expf(x); }
 
-// Feature map on eight packed bf16 values.
-__device__ __forceinline__ uint4 phi8(uint4 x) {
-  float f[8];
-  umma::unpack8_bf16(x, f);
-#pragma unroll
-  for (int e = 0; e < 8; ++e) f[e] = phi(f[e]);
-  return umma::pack8_bf16(f);
+// Feature map elu(x) + 1 on packed bf16 pairs: x + 1 for x > 0, exp(x) otherwise,
+// entirely in bf16x2 arithmetic (the result is rounded to bf16 anyway): one
+// multiply by log2(e), one ex2, one add, one compare mask, one blend per pair.
+__device__ __forceinline__ uint32_t phi2(uint32_t x) {
+  uint32_t t, ex, pos, mask;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(t) : "r"(x), "r"(0x3FB93FB9u));     // log2(e) = 1.4453 in bf16
+  asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(ex) : "r"(t));
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(pos) : "r"(x), "r"(0x3F803F80u));    // 1.0
+  asm("set.gt.u32.bf16x2 %0, %1, %2;" : "=r"(mask) : "r"(x), "r"(0u));        // 0xFFFF per lane where x > 0
+  return (pos & mask) | (ex & ~mask);
 }
+__device__ __forceinline__ uint4 phi8(uint4 x) { return make_uint4(phi2(x.x), phi2(x.y), phi2(x.z), phi2(x.w)); }
 
 // 64 done flags of the chunk starting at t0 as a bit mask (bit i = token t0+i).
 __device__ __forceinline__ uint64_t chunk_done_mask(const uint8_t* drow, int t0, int T, int lane) {
