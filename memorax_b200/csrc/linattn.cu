@@ -58,6 +58,14 @@ static_assert(sizeof(FwdSmem) <= 55 * 1024, "four CTAs per SM");
 // warp's TMEM quarter, so two of them share columns: P and later O in lanes
 // 0..15 ("lower" threads, one query row each), the state S^T|z in lanes 16..31
 // ("upper" threads, one key-feature row each).
+#ifdef MXK_TIMING
+}  // namespace
+__device__ unsigned long long g_phase_cycles[8];
+namespace {
+#define MXK_T(i) do { if (tid == 0 && (blockIdx.x % 37) == 0) { const long long now_ = clock64(); atomicAdd(&g_phase_cycles[i], (unsigned long long)(now_ - t_prev_)); t_prev_ = now_; } } while (0)
+#else
+#define MXK_T(i) do {} while (0)
+#endif
 constexpr uint32_t kTmemCols = 128;
 constexpr uint32_t kUpper = 16u << 16;
 
@@ -116,34 +124,46 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const FwdParam
   const uint32_t idesc_s = idesc_bf16(kD, kDX, true, true);
   bool timed_out = false;
   int cur = 0;
+#ifdef MXK_TIMING
+  long long t_prev_ = clock64();
+#endif
 
   for (int c = 0; c < nchunks; ++c) {
     const int t0 = c * kC;
     const int valid = min(kC, p.T - t0);
     const uint64_t dm = chunk_done_mask(drow, t0, p.T, lane);
     const bool has_reset = dm != 0ull;
+    MXK_T(0);
 
     // ---- stage phi(Q), phi(K), V|1 (keep-masked copy only if the chunk has a reset) ----
+    {
+      uint4 raw[12];   // all twelve loads are issued before any of them is consumed
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      int trow, seg;
-      tile_vec(r * kThreads + tid, trow, seg);
-      const size_t g = seq_base + static_cast<size_t>(t0 + trow) * stride_t + seg * 8;
-      uint4 qv = zero4, kv = zero4, vv = zero4;
-      if (trow < valid) {
-        qv = __ldg(reinterpret_cast<const uint4*>(p.q + g));
-        kv = __ldg(reinterpret_cast<const uint4*>(p.k + g));
-        vv = __ldg(reinterpret_cast<const uint4*>(p.v + g));
-        if (p.feature_map) {
+      for (int r = 0; r < 4; ++r) {
+        int trow, seg;
+        tile_vec(r * kThreads + tid, trow, seg);
+        const size_t g = seq_base + static_cast<size_t>(t0 + trow) * stride_t + seg * 8;
+        const bool in = trow < valid;
+        raw[3 * r] = in ? __ldg(reinterpret_cast<const uint4*>(p.q + g)) : zero4;
+        raw[3 * r + 1] = in ? __ldg(reinterpret_cast<const uint4*>(p.k + g)) : zero4;
+        raw[3 * r + 2] = in ? __ldg(reinterpret_cast<const uint4*>(p.v + g)) : zero4;
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        int trow, seg;
+        tile_vec(r * kThreads + tid, trow, seg);
+        uint4 qv = raw[3 * r], kv = raw[3 * r + 1];
+        const uint4 vv = raw[3 * r + 2];
+        if (p.feature_map && trow < valid) {
           qv = phi8(qv);
           kv = phi8(kv);
         }
+        const int slot = seg * kC + trow;
+        sm.q[slot] = qv;
+        sm.k[slot] = kv;
+        sm.v[slot] = vv;
+        if (has_reset) sm.alt[slot] = row_keep(dm, trow) ? vv : zero4;
       }
-      const int slot = seg * kC + trow;
-      sm.q[slot] = qv;
-      sm.k[slot] = kv;
-      sm.v[slot] = vv;
-      if (has_reset) sm.alt[slot] = row_keep(dm, trow) ? vv : zero4;
     }
     if (tid < kC) {
       const uint4 one = make_uint4(tid < valid ? kOneBf16 : 0u, 0, 0, 0);
@@ -152,7 +172,9 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const FwdParam
     }
     fence_smem_to_async();
     fence_before_sync();
+    MXK_T(1);
     __syncthreads();
+    MXK_T(2);
 
     if (tid == 0) {
       fence_after_sync();
@@ -169,6 +191,7 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const FwdParam
     }
     if (!mbar_wait(&sm.bar[0], c & 1)) timed_out = true;
     fence_after_sync();
+    MXK_T(3);
 
     // ---- epilogue A, one instruction stream for both halves: lower rows mask P into
     //      the bf16 A operand (over phi(K), which is dead now), upper rows convert the
@@ -209,7 +232,9 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const FwdParam
     }
     fence_smem_to_async();
     fence_before_sync();
+    MXK_T(4);
     __syncthreads();
+    MXK_T(5);
 
     if (tid == 0) {
       fence_after_sync();
@@ -221,6 +246,7 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const FwdParam
     }
     if (!mbar_wait(&sm.bar[1], c & 1)) timed_out = true;
     fence_after_sync();
+    MXK_T(6);
 
     // ---- epilogue B: lower rows normalise and store ----
     {
@@ -239,6 +265,7 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const FwdParam
       }
     }
     cur ^= 1;
+    MXK_T(7);
   }
 
   if (timed_out && p.status) atomicExch(p.status, 1);
@@ -249,6 +276,16 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const FwdParam
 
 }  // namespace
 }  // namespace mxk
+
+#ifdef MXK_TIMING
+extern "C" int mxk_debug_phase_cycles(unsigned long long* out, int reset) {
+  if (reset) {
+    unsigned long long z[8] = {};
+    return (int)cudaMemcpyToSymbol(mxk::g_phase_cycles, z, sizeof(z));
+  }
+  return (int)cudaMemcpyFromSymbol(out, mxk::g_phase_cycles, 8 * sizeof(unsigned long long));
+}
+#endif
 
 extern "C" {
 
