@@ -1,0 +1,72 @@
+"""Host-buffer entry to the ops: pinned host tensors in, pinned host tensors out.
+
+A caller that keeps its batch in host memory (the reference's CPU-environment
+setups do: docs/source/guides/sharp_bits.md:3-9) pays PCIe both ways.  Every op
+here is independent per sequence, so the batch is cut into slices that flow
+through three streams -- host-to-device copy, kernels, device-to-host copy --
+and the two copy directions and the kernels overlap."""
+from __future__ import annotations
+
+import torch
+
+
+class HostPipeline:
+    """``run(host_inputs, host_outputs)`` applies ``step`` (a function from a dict
+    of device tensors to a tuple of device tensors) slice by slice.
+
+    Tensors whose leading dimension equals ``batch`` are sliced; anything else is
+    copied whole with the first slice.  ``slices=1`` degenerates to copy, run,
+    copy on one stream each (for steps that are not separable over the batch)."""
+
+    def __init__(self, step, batch, device, slices=4):
+        self.step, self.batch, self.device = step, batch, device
+        self.slices = max(1, min(slices, batch))
+        self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(device=device) for _ in range(3))
+
+    def _bounds(self, i):
+        per = -(-self.batch // self.slices)
+        return i * per, min(self.batch, (i + 1) * per)
+
+    def run(self, host_inputs, host_outputs):
+        main = torch.cuda.current_stream(self.device)
+        start = torch.cuda.Event()
+        start.record(main)
+        for s in (self.s_in, self.s_run, self.s_out):
+            s.wait_event(start)
+        keep = []
+        shared = {}
+        for i in range(self.slices):
+            lo, hi = self._bounds(i)
+            if lo >= hi:
+                break
+            with torch.cuda.stream(self.s_in):
+                x = {}
+                for name, t in host_inputs.items():
+                    if t.dim() > 0 and t.shape[0] == self.batch:
+                        x[name] = t[lo:hi].to(self.device, non_blocking=True)
+                    else:
+                        if name not in shared:
+                            shared[name] = t.to(self.device, non_blocking=True)
+                        x[name] = shared[name]
+                    x[name].record_stream(self.s_run)
+                ready = torch.cuda.Event()
+                ready.record(self.s_in)
+            self.s_run.wait_event(ready)
+            with torch.cuda.stream(self.s_run):
+                outs = self.step(x)
+                for o in outs:
+                    o.record_stream(self.s_out)
+                done = torch.cuda.Event()
+                done.record(self.s_run)
+            self.s_out.wait_event(done)
+            with torch.cuda.stream(self.s_out):
+                for dst, src in zip(host_outputs, outs):
+                    if dst.dim() > 0 and dst.shape[0] == self.batch and src.shape[0] == hi - lo:
+                        dst[lo:hi].copy_(src, non_blocking=True)
+                    else:
+                        dst.copy_(src, non_blocking=True)
+            keep.append((x, outs))
+        finished = torch.cuda.Event()
+        finished.record(self.s_out)
+        main.wait_event(finished)
+        return keep
