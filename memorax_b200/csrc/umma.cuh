@@ -100,16 +100,18 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 
-// Waits for the phase with the given parity, at most `limit` polls.  Returns
-// false when the limit ran out (the caller records it and carries on, so a
-// kernel can never spin forever).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int limit = 1 << 22) {
+// Waits for the phase with the given parity.  Each poll lets the hardware suspend
+// the thread for up to ~1 ms or until the phase completes (suspend-time hint), so
+// waiting threads do not burn issue slots re-polling; after `limit` polls (about a
+// second) the wait gives up and returns false -- the caller records it and carries
+// on, so a kernel can never spin forever.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int limit = 1024) {
   uint32_t ok = 0;
   for (int it = 0; it < limit && !ok; ++it) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(1000000u)
         : "memory");
   }
   return ok != 0;
