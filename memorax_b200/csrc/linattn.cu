@@ -252,18 +252,21 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const FwdParam
     {
       float orow[kDX];
       tmem_ld_row<kDX>(lane_base, orow);
-      if (!upper && row < valid) {
-        const float inv = 1.f / fmaxf(orow[kD], p.eps);
-        uint4* dst = reinterpret_cast<uint4*>(p.o + seq_base + static_cast<size_t>(t0 + row) * stride_t);
+      const float inv = 1.f / fmaxf(orow[kD], p.eps);
+      uint4 packed[kPanels];
 #pragma unroll
-        for (int pn = 0; pn < kPanels; ++pn) {
-          float f[8];
+      for (int pn = 0; pn < kPanels; ++pn) {
+        float f[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = orow[pn * 8 + e] * inv;
-          dst[pn] = pack8_bf16(f);
-        }
+        for (int e = 0; e < 8; ++e) f[e] = orow[pn * 8 + e] * inv;
+        packed[pn] = pack8_bf16(f);
       }
+      // V|1 is dead once the second MMA group has completed: its buffer stages the output rows
+      store_rows_coalesced(sm.v + warp * (16 * 9), packed, !upper, lane,
+                           p.o + seq_base + static_cast<size_t>(t0 + warp * 16) * stride_t, stride_t,
+                           valid - warp * 16);
     }
+    __syncthreads();   // the staging rows live in sm.v, which the next chunk's staging overwrites
     cur ^= 1;
     MXK_T(7);
   }

@@ -302,36 +302,41 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
 
     // ---- epilogue 2 ----
     {
-      const bool store = row < valid;
-      const size_t g = seq_base + static_cast<size_t>(t0 + row) * stride_t;
-      // one stream: lower chains dphiQ through phi'(q) into dq, upper dphiK through phi'(k) into dk
+      // one stream: lower chains dphiQ through phi'(q) into dq, upper dphiK through phi'(k) into dk.
+      // Output rows leave through per-warp staging areas (buffers the finished MMAs no longer
+      // need) so that every store instruction writes complete 128-byte rows.
+      const int rows_valid = valid - warp * 16;
+      __nv_bfloat16* const gq = p.dq + seq_base + static_cast<size_t>(t0 + warp * 16) * stride_t;
+      __nv_bfloat16* const gk = p.dk + seq_base + static_cast<size_t>(t0 + warp * 16) * stride_t;
+      __nv_bfloat16* const gv = p.dv + seq_base + static_cast<size_t>(t0 + warp * 16) * stride_t;
       {
         float acc[kD];
         tmem_ld_row<kD>(lane_base + kColLo, acc);
         const uint4* feat = upper ? &sm.k[row] : &sm.q[row];
-        uint4* dst = reinterpret_cast<uint4*>((upper ? p.dk : p.dq) + g);
-        if (store) {
+        uint4 packed[kPanels];
 #pragma unroll
-          for (int pn = 0; pn < kPanels; ++pn) {
-            float f[8];
-            unpack8_bf16(feat[pn * kC], f);
+        for (int pn = 0; pn < kPanels; ++pn) {
+          float f[8];
+          unpack8_bf16(feat[pn * kC], f);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = acc[pn * 8 + e] * ((p.feature_map && f[e] <= 1.f) ? f[e] : 1.f);
-            dst[pn] = pack8_bf16(f);
-          }
+          for (int e = 0; e < 8; ++e) f[e] = acc[pn * 8 + e] * ((p.feature_map && f[e] <= 1.f) ? f[e] : 1.f);
+          packed[pn] = pack8_bf16(f);
         }
+        store_rows_coalesced(sm.dos + warp * (16 * 9), packed, !upper, lane, gq, stride_t, rows_valid);
+        store_rows_coalesced(sm.vk + warp * (16 * 9), packed, upper, lane, gk, stride_t, rows_valid);
       }
       // one stream: lower stores dV, upper refreshes the bf16 operand copy of G | gz
       {
         float acc[kDX];
         tmem_ld_row<kDX>(lane_base + kColHi, acc);
-        uint4* dst = upper ? &sm.g[row] : reinterpret_cast<uint4*>(p.dv + g);
-        const int step = upper ? kD : 1;
-        if (upper || store) {
+        uint4 packed[kPanelsX];
 #pragma unroll
-          for (int pn = 0; pn < kPanelsX; ++pn)
-            if (pn < kPanels || upper) dst[pn * step] = pack8_bf16(acc + pn * 8);
+        for (int pn = 0; pn < kPanelsX; ++pn) packed[pn] = pack8_bf16(acc + pn * 8);
+        if (upper) {
+#pragma unroll
+          for (int pn = 0; pn < kPanelsX; ++pn) sm.g[pn * kD + row] = packed[pn];
         }
+        store_rows_coalesced(sm.pn + warp * (16 * 9), packed, !upper, lane, gv, stride_t, rows_valid);   // pn, dp: one 16 KB region
         if (upper && c == 0) {
           if (p.ds0) {
             float* out = p.ds0 + static_cast<size_t>(bh) * kD * kD;
@@ -342,6 +347,7 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
         }
       }
     }
+    __syncthreads();   // staging areas alias buffers that the next chunk refills
   }
 
   if (timed_out && p.status) atomicExch(p.status, 1);

@@ -57,5 +57,26 @@ __device__ __forceinline__ void tile_vec(int vid, int& row, int& seg) {
 }
 
 
+// Coalesced store of 16 rows x 64 bf16 owned by one warp.  The 16 `writer` lanes
+// each hold one row (eight 16-byte vectors); writing them straight to memory
+// would touch 16 different 128-byte lines per instruction.  Instead the rows go
+// through a per-warp staging area (row stride 9 vectors = 144 bytes, conflict
+// free) and all 32 lanes store four complete rows per instruction.
+// `stage` is this warp's 16 * 9 vectors; `grow0` points at the warp's first row.
+__device__ __forceinline__ void store_rows_coalesced(uint4* stage, const uint4* vals, bool writer, int lane,
+                                                     __nv_bfloat16* grow0, size_t stride_t, int rows_valid) {
+  if (writer) {
+#pragma unroll
+    for (int s8 = 0; s8 < 8; ++s8) stage[(lane & 15) * 9 + s8] = vals[s8];
+  }
+  __syncwarp();
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int r = 4 * it + (lane >> 3), seg = lane & 7;
+    if (r < rows_valid) *reinterpret_cast<uint4*>(grow0 + r * stride_t + seg * 8) = stage[r * 9 + seg];
+  }
+  __syncwarp();
+}
+
 }  // namespace linattn
 }  // namespace mxk
