@@ -268,21 +268,25 @@ linrec_bwd_kernel(const float* __restrict__ a, int a_tinv, const float* __restri
 }
 
 // Sums the (B, row) per-sequence partials of the time-invariant decay gradient
-// over the batch in a fixed order (deterministic; no atomics).
+// over the batch in a fixed order (deterministic; no atomics).  A block owns 32
+// columns; its eight thread rows each sum every eighth sequence, then thread row
+// 0 adds the eight partials in order.
 __global__ void __launch_bounds__(kBlock)
 reduce_rows_kernel(const float* __restrict__ partial, float* __restrict__ out, int B, int row) {
-  const int col = blockIdx.x * kBlock + threadIdx.x;
-  if (col >= row) return;
-  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-  int bi = 0;
-  for (; bi + 3 < B; bi += 4) {
-    s0 += partial[static_cast<size_t>(bi) * row + col];
-    s1 += partial[static_cast<size_t>(bi + 1) * row + col];
-    s2 += partial[static_cast<size_t>(bi + 2) * row + col];
-    s3 += partial[static_cast<size_t>(bi + 3) * row + col];
+  __shared__ float part[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + tx;
+  float s = 0.f;
+  if (col < row)
+    for (int bi = ty; bi < B; bi += 8) s += partial[static_cast<size_t>(bi) * row + col];
+  part[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && col < row) {
+    float t = part[0][tx];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) t += part[i][tx];
+    out[col] = t;
   }
-  for (; bi < B; ++bi) s0 += partial[static_cast<size_t>(bi) * row + col];
-  out[col] = (s0 + s1) + (s2 + s3);
 }
 
 // ------------------------------------------------------------ log-space form
@@ -483,7 +487,7 @@ int linrec_bwd(const float* a, int a_tinv, const float* h, const float* h0, cons
     linrec_bwd_kernel<CPLX, CPLX ? 2 : 1><<<blocks_for(total / (CPLX ? 2 : 1)), kBlock, 0, s>>>(a, a_tinv, h, h0, done, gh, gh_last, gb, ga_full, partial, gh0, B, T, row, conj_ops);
   if (int st = launch_status()) return st;
   if (partial) {
-    reduce_rows_kernel<<<(row + kBlock - 1) / kBlock, kBlock, 0, s>>>(partial, ga, B, row);
+    reduce_rows_kernel<<<(row + 31) / 32, kBlock, 0, s>>>(partial, ga, B, row);
     return launch_status();
   }
   return MXK_OK;
