@@ -34,29 +34,34 @@ struct FwdParams {
 };
 
 struct FwdSmem {
-  uint4 s[kStateVecs];        // S_in bf16     [k/8][v][8]
-  uint4 k[kPanD * kC];        // K             [k/8][t][8]
-  uint4 q[kPanD * kC];        // Q             [k/8][t][8]
-  uint4 vplain[kC * 16];      // V row-major [t][v]; later the output tile [t][v]
-  uint4 u[kPanC * kD];        // U^T           [j/8][v][8]
-  uint4 ug[kPanC * kD];       // (gam U)^T
-  uint4 p[kPanC * kC];        // tril(G o QK^T) [j/8][t][8]
-  float lt[kC * kC];          // lt[j][t] = -beta_t L_tj
+  uint4 s[kStateVecs];        // S_in bf16                      [k/8][v][8]
+  uint4 k[kPanD * kC];        // K, after the first MMAs gam K  [k/8][t][8]
+  uint4 q[kPanD * kC];        // Q, after the first MMAs g Q    [k/8][t][8]
+  uint4 vu[kC * 16];          // V row-major [t][v], then U^T   [j/8][v][8]
+  uint4 p[kPanC * kC];        // tril(G o QK^T)                 [j/8][t][8]
+  float lt[kC * kC];          // lt[j][t] = -beta_t L_tj, then the bf16 output tile [t][v]
   ChunkDecay cd;
   uint64_t bar[2];
   uint32_t tmem;
 };
+static_assert(sizeof(FwdSmem) <= 112 * 1024, "two CTAs per SM");
 
-constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColS = 0, kColKK = 128, kColOA = 128, kColQK = 192, kColY = 256, kColDS = 192, kColOI = 320;
+// 256 TMEM columns per CTA (two CTAs per SM):
+//   columns   0..127  S (fp32, all 128 lanes = value rows)
+//   columns 128..191  first K K^T (lanes 0..15 of each warp) and Q K^T (lanes 16..31),
+//                     both M = 64; afterwards O^T (all lanes)
+//   columns 192..255  Y^T = S_in K^T
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kUpper = 16u << 16;
+constexpr uint32_t kColS = 0, kColKQ = 128, kColO = 128, kColY = 192;
 
-__global__ void __launch_bounds__(kThreads) gdelta_fwd_kernel(const FwdParams p) {
+__global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const FwdParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   FwdSmem& sm = *reinterpret_cast<FwdSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
-  const int row = warp * 16 + (lane & 15);  // token row owned in M = 64 accumulators
-  const bool row_active = lane < 16;
+  const bool upper = lane >= 16;
+  const int row = warp * 16 + (lane & 15);  // token row owned in the M = 64 accumulators
   const int nchunks = (p.T + kC - 1) / kC;
 
   if (tid == 0) {
@@ -108,7 +113,7 @@ __global__ void __launch_bounds__(kThreads) gdelta_fwd_kernel(const FwdParams p)
 
     stage_panel_tile(sm.k, p.k + seq_base + static_cast<size_t>(t0) * stride_t, stride_t, valid, tid);
     stage_panel_tile(sm.q, p.q + seq_base + static_cast<size_t>(t0) * stride_t, stride_t, valid, tid);
-    stage_plain_tile(sm.vplain, p.v + seq_base + static_cast<size_t>(t0) * stride_t, stride_t, valid, tid);
+    stage_plain_tile(sm.vu, p.v + seq_base + static_cast<size_t>(t0) * stride_t, stride_t, valid, tid);
     if (p.chunk_states) {
       uint4* dst = p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * kStateVecs;
       for (int i = tid; i < kStateVecs; i += kThreads) dst[i] = sm.s[i];
@@ -120,57 +125,73 @@ __global__ void __launch_bounds__(kThreads) gdelta_fwd_kernel(const FwdParams p)
     if (tid == 0) {
       fence_after_sync();
       const Operand ak{smem_u32(sm.k), kC, false}, aq{smem_u32(sm.q), kC, false}, as{smem_u32(sm.s), kD, false};
-      gemm(tmem + kColKK, ak, ak, id_64, kD / 16, false);
-      gemm(tmem + kColQK, aq, ak, id_64, kD / 16, false);
-      gemm(tmem + kColY, as, ak, id_128x64, kD / 16, false);
-      gemm(tmem + kColOI, as, aq, id_128x64, kD / 16, false);
+      gemm(tmem + kColKQ, ak, ak, id_64, kD / 16, false);              // K K^T -> lower lanes
+      gemm(tmem + kUpper + kColKQ, aq, ak, id_64, kD / 16, false);     // Q K^T -> upper lanes
+      gemm(tmem + kColY, as, ak, id_128x64, kD / 16, false);           // Y^T = S_in K^T
       commit(&sm.bar[0]);
     }
     if (!mbar_wait(&sm.bar[0], c & 1)) timed_out = true;
     fence_after_sync();
 
-    // ---- epilogue 1a: row threads -> beta L (fp32) and masked decayed QK^T (bf16) ----
+    // ---- epilogue 1a: lower lanes turn their K K^T row into -beta L (fp32), upper lanes their
+    //      Q K^T row into the masked, decayed bf16 operand; then Q and K are rescaled in place
+    //      (g_t q_t for the inter-chunk output, gam_j k_j for the state update) ----
     {
       const int lo = row_first_key(dm, row);
       const float cum_t = sm.cd.cum[row], beta_t = sm.cd.beta[row];
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        float kk[32], qk[32];
-        tmem_ld_row<32>(lane_base + kColKK + half * 32, kk);
-        tmem_ld_row<32>(lane_base + kColQK + half * 32, qk);
+        float x[32];
+        tmem_ld_row<32>(lane_base + kColKQ + half * 32, x);
 #pragma unroll
-        for (int jq = 0; jq < 4; ++jq) {
-          float pm[8];
+        for (int e = 0; e < 32; ++e) {
+          const int j = half * 32 + e;
+          const bool in = (j >= lo && j <= row);
+          x[e] *= in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
+        }
+        if (upper) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int j = half * 32 + jq * 8 + e;
-            const bool in = (j >= lo && j <= row);
-            const float gtj = in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
-            pm[e] = gtj * qk[jq * 8 + e];
-            if (row_active) sm.lt[j * kC + row] = (j < row) ? -beta_t * gtj * kk[jq * 8 + e] : 0.f;
+          for (int jq = 0; jq < 4; ++jq) sm.p[(half * 4 + jq) * kC + row] = pack8_bf16(x + jq * 8);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int j = half * 32 + e;
+            sm.lt[j * kC + row] = (j < row) ? -beta_t * x[e] : 0.f;
           }
-          if (row_active) sm.p[(half * 4 + jq) * kC + row] = pack8_bf16(pm);
         }
       }
-    }
-    __syncthreads();
-
-    // ---- epilogue 1b: thread v solves for its column of U ----
-    {
-      __align__(8) float r[kC];
-      tmem_ld_row<kC>(lane_base + kColY, r);
+      uint4* tile = upper ? sm.k : sm.q;
+      const float sc = upper ? sm.cd.gam[row] : sm.cd.g[row];
 #pragma unroll
-      for (int t = 0; t < kC; ++t)
-        r[t] = sm.cd.beta[t] * (bf16_at(sm.vplain, t, tid) - sm.cd.g[t] * r[t]);
-      forward_substitute(reinterpret_cast<float2*>(r), sm.lt);
+      for (int pn = 0; pn < kPanD; ++pn) {
+        float f[8];
+        unpack8_bf16(tile[pn * kC + row], f);
 #pragma unroll
-      for (int jp = 0; jp < kPanC; ++jp) {
-        float sc[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) sc[e] = r[jp * 8 + e] * sm.cd.gam[jp * 8 + e];
-        sm.u[jp * kD + tid] = pack8_bf16(r + jp * 8);
-        sm.ug[jp * kD + tid] = pack8_bf16(sc);
+        for (int e = 0; e < 8; ++e) f[e] *= sc;
+        tile[pn * kC + row] = pack8_bf16(f);
       }
+    }
+    // ---- epilogue 1b: thread v solves for its column of U; S <- g_last S in place ----
+    __align__(8) float r[kC];
+    tmem_ld_row<kC>(lane_base + kColY, r);
+#pragma unroll
+    for (int t = 0; t < kC; ++t) r[t] = sm.cd.beta[t] * (bf16_at(sm.vu, t, tid) - sm.cd.g[t] * r[t]);
+    __syncthreads();   // -beta L complete; V consumed (U^T reuses its buffer)
+    forward_substitute(reinterpret_cast<float2*>(r), sm.lt);
+#pragma unroll
+    for (int jp = 0; jp < kPanC; ++jp) sm.vu[jp * kD + tid] = pack8_bf16(r + jp * 8);
+    {
+      const float g_last = sm.cd.g[kC - 1];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        float s[32];
+        tmem_ld_row<32>(lane_base + kColS + q4 * 32, s);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) s[e] *= g_last;
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) tmem_st8(lane_base + kColS + q4 * 32 + c8 * 8, s + c8 * 8);
+      }
+      tmem_st_wait();
     }
     fence_smem_to_async();
     fence_before_sync();
@@ -178,42 +199,34 @@ __global__ void __launch_bounds__(kThreads) gdelta_fwd_kernel(const FwdParams p)
 
     if (tid == 0) {
       fence_after_sync();
-      const Operand au{smem_u32(sm.u), kD, false}, aug{smem_u32(sm.ug), kD, false};
-      const Operand bp{smem_u32(sm.p), kC, false}, bk{smem_u32(sm.k), kC, true};
-      gemm(tmem + kColOA, au, bp, id_128x64, kC / 16, false);
-      gemm(tmem + kColDS, aug, bk, id_ds, kC / 16, false);
+      const Operand as{smem_u32(sm.s), kD, false}, bgq{smem_u32(sm.q), kC, false};
+      const Operand au{smem_u32(sm.vu), kD, false}, bp{smem_u32(sm.p), kC, false}, bgk{smem_u32(sm.k), kC, true};
+      gemm(tmem + kColO, as, bgq, id_128x64, kD / 16, false);   // O^T  = S_in (g Q)^T
+      gemm(tmem + kColO, au, bp, id_128x64, kC / 16, true);     // O^T += U^T P^T
+      gemm(tmem + kColS, au, bgk, id_ds, kC / 16, true);        // S    = g_last S_in + U^T (gam K)
       commit(&sm.bar[1]);
     }
     if (!mbar_wait(&sm.bar[1], c & 1)) timed_out = true;
     fence_after_sync();
 
-    // ---- epilogue 2: outputs and state update ----
+    // ---- epilogue 2: output tile (staged for 16-byte stores), bf16 copy of the new state ----
     {
-      __nv_bfloat16* otile = reinterpret_cast<__nv_bfloat16*>(sm.vplain);
+      __nv_bfloat16* otile = reinterpret_cast<__nv_bfloat16*>(sm.lt);
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        float oi[32], oa[32];
-        tmem_ld_row<32>(lane_base + kColOI + half * 32, oi);
-        tmem_ld_row<32>(lane_base + kColOA + half * 32, oa);
+        float o[32];
+        tmem_ld_row<32>(lane_base + kColO + half * 32, o);
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int t = half * 32 + e;
-          otile[t * kD + tid] = __float2bfloat16(fmaf(sm.cd.g[t], oi[e], oa[e]));
-        }
+        for (int e = 0; e < 32; ++e) otile[(half * 32 + e) * kD + tid] = __float2bfloat16(o[e]);
       }
-      const float g_last = sm.cd.g[kC - 1];
       const bool last = (c == nchunks - 1);
       float* sl = (last && p.s_last) ? p.s_last + (static_cast<size_t>(bh) * kD + tid) * kD : nullptr;
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
-        float s[32], ds[32];
+        float s[32];
         tmem_ld_row<32>(lane_base + kColS + q4 * 32, s);
-        tmem_ld_row<32>(lane_base + kColDS + q4 * 32, ds);
-#pragma unroll
-        for (int e = 0; e < 32; ++e) s[e] = fmaf(g_last, s[e], ds[e]);
 #pragma unroll
         for (int c8 = 0; c8 < 4; ++c8) {
-          tmem_st8(lane_base + kColS + q4 * 32 + c8 * 8, s + c8 * 8);
           sm.s[(q4 * 4 + c8) * kD + tid] = pack8_bf16(s + c8 * 8);
           if (sl) {
             *reinterpret_cast<float4*>(sl + q4 * 32 + c8 * 8) = make_float4(s[c8 * 8], s[c8 * 8 + 1], s[c8 * 8 + 2], s[c8 * 8 + 3]);
@@ -221,16 +234,16 @@ __global__ void __launch_bounds__(kThreads) gdelta_fwd_kernel(const FwdParams p)
           }
         }
       }
-      tmem_st_wait();
     }
     __syncthreads();
     {
       __nv_bfloat16* obase = p.o + seq_base + static_cast<size_t>(t0) * stride_t;
+      const uint4* src = reinterpret_cast<const uint4*>(sm.lt);
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const int vid = r * kThreads + tid;
+      for (int rr = 0; rr < 8; ++rr) {
+        const int vid = rr * kThreads + tid;
         const int trow = vid >> 4, seg = vid & 15;
-        if (trow < valid) *reinterpret_cast<uint4*>(obase + trow * stride_t + seg * 8) = sm.vplain[trow * 16 + seg];
+        if (trow < valid) *reinterpret_cast<uint4*>(obase + trow * stride_t + seg * 8) = src[trow * 16 + seg];
       }
     }
   }
