@@ -273,3 +273,63 @@ class DeltaNetCell(MemoroidCellBase):
         o, s_last = ops.GatedDelta.apply(q.to(bf), k.to(bf), v.to(bf), alpha.contiguous(), beta.contiguous(), s0, done)
         o = o.reshape(*o.shape[:2], -1).to(inputs.dtype)
         return (s_last[:, None],), self.output_projection(self.norm(o))
+
+
+# ----------------------------------------------------------------------- S5
+class S5Cell(MemoroidCellBase):
+    """Diagonal state-space cell (s5.py:18-149): the same (state, decay) operator
+    as the LRU with a discretised, time-invariant ``lambda_bar`` (ZOH or bilinear,
+    hippo.py:34-50).  The HiPPO-DPLR initialisation of the reference is
+    initialisation-time CPU work outside this path; ``lambda`` starts at
+    ``-1/2 + i pi n`` here."""
+
+    def __init__(self, features, state_size, discretization="zoh", dt_min=0.001, dt_max=0.1, step_rescale=1.0):
+        super().__init__()
+        self.features, self.state_size = features, state_size
+        self.discretization, self.step_rescale = discretization, step_rescale
+        self.lambda_real = nn.Parameter(torch.full((state_size,), -0.5))
+        self.lambda_imag = nn.Parameter(math.pi * torch.arange(state_size, dtype=torch.float32))
+        self.B = nn.Parameter(torch.randn(state_size, features, 2) / math.sqrt(2 * features))
+        self.C = nn.Parameter(torch.randn(features, state_size, 2) * math.sqrt(0.5))
+        self.d = nn.Parameter(torch.randn(features))
+        u = torch.rand(state_size, 1)
+        self.log_step = nn.Parameter(u * (math.log(dt_max) - math.log(dt_min)) + math.log(dt_min))
+
+    def _discretized(self):
+        lam = torch.complex(self.lambda_real, self.lambda_imag)
+        b_tilde = torch.view_as_complex(self.B.contiguous())
+        step = (self.step_rescale * torch.exp(self.log_step[:, 0])).to(torch.complex64)
+        if self.discretization == "zoh":
+            lambda_bar = torch.exp(lam * step)
+            b_bar = ((lambda_bar - 1.0) / lam)[:, None] * b_tilde
+        elif self.discretization == "bilinear":
+            bl = 1.0 / (1.0 - step / 2.0 * lam)
+            lambda_bar = bl * (1.0 + step / 2.0 * lam)
+            b_bar = (bl * step)[:, None] * b_tilde
+        else:
+            raise ValueError(f"Invalid discretization: {self.discretization}")
+        return lambda_bar, b_bar
+
+    def forward(self, x, **kwargs):
+        lambda_bar, b_bar = self._discretized()
+        return torch.matmul(x.to(torch.complex64), b_bar.t()), lambda_bar
+
+    def binary_operator(self, a, b):
+        s_i, a_i = a
+        s_j, a_j = b
+        return a_j * s_i + s_j, a_j * a_i
+
+    def read(self, h, x, **kwargs):
+        c_tilde = torch.view_as_complex(self.C.contiguous())
+        return torch.matmul(h[0], c_tilde.t()).real + self.d * x
+
+    def initialize_carry(self, key, input_shape):
+        *batch, _ = input_shape
+        return (torch.zeros(*batch, 1, self.state_size, dtype=torch.complex64),
+                torch.ones(*batch, 1, self.state_size, dtype=torch.complex64))
+
+    def scan(self, z, initial_carry, done, inputs):
+        state, lambda_bar = z
+        h0, a0 = _squeeze_carry(initial_carry, 2)
+        h, a_last = ops.LinRec.apply(lambda_bar, state.contiguous(), h0, a0, done)
+        return (h[:, -1:], a_last[:, None]), self.read((h, None), inputs)

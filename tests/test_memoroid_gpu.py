@@ -66,3 +66,23 @@ def test_linear_attention_and_deltanet_modules_run_and_thread_carry():
         assert torch.allclose(torch.cat([y1, y2], 1), y, atol=2e-2)
         y.square().mean().backward()
         assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())
+
+
+@pytest.mark.parametrize("disc", ["zoh", "bilinear"])
+def test_s5_module_matches_oracle(disc):
+    from memorax_b200.memoroid import Memoroid, S5Cell
+    torch.manual_seed(3)
+    cell = S5Cell(features=6, state_size=16, discretization=disc).cuda()
+    model = Memoroid(cell)
+    x, done = torch.randn(2, 40, 6, device="cuda"), _done(2, 40, 0.05, seed=4)
+    (h_last, a_last), y = model(x, done)
+    state, lam = cell(x)
+    h_ref, a_ref = mo.linrec_seq(lam.detach().cpu().to(torch.complex128), state.detach().cpu().to(torch.complex128),
+                                 torch.zeros(2, 16, dtype=torch.complex128), done.cpu().double())
+    scale = float(h_ref.abs().max())
+    assert float((h_last[:, 0].detach().cpu() - h_ref[:, -1]).abs().max()) <= 1e-5 * scale
+    c = torch.view_as_complex(cell.C.detach().cpu().contiguous()).to(torch.complex128)
+    y_ref = (h_ref @ c.t()).real + cell.d.detach().cpu().double() * x.cpu().double()
+    assert float((y.detach().cpu().double() - y_ref).abs().max()) <= 1e-4 * max(1.0, float(y_ref.abs().max()))
+    y.square().mean().backward()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in cell.parameters())
