@@ -194,6 +194,84 @@ linrec_fwd_kernel(const float* __restrict__ a, int a_tinv, const float* __restri
   }
 }
 
+// ---------------------------------------------- forward, time-split (small B*D)
+// When there are too few channels to fill the machine with one thread per
+// channel walking all of T, the time axis is split as well: a block owns
+// 32 x W channels (a warp reads 128 W contiguous bytes per step) x 16 contiguous
+// time segments.  Every thread loads its segment (<= L steps) into registers,
+// folds it into an affine map (P, Q) with h_out = P h_in + Q (a reset makes
+// P = 0), the sixteen maps of a channel are chained through shared memory, and
+// each thread replays its segment from the right incoming state.  One pass over
+// memory, T/16 sequential steps per thread.
+constexpr int kSegs = 16;
+
+template <int L, int W>
+__global__ void __launch_bounds__(32 * kSegs)
+linrec_fwd_tsplit_kernel(const float* __restrict__ a, int a_tinv, const float* __restrict__ b,
+                         const float* __restrict__ h0, const float* __restrict__ a0,
+                         const uint8_t* __restrict__ done, float* __restrict__ h, float* __restrict__ a_last,
+                         int B, int T, int D) {
+  __shared__ float sp[kSegs][32 * W], sq[kSegs][32 * W], sd[kSegs][32 * W];
+  __shared__ int sr[kSegs][32];
+  const int cx = threadIdx.x & 31, seg = threadIdx.x >> 5;
+  const long long ch = (static_cast<long long>(blockIdx.x) * 32 + cx) * W;   // first channel = b * D + d
+  const bool active = ch < static_cast<long long>(B) * D;
+  const int bi = active ? static_cast<int>(ch / D) : 0, d = active ? static_cast<int>(ch % D) : 0;
+  const int len = (T + kSegs - 1) / kSegs;
+  const int t_begin = seg * len, t_end = min(T, t_begin + len);
+  const size_t base = static_cast<size_t>(bi) * T * D + d;
+  const uint8_t* drow = done ? done + static_cast<size_t>(bi) * T : nullptr;
+
+  Pack<W> av[L], bv[L];
+  bool rs[L];
+  Pack<W> a_fix = fill_pack<W>(0.f, 0.f, false);
+  if (a_tinv && active) a_fix = load_pack_cached<W>(a + d);
+#pragma unroll
+  for (int i = 0; i < L; ++i) {
+    const int t = t_begin + i;
+    const bool in = active && t < t_end;
+    bv[i] = in ? load_pack<W>(b + base + static_cast<size_t>(t) * D) : fill_pack<W>(0.f, 0.f, false);
+    av[i] = in ? (a_tinv ? a_fix : load_pack<W>(a + base + static_cast<size_t>(t) * D)) : fill_pack<W>(1.f, 0.f, false);
+    rs[i] = in && drow && drow[t] != 0;
+  }
+  // segment summary: state map (P, Q); decay leaf: product since the last reset, and whether there was one
+  Pack<W> P = fill_pack<W>(1.f, 0.f, false), Q = fill_pack<W>(0.f, 0.f, false), dec = fill_pack<W>(1.f, 0.f, false);
+  int had_reset = 0;
+#pragma unroll
+  for (int i = 0; i < L; ++i) {
+    if (rs[i]) { P = fill_pack<W>(0.f, 0.f, false); Q = bv[i]; dec = av[i]; had_reset = 1; }
+    else { P = mul<false, W>(P, av[i]); Q = mul_add<false, W>(av[i], Q, bv[i]); dec = mul<false, W>(dec, av[i]); }
+  }
+#pragma unroll
+  for (int e = 0; e < W; ++e) {
+    sp[seg][cx * W + e] = P.v[e];
+    sq[seg][cx * W + e] = Q.v[e];
+    sd[seg][cx * W + e] = dec.v[e];
+  }
+  sr[seg][cx] = had_reset;
+  __syncthreads();
+  Pack<W> hin = (active && h0) ? load_pack_cached<W>(h0 + static_cast<size_t>(bi) * D + d) : fill_pack<W>(0.f, 0.f, false);
+  for (int s2 = 0; s2 < seg; ++s2) {
+#pragma unroll
+    for (int e = 0; e < W; ++e) hin.v[e] = fmaf(sp[s2][cx * W + e], hin.v[e], sq[s2][cx * W + e]);
+  }
+#pragma unroll
+  for (int i = 0; i < L; ++i) {
+    const int t = t_begin + i;
+    hin = rs[i] ? bv[i] : mul_add<false, W>(av[i], hin, bv[i]);
+    if (active && t < t_end) store_pack<W>(h + base + static_cast<size_t>(t) * D, hin);
+  }
+  if (a_last && seg == kSegs - 1 && active) {
+    Pack<W> acc = a0 ? load_pack_cached<W>(a0 + static_cast<size_t>(bi) * D + d) : fill_pack<W>(1.f, 0.f, false);
+    for (int s2 = 0; s2 < kSegs; ++s2) {
+#pragma unroll
+      for (int e = 0; e < W; ++e) acc.v[e] = sr[s2][cx] ? sd[s2][cx * W + e] : acc.v[e] * sd[s2][cx * W + e];
+    }
+#pragma unroll
+    for (int e = 0; e < W; ++e) a_last[static_cast<size_t>(bi) * D + d + e] = acc.v[e];
+  }
+}
+
 // ----------------------------------------------------------------- backward
 // Walks time right to left carrying c = a_{t+1} m_{t+1} g_{t+1}.
 template <bool CPLX, int W>
@@ -452,6 +530,25 @@ int linrec_fwd(const float* a, int a_tinv, const float* b, const float* h0, cons
   const long long total = static_cast<long long>(B) * row;
   const int w = pick_width(total, row, CPLX, {a, b, h0, a0, h, a_last});
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if constexpr (!CPLX) {
+    // few channels, moderate T: split time too (one launch, T/16 sequential steps per thread)
+    if (w == 1 && total <= 4LL * kNumSMs * kBlock && T >= 32 && T <= kSegs * 16) {
+      const int len = (T + kSegs - 1) / kSegs;
+      bool wide = (D % 4 == 0) && len <= 8;   // 16-byte lanes keep 8 steps x (a, b) in registers
+      for (const void* ptr : {(const void*)a, (const void*)b, (const void*)h0, (const void*)a0, (const void*)h, (const void*)a_last})
+        if (ptr && !aligned16(ptr)) wide = false;
+      const unsigned threads = 32 * kSegs;
+      if (wide) {
+        const unsigned blocks = static_cast<unsigned>((total / 4 + 31) / 32);
+        linrec_fwd_tsplit_kernel<8, 4><<<blocks, threads, 0, s>>>(a, a_tinv, b, h0, a0, done, h, a_last, B, T, D);
+      } else {
+        const unsigned blocks = static_cast<unsigned>((total + 31) / 32);
+        if (len <= 8) linrec_fwd_tsplit_kernel<8, 1><<<blocks, threads, 0, s>>>(a, a_tinv, b, h0, a0, done, h, a_last, B, T, D);
+        else linrec_fwd_tsplit_kernel<16, 1><<<blocks, threads, 0, s>>>(a, a_tinv, b, h0, a0, done, h, a_last, B, T, D);
+      }
+      return launch_status();
+    }
+  }
   if (w == 4)
     linrec_fwd_kernel<CPLX, 4><<<blocks_for(total / 4), kBlock, 0, s>>>(a, a_tinv, b, h0, a0, done, h, a_last, B, T, row);
   else

@@ -112,13 +112,32 @@ def test_linrec_split_sequence_is_bit_identical():
     """One call over T == two calls threading the carry (memoroid.py:89)."""
     from memorax_b200 import ops
     gen = torch.Generator().manual_seed(11)
-    a, b = torch.rand(4, 40, 64, generator=gen).cuda(), torch.randn(4, 40, 64, generator=gen).cuda()
-    done = make_done(gen, 4, 40, 0.1).cuda()
+    # wide enough for the streaming kernel (the time-split kernel for small B*D chains affine
+    # maps across segments and agrees to rounding, not bit for bit)
+    a, b = torch.rand(40, 40, 8192, generator=gen).cuda(), torch.randn(40, 40, 8192, generator=gen).cuda()
+    done = make_done(gen, 40, 40, 0.1).cuda()
     h, acc = ops.linrec_fwd(a, b, None, None, done)
     h1, acc1 = ops.linrec_fwd(a[:, :13].contiguous(), b[:, :13].contiguous(), None, None, done[:, :13])
     h2, acc2 = ops.linrec_fwd(a[:, 13:].contiguous(), b[:, 13:].contiguous(), h1[:, -1].contiguous(), acc1, done[:, 13:])
     assert torch.equal(torch.cat([h1, h2], 1), h)
     assert torch.equal(acc2, acc)
+
+
+@pytest.mark.parametrize("steps", [32, 33, 40, 128, 255, 256])
+@pytest.mark.parametrize("tinv", [False, True])
+def test_linrec_time_split_kernel(steps, tinv):
+    """Small B*D with moderate T takes the time-split forward kernel."""
+    from memorax_b200 import ops
+    gen = torch.Generator().manual_seed(steps)
+    bsz, dim = 5, 48
+    a = torch.rand(*((dim,) if tinv else (bsz, steps, dim)), generator=gen, dtype=torch.float64)
+    b, h0, a0 = rnd(gen, bsz, steps, dim), rnd(gen, bsz, dim), rnd(gen, bsz, dim)
+    done = make_done(gen, bsz, steps, 0.08)
+    h_ref, acc_ref = mo.linrec_seq(a, b, h0, done.double(), a0)
+    cu = lambda t: t.float().cuda()
+    h, acc = ops.linrec_fwd(cu(a), cu(b), cu(h0), cu(a0), done.cuda())
+    close(h, h_ref, what="h")
+    close(acc, acc_ref, what="a_last")
 
 
 def test_linrec_rejects_bad_arguments():
