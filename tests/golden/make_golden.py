@@ -203,7 +203,7 @@ def done_patterns(rng, bsz, steps):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a memorax 1.0.1 checkout")
     ap.add_argument("--out", default=os.path.join(os.path.dirname(__file__), "memoroid_golden.npz"))
     args = ap.parse_args()
     install_stand_ins(args.reference)
