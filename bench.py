@@ -56,7 +56,7 @@ class LinAttnC2:
     launches_per_step = 2
     e2e_slices = 4   # independent sequences: copy-in, kernels and copy-out overlap slice by slice
     # dram__bytes_read.sum + dram__bytes_write.sum of one linattn_bwd_kernel launch at
-    # this size; see profiles/linattn_c2.md
+    # this size (ncu capture summarised under profiles/)
     dominant_traffic_bytes = 249.7e6
 
     def __init__(self, batch=None):
@@ -543,7 +543,7 @@ def run_gpu_arm(args):
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     from memorax_b200.host import HostPipeline
-    nslices = getattr(w, "e2e_slices", 1)
+    nslices = args.e2e_slices or getattr(w, "e2e_slices", 1)
     pipe = HostPipeline(lambda xs: w.step(xs, ops), w.B, dev, slices=nslices)
     pipe.run(pinned_in, pinned_out)          # warm the three streams' allocator pools
     barrier()
@@ -599,6 +599,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=None, help="override sequences per GPU (profiling only)")
+    ap.add_argument("--e2e-slices", type=int, default=None, help="override the batch slices of the host pipeline")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     if args.impl == "reference":
