@@ -196,7 +196,8 @@ int mxk_linattn_bf16_bwd(const void* q, const void* k, const void* v, const void
  *   s0        (B,H,d_v,d_k) fp32 carried state, NULL = zeros
  *   o         (B,T,H,d) bf16 out;  s_last (B,H,d_v,d_k) fp32 out, optional
  *   chunk_states  optional residual for the backward call,
- *             mxk_gdelta_chunk_states_bytes(...) bytes
+ *             mxk_gdelta_chunk_states_bytes(...) bytes (per chunk: the bf16 state
+ *             entering it and the solved pseudo-values U)
  *   status    optional device int, set non-zero if a bounded wait gave up
  * ------------------------------------------------------------------------- */
 size_t mxk_gdelta_chunk_states_bytes(int B, int T, int H, int d);

@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const FwdParams
     stage_panel_tile(sm.q, p.q + seq_base + static_cast<size_t>(t0) * stride_t, stride_t, valid, tid);
     stage_plain_tile(sm.vu, p.v + seq_base + static_cast<size_t>(t0) * stride_t, stride_t, valid, tid);
     if (p.chunk_states) {
-      uint4* dst = p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * kStateVecs;
+      uint4* dst = p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * kResidualVecs;
       for (int i = tid; i < kStateVecs; i += kThreads) dst[i] = sm.s[i];
     }
     fence_smem_to_async();
@@ -178,8 +178,15 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const FwdParams
     for (int t = 0; t < kC; ++t) r[t] = sm.cd.beta[t] * (bf16_at(sm.vu, t, tid) - sm.cd.g[t] * r[t]);
     __syncthreads();   // -beta L complete; V consumed (U^T reuses its buffer)
     forward_substitute(reinterpret_cast<float2*>(r), sm.lt);
+    {
+      uint4* res = p.chunk_states ? p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * kResidualVecs + kStateVecs : nullptr;
 #pragma unroll
-    for (int jp = 0; jp < kPanC; ++jp) sm.vu[jp * kD + tid] = pack8_bf16(r + jp * 8);
+      for (int jp = 0; jp < kPanC; ++jp) {
+        const uint4 u8 = pack8_bf16(r + jp * 8);
+        sm.vu[jp * kD + tid] = u8;
+        if (res) res[jp * kD + tid] = u8;   // the backward pass reuses U instead of solving again
+      }
+    }
     {
       const float g_last = sm.cd.g[kC - 1];
 #pragma unroll
@@ -262,7 +269,7 @@ extern "C" {
 size_t mxk_gdelta_chunk_states_bytes(int B, int T, int H, int d) {
   if (B <= 0 || T <= 0 || H <= 0 || d != mxk::gdelta::kD) return 0;
   const size_t nchunks = (static_cast<size_t>(T) + mxk::gdelta::kC - 1) / mxk::gdelta::kC;
-  return static_cast<size_t>(B) * H * nchunks * mxk::gdelta::kStateVecs * sizeof(uint4);
+  return static_cast<size_t>(B) * H * nchunks * mxk::gdelta::kResidualVecs * sizeof(uint4);
 }
 
 int mxk_gdelta_bf16_fwd(const void* q, const void* k, const void* v, const float* alpha, const float* beta,

@@ -2,7 +2,7 @@
 //
 // One CTA (128 threads) owns one (batch, head) sequence and walks its 64-token
 // chunks right to left with the fp32 cotangent of the state, dS (128 x 128),
-// resident in tensor memory.  S_in of every chunk is the forward call's residual.
+// resident in tensor memory.  S_in and U of every chunk are the forward call's residual.
 // With the chunk quantities of gdelta_common.cuh (A = I + diag(beta) L, P =
 // tril(G o QK^T), R = V - diag(g) K S_in^T, U = A^-1 diag(beta) R):
 //   dU   = P^T dO + diag(gam) K dS^T            dUt = A^-T dU      (back substitution)
@@ -148,11 +148,21 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
     stage_panel_tile(sm.k, p.k + tile, stride_t, valid, tid);
     stage_panel_tile(sm.q, p.q + tile, stride_t, valid, tid);
     stage_panel_tile(sm.d_o, p.d_o + tile, stride_t, valid, tid);
-    stage_plain_tile(sm.r1, p.v + tile, stride_t, valid, tid);
     stage_plain_tile(sm.r2, p.d_o + tile, stride_t, valid, tid);
     {
-      const uint4* src = p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * kStateVecs;
+      const uint4* src = p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * kResidualVecs;
       for (int i = tid; i < kStateVecs; i += kThreads) sm.s[i] = __ldg(src + i);
+      // U^T saved by the forward pass; thread v owns row v of every panel, so it can also write (gam U)^T
+#pragma unroll
+      for (int jp = 0; jp < kPanC; ++jp) {
+        const uint4 u8 = __ldg(src + kStateVecs + jp * kD + tid);
+        float f[8];
+        unpack8_bf16(u8, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] *= sm.cd.gam[jp * 8 + e];
+        sm.u[jp * kD + tid] = u8;
+        sm.ug[jp * kD + tid] = pack8_bf16(f);
+      }
     }
     fence_smem_to_async();
     fence_before_sync();
@@ -193,10 +203,7 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
             const float gtj = in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
             pm[e] = gtj * qk[jq * 8 + e];
             const float bl = (j < row) ? -beta_t * gtj * kk[jq * 8 + e] : 0.f;
-            if (row_active) {
-              sm.lt[j * kC + row] = bl;
-              sm.l[row * kC + j] = bl;
-            }
+            if (row_active) sm.l[row * kC + j] = bl;
           }
           if (row_active) sm.p[(half * 4 + jq) * kC + row] = pack8_bf16(pm);
         }
@@ -204,21 +211,9 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
     }
     __syncthreads();
 
-    // ---- epilogue A2: thread v recomputes its column of U; first dg term ----
+    // ---- epilogue A2: first dg term ----
     {
-      __align__(8) float r[kC];
-      tmem_ld_row<kC>(lane_base + kColY, r);
-#pragma unroll
-      for (int t = 0; t < kC; ++t) r[t] = sm.cd.beta[t] * (bf16_at(sm.r1, t, tid) - sm.cd.g[t] * r[t]);
-      forward_substitute(reinterpret_cast<float2*>(r), sm.lt);
-#pragma unroll
-      for (int jp = 0; jp < kPanC; ++jp) {
-        float sc[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) sc[e] = r[jp * 8 + e] * sm.cd.gam[jp * 8 + e];
-        sm.u[jp * kD + tid] = pack8_bf16(r + jp * 8);
-        sm.ug[jp * kD + tid] = pack8_bf16(sc);
-      }
+      float r[kC];
       // dg_t += sum_v dO[t][v] (S_in q_t)[v]
       tmem_ld_row<kC>(lane_base + kColOI, r);
 #pragma unroll

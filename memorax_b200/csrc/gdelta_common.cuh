@@ -32,6 +32,9 @@ constexpr int kThreads = 128;
 constexpr int kPanD = kD / 8;   // panels of a matrix with 128 columns
 constexpr int kPanC = kC / 8;   // panels of a matrix with 64 columns
 constexpr int kStateVecs = kPanD * kD;  // uint4 per bf16 state copy (32 KiB)
+constexpr int kUVecs = kPanC * kD;      // uint4 per bf16 U^T of one chunk (16 KiB)
+// Residual the forward call leaves per (sequence, chunk): the state entering the chunk, then U^T.
+constexpr int kResidualVecs = kStateVecs + kUVecs;
 
 struct ChunkDecay {
   float alpha[kC], beta[kC], cum[kC], g[kC], gam[kC];

@@ -51,7 +51,7 @@ def test_status_strings_and_validation_without_a_gpu(lib):
     assert L.mxk_gdelta_bf16_fwd(p, p, p, p, p, None, None, p + 2, None, None, None, 1, 1, 1, 128, None) == -3
     assert L.mxk_linrec_c64_bwd_noalloc(p, p, None, None, p, None, p, p, None, 1 << 12, 1, 1 << 12, 0, None) == -6
     assert L.mxk_linattn_chunk_states_bytes(2, 65, 3, 64) == 2 * 3 * 2 * 9 * 64 * 16
-    assert L.mxk_gdelta_chunk_states_bytes(2, 65, 3, 128) == 2 * 3 * 2 * 16 * 128 * 16
+    assert L.mxk_gdelta_chunk_states_bytes(2, 65, 3, 128) == 2 * 3 * 2 * (16 + 8) * 128 * 16
     assert L.mxk_linrec_bwd_workspace_bytes(1, 1, 4, 9, 8) == 4 * 8 * 8
 
 
