@@ -67,6 +67,7 @@ struct BwdSmem {
 static_assert(sizeof(BwdSmem) <= 227 * 1024, "backward shared memory exceeds one SM");
 
 constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kUpper = 16u << 16;
 constexpr uint32_t kColDS = 0, kColKK = 128, kColQK = 192, kColY = 256, kColOI = 320, kColX1 = 320, kColW = 320,
                    kColX2 = 384, kColDP = 448, kColDQ = 128, kColDK = 256, kColDelta = 384;
 
@@ -95,6 +96,7 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
   const int row = warp * 16 + (lane & 15);
   const bool row_active = lane < 16;
+  const bool upper = lane >= 16;
   const int nchunks = (p.T + kC - 1) / kC;
 
   if (tid == 0) {
@@ -173,9 +175,16 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
       fence_after_sync();
       const Operand ak{smem_u32(sm.k), kC, false}, aq{smem_u32(sm.q), kC, false};
       const Operand as{smem_u32(sm.s), kD, false}, ads{smem_u32(sm.ds), kD, false};
-      const uint32_t id_64 = idesc_bf16(kC, kC, false, false), id_128 = idesc_bf16(kD, kC, false, false);
-      gemm(tmem + kColKK, ak, ak, id_64, kD / 16, false);
-      gemm(tmem + kColQK, aq, ak, id_64, kD / 16, false);
+      const uint32_t id_128 = idesc_bf16(kD, kC, false, false);
+      // 64 x 64 products are issued as two N = 32 halves: keys 0..31 land in lanes 0..15 of each
+      // warp's TMEM quarter, keys 32..63 in lanes 16..31 of the same columns, so both half-warps
+      // work on the same token row in the epilogues
+      const Operand bk_lo{smem_u32(sm.k), kC, false}, bk_hi{smem_u32(sm.k) + 32 * 16, kC, false};
+      const uint32_t id_half = idesc_bf16(kC, 32, false, false);
+      gemm(tmem + kColKK, ak, bk_lo, id_half, kD / 16, false);
+      gemm(tmem + kUpper + kColKK, ak, bk_hi, id_half, kD / 16, false);
+      gemm(tmem + kColQK, aq, bk_lo, id_half, kD / 16, false);
+      gemm(tmem + kUpper + kColQK, aq, bk_hi, id_half, kD / 16, false);
       gemm(tmem + kColY, as, ak, id_128, kD / 16, false);
       gemm(tmem + kColOI, as, aq, id_128, kD / 16, false);
       gemm(tmem + kColX2, ads, ak, id_128, kD / 16, false);
@@ -184,29 +193,27 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
     if (!mbar_wait(&sm.bar[0], 0)) timed_out = true;
     fence_after_sync();
 
-    // ---- epilogue A1: row threads -> beta L (both orientations), tril(G o QK^T) ----
+    // ---- epilogue A1: -beta L (fp32, row-major) and tril(G o QK^T) (bf16); every thread owns
+    //      32 keys of its token row ----
     {
       const int lo = row_first_key(dm, row);
       const float cum_t = sm.cd.cum[row], beta_t = sm.cd.beta[row];
+      const int j0 = upper ? 32 : 0;
+      float kk[32], qk[32];
+      tmem_ld_row<32>(lane_base + kColKK, kk);
+      tmem_ld_row<32>(lane_base + kColQK, qk);
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        float kk[32], qk[32];
-        tmem_ld_row<32>(lane_base + kColKK + half * 32, kk);
-        tmem_ld_row<32>(lane_base + kColQK + half * 32, qk);
+      for (int jq = 0; jq < 4; ++jq) {
+        float pm[8];
 #pragma unroll
-        for (int jq = 0; jq < 4; ++jq) {
-          float pm[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int j = half * 32 + jq * 8 + e;
-            const bool in = (j >= lo && j <= row);
-            const float gtj = in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
-            pm[e] = gtj * qk[jq * 8 + e];
-            const float bl = (j < row) ? -beta_t * gtj * kk[jq * 8 + e] : 0.f;
-            if (row_active) sm.l[row * kC + j] = bl;
-          }
-          if (row_active) sm.p[(half * 4 + jq) * kC + row] = pack8_bf16(pm);
+        for (int e = 0; e < 8; ++e) {
+          const int x = jq * 8 + e, j = j0 + x;
+          const bool in = (j >= lo && j <= row);
+          const float gtj = in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
+          pm[e] = gtj * qk[x];
+          sm.l[row * kC + j] = (j < row) ? -beta_t * gtj * kk[x] : 0.f;
         }
+        sm.p[((j0 >> 3) + jq) * kC + row] = pack8_bf16(pm);
       }
     }
     __syncthreads();
@@ -232,7 +239,9 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
       gemm(tmem + kColX1, Operand{smem_u32(sm.d_o), kC, true}, Operand{smem_u32(sm.p), kC, true},
            idesc_bf16(kD, kC, true, true), kC / 16, false);
       gemm(tmem + kColDP, Operand{smem_u32(sm.d_o), kC, false}, Operand{smem_u32(sm.u), kD, true},
-           idesc_bf16(kC, kC, false, true), kD / 16, false);
+           idesc_bf16(kC, 32, false, true), kD / 16, false);
+      gemm(tmem + kUpper + kColDP, Operand{smem_u32(sm.d_o), kC, false}, Operand{smem_u32(sm.u) + 4 * kD * 16, kD, true},
+           idesc_bf16(kC, 32, false, true), kD / 16, false);
       commit(&sm.bar[1]);
     }
     if (!mbar_wait(&sm.bar[1], 0)) timed_out = true;
@@ -320,33 +329,37 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
     if (tid == 0) {
       fence_after_sync();
       gemm(tmem + kColW, Operand{smem_u32(sm.r1), kD, true}, Operand{smem_u32(sm.u), kD, true},
-           idesc_bf16(kC, kC, true, true), kD / 16, false);
+           idesc_bf16(kC, 32, true, true), kD / 16, false);
+      gemm(tmem + kUpper + kColW, Operand{smem_u32(sm.r1), kD, true}, Operand{smem_u32(sm.u) + 4 * kD * 16, kD, true},
+           idesc_bf16(kC, 32, true, true), kD / 16, false);
       commit(&sm.bar[0]);
     }
     if (!mbar_wait(&sm.bar[0], 1)) timed_out = true;
     fence_after_sync();
     __syncthreads();  // every thread has flushed its part of the dV tile before `lt` is reused
 
-    // ---- epilogue C: row threads: (dP o G), (dL o G), E, dbeta; g-scaled dO ----
+    // ---- epilogue C: (dP o G), (dL o G), E, dbeta; g-scaled dO.  Every thread owns 32 keys of
+    //      its token row ----
     {
       uint4* dpg = reinterpret_cast<uint4*>(sm.lt);           // [j/8][t][8]
       uint4* dlg = dpg + kPanC * kC;
       const int lo = row_first_key(dm, row);
       const float cum_t = sm.cd.cum[row], beta_t = sm.cd.beta[row];
+      const int j0 = upper ? 32 : 0;
       float rs = 0.f, wtt = 0.f;
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
+      for (int h2 = 0; h2 < 2; ++h2) {
         float kk[16], qk[16], dp[16], w[16];
-        tmem_ld_row<16>(lane_base + kColKK + q4 * 16, kk);
-        tmem_ld_row<16>(lane_base + kColQK + q4 * 16, qk);
-        tmem_ld_row<16>(lane_base + kColDP + q4 * 16, dp);
-        tmem_ld_row<16>(lane_base + kColW + q4 * 16, w);
+        tmem_ld_row<16>(lane_base + kColKK + h2 * 16, kk);
+        tmem_ld_row<16>(lane_base + kColQK + h2 * 16, qk);
+        tmem_ld_row<16>(lane_base + kColDP + h2 * 16, dp);
+        tmem_ld_row<16>(lane_base + kColW + h2 * 16, w);
 #pragma unroll
         for (int jq = 0; jq < 2; ++jq) {
           float a8[8], b8[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            const int x = jq * 8 + e, j = q4 * 16 + x;
+            const int x = jq * 8 + e, j = j0 + h2 * 16 + x;
             const bool in = (j >= lo && j <= row);
             const float gtj = in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
             const float dl = (j < row) ? -beta_t * w[x] : 0.f;
@@ -355,26 +368,28 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
             b8[e] = dl * gtj;
             const float ev = (dp[x] * qk[x] + dl * kk[x]) * gtj;
             rs += ev;
-            if (row_active) sm.l[row * kC + j] = ev;
+            sm.l[row * kC + j] = ev;
           }
-          if (row_active) {
-            dpg[(q4 * 2 + jq) * kC + row] = pack8_bf16(a8);
-            dlg[(q4 * 2 + jq) * kC + row] = pack8_bf16(b8);
-          }
+          const int pn = (j0 >> 3) + h2 * 2 + jq;
+          dpg[pn * kC + row] = pack8_bf16(a8);
+          dlg[pn * kC + row] = pack8_bf16(b8);
         }
       }
-      if (row_active) {
+      rs += __shfl_xor_sync(0xffffffffu, rs, 16);
+      wtt += __shfl_xor_sync(0xffffffffu, wtt, 16);
+      if (!upper) {
         sm.rowsum[row] = rs;
         if (row < valid) p.dbeta[(static_cast<size_t>(b) * p.T + t0 + row) * p.H + h] = beta_t > 0.f ? wtt / beta_t : 0.f;
-        const float gt = sm.cd.g[row];
+      }
+      const float gt = sm.cd.g[row];
+      const int p0 = upper ? kPanD / 2 : 0;
 #pragma unroll
-        for (int pn = 0; pn < kPanD; ++pn) {
-          float f[8];
-          unpack8_bf16(sm.d_o[pn * kC + row], f);
+      for (int pp = 0; pp < kPanD / 2; ++pp) {
+        float f[8];
+        unpack8_bf16(sm.d_o[(p0 + pp) * kC + row], f);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] *= gt;
-          sm.d_o[pn * kC + row] = pack8_bf16(f);
-        }
+        for (int e = 0; e < 8; ++e) f[e] *= gt;
+        sm.d_o[(p0 + pp) * kC + row] = pack8_bf16(f);
       }
     }
     fence_smem_to_async();
