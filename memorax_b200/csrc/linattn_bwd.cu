@@ -70,11 +70,15 @@ struct BwdSmem {
 // 256 TMEM columns per CTA (two CTAs per SM).  M = 64 accumulators use 16 of a
 // warp's 32 TMEM lanes, so lanes 0..15 ("lower" threads) and 16..31 ("upper"
 // threads) hold different matrices in the same columns:
-//   columns   0.. 63   lower: P, later dphiQ      upper: dA, later dphiK
-//   columns  64..135   lower: R, later dV         upper: G^T | gz (persistent)
+//   columns   0.. 63   first P (0..31) and dA (32..63), each issued as two N = 32 halves: keys
+//                      0..31 in the lower lanes, keys 32..63 in the upper lanes, so that both
+//                      half-warps own 32 keys of the same query row; later dphiQ (lower) and
+//                      dphiK (upper)
+//   columns  64..135   lower: dV                  upper: G^T | gz (persistent)
+//   columns 136..167   R, state features 0..31 in the lower lanes, 32..63 in the upper lanes
 constexpr uint32_t kBwdTmemCols = 256;
 constexpr uint32_t kUpper = 16u << 16;
-constexpr uint32_t kColLo = 0, kColHi = 64;
+constexpr uint32_t kColLo = 0, kColHi = 64, kColP = 0, kColA = 32, kColR = 136;
 
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 
@@ -199,68 +203,70 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
       const Operand aq{smem_u32(sm.q), kC, false}, bk{smem_u32(sm.k), kC, false};
       const Operand ado{smem_u32(sm.d_o), kC, false}, bv{smem_u32(sm.v), kC, false};
       const Operand bs{smem_u32(sm.s), kD, false};
-      gemm(tmem + kColLo, aq, bk, id_kk, kD / 16, false);             // P  (lower)
-      gemm(tmem + kUpper + kColLo, ado, bv, id_kk, kD / 16, false);   // dA (upper)
-      gemm(tmem + kColHi, ado, bs, id_kk, kD / 16, false);            // R  (lower)
+      const uint32_t id_half = idesc_bf16(kC, 32, false, false);
+      const Operand bk_hi{smem_u32(sm.k) + 32 * 16, kC, false}, bv_hi{smem_u32(sm.v) + 32 * 16, kC, false};
+      const Operand bs_hi{smem_u32(sm.s) + 32 * 16, kD, false};
+      gemm(tmem + kColP, aq, bk, id_half, kD / 16, false);                 // P,  keys 0..31
+      gemm(tmem + kUpper + kColP, aq, bk_hi, id_half, kD / 16, false);     // P,  keys 32..63
+      gemm(tmem + kColA, ado, bv, id_half, kD / 16, false);                // dA, keys 0..31
+      gemm(tmem + kUpper + kColA, ado, bv_hi, id_half, kD / 16, false);    // dA, keys 32..63
+      gemm(tmem + kColR, ado, bs, id_half, kD / 16, false);                // R,  features 0..31
+      gemm(tmem + kUpper + kColR, ado, bs_hi, id_half, kD / 16, false);    // R,  features 32..63
       commit(&sm.bar[0]);
     }
     if (!mbar_wait(&sm.bar[0], it & 1)) timed_out = true;
     fence_after_sync();
 
-    // ---- epilogue 1 ----
+    // ---- epilogue 1: both half-warps own the same query row; each covers 32 keys / features ----
     {
       const bool live = row_live(dm, row);
       const int lo = row_first_key(dm, row);
-      // lower: s_dot = phi(q_i).R_i, z_dot = phi(q_i).z_in
+      const int j0 = upper ? 32 : 0, p0 = upper ? 4 : 0;
       float s_dot = 0.f, z_dot = 0.f;
       {
-        float rrow[kD];
-        tmem_ld_row<kD>(lane_base + kColHi, rrow);   // upper lanes read (and ignore) G
-        if (!upper) {
+        float rr[32];
+        tmem_ld_row<32>(lane_base + kColR, rr);
 #pragma unroll
-          for (int pn = 0; pn < kPanels; ++pn) {
-            float fq[8];
-            unpack8_bf16(sm.q[pn * kC + row], fq);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const int kk = pn * 8 + e;
-              s_dot = fmaf(fq[e], rrow[kk], s_dot);
-              z_dot = fmaf(fq[e], bf16_lo(sm.s[kPanels * kD + kk].x), z_dot);
-            }
-          }
-        }
-      }
-      // vals: lower = P row, upper = dA row of the same query
-      float vals[kC];
-      tmem_ld_row<kC>(lane_base + kColLo, vals);
-      float den = live ? z_dot : 0.f, don = live ? s_dot : 0.f;
-#pragma unroll
-      for (int j = 0; j < kC; ++j) {
-        const bool m = (j >= lo && j <= row);
-        vals[j] = m ? vals[j] : 0.f;
-        const float da = __shfl_sync(0xffffffffu, vals[j], lane | 16);   // dA_ij from the upper partner
-        den += vals[j];
-        don = fmaf(vals[j], da, don);
-      }
-      const float dcl = fmaxf(den, p.eps);
-      float inv = 1.f / dcl;
-      float dden = den > p.eps ? -don * inv * inv : 0.f;
-      inv = __shfl_sync(0xffffffffu, inv, lane & 15);     // lower row statistics to both halves
-      dden = __shfl_sync(0xffffffffu, dden, lane & 15);
-      // one stream: lower writes P / D, upper writes dP = M (dA / D + dden)
-      {
-        const float add = upper ? dden : 0.f;
-        uint4* dst = upper ? &sm.dp[row] : &sm.pn[row];
-#pragma unroll
-        for (int jp = 0; jp < kPanels; ++jp) {
-          float a[8];
+        for (int pp = 0; pp < 4; ++pp) {
+          float fq[8];
+          unpack8_bf16(sm.q[(p0 + pp) * kC + row], fq);
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            const int j = jp * 8 + e;
-            a[e] = (j >= lo && j <= row) ? fmaf(vals[j], inv, add) : 0.f;
+            const int kk = (p0 + pp) * 8 + e;
+            s_dot = fmaf(fq[e], rr[pp * 8 + e], s_dot);
+            z_dot = fmaf(fq[e], bf16_lo(sm.s[kPanels * kD + kk].x), z_dot);
           }
-          dst[jp * kC] = pack8_bf16(a);
         }
+      }
+      float pv[32], av[32];
+      tmem_ld_row<32>(lane_base + kColP, pv);
+      tmem_ld_row<32>(lane_base + kColA, av);
+      float den = live ? z_dot : 0.f, don = live ? s_dot : 0.f;
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const int j = j0 + e;
+        const bool m = (j >= lo && j <= row);
+        pv[e] = m ? pv[e] : 0.f;
+        av[e] = m ? av[e] : 0.f;
+        den += pv[e];
+        don = fmaf(pv[e], av[e], don);
+      }
+      den += __shfl_xor_sync(0xffffffffu, den, 16);
+      don += __shfl_xor_sync(0xffffffffu, don, 16);
+      const float dcl = fmaxf(den, p.eps);
+      const float inv = 1.f / dcl;
+      const float dden = den > p.eps ? -don * inv * inv : 0.f;
+#pragma unroll
+      for (int jq = 0; jq < 4; ++jq) {
+        float a[8], d8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int x = jq * 8 + e, j = j0 + x;
+          a[e] = pv[x] * inv;
+          d8[e] = (j >= lo && j <= row) ? fmaf(av[x], inv, dden) : 0.f;
+        }
+        sm.pn[(p0 + jq) * kC + row] = pack8_bf16(a);
+        sm.dp[(p0 + jq) * kC + row] = pack8_bf16(d8);
       }
       // scaled dO rows: two panels per thread pair member (lower: panels 0..3, upper: 4..7 and the extra column)
       {
