@@ -76,6 +76,14 @@ struct BwdSmem {
 //                      dphiK (upper)
 //   columns  64..135   lower: dV                  upper: G^T | gz (persistent)
 //   columns 136..167   R, state features 0..31 in the lower lanes, 32..63 in the upper lanes
+#ifdef MXK_TIMING
+}  // namespace
+__device__ unsigned long long g_bwd_phase_cycles[8];
+namespace {
+#define MXK_TB(i) do { if (tid == 0 && (blockIdx.x % 37) == 0) { const long long now_ = clock64(); atomicAdd(&g_bwd_phase_cycles[i], (unsigned long long)(now_ - t_prev_)); t_prev_ = now_; } } while (0)
+#else
+#define MXK_TB(i) do {} while (0)
+#endif
 constexpr uint32_t kBwdTmemCols = 256;
 constexpr uint32_t kUpper = 16u << 16;
 constexpr uint32_t kColLo = 0, kColHi = 64, kColP = 0, kColA = 32, kColR = 136;
@@ -146,8 +154,15 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
 
   // This thread's 16 vectors (q, k, v, dO of four tile positions) of chunk cc.
   uint4 pre[16];
+  uint4 pre_s[5];   // this thread's share of the 576 vectors of S_in
   auto prefetch = [&](int cc) {
     const int base_t = cc * kC;
+    {
+      const uint4* src = p.chunk_states + (static_cast<size_t>(bh) * nchunks + cc) * (kPanelsX * kD);
+#pragma unroll
+      for (int i = 0; i < 5; ++i)
+        if (i * kThreads + tid < kPanelsX * kD) pre_s[i] = __ldg(src + i * kThreads + tid);
+    }
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
       int trow, seg;
@@ -161,6 +176,9 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
     }
   };
   prefetch(nchunks - 1);
+#ifdef MXK_TIMING
+  long long t_prev_ = clock64();
+#endif
 
   for (int it = 0; it < nchunks; ++it) {
     const int c = nchunks - 1 - it;
@@ -168,6 +186,7 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
     const int valid = min(kC, p.T - t0);
     const uint64_t dm = chunk_done_mask(drow, t0, p.T, lane);
     const bool has_reset = dm != 0ull;
+    MXK_TB(0);
 
     // ---- stage phi(Q), phi(K), V, dO (prefetched during the previous chunk), S_in ----
 #pragma unroll
@@ -190,12 +209,12 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
       sm.d_o[slot] = gv;
     }
     if (tid < kC) sm.vk[kPanels * kC + tid] = make_uint4((tid < valid && row_keep(dm, tid)) ? kOneBf16 : 0u, 0, 0, 0);
-    {
-      const uint4* src = p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * (kPanelsX * kD);
-      for (int i = tid; i < kPanelsX * kD; i += kThreads) sm.s[i] = __ldg(src + i);
-    }
+#pragma unroll
+    for (int i = 0; i < 5; ++i)
+      if (i * kThreads + tid < kPanelsX * kD) sm.s[i * kThreads + tid] = pre_s[i];
     fence_smem_to_async();
     fence_before_sync();
+    MXK_TB(1);
     __syncthreads();
 
     if (tid == 0) {
@@ -216,6 +235,7 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
     }
     if (!mbar_wait(&sm.bar[0], it & 1)) timed_out = true;
     fence_after_sync();
+    MXK_TB(2);
 
     // ---- epilogue 1: both half-warps own the same query row; each covers 32 keys / features ----
     {
@@ -285,6 +305,7 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
     }
     fence_smem_to_async();
     fence_before_sync();
+    MXK_TB(3);
     __syncthreads();
 
     if (tid == 0) {
@@ -305,6 +326,7 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
     if (c > 0) prefetch(c - 1);   // in flight while the MMAs and the output epilogue run
     if (!mbar_wait(&sm.bar[1], it & 1)) timed_out = true;
     fence_after_sync();
+    MXK_TB(4);
 
     // ---- epilogue 2 ----
     {
@@ -353,7 +375,9 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
         }
       }
     }
+    MXK_TB(5);
     __syncthreads();   // staging areas alias buffers that the next chunk refills
+    MXK_TB(6);
   }
 
   if (timed_out && p.status) atomicExch(p.status, 1);
@@ -364,6 +388,16 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
 
 }  // namespace
 }  // namespace mxk
+
+#ifdef MXK_TIMING
+extern "C" int mxk_debug_bwd_phase_cycles(unsigned long long* out, int reset) {
+  if (reset) {
+    unsigned long long z[8] = {};
+    return (int)cudaMemcpyToSymbol(mxk::g_bwd_phase_cycles, z, sizeof(z));
+  }
+  return (int)cudaMemcpyFromSymbol(out, mxk::g_bwd_phase_cycles, 8 * sizeof(unsigned long long));
+}
+#endif
 
 extern "C" {
 
