@@ -79,19 +79,17 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const FwdParams
   // carried state: thread v owns S[v][.]
   {
     const float* s0 = p.s0 ? p.s0 + (static_cast<size_t>(bh) * kD + tid) * kD : nullptr;
+    float vals[kD];   // all loads first: the TMEM stores below are compiler memory barriers
+#pragma unroll
+    for (int c4 = 0; c4 < kD / 4; ++c4) {
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (s0) x = *reinterpret_cast<const float4*>(s0 + c4 * 4);
+      vals[c4 * 4] = x.x; vals[c4 * 4 + 1] = x.y; vals[c4 * 4 + 2] = x.z; vals[c4 * 4 + 3] = x.w;
+    }
 #pragma unroll
     for (int c8 = 0; c8 < kPanD; ++c8) {
-      float vals[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) vals[e] = 0.f;
-      if (s0) {
-        const float4 a = *reinterpret_cast<const float4*>(s0 + c8 * 8);
-        const float4 c = *reinterpret_cast<const float4*>(s0 + c8 * 8 + 4);
-        vals[0] = a.x; vals[1] = a.y; vals[2] = a.z; vals[3] = a.w;
-        vals[4] = c.x; vals[5] = c.y; vals[6] = c.z; vals[7] = c.w;
-      }
-      tmem_st8(lane_base + kColS + c8 * 8, vals);
-      sm.s[c8 * kD + tid] = pack8_bf16(vals);
+      tmem_st8(lane_base + kColS + c8 * 8, vals + c8 * 8);
+      sm.s[c8 * kD + tid] = pack8_bf16(vals + c8 * 8);
     }
     tmem_st_wait();
   }

@@ -114,19 +114,17 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
   // cotangent of the next carry: thread v owns dS[v][.]
   {
     const float* g0 = p.ds_last ? p.ds_last + (static_cast<size_t>(bh) * kD + tid) * kD : nullptr;
+    float vals[kD];   // all loads first: the TMEM stores below are compiler memory barriers
+#pragma unroll
+    for (int c4 = 0; c4 < kD / 4; ++c4) {
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (g0) x = *reinterpret_cast<const float4*>(g0 + c4 * 4);
+      vals[c4 * 4] = x.x; vals[c4 * 4 + 1] = x.y; vals[c4 * 4 + 2] = x.z; vals[c4 * 4 + 3] = x.w;
+    }
 #pragma unroll
     for (int c8 = 0; c8 < kPanD; ++c8) {
-      float vals[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) vals[e] = 0.f;
-      if (g0) {
-        const float4 a = *reinterpret_cast<const float4*>(g0 + c8 * 8);
-        const float4 c = *reinterpret_cast<const float4*>(g0 + c8 * 8 + 4);
-        vals[0] = a.x; vals[1] = a.y; vals[2] = a.z; vals[3] = a.w;
-        vals[4] = c.x; vals[5] = c.y; vals[6] = c.z; vals[7] = c.w;
-      }
-      tmem_st8(lane_base + kColDS + c8 * 8, vals);
-      sm.ds[c8 * kD + tid] = pack8_bf16(vals);
+      tmem_st8(lane_base + kColDS + c8 * 8, vals + c8 * 8);
+      sm.ds[c8 * kD + tid] = pack8_bf16(vals + c8 * 8);
     }
     tmem_st_wait();
   }
@@ -153,7 +151,12 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
     stage_plain_tile(sm.r2, p.d_o + tile, stride_t, valid, tid);
     {
       const uint4* src = p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * kResidualVecs;
-      for (int i = tid; i < kStateVecs; i += kThreads) sm.s[i] = __ldg(src + i);
+      // 32 KB straight into shared memory without a register round trip (all 16 copies in flight)
+#pragma unroll
+      for (int i = 0; i < kStateVecs / kThreads; ++i)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(&sm.s[i * kThreads + tid])),
+                     "l"(src + i * kThreads + tid));
+      asm volatile("cp.async.commit_group;" ::: "memory");
       // U^T saved by the forward pass; thread v owns row v of every panel, so it can also write (gam U)^T
 #pragma unroll
       for (int jp = 0; jp < kPanC; ++jp) {
@@ -166,6 +169,7 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
         sm.ug[jp * kD + tid] = pack8_bf16(f);
       }
     }
+    asm volatile("cp.async.wait_all;" ::: "memory");
     fence_smem_to_async();
     fence_before_sync();
     __syncthreads();

@@ -97,21 +97,20 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const FwdParam
   {
     const float* s0 = p.s0 ? p.s0 + static_cast<size_t>(bh) * kD * kD : nullptr;
     const float* z0 = p.z0 ? p.z0 + static_cast<size_t>(bh) * kD : nullptr;
+    float vals[kDX];   // all loads first: the TMEM stores below are compiler memory barriers
+#pragma unroll
+    for (int vcol = 0; vcol < kDX; ++vcol) {
+      float x = 0.f;
+      if (upper) {
+        if (vcol < kD) x = s0 ? s0[vcol * kD + row] : 0.f;
+        else if (vcol == kD) x = z0 ? z0[row] : 0.f;
+      }
+      vals[vcol] = x;
+    }
 #pragma unroll
     for (int pn = 0; pn < kPanelsX; ++pn) {
-      float vals[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const int vcol = pn * 8 + e;
-        float x = 0.f;
-        if (upper) {
-          if (vcol < kD) x = s0 ? s0[vcol * kD + row] : 0.f;
-          else if (vcol == kD) x = z0 ? z0[row] : 0.f;
-        }
-        vals[e] = x;
-      }
-      tmem_st8(lane_base + pn * 8, vals);
-      if (upper) sm.s[0][pn * kD + row] = pack8_bf16(vals);
+      tmem_st8(lane_base + pn * 8, vals + pn * 8);
+      if (upper) sm.s[0][pn * kD + row] = pack8_bf16(vals + pn * 8);
     }
     tmem_st_wait();
   }
