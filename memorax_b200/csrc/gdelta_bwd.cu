@@ -66,6 +66,14 @@ struct BwdSmem {
 };
 static_assert(sizeof(BwdSmem) <= 227 * 1024, "backward shared memory exceeds one SM");
 
+#ifdef MXK_TIMING
+}  // namespace
+__device__ unsigned long long g_gd_phase_cycles[16];
+namespace {
+#define MXK_TG(i) do { if (tid == 0 && (blockIdx.x % 37) == 0) { const long long now_ = clock64(); atomicAdd(&g_gd_phase_cycles[i], (unsigned long long)(now_ - t_prev_)); t_prev_ = now_; } } while (0)
+#else
+#define MXK_TG(i) do {} while (0)
+#endif
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kUpper = 16u << 16;
 constexpr uint32_t kColDS = 0, kColKK = 128, kColQK = 192, kColY = 256, kColOI = 320, kColX1 = 320, kColW = 320,
@@ -133,6 +141,9 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
   const size_t seq_base = (static_cast<size_t>(b) * p.T * p.H + h) * kD;
   const uint8_t* drow = p.done ? p.done + static_cast<size_t>(b) * p.T : nullptr;
   bool timed_out = false;
+#ifdef MXK_TIMING
+  long long t_prev_ = clock64();
+#endif
 
   for (int it = 0; it < nchunks; ++it) {
     const int c = nchunks - 1 - it;
@@ -144,6 +155,7 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
     if (tid < kC) sm.dg[tid] = sm.dgam[tid] = 0.f;
     if (tid < 4) sm.dgl[tid] = 0.f;
 
+    MXK_TG(0);
     const size_t tile = seq_base + static_cast<size_t>(t0) * stride_t;
     stage_panel_tile(sm.k, p.k + tile, stride_t, valid, tid);
     stage_panel_tile(sm.q, p.q + tile, stride_t, valid, tid);
@@ -174,6 +186,7 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
     fence_before_sync();
     __syncthreads();
 
+    MXK_TG(1);
     // ---- MMAs A: K K^T, Q K^T, Y^T = S_in K^T, OI^T = S_in Q^T, X2^T = dS K^T ----
     if (tid == 0) {
       fence_after_sync();
@@ -196,6 +209,7 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
     }
     if (!mbar_wait(&sm.bar[0], 0)) timed_out = true;
     fence_after_sync();
+    MXK_TG(2);
 
     // ---- epilogue A1: -beta L (fp32, row-major) and tril(G o QK^T) (bf16); every thread owns
     //      32 keys of its token row ----
@@ -237,6 +251,7 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
     fence_before_sync();
     __syncthreads();
 
+    MXK_TG(3);
     // ---- MMAs B: X1^T = dO^T P (128 x 64), DP = dO U^T (64 x 64) ----
     if (tid == 0) {
       fence_after_sync();
@@ -250,6 +265,7 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
     }
     if (!mbar_wait(&sm.bar[1], 0)) timed_out = true;
     fence_after_sync();
+    MXK_TG(4);
 
     // ---- epilogue B: thread v: dU column, back substitution, dV, decay partials ----
     {
@@ -329,6 +345,7 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
       }
     }
 
+    MXK_TG(5);
     // ---- MMA C: W = dUt U^T (64 x 64) ----
     if (tid == 0) {
       fence_after_sync();
@@ -340,6 +357,7 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
     }
     if (!mbar_wait(&sm.bar[0], 1)) timed_out = true;
     fence_after_sync();
+    MXK_TG(6);
     __syncthreads();  // every thread has flushed its part of the dV tile before `lt` is reused
 
     // ---- epilogue C: (dP o G), (dL o G), E, dbeta; g-scaled dO.  Every thread owns 32 keys of
@@ -400,6 +418,7 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
     fence_before_sync();
     __syncthreads();
 
+    MXK_TG(7);
     // ---- MMAs D: dQ, dK (64 x 128), dS_in increment (128 x 128) ----
     if (tid == 0) {
       fence_after_sync();
@@ -453,8 +472,10 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
       if (i1 < valid) p.dalpha[base + static_cast<size_t>(i1) * p.H] = ((dm >> i1) & 1ull) ? 0.f : dla1 / sm.cd.alpha[i1];
     }
 
+    MXK_TG(8);
     if (!mbar_wait(&sm.bar[1], 1)) timed_out = true;
     fence_after_sync();
+    MXK_TG(9);
 
     // ---- epilogue D: dq, dk rows; dS = g_last dS + increment ----
     {
@@ -495,6 +516,7 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
       }
       tmem_st_wait();
     }
+    MXK_TG(10);
   }
 
   if (timed_out && p.status) atomicExch(p.status, 1);
@@ -505,6 +527,16 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
 
 }  // namespace
 }  // namespace mxk
+
+#ifdef MXK_TIMING
+extern "C" int mxk_debug_gd_phase_cycles(unsigned long long* out, int reset) {
+  if (reset) {
+    unsigned long long z[16] = {};
+    return (int)cudaMemcpyToSymbol(mxk::g_gd_phase_cycles, z, sizeof(z));
+  }
+  return (int)cudaMemcpyFromSymbol(out, mxk::g_gd_phase_cycles, 16 * sizeof(unsigned long long));
+}
+#endif
 
 extern "C" {
 
