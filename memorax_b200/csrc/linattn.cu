@@ -126,11 +126,13 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const FwdParam
 #ifdef MXK_TIMING
   long long t_prev_ = clock64();
 #endif
+  uint32_t done_flags = load_done_flags(drow, 0, p.T, lane);
 
   for (int c = 0; c < nchunks; ++c) {
     const int t0 = c * kC;
     const int valid = min(kC, p.T - t0);
-    const uint64_t dm = chunk_done_mask(drow, t0, p.T, lane);
+    const uint64_t dm = done_mask_from_flags(done_flags);
+    done_flags = load_done_flags(drow, t0 + kC, p.T, lane);   // the next chunk's flags, needed a chunk from now
     const bool has_reset = dm != 0ull;
     MXK_T(0);
 

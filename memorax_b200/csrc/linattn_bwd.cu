@@ -175,6 +175,7 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
     }
   };
   prefetch(nchunks - 1);
+  uint32_t done_flags = load_done_flags(drow, (nchunks - 1) * kC, p.T, lane);
 #ifdef MXK_TIMING
   long long t_prev_ = clock64();
 #endif
@@ -183,7 +184,8 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
     const int c = nchunks - 1 - it;
     const int t0 = c * kC;
     const int valid = min(kC, p.T - t0);
-    const uint64_t dm = chunk_done_mask(drow, t0, p.T, lane);
+    const uint64_t dm = done_mask_from_flags(done_flags);
+    done_flags = load_done_flags(drow, t0 - kC, p.T, lane);   // the next (earlier) chunk's flags
     const bool has_reset = dm != 0ull;
     MXK_TB(0);
 

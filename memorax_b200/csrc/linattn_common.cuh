@@ -41,6 +41,21 @@ __device__ __forceinline__ uint64_t chunk_done_mask(const uint8_t* drow, int t0,
   const unsigned hi = __ballot_sync(0xffffffffu, tb < T && drow[tb] != 0);
   return (static_cast<uint64_t>(hi) << 32) | lo;
 }
+// The same in two steps, so that the byte loads of a later chunk can be issued
+// long before their values are needed: bit 0 / bit 1 = flags of tokens t0+lane / t0+32+lane.
+__device__ __forceinline__ uint32_t load_done_flags(const uint8_t* drow, int t0, int T, int lane) {
+  if (!drow || t0 < 0) return 0u;
+  const int ta = t0 + lane, tb = t0 + 32 + lane;
+  uint32_t f = 0u;
+  if (ta < T) f |= drow[ta] != 0 ? 1u : 0u;
+  if (tb < T) f |= drow[tb] != 0 ? 2u : 0u;
+  return f;
+}
+__device__ __forceinline__ uint64_t done_mask_from_flags(uint32_t f) {
+  const unsigned lo = __ballot_sync(0xffffffffu, (f & 1u) != 0u);
+  const unsigned hi = __ballot_sync(0xffffffffu, (f & 2u) != 0u);
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
 __device__ __forceinline__ bool row_live(uint64_t dm, int i) { return (dm & ((2ull << i) - 1ull)) == 0ull; }
 __device__ __forceinline__ bool row_keep(uint64_t dm, int j) { return j >= 63 || (dm >> (j + 1)) == 0ull; }
 __device__ __forceinline__ int row_first_key(uint64_t dm, int i) {
