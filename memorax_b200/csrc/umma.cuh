@@ -70,9 +70,19 @@ __device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint6
 }
 
 // D[M x N] (+)= A B^T-style product over `ksteps` K=16 slices, issued by ONE thread.
+// Only the start-address field (low 14 bits, 16-byte units) changes from slice to
+// slice, so the descriptors are built once and advanced with one add each.
 __device__ __forceinline__ void gemm(uint32_t tmem_d, const Operand& a, const Operand& b, uint32_t idesc,
                                      int ksteps, bool accumulate) {
-  for (int k = 0; k < ksteps; ++k) mma_bf16(tmem_d, a.desc(k), b.desc(k), idesc, (accumulate || k > 0) ? 1u : 0u);
+  uint64_t da = a.desc(0), db = b.desc(0);
+  const uint64_t adv_a = (a.contract_rows ? 256u : 2u * a.rows * 16u) >> 4;
+  const uint64_t adv_b = (b.contract_rows ? 256u : 2u * b.rows * 16u) >> 4;
+#pragma unroll 1
+  for (int k = 0; k < ksteps; ++k) {
+    mma_bf16(tmem_d, da, db, idesc, (accumulate || k > 0) ? 1u : 0u);
+    da += adv_a;
+    db += adv_b;
+  }
 }
 
 __device__ __forceinline__ void commit(uint64_t* bar) {
