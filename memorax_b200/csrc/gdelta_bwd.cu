@@ -18,6 +18,7 @@
 // Matrices with d_v on their rows are kept transposed ([v][t]) so that thread v
 // owns one value column, as in the forward kernel.
 #include "gdelta_common.cuh"
+#include "tma.cuh"
 
 namespace mxk {
 namespace {
@@ -43,6 +44,8 @@ struct BwdParams {
   float* ds0;
   int* status;
   int B, T, H;
+  CUtensorMap map_k, map_q, map_do;   // 64-token tiles in panel order
+  CUtensorMap map_do_plain;           // the same dO tile row-major
 };
 
 struct BwdSmem {
@@ -62,6 +65,7 @@ struct BwdSmem {
   float dg[kC], dgam[kC], rowsum[kC], colsum[kC], dcum[kC];
   float dgl[4];
   uint64_t bar[2];
+  uint64_t bar_load;
   uint32_t tmem;
 };
 static_assert(sizeof(BwdSmem) <= 227 * 1024, "backward shared memory exceeds one SM");
@@ -97,7 +101,26 @@ __device__ __forceinline__ void warp_reduce64(float* vals, int lane) {
   }
 }
 
-__global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p) {
+// All global -> shared traffic of chunk `c` (K, Q, dO twice, S_in, U^T): four TMA tile
+// loads and two bulk copies issued by ONE thread, completing on sm.bar_load.  The
+// kernel issues them one chunk ahead, right after the last MMAs of the previous chunk
+// have released the buffers, so that they overlap that chunk's last epilogue.
+constexpr uint32_t kChunkLoadBytes = (4 * kPanD * kC + kResidualVecs) * 16;
+__device__ __forceinline__ void issue_chunk_loads(BwdSmem& sm, const BwdParams& p, int b, int h, int c, int nchunks) {
+  // earlier generic-proxy accesses to these buffers are ordered before the async-proxy writes
+  fence_smem_to_async();
+  tma::expect_bytes(&sm.bar_load, kChunkLoadBytes);
+  const int t0 = c * kC;
+  tma::load_panel_tile(sm.k, &p.map_k, &sm.bar_load, t0, h, b);
+  tma::load_panel_tile(sm.q, &p.map_q, &sm.bar_load, t0, h, b);
+  tma::load_panel_tile(sm.d_o, &p.map_do, &sm.bar_load, t0, h, b);
+  tma::load_plain_tile(sm.r2, &p.map_do_plain, &sm.bar_load, t0, h, b);
+  const uint4* src = p.chunk_states + (static_cast<size_t>(b * p.H + h) * nchunks + c) * kResidualVecs;
+  tma::load_bulk(sm.s, src, kStateVecs * 16, &sm.bar_load);
+  tma::load_bulk(sm.u, src + kStateVecs, kUVecs * 16, &sm.bar_load);
+}
+
+__global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const __grid_constant__ BwdParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   BwdSmem& sm = *reinterpret_cast<BwdSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -110,6 +133,7 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
   if (tid == 0) {
     mbar_init(&sm.bar[0], 1);
     mbar_init(&sm.bar[1], 1);
+    mbar_init(&sm.bar_load, 1);
     mbar_init_fence();
   }
   if (warp == 0) tmem_alloc(&sm.tmem, kTmemCols);
@@ -119,6 +143,15 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
   const uint32_t tmem = sm.tmem;
   const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
 
+  const size_t stride_t = static_cast<size_t>(p.H) * kD;
+  const size_t seq_base = (static_cast<size_t>(b) * p.T * p.H + h) * kD;
+  const size_t bt_base = static_cast<size_t>(b) * p.T;
+  const uint8_t* drow = p.done ? p.done + static_cast<size_t>(b) * p.T : nullptr;
+  bool timed_out = false;
+
+  if (tid == 0) issue_chunk_loads(sm, p, b, h, nchunks - 1, nchunks);
+  float2 ab_next = fetch_chunk_decay(p.alpha, p.beta, bt_base, p.H, h, (nchunks - 1) * kC, p.T, tid);
+  uint32_t flags_next = linattn::load_done_flags(drow, (nchunks - 1) * kC, p.T, lane);
   // cotangent of the next carry: thread v owns dS[v][.]
   {
     const float* g0 = p.ds_last ? p.ds_last + (static_cast<size_t>(bh) * kD + tid) * kD : nullptr;
@@ -137,10 +170,6 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
     tmem_st_wait();
   }
 
-  const size_t stride_t = static_cast<size_t>(p.H) * kD;
-  const size_t seq_base = (static_cast<size_t>(b) * p.T * p.H + h) * kD;
-  const uint8_t* drow = p.done ? p.done + static_cast<size_t>(b) * p.T : nullptr;
-  bool timed_out = false;
 #ifdef MXK_TIMING
   long long t_prev_ = clock64();
 #endif
@@ -149,39 +178,24 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
     const int c = nchunks - 1 - it;
     const int t0 = c * kC;
     const int valid = min(kC, p.T - t0);
-    const uint64_t dm = chunk_done_mask(drow, t0, p.T, lane);
+    const uint64_t dm = linattn::done_mask_from_flags(flags_next);
     __syncthreads();
-    load_chunk_decay(sm.cd, p.alpha, p.beta, static_cast<size_t>(b) * p.T, p.H, h, t0, p.T, dm, tid);
+    chunk_decay_from_regs(sm.cd, ab_next, dm, tid);
     if (tid < kC) sm.dg[tid] = sm.dgam[tid] = 0.f;
     if (tid < 4) sm.dgl[tid] = 0.f;
 
     MXK_TG(0);
     const size_t tile = seq_base + static_cast<size_t>(t0) * stride_t;
-    stage_panel_tile(sm.k, p.k + tile, stride_t, valid, tid);
-    stage_panel_tile(sm.q, p.q + tile, stride_t, valid, tid);
-    stage_panel_tile(sm.d_o, p.d_o + tile, stride_t, valid, tid);
-    stage_plain_tile(sm.r2, p.d_o + tile, stride_t, valid, tid);
-    {
-      const uint4* src = p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * kResidualVecs;
-      // 32 KB straight into shared memory without a register round trip (all 16 copies in flight)
+    if (!mbar_wait(&sm.bar_load, it & 1)) timed_out = true;
+    // (gam U)^T from row v of U^T
 #pragma unroll
-      for (int i = 0; i < kStateVecs / kThreads; ++i)
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(&sm.s[i * kThreads + tid])),
-                     "l"(src + i * kThreads + tid));
-      asm volatile("cp.async.commit_group;" ::: "memory");
-      // U^T saved by the forward pass; thread v owns row v of every panel, so it can also write (gam U)^T
+    for (int jp = 0; jp < kPanC; ++jp) {
+      float f[8];
+      unpack8_bf16(sm.u[jp * kD + tid], f);
 #pragma unroll
-      for (int jp = 0; jp < kPanC; ++jp) {
-        const uint4 u8 = __ldg(src + kStateVecs + jp * kD + tid);
-        float f[8];
-        unpack8_bf16(u8, f);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] *= sm.cd.gam[jp * 8 + e];
-        sm.u[jp * kD + tid] = u8;
-        sm.ug[jp * kD + tid] = pack8_bf16(f);
-      }
+      for (int e = 0; e < 8; ++e) f[e] *= sm.cd.gam[jp * 8 + e];
+      sm.ug[jp * kD + tid] = pack8_bf16(f);
     }
-    asm volatile("cp.async.wait_all;" ::: "memory");
     fence_smem_to_async();
     fence_before_sync();
     __syncthreads();
@@ -476,6 +490,12 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const BwdParams p)
     if (!mbar_wait(&sm.bar[1], 1)) timed_out = true;
     fence_after_sync();
     MXK_TG(9);
+    // the MMAs above were the last readers of the staged tiles: fetch the next chunk
+    if (c > 0) {
+      if (tid == 0) issue_chunk_loads(sm, p, b, h, c - 1, nchunks);
+      ab_next = fetch_chunk_decay(p.alpha, p.beta, bt_base, p.H, h, t0 - kC, p.T, tid);
+      flags_next = linattn::load_done_flags(drow, t0 - kC, p.T, lane);
+    }
 
     // ---- epilogue D: dq, dk rows; dS = g_last dS + increment ----
     {
@@ -571,6 +591,10 @@ int mxk_gdelta_bf16_bwd(const void* q, const void* k, const void* v, const float
   prm.ds0 = ds0;
   prm.status = status;
   prm.B = B; prm.T = T; prm.H = H;
+  if (!tma::make_panel_map(&prm.map_k, k, B, T, H, kD, kC) || !tma::make_panel_map(&prm.map_q, q, B, T, H, kD, kC) ||
+      !tma::make_panel_map(&prm.map_do, d_o, B, T, H, kD, kC) ||
+      !tma::make_plain_map(&prm.map_do_plain, d_o, B, T, H, kD, kC))
+    return MXK_ERR_UNSUPPORTED;
   cudaError_t e = cudaFuncSetAttribute(gdelta_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(BwdSmem)));
   if (e != cudaSuccess) return static_cast<int>(e);

@@ -40,18 +40,9 @@ struct ChunkDecay {
   float alpha[kC], beta[kC], cum[kC], g[kC], gam[kC];
 };
 
-// Loads alpha/beta of one chunk, builds cum / g / gam.  Call with all threads;
-// ends with a __syncthreads().  Rows past the end of the sequence get alpha = 1,
-// beta = 0, i.e. they leave the state untouched.
-__device__ __forceinline__ void load_chunk_decay(ChunkDecay& cd, const float* alpha, const float* beta, size_t bt_base,
-                                                 int H, int h, int t0, int T, uint64_t dm, int tid) {
-  if (tid < kC) {
-    const bool in = t0 + tid < T;
-    const size_t idx = (bt_base + t0 + tid) * H + h;
-    cd.alpha[tid] = in ? alpha[idx] : 1.f;
-    cd.beta[tid] = in ? beta[idx] : 0.f;
-  }
-  __syncthreads();
+// Builds cum / g / gam from cd.alpha / cd.beta of one chunk (already in shared
+// memory and visible to all threads).  Call with all threads; ends with a __syncthreads().
+__device__ __forceinline__ void finish_chunk_decay(ChunkDecay& cd, uint64_t dm, int tid) {
   if (tid < 32) {
     const float l0 = __logf(cd.alpha[2 * tid]), l1 = __logf(cd.alpha[2 * tid + 1]);
     float s = l0 + l1;
@@ -70,6 +61,43 @@ __device__ __forceinline__ void load_chunk_decay(ChunkDecay& cd, const float* al
   }
   __syncthreads();
 }
+
+// alpha / beta of token t0 + tid (threads 0..63) for a later chunk_decay_from_regs.
+// Rows past the end of the sequence get alpha = 1, beta = 0, i.e. they leave the
+// state untouched.
+__device__ __forceinline__ float2 fetch_chunk_decay(const float* alpha, const float* beta, size_t bt_base, int H, int h,
+                                                    int t0, int T, int tid) {
+  float2 ab = make_float2(1.f, 0.f);
+  if (tid < kC && t0 >= 0 && t0 + tid < T) {
+    const size_t idx = (bt_base + t0 + tid) * H + h;
+    ab = make_float2(__ldg(alpha + idx), __ldg(beta + idx));
+  }
+  return ab;
+}
+__device__ __forceinline__ void chunk_decay_from_regs(ChunkDecay& cd, float2 ab, uint64_t dm, int tid) {
+  if (tid < kC) {
+    cd.alpha[tid] = ab.x;
+    cd.beta[tid] = ab.y;
+  }
+  __syncthreads();
+  finish_chunk_decay(cd, dm, tid);
+}
+
+// Loads alpha/beta of one chunk, builds cum / g / gam.  Call with all threads;
+// ends with a __syncthreads().
+__device__ __forceinline__ void load_chunk_decay(ChunkDecay& cd, const float* alpha, const float* beta, size_t bt_base,
+                                                 int H, int h, int t0, int T, uint64_t dm, int tid) {
+  chunk_decay_from_regs(cd, fetch_chunk_decay(alpha, beta, bt_base, H, h, t0, T, tid), dm, tid);
+}
+
+// 16-byte asynchronous global -> shared copy (zero fill when !valid; the source
+// address must still be a mapped one).
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid = true) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(umma::smem_u32(dst)), "l"(src),
+               "r"(valid ? 16u : 0u)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 // 64 x 128 bf16 tile (rows = tokens) -> panels [c/8][t][8].  Eight consecutive
 // lanes take eight different rows, so the 16-byte shared stores are conflict-free.
@@ -96,6 +124,29 @@ __device__ __forceinline__ void stage_plain_tile(uint4* dst, const __nv_bfloat16
     uint4 x = make_uint4(0, 0, 0, 0);
     if (row < valid) x = __ldg(reinterpret_cast<const uint4*>(src + row * stride_t + seg * 8));
     dst[row * 16 + seg] = x;
+  }
+}
+
+// Asynchronous forms of the two staging routines (cp.async; complete after cp_async_wait_all()).
+__device__ __forceinline__ void stage_panel_tile_async(uint4* dst, const __nv_bfloat16* src, size_t stride_t, int valid,
+                                                       int tid) {
+#pragma unroll
+  for (int r = 0; r < 8; ++r) {
+    const int vid = r * kThreads + tid;
+    const int row = (vid & 7) + 8 * (vid >> 7);
+    const int seg = (vid >> 3) & 15;
+    const bool in = row < valid;
+    cp_async16(&dst[seg * kC + row], src + (in ? row : 0) * stride_t + seg * 8, in);
+  }
+}
+__device__ __forceinline__ void stage_plain_tile_async(uint4* dst, const __nv_bfloat16* src, size_t stride_t, int valid,
+                                                       int tid) {
+#pragma unroll
+  for (int r = 0; r < 8; ++r) {
+    const int vid = r * kThreads + tid;
+    const int row = vid >> 4, seg = vid & 15;
+    const bool in = row < valid;
+    cp_async16(&dst[row * 16 + seg], src + (in ? row : 0) * stride_t + seg * 8, in);
   }
 }
 
