@@ -11,6 +11,7 @@
 //   epilogue 2: o = g OI + OA (staged through shared memory for 16-byte stores);
 //               S = g_last S + dS back into TMEM, bf16 operand copy for the next chunk.
 #include "gdelta_common.cuh"
+#include "tma.cuh"
 
 namespace mxk {
 namespace {
@@ -31,6 +32,8 @@ struct FwdParams {
   uint4* chunk_states;
   int* status;
   int B, T, H;
+  CUtensorMap map_k, map_q;   // 64-token tiles in panel order
+  CUtensorMap map_v, map_o;   // 64-token tiles row-major
 };
 
 struct FwdSmem {
@@ -42,6 +45,7 @@ struct FwdSmem {
   float lt[kC * kC];          // lt[j][t] = -beta_t L_tj, then the bf16 output tile [t][v]
   ChunkDecay cd;
   uint64_t bar[2];
+  uint64_t bar_load;
   uint32_t tmem;
 };
 static_assert(sizeof(FwdSmem) <= 112 * 1024, "two CTAs per SM");
@@ -55,7 +59,7 @@ constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kUpper = 16u << 16;
 constexpr uint32_t kColS = 0, kColKQ = 128, kColO = 128, kColY = 192;
 
-__global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const FwdParams p) {
+__global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_constant__ FwdParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   FwdSmem& sm = *reinterpret_cast<FwdSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -67,6 +71,7 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const FwdParams
   if (tid == 0) {
     mbar_init(&sm.bar[0], 1);
     mbar_init(&sm.bar[1], 1);
+    mbar_init(&sm.bar_load, 1);
     mbar_init_fence();
   }
   if (warp == 0) tmem_alloc(&sm.tmem, kTmemCols);
@@ -94,29 +99,43 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const FwdParams
     tmem_st_wait();
   }
 
-  const size_t stride_t = static_cast<size_t>(p.H) * kD;
-  const size_t seq_base = (static_cast<size_t>(b) * p.T * p.H + h) * kD;
   const uint8_t* drow = p.done ? p.done + static_cast<size_t>(b) * p.T : nullptr;
+  const size_t bt_base = static_cast<size_t>(b) * p.T;
   const uint32_t id_64 = idesc_bf16(kC, kC, false, false);
   const uint32_t id_128x64 = idesc_bf16(kD, kC, false, false);
   const uint32_t id_ds = idesc_bf16(kD, kD, false, true);
   bool timed_out = false;
 
+  // K, Q (panel order) and V (row-major) of a chunk arrive by TMA, issued by one thread
+  // one chunk ahead: as soon as the second MMA group of the previous chunk has released
+  // the buffers, so that the copies overlap that chunk's output epilogue.
+  auto issue_chunk_loads = [&](int cc) {
+    fence_smem_to_async();   // earlier generic-proxy accesses to the buffers come first
+    tma::expect_bytes(&sm.bar_load, 3 * kPanD * kC * 16);
+    tma::load_panel_tile(sm.k, &p.map_k, &sm.bar_load, cc * kC, h, b);
+    tma::load_panel_tile(sm.q, &p.map_q, &sm.bar_load, cc * kC, h, b);
+    tma::load_plain_tile(sm.vu, &p.map_v, &sm.bar_load, cc * kC, h, b);
+  };
+  if (tid == 0) issue_chunk_loads(0);
+  float2 ab_next = fetch_chunk_decay(p.alpha, p.beta, bt_base, p.H, h, 0, p.T, tid);
+  uint32_t flags_next = linattn::load_done_flags(drow, 0, p.T, lane);
+
   for (int c = 0; c < nchunks; ++c) {
     const int t0 = c * kC;
-    const int valid = min(kC, p.T - t0);
-    const uint64_t dm = chunk_done_mask(drow, t0, p.T, lane);
+    const uint64_t dm = linattn::done_mask_from_flags(flags_next);
+    fence_smem_to_async();   // the bf16 state copy written below / above is read by bulk copies and MMAs
     __syncthreads();
-    load_chunk_decay(sm.cd, p.alpha, p.beta, static_cast<size_t>(b) * p.T, p.H, h, t0, p.T, dm, tid);
-
-    stage_panel_tile(sm.k, p.k + seq_base + static_cast<size_t>(t0) * stride_t, stride_t, valid, tid);
-    stage_panel_tile(sm.q, p.q + seq_base + static_cast<size_t>(t0) * stride_t, stride_t, valid, tid);
-    stage_plain_tile(sm.vu, p.v + seq_base + static_cast<size_t>(t0) * stride_t, stride_t, valid, tid);
-    if (p.chunk_states) {
-      uint4* dst = p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * kResidualVecs;
-      for (int i = tid; i < kStateVecs; i += kThreads) dst[i] = sm.s[i];
+    chunk_decay_from_regs(sm.cd, ab_next, dm, tid);
+    if (tid == 0) {
+      if (p.chunk_states) {
+        // residual for the backward pass: the state entering the chunk
+        tma::store_bulk(p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * kResidualVecs, sm.s, kStateVecs * 16);
+        tma::commit_group();
+      }
+      // the previous chunk's output tile (older group) has left `lt` before epilogue 1a rewrites it
+      if (p.chunk_states) tma::wait_group_read<1>(); else tma::wait_group_read<0>();
     }
-    fence_smem_to_async();
+    if (!mbar_wait(&sm.bar_load, c & 1)) timed_out = true;
     fence_before_sync();
     __syncthreads();
 
@@ -198,6 +217,7 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const FwdParams
       }
       tmem_st_wait();
     }
+    if (tid == 0) tma::wait_group_read<0>();   // the residual copy has finished reading `s` (rewritten in epilogue 2)
     fence_smem_to_async();
     fence_before_sync();
     __syncthreads();
@@ -213,6 +233,11 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const FwdParams
     }
     if (!mbar_wait(&sm.bar[1], c & 1)) timed_out = true;
     fence_after_sync();
+    if (c + 1 < nchunks) {
+      if (tid == 0) issue_chunk_loads(c + 1);
+      ab_next = fetch_chunk_decay(p.alpha, p.beta, bt_base, p.H, h, t0 + kC, p.T, tid);
+      flags_next = linattn::load_done_flags(drow, t0 + kC, p.T, lane);
+    }
 
     // ---- epilogue 2: output tile (staged for 16-byte stores), bf16 copy of the new state ----
     {
@@ -240,18 +265,14 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const FwdParams
         }
       }
     }
+    fence_smem_to_async();
     __syncthreads();
-    {
-      __nv_bfloat16* obase = p.o + seq_base + static_cast<size_t>(t0) * stride_t;
-      const uint4* src = reinterpret_cast<const uint4*>(sm.lt);
-#pragma unroll
-      for (int rr = 0; rr < 8; ++rr) {
-        const int vid = rr * kThreads + tid;
-        const int trow = vid >> 4, seg = vid & 15;
-        if (trow < valid) *reinterpret_cast<uint4*>(obase + trow * stride_t + seg * 8) = src[trow * 16 + seg];
-      }
+    if (tid == 0) {
+      tma::store_plain_tile(&p.map_o, sm.lt, t0, h, b);   // rows past the end of the sequence are clipped
+      tma::commit_group();
     }
   }
+  if (tid == 0) tma::wait_group_all();
 
   if (timed_out && p.status) atomicExch(p.status, 1);
   fence_before_sync();
@@ -293,6 +314,9 @@ int mxk_gdelta_bf16_fwd(const void* q, const void* k, const void* v, const float
   prm.chunk_states = static_cast<uint4*>(chunk_states);
   prm.status = status;
   prm.B = B; prm.T = T; prm.H = H;
+  if (!tma::make_panel_map(&prm.map_k, k, B, T, H, kD, kC) || !tma::make_panel_map(&prm.map_q, q, B, T, H, kD, kC) ||
+      !tma::make_plain_map(&prm.map_v, v, B, T, H, kD, kC) || !tma::make_plain_map(&prm.map_o, o, B, T, H, kD, kC))
+    return MXK_ERR_UNSUPPORTED;
   cudaError_t e = cudaFuncSetAttribute(gdelta_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(FwdSmem)));
   if (e != cudaSuccess) return static_cast<int>(e);

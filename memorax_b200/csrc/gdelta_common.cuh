@@ -21,7 +21,6 @@
 namespace mxk {
 namespace gdelta {
 
-using linattn::chunk_done_mask;
 using linattn::row_first_key;
 using linattn::row_keep;
 using linattn::row_live;
@@ -83,73 +82,7 @@ __device__ __forceinline__ void chunk_decay_from_regs(ChunkDecay& cd, float2 ab,
   finish_chunk_decay(cd, dm, tid);
 }
 
-// Loads alpha/beta of one chunk, builds cum / g / gam.  Call with all threads;
-// ends with a __syncthreads().
-__device__ __forceinline__ void load_chunk_decay(ChunkDecay& cd, const float* alpha, const float* beta, size_t bt_base,
-                                                 int H, int h, int t0, int T, uint64_t dm, int tid) {
-  chunk_decay_from_regs(cd, fetch_chunk_decay(alpha, beta, bt_base, H, h, t0, T, tid), dm, tid);
-}
-
-// 16-byte asynchronous global -> shared copy (zero fill when !valid; the source
-// address must still be a mapped one).
-__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid = true) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(umma::smem_u32(dst)), "l"(src),
-               "r"(valid ? 16u : 0u)
-               : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-
-// 64 x 128 bf16 tile (rows = tokens) -> panels [c/8][t][8].  Eight consecutive
-// lanes take eight different rows, so the 16-byte shared stores are conflict-free.
-__device__ __forceinline__ void stage_panel_tile(uint4* dst, const __nv_bfloat16* src, size_t stride_t, int valid,
-                                                 int tid) {
-#pragma unroll
-  for (int r = 0; r < 8; ++r) {
-    const int vid = r * kThreads + tid;
-    const int row = (vid & 7) + 8 * (vid >> 7);
-    const int seg = (vid >> 3) & 15;
-    uint4 x = make_uint4(0, 0, 0, 0);
-    if (row < valid) x = __ldg(reinterpret_cast<const uint4*>(src + row * stride_t + seg * 8));
-    dst[seg * kC + row] = x;
-  }
-}
-
-// Same tile -> plain row-major [t][c] (for element-wise transposed reads).
-__device__ __forceinline__ void stage_plain_tile(uint4* dst, const __nv_bfloat16* src, size_t stride_t, int valid,
-                                                 int tid) {
-#pragma unroll
-  for (int r = 0; r < 8; ++r) {
-    const int vid = r * kThreads + tid;
-    const int row = vid >> 4, seg = vid & 15;
-    uint4 x = make_uint4(0, 0, 0, 0);
-    if (row < valid) x = __ldg(reinterpret_cast<const uint4*>(src + row * stride_t + seg * 8));
-    dst[row * 16 + seg] = x;
-  }
-}
-
-// Asynchronous forms of the two staging routines (cp.async; complete after cp_async_wait_all()).
-__device__ __forceinline__ void stage_panel_tile_async(uint4* dst, const __nv_bfloat16* src, size_t stride_t, int valid,
-                                                       int tid) {
-#pragma unroll
-  for (int r = 0; r < 8; ++r) {
-    const int vid = r * kThreads + tid;
-    const int row = (vid & 7) + 8 * (vid >> 7);
-    const int seg = (vid >> 3) & 15;
-    const bool in = row < valid;
-    cp_async16(&dst[seg * kC + row], src + (in ? row : 0) * stride_t + seg * 8, in);
-  }
-}
-__device__ __forceinline__ void stage_plain_tile_async(uint4* dst, const __nv_bfloat16* src, size_t stride_t, int valid,
-                                                       int tid) {
-#pragma unroll
-  for (int r = 0; r < 8; ++r) {
-    const int vid = r * kThreads + tid;
-    const int row = vid >> 4, seg = vid & 15;
-    const bool in = row < valid;
-    cp_async16(&dst[row * 16 + seg], src + (in ? row : 0) * stride_t + seg * 8, in);
-  }
-}
-
+// Element [t][c] of a 64 x 128 bf16 tile stored row-major.
 __device__ __forceinline__ float bf16_at(const uint4* plain, int t, int c) {
   const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(plain);
   return __bfloat162float(p[t * kD + c]);

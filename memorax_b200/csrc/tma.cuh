@@ -96,6 +96,27 @@ __device__ __forceinline__ void load_bulk(void* dst, const void* src, uint32_t b
                "l"(src), "r"(bytes), "r"(umma::smem_u32(bar))
                : "memory");
 }
+// ---- shared -> global (bulk groups of the issuing thread) ----
+// Tile store through a plain map; rows past the end of the sequence are clipped.
+__device__ __forceinline__ void store_plain_tile(const CUtensorMap* map, const void* src, int t0, int h, int b) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(umma::smem_u32(src)), "r"(0), "r"(h), "r"(t0), "r"(b)
+               : "memory");
+}
+__device__ __forceinline__ void store_bulk(void* dst, const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(umma::smem_u32(src)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Returns once all but the newest N groups of this thread have finished READING shared memory.
+template <int N>
+__device__ __forceinline__ void wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Returns once every group of this thread has completed.
+__device__ __forceinline__ void wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 #endif
 
 }  // namespace tma
