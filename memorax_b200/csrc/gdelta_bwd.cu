@@ -48,6 +48,10 @@ struct BwdParams {
   CUtensorMap map_do_plain;           // the same dO tile row-major
 };
 
+// Row stride of the fp32 64 x 64 matrices that threads write row by row: 68 floats keep
+// rows 16-byte aligned and spread the 16-byte stores of eight rows over all banks.
+constexpr int kLS = kC + 4;
+
 struct BwdSmem {
   uint4 s[kStateVecs];      // S_in bf16          [k/8][v][8]
   uint4 ds[kStateVecs];     // dS bf16            [k/8][v][8]
@@ -59,7 +63,7 @@ struct BwdSmem {
   uint4 u[kPanC * kD];      // U^T                [j/8][v][8]
   uint4 ug[kPanC * kD];     // (gam U)^T
   uint4 p[kPanC * kC];      // tril(G o QK^T)     [j/8][t][8]
-  float l[kC * kC];         // l[t][j] = -beta_t L_tj        -> E[t][j]
+  float l[kC * kLS];        // l[t][j] = -beta_t L_tj        -> E[t][j]   (row stride kLS)
   float lt[kC * kC];        // lt[j][t] = -beta_t L_tj       -> dV tile -> (dP o G), (dL o G) panels
   ChunkDecay cd;
   float dg[kC], dgam[kC], rowsum[kC], colsum[kC], dcum[kC];
@@ -236,15 +240,18 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const __grid_const
       tmem_ld_row<32>(lane_base + kColQK, qk);
 #pragma unroll
       for (int jq = 0; jq < 4; ++jq) {
-        float pm[8];
+        float pm[8], lv[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int x = jq * 8 + e, j = j0 + x;
           const bool in = (j >= lo && j <= row);
           const float gtj = in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
           pm[e] = gtj * qk[x];
-          sm.l[row * kC + j] = (j < row) ? -beta_t * gtj * kk[x] : 0.f;
+          lv[e] = (j < row) ? -beta_t * gtj * kk[x] : 0.f;
         }
+        float4* lrow = reinterpret_cast<float4*>(&sm.l[row * kLS + j0 + jq * 8]);
+        lrow[0] = make_float4(lv[0], lv[1], lv[2], lv[3]);
+        lrow[1] = make_float4(lv[4], lv[5], lv[6], lv[7]);
         sm.p[((j0 >> 3) + jq) * kC + row] = pack8_bf16(pm);
       }
     }
@@ -302,7 +309,7 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const __grid_const
       atomicAdd(&sm.dgam[2 * lane], ga[0]);
       atomicAdd(&sm.dgam[2 * lane + 1], ga[1]);
 
-      backward_substitute(reinterpret_cast<float2*>(r), sm.l);                  // r = dUt[v][.]
+      backward_substitute<kLS>(reinterpret_cast<float2*>(r), sm.l);                  // r = dUt[v][.]
 
       // dR = beta dUt: the dV tile (row-major [t][v], staged in `lt`), -(g dR)^T panels,
       // dUt^T panels, and dg_t -= dr_t . (S_in k_t)
@@ -392,7 +399,7 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const __grid_const
         tmem_ld_row<16>(lane_base + kColW + h2 * 16, w);
 #pragma unroll
         for (int jq = 0; jq < 2; ++jq) {
-          float a8[8], b8[8];
+          float a8[8], b8[8], ev[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const int x = jq * 8 + e, j = j0 + h2 * 16 + x;
@@ -402,10 +409,12 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const __grid_const
             if (j == row) wtt = w[x];
             a8[e] = dp[x] * gtj;
             b8[e] = dl * gtj;
-            const float ev = (dp[x] * qk[x] + dl * kk[x]) * gtj;
-            rs += ev;
-            sm.l[row * kC + j] = ev;
+            ev[e] = (dp[x] * qk[x] + dl * kk[x]) * gtj;
+            rs += ev[e];
           }
+          float4* erow = reinterpret_cast<float4*>(&sm.l[row * kLS + j0 + h2 * 16 + jq * 8]);
+          erow[0] = make_float4(ev[0], ev[1], ev[2], ev[3]);
+          erow[1] = make_float4(ev[4], ev[5], ev[6], ev[7]);
           const int pn = (j0 >> 3) + h2 * 2 + jq;
           dpg[pn * kC + row] = pack8_bf16(a8);
           dlg[pn * kC + row] = pack8_bf16(b8);
@@ -460,7 +469,7 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const __grid_const
     if (tid < kC) {
       float cs = 0.f;
 #pragma unroll 8
-      for (int t = 0; t < kC; ++t) cs += sm.l[t * kC + tid];
+      for (int t = 0; t < kC; ++t) cs += sm.l[t * kLS + tid];
       sm.dcum[tid] = sm.rowsum[tid] - cs + sm.dg[tid] * sm.cd.g[tid] - sm.dgam[tid] * sm.cd.gam[tid];
       sm.colsum[tid] = sm.dgam[tid] * sm.cd.gam[tid];
     }

@@ -109,7 +109,8 @@ __device__ __forceinline__ void forward_substitute(float2* r2, const float* nlt)
 }
 
 // backward_substitute: r holds dU on entry and (I + diag(beta) L)^-T dU on exit;
-// nl[i * 64 + t] = -beta_i L_it (zero for t >= i).
+// nl[i * kStride + t] = -beta_i L_it (zero for t >= i), kStride a multiple of 4.
+template <int kStride>
 __device__ __forceinline__ void backward_substitute(float2* r2, const float* nl) {
   const float4* l4 = reinterpret_cast<const float4*>(nl);
 #pragma unroll
@@ -118,7 +119,7 @@ __device__ __forceinline__ void backward_substitute(float2* r2, const float* nl)
     const float2 x2 = make_float2(xi, xi);
 #pragma unroll
     for (int m = 0; m <= (i - 1) / 4; ++m) {
-      const float4 c = l4[i * (kC / 4) + m];
+      const float4 c = l4[i * (kStride / 4) + m];
       r2[2 * m] = __ffma2_rn(make_float2(c.x, c.y), x2, r2[2 * m]);
       r2[2 * m + 1] = __ffma2_rn(make_float2(c.z, c.w), x2, r2[2 * m + 1]);
     }
