@@ -1,6 +1,6 @@
 // Gated delta rule, backward, on the sm_100a tensor cores.
 //
-// One CTA (128 threads) owns one (batch, head) sequence and walks its 64-token
+// One CTA (256 threads) owns one (batch, head) sequence and walks its 64-token
 // chunks right to left with the fp32 cotangent of the state, dS (128 x 128),
 // resident in tensor memory.  S_in and U of every chunk are the forward call's residual.
 // With the chunk quantities of gdelta_common.cuh (A = I + diag(beta) L, P =
@@ -87,15 +87,16 @@ constexpr uint32_t kUpper = 16u << 16;
 constexpr uint32_t kColDS = 0, kColKK = 128, kColQK = 192, kColY = 256, kColOI = 320, kColX1 = 320, kColW = 320,
                    kColX2 = 384, kColDP = 448, kColDQ = 128, kColDK = 256, kColDelta = 384;
 
-// Sums 64 per-thread values over the 32 lanes of a warp; on return lane l holds
-// the totals of indices 2l and 2l+1 in vals[0], vals[1].
-__device__ __forceinline__ void warp_reduce64(float* vals, int lane) {
+// Sums N (32 or 64) per-thread values over the 32 lanes of a warp; on return lane l holds
+// the totals of indices (N / 32) l .. (N / 32) l + N / 32 - 1 in vals[0 .. N / 32 - 1].
+template <int N>
+__device__ __forceinline__ void warp_reduce(float* vals, int lane) {
 #pragma unroll
-  for (int off = 16, n = kC; off >= 1; off >>= 1, n >>= 1) {
+  for (int off = 16, n = N; off >= 1; off >>= 1, n >>= 1) {
     const int half = n >> 1;
     const bool upper = (lane & off) != 0;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
+    for (int i = 0; i < N / 2; ++i) {
       if (i < half) {
         const float send = upper ? vals[i] : vals[i + half];
         const float keep = upper ? vals[i + half] : vals[i];
@@ -124,13 +125,20 @@ __device__ __forceinline__ void issue_chunk_loads(BwdSmem& sm, const BwdParams& 
   tma::load_bulk(sm.u, src + kStateVecs, kUVecs * 16, &sm.bar_load);
 }
 
-__global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const __grid_constant__ BwdParams p) {
+// 256 threads: two warpgroups that see the same TMEM lanes (warp w and warp w + 4 share a lane
+// quarter) and split every epilogue between them -- by key / state columns where a thread
+// owns a token or value row, by role around the back substitution.
+constexpr int kBwdThreads = 256;
+
+__global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_constant__ BwdParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   BwdSmem& sm = *reinterpret_cast<BwdSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wg = warp >> 2;            // warpgroup
+  const int qw = warp & 3;             // TMEM lane quarter of this warp
+  const int vt = tid & 127;            // value row owned in the transposed (M = 128) accumulators
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
-  const int row = warp * 16 + (lane & 15);
-  const bool row_active = lane < 16;
+  const int row = qw * 16 + (lane & 15);   // token row owned in the M = 64 accumulators
   const bool upper = lane >= 16;
   const int nchunks = (p.T + kC - 1) / kC;
 
@@ -145,7 +153,7 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const __grid_const
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem = sm.tmem;
-  const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+  const uint32_t lane_base = tmem + (static_cast<uint32_t>(qw * 32) << 16);
 
   const size_t stride_t = static_cast<size_t>(p.H) * kD;
   const size_t seq_base = (static_cast<size_t>(b) * p.T * p.H + h) * kD;
@@ -156,20 +164,20 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const __grid_const
   if (tid == 0) issue_chunk_loads(sm, p, b, h, nchunks - 1, nchunks);
   float2 ab_next = fetch_chunk_decay(p.alpha, p.beta, bt_base, p.H, h, (nchunks - 1) * kC, p.T, tid);
   uint32_t flags_next = linattn::load_done_flags(drow, (nchunks - 1) * kC, p.T, lane);
-  // cotangent of the next carry: thread v owns dS[v][.]
+  // cotangent of the next carry: thread (v, wg) owns dS[v][64 wg .. 64 wg + 63]
   {
-    const float* g0 = p.ds_last ? p.ds_last + (static_cast<size_t>(bh) * kD + tid) * kD : nullptr;
-    float vals[kD];   // all loads first: the TMEM stores below are compiler memory barriers
+    const float* g0 = p.ds_last ? p.ds_last + (static_cast<size_t>(bh) * kD + vt) * kD + wg * 64 : nullptr;
+    float vals[64];   // all loads first: the TMEM stores below are compiler memory barriers
 #pragma unroll
-    for (int c4 = 0; c4 < kD / 4; ++c4) {
+    for (int c4 = 0; c4 < 16; ++c4) {
       float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
       if (g0) x = *reinterpret_cast<const float4*>(g0 + c4 * 4);
       vals[c4 * 4] = x.x; vals[c4 * 4 + 1] = x.y; vals[c4 * 4 + 2] = x.z; vals[c4 * 4 + 3] = x.w;
     }
 #pragma unroll
-    for (int c8 = 0; c8 < kPanD; ++c8) {
-      tmem_st8(lane_base + kColDS + c8 * 8, vals + c8 * 8);
-      sm.ds[c8 * kD + tid] = pack8_bf16(vals + c8 * 8);
+    for (int c8 = 0; c8 < 8; ++c8) {
+      tmem_st8(lane_base + kColDS + wg * 64 + c8 * 8, vals + c8 * 8);
+      sm.ds[(wg * 8 + c8) * kD + vt] = pack8_bf16(vals + c8 * 8);
     }
     tmem_st_wait();
   }
@@ -185,20 +193,21 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const __grid_const
     const uint64_t dm = linattn::done_mask_from_flags(flags_next);
     __syncthreads();
     chunk_decay_from_regs(sm.cd, ab_next, dm, tid);
-    if (tid < kC) sm.dg[tid] = sm.dgam[tid] = 0.f;
+    if (tid < kC) sm.dg[tid] = sm.dgam[tid] = sm.rowsum[tid] = 0.f;
     if (tid < 4) sm.dgl[tid] = 0.f;
 
     MXK_TG(0);
     const size_t tile = seq_base + static_cast<size_t>(t0) * stride_t;
     if (!mbar_wait(&sm.bar_load, it & 1)) timed_out = true;
-    // (gam U)^T from row v of U^T
+    // (gam U)^T from row v of U^T, four panels per warpgroup
 #pragma unroll
-    for (int jp = 0; jp < kPanC; ++jp) {
+    for (int j4 = 0; j4 < kPanC / 2; ++j4) {
+      const int jp = wg * (kPanC / 2) + j4;
       float f[8];
-      unpack8_bf16(sm.u[jp * kD + tid], f);
+      unpack8_bf16(sm.u[jp * kD + vt], f);
 #pragma unroll
       for (int e = 0; e < 8; ++e) f[e] *= sm.cd.gam[jp * 8 + e];
-      sm.ug[jp * kD + tid] = pack8_bf16(f);
+      sm.ug[jp * kD + vt] = pack8_bf16(f);
     }
     fence_smem_to_async();
     fence_before_sync();
@@ -230,16 +239,16 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const __grid_const
     MXK_TG(2);
 
     // ---- epilogue A1: -beta L (fp32, row-major) and tril(G o QK^T) (bf16); every thread owns
-    //      32 keys of its token row ----
+    //      16 keys of its token row ----
     {
       const int lo = row_first_key(dm, row);
       const float cum_t = sm.cd.cum[row], beta_t = sm.cd.beta[row];
-      const int j0 = upper ? 32 : 0;
-      float kk[32], qk[32];
-      tmem_ld_row<32>(lane_base + kColKK, kk);
-      tmem_ld_row<32>(lane_base + kColQK, qk);
+      const int j0 = (upper ? 32 : 0) + wg * 16;
+      float kk[16], qk[16];
+      tmem_ld_row<16>(lane_base + kColKK + wg * 16, kk);
+      tmem_ld_row<16>(lane_base + kColQK + wg * 16, qk);
 #pragma unroll
-      for (int jq = 0; jq < 4; ++jq) {
+      for (int jq = 0; jq < 2; ++jq) {
         float pm[8], lv[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
@@ -255,18 +264,15 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const __grid_const
         sm.p[((j0 >> 3) + jq) * kC + row] = pack8_bf16(pm);
       }
     }
-    __syncthreads();
-
-    // ---- epilogue A2: first dg term ----
+    // ---- epilogue A2: first dg term, dg_t += sum_v dO[t][v] (S_in q_t)[v]; thread (v, wg) covers
+    //      tokens 32 wg .. 32 wg + 31 ----
     {
-      float r[kC];
-      // dg_t += sum_v dO[t][v] (S_in q_t)[v]
-      tmem_ld_row<kC>(lane_base + kColOI, r);
+      float r[32];
+      tmem_ld_row<32>(lane_base + kColOI + wg * 32, r);
 #pragma unroll
-      for (int t = 0; t < kC; ++t) r[t] *= bf16_at(sm.r2, t, tid);
-      warp_reduce64(r, lane);
-      atomicAdd(&sm.dg[2 * lane], r[0]);
-      atomicAdd(&sm.dg[2 * lane + 1], r[1]);
+      for (int t = 0; t < 32; ++t) r[t] *= bf16_at(sm.r2, wg * 32 + t, vt);
+      warp_reduce<32>(r, lane);
+      atomicAdd(&sm.dg[wg * 32 + lane], r[0]);
     }
     fence_smem_to_async();
     fence_before_sync();
@@ -288,28 +294,19 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const __grid_const
     fence_after_sync();
     MXK_TG(4);
 
-    // ---- epilogue B: thread v: dU column, back substitution, dV, decay partials ----
-    {
+    // ---- epilogue B.  Warpgroup 0, thread v: dU column, back substitution, dV, second dg term.
+    //      Warpgroup 1 meanwhile: the dgam reduction and <dS, S_in>. ----
+    if (wg == 0) {
       __align__(8) float r[kC];
       float ga[kC];
       tmem_ld_row<kC>(lane_base + kColX2, ga);   // (dS k_j)[v]
       tmem_ld_row<kC>(lane_base + kColX1, r);
 #pragma unroll
-      for (int jp = 0; jp < kPanC; ++jp) {
-        float uf[8];
-        unpack8_bf16(sm.u[jp * kD + tid], uf);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int j = jp * 8 + e;
-          r[j] = fmaf(sm.cd.gam[j], ga[j], r[j]);   // dU[v][j]
-          ga[j] *= uf[e];                            // u_j[v] (dS k_j)[v]
-        }
-      }
-      warp_reduce64(ga, lane);
-      atomicAdd(&sm.dgam[2 * lane], ga[0]);
-      atomicAdd(&sm.dgam[2 * lane + 1], ga[1]);
+      for (int j = 0; j < kC; ++j) r[j] = fmaf(sm.cd.gam[j], ga[j], r[j]);   // dU[v][j]
+      MXK_TG(11);
 
-      backward_substitute<kLS>(reinterpret_cast<float2*>(r), sm.l);                  // r = dUt[v][.]
+      backward_substitute<kLS>(reinterpret_cast<float2*>(r), sm.l);          // r = dUt[v][.]
+      MXK_TG(12);
 
       // dR = beta dUt: the dV tile (row-major [t][v], staged in `lt`), -(g dR)^T panels,
       // dUt^T panels, and dg_t -= dr_t . (S_in k_t)
@@ -322,16 +319,32 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const __grid_const
         for (int e = 0; e < 8; ++e) {
           const int t = tp * 8 + e;
           const float dr = sm.cd.beta[t] * r[t];
-          dvt[t * kD + tid] = __float2bfloat16(dr);
+          dvt[t * kD + vt] = __float2bfloat16(dr);
           ng[e] = -sm.cd.g[t] * dr;
           ga[t] *= -dr;
         }
-        sm.r1[tp * kD + tid] = pack8_bf16(r + tp * 8);
-        sm.r2[tp * kD + tid] = pack8_bf16(ng);
+        sm.r1[tp * kD + vt] = pack8_bf16(r + tp * 8);
+        sm.r2[tp * kD + vt] = pack8_bf16(ng);
       }
-      warp_reduce64(ga, lane);
+      MXK_TG(13);
+      warp_reduce<64>(ga, lane);
       atomicAdd(&sm.dg[2 * lane], ga[0]);
       atomicAdd(&sm.dg[2 * lane + 1], ga[1]);
+      MXK_TG(14);
+    } else {
+      // dgam_j = sum_v u_j[v] (dS k_j)[v]
+      float ga[kC];
+      tmem_ld_row<kC>(lane_base + kColX2, ga);
+#pragma unroll
+      for (int jp = 0; jp < kPanC; ++jp) {
+        float uf[8];
+        unpack8_bf16(sm.u[jp * kD + vt], uf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ga[jp * 8 + e] *= uf[e];
+      }
+      warp_reduce<64>(ga, lane);
+      atomicAdd(&sm.dgam[2 * lane], ga[0]);
+      atomicAdd(&sm.dgam[2 * lane + 1], ga[1]);
 
       // <dS, S_in> for the g_last gradient
       float dot = 0.f;
@@ -342,14 +355,14 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const __grid_const
 #pragma unroll
         for (int c8 = 0; c8 < 4; ++c8) {
           float s8[8];
-          unpack8_bf16(sm.s[(q4 * 4 + c8) * kD + tid], s8);
+          unpack8_bf16(sm.s[(q4 * 4 + c8) * kD + vt], s8);
 #pragma unroll
           for (int e = 0; e < 8; ++e) dot = fmaf(d32[c8 * 8 + e], s8[e], dot);
         }
       }
 #pragma unroll
       for (int off = 16; off >= 1; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-      if (lane == 0) sm.dgl[warp] = dot;
+      if (lane == 0) sm.dgl[qw] = dot;
     }
     fence_smem_to_async();
     fence_before_sync();
@@ -359,8 +372,8 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const __grid_const
       __nv_bfloat16* base = p.dv + tile;
       const uint4* src = reinterpret_cast<const uint4*>(sm.lt);
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const int vid = r * kThreads + tid;
+      for (int r = 0; r < 4; ++r) {
+        const int vid = r * kBwdThreads + tid;
         const int trow = vid >> 4, seg = vid & 15;
         if (trow < valid) *reinterpret_cast<uint4*>(base + trow * stride_t + seg * 8) = src[trow * 16 + seg];
       }
@@ -381,55 +394,50 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const __grid_const
     MXK_TG(6);
     __syncthreads();  // every thread has flushed its part of the dV tile before `lt` is reused
 
-    // ---- epilogue C: (dP o G), (dL o G), E, dbeta; g-scaled dO.  Every thread owns 32 keys of
+    // ---- epilogue C: (dP o G), (dL o G), E, dbeta; g-scaled dO.  Every thread owns 16 keys of
     //      its token row ----
     {
       uint4* dpg = reinterpret_cast<uint4*>(sm.lt);           // [j/8][t][8]
       uint4* dlg = dpg + kPanC * kC;
       const int lo = row_first_key(dm, row);
       const float cum_t = sm.cd.cum[row], beta_t = sm.cd.beta[row];
-      const int j0 = upper ? 32 : 0;
-      float rs = 0.f, wtt = 0.f;
+      const int j0 = (upper ? 32 : 0) + wg * 16;
+      float rs = 0.f;
+      float kk[16], qk[16], dp[16], w[16];
+      tmem_ld_row<16>(lane_base + kColKK + wg * 16, kk);
+      tmem_ld_row<16>(lane_base + kColQK + wg * 16, qk);
+      tmem_ld_row<16>(lane_base + kColDP + wg * 16, dp);
+      tmem_ld_row<16>(lane_base + kColW + wg * 16, w);
 #pragma unroll
-      for (int h2 = 0; h2 < 2; ++h2) {
-        float kk[16], qk[16], dp[16], w[16];
-        tmem_ld_row<16>(lane_base + kColKK + h2 * 16, kk);
-        tmem_ld_row<16>(lane_base + kColQK + h2 * 16, qk);
-        tmem_ld_row<16>(lane_base + kColDP + h2 * 16, dp);
-        tmem_ld_row<16>(lane_base + kColW + h2 * 16, w);
+      for (int jq = 0; jq < 2; ++jq) {
+        float a8[8], b8[8], ev[8];
 #pragma unroll
-        for (int jq = 0; jq < 2; ++jq) {
-          float a8[8], b8[8], ev[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int x = jq * 8 + e, j = j0 + h2 * 16 + x;
-            const bool in = (j >= lo && j <= row);
-            const float gtj = in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
-            const float dl = (j < row) ? -beta_t * w[x] : 0.f;
-            if (j == row) wtt = w[x];
-            a8[e] = dp[x] * gtj;
-            b8[e] = dl * gtj;
-            ev[e] = (dp[x] * qk[x] + dl * kk[x]) * gtj;
-            rs += ev[e];
-          }
-          float4* erow = reinterpret_cast<float4*>(&sm.l[row * kLS + j0 + h2 * 16 + jq * 8]);
-          erow[0] = make_float4(ev[0], ev[1], ev[2], ev[3]);
-          erow[1] = make_float4(ev[4], ev[5], ev[6], ev[7]);
-          const int pn = (j0 >> 3) + h2 * 2 + jq;
-          dpg[pn * kC + row] = pack8_bf16(a8);
-          dlg[pn * kC + row] = pack8_bf16(b8);
+        for (int e = 0; e < 8; ++e) {
+          const int x = jq * 8 + e, j = j0 + x;
+          const bool in = (j >= lo && j <= row);
+          const float gtj = in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
+          const float dl = (j < row) ? -beta_t * w[x] : 0.f;
+          // dbeta_t = (dUt_t . U_t) / beta_t: the diagonal of W, held by exactly one thread per row
+          if (j == row && row < valid)
+            p.dbeta[(static_cast<size_t>(b) * p.T + t0 + row) * p.H + h] = beta_t > 0.f ? w[x] / beta_t : 0.f;
+          a8[e] = dp[x] * gtj;
+          b8[e] = dl * gtj;
+          ev[e] = (dp[x] * qk[x] + dl * kk[x]) * gtj;
+          rs += ev[e];
         }
+        float4* erow = reinterpret_cast<float4*>(&sm.l[row * kLS + j0 + jq * 8]);
+        erow[0] = make_float4(ev[0], ev[1], ev[2], ev[3]);
+        erow[1] = make_float4(ev[4], ev[5], ev[6], ev[7]);
+        const int pn = (j0 >> 3) + jq;
+        dpg[pn * kC + row] = pack8_bf16(a8);
+        dlg[pn * kC + row] = pack8_bf16(b8);
       }
       rs += __shfl_xor_sync(0xffffffffu, rs, 16);
-      wtt += __shfl_xor_sync(0xffffffffu, wtt, 16);
-      if (!upper) {
-        sm.rowsum[row] = rs;
-        if (row < valid) p.dbeta[(static_cast<size_t>(b) * p.T + t0 + row) * p.H + h] = beta_t > 0.f ? wtt / beta_t : 0.f;
-      }
+      if (!upper) atomicAdd(&sm.rowsum[row], rs);
       const float gt = sm.cd.g[row];
-      const int p0 = upper ? kPanD / 2 : 0;
+      const int p0 = (upper ? kPanD / 2 : 0) + wg * (kPanD / 4);
 #pragma unroll
-      for (int pp = 0; pp < kPanD / 2; ++pp) {
+      for (int pp = 0; pp < kPanD / 4; ++pp) {
         float f[8];
         unpack8_bf16(sm.d_o[(p0 + pp) * kC + row], f);
 #pragma unroll
@@ -506,28 +514,27 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const __grid_const
       flags_next = linattn::load_done_flags(drow, t0 - kC, p.T, lane);
     }
 
-    // ---- epilogue D: dq, dk rows; dS = g_last dS + increment ----
+    // ---- epilogue D: dq rows (warpgroup 0), dk rows (warpgroup 1); dS = g_last dS + increment,
+    //      64 state columns per warpgroup ----
     {
-      const bool store = row_active && row < valid;
+      const bool store = !upper && row < valid;
+      __nv_bfloat16* dst = (wg == 0 ? p.dq : p.dk) + tile + static_cast<size_t>(row) * stride_t;
+      const uint32_t col = wg == 0 ? kColDQ : kColDK;
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        __nv_bfloat16* dst = (which == 0 ? p.dq : p.dk) + tile + static_cast<size_t>(row) * stride_t;
-        const uint32_t col = which == 0 ? kColDQ : kColDK;
+      for (int half = 0; half < 2; ++half) {
+        float acc[kC];
+        tmem_ld_row<kC>(lane_base + col + half * kC, acc);
+        if (store) {
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          float acc[kC];
-          tmem_ld_row<kC>(lane_base + col + half * kC, acc);
-          if (store) {
-#pragma unroll
-            for (int pn = 0; pn < kPanC; ++pn)
-              reinterpret_cast<uint4*>(dst)[half * kPanC + pn] = pack8_bf16(acc + pn * 8);
-          }
+          for (int pn = 0; pn < kPanC; ++pn)
+            reinterpret_cast<uint4*>(dst)[half * kPanC + pn] = pack8_bf16(acc + pn * 8);
         }
       }
       const float g_last = sm.cd.g[kC - 1];
-      float* out0 = (c == 0 && p.ds0) ? p.ds0 + (static_cast<size_t>(bh) * kD + tid) * kD : nullptr;
+      float* out0 = (c == 0 && p.ds0) ? p.ds0 + (static_cast<size_t>(bh) * kD + vt) * kD : nullptr;
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
+      for (int q2 = 0; q2 < 2; ++q2) {
+        const int q4 = wg * 2 + q2;
         float s[32], inc[32];
         tmem_ld_row<32>(lane_base + kColDS + q4 * 32, s);
         tmem_ld_row<32>(lane_base + kColDelta + q4 * 32, inc);
@@ -536,7 +543,7 @@ __global__ void __launch_bounds__(kThreads) gdelta_bwd_kernel(const __grid_const
 #pragma unroll
         for (int c8 = 0; c8 < 4; ++c8) {
           tmem_st8(lane_base + kColDS + q4 * 32 + c8 * 8, s + c8 * 8);
-          sm.ds[(q4 * 4 + c8) * kD + tid] = pack8_bf16(s + c8 * 8);
+          sm.ds[(q4 * 4 + c8) * kD + vt] = pack8_bf16(s + c8 * 8);
           if (out0) {
             *reinterpret_cast<float4*>(out0 + q4 * 32 + c8 * 8) = make_float4(s[c8 * 8], s[c8 * 8 + 1], s[c8 * 8 + 2], s[c8 * 8 + 3]);
             *reinterpret_cast<float4*>(out0 + q4 * 32 + c8 * 8 + 4) = make_float4(s[c8 * 8 + 4], s[c8 * 8 + 5], s[c8 * 8 + 6], s[c8 * 8 + 7]);
@@ -607,7 +614,7 @@ int mxk_gdelta_bf16_bwd(const void* q, const void* k, const void* v, const float
   cudaError_t e = cudaFuncSetAttribute(gdelta_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(BwdSmem)));
   if (e != cudaSuccess) return static_cast<int>(e);
-  gdelta_bwd_kernel<<<B * H, kThreads, sizeof(BwdSmem), static_cast<cudaStream_t>(stream)>>>(prm);
+  gdelta_bwd_kernel<<<B * H, kBwdThreads, sizeof(BwdSmem), static_cast<cudaStream_t>(stream)>>>(prm);
   return launch_status();
 }
 
