@@ -55,6 +55,7 @@ class LinAttnC2:
     dominant = "linattn_bwd_kernel"
     launches_per_step = 2
     e2e_slices = 4   # independent sequences: copy-in, kernels and copy-out overlap slice by slice
+    e2e_graph = True
     # dram__bytes_read.sum + dram__bytes_write.sum of one linattn_bwd_kernel launch at
     # this size (ncu capture summarised under profiles/)
     dominant_traffic_bytes = 249.7e6
@@ -213,6 +214,7 @@ class GDeltaC3:
     dominant = "gdelta_bwd_kernel"
     launches_per_step = 2
     e2e_slices = 4
+    e2e_graph = True
     dominant_traffic_bytes = None
     cpu_sample_batch = 4
 
@@ -544,7 +546,8 @@ def run_gpu_arm(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     from memorax_b200.host import HostPipeline
     nslices = args.e2e_slices or getattr(w, "e2e_slices", 1)
-    pipe = HostPipeline(lambda xs: w.step(xs, ops), w.B, dev, slices=nslices)
+    use_graph = bool(getattr(w, "e2e_graph", False)) and not args.no_e2e_graph
+    pipe = HostPipeline(lambda xs: w.step(xs, ops), w.B, dev, slices=nslices, graph=use_graph)
     pipe.run(pinned_in, pinned_out)          # warm the three streams' allocator pools
     barrier()
     e0.record()
@@ -580,7 +583,8 @@ def run_gpu_arm(args):
                        "launch": "cuda graph replay" if graphs else "direct"},
             "clocks": clocks.summary(),
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": e2e_steps, "batch_slices_in_flight": nslices},
+                    "steps": e2e_steps, "batch_slices_in_flight": nslices,
+                    "launch": "cuda graph replay of the three-stream schedule" if use_graph else "direct"},
             "gpu_launches": w.launches_per_step * args.steps,
             "roofline": roof,
         }
@@ -600,6 +604,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=None, help="override sequences per GPU (profiling only)")
     ap.add_argument("--e2e-slices", type=int, default=None, help="override the batch slices of the host pipeline")
+    ap.add_argument("--no-e2e-graph", action="store_true", help="enqueue the host pipeline call by call instead of replaying a graph")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     if args.impl == "reference":

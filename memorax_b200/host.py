@@ -4,7 +4,12 @@ A caller that keeps its batch in host memory (the reference's CPU-environment
 setups do: docs/source/guides/sharp_bits.md:3-9) pays PCIe both ways.  Every op
 here is independent per sequence, so the batch is cut into slices that flow
 through three streams -- host-to-device copy, kernels, device-to-host copy --
-and the two copy directions and the kernels overlap."""
+and the two copy directions and the kernels overlap.
+
+With ``graph=True`` the whole three-stream schedule of one call is captured into a
+CUDA graph the first time a given set of host buffers is seen and replayed
+afterwards, so that a step costs one launch on the host however many slices it has
+(the usual pattern: the caller refills the same pinned staging buffers every step)."""
 from __future__ import annotations
 
 import torch
@@ -16,18 +21,42 @@ class HostPipeline:
 
     Tensors whose leading dimension equals ``batch`` are sliced; anything else is
     copied whole with the first slice.  ``slices=1`` degenerates to copy, run,
-    copy on one stream each (for steps that are not separable over the batch)."""
+    copy on one stream each (for steps that are not separable over the batch).
 
-    def __init__(self, step, batch, device, slices=4):
+    ``graph=True``: ``step`` must then be capturable (no host synchronisation, no
+    data-dependent host control flow) and the host tensors must stay alive and in
+    place for as long as the pipeline is used with them."""
+
+    def __init__(self, step, batch, device, slices=4, graph=False):
         self.step, self.batch, self.device = step, batch, device
         self.slices = max(1, min(slices, batch))
+        self.graph = graph
+        self._graphs = {}
         self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(device=device) for _ in range(3))
+        self.s_capture = torch.cuda.Stream(device=device) if graph else None
 
     def _bounds(self, i):
         per = -(-self.batch // self.slices)
         return i * per, min(self.batch, (i + 1) * per)
 
     def run(self, host_inputs, host_outputs):
+        if not self.graph:
+            return self._enqueue(host_inputs, host_outputs, capturing=False)
+        key = (tuple((n, t.data_ptr(), tuple(t.shape), t.dtype) for n, t in host_inputs.items()),
+               tuple((t.data_ptr(), tuple(t.shape), t.dtype) for t in host_outputs))
+        entry = self._graphs.get(key)
+        if entry is None:
+            # once eagerly (lazy initialisation, allocator warm-up), then capture
+            self._enqueue(host_inputs, host_outputs, capturing=False)
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=self.s_capture):
+                keep = self._enqueue(host_inputs, host_outputs, capturing=True)
+            entry = self._graphs[key] = (g, keep, host_inputs, host_outputs)
+        entry[0].replay()
+        return entry[1]
+
+    def _enqueue(self, host_inputs, host_outputs, capturing):
         main = torch.cuda.current_stream(self.device)
         start = torch.cuda.Event()
         start.record(main)
@@ -48,14 +77,16 @@ class HostPipeline:
                         if name not in shared:
                             shared[name] = t.to(self.device, non_blocking=True)
                         x[name] = shared[name]
-                    x[name].record_stream(self.s_run)
+                    if not capturing:   # a captured schedule keeps its tensors alive in `keep`
+                        x[name].record_stream(self.s_run)
                 ready = torch.cuda.Event()
                 ready.record(self.s_in)
             self.s_run.wait_event(ready)
             with torch.cuda.stream(self.s_run):
                 outs = self.step(x)
-                for o in outs:
-                    o.record_stream(self.s_out)
+                if not capturing:
+                    for o in outs:
+                        o.record_stream(self.s_out)
                 done = torch.cuda.Event()
                 done.record(self.s_run)
             self.s_out.wait_event(done)

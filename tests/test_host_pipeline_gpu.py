@@ -29,3 +29,40 @@ def test_host_pipeline_matches_direct_call():
         torch.cuda.synchronize()
         for got, want in zip(outs, ref):
             assert torch.equal(got, want.cpu()), slices
+
+
+def test_host_pipeline_graph_replay_tracks_buffer_contents():
+    """graph=True captures the schedule once; later calls replay it and must see the
+    host buffers' CURRENT contents."""
+    from memorax_b200 import ops
+    from memorax_b200.host import HostPipeline
+    g = torch.Generator().manual_seed(1)
+    B, T, H, D = 12, 130, 2, 128
+    mk = lambda *s: torch.randn(*s, generator=g)
+    nrm = lambda x: x / x.norm(dim=-1, keepdim=True)
+
+    def fresh():
+        return dict(q=nrm(mk(B, T, H, D)).bfloat16(), k=nrm(mk(B, T, H, D)).bfloat16(), v=mk(B, T, H, D).bfloat16(),
+                    alpha=torch.sigmoid(mk(B, T, H) + 2), beta=torch.sigmoid(mk(B, T, H)),
+                    done=(torch.rand(B, T, generator=g) < 0.02).to(torch.uint8))
+
+    def step(x):
+        o, s_last, _ = ops.gdelta_fwd(x["q"], x["k"], x["v"], x["alpha"], x["beta"], None, x["done"])
+        return o, s_last
+
+    host = {k: v.pin_memory() for k, v in fresh().items()}
+    ref = step({k: v.cuda() for k, v in host.items()})
+    outs = [torch.empty(r.shape, dtype=r.dtype, pin_memory=True) for r in ref]
+    pipe = HostPipeline(step, B, torch.device("cuda", 0), slices=3, graph=True)
+    for trial in range(3):
+        if trial:
+            for k, v in fresh().items():
+                host[k].copy_(v)          # same pinned buffers, new contents
+            ref = step({k: v.cuda() for k, v in host.items()})
+        for o in outs:
+            o.zero_()
+        pipe.run(host, outs)
+        torch.cuda.synchronize()
+        for got, want in zip(outs, ref):
+            assert torch.equal(got, want.cpu()), trial
+    assert len(pipe._graphs) == 1
