@@ -19,6 +19,7 @@
 
 #include "mxk_common.cuh"
 #include "linattn_common.cuh"
+#include "tma.cuh"
 
 namespace mxk {
 namespace {
@@ -41,6 +42,7 @@ struct FwdParams {
   int B, T, H;
   float eps;
   int feature_map;
+  CUtensorMap map_q, map_k, map_v;   // 64-token tiles in panel order
 };
 
 struct FwdSmem {
@@ -50,6 +52,7 @@ struct FwdSmem {
   uint4 alt[kPanelsX * kC];     // chunks with a reset: keep rows of V|1, then live rows of phi(Q)
   uint4 s[2][kPanelsX * kD];    // bf16 S^T | z entering / leaving the chunk   [v/8][k]
   uint64_t bar[2];
+  uint64_t bar_load;
   uint32_t tmem;
 };
 static_assert(sizeof(FwdSmem) <= 55 * 1024, "four CTAs per SM");
@@ -69,7 +72,7 @@ namespace {
 constexpr uint32_t kTmemCols = 128;
 constexpr uint32_t kUpper = 16u << 16;
 
-__global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const FwdParams p) {
+__global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_constant__ FwdParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   FwdSmem& sm = *reinterpret_cast<FwdSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -82,6 +85,7 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const FwdParam
   if (tid == 0) {
     mbar_init(&sm.bar[0], 1);
     mbar_init(&sm.bar[1], 1);
+    mbar_init(&sm.bar_load, 1);
     mbar_init_fence();
   }
   if (warp == 0) tmem_alloc(&sm.tmem, kTmemCols);
@@ -90,6 +94,18 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const FwdParam
   fence_after_sync();
   const uint32_t tmem = sm.tmem;
   const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+
+  // The raw Q, K, V tiles of a chunk arrive by TMA straight in operand order, issued by one
+  // thread one chunk ahead: as soon as the second MMA group of the previous chunk has released
+  // the buffers, so that the copies overlap that chunk's output epilogue.
+  auto issue_chunk_loads = [&](int cc) {
+    fence_smem_to_async();   // earlier generic-proxy accesses to the buffers come first
+    tma::expect_bytes(&sm.bar_load, 3 * kPanels * kC * 16);
+    tma::load_panel_tile(sm.q, &p.map_q, &sm.bar_load, cc * kC, h, b);
+    tma::load_panel_tile(sm.k, &p.map_k, &sm.bar_load, cc * kC, h, b);
+    tma::load_panel_tile(sm.v, &p.map_v, &sm.bar_load, cc * kC, h, b);
+  };
+  if (tid == 0) issue_chunk_loads(0);
 
   // Carried state -> TMEM (fp32, upper lanes) and its bf16 operand copy.  Upper
   // thread `row` owns S^T[row][.] = S[.][row]; S is (d_v, d_k) row-major in
@@ -136,41 +152,26 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const FwdParam
     const bool has_reset = dm != 0ull;
     MXK_T(0);
 
-    // ---- stage phi(Q), phi(K), V|1 (keep-masked copy only if the chunk has a reset) ----
-    {
-      uint4 raw[12];   // all twelve loads are issued before any of them is consumed
+    // ---- the tiles have landed: feature map in place, keep-masked copy of V only if the
+    //      chunk has a reset ----
+    if (!mbar_wait(&sm.bar_load, c & 1)) timed_out = true;
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        int trow, seg;
-        tile_vec(r * kThreads + tid, trow, seg);
-        const size_t g = seq_base + static_cast<size_t>(t0 + trow) * stride_t + seg * 8;
-        const bool in = trow < valid;
-        raw[3 * r] = in ? __ldg(reinterpret_cast<const uint4*>(p.q + g)) : zero4;
-        raw[3 * r + 1] = in ? __ldg(reinterpret_cast<const uint4*>(p.k + g)) : zero4;
-        raw[3 * r + 2] = in ? __ldg(reinterpret_cast<const uint4*>(p.v + g)) : zero4;
+    for (int r = 0; r < 4; ++r) {
+      int trow, seg;
+      tile_vec(r * kThreads + tid, trow, seg);
+      const int slot = seg * kC + trow;
+      if (p.feature_map && trow < valid) {
+        sm.q[slot] = phi8(sm.q[slot]);
+        sm.k[slot] = phi8(sm.k[slot]);
       }
-#pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        int trow, seg;
-        tile_vec(r * kThreads + tid, trow, seg);
-        uint4 qv = raw[3 * r], kv = raw[3 * r + 1];
-        const uint4 vv = raw[3 * r + 2];
-        if (p.feature_map && trow < valid) {
-          qv = phi8(qv);
-          kv = phi8(kv);
-        }
-        const int slot = seg * kC + trow;
-        sm.q[slot] = qv;
-        sm.k[slot] = kv;
-        sm.v[slot] = vv;
-        if (has_reset) sm.alt[slot] = row_keep(dm, trow) ? vv : zero4;
-      }
+      if (has_reset) sm.alt[slot] = row_keep(dm, trow) ? sm.v[slot] : zero4;
     }
     if (tid < kC) {
       const uint4 one = make_uint4(tid < valid ? kOneBf16 : 0u, 0, 0, 0);
       sm.v[kPanels * kC + tid] = one;
       if (has_reset) sm.alt[kPanels * kC + tid] = row_keep(dm, tid) ? one : zero4;
     }
+    if (tid == 0) tma::wait_group_read<0>();   // the previous residual copy has finished reading s[cur ^ 1]
     fence_smem_to_async();
     fence_before_sync();
     MXK_T(1);
@@ -184,11 +185,12 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const FwdParam
       gemm(tmem, aq, bk, idesc_p, kD / 16, false);                           // P        -> lower lanes
       gemm(tmem + kUpper, ak, bvk, idesc_s, kC / 16, !has_reset);            // S^T | z  -> upper lanes
       commit(&sm.bar[0]);
-    }
-    // residual for the backward pass: the state entering this chunk
-    if (p.chunk_states) {
-      uint4* dst = p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * (kPanelsX * kD);
-      for (int i = tid; i < kPanelsX * kD; i += kThreads) dst[i] = sm.s[cur][i];
+      // residual for the backward pass: the state entering this chunk
+      if (p.chunk_states) {
+        tma::store_bulk(p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * (kPanelsX * kD), sm.s[cur],
+                        kPanelsX * kD * 16);
+        tma::commit_group();
+      }
     }
     if (!mbar_wait(&sm.bar[0], c & 1)) timed_out = true;
     fence_after_sync();
@@ -247,6 +249,7 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const FwdParam
     }
     if (!mbar_wait(&sm.bar[1], c & 1)) timed_out = true;
     fence_after_sync();
+    if (tid == 0 && c + 1 < nchunks) issue_chunk_loads(c + 1);
     MXK_T(6);
 
     // ---- epilogue B: lower rows normalise and store ----
@@ -262,16 +265,17 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const FwdParam
         for (int e = 0; e < 8; ++e) f[e] = orow[pn * 8 + e] * inv;
         packed[pn] = pack8_bf16(f);
       }
-      // V|1 is dead once the second MMA group has completed: its buffer stages the output rows
-      store_rows_coalesced(sm.v + warp * (16 * 9), packed, !upper, lane,
+      // the masked copies are dead once the second MMA group has completed: `alt` stages the output rows
+      store_rows_coalesced(sm.alt + warp * (16 * 9), packed, !upper, lane,
                            p.o + seq_base + static_cast<size_t>(t0 + warp * 16) * stride_t, stride_t,
                            valid - warp * 16);
     }
-    __syncthreads();   // the staging rows live in sm.v, which the next chunk's staging overwrites
+    __syncthreads();   // the staging rows live in sm.alt, which the next chunk may overwrite
     cur ^= 1;
     MXK_T(7);
   }
 
+  if (tid == 0) tma::wait_group_all();
   if (timed_out && p.status) atomicExch(p.status, 1);
   fence_before_sync();
   __syncthreads();
@@ -326,6 +330,9 @@ int mxk_linattn_bf16_fwd(const void* q, const void* k, const void* v, const floa
   prm.B = B; prm.T = T; prm.H = H;
   prm.eps = eps;
   prm.feature_map = feature_map;
+  if (!tma::make_panel_map(&prm.map_q, q, B, T, H, kD, kC) || !tma::make_panel_map(&prm.map_k, k, B, T, H, kD, kC) ||
+      !tma::make_panel_map(&prm.map_v, v, B, T, H, kD, kC))
+    return MXK_ERR_UNSUPPORTED;
   cudaError_t e = cudaFuncSetAttribute(linattn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(FwdSmem)));
   if (e != cudaSuccess) return static_cast<int>(e);
