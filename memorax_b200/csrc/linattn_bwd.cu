@@ -22,6 +22,7 @@
 
 #include "linattn_common.cuh"
 #include "mxk_common.cuh"
+#include "tma.cuh"
 
 namespace mxk {
 namespace {
@@ -30,6 +31,9 @@ using namespace umma;
 using namespace linattn;
 
 constexpr int kPanelsK = kPanels + 2;  // 80 columns: a K = 80 contraction needs whole K=16 steps
+// 256 threads: two warpgroups that see the same TMEM lanes (warp w and warp w + 4 share a
+// lane quarter) and split the columns of every row between them.
+constexpr int kBwdThreads = 256;
 
 struct BwdParams {
   const __nv_bfloat16* q;
@@ -49,23 +53,27 @@ struct BwdParams {
   int B, T, H;
   float eps;
   int feature_map;
+  CUtensorMap map_q, map_k, map_v, map_do;   // 64-token tiles in panel order
 };
 
 struct BwdSmem {
   uint4 q[kPanels * kC];      // phi(Q)                 [k/8][i]
   uint4 k[kPanels * kC];      // phi(K)                 [k/8][j]
-  uint4 kk[kPanels * kC];     // keep rows of phi(K)
-  uint4 v[kPanels * kC];      // V                      [v/8][j]
-  uint4 vk[kPanelsK * kC];    // keep rows of V | 1 | 0 [v/8][j]
+  uint4 kk[kPanels * kC];     // keep rows of phi(K)    (written only for chunks with a reset)
+  uint4 v[kPanelsK * kC];     // V | 1 | 0              [v/8][j]
+  uint4 vk[kPanelsK * kC];    // keep rows of V | 1 | 0 (written only for chunks with a reset)
   uint4 d_o[kPanels * kC];    // dO                     [v/8][i]
   uint4 dos[kPanelsK * kC];   // live rows of dO/D | dden | 0
   uint4 s[kPanelsK * kD];     // S_in^T | z_in | 0      [v/8][k]
   uint4 g[kPanelsK * kD];     // G^T | gz | 0           [v/8][k]
   uint4 pn[kPanels * kC];     // P / D                  [j/8][i]
   uint4 dp[kPanels * kC];     // dP                     [j/8][i]
+  float xch[2][2][kC];        // per warpgroup: partial den and don of every query row
   uint64_t bar[2];
+  uint64_t bar_load;
   uint32_t tmem;
 };
+static_assert(sizeof(BwdSmem) <= 113 * 1024, "two CTAs per SM");
 
 // 256 TMEM columns per CTA (two CTAs per SM).  M = 64 accumulators use 16 of a
 // warp's 32 TMEM lanes, so lanes 0..15 ("lower" threads) and 16..31 ("upper"
@@ -76,6 +84,7 @@ struct BwdSmem {
 //                      dphiK (upper)
 //   columns  64..135   lower: dV                  upper: G^T | gz (persistent)
 //   columns 136..167   R, state features 0..31 in the lower lanes, 32..63 in the upper lanes
+// Within a half-warp's 32 columns, warpgroup 0 takes the first 16 and warpgroup 1 the rest.
 #ifdef MXK_TIMING
 }  // namespace
 __device__ unsigned long long g_bwd_phase_cycles[8];
@@ -90,24 +99,48 @@ constexpr uint32_t kColLo = 0, kColHi = 64, kColP = 0, kColA = 32, kColR = 136;
 
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 
-__global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParams p) {
+// Coalesced store of 16 rows x 32 bf16 (half rows) owned by one warp: the 16 `writer`
+// lanes each hold four 16-byte vectors of one row; they go through a per-warp staging
+// area (row stride 5 vectors, conflict free) and all 32 lanes store eight complete
+// 64-byte half rows per instruction.  `stage`: this warp's 80 vectors; `grow0`: the
+// warp's first row, already offset to its column block.
+__device__ __forceinline__ void store_half_rows(uint4* stage, const uint4* vals, bool writer, int lane,
+                                                __nv_bfloat16* grow0, size_t stride_t, int rows_valid) {
+  if (writer) {
+#pragma unroll
+    for (int s4 = 0; s4 < 4; ++s4) stage[(lane & 15) * 5 + s4] = vals[s4];
+  }
+  __syncwarp();
+#pragma unroll
+  for (int it = 0; it < 2; ++it) {
+    const int r = 8 * it + (lane >> 2), seg = lane & 3;
+    if (r < rows_valid) *reinterpret_cast<uint4*>(grow0 + r * stride_t + seg * 8) = stage[r * 5 + seg];
+  }
+  __syncwarp();
+}
+
+__global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __grid_constant__ BwdParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   BwdSmem& sm = *reinterpret_cast<BwdSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wg = warp >> 2;   // warpgroup
+  const int qw = warp & 3;    // TMEM lane quarter of this warp
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
   const bool upper = lane >= 16;
-  const int row = warp * 16 + (lane & 15);
+  const int row = qw * 16 + (lane & 15);
   const int nchunks = (p.T + kC - 1) / kC;
   const uint4 zero4 = make_uint4(0, 0, 0, 0);
 
   if (tid == 0) {
     mbar_init(&sm.bar[0], 1);
     mbar_init(&sm.bar[1], 1);
+    mbar_init(&sm.bar_load, 2);   // two groups of copies per chunk, issued at different times
     mbar_init_fence();
   }
   if (warp == 0) tmem_alloc(&sm.tmem, kBwdTmemCols);
   // zero padding panels that never change (columns 72..79 of the 80-wide operands)
   if (tid < kC) {
+    sm.v[(kPanelsK - 1) * kC + tid] = zero4;
     sm.vk[(kPanelsK - 1) * kC + tid] = zero4;
     sm.dos[(kPanelsK - 1) * kC + tid] = zero4;
     sm.s[(kPanelsK - 1) * kD + tid] = zero4;
@@ -117,27 +150,55 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem = sm.tmem;
-  const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+  const uint32_t lane_base = tmem + (static_cast<uint32_t>(qw * 32) << 16);
+
+  // A chunk's tiles arrive by TMA in operand order, issued by one thread as soon as the
+  // previous chunk no longer needs the buffers: V, dO and S_in (the forward call's
+  // residual) once its second MMA group has completed, Q and K once its epilogue has
+  // read the feature-map derivative from them.
+  auto issue_state_loads = [&](int cc) {
+    fence_smem_to_async();   // earlier generic-proxy accesses to the buffers come first
+    tma::expect_bytes(&sm.bar_load, (2 * kPanels * kC + kPanelsX * kD) * 16);
+    tma::load_panel_tile(sm.v, &p.map_v, &sm.bar_load, cc * kC, h, b);
+    tma::load_panel_tile(sm.d_o, &p.map_do, &sm.bar_load, cc * kC, h, b);
+    tma::load_bulk(sm.s, p.chunk_states + (static_cast<size_t>(bh) * nchunks + cc) * (kPanelsX * kD),
+                   kPanelsX * kD * 16, &sm.bar_load);
+  };
+  auto issue_qk_loads = [&](int cc) {
+    fence_smem_to_async();
+    tma::expect_bytes(&sm.bar_load, 2 * kPanels * kC * 16);
+    tma::load_panel_tile(sm.q, &p.map_q, &sm.bar_load, cc * kC, h, b);
+    tma::load_panel_tile(sm.k, &p.map_k, &sm.bar_load, cc * kC, h, b);
+  };
+  if (tid == 0) {
+    issue_state_loads(nchunks - 1);
+    issue_qk_loads(nchunks - 1);
+  }
 
   // Cotangent of the next carry -> TMEM (upper lanes) and its bf16 operand copy
-  // (upper thread `row` owns G^T[row][.] = dS[.][row]).
+  // (upper thread `row` owns G^T[row][.] = dS[.][row]; warpgroup 0 takes value columns
+  // 0..31, warpgroup 1 columns 32..63 and gz).
+  const int gp0 = wg ? 4 : 0, gpn = wg ? 5 : 4;   // this warpgroup's panels of the 72-column accumulator
   {
     const float* gs = p.ds_last ? p.ds_last + static_cast<size_t>(bh) * kD * kD : nullptr;
     const float* gz = p.dz_last ? p.dz_last + static_cast<size_t>(bh) * kD : nullptr;
-    float vals[kDX];   // all loads first: the TMEM stores below are compiler memory barriers
+    float vals[40];   // all loads first: the TMEM stores below are compiler memory barriers
 #pragma unroll
-    for (int vcol = 0; vcol < kDX; ++vcol) {
+    for (int i = 0; i < 40; ++i) {
+      const int vcol = gp0 * 8 + i;
       float x = 0.f;
-      if (upper) {
+      if (upper && i < gpn * 8) {
         if (vcol < kD) x = gs ? gs[vcol * kD + row] : 0.f;
         else if (vcol == kD) x = gz ? gz[row] : 0.f;
       }
-      vals[vcol] = x;
+      vals[i] = x;
     }
 #pragma unroll
-    for (int pn = 0; pn < kPanelsX; ++pn) {
-      tmem_st8(lane_base + kColHi + pn * 8, vals + pn * 8);
-      if (upper) sm.g[pn * kD + row] = pack8_bf16(vals + pn * 8);
+    for (int pn = 0; pn < 5; ++pn) {
+      if (pn < gpn) {
+        tmem_st8(lane_base + kColHi + (gp0 + pn) * 8, vals + pn * 8);
+        if (upper) sm.g[(gp0 + pn) * kD + row] = pack8_bf16(vals + pn * 8);
+      }
     }
     tmem_st_wait();
   }
@@ -150,31 +211,6 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
   const uint32_t id_mm = idesc_bf16(kC, kC, true, true);
   const uint32_t id_g = idesc_bf16(kD, kDX, true, true);
   bool timed_out = false;
-
-  // This thread's 16 vectors (q, k, v, dO of four tile positions) of chunk cc.
-  uint4 pre[16];
-  uint4 pre_s[5];   // this thread's share of the 576 vectors of S_in
-  auto prefetch = [&](int cc) {
-    const int base_t = cc * kC;
-    {
-      const uint4* src = p.chunk_states + (static_cast<size_t>(bh) * nchunks + cc) * (kPanelsX * kD);
-#pragma unroll
-      for (int i = 0; i < 5; ++i)
-        if (i * kThreads + tid < kPanelsX * kD) pre_s[i] = __ldg(src + i * kThreads + tid);
-    }
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      int trow, seg;
-      tile_vec(r * kThreads + tid, trow, seg);
-      const size_t g = seq_base + static_cast<size_t>(base_t + trow) * stride_t + seg * 8;
-      const bool in = base_t + trow < p.T;
-      pre[4 * r] = in ? __ldg(reinterpret_cast<const uint4*>(p.q + g)) : zero4;
-      pre[4 * r + 1] = in ? __ldg(reinterpret_cast<const uint4*>(p.k + g)) : zero4;
-      pre[4 * r + 2] = in ? __ldg(reinterpret_cast<const uint4*>(p.v + g)) : zero4;
-      pre[4 * r + 3] = in ? __ldg(reinterpret_cast<const uint4*>(p.d_o + g)) : zero4;
-    }
-  };
-  prefetch(nchunks - 1);
   uint32_t done_flags = load_done_flags(drow, (nchunks - 1) * kC, p.T, lane);
 #ifdef MXK_TIMING
   long long t_prev_ = clock64();
@@ -189,30 +225,31 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
     const bool has_reset = dm != 0ull;
     MXK_TB(0);
 
-    // ---- stage phi(Q), phi(K), V, dO (prefetched during the previous chunk), S_in ----
+    // ---- the tiles have landed: feature map in place; keep-masked copies of phi(K) and V|1
+    //      only if the chunk has a reset ----
+    if (!mbar_wait(&sm.bar_load, it & 1)) timed_out = true;
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
+    for (int r = 0; r < 2; ++r) {
       int trow, seg;
-      tile_vec(r * kThreads + tid, trow, seg);
-      uint4 qv = pre[4 * r], kv = pre[4 * r + 1];
-      const uint4 vv = pre[4 * r + 2], gv = pre[4 * r + 3];
-      if (p.feature_map && trow < valid) {
-        qv = phi8(qv);
-        kv = phi8(kv);
-      }
+      tile_vec(r * kBwdThreads + tid, trow, seg);
       const int slot = seg * kC + trow;
-      const bool keep = row_keep(dm, trow);
-      sm.q[slot] = qv;
-      sm.k[slot] = kv;
-      sm.kk[slot] = keep ? kv : zero4;
-      sm.v[slot] = vv;
-      sm.vk[slot] = keep ? vv : zero4;
-      sm.d_o[slot] = gv;
+      uint4 kv = sm.k[slot];
+      if (p.feature_map && trow < valid) {
+        sm.q[slot] = phi8(sm.q[slot]);
+        kv = phi8(kv);
+        sm.k[slot] = kv;
+      }
+      if (has_reset) {
+        const bool keep = row_keep(dm, trow);
+        sm.kk[slot] = keep ? kv : zero4;
+        sm.vk[slot] = keep ? sm.v[slot] : zero4;
+      }
     }
-    if (tid < kC) sm.vk[kPanels * kC + tid] = make_uint4((tid < valid && row_keep(dm, tid)) ? kOneBf16 : 0u, 0, 0, 0);
-#pragma unroll
-    for (int i = 0; i < 5; ++i)
-      if (i * kThreads + tid < kPanelsX * kD) sm.s[i * kThreads + tid] = pre_s[i];
+    if (tid < kC) {
+      const uint32_t one = tid < valid ? kOneBf16 : 0u;
+      sm.v[kPanels * kC + tid] = make_uint4(one, 0, 0, 0);
+      if (has_reset) sm.vk[kPanels * kC + tid] = make_uint4(row_keep(dm, tid) ? one : 0u, 0, 0, 0);
+    }
     fence_smem_to_async();
     fence_before_sync();
     MXK_TB(1);
@@ -238,17 +275,19 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
     fence_after_sync();
     MXK_TB(2);
 
-    // ---- epilogue 1: both half-warps own the same query row; each covers 32 keys / features ----
+    // ---- epilogue 1: the four threads of a query row (two half-warps x two warpgroups) each
+    //      cover 16 keys / state features; den and don are completed through shared memory ----
     {
       const bool live = row_live(dm, row);
       const int lo = row_first_key(dm, row);
-      const int j0 = upper ? 32 : 0, p0 = upper ? 4 : 0;
+      const int j0 = (upper ? 32 : 0) + wg * 16;   // first key / feature of this thread
+      const int p0 = j0 >> 3;                      // and its first panel
       float s_dot = 0.f, z_dot = 0.f;
       {
-        float rr[32];
-        tmem_ld_row<32>(lane_base + kColR, rr);
+        float rr[16];
+        tmem_ld_row<16>(lane_base + kColR + wg * 16, rr);
 #pragma unroll
-        for (int pp = 0; pp < 4; ++pp) {
+        for (int pp = 0; pp < 2; ++pp) {
           float fq[8];
           unpack8_bf16(sm.q[(p0 + pp) * kC + row], fq);
 #pragma unroll
@@ -259,12 +298,12 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
           }
         }
       }
-      float pv[32], av[32];
-      tmem_ld_row<32>(lane_base + kColP, pv);
-      tmem_ld_row<32>(lane_base + kColA, av);
+      float pv[16], av[16];
+      tmem_ld_row<16>(lane_base + kColP + wg * 16, pv);
+      tmem_ld_row<16>(lane_base + kColA + wg * 16, av);
       float den = live ? z_dot : 0.f, don = live ? s_dot : 0.f;
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
+      for (int e = 0; e < 16; ++e) {
         const int j = j0 + e;
         const bool m = (j >= lo && j <= row);
         pv[e] = m ? pv[e] : 0.f;
@@ -274,11 +313,18 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
       }
       den += __shfl_xor_sync(0xffffffffu, den, 16);
       don += __shfl_xor_sync(0xffffffffu, don, 16);
+      if (!upper) {
+        sm.xch[wg][0][row] = den;
+        sm.xch[wg][1][row] = don;
+      }
+      __syncthreads();
+      den += sm.xch[wg ^ 1][0][row];
+      don += sm.xch[wg ^ 1][1][row];
       const float dcl = fmaxf(den, p.eps);
       const float inv = 1.f / dcl;
       const float dden = den > p.eps ? -don * inv * inv : 0.f;
 #pragma unroll
-      for (int jq = 0; jq < 4; ++jq) {
+      for (int jq = 0; jq < 2; ++jq) {
         float a[8], d8[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
@@ -289,20 +335,17 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
         sm.pn[(p0 + jq) * kC + row] = pack8_bf16(a);
         sm.dp[(p0 + jq) * kC + row] = pack8_bf16(d8);
       }
-      // scaled dO rows: two panels per thread pair member (lower: panels 0..3, upper: 4..7 and the extra column)
-      {
-        const float sc = live ? inv : 0.f;
-        const int p0 = upper ? 4 : 0;
+      // scaled dO rows: two of the eight panels per thread, the extra column by one of the four
+      const float sc = live ? inv : 0.f;
 #pragma unroll
-        for (int pp = 0; pp < 4; ++pp) {
-          float f[8];
-          unpack8_bf16(sm.d_o[(p0 + pp) * kC + row], f);
+      for (int pp = 0; pp < 2; ++pp) {
+        float f[8];
+        unpack8_bf16(sm.d_o[(p0 + pp) * kC + row], f);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] *= sc;
-          sm.dos[(p0 + pp) * kC + row] = pack8_bf16(f);
-        }
-        if (upper) sm.dos[kPanels * kC + row] = make_uint4(pack_bf16(live ? dden : 0.f, 0.f), 0, 0, 0);
+        for (int e = 0; e < 8; ++e) f[e] *= sc;
+        sm.dos[(p0 + pp) * kC + row] = pack8_bf16(f);
       }
+      if (upper && wg == 1) sm.dos[kPanels * kC + row] = make_uint4(pack_bf16(live ? dden : 0.f, 0.f), 0, 0, 0);
     }
     fence_smem_to_async();
     fence_before_sync();
@@ -311,68 +354,80 @@ __global__ void __launch_bounds__(kThreads, 2) linattn_bwd_kernel(const BwdParam
 
     if (tid == 0) {
       fence_after_sync();
+      // without a reset every key is kept: the unmasked tiles serve as the "keep" operands
+      const uint32_t keep_k = smem_u32(has_reset ? sm.kk : sm.k), keep_v = smem_u32(has_reset ? sm.vk : sm.v);
       // dphiQ = dP phi(K) + dOs [S|z]                      (lower, columns 0..63)
       gemm(tmem + kColLo, Operand{smem_u32(sm.dp), kC, false}, Operand{smem_u32(sm.k), kC, true}, id_km, kC / 16, false);
       gemm(tmem + kColLo, Operand{smem_u32(sm.dos), kC, false}, Operand{smem_u32(sm.s), kD, false}, id_kk, 5, true);
       // dphiK = dP^T phi(Q) + keep[V|1] [G|gz]^T           (upper, columns 0..63)
       gemm(tmem + kUpper + kColLo, Operand{smem_u32(sm.dp), kC, true}, Operand{smem_u32(sm.q), kC, true}, id_mm, kC / 16, false);
-      gemm(tmem + kUpper + kColLo, Operand{smem_u32(sm.vk), kC, false}, Operand{smem_u32(sm.g), kD, false}, id_kk, 5, true);
+      gemm(tmem + kUpper + kColLo, Operand{keep_v, kC, false}, Operand{smem_u32(sm.g), kD, false}, id_kk, 5, true);
       // dV = (P/D)^T dO + keep phi(K) G^T                  (lower, columns 64..127)
       gemm(tmem + kColHi, Operand{smem_u32(sm.pn), kC, true}, Operand{smem_u32(sm.d_o), kC, true}, id_mm, kC / 16, false);
-      gemm(tmem + kColHi, Operand{smem_u32(sm.kk), kC, false}, Operand{smem_u32(sm.g), kD, true}, id_km, kD / 16, true);
+      gemm(tmem + kColHi, Operand{keep_k, kC, false}, Operand{smem_u32(sm.g), kD, true}, id_km, kD / 16, true);
       // [G|gz]^T = [no reset][G|gz]^T + phi(Q)^T dOs       (upper, columns 64..135)
       gemm(tmem + kUpper + kColHi, Operand{smem_u32(sm.q), kC, true}, Operand{smem_u32(sm.dos), kC, true}, id_g, kC / 16, !has_reset);
       commit(&sm.bar[1]);
     }
-    if (c > 0) prefetch(c - 1);   // in flight while the MMAs and the output epilogue run
     if (!mbar_wait(&sm.bar[1], it & 1)) timed_out = true;
     fence_after_sync();
+    if (tid == 0 && c > 0) issue_state_loads(c - 1);   // in flight while the output epilogue runs
     MXK_TB(4);
 
-    // ---- epilogue 2 ----
+    // ---- epilogue 2: every thread owns 32 (36, 40) columns of its row ----
     {
-      // one stream: lower chains dphiQ through phi'(q) into dq, upper dphiK through phi'(k) into dk.
       // Output rows leave through per-warp staging areas (buffers the finished MMAs no longer
-      // need) so that every store instruction writes complete 128-byte rows.
-      const int rows_valid = valid - warp * 16;
-      __nv_bfloat16* const gq = p.dq + seq_base + static_cast<size_t>(t0 + warp * 16) * stride_t;
-      __nv_bfloat16* const gk = p.dk + seq_base + static_cast<size_t>(t0 + warp * 16) * stride_t;
-      __nv_bfloat16* const gv = p.dv + seq_base + static_cast<size_t>(t0 + warp * 16) * stride_t;
+      // need) so that every store instruction writes complete 64-byte half rows.
+      const int rows_valid = valid - qw * 16;
+      const int c0 = wg * 32;
+      const size_t out_off = seq_base + static_cast<size_t>(t0 + qw * 16) * stride_t + c0;
       {
-        float acc[kD];
-        tmem_ld_row<kD>(lane_base + kColLo, acc);
+        // one stream: lower chains dphiQ through phi'(q) into dq, upper dphiK through phi'(k) into dk
+        float acc[32];
+        tmem_ld_row<32>(lane_base + kColLo + c0, acc);
         const uint4* feat = upper ? &sm.k[row] : &sm.q[row];
-        uint4 packed[kPanels];
+        uint4 packed[4];
 #pragma unroll
-        for (int pn = 0; pn < kPanels; ++pn) {
+        for (int pn = 0; pn < 4; ++pn) {
           float f[8];
-          unpack8_bf16(feat[pn * kC], f);
+          unpack8_bf16(feat[(wg * 4 + pn) * kC], f);
 #pragma unroll
           for (int e = 0; e < 8; ++e) f[e] = acc[pn * 8 + e] * ((p.feature_map && f[e] <= 1.f) ? f[e] : 1.f);
           packed[pn] = pack8_bf16(f);
         }
-        store_rows_coalesced(sm.dos + warp * (16 * 9), packed, !upper, lane, gq, stride_t, rows_valid);
-        store_rows_coalesced(sm.vk + warp * (16 * 9), packed, upper, lane, gk, stride_t, rows_valid);
+        __syncthreads();   // phi(Q), phi(K) have been read by everyone: their buffers can be refilled
+        if (tid == 0 && c > 0) issue_qk_loads(c - 1);
+        store_half_rows(sm.dos + warp * 80, packed, !upper, lane, p.dq + out_off, stride_t, rows_valid);
+        store_half_rows(sm.vk + warp * 80, packed, upper, lane, p.dk + out_off, stride_t, rows_valid);
       }
       // one stream: lower stores dV, upper refreshes the bf16 operand copy of G | gz
       {
-        float acc[kDX];
-        tmem_ld_row<kDX>(lane_base + kColHi, acc);
-        uint4 packed[kPanelsX];
+        float acc[40];
+        if (wg == 0) tmem_ld_row<32>(lane_base + kColHi, acc);
+        else tmem_ld_row<40>(lane_base + kColHi + 32, acc);
+        uint4 packed[5];
 #pragma unroll
-        for (int pn = 0; pn < kPanelsX; ++pn) packed[pn] = pack8_bf16(acc + pn * 8);
+        for (int pn = 0; pn < 5; ++pn)
+          if (pn < gpn) packed[pn] = pack8_bf16(acc + pn * 8);
         if (upper) {
 #pragma unroll
-          for (int pn = 0; pn < kPanelsX; ++pn) sm.g[pn * kD + row] = packed[pn];
+          for (int pn = 0; pn < 5; ++pn)
+            if (pn < gpn) sm.g[(gp0 + pn) * kD + row] = packed[pn];
         }
-        store_rows_coalesced(sm.pn + warp * (16 * 9), packed, !upper, lane, gv, stride_t, rows_valid);   // pn, dp: one 16 KB region
+        store_half_rows(sm.pn + warp * 80, packed, !upper, lane, p.dv + out_off, stride_t, rows_valid);   // pn, dp: one 16 KB region
         if (upper && c == 0) {
-          if (p.ds0) {
-            float* out = p.ds0 + static_cast<size_t>(bh) * kD * kD;
+          float* out = p.ds0 ? p.ds0 + static_cast<size_t>(bh) * kD * kD : nullptr;
 #pragma unroll
-            for (int vcol = 0; vcol < kD; ++vcol) out[vcol * kD + row] = acc[vcol];
+          for (int i = 0; i < 40; ++i) {
+            const int vcol = gp0 * 8 + i;
+            if (i < gpn * 8) {
+              if (vcol < kD) {
+                if (out) out[vcol * kD + row] = acc[i];
+              } else if (vcol == kD && p.dz0) {
+                p.dz0[static_cast<size_t>(bh) * kD + row] = acc[i];
+              }
+            }
           }
-          if (p.dz0) p.dz0[static_cast<size_t>(bh) * kD + row] = acc[kD];
         }
       }
     }
@@ -433,10 +488,13 @@ int mxk_linattn_bf16_bwd(const void* q, const void* k, const void* v, const void
   prm.B = B; prm.T = T; prm.H = H;
   prm.eps = eps;
   prm.feature_map = feature_map;
+  if (!tma::make_panel_map(&prm.map_q, q, B, T, H, kD, kC) || !tma::make_panel_map(&prm.map_k, k, B, T, H, kD, kC) ||
+      !tma::make_panel_map(&prm.map_v, v, B, T, H, kD, kC) || !tma::make_panel_map(&prm.map_do, d_o, B, T, H, kD, kC))
+    return MXK_ERR_UNSUPPORTED;
   cudaError_t e = cudaFuncSetAttribute(linattn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(BwdSmem)));
   if (e != cudaSuccess) return static_cast<int>(e);
-  linattn_bwd_kernel<<<B * H, kThreads, sizeof(BwdSmem), static_cast<cudaStream_t>(stream)>>>(prm);
+  linattn_bwd_kernel<<<B * H, kBwdThreads, sizeof(BwdSmem), static_cast<cudaStream_t>(stream)>>>(prm);
   return launch_status();
 }
 
