@@ -63,7 +63,7 @@ static_assert(sizeof(FwdSmem) <= 55 * 1024, "four CTAs per SM");
 // ("upper" threads, one key-feature row each).
 #ifdef MXK_TIMING
 }  // namespace
-__device__ unsigned long long g_phase_cycles[8];
+__device__ unsigned long long g_phase_cycles[16];
 namespace {
 #define MXK_T(i) do { if (tid == 0 && (blockIdx.x % 37) == 0) { const long long now_ = clock64(); atomicAdd(&g_phase_cycles[i], (unsigned long long)(now_ - t_prev_)); t_prev_ = now_; } } while (0)
 #else
@@ -155,6 +155,7 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
     // ---- the tiles have landed: feature map in place, keep-masked copy of V only if the
     //      chunk has a reset ----
     if (!mbar_wait(&sm.bar_load, c & 1)) timed_out = true;
+    MXK_T(8);
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
       int trow, seg;
@@ -288,10 +289,10 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
 #ifdef MXK_TIMING
 extern "C" int mxk_debug_phase_cycles(unsigned long long* out, int reset) {
   if (reset) {
-    unsigned long long z[8] = {};
+    unsigned long long z[16] = {};
     return (int)cudaMemcpyToSymbol(mxk::g_phase_cycles, z, sizeof(z));
   }
-  return (int)cudaMemcpyFromSymbol(out, mxk::g_phase_cycles, 8 * sizeof(unsigned long long));
+  return (int)cudaMemcpyFromSymbol(out, mxk::g_phase_cycles, 16 * sizeof(unsigned long long));
 }
 #endif
 

@@ -8,7 +8,6 @@
 // thread fetches a whole rows x D tile in tensor-core operand order, zero-filling
 // rows past the end of the sequence.  The innermost coordinate is always 0, so the
 // 16-byte alignment rule of TMA copies holds by construction.
-// No load here uses cluster multicast.
 #pragma once
 
 #include <cuda.h>
