@@ -139,13 +139,14 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_co
     fence_before_sync();
     __syncthreads();
 
-    if (tid == 0) {
+    if (warp == 0) {
+      const bool leader = elect_one();
       fence_after_sync();
       const Operand ak{smem_u32(sm.k), kC, false}, aq{smem_u32(sm.q), kC, false}, as{smem_u32(sm.s), kD, false};
-      gemm(tmem + kColKQ, ak, ak, id_64, kD / 16, false);              // K K^T -> lower lanes
-      gemm(tmem + kUpper + kColKQ, aq, ak, id_64, kD / 16, false);     // Q K^T -> upper lanes
-      gemm(tmem + kColY, as, ak, id_128x64, kD / 16, false);           // Y^T = S_in K^T
-      commit(&sm.bar[0]);
+      gemm<kD / 16>(tmem + kColKQ, ak, ak, id_64, false, leader);              // K K^T -> lower lanes
+      gemm<kD / 16>(tmem + kUpper + kColKQ, aq, ak, id_64, false, leader);     // Q K^T -> upper lanes
+      gemm<kD / 16>(tmem + kColY, as, ak, id_128x64, false, leader);           // Y^T = S_in K^T
+      if (leader) commit(&sm.bar[0]);
     }
     if (!mbar_wait(&sm.bar[0], c & 1)) timed_out = true;
     fence_after_sync();
@@ -222,14 +223,15 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_co
     fence_before_sync();
     __syncthreads();
 
-    if (tid == 0) {
+    if (warp == 0) {
+      const bool leader = elect_one();
       fence_after_sync();
       const Operand as{smem_u32(sm.s), kD, false}, bgq{smem_u32(sm.q), kC, false};
       const Operand au{smem_u32(sm.vu), kD, false}, bp{smem_u32(sm.p), kC, false}, bgk{smem_u32(sm.k), kC, true};
-      gemm(tmem + kColO, as, bgq, id_128x64, kD / 16, false);   // O^T  = S_in (g Q)^T
-      gemm(tmem + kColO, au, bp, id_128x64, kC / 16, true);     // O^T += U^T P^T
-      gemm(tmem + kColS, au, bgk, id_ds, kC / 16, true);        // S    = g_last S_in + U^T (gam K)
-      commit(&sm.bar[1]);
+      gemm<kD / 16>(tmem + kColO, as, bgq, id_128x64, false, leader);   // O^T  = S_in (g Q)^T
+      gemm<kC / 16>(tmem + kColO, au, bp, id_128x64, true, leader);     // O^T += U^T P^T
+      gemm<kC / 16>(tmem + kColS, au, bgk, id_ds, true, leader);        // S    = g_last S_in + U^T (gam K)
+      if (leader) commit(&sm.bar[1]);
     }
     if (!mbar_wait(&sm.bar[1], c & 1)) timed_out = true;
     fence_after_sync();

@@ -215,7 +215,8 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
 
     MXK_TG(1);
     // ---- MMAs A: K K^T, Q K^T, Y^T = S_in K^T, OI^T = S_in Q^T, X2^T = dS K^T ----
-    if (tid == 0) {
+    if (warp == 0) {
+      const bool leader = elect_one();
       fence_after_sync();
       const Operand ak{smem_u32(sm.k), kC, false}, aq{smem_u32(sm.q), kC, false};
       const Operand as{smem_u32(sm.s), kD, false}, ads{smem_u32(sm.ds), kD, false};
@@ -225,14 +226,14 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
       // work on the same token row in the epilogues
       const Operand bk_lo{smem_u32(sm.k), kC, false}, bk_hi{smem_u32(sm.k) + 32 * 16, kC, false};
       const uint32_t id_half = idesc_bf16(kC, 32, false, false);
-      gemm(tmem + kColKK, ak, bk_lo, id_half, kD / 16, false);
-      gemm(tmem + kUpper + kColKK, ak, bk_hi, id_half, kD / 16, false);
-      gemm(tmem + kColQK, aq, bk_lo, id_half, kD / 16, false);
-      gemm(tmem + kUpper + kColQK, aq, bk_hi, id_half, kD / 16, false);
-      gemm(tmem + kColY, as, ak, id_128, kD / 16, false);
-      gemm(tmem + kColOI, as, aq, id_128, kD / 16, false);
-      gemm(tmem + kColX2, ads, ak, id_128, kD / 16, false);
-      commit(&sm.bar[0]);
+      gemm<kD / 16>(tmem + kColKK, ak, bk_lo, id_half, false, leader);
+      gemm<kD / 16>(tmem + kUpper + kColKK, ak, bk_hi, id_half, false, leader);
+      gemm<kD / 16>(tmem + kColQK, aq, bk_lo, id_half, false, leader);
+      gemm<kD / 16>(tmem + kUpper + kColQK, aq, bk_hi, id_half, false, leader);
+      gemm<kD / 16>(tmem + kColY, as, ak, id_128, false, leader);
+      gemm<kD / 16>(tmem + kColOI, as, aq, id_128, false, leader);
+      gemm<kD / 16>(tmem + kColX2, ads, ak, id_128, false, leader);
+      if (leader) commit(&sm.bar[0]);
     }
     if (!mbar_wait(&sm.bar[0], 0)) timed_out = true;
     fence_after_sync();
@@ -280,15 +281,13 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
 
     MXK_TG(3);
     // ---- MMAs B: X1^T = dO^T P (128 x 64), DP = dO U^T (64 x 64) ----
-    if (tid == 0) {
+    if (warp == 0) {
+      const bool leader = elect_one();
       fence_after_sync();
-      gemm(tmem + kColX1, Operand{smem_u32(sm.d_o), kC, true}, Operand{smem_u32(sm.p), kC, true},
-           idesc_bf16(kD, kC, true, true), kC / 16, false);
-      gemm(tmem + kColDP, Operand{smem_u32(sm.d_o), kC, false}, Operand{smem_u32(sm.u), kD, true},
-           idesc_bf16(kC, 32, false, true), kD / 16, false);
-      gemm(tmem + kUpper + kColDP, Operand{smem_u32(sm.d_o), kC, false}, Operand{smem_u32(sm.u) + 4 * kD * 16, kD, true},
-           idesc_bf16(kC, 32, false, true), kD / 16, false);
-      commit(&sm.bar[1]);
+      gemm<kC / 16>(tmem + kColX1, Operand{smem_u32(sm.d_o), kC, true}, Operand{smem_u32(sm.p), kC, true}, idesc_bf16(kD, kC, true, true), false, leader);
+      gemm<kD / 16>(tmem + kColDP, Operand{smem_u32(sm.d_o), kC, false}, Operand{smem_u32(sm.u), kD, true}, idesc_bf16(kC, 32, false, true), false, leader);
+      gemm<kD / 16>(tmem + kUpper + kColDP, Operand{smem_u32(sm.d_o), kC, false}, Operand{smem_u32(sm.u) + 4 * kD * 16, kD, true}, idesc_bf16(kC, 32, false, true), false, leader);
+      if (leader) commit(&sm.bar[1]);
     }
     if (!mbar_wait(&sm.bar[1], 0)) timed_out = true;
     fence_after_sync();
@@ -381,13 +380,12 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
 
     MXK_TG(5);
     // ---- MMA C: W = dUt U^T (64 x 64) ----
-    if (tid == 0) {
+    if (warp == 0) {
+      const bool leader = elect_one();
       fence_after_sync();
-      gemm(tmem + kColW, Operand{smem_u32(sm.r1), kD, true}, Operand{smem_u32(sm.u), kD, true},
-           idesc_bf16(kC, 32, true, true), kD / 16, false);
-      gemm(tmem + kUpper + kColW, Operand{smem_u32(sm.r1), kD, true}, Operand{smem_u32(sm.u) + 4 * kD * 16, kD, true},
-           idesc_bf16(kC, 32, true, true), kD / 16, false);
-      commit(&sm.bar[0]);
+      gemm<kD / 16>(tmem + kColW, Operand{smem_u32(sm.r1), kD, true}, Operand{smem_u32(sm.u), kD, true}, idesc_bf16(kC, 32, true, true), false, leader);
+      gemm<kD / 16>(tmem + kUpper + kColW, Operand{smem_u32(sm.r1), kD, true}, Operand{smem_u32(sm.u) + 4 * kD * 16, kD, true}, idesc_bf16(kC, 32, true, true), false, leader);
+      if (leader) commit(&sm.bar[0]);
     }
     if (!mbar_wait(&sm.bar[0], 1)) timed_out = true;
     fence_after_sync();
@@ -451,7 +449,8 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
 
     MXK_TG(7);
     // ---- MMAs D: dQ, dK (64 x 128), dS_in increment (128 x 128) ----
-    if (tid == 0) {
+    if (warp == 0) {
+      const bool leader = elect_one();
       fence_after_sync();
       const uint4* dpg_p = reinterpret_cast<const uint4*>(sm.lt);
       const uint32_t dpg = smem_u32(dpg_p), dlg = smem_u32(dpg_p + kPanC * kC);
@@ -459,18 +458,18 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
       const Operand bs{smem_u32(sm.s), kD, true}, bds{smem_u32(sm.ds), kD, true};
       const uint32_t id_km = idesc_bf16(kC, kD, false, true), id_mm = idesc_bf16(kC, kD, true, true);
       // dQ = (dP o G) K + (g dO) S_in
-      gemm(tmem + kColDQ, Operand{dpg, kC, false}, bk, id_km, kC / 16, false);
-      gemm(tmem + kColDQ, Operand{smem_u32(sm.d_o), kC, false}, bs, id_km, kD / 16, true);
+      gemm<kC / 16>(tmem + kColDQ, Operand{dpg, kC, false}, bk, id_km, false, leader);
+      gemm<kD / 16>(tmem + kColDQ, Operand{smem_u32(sm.d_o), kC, false}, bs, id_km, true, leader);
       // dK = (dP o G)^T Q + (dL o G) K + (dL o G)^T K + (gam U) dS - (g dR) S_in
-      gemm(tmem + kColDK, Operand{dpg, kC, true}, bq, id_mm, kC / 16, false);
-      gemm(tmem + kColDK, Operand{dlg, kC, false}, bk, id_km, kC / 16, true);
-      gemm(tmem + kColDK, Operand{dlg, kC, true}, bk, id_mm, kC / 16, true);
-      gemm(tmem + kColDK, Operand{smem_u32(sm.ug), kD, true}, bds, id_mm, kD / 16, true);
-      gemm(tmem + kColDK, Operand{smem_u32(sm.r2), kD, true}, bs, id_mm, kD / 16, true);
+      gemm<kC / 16>(tmem + kColDK, Operand{dpg, kC, true}, bq, id_mm, false, leader);
+      gemm<kC / 16>(tmem + kColDK, Operand{dlg, kC, false}, bk, id_km, true, leader);
+      gemm<kC / 16>(tmem + kColDK, Operand{dlg, kC, true}, bk, id_mm, true, leader);
+      gemm<kD / 16>(tmem + kColDK, Operand{smem_u32(sm.ug), kD, true}, bds, id_mm, true, leader);
+      gemm<kD / 16>(tmem + kColDK, Operand{smem_u32(sm.r2), kD, true}, bs, id_mm, true, leader);
       // dS_in - g_last dS = (g dO)^T Q - (g dR)^T K
-      gemm(tmem + kColDelta, Operand{smem_u32(sm.d_o), kC, true}, bq, idesc_bf16(kD, kD, true, true), kC / 16, false);
-      gemm(tmem + kColDelta, Operand{smem_u32(sm.r2), kD, false}, bk, idesc_bf16(kD, kD, false, true), kC / 16, true);
-      commit(&sm.bar[1]);
+      gemm<kC / 16>(tmem + kColDelta, Operand{smem_u32(sm.d_o), kC, true}, bq, idesc_bf16(kD, kD, true, true), false, leader);
+      gemm<kC / 16>(tmem + kColDelta, Operand{smem_u32(sm.r2), kD, false}, bk, idesc_bf16(kD, kD, false, true), true, leader);
+      if (leader) commit(&sm.bar[1]);
     }
 
     // ---- decay gradients (overlaps the MMAs) ----

@@ -179,15 +179,16 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
     __syncthreads();
     MXK_T(2);
 
-    if (tid == 0) {
+    if (warp == 0) {
+      const bool leader = elect_one();
       fence_after_sync();
       const Operand aq{smem_u32(sm.q), kC, false}, bk{smem_u32(sm.k), kC, false}, ak{smem_u32(sm.k), kC, true};
       const Operand bvk{smem_u32(has_reset ? sm.alt : sm.v), kC, true};
-      gemm(tmem, aq, bk, idesc_p, kD / 16, false);                           // P        -> lower lanes
-      gemm(tmem + kUpper, ak, bvk, idesc_s, kC / 16, !has_reset);            // S^T | z  -> upper lanes
-      commit(&sm.bar[0]);
+      gemm<kD / 16>(tmem, aq, bk, idesc_p, false, leader);                           // P        -> lower lanes
+      gemm<kC / 16>(tmem + kUpper, ak, bvk, idesc_s, !has_reset, leader);            // S^T | z  -> upper lanes
+      if (leader) commit(&sm.bar[0]);
       // residual for the backward pass: the state entering this chunk
-      if (p.chunk_states) {
+      if (p.chunk_states && tid == 0) {
         tma::store_bulk(p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * (kPanelsX * kD), sm.s[cur],
                         kPanelsX * kD * 16);
         tma::commit_group();
@@ -240,13 +241,14 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
     __syncthreads();
     MXK_T(5);
 
-    if (tid == 0) {
+    if (warp == 0) {
+      const bool leader = elect_one();
       fence_after_sync();
       const Operand aql{smem_u32(has_reset ? sm.alt : sm.q), kC, false}, bs{smem_u32(sm.s[cur]), kD, true};
       const Operand ap{smem_u32(sm.k), kC, false}, bv{smem_u32(sm.v), kC, true};
-      gemm(tmem, aql, bs, idesc_o, kD / 16, false);     // O  = live(phi(Q)) S_in^T
-      gemm(tmem, ap, bv, idesc_o, kC / 16, true);       // O += mask(P) (V|1)
-      commit(&sm.bar[1]);
+      gemm<kD / 16>(tmem, aql, bs, idesc_o, false, leader);     // O  = live(phi(Q)) S_in^T
+      gemm<kC / 16>(tmem, ap, bv, idesc_o, true, leader);       // O += mask(P) (V|1)
+      if (leader) commit(&sm.bar[1]);
     }
     if (!mbar_wait(&sm.bar[1], c & 1)) timed_out = true;
     fence_after_sync();

@@ -87,7 +87,7 @@ static_assert(sizeof(BwdSmem) <= 113 * 1024, "two CTAs per SM");
 // Within a half-warp's 32 columns, warpgroup 0 takes the first 16 and warpgroup 1 the rest.
 #ifdef MXK_TIMING
 }  // namespace
-__device__ unsigned long long g_bwd_phase_cycles[8];
+__device__ unsigned long long g_bwd_phase_cycles[16];
 namespace {
 #define MXK_TB(i) do { if (tid == 0 && (blockIdx.x % 37) == 0) { const long long now_ = clock64(); atomicAdd(&g_bwd_phase_cycles[i], (unsigned long long)(now_ - t_prev_)); t_prev_ = now_; } } while (0)
 #else
@@ -254,8 +254,10 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
     fence_before_sync();
     MXK_TB(1);
     __syncthreads();
+    MXK_TB(7);
 
-    if (tid == 0) {
+    if (warp == 0) {
+      const bool leader = elect_one();
       fence_after_sync();
       const Operand aq{smem_u32(sm.q), kC, false}, bk{smem_u32(sm.k), kC, false};
       const Operand ado{smem_u32(sm.d_o), kC, false}, bv{smem_u32(sm.v), kC, false};
@@ -263,14 +265,15 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
       const uint32_t id_half = idesc_bf16(kC, 32, false, false);
       const Operand bk_hi{smem_u32(sm.k) + 32 * 16, kC, false}, bv_hi{smem_u32(sm.v) + 32 * 16, kC, false};
       const Operand bs_hi{smem_u32(sm.s) + 32 * 16, kD, false};
-      gemm(tmem + kColP, aq, bk, id_half, kD / 16, false);                 // P,  keys 0..31
-      gemm(tmem + kUpper + kColP, aq, bk_hi, id_half, kD / 16, false);     // P,  keys 32..63
-      gemm(tmem + kColA, ado, bv, id_half, kD / 16, false);                // dA, keys 0..31
-      gemm(tmem + kUpper + kColA, ado, bv_hi, id_half, kD / 16, false);    // dA, keys 32..63
-      gemm(tmem + kColR, ado, bs, id_half, kD / 16, false);                // R,  features 0..31
-      gemm(tmem + kUpper + kColR, ado, bs_hi, id_half, kD / 16, false);    // R,  features 32..63
-      commit(&sm.bar[0]);
+      gemm<kD / 16>(tmem + kColP, aq, bk, id_half, false, leader);                 // P,  keys 0..31
+      gemm<kD / 16>(tmem + kUpper + kColP, aq, bk_hi, id_half, false, leader);     // P,  keys 32..63
+      gemm<kD / 16>(tmem + kColA, ado, bv, id_half, false, leader);                // dA, keys 0..31
+      gemm<kD / 16>(tmem + kUpper + kColA, ado, bv_hi, id_half, false, leader);    // dA, keys 32..63
+      gemm<kD / 16>(tmem + kColR, ado, bs, id_half, false, leader);                // R,  features 0..31
+      gemm<kD / 16>(tmem + kUpper + kColR, ado, bs_hi, id_half, false, leader);    // R,  features 32..63
+      if (leader) commit(&sm.bar[0]);
     }
+    MXK_TB(8);
     if (!mbar_wait(&sm.bar[0], it & 1)) timed_out = true;
     fence_after_sync();
     MXK_TB(2);
@@ -351,24 +354,27 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
     fence_before_sync();
     MXK_TB(3);
     __syncthreads();
+    MXK_TB(9);
 
-    if (tid == 0) {
+    if (warp == 0) {
+      const bool leader = elect_one();
       fence_after_sync();
       // without a reset every key is kept: the unmasked tiles serve as the "keep" operands
       const uint32_t keep_k = smem_u32(has_reset ? sm.kk : sm.k), keep_v = smem_u32(has_reset ? sm.vk : sm.v);
       // dphiQ = dP phi(K) + dOs [S|z]                      (lower, columns 0..63)
-      gemm(tmem + kColLo, Operand{smem_u32(sm.dp), kC, false}, Operand{smem_u32(sm.k), kC, true}, id_km, kC / 16, false);
-      gemm(tmem + kColLo, Operand{smem_u32(sm.dos), kC, false}, Operand{smem_u32(sm.s), kD, false}, id_kk, 5, true);
+      gemm<kC / 16>(tmem + kColLo, Operand{smem_u32(sm.dp), kC, false}, Operand{smem_u32(sm.k), kC, true}, id_km, false, leader);
+      gemm<5>(tmem + kColLo, Operand{smem_u32(sm.dos), kC, false}, Operand{smem_u32(sm.s), kD, false}, id_kk, true, leader);
       // dphiK = dP^T phi(Q) + keep[V|1] [G|gz]^T           (upper, columns 0..63)
-      gemm(tmem + kUpper + kColLo, Operand{smem_u32(sm.dp), kC, true}, Operand{smem_u32(sm.q), kC, true}, id_mm, kC / 16, false);
-      gemm(tmem + kUpper + kColLo, Operand{keep_v, kC, false}, Operand{smem_u32(sm.g), kD, false}, id_kk, 5, true);
+      gemm<kC / 16>(tmem + kUpper + kColLo, Operand{smem_u32(sm.dp), kC, true}, Operand{smem_u32(sm.q), kC, true}, id_mm, false, leader);
+      gemm<5>(tmem + kUpper + kColLo, Operand{keep_v, kC, false}, Operand{smem_u32(sm.g), kD, false}, id_kk, true, leader);
       // dV = (P/D)^T dO + keep phi(K) G^T                  (lower, columns 64..127)
-      gemm(tmem + kColHi, Operand{smem_u32(sm.pn), kC, true}, Operand{smem_u32(sm.d_o), kC, true}, id_mm, kC / 16, false);
-      gemm(tmem + kColHi, Operand{keep_k, kC, false}, Operand{smem_u32(sm.g), kD, true}, id_km, kD / 16, true);
+      gemm<kC / 16>(tmem + kColHi, Operand{smem_u32(sm.pn), kC, true}, Operand{smem_u32(sm.d_o), kC, true}, id_mm, false, leader);
+      gemm<kD / 16>(tmem + kColHi, Operand{keep_k, kC, false}, Operand{smem_u32(sm.g), kD, true}, id_km, true, leader);
       // [G|gz]^T = [no reset][G|gz]^T + phi(Q)^T dOs       (upper, columns 64..135)
-      gemm(tmem + kUpper + kColHi, Operand{smem_u32(sm.q), kC, true}, Operand{smem_u32(sm.dos), kC, true}, id_g, kC / 16, !has_reset);
-      commit(&sm.bar[1]);
+      gemm<kC / 16>(tmem + kUpper + kColHi, Operand{smem_u32(sm.q), kC, true}, Operand{smem_u32(sm.dos), kC, true}, id_g, !has_reset, leader);
+      if (leader) commit(&sm.bar[1]);
     }
+    MXK_TB(10);
     if (!mbar_wait(&sm.bar[1], it & 1)) timed_out = true;
     fence_after_sync();
     if (tid == 0 && c > 0) issue_state_loads(c - 1);   // in flight while the output epilogue runs
@@ -448,10 +454,10 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
 #ifdef MXK_TIMING
 extern "C" int mxk_debug_bwd_phase_cycles(unsigned long long* out, int reset) {
   if (reset) {
-    unsigned long long z[8] = {};
+    unsigned long long z[16] = {};
     return (int)cudaMemcpyToSymbol(mxk::g_bwd_phase_cycles, z, sizeof(z));
   }
-  return (int)cudaMemcpyFromSymbol(out, mxk::g_bwd_phase_cycles, 8 * sizeof(unsigned long long));
+  return (int)cudaMemcpyFromSymbol(out, mxk::g_bwd_phase_cycles, 16 * sizeof(unsigned long long));
 }
 #endif
 
