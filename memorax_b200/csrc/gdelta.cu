@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_co
   };
   if (tid == 0) issue_chunk_loads(0);
   float2 ab_next = fetch_chunk_decay(p.alpha, p.beta, bt_base, p.H, h, 0, p.T, tid);
-  uint32_t flags_next = linattn::load_done_flags(drow, 0, p.T, lane);
+  linattn::DoneFlags flags_next = linattn::load_done_flags(drow, 0, p.T, lane);
 
   for (int c = 0; c < nchunks; ++c) {
     const int t0 = c * kC;

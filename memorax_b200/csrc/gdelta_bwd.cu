@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
 
   if (tid == 0) issue_chunk_loads(sm, p, b, h, nchunks - 1, nchunks);
   float2 ab_next = fetch_chunk_decay(p.alpha, p.beta, bt_base, p.H, h, (nchunks - 1) * kC, p.T, tid);
-  uint32_t flags_next = linattn::load_done_flags(drow, (nchunks - 1) * kC, p.T, lane);
+  linattn::DoneFlags flags_next = linattn::load_done_flags(drow, (nchunks - 1) * kC, p.T, lane);
   // cotangent of the next carry: thread (v, wg) owns dS[v][64 wg .. 64 wg + 63]
   {
     const float* g0 = p.ds_last ? p.ds_last + (static_cast<size_t>(bh) * kD + vt) * kD + wg * 64 : nullptr;

@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
 #ifdef MXK_TIMING
   long long t_prev_ = clock64();
 #endif
-  uint32_t done_flags = load_done_flags(drow, 0, p.T, lane);
+  DoneFlags done_flags = load_done_flags(drow, 0, p.T, lane);
 
   for (int c = 0; c < nchunks; ++c) {
     const int t0 = c * kC;

@@ -211,7 +211,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
   const uint32_t id_mm = idesc_bf16(kC, kC, true, true);
   const uint32_t id_g = idesc_bf16(kD, kDX, true, true);
   bool timed_out = false;
-  uint32_t done_flags = load_done_flags(drow, (nchunks - 1) * kC, p.T, lane);
+  DoneFlags done_flags = load_done_flags(drow, (nchunks - 1) * kC, p.T, lane);
 #ifdef MXK_TIMING
   long long t_prev_ = clock64();
 #endif

@@ -41,19 +41,25 @@ __device__ __forceinline__ uint64_t chunk_done_mask(const uint8_t* drow, int t0,
   const unsigned hi = __ballot_sync(0xffffffffu, tb < T && drow[tb] != 0);
   return (static_cast<uint64_t>(hi) << 32) | lo;
 }
-// The same in two steps, so that the byte loads of a later chunk can be issued
-// long before their values are needed: bit 0 / bit 1 = flags of tokens t0+lane / t0+32+lane.
-__device__ __forceinline__ uint32_t load_done_flags(const uint8_t* drow, int t0, int T, int lane) {
-  if (!drow || t0 < 0) return 0u;
-  const int ta = t0 + lane, tb = t0 + 32 + lane;
-  uint32_t f = 0u;
-  if (ta < T) f |= drow[ta] != 0 ? 1u : 0u;
-  if (tb < T) f |= drow[tb] != 0 ? 2u : 0u;
+// The same in two steps, so that the byte loads of a later chunk can be issued long
+// before their values are needed.  The loaded bytes stay untouched in registers until
+// done_mask_from_flags(): any arithmetic on them at load time would make the in-order
+// thread wait for the loads right there.
+struct DoneFlags {
+  uint32_t a, b;   // raw flag bytes of tokens t0 + lane and t0 + 32 + lane (0 when out of range)
+};
+__device__ __forceinline__ DoneFlags load_done_flags(const uint8_t* drow, int t0, int T, int lane) {
+  DoneFlags f{0u, 0u};
+  if (drow && t0 >= 0) {
+    const int ta = t0 + lane, tb = t0 + 32 + lane;
+    if (ta < T) f.a = drow[ta];
+    if (tb < T) f.b = drow[tb];
+  }
   return f;
 }
-__device__ __forceinline__ uint64_t done_mask_from_flags(uint32_t f) {
-  const unsigned lo = __ballot_sync(0xffffffffu, (f & 1u) != 0u);
-  const unsigned hi = __ballot_sync(0xffffffffu, (f & 2u) != 0u);
+__device__ __forceinline__ uint64_t done_mask_from_flags(DoneFlags f) {
+  const unsigned lo = __ballot_sync(0xffffffffu, f.a != 0u);
+  const unsigned hi = __ballot_sync(0xffffffffu, f.b != 0u);
   return (static_cast<uint64_t>(hi) << 32) | lo;
 }
 __device__ __forceinline__ bool row_live(uint64_t dm, int i) { return (dm & ((2ull << i) - 1ull)) == 0ull; }
