@@ -17,6 +17,8 @@
 // the last reset ("keep") reach the outgoing state.
 #include <cuda_bf16.h>
 
+#include <cstddef>
+
 #include "mxk_common.cuh"
 #include "linattn_common.cuh"
 #include "tma.cuh"
@@ -42,20 +44,22 @@ struct FwdParams {
   int B, T, H;
   float eps;
   int feature_map;
-  CUtensorMap map_q, map_k, map_v;   // 64-token tiles in panel order
+  CUtensorMap map_q, map_k;   // 64-token tiles as SW tiles
+  CUtensorMap map_v;          // 64-token tiles in panel order
 };
 
 struct FwdSmem {
-  uint4 q[kPanels * kC];        // phi(Q)                      [k/8][i]
-  uint4 k[kPanelsX * kC];       // phi(K) [k/8][j]; after the first MMAs: masked P [j/8][i]
+  uint4 q[kPanels * kC];        // phi(Q), SW tile (128-byte-swizzled rows, umma.cuh)
+  uint4 k[kPanels * kC];        // phi(K), SW tile; after the first MMAs: masked P, SW tile
+  uint4 alt[kPanelsX * kC];     // chunks with a reset: keep rows of V|1 (panels), then live rows of phi(Q) (SW tile)
   uint4 v[kPanelsX * kC];       // V | 1                       [v/8][j]
-  uint4 alt[kPanelsX * kC];     // chunks with a reset: keep rows of V|1, then live rows of phi(Q)
   uint4 s[2][kPanelsX * kD];    // bf16 S^T | z entering / leaving the chunk   [v/8][k]
   uint64_t bar[2];
   uint64_t bar_load;
   uint32_t tmem;
 };
 static_assert(sizeof(FwdSmem) <= 55 * 1024, "four CTAs per SM");
+static_assert(offsetof(FwdSmem, k) % 1024 == 0 && offsetof(FwdSmem, alt) % 1024 == 0, "SW tiles are 1024-byte aligned");
 
 // 128 TMEM columns per CTA.  M = 64 accumulators occupy 16 of the 32 lanes of a
 // warp's TMEM quarter, so two of them share columns: P and later O in lanes
@@ -73,7 +77,7 @@ constexpr uint32_t kTmemCols = 128;
 constexpr uint32_t kUpper = 16u << 16;
 
 __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_constant__ FwdParams p) {
-  extern __shared__ __align__(128) uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   FwdSmem& sm = *reinterpret_cast<FwdSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
@@ -101,8 +105,8 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
   auto issue_chunk_loads = [&](int cc) {
     fence_smem_to_async();   // earlier generic-proxy accesses to the buffers come first
     tma::expect_bytes(&sm.bar_load, 3 * kPanels * kC * 16);
-    tma::load_panel_tile(sm.q, &p.map_q, &sm.bar_load, cc * kC, h, b);
-    tma::load_panel_tile(sm.k, &p.map_k, &sm.bar_load, cc * kC, h, b);
+    tma::load_plain_tile(sm.q, &p.map_q, &sm.bar_load, cc * kC, h, b);
+    tma::load_plain_tile(sm.k, &p.map_k, &sm.bar_load, cc * kC, h, b);
     tma::load_panel_tile(sm.v, &p.map_v, &sm.bar_load, cc * kC, h, b);
   };
   if (tid == 0) issue_chunk_loads(0);
@@ -158,14 +162,18 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
     MXK_T(8);
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-      int trow, seg;
-      tile_vec(r * kThreads + tid, trow, seg);
-      const int slot = seg * kC + trow;
-      if (p.feature_map && trow < valid) {
-        sm.q[slot] = phi8(sm.q[slot]);
-        sm.k[slot] = phi8(sm.k[slot]);
+      // Q, K: element-wise, so the physical vector index serves (8 vectors = one token row)
+      const int vid = r * kThreads + tid;
+      if (p.feature_map && (vid >> 3) < valid) {
+        sm.q[vid] = phi8(sm.q[vid]);
+        sm.k[vid] = phi8(sm.k[vid]);
       }
-      if (has_reset) sm.alt[slot] = row_keep(dm, trow) ? sm.v[slot] : zero4;
+      if (has_reset) {
+        int trow, seg;
+        tile_vec(vid, trow, seg);
+        const int slot = seg * kC + trow;
+        sm.alt[slot] = row_keep(dm, trow) ? sm.v[slot] : zero4;
+      }
     }
     if (tid < kC) {
       const uint4 one = make_uint4(tid < valid ? kOneBf16 : 0u, 0, 0, 0);
@@ -182,7 +190,8 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
     if (warp == 0) {
       const bool leader = elect_one();
       fence_after_sync();
-      const Operand aq{smem_u32(sm.q), kC, false}, bk{smem_u32(sm.k), kC, false}, ak{smem_u32(sm.k), kC, true};
+      const Operand aq = sw_operand(smem_u32(sm.q), false), bk = sw_operand(smem_u32(sm.k), false);
+      const Operand ak = sw_operand(smem_u32(sm.k), true);
       const Operand bvk{smem_u32(has_reset ? sm.alt : sm.v), kC, true};
       gemm<kD / 16>(tmem, aq, bk, idesc_p, false, leader);                           // P        -> lower lanes
       gemm<kC / 16>(tmem + kUpper, ak, bvk, idesc_s, !has_reset, leader);            // S^T | z  -> upper lanes
@@ -206,7 +215,6 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
       tmem_ld_row<kDX>(lane_base, vals);
       const int lo = upper ? 0 : row_first_key(dm, row);
       const int hi = upper ? kDX : row;
-      uint4* dst = upper ? &sm.s[cur ^ 1][row] : &sm.k[row];
 #pragma unroll
       for (int pn = 0; pn < kPanelsX; ++pn) {
         float m[8];
@@ -215,7 +223,8 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
           const int j = pn * 8 + e;
           m[e] = (j >= lo && j <= hi) ? vals[j] : 0.f;
         }
-        if (pn < kPanels || upper) dst[pn * kC] = pack8_bf16(m);
+        if (upper) sm.s[cur ^ 1][pn * kD + row] = pack8_bf16(m);
+        else if (pn < kPanels) sm.k[sw_idx(row, pn)] = pack8_bf16(m);
       }
       if (upper && c == nchunks - 1) {
         if (p.s_last) {
@@ -229,10 +238,8 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
     if (has_reset) {   // live rows of phi(Q) for the inter-chunk product (the keep copy is dead now)
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
-        int trow, seg;
-        tile_vec(r * kThreads + tid, trow, seg);
-        const int slot = seg * kC + trow;
-        sm.alt[slot] = row_live(dm, trow) ? sm.q[slot] : zero4;
+        const int vid = r * kThreads + tid;
+        sm.alt[vid] = row_live(dm, vid >> 3) ? sm.q[vid] : zero4;
       }
     }
     fence_smem_to_async();
@@ -244,8 +251,8 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
     if (warp == 0) {
       const bool leader = elect_one();
       fence_after_sync();
-      const Operand aql{smem_u32(has_reset ? sm.alt : sm.q), kC, false}, bs{smem_u32(sm.s[cur]), kD, true};
-      const Operand ap{smem_u32(sm.k), kC, false}, bv{smem_u32(sm.v), kC, true};
+      const Operand aql = sw_operand(smem_u32(has_reset ? sm.alt : sm.q), false), bs{smem_u32(sm.s[cur]), kD, true};
+      const Operand ap = sw_operand(smem_u32(sm.k), false), bv{smem_u32(sm.v), kC, true};
       gemm<kD / 16>(tmem, aql, bs, idesc_o, false, leader);     // O  = live(phi(Q)) S_in^T
       gemm<kC / 16>(tmem, ap, bv, idesc_o, true, leader);       // O += mask(P) (V|1)
       if (leader) commit(&sm.bar[1]);
@@ -333,7 +340,7 @@ int mxk_linattn_bf16_fwd(const void* q, const void* k, const void* v, const floa
   prm.B = B; prm.T = T; prm.H = H;
   prm.eps = eps;
   prm.feature_map = feature_map;
-  if (!tma::make_panel_map(&prm.map_q, q, B, T, H, kD, kC) || !tma::make_panel_map(&prm.map_k, k, B, T, H, kD, kC) ||
+  if (!tma::make_sw_map(&prm.map_q, q, B, T, H, kC) || !tma::make_sw_map(&prm.map_k, k, B, T, H, kC) ||
       !tma::make_panel_map(&prm.map_v, v, B, T, H, kD, kC))
     return MXK_ERR_UNSUPPORTED;
   cudaError_t e = cudaFuncSetAttribute(linattn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -68,6 +68,22 @@ inline bool make_plain_map(CUtensorMap* map, const void* base, int B, int T, int
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Map whose loads write `rows` x 64 tiles (d = 64) as 128-byte-swizzled row-major lines (umma.cuh "SW
+// tiles"): 128-byte pieces, about five times faster per byte than the panel map.  Coordinates as for the
+// plain map, {0, h, t0, b}; the destination must be 1024-byte aligned.
+inline bool make_sw_map(CUtensorMap* map, const void* base, int B, int T, int H, int rows) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return false;
+  const cuuint64_t row_bytes = static_cast<cuuint64_t>(H) * 64 * 2;
+  const cuuint64_t dims[4] = {64, static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
+  const cuuint64_t strides[3] = {128, row_bytes, row_bytes * T};
+  const cuuint32_t box[4] = {64, 1, static_cast<cuuint32_t>(rows), 1};
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 #ifdef __CUDACC__
 // Announces `bytes` of asynchronous copies that will complete on `bar` (one arrival).
 __device__ __forceinline__ void expect_bytes(uint64_t* bar, uint32_t bytes) {

@@ -47,17 +47,41 @@ __host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, bool a_mn_major,
          (static_cast<uint32_t>(M >> 4) << 24);
 }
 
-// Operand in panel format with `rows` rows; `contract_rows` selects which index
-// is the contraction (K) index of the MMA.
+// 128-byte-swizzled row-major tiles ("SW tiles"): rows of 64 two-byte elements, one 128-byte line per
+// row, the 16-byte chunk j of row r stored at chunk position j ^ (r & 7); tile base 1024-byte aligned.
+// This is what a tiled TMA load with CU_TENSOR_MAP_SWIZZLE_128B writes (128-byte pieces instead of the
+// panel format's 16-byte pieces), and it is again both canonical tcgen05 layouts:
+//   - contraction over the columns (K-major): SBO = 1024 (next 8 rows), 32 bytes per K = 16 step;
+//   - contraction over the rows (MN-major): SBO = 1024 (next 8 rows), 2048 bytes per K = 16 step,
+//     LBO = distance to the next 64-column block when M or N exceeds 64.
+// Validated on the device against a CPU GEMM for both majors, M = 64 / 128, N = 32..128.
+__device__ __forceinline__ int sw_idx(int r, int chunk) { return r * 8 + (chunk ^ (r & 7)); }   // uint4 index
+
+// Operand in panel format with `rows` rows, or (swizzled) an SW tile; `contract_rows` selects which
+// index is the contraction (K) index of the MMA.
 struct Operand {
   uint32_t saddr;
   uint32_t rows;
   bool contract_rows;
+  bool swizzled = false;
+  uint32_t block_stride = 16;   // SW tiles, contraction over rows: bytes to the next 64-column block
   __device__ __forceinline__ uint64_t desc(int kstep) const {
+    if (swizzled)
+      return smem_desc(saddr + kstep * (contract_rows ? 2048u : 32u), contract_rows ? block_stride : 16u, 1024u) |
+             (static_cast<uint64_t>(2) << 61);
     if (contract_rows) return smem_desc(saddr + kstep * 256u, 128u, rows * 16u);
     return smem_desc(saddr + kstep * 2u * rows * 16u, rows * 16u, 128u);
   }
+  // start-address advance per K = 16 step, in 16-byte units
+  __device__ __forceinline__ uint32_t advance() const {
+    if (swizzled) return contract_rows ? 128u : 2u;
+    return contract_rows ? 16u : 2u * rows;
+  }
 };
+// SW tile operand
+__device__ __forceinline__ Operand sw_operand(uint32_t saddr, bool contract_rows, uint32_t block_stride = 16) {
+  return Operand{saddr, 0u, contract_rows, true, block_stride};
+}
 
 // ---- instructions ----------------------------------------------------------
 __device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
@@ -86,8 +110,7 @@ template <int KSTEPS>
 __device__ __forceinline__ void gemm(uint32_t tmem_d, const Operand& a, const Operand& b, uint32_t idesc,
                                      bool accumulate, bool leader) {
   const uint64_t da = a.desc(0), db = b.desc(0);
-  const uint32_t adv_a = (a.contract_rows ? 256u : 2u * a.rows * 16u) >> 4;
-  const uint32_t adv_b = (b.contract_rows ? 256u : 2u * b.rows * 16u) >> 4;
+  const uint32_t adv_a = a.advance(), adv_b = b.advance();
 #pragma unroll
   for (int k = 0; k < KSTEPS; ++k) {
     if (leader)
