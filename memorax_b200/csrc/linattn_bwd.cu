@@ -53,16 +53,20 @@ struct BwdParams {
   int B, T, H;
   float eps;
   int feature_map;
-  CUtensorMap map_q, map_k, map_v, map_do;   // 64-token tiles in panel order
+  CUtensorMap map_q, map_k, map_v, map_do;   // 64-token tiles as SW tiles
 };
 
 struct BwdSmem {
-  uint4 q[kPanels * kC];      // phi(Q)                 [k/8][i]
-  uint4 k[kPanels * kC];      // phi(K)                 [k/8][j]
+  // 128-byte-swizzled row-major tiles (umma.cuh "SW tiles"), 8 KB each, 1024-byte aligned
+  uint4 q[kPanels * kC];      // phi(Q)
+  uint4 k[kPanels * kC];      // phi(K)
+  uint4 v[kPanels * kC];      // V
+  uint4 d_o[kPanels * kC];    // dO
   uint4 kk[kPanels * kC];     // keep rows of phi(K)    (written only for chunks with a reset)
-  uint4 v[kPanelsK * kC];     // V | 1 | 0              [v/8][j]
-  uint4 vk[kPanelsK * kC];    // keep rows of V | 1 | 0 (written only for chunks with a reset)
-  uint4 d_o[kPanels * kC];    // dO                     [v/8][i]
+  uint4 vk[kPanels * kC];     // keep rows of V         (written only for chunks with a reset)
+  // panel format
+  uint4 vx[2 * kC];           // columns 64..79 of V | 1 | 0: the "1" column of the valid rows, then zeros
+  uint4 vkx[2 * kC];          // the same for the keep rows
   uint4 dos[kPanelsK * kC];   // live rows of dO/D | dden | 0
   uint4 s[kPanelsK * kD];     // S_in^T | z_in | 0      [v/8][k]
   uint4 g[kPanelsK * kD];     // G^T | gz | 0           [v/8][k]
@@ -120,7 +124,7 @@ __device__ __forceinline__ void store_half_rows(uint4* stage, const uint4* vals,
 }
 
 __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __grid_constant__ BwdParams p) {
-  extern __shared__ __align__(128) uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   BwdSmem& sm = *reinterpret_cast<BwdSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wg = warp >> 2;   // warpgroup
@@ -140,8 +144,8 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
   if (warp == 0) tmem_alloc(&sm.tmem, kBwdTmemCols);
   // zero padding panels that never change (columns 72..79 of the 80-wide operands)
   if (tid < kC) {
-    sm.v[(kPanelsK - 1) * kC + tid] = zero4;
-    sm.vk[(kPanelsK - 1) * kC + tid] = zero4;
+    sm.vx[kC + tid] = zero4;
+    sm.vkx[kC + tid] = zero4;
     sm.dos[(kPanelsK - 1) * kC + tid] = zero4;
     sm.s[(kPanelsK - 1) * kD + tid] = zero4;
     sm.g[(kPanelsK - 1) * kD + tid] = zero4;
@@ -159,16 +163,16 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
   auto issue_state_loads = [&](int cc) {
     fence_smem_to_async();   // earlier generic-proxy accesses to the buffers come first
     tma::expect_bytes(&sm.bar_load, (2 * kPanels * kC + kPanelsX * kD) * 16);
-    tma::load_panel_tile(sm.v, &p.map_v, &sm.bar_load, cc * kC, h, b);
-    tma::load_panel_tile(sm.d_o, &p.map_do, &sm.bar_load, cc * kC, h, b);
+    tma::load_plain_tile(sm.v, &p.map_v, &sm.bar_load, cc * kC, h, b);
+    tma::load_plain_tile(sm.d_o, &p.map_do, &sm.bar_load, cc * kC, h, b);
     tma::load_bulk(sm.s, p.chunk_states + (static_cast<size_t>(bh) * nchunks + cc) * (kPanelsX * kD),
                    kPanelsX * kD * 16, &sm.bar_load);
   };
   auto issue_qk_loads = [&](int cc) {
     fence_smem_to_async();
     tma::expect_bytes(&sm.bar_load, 2 * kPanels * kC * 16);
-    tma::load_panel_tile(sm.q, &p.map_q, &sm.bar_load, cc * kC, h, b);
-    tma::load_panel_tile(sm.k, &p.map_k, &sm.bar_load, cc * kC, h, b);
+    tma::load_plain_tile(sm.q, &p.map_q, &sm.bar_load, cc * kC, h, b);
+    tma::load_plain_tile(sm.k, &p.map_k, &sm.bar_load, cc * kC, h, b);
   };
   if (tid == 0) {
     issue_state_loads(nchunks - 1);
@@ -230,25 +234,25 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
     if (!mbar_wait(&sm.bar_load, it & 1)) timed_out = true;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-      int trow, seg;
-      tile_vec(r * kBwdThreads + tid, trow, seg);
-      const int slot = seg * kC + trow;
-      uint4 kv = sm.k[slot];
+      // element-wise, so the physical vector index serves (8 vectors = one token row)
+      const int vid = r * kBwdThreads + tid;
+      const int trow = vid >> 3;
+      uint4 kv = sm.k[vid];
       if (p.feature_map && trow < valid) {
-        sm.q[slot] = phi8(sm.q[slot]);
+        sm.q[vid] = phi8(sm.q[vid]);
         kv = phi8(kv);
-        sm.k[slot] = kv;
+        sm.k[vid] = kv;
       }
       if (has_reset) {
         const bool keep = row_keep(dm, trow);
-        sm.kk[slot] = keep ? kv : zero4;
-        sm.vk[slot] = keep ? sm.v[slot] : zero4;
+        sm.kk[vid] = keep ? kv : zero4;
+        sm.vk[vid] = keep ? sm.v[vid] : zero4;
       }
     }
     if (tid < kC) {
       const uint32_t one = tid < valid ? kOneBf16 : 0u;
-      sm.v[kPanels * kC + tid] = make_uint4(one, 0, 0, 0);
-      if (has_reset) sm.vk[kPanels * kC + tid] = make_uint4(row_keep(dm, tid) ? one : 0u, 0, 0, 0);
+      sm.vx[tid] = make_uint4(one, 0, 0, 0);
+      if (has_reset) sm.vkx[tid] = make_uint4(row_keep(dm, tid) ? one : 0u, 0, 0, 0);
     }
     fence_smem_to_async();
     fence_before_sync();
@@ -259,11 +263,12 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
     if (warp == 0) {
       const bool leader = elect_one();
       fence_after_sync();
-      const Operand aq{smem_u32(sm.q), kC, false}, bk{smem_u32(sm.k), kC, false};
-      const Operand ado{smem_u32(sm.d_o), kC, false}, bv{smem_u32(sm.v), kC, false};
+      const Operand aq = sw_operand(smem_u32(sm.q), false), bk = sw_operand(smem_u32(sm.k), false);
+      const Operand ado = sw_operand(smem_u32(sm.d_o), false), bv = sw_operand(smem_u32(sm.v), false);
       const Operand bs{smem_u32(sm.s), kD, false};
       const uint32_t id_half = idesc_bf16(kC, 32, false, false);
-      const Operand bk_hi{smem_u32(sm.k) + 32 * 16, kC, false}, bv_hi{smem_u32(sm.v) + 32 * 16, kC, false};
+      // rows 32..63 of an SW tile start 32 lines further on
+      const Operand bk_hi = sw_operand(smem_u32(sm.k) + 32 * 128, false), bv_hi = sw_operand(smem_u32(sm.v) + 32 * 128, false);
       const Operand bs_hi{smem_u32(sm.s) + 32 * 16, kD, false};
       gemm<kD / 16>(tmem + kColP, aq, bk, id_half, false, leader);                 // P,  keys 0..31
       gemm<kD / 16>(tmem + kUpper + kColP, aq, bk_hi, id_half, false, leader);     // P,  keys 32..63
@@ -292,7 +297,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
 #pragma unroll
         for (int pp = 0; pp < 2; ++pp) {
           float fq[8];
-          unpack8_bf16(sm.q[(p0 + pp) * kC + row], fq);
+          unpack8_bf16(sm.q[sw_idx(row, p0 + pp)], fq);
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const int kk = (p0 + pp) * 8 + e;
@@ -343,7 +348,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
 #pragma unroll
       for (int pp = 0; pp < 2; ++pp) {
         float f[8];
-        unpack8_bf16(sm.d_o[(p0 + pp) * kC + row], f);
+        unpack8_bf16(sm.d_o[sw_idx(row, p0 + pp)], f);
 #pragma unroll
         for (int e = 0; e < 8; ++e) f[e] *= sc;
         sm.dos[(p0 + pp) * kC + row] = pack8_bf16(f);
@@ -360,18 +365,22 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
       const bool leader = elect_one();
       fence_after_sync();
       // without a reset every key is kept: the unmasked tiles serve as the "keep" operands
-      const uint32_t keep_k = smem_u32(has_reset ? sm.kk : sm.k), keep_v = smem_u32(has_reset ? sm.vk : sm.v);
+      const Operand keep_k = sw_operand(smem_u32(has_reset ? sm.kk : sm.k), false);
+      const Operand keep_v = sw_operand(smem_u32(has_reset ? sm.vk : sm.v), false);
+      const Operand keep_vx{smem_u32(has_reset ? sm.vkx : sm.vx), kC, false};           // columns 64..79 of keep[V|1|0]
+      const Operand g_k{smem_u32(sm.g), kD, false}, g_k4{smem_u32(sm.g) + 4 * 2 * kD * 16, kD, false};   // and G's K steps 0..3 / 4
       // dphiQ = dP phi(K) + dOs [S|z]                      (lower, columns 0..63)
-      gemm<kC / 16>(tmem + kColLo, Operand{smem_u32(sm.dp), kC, false}, Operand{smem_u32(sm.k), kC, true}, id_km, false, leader);
+      gemm<kC / 16>(tmem + kColLo, Operand{smem_u32(sm.dp), kC, false}, sw_operand(smem_u32(sm.k), true), id_km, false, leader);
       gemm<5>(tmem + kColLo, Operand{smem_u32(sm.dos), kC, false}, Operand{smem_u32(sm.s), kD, false}, id_kk, true, leader);
       // dphiK = dP^T phi(Q) + keep[V|1] [G|gz]^T           (upper, columns 0..63)
-      gemm<kC / 16>(tmem + kUpper + kColLo, Operand{smem_u32(sm.dp), kC, true}, Operand{smem_u32(sm.q), kC, true}, id_mm, false, leader);
-      gemm<5>(tmem + kUpper + kColLo, Operand{keep_v, kC, false}, Operand{smem_u32(sm.g), kD, false}, id_kk, true, leader);
+      gemm<kC / 16>(tmem + kUpper + kColLo, Operand{smem_u32(sm.dp), kC, true}, sw_operand(smem_u32(sm.q), true), id_mm, false, leader);
+      gemm<4>(tmem + kUpper + kColLo, keep_v, g_k, id_kk, true, leader);
+      gemm<1>(tmem + kUpper + kColLo, keep_vx, g_k4, id_kk, true, leader);
       // dV = (P/D)^T dO + keep phi(K) G^T                  (lower, columns 64..127)
-      gemm<kC / 16>(tmem + kColHi, Operand{smem_u32(sm.pn), kC, true}, Operand{smem_u32(sm.d_o), kC, true}, id_mm, false, leader);
-      gemm<kD / 16>(tmem + kColHi, Operand{keep_k, kC, false}, Operand{smem_u32(sm.g), kD, true}, id_km, true, leader);
+      gemm<kC / 16>(tmem + kColHi, Operand{smem_u32(sm.pn), kC, true}, sw_operand(smem_u32(sm.d_o), true), id_mm, false, leader);
+      gemm<kD / 16>(tmem + kColHi, keep_k, Operand{smem_u32(sm.g), kD, true}, id_km, true, leader);
       // [G|gz]^T = [no reset][G|gz]^T + phi(Q)^T dOs       (upper, columns 64..135)
-      gemm<kC / 16>(tmem + kUpper + kColHi, Operand{smem_u32(sm.q), kC, true}, Operand{smem_u32(sm.dos), kC, true}, id_g, !has_reset, leader);
+      gemm<kC / 16>(tmem + kUpper + kColHi, sw_operand(smem_u32(sm.q), true), Operand{smem_u32(sm.dos), kC, true}, id_g, !has_reset, leader);
       if (leader) commit(&sm.bar[1]);
     }
     MXK_TB(10);
@@ -391,12 +400,12 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
         // one stream: lower chains dphiQ through phi'(q) into dq, upper dphiK through phi'(k) into dk
         float acc[32];
         tmem_ld_row<32>(lane_base + kColLo + c0, acc);
-        const uint4* feat = upper ? &sm.k[row] : &sm.q[row];
+        const uint4* feat = upper ? sm.k : sm.q;
         uint4 packed[4];
 #pragma unroll
         for (int pn = 0; pn < 4; ++pn) {
           float f[8];
-          unpack8_bf16(feat[(wg * 4 + pn) * kC], f);
+          unpack8_bf16(feat[sw_idx(row, wg * 4 + pn)], f);
 #pragma unroll
           for (int e = 0; e < 8; ++e) f[e] = acc[pn * 8 + e] * ((p.feature_map && f[e] <= 1.f) ? f[e] : 1.f);
           packed[pn] = pack8_bf16(f);
@@ -404,7 +413,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
         __syncthreads();   // phi(Q), phi(K) have been read by everyone: their buffers can be refilled
         if (tid == 0 && c > 0) issue_qk_loads(c - 1);
         store_half_rows(sm.dos + warp * 80, packed, !upper, lane, p.dq + out_off, stride_t, rows_valid);
-        store_half_rows(sm.vk + warp * 80, packed, upper, lane, p.dk + out_off, stride_t, rows_valid);
+        store_half_rows(sm.kk + warp * 80, packed, upper, lane, p.dk + out_off, stride_t, rows_valid);
       }
       // one stream: lower stores dV, upper refreshes the bf16 operand copy of G | gz
       {
@@ -494,8 +503,8 @@ int mxk_linattn_bf16_bwd(const void* q, const void* k, const void* v, const void
   prm.B = B; prm.T = T; prm.H = H;
   prm.eps = eps;
   prm.feature_map = feature_map;
-  if (!tma::make_panel_map(&prm.map_q, q, B, T, H, kD, kC) || !tma::make_panel_map(&prm.map_k, k, B, T, H, kD, kC) ||
-      !tma::make_panel_map(&prm.map_v, v, B, T, H, kD, kC) || !tma::make_panel_map(&prm.map_do, d_o, B, T, H, kD, kC))
+  if (!tma::make_sw_map(&prm.map_q, q, B, T, H, kC) || !tma::make_sw_map(&prm.map_k, k, B, T, H, kC) ||
+      !tma::make_sw_map(&prm.map_v, v, B, T, H, kC) || !tma::make_sw_map(&prm.map_do, d_o, B, T, H, kC))
     return MXK_ERR_UNSUPPORTED;
   cudaError_t e = cudaFuncSetAttribute(linattn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(BwdSmem)));
