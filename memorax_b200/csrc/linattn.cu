@@ -223,8 +223,9 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
           const int j = pn * 8 + e;
           m[e] = (j >= lo && j <= hi) ? vals[j] : 0.f;
         }
-        if (upper) sm.s[cur ^ 1][pn * kD + row] = pack8_bf16(m);
-        else if (pn < kPanels) sm.k[sw_idx(row, pn)] = pack8_bf16(m);
+        // one store instruction for both halves
+        uint4* dst = upper ? &sm.s[cur ^ 1][pn * kD + row] : &sm.k[sw_idx(row, pn & 7)];
+        if (pn < kPanels || upper) *dst = pack8_bf16(m);
       }
       if (upper && c == nchunks - 1) {
         if (p.s_last) {

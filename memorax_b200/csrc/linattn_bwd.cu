@@ -75,6 +75,7 @@ struct BwdSmem {
   float xch[2][2][kC];        // per warpgroup: partial den and don of every query row
   uint64_t bar[2];
   uint64_t bar_load;
+  uint64_t bar_free;   // every thread arrives once it has taken its phi(Q) / phi(K) vectors for the epilogue
   uint32_t tmem;
 };
 static_assert(sizeof(BwdSmem) <= 113 * 1024, "two CTAs per SM");
@@ -138,7 +139,8 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
   if (tid == 0) {
     mbar_init(&sm.bar[0], 1);
     mbar_init(&sm.bar[1], 1);
-    mbar_init(&sm.bar_load, 2);   // two groups of copies per chunk, issued at different times
+    mbar_init(&sm.bar_load, 1);
+    mbar_init(&sm.bar_free, kBwdThreads);
     mbar_init_fence();
   }
   if (warp == 0) tmem_alloc(&sm.tmem, kBwdTmemCols);
@@ -156,28 +158,21 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
   const uint32_t tmem = sm.tmem;
   const uint32_t lane_base = tmem + (static_cast<uint32_t>(qw * 32) << 16);
 
-  // A chunk's tiles arrive by TMA in operand order, issued by one thread as soon as the
-  // previous chunk no longer needs the buffers: V, dO and S_in (the forward call's
-  // residual) once its second MMA group has completed, Q and K once its epilogue has
-  // read the feature-map derivative from them.
-  auto issue_state_loads = [&](int cc) {
+  // A chunk's tiles arrive by TMA as SW tiles (S_in, the forward call's residual, by bulk copy), issued
+  // by one thread the moment the previous chunk's second MMA group has completed.  The epilogue still
+  // needs phi(Q) / phi(K) for the feature-map derivative, so every thread copies its four vectors into
+  // registers while the MMAs run and arrives on bar_free; the issuing thread waits for that barrier.
+  auto issue_chunk_loads = [&](int cc) {
     fence_smem_to_async();   // earlier generic-proxy accesses to the buffers come first
-    tma::expect_bytes(&sm.bar_load, (2 * kPanels * kC + kPanelsX * kD) * 16);
+    tma::expect_bytes(&sm.bar_load, (4 * kPanels * kC + kPanelsX * kD) * 16);
+    tma::load_plain_tile(sm.q, &p.map_q, &sm.bar_load, cc * kC, h, b);
+    tma::load_plain_tile(sm.k, &p.map_k, &sm.bar_load, cc * kC, h, b);
     tma::load_plain_tile(sm.v, &p.map_v, &sm.bar_load, cc * kC, h, b);
     tma::load_plain_tile(sm.d_o, &p.map_do, &sm.bar_load, cc * kC, h, b);
     tma::load_bulk(sm.s, p.chunk_states + (static_cast<size_t>(bh) * nchunks + cc) * (kPanelsX * kD),
                    kPanelsX * kD * 16, &sm.bar_load);
   };
-  auto issue_qk_loads = [&](int cc) {
-    fence_smem_to_async();
-    tma::expect_bytes(&sm.bar_load, 2 * kPanels * kC * 16);
-    tma::load_plain_tile(sm.q, &p.map_q, &sm.bar_load, cc * kC, h, b);
-    tma::load_plain_tile(sm.k, &p.map_k, &sm.bar_load, cc * kC, h, b);
-  };
-  if (tid == 0) {
-    issue_state_loads(nchunks - 1);
-    issue_qk_loads(nchunks - 1);
-  }
+  if (tid == 0) issue_chunk_loads(nchunks - 1);
 
   // Cotangent of the next carry -> TMEM (upper lanes) and its bf16 operand copy
   // (upper thread `row` owns G^T[row][.] = dS[.][row]; warpgroup 0 takes value columns
@@ -384,9 +379,20 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
       if (leader) commit(&sm.bar[1]);
     }
     MXK_TB(10);
+    // phi(Q) (lower) / phi(K) (upper) of this thread's 32 columns, taken while the MMAs run
+    uint4 featv[4];
+    {
+      const uint4* feat = upper ? sm.k : sm.q;
+#pragma unroll
+      for (int pn = 0; pn < 4; ++pn) featv[pn] = feat[sw_idx(row, wg * 4 + pn)];
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.bar_free)) : "memory");
+    }
     if (!mbar_wait(&sm.bar[1], it & 1)) timed_out = true;
     fence_after_sync();
-    if (tid == 0 && c > 0) issue_state_loads(c - 1);   // in flight while the output epilogue runs
+    if (tid == 0 && c > 0) {   // in flight while the output epilogue runs
+      if (!mbar_wait(&sm.bar_free, it & 1)) timed_out = true;
+      issue_chunk_loads(c - 1);
+    }
     MXK_TB(4);
 
     // ---- epilogue 2: every thread owns 32 (36, 40) columns of its row ----
@@ -400,18 +406,15 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
         // one stream: lower chains dphiQ through phi'(q) into dq, upper dphiK through phi'(k) into dk
         float acc[32];
         tmem_ld_row<32>(lane_base + kColLo + c0, acc);
-        const uint4* feat = upper ? sm.k : sm.q;
         uint4 packed[4];
 #pragma unroll
         for (int pn = 0; pn < 4; ++pn) {
           float f[8];
-          unpack8_bf16(feat[sw_idx(row, wg * 4 + pn)], f);
+          unpack8_bf16(featv[pn], f);
 #pragma unroll
           for (int e = 0; e < 8; ++e) f[e] = acc[pn * 8 + e] * ((p.feature_map && f[e] <= 1.f) ? f[e] : 1.f);
           packed[pn] = pack8_bf16(f);
         }
-        __syncthreads();   // phi(Q), phi(K) have been read by everyone: their buffers can be refilled
-        if (tid == 0 && c > 0) issue_qk_loads(c - 1);
         store_half_rows(sm.dos + warp * 80, packed, !upper, lane, p.dq + out_off, stride_t, rows_valid);
         store_half_rows(sm.kk + warp * 80, packed, upper, lane, p.dk + out_off, stride_t, rows_valid);
       }
