@@ -20,16 +20,18 @@ constexpr uint32_t kOneBf16 = 0x3F80u;
 
 __device__ __forceinline__ float phi(float x) { return x > 0.f ? x + 1.f : __expf(x); }
 
-// Feature map elu(x) + 1 on packed bf16 pairs: x + 1 for x > 0, exp(x) otherwise,
-// entirely in bf16x2 arithmetic (the result is rounded to bf16 anyway): one
-// multiply by log2(e), one ex2, one add, one compare mask, one blend per pair.
+// Feature map elu(x) + 1 on packed bf16 pairs, entirely in bf16x2 arithmetic (the result is
+// rounded to bf16 anyway): elu(x) + 1 = max(x, 0) + min(exp(x), 1) -- for x > 0 the second term
+// is exactly 1, otherwise the first is exactly 0 -- i.e. one multiply by log2(e), one ex2, one
+// min, one max, one add per pair.
 __device__ __forceinline__ uint32_t phi2(uint32_t x) {
-  uint32_t t, ex, pos, mask;
+  uint32_t t, ex, pos, r;
   asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(t) : "r"(x), "r"(0x3FB93FB9u));     // log2(e) = 1.4453 in bf16
   asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(ex) : "r"(t));
-  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(pos) : "r"(x), "r"(0x3F803F80u));    // 1.0
-  asm("set.gt.u32.bf16x2 %0, %1, %2;" : "=r"(mask) : "r"(x), "r"(0u));        // 0xFFFF per lane where x > 0
-  return (pos & mask) | (ex & ~mask);
+  asm("min.bf16x2 %0, %1, %2;" : "=r"(ex) : "r"(ex), "r"(0x3F803F80u));       // min(exp(x), 1)
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(pos) : "r"(x), "r"(0u));                // max(x, 0)
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(pos), "r"(ex));
+  return r;
 }
 __device__ __forceinline__ uint4 phi8(uint4 x) { return make_uint4(phi2(x.x), phi2(x.y), phi2(x.z), phi2(x.w)); }
 
