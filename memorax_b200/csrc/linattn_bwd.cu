@@ -54,6 +54,7 @@ struct BwdParams {
   float eps;
   int feature_map;
   CUtensorMap map_q, map_k, map_v, map_do;   // 64-token tiles as SW tiles
+  CUtensorMap map_dq, map_dk, map_dv;        // the same for the outputs
 };
 
 struct BwdSmem {
@@ -103,26 +104,6 @@ constexpr uint32_t kUpper = 16u << 16;
 constexpr uint32_t kColLo = 0, kColHi = 64, kColP = 0, kColA = 32, kColR = 136;
 
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
-
-// Coalesced store of 16 rows x 32 bf16 (half rows) owned by one warp: the 16 `writer`
-// lanes each hold four 16-byte vectors of one row; they go through a per-warp staging
-// area (row stride 5 vectors, conflict free) and all 32 lanes store eight complete
-// 64-byte half rows per instruction.  `stage`: this warp's 80 vectors; `grow0`: the
-// warp's first row, already offset to its column block.
-__device__ __forceinline__ void store_half_rows(uint4* stage, const uint4* vals, bool writer, int lane,
-                                                __nv_bfloat16* grow0, size_t stride_t, int rows_valid) {
-  if (writer) {
-#pragma unroll
-    for (int s4 = 0; s4 < 4; ++s4) stage[(lane & 15) * 5 + s4] = vals[s4];
-  }
-  __syncwarp();
-#pragma unroll
-  for (int it = 0; it < 2; ++it) {
-    const int r = 8 * it + (lane >> 2), seg = lane & 3;
-    if (r < rows_valid) *reinterpret_cast<uint4*>(grow0 + r * stride_t + seg * 8) = stage[r * 5 + seg];
-  }
-  __syncwarp();
-}
 
 __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __grid_constant__ BwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -202,8 +183,6 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
     tmem_st_wait();
   }
 
-  const size_t stride_t = static_cast<size_t>(p.H) * kD;
-  const size_t seq_base = (static_cast<size_t>(b) * p.T * p.H + h) * kD;
   const uint8_t* drow = p.done ? p.done + static_cast<size_t>(b) * p.T : nullptr;
   const uint32_t id_kk = idesc_bf16(kC, kC, false, false);   // A, B contract over columns
   const uint32_t id_km = idesc_bf16(kC, kC, false, true);    // B contracts over rows
@@ -249,6 +228,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
       sm.vx[tid] = make_uint4(one, 0, 0, 0);
       if (has_reset) sm.vkx[tid] = make_uint4(row_keep(dm, tid) ? one : 0u, 0, 0, 0);
     }
+    if (tid == 0) tma::wait_group_read<0>();   // the previous chunk's output tiles have left their staging buffers
     fence_smem_to_async();
     fence_before_sync();
     MXK_TB(1);
@@ -397,15 +377,13 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
 
     // ---- epilogue 2: every thread owns 32 (36, 40) columns of its row ----
     {
-      // Output rows leave through per-warp staging areas (buffers the finished MMAs no longer
-      // need) so that every store instruction writes complete 64-byte half rows.
-      const int rows_valid = valid - qw * 16;
-      const int c0 = wg * 32;
-      const size_t out_off = seq_base + static_cast<size_t>(t0 + qw * 16) * stride_t + c0;
+      // Output rows are staged as SW tiles in buffers the finished MMAs no longer need (dq in `dos`,
+      // dk in `dp`, dv in `pn`) and leave by TMA stores after the chunk's last barrier; rows past the
+      // end of the sequence are clipped by the tensor map.
       {
         // one stream: lower chains dphiQ through phi'(q) into dq, upper dphiK through phi'(k) into dk
         float acc[32];
-        tmem_ld_row<32>(lane_base + kColLo + c0, acc);
+        tmem_ld_row<32>(lane_base + kColLo + wg * 32, acc);
         uint4 packed[4];
 #pragma unroll
         for (int pn = 0; pn < 4; ++pn) {
@@ -415,8 +393,9 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
           for (int e = 0; e < 8; ++e) f[e] = acc[pn * 8 + e] * ((p.feature_map && f[e] <= 1.f) ? f[e] : 1.f);
           packed[pn] = pack8_bf16(f);
         }
-        store_half_rows(sm.dos + warp * 80, packed, !upper, lane, p.dq + out_off, stride_t, rows_valid);
-        store_half_rows(sm.kk + warp * 80, packed, upper, lane, p.dk + out_off, stride_t, rows_valid);
+        uint4* stage = upper ? sm.dp : sm.dos;
+#pragma unroll
+        for (int pn = 0; pn < 4; ++pn) stage[sw_idx(row, wg * 4 + pn)] = packed[pn];
       }
       // one stream: lower stores dV, upper refreshes the bf16 operand copy of G | gz
       {
@@ -432,7 +411,10 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
           for (int pn = 0; pn < 5; ++pn)
             if (pn < gpn) sm.g[(gp0 + pn) * kD + row] = packed[pn];
         }
-        store_half_rows(sm.pn + warp * 80, packed, !upper, lane, p.dv + out_off, stride_t, rows_valid);   // pn, dp: one 16 KB region
+        if (!upper) {
+#pragma unroll
+          for (int pn = 0; pn < 4; ++pn) sm.pn[sw_idx(row, wg * 4 + pn)] = packed[pn];
+        }
         if (upper && c == 0) {
           float* out = p.ds0 ? p.ds0 + static_cast<size_t>(bh) * kD * kD : nullptr;
 #pragma unroll
@@ -450,9 +432,17 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
       }
     }
     MXK_TB(5);
-    __syncthreads();   // staging areas alias buffers that the next chunk refills
+    fence_smem_to_async();
+    __syncthreads();
+    if (tid == 0) {
+      tma::store_plain_tile(&p.map_dq, sm.dos, t0, h, b);
+      tma::store_plain_tile(&p.map_dk, sm.dp, t0, h, b);
+      tma::store_plain_tile(&p.map_dv, sm.pn, t0, h, b);
+      tma::commit_group();
+    }
     MXK_TB(6);
   }
+  if (tid == 0) tma::wait_group_all();
 
   if (timed_out && p.status) atomicExch(p.status, 1);
   fence_before_sync();
@@ -508,6 +498,9 @@ int mxk_linattn_bf16_bwd(const void* q, const void* k, const void* v, const void
   prm.feature_map = feature_map;
   if (!tma::make_sw_map(&prm.map_q, q, B, T, H, kC) || !tma::make_sw_map(&prm.map_k, k, B, T, H, kC) ||
       !tma::make_sw_map(&prm.map_v, v, B, T, H, kC) || !tma::make_sw_map(&prm.map_do, d_o, B, T, H, kC))
+    return MXK_ERR_UNSUPPORTED;
+  if (!tma::make_sw_map(&prm.map_dq, dq, B, T, H, kC) || !tma::make_sw_map(&prm.map_dk, dk, B, T, H, kC) ||
+      !tma::make_sw_map(&prm.map_dv, dv, B, T, H, kC))
     return MXK_ERR_UNSUPPORTED;
   cudaError_t e = cudaFuncSetAttribute(linattn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(BwdSmem)));
