@@ -44,7 +44,7 @@ struct FwdParams {
   int B, T, H;
   float eps;
   int feature_map;
-  CUtensorMap map_q, map_k;   // 64-token tiles as SW tiles
+  CUtensorMap map_q, map_k, map_o;   // 64-token tiles as SW tiles
   CUtensorMap map_v;          // 64-token tiles in panel order
 };
 
@@ -59,7 +59,9 @@ struct FwdSmem {
   uint32_t tmem;
 };
 static_assert(sizeof(FwdSmem) <= 55 * 1024, "four CTAs per SM");
-static_assert(offsetof(FwdSmem, k) % 1024 == 0 && offsetof(FwdSmem, alt) % 1024 == 0, "SW tiles are 1024-byte aligned");
+static_assert(offsetof(FwdSmem, k) % 1024 == 0 && offsetof(FwdSmem, alt) % 1024 == 0 && offsetof(FwdSmem, s) % 1024 == 0 &&
+                  (kPanelsX * kD * 16) % 1024 == 0,
+              "SW tiles are 1024-byte aligned");
 
 // 128 TMEM columns per CTA.  M = 64 accumulators occupy 16 of the 32 lanes of a
 // warp's TMEM quarter, so two of them share columns: P and later O in lanes
@@ -135,8 +137,6 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
     tmem_st_wait();
   }
 
-  const size_t stride_t = static_cast<size_t>(p.H) * kD;
-  const size_t seq_base = (static_cast<size_t>(b) * p.T * p.H + h) * kD;
   const uint8_t* drow = p.done ? p.done + static_cast<size_t>(b) * p.T : nullptr;
   const uint32_t idesc_p = idesc_bf16(kC, kC, false, false);
   const uint32_t idesc_o = idesc_bf16(kC, kDX, false, true);
@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
       sm.v[kPanels * kC + tid] = one;
       if (has_reset) sm.alt[kPanels * kC + tid] = row_keep(dm, tid) ? one : zero4;
     }
-    if (tid == 0) tma::wait_group_read<0>();   // the previous residual copy has finished reading s[cur ^ 1]
+    if (tid == 0) tma::wait_group_read<0>();   // the previous output tile has left s[cur ^ 1], rewritten in epilogue A
     fence_smem_to_async();
     fence_before_sync();
     MXK_T(1);
@@ -243,6 +243,7 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
         sm.alt[vid] = row_live(dm, vid >> 3) ? sm.q[vid] : zero4;
       }
     }
+    if (tid == 0) tma::wait_group_read<0>();   // the residual copy has left s[cur], which stages the output below
     fence_smem_to_async();
     fence_before_sync();
     MXK_T(4);
@@ -276,12 +277,20 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
         for (int e = 0; e < 8; ++e) f[e] = orow[pn * 8 + e] * inv;
         packed[pn] = pack8_bf16(f);
       }
-      // the masked copies are dead once the second MMA group has completed: `alt` stages the output rows
-      store_rows_coalesced(sm.alt + warp * (16 * 9), packed, !upper, lane,
-                           p.o + seq_base + static_cast<size_t>(t0 + warp * 16) * stride_t, stride_t,
-                           valid - warp * 16);
+      // s[cur] (the state that entered the chunk) is dead once the second MMA group has completed and
+      // is not rewritten before the next chunk's first epilogue: it stages the output rows as an SW
+      // tile for one TMA store (rows past the end of the sequence are clipped by the tensor map)
+      if (!upper) {
+#pragma unroll
+        for (int pn = 0; pn < kPanels; ++pn) sm.s[cur][sw_idx(row, pn)] = packed[pn];
+      }
     }
-    __syncthreads();   // the staging rows live in sm.alt, which the next chunk may overwrite
+    fence_smem_to_async();
+    __syncthreads();
+    if (tid == 0) {
+      tma::store_plain_tile(&p.map_o, sm.s[cur], t0, h, b);
+      tma::commit_group();
+    }
     cur ^= 1;
     MXK_T(7);
   }
@@ -342,7 +351,7 @@ int mxk_linattn_bf16_fwd(const void* q, const void* k, const void* v, const floa
   prm.eps = eps;
   prm.feature_map = feature_map;
   if (!tma::make_sw_map(&prm.map_q, q, B, T, H, kC) || !tma::make_sw_map(&prm.map_k, k, B, T, H, kC) ||
-      !tma::make_panel_map(&prm.map_v, v, B, T, H, kD, kC))
+      !tma::make_panel_map(&prm.map_v, v, B, T, H, kD, kC) || !tma::make_sw_map(&prm.map_o, o, B, T, H, kC))
     return MXK_ERR_UNSUPPORTED;
   cudaError_t e = cudaFuncSetAttribute(linattn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(FwdSmem)));

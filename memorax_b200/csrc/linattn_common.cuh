@@ -35,15 +35,8 @@ __device__ __forceinline__ uint32_t phi2(uint32_t x) {
 }
 __device__ __forceinline__ uint4 phi8(uint4 x) { return make_uint4(phi2(x.x), phi2(x.y), phi2(x.z), phi2(x.w)); }
 
-// 64 done flags of the chunk starting at t0 as a bit mask (bit i = token t0+i).
-__device__ __forceinline__ uint64_t chunk_done_mask(const uint8_t* drow, int t0, int T, int lane) {
-  if (!drow) return 0ull;
-  const int ta = t0 + lane, tb = t0 + 32 + lane;
-  const unsigned lo = __ballot_sync(0xffffffffu, ta < T && drow[ta] != 0);
-  const unsigned hi = __ballot_sync(0xffffffffu, tb < T && drow[tb] != 0);
-  return (static_cast<uint64_t>(hi) << 32) | lo;
-}
-// The same in two steps, so that the byte loads of a later chunk can be issued long
+// 64 done flags of a chunk as a bit mask (bit i = token t0 + i), built in two steps so that the byte
+// loads of a later chunk can be issued long
 // before their values are needed.  The loaded bytes stay untouched in registers until
 // done_mask_from_flags(): any arithmetic on them at load time would make the in-order
 // thread wait for the loads right there.
@@ -77,28 +70,6 @@ __device__ __forceinline__ int row_first_key(uint64_t dm, int i) {
 __device__ __forceinline__ void tile_vec(int vid, int& row, int& seg) {
   row = (vid & 7) + 8 * (vid >> 6);
   seg = (vid >> 3) & 7;
-}
-
-
-// Coalesced store of 16 rows x 64 bf16 owned by one warp.  The 16 `writer` lanes
-// each hold one row (eight 16-byte vectors); writing them straight to memory
-// would touch 16 different 128-byte lines per instruction.  Instead the rows go
-// through a per-warp staging area (row stride 9 vectors = 144 bytes, conflict
-// free) and all 32 lanes store four complete rows per instruction.
-// `stage` is this warp's 16 * 9 vectors; `grow0` points at the warp's first row.
-__device__ __forceinline__ void store_rows_coalesced(uint4* stage, const uint4* vals, bool writer, int lane,
-                                                     __nv_bfloat16* grow0, size_t stride_t, int rows_valid) {
-  if (writer) {
-#pragma unroll
-    for (int s8 = 0; s8 < 8; ++s8) stage[(lane & 15) * 9 + s8] = vals[s8];
-  }
-  __syncwarp();
-#pragma unroll
-  for (int it = 0; it < 4; ++it) {
-    const int r = 4 * it + (lane >> 3), seg = lane & 7;
-    if (r < rows_valid) *reinterpret_cast<uint4*>(grow0 + r * stride_t + seg * 8) = stage[r * 9 + seg];
-  }
-  __syncwarp();
 }
 
 }  // namespace linattn
