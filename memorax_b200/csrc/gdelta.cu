@@ -32,14 +32,14 @@ struct FwdParams {
   uint4* chunk_states;
   int* status;
   int B, T, H;
-  CUtensorMap map_k, map_q;   // 64-token tiles in panel order
+  CUtensorMap map_k, map_q;   // 64-token tiles as SW tiles (two 64-column blocks)
   CUtensorMap map_v, map_o;   // 64-token tiles row-major
 };
 
 struct FwdSmem {
   uint4 s[kStateVecs];        // S_in bf16                      [k/8][v][8]
-  uint4 k[kPanD * kC];        // K, after the first MMAs gam K  [k/8][t][8]
-  uint4 q[kPanD * kC];        // Q, after the first MMAs g Q    [k/8][t][8]
+  uint4 k[kPanD * kC];        // K, after the first MMAs gam K  (SW tiles: two 64-column blocks)
+  uint4 q[kPanD * kC];        // Q, after the first MMAs g Q    (SW tiles)
   uint4 vu[kC * 16];          // V row-major [t][v], then U^T   [j/8][v][8]
   uint4 p[kPanC * kC];        // tril(G o QK^T)                 [j/8][t][8]
   float lt[kC * kC];          // lt[j][t] = -beta_t L_tj, then the bf16 output tile [t][v]
@@ -60,7 +60,7 @@ constexpr uint32_t kUpper = 16u << 16;
 constexpr uint32_t kColS = 0, kColKQ = 128, kColO = 128, kColY = 192;
 
 __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_constant__ FwdParams p) {
-  extern __shared__ __align__(128) uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   FwdSmem& sm = *reinterpret_cast<FwdSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
@@ -112,8 +112,11 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_co
   auto issue_chunk_loads = [&](int cc) {
     fence_smem_to_async();   // earlier generic-proxy accesses to the buffers come first
     tma::expect_bytes(&sm.bar_load, 3 * kPanD * kC * 16);
-    tma::load_panel_tile(sm.k, &p.map_k, &sm.bar_load, cc * kC, h, b);
-    tma::load_panel_tile(sm.q, &p.map_q, &sm.bar_load, cc * kC, h, b);
+    // K, Q as SW tiles: two 64-column blocks of 64 x 128 bytes each
+    tma::load_plain_tile(sm.k, &p.map_k, &sm.bar_load, cc * kC, h, b, 0);
+    tma::load_plain_tile(sm.k + kSwBlockVecs, &p.map_k, &sm.bar_load, cc * kC, h, b, 64);
+    tma::load_plain_tile(sm.q, &p.map_q, &sm.bar_load, cc * kC, h, b, 0);
+    tma::load_plain_tile(sm.q + kSwBlockVecs, &p.map_q, &sm.bar_load, cc * kC, h, b, 64);
     tma::load_plain_tile(sm.vu, &p.map_v, &sm.bar_load, cc * kC, h, b);
   };
   if (tid == 0) issue_chunk_loads(0);
@@ -142,10 +145,11 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_co
     if (warp == 0) {
       const bool leader = elect_one();
       fence_after_sync();
-      const Operand ak{smem_u32(sm.k), kC, false}, aq{smem_u32(sm.q), kC, false}, as{smem_u32(sm.s), kD, false};
-      gemm<kD / 16>(tmem + kColKQ, ak, ak, id_64, false, leader);              // K K^T -> lower lanes
-      gemm<kD / 16>(tmem + kUpper + kColKQ, aq, ak, id_64, false, leader);     // Q K^T -> upper lanes
-      gemm<kD / 16>(tmem + kColY, as, ak, id_128x64, false, leader);           // Y^T = S_in K^T
+      const Operand ak = sw_operand(smem_u32(sm.k), false, kSwBlockVecs * 16), aq = sw_operand(smem_u32(sm.q), false, kSwBlockVecs * 16);
+      const Operand as{smem_u32(sm.s), kD, false};
+      gemm128(tmem + kColKQ, ak, ak, id_64, false, leader);              // K K^T -> lower lanes
+      gemm128(tmem + kUpper + kColKQ, aq, ak, id_64, false, leader);     // Q K^T -> upper lanes
+      gemm128(tmem + kColY, as, ak, id_128x64, false, leader);           // Y^T = S_in K^T
       if (leader) commit(&sm.bar[0]);
     }
     if (!mbar_wait(&sm.bar[0], c & 1)) timed_out = true;
@@ -183,10 +187,10 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_co
 #pragma unroll
       for (int pn = 0; pn < kPanD; ++pn) {
         float f[8];
-        unpack8_bf16(tile[pn * kC + row], f);
+        unpack8_bf16(tile[sw_slot(row, pn)], f);
 #pragma unroll
         for (int e = 0; e < 8; ++e) f[e] *= sc;
-        tile[pn * kC + row] = pack8_bf16(f);
+        tile[sw_slot(row, pn)] = pack8_bf16(f);
       }
     }
     // ---- epilogue 1b: thread v solves for its column of U; S <- g_last S in place ----
@@ -226,9 +230,10 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_co
     if (warp == 0) {
       const bool leader = elect_one();
       fence_after_sync();
-      const Operand as{smem_u32(sm.s), kD, false}, bgq{smem_u32(sm.q), kC, false};
-      const Operand au{smem_u32(sm.vu), kD, false}, bp{smem_u32(sm.p), kC, false}, bgk{smem_u32(sm.k), kC, true};
-      gemm<kD / 16>(tmem + kColO, as, bgq, id_128x64, false, leader);   // O^T  = S_in (g Q)^T
+      const Operand as{smem_u32(sm.s), kD, false}, bgq = sw_operand(smem_u32(sm.q), false, kSwBlockVecs * 16);
+      const Operand au{smem_u32(sm.vu), kD, false}, bp{smem_u32(sm.p), kC, false};
+      const Operand bgk = sw_operand(smem_u32(sm.k), true, kSwBlockVecs * 16);
+      gemm128(tmem + kColO, as, bgq, id_128x64, false, leader);         // O^T  = S_in (g Q)^T
       gemm<kC / 16>(tmem + kColO, au, bp, id_128x64, true, leader);     // O^T += U^T P^T
       gemm<kC / 16>(tmem + kColS, au, bgk, id_ds, true, leader);        // S    = g_last S_in + U^T (gam K)
       if (leader) commit(&sm.bar[1]);
@@ -316,7 +321,7 @@ int mxk_gdelta_bf16_fwd(const void* q, const void* k, const void* v, const float
   prm.chunk_states = static_cast<uint4*>(chunk_states);
   prm.status = status;
   prm.B = B; prm.T = T; prm.H = H;
-  if (!tma::make_panel_map(&prm.map_k, k, B, T, H, kD, kC) || !tma::make_panel_map(&prm.map_q, q, B, T, H, kD, kC) ||
+  if (!tma::make_sw_map(&prm.map_k, k, B, T, H, kC, kD) || !tma::make_sw_map(&prm.map_q, q, B, T, H, kC, kD) ||
       !tma::make_plain_map(&prm.map_v, v, B, T, H, kD, kC) || !tma::make_plain_map(&prm.map_o, o, B, T, H, kD, kC))
     return MXK_ERR_UNSUPPORTED;
   cudaError_t e = cudaFuncSetAttribute(gdelta_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

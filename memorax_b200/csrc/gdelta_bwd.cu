@@ -44,8 +44,7 @@ struct BwdParams {
   float* ds0;
   int* status;
   int B, T, H;
-  CUtensorMap map_k, map_q, map_do;   // 64-token tiles in panel order
-  CUtensorMap map_do_plain;           // the same dO tile row-major
+  CUtensorMap map_k, map_q, map_do;   // 64-token tiles as SW tiles (two 64-column blocks)
 };
 
 // Row stride of the fp32 64 x 64 matrices that threads write row by row: 68 floats keep
@@ -55,11 +54,11 @@ constexpr int kLS = kC + 4;
 struct BwdSmem {
   uint4 s[kStateVecs];      // S_in bf16          [k/8][v][8]
   uint4 ds[kStateVecs];     // dS bf16            [k/8][v][8]
-  uint4 k[kPanD * kC];      // K                  [k/8][t][8]
-  uint4 q[kPanD * kC];      // Q                  [k/8][t][8]
-  uint4 d_o[kPanD * kC];    // dO, later g dO     [v/8][t][8]
+  uint4 k[kPanD * kC];      // K                  SW tiles (two 64-column blocks)
+  uint4 q[kPanD * kC];      // Q                  SW tiles
+  uint4 d_o[kPanD * kC];    // dO, later g dO     SW tiles
   uint4 r1[kC * 16];        // V [t][v]   -> dUt^T            [t/8][v][8]
-  uint4 r2[kC * 16];        // dO [t][v]  -> -(g dR)^T        [j/8][v][8]
+  uint4 r2[kC * 16];        // -(g dR)^T                      [j/8][v][8]
   uint4 u[kPanC * kD];      // U^T                [j/8][v][8]
   uint4 ug[kPanC * kD];     // (gam U)^T
   uint4 p[kPanC * kC];      // tril(G o QK^T)     [j/8][t][8]
@@ -106,20 +105,23 @@ __device__ __forceinline__ void warp_reduce(float* vals, int lane) {
   }
 }
 
-// All global -> shared traffic of chunk `c` (K, Q, dO twice, S_in, U^T): four TMA tile
+// All global -> shared traffic of chunk `c` (K, Q, dO, S_in, U^T): six TMA tile
 // loads and two bulk copies issued by ONE thread, completing on sm.bar_load.  The
 // kernel issues them one chunk ahead, right after the last MMAs of the previous chunk
 // have released the buffers, so that they overlap that chunk's last epilogue.
-constexpr uint32_t kChunkLoadBytes = (4 * kPanD * kC + kResidualVecs) * 16;
+constexpr uint32_t kChunkLoadBytes = (3 * kPanD * kC + kResidualVecs) * 16;
 __device__ __forceinline__ void issue_chunk_loads(BwdSmem& sm, const BwdParams& p, int b, int h, int c, int nchunks) {
   // earlier generic-proxy accesses to these buffers are ordered before the async-proxy writes
   fence_smem_to_async();
   tma::expect_bytes(&sm.bar_load, kChunkLoadBytes);
   const int t0 = c * kC;
-  tma::load_panel_tile(sm.k, &p.map_k, &sm.bar_load, t0, h, b);
-  tma::load_panel_tile(sm.q, &p.map_q, &sm.bar_load, t0, h, b);
-  tma::load_panel_tile(sm.d_o, &p.map_do, &sm.bar_load, t0, h, b);
-  tma::load_plain_tile(sm.r2, &p.map_do_plain, &sm.bar_load, t0, h, b);
+  // K, Q, dO as SW tiles: two 64-column blocks of 64 x 128 bytes each
+  tma::load_plain_tile(sm.k, &p.map_k, &sm.bar_load, t0, h, b, 0);
+  tma::load_plain_tile(sm.k + kSwBlockVecs, &p.map_k, &sm.bar_load, t0, h, b, 64);
+  tma::load_plain_tile(sm.q, &p.map_q, &sm.bar_load, t0, h, b, 0);
+  tma::load_plain_tile(sm.q + kSwBlockVecs, &p.map_q, &sm.bar_load, t0, h, b, 64);
+  tma::load_plain_tile(sm.d_o, &p.map_do, &sm.bar_load, t0, h, b, 0);
+  tma::load_plain_tile(sm.d_o + kSwBlockVecs, &p.map_do, &sm.bar_load, t0, h, b, 64);
   const uint4* src = p.chunk_states + (static_cast<size_t>(b * p.H + h) * nchunks + c) * kResidualVecs;
   tma::load_bulk(sm.s, src, kStateVecs * 16, &sm.bar_load);
   tma::load_bulk(sm.u, src + kStateVecs, kUVecs * 16, &sm.bar_load);
@@ -131,7 +133,7 @@ __device__ __forceinline__ void issue_chunk_loads(BwdSmem& sm, const BwdParams& 
 constexpr int kBwdThreads = 256;
 
 __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_constant__ BwdParams p) {
-  extern __shared__ __align__(128) uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   BwdSmem& sm = *reinterpret_cast<BwdSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wg = warp >> 2;            // warpgroup
@@ -218,21 +220,22 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
     if (warp == 0) {
       const bool leader = elect_one();
       fence_after_sync();
-      const Operand ak{smem_u32(sm.k), kC, false}, aq{smem_u32(sm.q), kC, false};
+      constexpr uint32_t kBlk = kSwBlockVecs * 16;   // bytes between the two 64-column blocks of an SW tile pair
+      const Operand ak = sw_operand(smem_u32(sm.k), false, kBlk), aq = sw_operand(smem_u32(sm.q), false, kBlk);
       const Operand as{smem_u32(sm.s), kD, false}, ads{smem_u32(sm.ds), kD, false};
       const uint32_t id_128 = idesc_bf16(kD, kC, false, false);
       // 64 x 64 products are issued as two N = 32 halves: keys 0..31 land in lanes 0..15 of each
       // warp's TMEM quarter, keys 32..63 in lanes 16..31 of the same columns, so both half-warps
       // work on the same token row in the epilogues
-      const Operand bk_lo{smem_u32(sm.k), kC, false}, bk_hi{smem_u32(sm.k) + 32 * 16, kC, false};
+      const Operand bk_lo = ak, bk_hi = sw_operand(smem_u32(sm.k) + 32 * 128, false, kBlk);
       const uint32_t id_half = idesc_bf16(kC, 32, false, false);
-      gemm<kD / 16>(tmem + kColKK, ak, bk_lo, id_half, false, leader);
-      gemm<kD / 16>(tmem + kUpper + kColKK, ak, bk_hi, id_half, false, leader);
-      gemm<kD / 16>(tmem + kColQK, aq, bk_lo, id_half, false, leader);
-      gemm<kD / 16>(tmem + kUpper + kColQK, aq, bk_hi, id_half, false, leader);
-      gemm<kD / 16>(tmem + kColY, as, ak, id_128, false, leader);
-      gemm<kD / 16>(tmem + kColOI, as, aq, id_128, false, leader);
-      gemm<kD / 16>(tmem + kColX2, ads, ak, id_128, false, leader);
+      gemm128(tmem + kColKK, ak, bk_lo, id_half, false, leader);
+      gemm128(tmem + kUpper + kColKK, ak, bk_hi, id_half, false, leader);
+      gemm128(tmem + kColQK, aq, bk_lo, id_half, false, leader);
+      gemm128(tmem + kUpper + kColQK, aq, bk_hi, id_half, false, leader);
+      gemm128(tmem + kColY, as, ak, id_128, false, leader);
+      gemm128(tmem + kColOI, as, aq, id_128, false, leader);
+      gemm128(tmem + kColX2, ads, ak, id_128, false, leader);
       if (leader) commit(&sm.bar[0]);
     }
     if (!mbar_wait(&sm.bar[0], 0)) timed_out = true;
@@ -271,7 +274,7 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
       float r[32];
       tmem_ld_row<32>(lane_base + kColOI + wg * 32, r);
 #pragma unroll
-      for (int t = 0; t < 32; ++t) r[t] *= bf16_at(sm.r2, wg * 32 + t, vt);
+      for (int t = 0; t < 32; ++t) r[t] *= sw_bf16_at(sm.d_o, wg * 32 + t, vt);
       warp_reduce<32>(r, lane);
       atomicAdd(&sm.dg[wg * 32 + lane], r[0]);
     }
@@ -284,9 +287,10 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
     if (warp == 0) {
       const bool leader = elect_one();
       fence_after_sync();
-      gemm<kC / 16>(tmem + kColX1, Operand{smem_u32(sm.d_o), kC, true}, Operand{smem_u32(sm.p), kC, true}, idesc_bf16(kD, kC, true, true), false, leader);
-      gemm<kD / 16>(tmem + kColDP, Operand{smem_u32(sm.d_o), kC, false}, Operand{smem_u32(sm.u), kD, true}, idesc_bf16(kC, 32, false, true), false, leader);
-      gemm<kD / 16>(tmem + kUpper + kColDP, Operand{smem_u32(sm.d_o), kC, false}, Operand{smem_u32(sm.u) + 4 * kD * 16, kD, true}, idesc_bf16(kC, 32, false, true), false, leader);
+      constexpr uint32_t kBlk = kSwBlockVecs * 16;
+      gemm<kC / 16>(tmem + kColX1, sw_operand(smem_u32(sm.d_o), true, kBlk), Operand{smem_u32(sm.p), kC, true}, idesc_bf16(kD, kC, true, true), false, leader);
+      gemm128(tmem + kColDP, sw_operand(smem_u32(sm.d_o), false, kBlk), Operand{smem_u32(sm.u), kD, true}, idesc_bf16(kC, 32, false, true), false, leader);
+      gemm128(tmem + kUpper + kColDP, sw_operand(smem_u32(sm.d_o), false, kBlk), Operand{smem_u32(sm.u) + 4 * kD * 16, kD, true}, idesc_bf16(kC, 32, false, true), false, leader);
       if (leader) commit(&sm.bar[1]);
     }
     if (!mbar_wait(&sm.bar[1], 0)) timed_out = true;
@@ -437,10 +441,10 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
 #pragma unroll
       for (int pp = 0; pp < kPanD / 4; ++pp) {
         float f[8];
-        unpack8_bf16(sm.d_o[(p0 + pp) * kC + row], f);
+        unpack8_bf16(sm.d_o[sw_slot(row, p0 + pp)], f);
 #pragma unroll
         for (int e = 0; e < 8; ++e) f[e] *= gt;
-        sm.d_o[(p0 + pp) * kC + row] = pack8_bf16(f);
+        sm.d_o[sw_slot(row, p0 + pp)] = pack8_bf16(f);
       }
     }
     fence_smem_to_async();
@@ -454,12 +458,14 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
       fence_after_sync();
       const uint4* dpg_p = reinterpret_cast<const uint4*>(sm.lt);
       const uint32_t dpg = smem_u32(dpg_p), dlg = smem_u32(dpg_p + kPanC * kC);
-      const Operand bk{smem_u32(sm.k), kC, true}, bq{smem_u32(sm.q), kC, true};
+      constexpr uint32_t kBlk = kSwBlockVecs * 16;
+      const Operand bk = sw_operand(smem_u32(sm.k), true, kBlk), bq = sw_operand(smem_u32(sm.q), true, kBlk);
+      const Operand ado_k = sw_operand(smem_u32(sm.d_o), false, kBlk), ado_t = sw_operand(smem_u32(sm.d_o), true, kBlk);
       const Operand bs{smem_u32(sm.s), kD, true}, bds{smem_u32(sm.ds), kD, true};
       const uint32_t id_km = idesc_bf16(kC, kD, false, true), id_mm = idesc_bf16(kC, kD, true, true);
       // dQ = (dP o G) K + (g dO) S_in
       gemm<kC / 16>(tmem + kColDQ, Operand{dpg, kC, false}, bk, id_km, false, leader);
-      gemm<kD / 16>(tmem + kColDQ, Operand{smem_u32(sm.d_o), kC, false}, bs, id_km, true, leader);
+      gemm128(tmem + kColDQ, ado_k, bs, id_km, true, leader);
       // dK = (dP o G)^T Q + (dL o G) K + (dL o G)^T K + (gam U) dS - (g dR) S_in
       gemm<kC / 16>(tmem + kColDK, Operand{dpg, kC, true}, bq, id_mm, false, leader);
       gemm<kC / 16>(tmem + kColDK, Operand{dlg, kC, false}, bk, id_km, true, leader);
@@ -467,7 +473,7 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
       gemm<kD / 16>(tmem + kColDK, Operand{smem_u32(sm.ug), kD, true}, bds, id_mm, true, leader);
       gemm<kD / 16>(tmem + kColDK, Operand{smem_u32(sm.r2), kD, true}, bs, id_mm, true, leader);
       // dS_in - g_last dS = (g dO)^T Q - (g dR)^T K
-      gemm<kC / 16>(tmem + kColDelta, Operand{smem_u32(sm.d_o), kC, true}, bq, idesc_bf16(kD, kD, true, true), false, leader);
+      gemm<kC / 16>(tmem + kColDelta, ado_t, bq, idesc_bf16(kD, kD, true, true), false, leader);
       gemm<kC / 16>(tmem + kColDelta, Operand{smem_u32(sm.r2), kD, false}, bk, idesc_bf16(kD, kD, false, true), true, leader);
       if (leader) commit(&sm.bar[1]);
     }
@@ -606,9 +612,8 @@ int mxk_gdelta_bf16_bwd(const void* q, const void* k, const void* v, const float
   prm.ds0 = ds0;
   prm.status = status;
   prm.B = B; prm.T = T; prm.H = H;
-  if (!tma::make_panel_map(&prm.map_k, k, B, T, H, kD, kC) || !tma::make_panel_map(&prm.map_q, q, B, T, H, kD, kC) ||
-      !tma::make_panel_map(&prm.map_do, d_o, B, T, H, kD, kC) ||
-      !tma::make_plain_map(&prm.map_do_plain, d_o, B, T, H, kD, kC))
+  if (!tma::make_sw_map(&prm.map_k, k, B, T, H, kC, kD) || !tma::make_sw_map(&prm.map_q, q, B, T, H, kC, kD) ||
+      !tma::make_sw_map(&prm.map_do, d_o, B, T, H, kC, kD))
     return MXK_ERR_UNSUPPORTED;
   cudaError_t e = cudaFuncSetAttribute(gdelta_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(BwdSmem)));

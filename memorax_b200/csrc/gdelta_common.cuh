@@ -35,6 +35,17 @@ constexpr int kUVecs = kPanC * kD;      // uint4 per bf16 U^T of one chunk (16 K
 // Residual the forward call leaves per (sequence, chunk): the state entering the chunk, then U^T.
 constexpr int kResidualVecs = kStateVecs + kUVecs;
 
+// A 64 x 128 bf16 tile as SW tiles (umma.cuh): two 64-column blocks of 64 lines x 128 bytes.
+constexpr int kSwBlockVecs = kC * 8;   // uint4 per block (8 KiB)
+// uint4 index of the 16-byte vector `pn` (0..15) of token row `r`
+__device__ __forceinline__ int sw_slot(int r, int pn) { return (pn >> 3) * kSwBlockVecs + umma::sw_idx(r, pn & 7); }
+
+// Element [t][c] of a 64 x 128 bf16 tile stored as SW tiles.
+__device__ __forceinline__ float sw_bf16_at(const uint4* tile, int t, int c) {
+  const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(tile + sw_slot(t, c >> 3));
+  return __bfloat162float(p[c & 7]);
+}
+
 struct ChunkDecay {
   float alpha[kC], beta[kC], cum[kC], g[kC], gam[kC];
 };

@@ -68,15 +68,17 @@ inline bool make_plain_map(CUtensorMap* map, const void* base, int B, int T, int
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Map whose loads write `rows` x 64 tiles (d = 64) as 128-byte-swizzled row-major lines (umma.cuh "SW
-// tiles"): 128-byte pieces, about five times faster per byte than the panel map.  Coordinates as for the
-// plain map, {0, h, t0, b}; the destination must be 1024-byte aligned.
-inline bool make_sw_map(CUtensorMap* map, const void* base, int B, int T, int H, int rows) {
+// Map whose loads write `rows` x 64 column blocks of a [B][T][H][D] tensor as 128-byte-swizzled row-major
+// lines (umma.cuh "SW tiles"): 128-byte pieces, about five times faster per byte than the panel map.
+// Coordinates {c0, h, t0, b} with c0 the first column of the block (a multiple of 64); the destination
+// must be 1024-byte aligned.
+inline bool make_sw_map(CUtensorMap* map, const void* base, int B, int T, int H, int rows, int D = 64) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return false;
-  const cuuint64_t row_bytes = static_cast<cuuint64_t>(H) * 64 * 2;
-  const cuuint64_t dims[4] = {64, static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
-  const cuuint64_t strides[3] = {128, row_bytes, row_bytes * T};
+  const cuuint64_t row_bytes = static_cast<cuuint64_t>(H) * D * 2;
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(T),
+                              static_cast<cuuint64_t>(B)};
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(D) * 2, row_bytes, row_bytes * T};
   const cuuint32_t box[4] = {64, 1, static_cast<cuuint32_t>(rows), 1};
   const cuuint32_t elem[4] = {1, 1, 1, 1};
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, elem,
@@ -97,11 +99,12 @@ __device__ __forceinline__ void load_panel_tile(void* dst, const CUtensorMap* ma
       "l"(reinterpret_cast<uint64_t>(map)), "r"(umma::smem_u32(bar)), "r"(0), "r"(t0), "r"(0), "r"(h), "r"(b)
       : "memory");
 }
-__device__ __forceinline__ void load_plain_tile(void* dst, const CUtensorMap* map, uint64_t* bar, int t0, int h, int b) {
+__device__ __forceinline__ void load_plain_tile(void* dst, const CUtensorMap* map, uint64_t* bar, int t0, int h, int b,
+                                                int c0 = 0) {
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::
           "r"(umma::smem_u32(dst)),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(umma::smem_u32(bar)), "r"(0), "r"(h), "r"(t0), "r"(b)
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(umma::smem_u32(bar)), "r"(c0), "r"(h), "r"(t0), "r"(b)
       : "memory");
 }
 // Contiguous copy; both addresses 16-byte aligned, `bytes` a multiple of 16.

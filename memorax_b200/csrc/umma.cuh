@@ -119,6 +119,21 @@ __device__ __forceinline__ void gemm(uint32_t tmem_d, const Operand& a, const Op
   }
 }
 
+// Operand advanced by `half` * 4 K steps (64 columns of a K = 128 contraction).  For an SW tile
+// contracted over its columns the second half is the next 64-column block (block_stride bytes on).
+__device__ __forceinline__ Operand k_half(Operand o, int half) {
+  if (o.swizzled && !o.contract_rows) o.saddr += half * o.block_stride;
+  else o.saddr += half * 4 * o.advance() * 16;
+  return o;
+}
+// K = 128 contraction as two runs of four K steps, so that SW tiles (two 64-column blocks) and panel
+// operands can be mixed.
+__device__ __forceinline__ void gemm128(uint32_t tmem_d, const Operand& a, const Operand& b, uint32_t idesc,
+                                        bool accumulate, bool leader) {
+  gemm<4>(tmem_d, k_half(a, 0), k_half(b, 0), idesc, accumulate, leader);
+  gemm<4>(tmem_d, k_half(a, 1), k_half(b, 1), idesc, true, leader);
+}
+
 __device__ __forceinline__ void commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
