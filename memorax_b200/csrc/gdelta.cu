@@ -55,6 +55,14 @@ static_assert(sizeof(FwdSmem) <= 112 * 1024, "two CTAs per SM");
 //   columns 128..191  first K K^T (lanes 0..15 of each warp) and Q K^T (lanes 16..31),
 //                     both M = 64; afterwards O^T (all lanes)
 //   columns 192..255  Y^T = S_in K^T
+#ifdef MXK_TIMING
+}  // namespace
+__device__ unsigned long long g_gdf_phase_cycles[16];
+namespace {
+#define MXK_TF(i) do { if (tid == 0 && (blockIdx.x % 37) == 0) { const long long now_ = clock64(); atomicAdd(&g_gdf_phase_cycles[i], (unsigned long long)(now_ - t_prev_)); t_prev_ = now_; } } while (0)
+#else
+#define MXK_TF(i) do {} while (0)
+#endif
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kUpper = 16u << 16;
 constexpr uint32_t kColS = 0, kColKQ = 128, kColO = 128, kColY = 192;
@@ -123,6 +131,9 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_co
   float2 ab_next = fetch_chunk_decay(p.alpha, p.beta, bt_base, p.H, h, 0, p.T, tid);
   linattn::DoneFlags flags_next = linattn::load_done_flags(drow, 0, p.T, lane);
 
+#ifdef MXK_TIMING
+  long long t_prev_ = clock64();
+#endif
   for (int c = 0; c < nchunks; ++c) {
     const int t0 = c * kC;
     const uint64_t dm = linattn::done_mask_from_flags(flags_next);
@@ -138,9 +149,11 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_co
       // the previous chunk's output tile (older group) has left `lt` before epilogue 1a rewrites it
       if (p.chunk_states) tma::wait_group_read<1>(); else tma::wait_group_read<0>();
     }
+    MXK_TF(0);
     if (!mbar_wait(&sm.bar_load, c & 1)) timed_out = true;
     fence_before_sync();
     __syncthreads();
+    MXK_TF(1);
 
     if (warp == 0) {
       const bool leader = elect_one();
@@ -154,6 +167,7 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_co
     }
     if (!mbar_wait(&sm.bar[0], c & 1)) timed_out = true;
     fence_after_sync();
+    MXK_TF(2);
 
     // ---- epilogue 1a: lower lanes turn their K K^T row into -beta L (fp32), upper lanes their
     //      Q K^T row into the masked, decayed bf16 operand; then Q and K are rescaled in place
@@ -193,13 +207,16 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_co
         tile[sw_slot(row, pn)] = pack8_bf16(f);
       }
     }
+    MXK_TF(3);
     // ---- epilogue 1b: thread v solves for its column of U; S <- g_last S in place ----
     __align__(8) float r[kC];
     tmem_ld_row<kC>(lane_base + kColY, r);
 #pragma unroll
     for (int t = 0; t < kC; ++t) r[t] = sm.cd.beta[t] * (bf16_at(sm.vu, t, tid) - sm.cd.g[t] * r[t]);
     __syncthreads();   // -beta L complete; V consumed (U^T reuses its buffer)
+    MXK_TF(4);
     forward_substitute(reinterpret_cast<float2*>(r), sm.lt);
+    MXK_TF(5);
     {
       uint4* res = p.chunk_states ? p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * kResidualVecs + kStateVecs : nullptr;
 #pragma unroll
@@ -222,6 +239,7 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_co
       }
       tmem_st_wait();
     }
+    MXK_TF(6);
     if (tid == 0) tma::wait_group_read<0>();   // the residual copy has finished reading `s` (rewritten in epilogue 2)
     fence_smem_to_async();
     fence_before_sync();
@@ -240,6 +258,7 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_co
     }
     if (!mbar_wait(&sm.bar[1], c & 1)) timed_out = true;
     fence_after_sync();
+    MXK_TF(7);
     if (c + 1 < nchunks) {
       if (tid == 0) issue_chunk_loads(c + 1);
       ab_next = fetch_chunk_decay(p.alpha, p.beta, bt_base, p.H, h, t0 + kC, p.T, tid);
@@ -278,6 +297,7 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_co
       tma::store_plain_tile(&p.map_o, sm.lt, t0, h, b);   // rows past the end of the sequence are clipped
       tma::commit_group();
     }
+    MXK_TF(8);
   }
   if (tid == 0) tma::wait_group_all();
 
@@ -289,6 +309,16 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_co
 
 }  // namespace
 }  // namespace mxk
+
+#ifdef MXK_TIMING
+extern "C" int mxk_debug_gdf_phase_cycles(unsigned long long* out, int reset) {
+  if (reset) {
+    unsigned long long z[16] = {};
+    return (int)cudaMemcpyToSymbol(mxk::g_gdf_phase_cycles, z, sizeof(z));
+  }
+  return (int)cudaMemcpyFromSymbol(out, mxk::g_gdf_phase_cycles, 16 * sizeof(unsigned long long));
+}
+#endif
 
 extern "C" {
 

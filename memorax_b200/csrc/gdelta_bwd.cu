@@ -45,6 +45,8 @@ struct BwdParams {
   int* status;
   int B, T, H;
   CUtensorMap map_k, map_q, map_do;   // 64-token tiles as SW tiles (two 64-column blocks)
+  CUtensorMap map_dq, map_dk;         // the same for the outputs
+  CUtensorMap map_dv;                 // 64-token tiles row-major
 };
 
 // Row stride of the fp32 64 x 64 matrices that threads write row by row: 68 floats keep
@@ -157,8 +159,6 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
   const uint32_t tmem = sm.tmem;
   const uint32_t lane_base = tmem + (static_cast<uint32_t>(qw * 32) << 16);
 
-  const size_t stride_t = static_cast<size_t>(p.H) * kD;
-  const size_t seq_base = (static_cast<size_t>(b) * p.T * p.H + h) * kD;
   const size_t bt_base = static_cast<size_t>(b) * p.T;
   const uint8_t* drow = p.done ? p.done + static_cast<size_t>(b) * p.T : nullptr;
   bool timed_out = false;
@@ -199,7 +199,6 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
     if (tid < 4) sm.dgl[tid] = 0.f;
 
     MXK_TG(0);
-    const size_t tile = seq_base + static_cast<size_t>(t0) * stride_t;
     if (!mbar_wait(&sm.bar_load, it & 1)) timed_out = true;
     // (gam U)^T from row v of U^T, four panels per warpgroup
 #pragma unroll
@@ -211,6 +210,7 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
       for (int e = 0; e < 8; ++e) f[e] *= sm.cd.gam[jp * 8 + e];
       sm.ug[jp * kD + vt] = pack8_bf16(f);
     }
+    if (tid == 0) tma::wait_group_read<0>();   // the previous chunk's dq / dk tiles have left `r1` / `lt`
     fence_smem_to_async();
     fence_before_sync();
     __syncthreads();
@@ -370,16 +370,9 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
     fence_smem_to_async();
     fence_before_sync();
     __syncthreads();
-    {
-      // flush the dV tile
-      __nv_bfloat16* base = p.dv + tile;
-      const uint4* src = reinterpret_cast<const uint4*>(sm.lt);
-#pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const int vid = r * kBwdThreads + tid;
-        const int trow = vid >> 4, seg = vid & 15;
-        if (trow < valid) *reinterpret_cast<uint4*>(base + trow * stride_t + seg * 8) = src[trow * 16 + seg];
-      }
+    if (tid == 0) {   // the dV tile leaves by one TMA store (rows past the end of the sequence are clipped)
+      tma::store_plain_tile(&p.map_dv, sm.lt, t0, h, b);
+      tma::commit_group();
     }
 
     MXK_TG(5);
@@ -394,7 +387,8 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
     if (!mbar_wait(&sm.bar[0], 1)) timed_out = true;
     fence_after_sync();
     MXK_TG(6);
-    __syncthreads();  // every thread has flushed its part of the dV tile before `lt` is reused
+    if (tid == 0) tma::wait_group_read<0>();   // the dV tile has left `lt` before it is reused
+    __syncthreads();
 
     // ---- epilogue C: (dP o G), (dL o G), E, dbeta; g-scaled dO.  Every thread owns 16 keys of
     //      its token row ----
@@ -522,17 +516,17 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
     // ---- epilogue D: dq rows (warpgroup 0), dk rows (warpgroup 1); dS = g_last dS + increment,
     //      64 state columns per warpgroup ----
     {
-      const bool store = !upper && row < valid;
-      __nv_bfloat16* dst = (wg == 0 ? p.dq : p.dk) + tile + static_cast<size_t>(row) * stride_t;
+      // staged as SW tiles in buffers the finished MMAs no longer need (dq in `r1`, dk in `lt`),
+      // stored by TMA after the barrier that ends the chunk
+      uint4* stage = wg == 0 ? sm.r1 : reinterpret_cast<uint4*>(sm.lt);
       const uint32_t col = wg == 0 ? kColDQ : kColDK;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         float acc[kC];
         tmem_ld_row<kC>(lane_base + col + half * kC, acc);
-        if (store) {
+        if (!upper) {
 #pragma unroll
-          for (int pn = 0; pn < kPanC; ++pn)
-            reinterpret_cast<uint4*>(dst)[half * kPanC + pn] = pack8_bf16(acc + pn * 8);
+          for (int pn = 0; pn < kPanC; ++pn) stage[sw_slot(row, half * kPanC + pn)] = pack8_bf16(acc + pn * 8);
         }
       }
       const float g_last = sm.cd.g[kC - 1];
@@ -558,7 +552,17 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
       tmem_st_wait();
     }
     MXK_TG(10);
+    fence_smem_to_async();
+    __syncthreads();
+    if (tid == 0) {
+      tma::store_plain_tile(&p.map_dq, sm.r1, t0, h, b, 0);
+      tma::store_plain_tile(&p.map_dq, sm.r1 + kSwBlockVecs, t0, h, b, 64);
+      tma::store_plain_tile(&p.map_dk, sm.lt, t0, h, b, 0);
+      tma::store_plain_tile(&p.map_dk, reinterpret_cast<uint4*>(sm.lt) + kSwBlockVecs, t0, h, b, 64);
+      tma::commit_group();
+    }
   }
+  if (tid == 0) tma::wait_group_all();
 
   if (timed_out && p.status) atomicExch(p.status, 1);
   fence_before_sync();
@@ -613,7 +617,8 @@ int mxk_gdelta_bf16_bwd(const void* q, const void* k, const void* v, const float
   prm.status = status;
   prm.B = B; prm.T = T; prm.H = H;
   if (!tma::make_sw_map(&prm.map_k, k, B, T, H, kC, kD) || !tma::make_sw_map(&prm.map_q, q, B, T, H, kC, kD) ||
-      !tma::make_sw_map(&prm.map_do, d_o, B, T, H, kC, kD))
+      !tma::make_sw_map(&prm.map_do, d_o, B, T, H, kC, kD) || !tma::make_sw_map(&prm.map_dq, dq, B, T, H, kC, kD) ||
+      !tma::make_sw_map(&prm.map_dk, dk, B, T, H, kC, kD) || !tma::make_plain_map(&prm.map_dv, dv, B, T, H, kD, kC))
     return MXK_ERR_UNSUPPORTED;
   cudaError_t e = cudaFuncSetAttribute(gdelta_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(BwdSmem)));

@@ -116,10 +116,11 @@ __device__ __forceinline__ void load_bulk(void* dst, const void* src, uint32_t b
 }
 // ---- shared -> global (bulk groups of the issuing thread) ----
 // Tile store through a plain map; rows past the end of the sequence are clipped.
-__device__ __forceinline__ void store_plain_tile(const CUtensorMap* map, const void* src, int t0, int h, int b) {
+__device__ __forceinline__ void store_plain_tile(const CUtensorMap* map, const void* src, int t0, int h, int b,
+                                                 int c0 = 0) {
   asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
                    reinterpret_cast<uint64_t>(map)),
-               "r"(umma::smem_u32(src)), "r"(0), "r"(h), "r"(t0), "r"(b)
+               "r"(umma::smem_u32(src)), "r"(c0), "r"(h), "r"(t0), "r"(b)
                : "memory");
 }
 __device__ __forceinline__ void store_bulk(void* dst, const void* src, uint32_t bytes) {
