@@ -67,13 +67,21 @@ constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kUpper = 16u << 16;
 constexpr uint32_t kColS = 0, kColKQ = 128, kColO = 128, kColY = 192;
 
-__global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_constant__ FwdParams p) {
+// 256 threads: two warpgroups that see the same TMEM lanes (warp w and warp w + 4 share a lane
+// quarter).  They split the columns of every row in the epilogues; around the forward
+// substitution warpgroup 0 solves while warpgroup 1 decays the state.
+constexpr int kFwdThreads = 256;
+
+__global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid_constant__ FwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   FwdSmem& sm = *reinterpret_cast<FwdSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wg = warp >> 2;            // warpgroup
+  const int qw = warp & 3;             // TMEM lane quarter of this warp
+  const int vt = tid & 127;            // value row owned in the transposed (M = 128) accumulators
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
   const bool upper = lane >= 16;
-  const int row = warp * 16 + (lane & 15);  // token row owned in the M = 64 accumulators
+  const int row = qw * 16 + (lane & 15);  // token row owned in the M = 64 accumulators
   const int nchunks = (p.T + kC - 1) / kC;
 
   if (tid == 0) {
@@ -87,22 +95,22 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_co
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem = sm.tmem;
-  const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+  const uint32_t lane_base = tmem + (static_cast<uint32_t>(qw * 32) << 16);
 
-  // carried state: thread v owns S[v][.]
+  // carried state: thread (v, wg) owns S[v][64 wg .. 64 wg + 63]
   {
-    const float* s0 = p.s0 ? p.s0 + (static_cast<size_t>(bh) * kD + tid) * kD : nullptr;
-    float vals[kD];   // all loads first: the TMEM stores below are compiler memory barriers
+    const float* s0 = p.s0 ? p.s0 + (static_cast<size_t>(bh) * kD + vt) * kD + wg * 64 : nullptr;
+    float vals[64];   // all loads first: the TMEM stores below are compiler memory barriers
 #pragma unroll
-    for (int c4 = 0; c4 < kD / 4; ++c4) {
+    for (int c4 = 0; c4 < 16; ++c4) {
       float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
       if (s0) x = *reinterpret_cast<const float4*>(s0 + c4 * 4);
       vals[c4 * 4] = x.x; vals[c4 * 4 + 1] = x.y; vals[c4 * 4 + 2] = x.z; vals[c4 * 4 + 3] = x.w;
     }
 #pragma unroll
-    for (int c8 = 0; c8 < kPanD; ++c8) {
-      tmem_st8(lane_base + kColS + c8 * 8, vals + c8 * 8);
-      sm.s[c8 * kD + tid] = pack8_bf16(vals + c8 * 8);
+    for (int c8 = 0; c8 < 8; ++c8) {
+      tmem_st8(lane_base + kColS + wg * 64 + c8 * 8, vals + c8 * 8);
+      sm.s[(wg * 8 + c8) * kD + vt] = pack8_bf16(vals + c8 * 8);
     }
     tmem_st_wait();
   }
@@ -170,28 +178,28 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_co
     MXK_TF(2);
 
     // ---- epilogue 1a: lower lanes turn their K K^T row into -beta L (fp32), upper lanes their
-    //      Q K^T row into the masked, decayed bf16 operand; then Q and K are rescaled in place
-    //      (g_t q_t for the inter-chunk output, gam_j k_j for the state update) ----
+    //      Q K^T row into the masked, decayed bf16 operand, 32 keys per warpgroup; then Q and K are
+    //      rescaled in place (g_t q_t for the inter-chunk output, gam_j k_j for the state update),
+    //      eight 16-byte vectors per thread ----
     {
       const int lo = row_first_key(dm, row);
       const float cum_t = sm.cd.cum[row], beta_t = sm.cd.beta[row];
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      {
         float x[32];
-        tmem_ld_row<32>(lane_base + kColKQ + half * 32, x);
+        tmem_ld_row<32>(lane_base + kColKQ + wg * 32, x);
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
-          const int j = half * 32 + e;
+          const int j = wg * 32 + e;
           const bool in = (j >= lo && j <= row);
           x[e] *= in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
         }
         if (upper) {
 #pragma unroll
-          for (int jq = 0; jq < 4; ++jq) sm.p[(half * 4 + jq) * kC + row] = pack8_bf16(x + jq * 8);
+          for (int jq = 0; jq < 4; ++jq) sm.p[(wg * 4 + jq) * kC + row] = pack8_bf16(x + jq * 8);
         } else {
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
-            const int j = half * 32 + e;
+            const int j = wg * 32 + e;
             sm.lt[j * kC + row] = (j < row) ? -beta_t * x[e] : 0.f;
           }
         }
@@ -199,7 +207,8 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_co
       uint4* tile = upper ? sm.k : sm.q;
       const float sc = upper ? sm.cd.gam[row] : sm.cd.g[row];
 #pragma unroll
-      for (int pn = 0; pn < kPanD; ++pn) {
+      for (int p8 = 0; p8 < kPanD / 2; ++p8) {
+        const int pn = wg * (kPanD / 2) + p8;
         float f[8];
         unpack8_bf16(tile[sw_slot(row, pn)], f);
 #pragma unroll
@@ -208,25 +217,14 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_co
       }
     }
     MXK_TF(3);
-    // ---- epilogue 1b: thread v solves for its column of U; S <- g_last S in place ----
+    // ---- epilogue 1b.  Warpgroup 0, thread v: right-hand side and forward substitution for its
+    //      column of U.  Warpgroup 1 meanwhile: S <- g_last S in place. ----
     __align__(8) float r[kC];
-    tmem_ld_row<kC>(lane_base + kColY, r);
+    if (wg == 0) {
+      tmem_ld_row<kC>(lane_base + kColY, r);
 #pragma unroll
-    for (int t = 0; t < kC; ++t) r[t] = sm.cd.beta[t] * (bf16_at(sm.vu, t, tid) - sm.cd.g[t] * r[t]);
-    __syncthreads();   // -beta L complete; V consumed (U^T reuses its buffer)
-    MXK_TF(4);
-    forward_substitute(reinterpret_cast<float2*>(r), sm.lt);
-    MXK_TF(5);
-    {
-      uint4* res = p.chunk_states ? p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * kResidualVecs + kStateVecs : nullptr;
-#pragma unroll
-      for (int jp = 0; jp < kPanC; ++jp) {
-        const uint4 u8 = pack8_bf16(r + jp * 8);
-        sm.vu[jp * kD + tid] = u8;
-        if (res) res[jp * kD + tid] = u8;   // the backward pass reuses U instead of solving again
-      }
-    }
-    {
+      for (int t = 0; t < kC; ++t) r[t] = sm.cd.beta[t] * (bf16_at(sm.vu, t, vt) - sm.cd.g[t] * r[t]);
+    } else {
       const float g_last = sm.cd.g[kC - 1];
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
@@ -239,6 +237,19 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_co
       }
       tmem_st_wait();
     }
+    __syncthreads();   // -beta L complete; V consumed (U^T reuses its buffer)
+    MXK_TF(4);
+    if (wg == 0) {
+      forward_substitute(reinterpret_cast<float2*>(r), sm.lt);
+      uint4* res = p.chunk_states ? p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * kResidualVecs + kStateVecs : nullptr;
+#pragma unroll
+      for (int jp = 0; jp < kPanC; ++jp) {
+        const uint4 u8 = pack8_bf16(r + jp * 8);
+        sm.vu[jp * kD + vt] = u8;
+        if (res) res[jp * kD + vt] = u8;   // the backward pass reuses U instead of solving again
+      }
+    }
+    MXK_TF(5);
     MXK_TF(6);
     if (tid == 0) tma::wait_group_read<0>();   // the residual copy has finished reading `s` (rewritten in epilogue 2)
     fence_smem_to_async();
@@ -265,25 +276,26 @@ __global__ void __launch_bounds__(kThreads, 2) gdelta_fwd_kernel(const __grid_co
       flags_next = linattn::load_done_flags(drow, t0 + kC, p.T, lane);
     }
 
-    // ---- epilogue 2: output tile (staged for 16-byte stores), bf16 copy of the new state ----
+    // ---- epilogue 2: output tile (staged row-major for one TMA store), bf16 copy of the new state;
+    //      thread (v, wg) covers tokens 32 wg .. 32 wg + 31 and state columns 64 wg .. 64 wg + 63 ----
     {
       __nv_bfloat16* otile = reinterpret_cast<__nv_bfloat16*>(sm.lt);
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      {
         float o[32];
-        tmem_ld_row<32>(lane_base + kColO + half * 32, o);
+        tmem_ld_row<32>(lane_base + kColO + wg * 32, o);
 #pragma unroll
-        for (int e = 0; e < 32; ++e) otile[(half * 32 + e) * kD + tid] = __float2bfloat16(o[e]);
+        for (int e = 0; e < 32; ++e) otile[(wg * 32 + e) * kD + vt] = __float2bfloat16(o[e]);
       }
       const bool last = (c == nchunks - 1);
-      float* sl = (last && p.s_last) ? p.s_last + (static_cast<size_t>(bh) * kD + tid) * kD : nullptr;
+      float* sl = (last && p.s_last) ? p.s_last + (static_cast<size_t>(bh) * kD + vt) * kD : nullptr;
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
+      for (int q2 = 0; q2 < 2; ++q2) {
+        const int q4 = wg * 2 + q2;
         float s[32];
         tmem_ld_row<32>(lane_base + kColS + q4 * 32, s);
 #pragma unroll
         for (int c8 = 0; c8 < 4; ++c8) {
-          sm.s[(q4 * 4 + c8) * kD + tid] = pack8_bf16(s + c8 * 8);
+          sm.s[(q4 * 4 + c8) * kD + vt] = pack8_bf16(s + c8 * 8);
           if (sl) {
             *reinterpret_cast<float4*>(sl + q4 * 32 + c8 * 8) = make_float4(s[c8 * 8], s[c8 * 8 + 1], s[c8 * 8 + 2], s[c8 * 8 + 3]);
             *reinterpret_cast<float4*>(sl + q4 * 32 + c8 * 8 + 4) = make_float4(s[c8 * 8 + 4], s[c8 * 8 + 5], s[c8 * 8 + 6], s[c8 * 8 + 7]);
@@ -357,7 +369,7 @@ int mxk_gdelta_bf16_fwd(const void* q, const void* k, const void* v, const float
   cudaError_t e = cudaFuncSetAttribute(gdelta_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(FwdSmem)));
   if (e != cudaSuccess) return static_cast<int>(e);
-  gdelta_fwd_kernel<<<B * H, kThreads, sizeof(FwdSmem), static_cast<cudaStream_t>(stream)>>>(prm);
+  gdelta_fwd_kernel<<<B * H, kFwdThreads, sizeof(FwdSmem), static_cast<cudaStream_t>(stream)>>>(prm);
   return launch_status();
 }
 
