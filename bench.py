@@ -55,7 +55,7 @@ class LinAttnC2:
     dominant = "linattn_bwd_kernel"
     launches_per_step = 2
     e2e_slices = 4   # independent sequences: copy-in, kernels and copy-out overlap slice by slice
-    e2e_graph = True
+    e2e_mode = "stream"
     # dram__bytes_read.sum + dram__bytes_write.sum of one linattn_bwd_kernel launch at
     # this size (ncu capture summarised under profiles/)
     dominant_traffic_bytes = 254.0e6
@@ -214,7 +214,7 @@ class GDeltaC3:
     dominant = "gdelta_bwd_kernel"
     launches_per_step = 2
     e2e_slices = 4
-    e2e_graph = True
+    e2e_mode = "stream"
     dominant_traffic_bytes = None
     cpu_sample_batch = 4
 
@@ -546,13 +546,18 @@ def run_gpu_arm(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     from memorax_b200.host import HostPipeline
     nslices = args.e2e_slices or getattr(w, "e2e_slices", 1)
-    use_graph = bool(getattr(w, "e2e_graph", False)) and not args.no_e2e_graph
-    pipe = HostPipeline(lambda xs: w.step(xs, ops), w.B, dev, slices=nslices, graph=use_graph)
+    # "stream": consecutive steps overlap (copy-in of step i+1 under the copy-out of step i, at most two
+    # steps in flight); "graph": one CUDA-graph replay per step; "plain": call by call
+    mode = args.e2e_mode or getattr(w, "e2e_mode", "plain")
+    pipe = HostPipeline(lambda xs: w.step(xs, ops), w.B, dev, slices=nslices, graph=(mode == "graph"),
+                        overlap_calls=2 if mode == "stream" else 1)
     pipe.run(pinned_in, pinned_out)          # warm the three streams' allocator pools
+    pipe.wait()
     barrier()
     e0.record()
     for _ in range(e2e_steps):
         pipe.run(pinned_in, pinned_out)
+    pipe.join()
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
@@ -584,7 +589,9 @@ def run_gpu_arm(args):
             "clocks": clocks.summary(),
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "batch_slices_in_flight": nslices,
-                    "launch": "cuda graph replay of the three-stream schedule" if use_graph else "direct"},
+                    "mode": {"stream": "three streams, copy-in of step i+1 overlaps copy-out of step i (two steps in flight)",
+                             "graph": "cuda graph replay of the three-stream schedule",
+                             "plain": "three streams, step by step"}[mode]},
             "gpu_launches": w.launches_per_step * args.steps,
             "roofline": roof,
         }
@@ -604,7 +611,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=None, help="override sequences per GPU (profiling only)")
     ap.add_argument("--e2e-slices", type=int, default=None, help="override the batch slices of the host pipeline")
-    ap.add_argument("--no-e2e-graph", action="store_true", help="enqueue the host pipeline call by call instead of replaying a graph")
+    ap.add_argument("--e2e-mode", choices=["stream", "graph", "plain"], default=None, help="host pipeline mode for the e2e figure")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -158,7 +158,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
       if (p.chunk_states) tma::wait_group_read<1>(); else tma::wait_group_read<0>();
     }
     MXK_TF(0);
-    if (!mbar_wait(&sm.bar_load, c & 1)) timed_out = true;
+    mbar_wait_flag(&sm.bar_load, c & 1, timed_out);
     fence_before_sync();
     __syncthreads();
     MXK_TF(1);
@@ -173,7 +173,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
       gemm128(tmem + kColY, as, ak, id_128x64, false, leader);           // Y^T = S_in K^T
       if (leader) commit(&sm.bar[0]);
     }
-    if (!mbar_wait(&sm.bar[0], c & 1)) timed_out = true;
+    mbar_wait_flag(&sm.bar[0], c & 1, timed_out);
     fence_after_sync();
     MXK_TF(2);
 
@@ -267,7 +267,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
       gemm<kC / 16>(tmem + kColS, au, bgk, id_ds, true, leader);        // S    = g_last S_in + U^T (gam K)
       if (leader) commit(&sm.bar[1]);
     }
-    if (!mbar_wait(&sm.bar[1], c & 1)) timed_out = true;
+    mbar_wait_flag(&sm.bar[1], c & 1, timed_out);
     fence_after_sync();
     MXK_TF(7);
     if (c + 1 < nchunks) {

@@ -199,7 +199,7 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
     if (tid < 4) sm.dgl[tid] = 0.f;
 
     MXK_TG(0);
-    if (!mbar_wait(&sm.bar_load, it & 1)) timed_out = true;
+    mbar_wait_flag(&sm.bar_load, it & 1, timed_out);
     // (gam U)^T from row v of U^T, four panels per warpgroup
 #pragma unroll
     for (int j4 = 0; j4 < kPanC / 2; ++j4) {
@@ -238,7 +238,7 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
       gemm128(tmem + kColX2, ads, ak, id_128, false, leader);
       if (leader) commit(&sm.bar[0]);
     }
-    if (!mbar_wait(&sm.bar[0], 0)) timed_out = true;
+    mbar_wait_flag(&sm.bar[0], 0, timed_out);
     fence_after_sync();
     MXK_TG(2);
 
@@ -293,7 +293,7 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
       gemm128(tmem + kUpper + kColDP, sw_operand(smem_u32(sm.d_o), false, kBlk), Operand{smem_u32(sm.u) + 4 * kD * 16, kD, true}, idesc_bf16(kC, 32, false, true), false, leader);
       if (leader) commit(&sm.bar[1]);
     }
-    if (!mbar_wait(&sm.bar[1], 0)) timed_out = true;
+    mbar_wait_flag(&sm.bar[1], 0, timed_out);
     fence_after_sync();
     MXK_TG(4);
 
@@ -384,7 +384,7 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
       gemm<kD / 16>(tmem + kUpper + kColW, Operand{smem_u32(sm.r1), kD, true}, Operand{smem_u32(sm.u) + 4 * kD * 16, kD, true}, idesc_bf16(kC, 32, true, true), false, leader);
       if (leader) commit(&sm.bar[0]);
     }
-    if (!mbar_wait(&sm.bar[0], 1)) timed_out = true;
+    mbar_wait_flag(&sm.bar[0], 1, timed_out);
     fence_after_sync();
     MXK_TG(6);
     if (tid == 0) tma::wait_group_read<0>();   // the dV tile has left `lt` before it is reused
@@ -503,7 +503,7 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
     }
 
     MXK_TG(8);
-    if (!mbar_wait(&sm.bar[1], 1)) timed_out = true;
+    mbar_wait_flag(&sm.bar[1], 1, timed_out);
     fence_after_sync();
     MXK_TG(9);
     // the MMAs above were the last readers of the staged tiles: fetch the next chunk

@@ -158,7 +158,7 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
 
     // ---- the tiles have landed: feature map in place, keep-masked copy of V only if the
     //      chunk has a reset ----
-    if (!mbar_wait(&sm.bar_load, c & 1)) timed_out = true;
+    mbar_wait_flag(&sm.bar_load, c & 1, timed_out);
     MXK_T(8);
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
@@ -203,7 +203,7 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
         tma::commit_group();
       }
     }
-    if (!mbar_wait(&sm.bar[0], c & 1)) timed_out = true;
+    mbar_wait_flag(&sm.bar[0], c & 1, timed_out);
     fence_after_sync();
     MXK_T(3);
 
@@ -259,7 +259,7 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
       gemm<kC / 16>(tmem, ap, bv, idesc_o, true, leader);       // O += mask(P) (V|1)
       if (leader) commit(&sm.bar[1]);
     }
-    if (!mbar_wait(&sm.bar[1], c & 1)) timed_out = true;
+    mbar_wait_flag(&sm.bar[1], c & 1, timed_out);
     fence_after_sync();
     if (tid == 0 && c + 1 < nchunks) issue_chunk_loads(c + 1);
     MXK_T(6);

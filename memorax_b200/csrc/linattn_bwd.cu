@@ -205,7 +205,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
 
     // ---- the tiles have landed: feature map in place; keep-masked copies of phi(K) and V|1
     //      only if the chunk has a reset ----
-    if (!mbar_wait(&sm.bar_load, it & 1)) timed_out = true;
+    mbar_wait_flag(&sm.bar_load, it & 1, timed_out);
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       // element-wise, so the physical vector index serves (8 vectors = one token row)
@@ -254,7 +254,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
       if (leader) commit(&sm.bar[0]);
     }
     MXK_TB(8);
-    if (!mbar_wait(&sm.bar[0], it & 1)) timed_out = true;
+    mbar_wait_flag(&sm.bar[0], it & 1, timed_out);
     fence_after_sync();
     MXK_TB(2);
 
@@ -367,10 +367,10 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
       for (int pn = 0; pn < 4; ++pn) featv[pn] = feat[sw_idx(row, wg * 4 + pn)];
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.bar_free)) : "memory");
     }
-    if (!mbar_wait(&sm.bar[1], it & 1)) timed_out = true;
+    mbar_wait_flag(&sm.bar[1], it & 1, timed_out);
     fence_after_sync();
     if (tid == 0 && c > 0) {   // in flight while the output epilogue runs
-      if (!mbar_wait(&sm.bar_free, it & 1)) timed_out = true;
+      mbar_wait_flag(&sm.bar_free, it & 1, timed_out);
       issue_chunk_loads(c - 1);
     }
     MXK_TB(4);

@@ -176,6 +176,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int li
   return ok != 0;
 }
 
+// The form the kernels use: records a wait that gave up in `timed_out`, and once one has, later
+// waits of the same thread poll only once, so a kernel whose copies or MMAs never complete still
+// drains in about a second instead of a second per wait.
+__device__ __forceinline__ void mbar_wait_flag(uint64_t* bar, uint32_t parity, bool& timed_out) {
+  if (!mbar_wait(bar, parity, timed_out ? 1 : 1024)) timed_out = true;
+}
+
 // ---- TMEM <-> registers (each thread: its own lane, 8 consecutive columns) ----
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float* out) {
   uint32_t r[8];

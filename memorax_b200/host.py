@@ -9,7 +9,13 @@ and the two copy directions and the kernels overlap.
 With ``graph=True`` the whole three-stream schedule of one call is captured into a
 CUDA graph the first time a given set of host buffers is seen and replayed
 afterwards, so that a step costs one launch on the host however many slices it has
-(the usual pattern: the caller refills the same pinned staging buffers every step)."""
+(the usual pattern: the caller refills the same pinned staging buffers every step).
+
+With ``overlap_calls=N`` (eager mode) consecutive calls stream: the copy-in of call
+i+1 no longer waits for the copy-out of call i (host inputs have no producer on the
+device), so both copy engines stay busy across calls; at most N calls are in flight.
+The caller then must not rewrite a host input buffer before ``inputs_consumed`` (an
+event recorded after the last copy-in of the latest call) has completed."""
 from __future__ import annotations
 
 import torch
@@ -27,10 +33,15 @@ class HostPipeline:
     data-dependent host control flow) and the host tensors must stay alive and in
     place for as long as the pipeline is used with them."""
 
-    def __init__(self, step, batch, device, slices=4, graph=False):
+    def __init__(self, step, batch, device, slices=4, graph=False, overlap_calls=1):
+        if graph and overlap_calls > 1:
+            raise ValueError("overlap_calls applies to the eager mode: replayed graphs run back to back")
         self.step, self.batch, self.device = step, batch, device
         self.slices = max(1, min(slices, batch))
         self.graph = graph
+        self.overlap_calls = max(1, int(overlap_calls))
+        self._finished = []          # completion events of the calls still in flight, oldest first
+        self.inputs_consumed = None
         self._graphs = {}
         self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(device=device) for _ in range(3))
         self.s_capture = torch.cuda.Stream(device=device) if graph else None
@@ -60,8 +71,15 @@ class HostPipeline:
         main = torch.cuda.current_stream(self.device)
         start = torch.cuda.Event()
         start.record(main)
-        for s in (self.s_in, self.s_run, self.s_out):
+        streaming = self.overlap_calls > 1 and not capturing
+        # kernels and copy-out always follow the caller's stream (weights or other device state the step
+        # reads); the copy-in does too unless calls may overlap, in which case it only waits for the call
+        # `overlap_calls` back, which bounds the device buffers in flight
+        for s in ((self.s_run, self.s_out) if streaming else (self.s_in, self.s_run, self.s_out)):
             s.wait_event(start)
+        if streaming and len(self._finished) >= self.overlap_calls:
+            self.s_in.wait_event(self._finished[-self.overlap_calls])
+            del self._finished[:-self.overlap_calls]
         keep = []
         shared = {}
         for i in range(self.slices):
@@ -99,5 +117,24 @@ class HostPipeline:
             keep.append((x, outs))
         finished = torch.cuda.Event()
         finished.record(self.s_out)
-        main.wait_event(finished)
+        if streaming:
+            # the caller's stream is NOT made to wait here (that would serialise the next call's kernels
+            # behind this call's copy-out); call wait() before reading the host outputs
+            self._finished.append(finished)
+            self.inputs_consumed = ready
+        else:
+            main.wait_event(finished)
         return keep
+
+    def join(self):
+        """Makes the caller's current stream wait (on the device) for every call issued so far."""
+        main = torch.cuda.current_stream(self.device)
+        for ev in self._finished:
+            main.wait_event(ev)
+
+    def wait(self):
+        """Blocks the host until every call issued so far has delivered its host outputs."""
+        for ev in self._finished:
+            ev.synchronize()
+        self._finished.clear()
+        torch.cuda.current_stream(self.device).synchronize()

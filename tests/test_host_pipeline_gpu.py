@@ -66,3 +66,34 @@ def test_host_pipeline_graph_replay_tracks_buffer_contents():
         for got, want in zip(outs, ref):
             assert torch.equal(got, want.cpu()), trial
     assert len(pipe._graphs) == 1
+
+
+def test_host_pipeline_overlapping_calls():
+    """overlap_calls=2: calls stream (copy-in of call i+1 under the copy-out of call i); every call must
+    still deliver exactly the single-call results into its own output buffers."""
+    from memorax_b200 import ops
+    from memorax_b200.host import HostPipeline
+    g = torch.Generator().manual_seed(2)
+    B, T, H, D = 9, 200, 2, 64
+    mk = lambda *s: torch.randn(*s, generator=g)
+
+    def fresh():
+        d = dict(q=(mk(B, T, H, D) / 8).bfloat16(), k=(mk(B, T, H, D) / 8).bfloat16(), v=(mk(B, T, H, D) / 8).bfloat16(),
+                 s0=mk(B, H, D, D) * 0.1, z0=mk(B, H, D).abs() * 0.1, done=(torch.rand(B, T, generator=g) < 0.02).to(torch.uint8))
+        return {k: v.pin_memory() for k, v in d.items()}
+
+    def step(x):
+        o, s_last, z_last, _ = ops.linattn_fwd(x["q"], x["k"], x["v"], x["s0"], x["z0"], x["done"])
+        return o, s_last, z_last
+
+    calls = [fresh() for _ in range(5)]
+    refs = [step({k: v.cuda() for k, v in c.items()}) for c in calls]
+    outs = [[torch.zeros(r.shape, dtype=r.dtype).pin_memory() for r in ref] for ref in refs]
+    pipe = HostPipeline(step, B, torch.device("cuda", 0), slices=3, overlap_calls=2)
+    for c, o in zip(calls, outs):
+        pipe.run(c, o)
+    pipe.wait()
+    for i, (ref, out) in enumerate(zip(refs, outs)):
+        for got, want in zip(out, ref):
+            assert torch.equal(got, want.cpu()), i
+    assert pipe.inputs_consumed is not None and pipe.inputs_consumed.query()
