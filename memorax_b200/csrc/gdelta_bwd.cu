@@ -68,7 +68,10 @@ struct BwdSmem {
   float l[kC * kLS];        // l[t][j] = -beta_t L_tj        -> E[t][j]   (row stride kLS)
   float lt[kC * kC];        // lt[j][t] = -beta_t L_tj       -> dV tile -> (dP o G), (dL o G) panels
   ChunkDecay cd;
-  float dg[kC], dgam[kC], rowsum[kC], colsum[kC], dcum[kC];
+  // per-warp partial sums of the decay cotangents, combined in a fixed order (no floating-point atomics:
+  // the results are bit-reproducible)
+  float dg_a[4][kC], dg_b[4][kC], dgam_p[4][kC];
+  float rowsum[kC], colsum[kC], dcum[kC];
   float dgl[4];
   uint64_t bar[2];
   uint64_t bar_load;
@@ -196,7 +199,7 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
     const uint64_t dm = linattn::done_mask_from_flags(flags_next);
     __syncthreads();
     chunk_decay_from_regs(sm.cd, ab_next, dm, tid);
-    if (tid < kC) sm.dg[tid] = sm.dgam[tid] = sm.rowsum[tid] = 0.f;
+    if (tid < kC) sm.rowsum[tid] = 0.f;   // two contributions per row: order-independent
     if (tid < 4) sm.dgl[tid] = 0.f;
 
     MXK_TG(0);
@@ -277,7 +280,7 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
 #pragma unroll
       for (int t = 0; t < 32; ++t) r[t] *= sw_bf16_at(sm.d_o, wg * 32 + t, vt);
       warp_reduce<32>(r, lane);
-      atomicAdd(&sm.dg[wg * 32 + lane], r[0]);
+      sm.dg_a[qw][wg * 32 + lane] = r[0];
     }
     fence_smem_to_async();
     fence_before_sync();
@@ -332,8 +335,8 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
       }
       MXK_TG(13);
       warp_reduce<64>(ga, lane);
-      atomicAdd(&sm.dg[2 * lane], ga[0]);
-      atomicAdd(&sm.dg[2 * lane + 1], ga[1]);
+      sm.dg_b[qw][2 * lane] = ga[0];
+      sm.dg_b[qw][2 * lane + 1] = ga[1];
       MXK_TG(14);
     } else {
       // dgam_j = sum_v u_j[v] (dS k_j)[v]
@@ -347,8 +350,8 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
         for (int e = 0; e < 8; ++e) ga[jp * 8 + e] *= uf[e];
       }
       warp_reduce<64>(ga, lane);
-      atomicAdd(&sm.dgam[2 * lane], ga[0]);
-      atomicAdd(&sm.dgam[2 * lane + 1], ga[1]);
+      sm.dgam_p[qw][2 * lane] = ga[0];
+      sm.dgam_p[qw][2 * lane + 1] = ga[1];
 
       // <dS, S_in> for the g_last gradient
       float dot = 0.f;
@@ -483,8 +486,11 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
       float cs = 0.f;
 #pragma unroll 8
       for (int t = 0; t < kC; ++t) cs += sm.l[t * kLS + tid];
-      sm.dcum[tid] = sm.rowsum[tid] - cs + sm.dg[tid] * sm.cd.g[tid] - sm.dgam[tid] * sm.cd.gam[tid];
-      sm.colsum[tid] = sm.dgam[tid] * sm.cd.gam[tid];
+      const float dg = ((sm.dg_a[0][tid] + sm.dg_a[1][tid]) + (sm.dg_a[2][tid] + sm.dg_a[3][tid])) +
+                       ((sm.dg_b[0][tid] + sm.dg_b[1][tid]) + (sm.dg_b[2][tid] + sm.dg_b[3][tid]));
+      const float dgam = (sm.dgam_p[0][tid] + sm.dgam_p[1][tid]) + (sm.dgam_p[2][tid] + sm.dgam_p[3][tid]);
+      sm.dcum[tid] = sm.rowsum[tid] - cs + dg * sm.cd.g[tid] - dgam * sm.cd.gam[tid];
+      sm.colsum[tid] = dgam * sm.cd.gam[tid];
     }
     __syncthreads();
     if (tid < 32) {
