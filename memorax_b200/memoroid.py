@@ -87,6 +87,25 @@ class Memoroid(SequenceModel):
     def initialize_carry(self, key, input_shape):
         return self.cell.initialize_carry(key, input_shape)
 
+    def propagate_sensitivities(self, decay, jacobians, sensitivity, done):
+        """RTRL sensitivities after T steps (``Memoroid._propagate_sensitivities``,
+        memoroid.py:114-141): for every parameter leaf, S_t = done_t ? J_t : decay_t S_{t-1} + J_t
+        with ``decay`` (B,T,H) broadcast over the leaf's parameter axes, ``jacobians[name]``
+        (B,T,H,*param_shape), ``sensitivity[name]`` (B,1,H,*param_shape); returns the dict of
+        S_T, shaped like ``sensitivity``.  One real linear-recurrence launch per leaf -- the
+        reference's ``where(done, 0, decay)`` is the kernel's reset rule."""
+        bsz, steps, hid = decay.shape
+        out = {}
+        for name in sorted(jacobians.keys()):
+            jac, sens = jacobians[name], sensitivity[name]
+            param_shape = tuple(jac.shape[3:])
+            psize = math.prod(param_shape)
+            a = decay.float().repeat_interleave(psize, dim=-1)
+            h, _ = ops.linrec_fwd(a, jac.float().reshape(bsz, steps, hid * psize),
+                                  sens.float().reshape(bsz, hid * psize), None, done, want_decay=False)
+            out[name] = h[:, -1:].reshape(bsz, 1, hid, *param_shape)
+        return out
+
 
 # ---------------------------------------------------------------------- LRU
 class LRUCell(MemoroidCellBase):

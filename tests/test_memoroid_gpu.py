@@ -86,3 +86,20 @@ def test_s5_module_matches_oracle(disc):
     assert float((y.detach().cpu().double() - y_ref).abs().max()) <= 1e-4 * max(1.0, float(y_ref.abs().max()))
     y.square().mean().backward()
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in cell.parameters())
+
+
+def test_propagate_sensitivities_matches_the_reference_vectors():
+    """Memoroid.propagate_sensitivities against the vectors produced by the reference's own
+    ``_propagate_sensitivities`` source (tests/golden/make_golden.py)."""
+    import os
+    import numpy as np
+    from memorax_b200.memoroid import Memoroid, LRUCell
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "memoroid_golden.npz"))
+    model = Memoroid(LRUCell(4, 4))
+    f32 = lambda a: torch.from_numpy(np.asarray(a)).float().cuda()
+    nxt = model.propagate_sensitivities(f32(g["rt_decay"]), {"w": f32(g["rt_jac"])}, {"w": f32(g["rt_sens"])},
+                                        torch.from_numpy(g["rt_done"]).cuda())
+    ref = torch.from_numpy(g["rt_next"])
+    assert nxt["w"].shape == ref.shape
+    err = float((nxt["w"].double().cpu() - ref).abs().max())
+    assert err <= 1e-5 * max(1.0, float(ref.abs().max())), err
