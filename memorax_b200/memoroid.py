@@ -352,3 +352,92 @@ class S5Cell(MemoroidCellBase):
         h0, a0 = _squeeze_carry(initial_carry, 2)
         h, a_last = ops.LinRec.apply(lambda_bar, state.contiguous(), h0, a0, done)
         return (h[:, -1:], a_last[:, None]), self.read((h, None), inputs)
+
+
+# -------------------------------------------------------------------- Mamba
+class MambaCell(MemoroidCellBase):
+    """Selective state-space cell (mamba.py:33-150): per head a (state_dim x head_dim) matrix
+    state with one scalar decay per (b, t, head).  Elements and read-out follow the
+    reference -- ``h_t = (dt B_t) (x) x_t`` (mamba.py:109-117), operator
+    ``(decay_j h_i + h_j, decay_j decay_i)`` (:119-122), ``y = C . h + D x`` gated by
+    ``silu(z)`` after an RMSNorm (:124-135) -- and, like the reference, the scan runs over the
+    materialised (B, T, H, N, P) elements: here as ONE real linear-recurrence launch over
+    H*N*P channels (forward and backward through ``ops.LinRec``) instead of ~2 log2(T) passes."""
+
+    def __init__(self, features, num_heads=8, head_dim=16, state_dim=16, conv_dim=4, in_features=None):
+        super().__init__()
+        self.features, self.num_heads, self.head_dim, self.state_dim = features, num_heads, head_dim, state_dim
+        self.conv_dim = conv_dim
+        fin = in_features or features
+        hidden, sproj = num_heads * head_dim, num_heads * state_dim
+        self.A_log = nn.Parameter(torch.log(torch.empty(num_heads).uniform_(1.0, 16.0)))
+        self.D = nn.Parameter(torch.ones(num_heads))
+        dt0 = torch.exp(torch.rand(num_heads) * (math.log(0.1) - math.log(0.001)) + math.log(0.001))
+        self.dt_bias = nn.Parameter(dt0 + torch.log(-torch.expm1(-dt0)))
+        self.input_projection = nn.Linear(fin, 2 * hidden, bias=False)
+        self.B = nn.Linear(fin, sproj, bias=False)
+        self.C = nn.Linear(fin, sproj, bias=False)
+        self.dt = nn.Linear(fin, num_heads, bias=False)
+        channels = hidden + 2 * sproj
+        self.conv = nn.Conv1d(channels, channels, conv_dim, groups=channels, padding=conv_dim - 1)
+        self.norm = nn.RMSNorm(hidden)
+        self.output_projection = nn.Linear(hidden, features)
+
+    def _project(self, x):
+        bsz, steps, _ = x.shape
+        hidden_dim, sproj = self.num_heads * self.head_dim, self.num_heads * self.state_dim
+        hidden, gate = self.input_projection(x).chunk(2, dim=-1)
+        conv_in = torch.cat([hidden, self.B(x), self.C(x)], dim=-1).transpose(1, 2)
+        conv = torch.nn.functional.silu(self.conv(conv_in)[..., :steps]).transpose(1, 2)   # causal (left padding)
+        hidden = conv[..., :hidden_dim].reshape(bsz, steps, self.num_heads, self.head_dim)
+        b_proj = conv[..., hidden_dim:hidden_dim + sproj].reshape(bsz, steps, self.num_heads, self.state_dim)
+        c_proj = conv[..., hidden_dim + sproj:].reshape(bsz, steps, self.num_heads, self.state_dim)
+        dt = torch.nn.functional.softplus(self.dt(x) + self.dt_bias)
+        return hidden, b_proj, c_proj, gate, dt
+
+    def forward(self, x, **kwargs):
+        """-> (h (B,T,H,N,P), decay (B,T,H,1,1)) as mamba.py:109-117, plus what ``read`` needs."""
+        hidden, b_proj, c_proj, gate, dt = self._project(x)
+        decay = torch.exp(dt * -torch.exp(self.A_log))[..., None, None]
+        h = torch.einsum("bthn,bthd->bthnd", b_proj * dt[..., None], hidden)
+        return h, decay, (hidden, c_proj, gate)
+
+    def binary_operator(self, a, b):
+        h_i, d_i = a
+        h_j, d_j = b
+        return d_j * h_i + h_j, d_j * d_i
+
+    def read_state(self, h, hidden, c_proj):
+        """The read-out in front of the norm and the gate: ``C . h + D x`` (mamba.py:130-131)."""
+        return torch.einsum("bthn,bthnd->bthd", c_proj, h) + self.D[None, None, :, None] * hidden
+
+    def read(self, h, x, projected=None, **kwargs):
+        state, _ = h
+        hidden, c_proj, gate = projected if projected is not None else self.forward(x)[2]
+        bsz, steps = state.shape[:2]
+        y = self.read_state(state, hidden, c_proj).reshape(bsz, steps, self.num_heads * self.head_dim)
+        return self.output_projection(self.norm(y) * torch.nn.functional.silu(gate))
+
+    def initialize_carry(self, key, input_shape):
+        *batch, _ = input_shape
+        return (torch.zeros(*batch, 1, self.num_heads, self.state_dim, self.head_dim),
+                torch.ones(*batch, 1, self.num_heads, 1, 1))
+
+    def scan_elements(self, h_elems, decay, initial_carry, done):
+        """The time scan alone: elements (B,T,H,N,P), decay (B,T,H,1,1), carry as
+        ``initialize_carry`` -> (h (B,T,H,N,P), next_carry)."""
+        bsz, steps, heads, sdim, hdim = h_elems.shape
+        width = heads * sdim * hdim
+        a = decay.expand(bsz, steps, heads, sdim, hdim).reshape(bsz, steps, width).contiguous()
+        h0 = a0 = None
+        if initial_carry is not None:
+            h0 = initial_carry[0].reshape(bsz, width).contiguous()
+            a0 = initial_carry[1].expand(bsz, 1, heads, sdim, hdim).reshape(bsz, width).contiguous()
+        h, a_last = ops.LinRec.apply(a, h_elems.reshape(bsz, steps, width).contiguous(), h0, a0, done)
+        h = h.reshape(bsz, steps, heads, sdim, hdim)
+        return h, (h[:, -1:], a_last.reshape(bsz, 1, heads, sdim, hdim)[..., :1, :1])
+
+    def scan(self, z, initial_carry, done, inputs):
+        h_elems, decay, projected = z
+        h, next_carry = self.scan_elements(h_elems, decay, initial_carry, done)
+        return next_carry, self.read((h, None), inputs, projected=projected)

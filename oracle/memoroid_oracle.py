@@ -237,6 +237,31 @@ def gdelta_seq(q, k, v, alpha, beta, s0, done):
     return torch.stack(out, dim=1), s
 
 
+def mamba_seq(hidden, b_proj, c_proj, dt, a_neg, d_skip, h0, done, a0=None):
+    """Selective state-space scan of ``MambaCell`` (mamba.py:109-135) under the reset rule
+    of ``Memoroid.scan_fn``: per head, with ``decay_t = exp(dt_t A)`` (A < 0, one scalar per
+    head) and ``z_t = (dt_t B_t) (x) x_t`` (state_dim x head_dim),
+    ``h_t = done_t ? z_t : decay_t h_{t-1} + z_t``, ``y_t = C_t . h_t + D x_t``.
+
+    hidden (B,T,H,P), b_proj / c_proj (B,T,H,N), dt (B,T,H), a_neg / d_skip (H,),
+    h0 (B,H,N,P), a0 the carry's decay leaf (B,H) or None for ones.
+    Returns y (B,T,H,P), the last state (B,H,N,P) and the decay leaf of the next carry (B,H).
+    """
+    bsz, steps = dt.shape[:2]
+    decay = torch.exp(dt * a_neg)                                                   # (B,T,H)
+    z = torch.einsum("bthn,bthd->bthnd", b_proj * dt[..., None], hidden)            # mamba.py:114
+    h = h0
+    acc = torch.ones_like(decay[:, 0]) if a0 is None else a0
+    ys = []
+    for t in range(steps):
+        m = (1.0 - done[:, t]).reshape(bsz, 1, 1, 1).to(h.dtype)
+        a_t = decay[:, t][..., None, None]
+        h = a_t * (m * h) + z[:, t]
+        acc = torch.where(m[:, :, 0, 0] > 0, decay[:, t] * acc, decay[:, t] + 0 * acc)
+        ys.append(torch.einsum("bhn,bhnd->bhd", c_proj[:, t], h) + d_skip[None, :, None] * hidden[:, t])
+    return torch.stack(ys, dim=1), h, acc
+
+
 def jax_cotangent(grad):
     """torch.autograd's gradient of a real loss w.r.t. a complex tensor is the
     conjugate of what JAX's reverse mode (and hence the reference) returns."""

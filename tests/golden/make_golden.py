@@ -14,7 +14,7 @@ operators, reset rule, carry layout, read-outs -- not XLA's rounding.
 
 Files executed: memorax/utils/axes.py,
 memorax/networks/sequence_models/{sequence_model,memoroid,lru,min_gru,
-linear_attention}.py.
+linear_attention,mamba}.py.
 
 Run (only where the reference checkout exists):
     python tests/golden/make_golden.py --reference /path/to/memorax
@@ -159,12 +159,14 @@ def install_stand_ins(reference_dir):
     nn.elu = lambda x: np.where(x > 0, x, np.expm1(np.minimum(x, 0)))
     nn.relu = lambda x: np.maximum(x, 0)
     nn.softplus = _softplus
+    nn.silu = lambda x: x / (1.0 + np.exp(-x))
     nn.Dense = _Dense
     nn.DenseGeneral = _Dense
     nn.RMSNorm = _Identity
     inits = types.ModuleType("flax.linen.initializers")
     inits.lecun_normal = lambda *a, **k: None
     inits.zeros_init = lambda *a, **k: None
+    inits.ones = lambda *a, **k: None
     nn.initializers = inits
     flax = types.ModuleType("flax")
     flax.linen = nn
@@ -285,6 +287,34 @@ def main():
     done = done_patterns(rng, bsz, steps)
     nxt = memoroid.Memoroid._propagate_sensitivities(None, decay, jac, sens, done)
     out.update(rt_decay=decay, rt_jac=jac["w"], rt_sens=sens["w"], rt_done=done, rt_next=nxt["w"])
+
+    # ---- Mamba selective scan: the cell's own __call__, binary_operator and read; the
+    #      projections / convolution in front of them are replaced by fixed arrays ----
+    mamba = importlib.import_module(sm + "mamba")
+    bsz, steps, heads, sdim, hdim = 2, 9, 3, 4, 5
+    cell = object.__new__(mamba.MambaCell)          # no setup(): parameters are set by hand below
+    cell.num_heads, cell.head_dim, cell.state_dim = heads, hdim, sdim
+    cell.A_log = np.log(rng.uniform(1.0, 4.0, heads))
+    cell.D = rng.normal(size=heads)
+    cell.norm = _Identity()
+    cell.output_projection = _Identity()
+    proj = (rng.normal(size=(bsz, steps, heads, hdim)), rng.normal(size=(bsz, steps, heads, sdim)),
+            rng.normal(size=(bsz, steps, heads, sdim)), rng.normal(size=(bsz, steps, heads * hdim)),
+            _softplus(rng.normal(size=(bsz, steps, heads))))
+    cell._project = lambda x: proj                  # (hidden, B, C, gate z, dt) of mamba.py:80-107
+    model = memoroid.Memoroid(cell=cell)
+    x = np.zeros((bsz, steps, 1))
+    done = done_patterns(rng, bsz, steps)
+    carry = (rng.normal(size=(bsz, 1, heads, sdim, hdim)), rng.uniform(0.3, 1.0, size=(bsz, 1, heads, 1, 1)))
+    z = cell(x)
+    h, nxt = model.scan_fn(z, carry, done)
+    nxt2, y = model(x, done, carry)
+    assert all(np.array_equal(p, q) for p, q in zip(nxt, nxt2))
+    gate = proj[3] / (1.0 + np.exp(-proj[3]))
+    out.update(mb_hidden=proj[0], mb_B=proj[1], mb_C=proj[2], mb_gate_in=proj[3], mb_dt=proj[4],
+               mb_A_log=cell.A_log, mb_D=cell.D, mb_done=done, mb_c_state=carry[0], mb_c_decay=carry[1],
+               mb_z_state=z[0], mb_z_decay=z[1], mb_h_state=h[0], mb_n_state=nxt[0], mb_n_decay=nxt[1],
+               mb_y=y, mb_y_pre_gate=(y / gate).reshape(bsz, steps, heads, hdim))
 
     np.savez_compressed(args.out, **out)
     print("wrote", args.out, "with", len(out), "arrays")

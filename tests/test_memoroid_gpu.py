@@ -103,3 +103,61 @@ def test_propagate_sensitivities_matches_the_reference_vectors():
     assert nxt["w"].shape == ref.shape
     err = float((nxt["w"].double().cpu() - ref).abs().max())
     assert err <= 1e-5 * max(1.0, float(ref.abs().max())), err
+
+
+def test_mamba_scan_and_read_match_the_reference_vectors():
+    """MambaCell.scan_elements / read_state against the vectors produced by the reference's own
+    MambaCell source under Memoroid.scan_fn (non-trivial carry, resets)."""
+    import os
+    import numpy as np
+    from memorax_b200.memoroid import MambaCell
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "memoroid_golden.npz"))
+    bsz, steps, heads, sdim, hdim = g["mb_z_state"].shape
+    cell = MambaCell(8, num_heads=heads, head_dim=hdim, state_dim=sdim).cuda()
+    f32 = lambda a: torch.from_numpy(np.asarray(a)).float().cuda()
+    with torch.no_grad():
+        cell.D.copy_(f32(g["mb_D"]))
+    carry = (f32(g["mb_c_state"]), f32(g["mb_c_decay"]))
+    h, nxt = cell.scan_elements(f32(g["mb_z_state"]), f32(g["mb_z_decay"]), carry, torch.from_numpy(g["mb_done"]).cuda())
+    close = lambda got, ref, what: float((got.double().cpu() - torch.from_numpy(ref)).abs().max()) <= \
+        1e-5 * max(1.0, float(np.abs(ref).max())) or pytest.fail(what)
+    close(h, g["mb_h_state"], "h")
+    close(nxt[0], g["mb_n_state"], "next state")
+    close(nxt[1], g["mb_n_decay"], "next decay")
+    y = cell.read_state(h, f32(g["mb_hidden"]), f32(g["mb_C"]))
+    close(y, g["mb_y_pre_gate"], "read-out")
+
+
+def test_mamba_model_gradients_match_the_oracle():
+    """Memoroid(MambaCell) end to end on the GPU against the fp64 oracle recurrence driven by the same
+    projections: outputs, next carry and the gradients of every parameter."""
+    from memorax_b200.memoroid import MambaCell, Memoroid
+    torch.manual_seed(5)
+    bsz, steps, feat = 3, 70, 24
+    model = Memoroid(MambaCell(feat, num_heads=2, head_dim=8, state_dim=4)).cuda()
+    cell = model.cell
+    x = torch.randn(bsz, steps, feat, device="cuda")
+    done = (torch.rand(bsz, steps, device="cuda") < 0.05)
+    done[0, 0] = True
+    carry = (torch.randn(bsz, 1, 2, 4, 8, device="cuda") * 0.3, torch.rand(bsz, 1, 2, 1, 1, device="cuda") * 0.5 + 0.5)
+    w = torch.randn(bsz, steps, feat, device="cuda")
+    nxt, y = model(x, done, carry)
+    ((y * w).sum() + (nxt[0] ** 2).sum()).backward()
+    got = {n: p.grad.detach().double().cpu() for n, p in model.named_parameters()}
+    model.zero_grad()
+    # oracle: same projections (torch, on the device), fp64 sequential recurrence on the host
+    hidden, b_proj, c_proj, gate, dt = cell._project(x)
+    y_o, h_last, a_last = mo.mamba_seq(hidden.double().cpu(), b_proj.double().cpu(), c_proj.double().cpu(),
+                                       dt.double().cpu(), -torch.exp(cell.A_log.double().cpu()), cell.D.double().cpu(),
+                                       carry[0][:, 0].double().cpu(), done.double().cpu(),
+                                       carry[1][:, 0, :, 0, 0].double().cpu())
+    y_o = y_o.reshape(bsz, steps, -1).to("cuda", torch.float32)
+    y_ref = cell.output_projection(cell.norm(y_o) * torch.nn.functional.silu(gate))
+    ((y_ref * w).sum() + (h_last.to("cuda", torch.float32) ** 2).sum()).backward()
+    assert float((y - y_ref).abs().max()) <= 1e-4 * max(1.0, float(y_ref.abs().max()))
+    assert float((nxt[0][:, 0].double().cpu() - h_last).abs().max()) <= 1e-5 * max(1.0, float(h_last.abs().max()))
+    assert float((nxt[1][:, 0, :, 0, 0].double().cpu() - a_last).abs().max()) <= 1e-5
+    for name, p in model.named_parameters():
+        ref = p.grad.detach().double().cpu()
+        err = float((got[name] - ref).abs().max())
+        assert err <= 2e-4 * max(1.0, float(ref.abs().max())), (name, err)

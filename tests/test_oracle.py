@@ -85,6 +85,21 @@ def _done(rng, bsz, steps, p=0.2):
     return d
 
 
+def test_golden_mamba_selective_scan(golden):
+    """mamba_seq against the vectors produced by the reference's own MambaCell.__call__,
+    binary_operator and read (mamba.py:109-135) under Memoroid.scan_fn."""
+    g = golden
+    y, h_last, a_last = mo.mamba_seq(T64(g["mb_hidden"]), T64(g["mb_B"]), T64(g["mb_C"]), T64(g["mb_dt"]),
+                                     -torch.exp(T64(g["mb_A_log"])), T64(g["mb_D"]), T64(g["mb_c_state"][:, 0]),
+                                     T64(g["mb_done"]), T64(g["mb_c_decay"][:, 0, :, 0, 0]))
+    assert float((y - T64(g["mb_y_pre_gate"])).abs().max()) < 1e-11
+    assert float((h_last - T64(g["mb_n_state"][:, 0])).abs().max()) < 1e-11
+    assert float((a_last - T64(g["mb_n_decay"][:, 0, :, 0, 0])).abs().max()) < 1e-11
+    # the per-step elements the scan consumes are what the reference's __call__ emits
+    z = torch.einsum("bthn,bthd->bthnd", T64(g["mb_B"]) * T64(g["mb_dt"])[..., None], T64(g["mb_hidden"]))
+    assert float((z - T64(g["mb_z_state"])).abs().max()) < 1e-12
+
+
 @pytest.mark.parametrize("steps", [1, 2, 7, 16, 33])
 @pytest.mark.parametrize("cplx", [False, True])
 def test_linear_operator_scan_equals_recurrence(steps, cplx):
