@@ -353,7 +353,61 @@ class TrainC5:
         return loss
 
 
-WORKLOADS = {"c2": LinAttnC2, "c3": GDeltaC3, "c4": LruC4, "c1": LinRecC1, "c5": TrainC5}
+class MambaN2:
+    """Mamba selective scan fwd+bwd (the scan of MambaCell, mamba.py:109-122, at the shipped example's
+    size, examples/gradient_ppo_craftax.py:70-98: MambaCell(features=512) = 8 heads x 16 x 16 state,
+    128 environments per device; T widened from 64 to 256 steps so that the inputs exceed L2): real fp32
+    recurrence over H*N*P = 2048 channels with a per-(b,t,head) decay, materialised as the reference does."""
+    name = "n2_mamba_scan_fwd_bwd"
+    dtype = "f32"
+    B, T, H, N, P = 128, 256, 8, 16, 16
+    p_done = 0.01
+    seed = 1234 + 6
+    dominant = "linrec_bwd_kernel"
+    launches_per_step = 2
+    dominant_traffic_bytes = None
+    cpu_sample_batch = 16
+
+    def __init__(self, batch=None):
+        self.B = batch or self.B
+
+    def tokens(self):
+        return self.B * self.T
+
+    def host_inputs(self, seed_offset=0):
+        g = torch.Generator().manual_seed(self.seed + seed_offset)
+        width = self.H * self.N * self.P
+        dt = torch.nn.functional.softplus(torch.randn(self.B, self.T, self.H, generator=g) - 2.0)
+        a_neg = -torch.exp(torch.empty(self.H).uniform_(0.0, math.log(16.0), generator=g))
+        decay = torch.exp(dt * a_neg)
+        return dict(a=decay[..., None].expand(self.B, self.T, self.H, self.N * self.P).reshape(self.B, self.T, width).contiguous(),
+                    z=torch.randn(self.B, self.T, width, generator=g) * 0.1,
+                    gh=torch.randn(self.B, self.T, width, generator=g),
+                    done=(torch.rand(self.B, self.T, generator=g) < self.p_done).to(torch.uint8))
+
+    def algorithmic_bytes(self):
+        n = self.B * self.T * self.H * self.N * self.P
+        # fwd: read a, z, write h; bwd: read a, h, gh, write gz, ga
+        return {"linrec_fwd_kernel": 12 * n, "linrec_bwd_kernel": 20 * n}
+
+    def step(self, x, ops, mark=None):
+        h, _ = ops.linrec_fwd(x["a"], x["z"], None, None, x["done"], want_decay=False)
+        if mark:
+            mark[0].record()
+        gb, ga, _ = ops.linrec_bwd(x["a"], h, None, x["done"], x["gh"], None, need_ga=True, need_gh0=False)
+        if mark:
+            mark[1].record()
+        return (h[:, -1], gb, ga)
+
+    def cpu_step(self, x):
+        from oracle import memoroid_oracle as mo
+        a, z = x["a"].clone().requires_grad_(), x["z"].clone().requires_grad_()
+        h, _ = mo.linrec_seq(a, z, torch.zeros(z.shape[0], z.shape[2]), x["done"].float())
+        (h * x["gh"]).sum().backward()
+        return h
+
+
+WORKLOADS = {"c2": LinAttnC2, "c3": GDeltaC3, "c4": LruC4, "c1": LinRecC1, "c5": TrainC5, "n2": MambaN2}
 
 
 # ------------------------------------------------------------ clock sampling
