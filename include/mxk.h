@@ -57,8 +57,9 @@ int mxk_abi_version(void);
  * with the decay leaf          A_t = done_t ? a_t : a_t * A_{t-1}.
  *
  * Replaces Memoroid.scan_fn over the (state, decay) operator of
- * lru.py:92-95 / s5.py:133-136 and the multiplicative-reset scan of
- * memoroid.py:114-141.
+ * lru.py:92-95 / s5.py:133-136 / mamba.py:119-122 (decay broadcast over the
+ * state_dim x head_dim elements of a head) and the multiplicative-reset scan
+ * of memoroid.py:114-141.
  *
  *   a       (B,T,D), or (D) when a_time_invariant != 0 (lru.py:86)
  *   b       (B,T,D)
