@@ -1,15 +1,15 @@
 // Gated delta rule, forward, on the sm_100a tensor cores (math in gdelta_common.cuh).
 //
-// One CTA (128 threads) owns one (batch, head) sequence and walks its 64-token
-// chunks in order with the fp32 state S (128 x 128) resident in tensor memory.
-// Per chunk:
-//   MMAs 1: K K^T, Q K^T (64 x 64), Y^T = S_in K^T, OI^T = S_in Q^T (128 x 64)
-//   epilogue 1: row threads build beta L (fp32, shared) and tril(G o QK^T) (bf16);
-//               thread v forms its column of beta (V - g Y) and solves the unit
-//               lower-triangular system by forward substitution in fp32 registers
-//   MMAs 2: OA^T = U^T P^T (128 x 64), dS = (gam U)^T K (128 x 128)
-//   epilogue 2: o = g OI + OA (staged through shared memory for 16-byte stores);
-//               S = g_last S + dS back into TMEM, bf16 operand copy for the next chunk.
+// One CTA (256 threads, two warpgroups) owns one (batch, head) sequence and walks its
+// 64-token chunks in order with the fp32 state S (128 x 128) resident in tensor memory;
+// K, Q (128-byte-swizzled tiles) and V arrive by TMA one chunk ahead.  Per chunk:
+//   MMAs 1: K K^T, Q K^T (64 x 64), Y^T = S_in K^T (128 x 64)
+//   epilogue 1: row threads build -beta L (fp32, shared) and tril(G o QK^T) (bf16) and
+//               rescale Q, K in place (g Q, gam K); warpgroup 0, thread v, forms its
+//               column of beta (V - g Y) and solves the unit lower-triangular system by
+//               forward substitution in fp32 registers while warpgroup 1 decays S in place
+//   MMAs 2: O^T = S_in (g Q)^T + U^T P^T (128 x 64), S += U^T (gam K) (128 x 128)
+//   epilogue 2: output tile (one TMA store), bf16 operand copy of the new state.
 #include "gdelta_common.cuh"
 #include "tma.cuh"
 
@@ -122,7 +122,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
   const uint32_t id_ds = idesc_bf16(kD, kD, false, true);
   bool timed_out = false;
 
-  // K, Q (panel order) and V (row-major) of a chunk arrive by TMA, issued by one thread
+  // K, Q (SW tiles) and V (row-major) of a chunk arrive by TMA, issued by one thread
   // one chunk ahead: as soon as the second MMA group of the previous chunk has released
   // the buffers, so that the copies overlap that chunk's output epilogue.
   auto issue_chunk_loads = [&](int cc) {

@@ -4,8 +4,9 @@
 // One CTA owns one (batch, head) sequence and walks its 64-token chunks in
 // order.  The fp32 state S^T (d_k x d_v, plus the normaliser z as one extra
 // column) stays resident in tensor memory for the whole sequence; every
-// contraction is a tcgen05.mma over bf16 operands staged in shared memory in
-// the panel format described in umma.cuh:
+// contraction is a tcgen05.mma over bf16 operands in shared memory (Q, K and the
+// masked P as 128-byte-swizzled "SW tiles", V|1 and S^T|z in the panel format, both
+// described in umma.cuh); Q, K, V arrive by TMA one chunk ahead:
 //   P      = phi(Q) phi(K)^T                      (64 x 64,  K = d_k)
 //   O      = live(phi(Q)) S_in^T                  (64 x 72,  K = d_k)
 //   S^T    = [no reset] S^T + phi(K)^T keep(V|1)  (64 x 72,  K = 64 tokens)

@@ -1,12 +1,12 @@
 // Backward of chunked causal linear attention on the sm_100a tensor cores.
 //
-// One CTA owns one (batch, head) sequence and walks its 64-token chunks right
-// to left, carrying G^T = (dL/dS)^T with gz = dL/dz as one extra column in
+// One CTA (256 threads, two warpgroups) owns one (batch, head) sequence and walks
+// its 64-token chunks right to left, carrying G^T = (dL/dS)^T with gz = dL/dz as one extra column in
 // tensor memory (fp32).  The state entering each chunk comes from the forward
 // call's residual (bf16, already in operand order).  Per chunk, with
 // D_i = max(den_i, eps), c_i = [den_i > eps]:
 //   phase 1 (independent MMAs):  P = phi(Q) phi(K)^T,  dA = dO V^T,  R = dO S_in
-//   epilogue 1 (one thread per query row):
+//   epilogue 1 (four threads per query row, 16 keys each):
 //     den_i  = sum_j M_ij P_ij + live_i phi(q_i).z_in
 //     don_i  = sum_j M_ij P_ij dA_ij + live_i phi(q_i).R_i          (= do_i . num_i)
 //     dden_i = -c_i don_i / D_i^2
