@@ -31,7 +31,8 @@ def max_abs(a, b):
 
 
 CASES = [((2, 64, 2), 0.0, True), ((2, 64, 2), 0.05, False), ((1, 512, 2), 0.005, True), ((2, 1, 1), 0.0, False),
-         ((2, 7, 3), 0.3, False), ((2, 65, 2), 0.05, False), ((1, 200, 2), 0.02, False), ((2, 128, 1), 1.0, False)]
+         ((2, 7, 3), 0.3, False), ((2, 65, 2), 0.05, False), ((1, 200, 2), 0.02, False), ((2, 128, 1), 1.0, False),
+         ((1, 1100, 1), 0.003, False)]   # 18 chunks: every barrier phase wraps many times
 
 
 @pytest.mark.parametrize("shape,p_done,zero_state", CASES)

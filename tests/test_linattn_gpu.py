@@ -32,7 +32,8 @@ def max_abs(a, b):
 
 @pytest.mark.parametrize("shape,p_done", [((2, 64, 2, 64), 0.0), ((2, 64, 2, 64), 0.05), ((3, 256, 4, 64), 0.01),
                                           ((2, 1, 1, 64), 0.0), ((2, 7, 3, 64), 0.3), ((2, 65, 2, 64), 0.05),
-                                          ((1, 200, 2, 64), 0.02), ((2, 128, 1, 64), 1.0)])
+                                          ((1, 200, 2, 64), 0.02), ((2, 128, 1, 64), 1.0),
+                                          ((1, 1100, 1, 64), 0.003)])   # 18 chunks
 def test_linattn_fwd(shape, p_done):
     from memorax_b200 import ops
     q, k, v, s0, z0, done = make_case(sum(shape), *shape, p_done)
@@ -78,7 +79,8 @@ def test_linattn_split_sequence_matches_single_call():
 
 @pytest.mark.parametrize("shape,p_done", [((2, 64, 2, 64), 0.0), ((2, 64, 2, 64), 0.05), ((2, 256, 4, 64), 0.01),
                                           ((2, 1, 1, 64), 0.0), ((2, 7, 3, 64), 0.3), ((2, 65, 2, 64), 0.05),
-                                          ((1, 200, 2, 64), 0.02), ((2, 128, 1, 64), 1.0)])
+                                          ((1, 200, 2, 64), 0.02), ((2, 128, 1, 64), 1.0),
+                                          ((1, 1100, 1, 64), 0.003)])   # 18 chunks
 def test_linattn_bwd(shape, p_done):
     from memorax_b200 import ops
     q, k, v, s0, z0, done = make_case(sum(shape) + 1, *shape, p_done)
