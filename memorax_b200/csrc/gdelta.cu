@@ -43,8 +43,9 @@ struct FwdSmem {
   uint4 vu[kC * 16];          // V row-major [t][v], then U^T   [j/8][v][8]
   uint4 p[kPanC * kC];        // tril(G o QK^T)                 [j/8][t][8]
   float lt[kC * kC];          // lt[j][t] = -beta_t L_tj, then the bf16 output tile [t][v]
+  uint4 lb[4 * 32];           // bf16 copy of the off-diagonal block, rows t = 32..63, columns j = 0..31: [j/8][t-32][8]
   ChunkDecay cd;
-  uint64_t bar[2];
+  uint64_t bar[3];
   uint64_t bar_load;
   uint32_t tmem;
 };
@@ -87,6 +88,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
   if (tid == 0) {
     mbar_init(&sm.bar[0], 1);
     mbar_init(&sm.bar[1], 1);
+    mbar_init(&sm.bar[2], 1);
     mbar_init(&sm.bar_load, 1);
     mbar_init_fence();
   }
@@ -200,7 +202,12 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
             const int j = wg * 32 + e;
-            sm.lt[j * kC + row] = (j < row) ? -beta_t * x[e] : 0.f;
+            x[e] = (j < row) ? -beta_t * x[e] : 0.f;
+            sm.lt[j * kC + row] = x[e];
+          }
+          if (wg == 0 && row >= 32) {   // rows 32..63 x columns 0..31: operand of the blocked solve's MMA
+#pragma unroll
+            for (int jq = 0; jq < 4; ++jq) sm.lb[jq * 32 + (row - 32)] = pack8_bf16(x + jq * 8);
           }
         }
       }
@@ -237,16 +244,45 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
       }
       tmem_st_wait();
     }
+    fence_before_sync();
     __syncthreads();   // -beta L complete; V consumed (U^T reuses its buffer)
     MXK_TF(4);
     if (wg == 0) {
-      forward_substitute(reinterpret_cast<float2*>(r), sm.lt);
+      // Blocked solve: rows 0..31 in fp32 registers; their effect on rows 32..63 (the 32 x 32
+      // off-diagonal block times U_lo, a quarter of the FMAs and half of the dependent chain) on the
+      // tensor core from the bf16 operands U_lo^T and -beta L, fp32 accumulate; then rows 32..63.
       uint4* res = p.chunk_states ? p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * kResidualVecs + kStateVecs : nullptr;
+      forward_substitute_range<0, 31, 32>(reinterpret_cast<float2*>(r), sm.lt);
 #pragma unroll
-      for (int jp = 0; jp < kPanC; ++jp) {
+      for (int jp = 0; jp < kPanC / 2; ++jp) {
         const uint4 u8 = pack8_bf16(r + jp * 8);
         sm.vu[jp * kD + vt] = u8;
         if (res) res[jp * kD + vt] = u8;   // the backward pass reuses U instead of solving again
+      }
+      fence_smem_to_async();
+      fence_before_sync();
+      asm volatile("bar.sync 1, 128;" ::: "memory");   // warpgroup 0 only
+      if (warp == 0) {
+        const bool leader = elect_one();
+        fence_after_sync();
+        gemm<2>(tmem + kColKQ, Operand{smem_u32(sm.vu), kD, false}, Operand{smem_u32(sm.lb), 32, false},
+                idesc_bf16(kD, 32, false, false), false, leader);
+        if (leader) commit(&sm.bar[2]);
+      }
+      mbar_wait_flag(&sm.bar[2], c & 1, timed_out);
+      fence_after_sync();
+      {
+        float delta[32];
+        tmem_ld_row<32>(lane_base + kColKQ, delta);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) r[32 + e] += delta[e];
+      }
+      forward_substitute_range<32, kC - 1, kC>(reinterpret_cast<float2*>(r), sm.lt);
+#pragma unroll
+      for (int jp = kPanC / 2; jp < kPanC; ++jp) {
+        const uint4 u8 = pack8_bf16(r + jp * 8);
+        sm.vu[jp * kD + vt] = u8;
+        if (res) res[jp * kD + vt] = u8;
       }
     }
     MXK_TF(5);

@@ -104,19 +104,26 @@ __device__ __forceinline__ float bf16_at(const uint4* plain, int t, int c) {
 //
 // forward_substitute: r holds the right-hand side on entry and the solution of
 // (I + diag(beta) L) u = r on exit; nlt[j * 64 + t] = -beta_t L_tj (zero for t <= j).
-__device__ __forceinline__ void forward_substitute(float2* r2, const float* nlt) {
+// The template form eliminates columns J0 .. J1 - 1 from rows < T1 only, so that a solve
+// can be blocked: rows 0..31 first (<0, 31, 32>), then -- once the 32 x 32 off-diagonal
+// block times the first half has been added to rows 32..63 -- the rest (<32, 63, 64>).
+template <int J0, int J1, int T1>
+__device__ __forceinline__ void forward_substitute_range(float2* r2, const float* nlt) {
   const float4* lt4 = reinterpret_cast<const float4*>(nlt);
 #pragma unroll
-  for (int j = 0; j < kC - 1; ++j) {
+  for (int j = J0; j < J1; ++j) {
     const float uj = (j & 1) ? r2[j >> 1].y : r2[j >> 1].x;
     const float2 u2 = make_float2(uj, uj);
 #pragma unroll
-    for (int m = (j + 1) / 4; m < kC / 4; ++m) {
+    for (int m = (j + 1) / 4; m < T1 / 4; ++m) {
       const float4 l = lt4[j * (kC / 4) + m];
       r2[2 * m] = __ffma2_rn(make_float2(l.x, l.y), u2, r2[2 * m]);
       r2[2 * m + 1] = __ffma2_rn(make_float2(l.z, l.w), u2, r2[2 * m + 1]);
     }
   }
+}
+__device__ __forceinline__ void forward_substitute(float2* r2, const float* nlt) {
+  forward_substitute_range<0, kC - 1, kC>(r2, nlt);
 }
 
 // backward_substitute: r holds dU on entry and (I + diag(beta) L)^-T dU on exit;
