@@ -67,13 +67,14 @@ struct BwdSmem {
   uint4 p[kPanC * kC];      // tril(G o QK^T)     [j/8][t][8]
   float l[kC * kLS];        // l[t][j] = -beta_t L_tj        -> E[t][j]   (row stride kLS)
   float lt[kC * kC];        // lt[j][t] = -beta_t L_tj       -> dV tile -> (dP o G), (dL o G) panels
+  uint4 lb[4 * 32];         // bf16 copy of -beta L, rows i = 32..63 x columns t = 0..31, as [(i-32)/8][t][8]
   ChunkDecay cd;
   // per-warp partial sums of the decay cotangents, combined in a fixed order (no floating-point atomics:
   // the results are bit-reproducible)
   float dg_a[4][kC], dg_b[4][kC], dgam_p[4][kC];
   float rowsum[kC], colsum[kC], dcum[kC];
   float dgl[4];
-  uint64_t bar[2];
+  uint64_t bar[3];
   uint64_t bar_load;
   uint32_t tmem;
 };
@@ -155,6 +156,7 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
   if (tid == 0) {
     mbar_init(&sm.bar[0], 1);
     mbar_init(&sm.bar[1], 1);
+    mbar_init(&sm.bar[2], 1);
     mbar_init(&sm.bar_load, 1);
     mbar_init_fence();
   }
@@ -269,6 +271,12 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
         float4* lrow = reinterpret_cast<float4*>(&sm.l[row * kLS + j0 + jq * 8]);
         lrow[0] = make_float4(lv[0], lv[1], lv[2], lv[3]);
         lrow[1] = make_float4(lv[4], lv[5], lv[6], lv[7]);
+        if (row >= 32 && !upper) {   // rows 32..63 x columns 0..31: operand of the blocked solve's MMA
+          __nv_bfloat16* lb = reinterpret_cast<__nv_bfloat16*>(sm.lb);
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            lb[(((row - 32) >> 3) * 32 + j0 + jq * 8 + e) * 8 + ((row - 32) & 7)] = __float2bfloat16(lv[e]);
+        }
         sm.p[((j0 >> 3) + jq) * kC + row] = pack8_bf16(pm);
       }
     }
@@ -312,7 +320,31 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
       for (int j = 0; j < kC; ++j) r[j] = fmaf(sm.cd.gam[j], ga[j], r[j]);   // dU[v][j]
       MXK_TG(11);
 
-      backward_substitute<kLS>(reinterpret_cast<float2*>(r), sm.l);          // r = dUt[v][.]
+      // Blocked solve (r = dUt[v][.] afterwards): rows 63..32 in fp32 registers; their effect on entries
+      // 0..31 (the 32 x 32 off-diagonal block) on the tensor core from bf16 operands, fp32 accumulate;
+      // then rows 31..1.
+      backward_substitute_range<kLS, kC - 1, 33, 32>(reinterpret_cast<float2*>(r), sm.l);
+#pragma unroll
+      for (int tp = kPanC / 2; tp < kPanC; ++tp) sm.r1[tp * kD + vt] = pack8_bf16(r + tp * 8);
+      fence_smem_to_async();
+      fence_before_sync();
+      asm volatile("bar.sync 1, 128;" ::: "memory");   // warpgroup 0 only
+      if (warp == 0) {
+        const bool leader = elect_one();
+        fence_after_sync();
+        gemm<2>(tmem + kColX1, Operand{smem_u32(sm.r1) + (kPanC / 2) * kD * 16, kD, false},
+                Operand{smem_u32(sm.lb), 32, false}, idesc_bf16(kD, 32, false, false), false, leader);
+        if (leader) commit(&sm.bar[2]);
+      }
+      mbar_wait_flag(&sm.bar[2], it & 1, timed_out);
+      fence_after_sync();
+      {
+        float delta[32];
+        tmem_ld_row<32>(lane_base + kColX1, delta);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) r[e] += delta[e];
+      }
+      backward_substitute_range<kLS, 31, 1, 0>(reinterpret_cast<float2*>(r), sm.l);
       MXK_TG(12);
 
       // dR = beta dUt: the dV tile (row-major [t][v], staged in `lt`), -(g dR)^T panels,

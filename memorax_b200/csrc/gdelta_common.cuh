@@ -128,20 +128,28 @@ __device__ __forceinline__ void forward_substitute(float2* r2, const float* nlt)
 
 // backward_substitute: r holds dU on entry and (I + diag(beta) L)^-T dU on exit;
 // nl[i * kStride + t] = -beta_i L_it (zero for t >= i), kStride a multiple of 4.
-template <int kStride>
-__device__ __forceinline__ void backward_substitute(float2* r2, const float* nl) {
+// The range form eliminates rows I1 down to I0 from the entries t >= T0 only (T0 a multiple of 4),
+// so that the solve can be blocked like the forward one: rows 63..33 over entries 32.. first
+// (<63, 33, 32>), then -- once the off-diagonal block times the second half has been added to
+// entries 0..31 -- rows 31..1 (<31, 1, 0>).
+template <int kStride, int I1, int I0, int T0>
+__device__ __forceinline__ void backward_substitute_range(float2* r2, const float* nl) {
   const float4* l4 = reinterpret_cast<const float4*>(nl);
 #pragma unroll
-  for (int i = kC - 1; i >= 1; --i) {
+  for (int i = I1; i >= I0; --i) {
     const float xi = (i & 1) ? r2[i >> 1].y : r2[i >> 1].x;
     const float2 x2 = make_float2(xi, xi);
 #pragma unroll
-    for (int m = 0; m <= (i - 1) / 4; ++m) {
+    for (int m = T0 / 4; m <= (i - 1) / 4; ++m) {
       const float4 c = l4[i * (kStride / 4) + m];
       r2[2 * m] = __ffma2_rn(make_float2(c.x, c.y), x2, r2[2 * m]);
       r2[2 * m + 1] = __ffma2_rn(make_float2(c.z, c.w), x2, r2[2 * m + 1]);
     }
   }
+}
+template <int kStride>
+__device__ __forceinline__ void backward_substitute(float2* r2, const float* nl) {
+  backward_substitute_range<kStride, kC - 1, 1, 0>(r2, nl);
 }
 
 }  // namespace gdelta
