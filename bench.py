@@ -66,15 +66,15 @@ class LinAttnC2:
     def tokens(self):
         return self.B * self.T
 
-    def host_inputs(self, seed_offset=0):
-        g = torch.Generator().manual_seed(self.seed + seed_offset)
+    def host_inputs(self, seed_offset=0, device="cpu"):
+        g = torch.Generator(device=device).manual_seed(self.seed + seed_offset)
         shp = (self.B, self.T, self.H, self.D)
-        mk = lambda *s: torch.randn(*s, generator=g)
+        mk = lambda *s: torch.randn(*s, generator=g, device=device)
         return dict(
             q=(mk(*shp) / 8).bfloat16(), k=(mk(*shp) / 8).bfloat16(), v=(mk(*shp) / 8).bfloat16(),
             d_o=mk(*shp).bfloat16(),
             s0=mk(self.B, self.H, self.D, self.D) * 0.1, z0=mk(self.B, self.H, self.D).abs() * 0.1,
-            done=(torch.rand(self.B, self.T, generator=g) < self.p_done).to(torch.uint8))
+            done=(torch.rand(self.B, self.T, generator=g, device=device) < self.p_done).to(torch.uint8))
 
     def state_bytes(self):
         return self.B * self.H * (self.D * self.D + self.D) * 4
@@ -84,6 +84,11 @@ class LinAttnC2:
         fwd = th * self.fwd_bytes_per_token_head + 2 * self.state_bytes()
         bwd = th * self.bwd_bytes_per_token_head + 2 * self.state_bytes()
         return {"linattn_fwd_kernel": fwd, "linattn_bwd_kernel": bwd}
+
+    def algorithmic_flops(self):
+        # dense 64 x 64 tiles: fwd 2(C d_k + C d_v + 2 d_k d_v), bwd 2C(3 d_k + 2 d_v) + 10 d_k d_v per token-head
+        th = self.B * self.T * self.H
+        return {"linattn_fwd_kernel": th * 32768, "linattn_bwd_kernel": th * 81920}
 
     def step(self, x, ops, mark=None):
         o, s_last, z_last, states = ops.linattn_fwd(x["q"], x["k"], x["v"], x["s0"], x["z0"], x["done"],
@@ -126,19 +131,22 @@ class LruC4:
     def tokens(self):
         return self.B * self.T
 
-    def host_inputs(self, seed_offset=0):
-        g = torch.Generator().manual_seed(self.seed + seed_offset)
-        mag = 0.9 + 0.099 * torch.rand(self.D, generator=g)
-        ph = torch.rand(self.D, generator=g) * math.pi / 10
+    def host_inputs(self, seed_offset=0, device="cpu"):
+        g = torch.Generator(device=device).manual_seed(self.seed + seed_offset)
+        mag = 0.9 + 0.099 * torch.rand(self.D, generator=g, device=device)
+        ph = torch.rand(self.D, generator=g, device=device) * math.pi / 10
         shp = (self.B, self.T, self.D)
-        return dict(lam=torch.polar(mag, ph).to(torch.complex64),
-                    bu=torch.complex(torch.randn(*shp, generator=g), torch.randn(*shp, generator=g)),
-                    gh=torch.complex(torch.randn(*shp, generator=g), torch.randn(*shp, generator=g)),
-                    done=(torch.rand(self.B, self.T, generator=g) < self.p_done).to(torch.uint8))
+        cplx = lambda: torch.view_as_complex(torch.randn(*shp, 2, generator=g, device=device))
+        return dict(lam=torch.polar(mag, ph).to(torch.complex64), bu=cplx(), gh=cplx(),
+                    done=(torch.rand(self.B, self.T, generator=g, device=device) < self.p_done).to(torch.uint8))
 
     def algorithmic_bytes(self):
         n = self.B * self.T * self.D
         return {"linrec_fwd_kernel": 16 * n, "linrec_bwd_kernel": 24 * n}
+
+    def algorithmic_flops(self):
+        n = self.B * self.T * self.D   # one complex multiply-add per element forward, two backward
+        return {"linrec_fwd_kernel": 8 * n, "linrec_bwd_kernel": 16 * n}
 
     def step(self, x, ops, mark=None):
         h, _ = ops.linrec_fwd(x["lam"], x["bu"], None, None, x["done"], want_decay=False)
@@ -178,15 +186,18 @@ class LinRecC1:
     def tokens(self):
         return self.B * self.T
 
-    def host_inputs(self, seed_offset=0):
-        g = torch.Generator().manual_seed(self.seed + seed_offset)
+    def host_inputs(self, seed_offset=0, device="cpu"):
+        g = torch.Generator(device=device).manual_seed(self.seed + seed_offset)
         shp = (self.B, self.T, self.D)
-        return dict(a=torch.sigmoid(torch.randn(*shp, generator=g)), b=torch.randn(*shp, generator=g),
-                    h0=torch.randn(self.B, self.D, generator=g),
-                    done=(torch.rand(self.B, self.T, generator=g) < self.p_done).to(torch.uint8))
+        rn = lambda *s: torch.randn(*s, generator=g, device=device)
+        return dict(a=torch.sigmoid(rn(*shp)), b=rn(*shp), h0=rn(self.B, self.D),
+                    done=(torch.rand(self.B, self.T, generator=g, device=device) < self.p_done).to(torch.uint8))
 
     def algorithmic_bytes(self):
         return {"linrec_fwd_kernel": 12 * self.B * self.T * self.D}
+
+    def algorithmic_flops(self):
+        return {"linrec_fwd_kernel": 2 * self.B * self.T * self.D}
 
     def step(self, x, ops, mark=None):
         if mark:
@@ -224,21 +235,29 @@ class GDeltaC3:
     def tokens(self):
         return self.B * self.T
 
-    def host_inputs(self, seed_offset=0):
-        g = torch.Generator().manual_seed(self.seed + seed_offset)
+    def host_inputs(self, seed_offset=0, device="cpu"):
+        g = torch.Generator(device=device).manual_seed(self.seed + seed_offset)
         shp = (self.B, self.T, self.H, self.D)
-        mk = lambda *s: torch.randn(*s, generator=g)
+        mk = lambda *s: torch.randn(*s, generator=g, device=device)
         nrm = lambda x: x / x.norm(dim=-1, keepdim=True)
         return dict(q=nrm(mk(*shp)).bfloat16(), k=nrm(mk(*shp)).bfloat16(), v=mk(*shp).bfloat16(),
                     d_o=mk(*shp).bfloat16(), beta=torch.sigmoid(mk(*shp[:3])),
                     alpha=torch.exp(-torch.nn.functional.softplus(mk(*shp[:3]))),
-                    done=(torch.rand(self.B, self.T, generator=g) < self.p_done).to(torch.uint8))
+                    done=(torch.rand(self.B, self.T, generator=g, device=device) < self.p_done).to(torch.uint8))
 
     def algorithmic_bytes(self):
         th = self.B * self.T * self.H
         state = self.B * self.H * self.D * self.D * 4
         # q,k,v,o bf16 + alpha,beta fp32 | q,k,v,do,dq,dk,dv bf16 + alpha,beta,dalpha,dbeta fp32
         return {"gdelta_fwd_kernel": th * (4 * 256 + 8) + state, "gdelta_bwd_kernel": th * (7 * 256 + 16) + state}
+
+    # FLOP per token-head of the algorithm the kernels run (tensor-core products plus the fp32 triangular work)
+    fwd_flop_per_token_head = 155648
+    bwd_flop_per_token_head = 426000
+
+    def algorithmic_flops(self):
+        th = self.B * self.T * self.H
+        return {"gdelta_fwd_kernel": th * self.fwd_flop_per_token_head, "gdelta_bwd_kernel": th * self.bwd_flop_per_token_head}
 
     def step(self, x, ops, mark=None):
         o, s_last, states = ops.gdelta_fwd(x["q"], x["k"], x["v"], x["alpha"], x["beta"], None, x["done"],
@@ -264,8 +283,7 @@ class TrainC5:
     """Training step (fwd + bwd + gradient all-reduce + Adam) of a 4-layer GTrXL-style value
     network with the delta-rule mixer: d_model 512, MLP 4x, bf16 parameters, fp32 Adam moments,
     512 sequences x 256 steps of 128-dim observations per GPU (4096 sequences over 8 GPUs),
-    done ~ Bernoulli(0.005).  Deviation from BASELINE.json: the mixer runs 4 heads of 128
-    (the delta-rule kernels are built for head dimension 128), not 8 heads of 64."""
+    done ~ Bernoulli(0.005); the mixer has 8 heads of 64."""
     name = "c5_gtrxl_deltanet_train_step"
     dtype = "bf16"
     B, T, OBS = 512, 256, 128
@@ -283,11 +301,11 @@ class TrainC5:
     def tokens(self):
         return self.B * self.T
 
-    def host_inputs(self, seed_offset=0):
-        g = torch.Generator().manual_seed(self.seed + seed_offset)
-        return dict(obs=torch.randn(self.B, self.T, self.OBS, generator=g).bfloat16(),
-                    target=torch.randn(self.B, self.T, generator=g),
-                    done=(torch.rand(self.B, self.T, generator=g) < self.p_done).to(torch.uint8))
+    def host_inputs(self, seed_offset=0, device="cpu"):
+        g = torch.Generator(device=device).manual_seed(self.seed + seed_offset)
+        return dict(obs=torch.randn(self.B, self.T, self.OBS, generator=g, device=device).bfloat16(),
+                    target=torch.randn(self.B, self.T, generator=g, device=device),
+                    done=(torch.rand(self.B, self.T, generator=g, device=device) < self.p_done).to(torch.uint8))
 
     def _build(self, device):
         import torch.distributed as dist
@@ -298,7 +316,7 @@ class TrainC5:
         self.trainer = FlatAdamTrainer(model, world_size=world)
         dense = sum(m.weight.numel() for m in model.modules() if isinstance(m, torch.nn.Linear))
         # 6 FLOP per dense weight per token (fwd + bwd) + the mixer's own 582 kFLOP per token-head
-        self.flop_per_token = 6.0 * dense + 4 * 4 * 582e3
+        self.flop_per_token = 6.0 * dense + 4 * 8 * 582e3 / 4   # per token-head at d = 64: a quarter of d = 128's products
 
     def step(self, x, ops, mark=None):
         if self.trainer is None:
@@ -330,7 +348,7 @@ class TrainC5:
         from oracle import memoroid_oracle as mo
         if not hasattr(self, "_cpu"):
             torch.manual_seed(0)
-            d, H, hd = 512, 4, 128
+            d, H, hd = 512, 8, 64
             lin = lambda i, o: torch.nn.Linear(i, o)
             self._cpu = dict(embed=lin(self.OBS, d), head=lin(d, 1), layers=[
                 dict(n1=torch.nn.LayerNorm(d), q=lin(d, d), k=lin(d, d), v=lin(d, d), gate=lin(d, 2 * H), rms=torch.nn.RMSNorm(d),
@@ -341,11 +359,11 @@ class TrainC5:
         B, T, _ = h.shape
         for L in P["layers"]:
             y = L["n1"](h)
-            hv = lambda t: t.view(B, T, 4, 128)
+            hv = lambda t: t.view(B, T, 8, 64)
             q, k = F.normalize(hv(L["q"](y)), dim=-1), F.normalize(hv(L["k"](y)), dim=-1)
             bl, al = L["gate"](y).chunk(2, -1)
             o, _ = mo.gdelta_seq(q, k, hv(L["v"](y)), torch.exp(-F.softplus(al)), torch.sigmoid(bl),
-                                 torch.zeros(B, 4, 128, 128), x["done"].float())
+                                 torch.zeros(B, 8, 64, 64), x["done"].float())
             h = h + torch.sigmoid(L["g1"](h)) * L["out"](L["rms"](o.reshape(B, T, -1)))
             h = h + torch.sigmoid(L["g2"](h)) * L["down"](F.gelu(L["up"](L["n2"](h))))
         loss = 0.5 * (P["head"](h).squeeze(-1) - x["target"]).square().mean()
@@ -374,21 +392,25 @@ class MambaN2:
     def tokens(self):
         return self.B * self.T
 
-    def host_inputs(self, seed_offset=0):
-        g = torch.Generator().manual_seed(self.seed + seed_offset)
+    def host_inputs(self, seed_offset=0, device="cpu"):
+        g = torch.Generator(device=device).manual_seed(self.seed + seed_offset)
         width = self.H * self.N * self.P
-        dt = torch.nn.functional.softplus(torch.randn(self.B, self.T, self.H, generator=g) - 2.0)
-        a_neg = -torch.exp(torch.empty(self.H).uniform_(0.0, math.log(16.0), generator=g))
+        rn = lambda *s: torch.randn(*s, generator=g, device=device)
+        dt = torch.nn.functional.softplus(rn(self.B, self.T, self.H) - 2.0)
+        a_neg = -torch.exp(torch.rand(self.H, generator=g, device=device) * math.log(16.0))
         decay = torch.exp(dt * a_neg)
         return dict(a=decay[..., None].expand(self.B, self.T, self.H, self.N * self.P).reshape(self.B, self.T, width).contiguous(),
-                    z=torch.randn(self.B, self.T, width, generator=g) * 0.1,
-                    gh=torch.randn(self.B, self.T, width, generator=g),
-                    done=(torch.rand(self.B, self.T, generator=g) < self.p_done).to(torch.uint8))
+                    z=rn(self.B, self.T, width) * 0.1, gh=rn(self.B, self.T, width),
+                    done=(torch.rand(self.B, self.T, generator=g, device=device) < self.p_done).to(torch.uint8))
 
     def algorithmic_bytes(self):
         n = self.B * self.T * self.H * self.N * self.P
         # fwd: read a, z, write h; bwd: read a, h, gh, write gz, ga
         return {"linrec_fwd_kernel": 12 * n, "linrec_bwd_kernel": 20 * n}
+
+    def algorithmic_flops(self):
+        n = self.B * self.T * self.H * self.N * self.P
+        return {"linrec_fwd_kernel": 2 * n, "linrec_bwd_kernel": 4 * n}
 
     def step(self, x, ops, mark=None):
         h, _ = ops.linrec_fwd(x["a"], x["z"], None, None, x["done"], want_decay=False)
@@ -518,78 +540,197 @@ def to_device(x, dev):
     return {k: v.to(dev, non_blocking=True) for k, v in x.items()}
 
 
-def run_gpu_arm(args):
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: memorax_b200 has no CPU path")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            d = json.load(fh)
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, 1590.0, "fallback"
 
-    from memorax_b200 import ops  # raises if libmxk.so is missing
 
-    cls = WORKLOADS[args.workload]
-    w = cls(batch=args.batch)
-    host = w.host_inputs(seed_offset=1000 * rank)
-    in_bytes = sum(v.numel() * v.element_size() for v in host.values())
-    # enough distinct input sets that a step never finds its inputs in the 126 MB L2
-    nsets = 1 if in_bytes > (1 << 30) else min(64, max(NSETS, -(-(512 << 20) // in_bytes)))
-    sets = [to_device(host if i == 0 else w.host_inputs(seed_offset=1000 * rank + i), dev) for i in range(nsets)]
-    torch.cuda.synchronize()
+def bind_to_gpu_numa_node(local):
+    """Pins this rank's host threads (and hence its pinned staging buffers, first-touch) to the CPUs
+    the kernel lists as local to its GPU's PCIe slot.  Read-only on the GPU side; returns a short
+    description for the JSON line."""
+    try:
+        bus = torch.cuda.get_device_properties(local).pci_bus_id
+        dom = torch.cuda.get_device_properties(local).pci_domain_id
+        dev = torch.cuda.get_device_properties(local).pci_device_id
+        base = f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev:02x}.0"
+        with open(base + "/numa_node") as fh:
+            node = int(fh.read().strip())
+        with open(base + "/local_cpulist") as fh:
+            cpulist = fh.read().strip()
+        cpus = set()
+        for part in cpulist.split(","):
+            if "-" in part:
+                lo, hi = part.split("-")
+                cpus.update(range(int(lo), int(hi) + 1))
+            elif part:
+                cpus.add(int(part))
+        allowed = os.sched_getaffinity(0)
+        target = cpus & allowed
+        if target and target != allowed:
+            os.sched_setaffinity(0, target)
+            return f"numa node {node}: bound to {len(target)} of {len(allowed)} cpus"
+        return f"numa node {node}: local cpus = all allowed cpus ({len(allowed)}), nothing to bind"
+    except Exception as exc:   # no sysfs entry (virtualised PCI topology): leave the affinity alone
+        return f"not bound ({type(exc).__name__})"
 
-    def barrier():
-        if dist:
-            dist.barrier()
+
+class Harness:
+    """One process per GPU; times blocks of K steps between barriers, max over ranks."""
+
+    def __init__(self, args):
+        self.args = args
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: memorax_b200 has no CPU path")
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        self.binding = bind_to_gpu_numa_node(self.local)
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=self.dev)
+            self.dist = dist
+        from memorax_b200 import ops  # raises if libmxk.so is missing
+        self.ops = ops
+
+    def barrier(self):
+        if self.dist:
+            self.dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(max(args.warmup, 3)):
-        w.step(sets[i % nsets], ops)
-    barrier()
+    def max_over_ranks(self, ms):
+        if not self.dist:
+            return ms
+        t = torch.tensor([ms], device=self.dev)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
 
-    marks = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    graphs = None
-    if getattr(w, "use_graph", False):
-        # launch-bound workload: one captured graph per input set (outputs stay alive in the graph's pool)
-        graphs, keep = [], []
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            for x in sets:
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=side):
-                    keep.append(w.step(x, ops))
-                graphs.append(g)
-        torch.cuda.current_stream().wait_stream(side)
-        for g in graphs:
-            g.replay()
-        barrier()
-    with ClockSampler(local) as clocks:
-        t_start.record()
-        for i in range(args.steps):
-            if graphs:
-                marks[i][0].record()
-                graphs[i % nsets].replay()
-                marks[i][1].record()
-            else:
-                w.step(sets[i % nsets], ops, marks[i])
-        t_stop.record()
-        barrier()
-    elapsed_ms = t_start.elapsed_time(t_stop)
-    dominant_ms = sum(a.elapsed_time(b) for a, b in marks) / args.steps
-    if dist:
-        t = torch.tensor([elapsed_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
-    ms_per_step = elapsed_ms / args.steps
+    def input_sets(self, w, on_device):
+        """Enough distinct input sets that a step never finds its inputs in the 126 MB L2."""
+        where = self.dev if on_device else "cpu"
+        first = w.host_inputs(seed_offset=1000 * self.rank, device=where)
+        in_bytes = sum(v.numel() * v.element_size() for v in first.values())
+        nsets = 1 if in_bytes > (1 << 30) else min(64, max(NSETS, -(-(512 << 20) // in_bytes)))
+        sets = [to_device(first, self.dev)]
+        for i in range(1, nsets):
+            sets.append(to_device(w.host_inputs(seed_offset=1000 * self.rank + i, device=where), self.dev))
+        torch.cuda.synchronize()
+        return first, sets, in_bytes
+
+    def time_workload(self, w, sets, steps, warmup, min_seconds):
+        """Blocks of exactly `steps` steps, each bracketed by barrier + synchronize, repeated until at least
+        `min_seconds` of device time have been measured; the reported block is the median one (max over
+        ranks per block).  Returns (ms_per_step, per-phase ms of the median block, blocks, clock summary)."""
+        ops, nsets = self.ops, len(sets)
+        for i in range(max(warmup, 3)):
+            w.step(sets[i % nsets], ops)
+        self.barrier()
+        graphs = None
+        if getattr(w, "use_graph", False):
+            # launch-bound workload: one captured graph per input set (outputs stay alive in the graph's pool)
+            graphs, keep = [], []
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for x in sets:
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side):
+                        keep.append(w.step(x, ops))
+                    graphs.append(g)
+            torch.cuda.current_stream().wait_stream(side)
+            for g in graphs:
+                g.replay()
+            self.barrier()
+        blocks, phases, total = [], [], 0.0
+        with ClockSampler(self.local) as clocks:
+            while True:
+                marks = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                self.barrier()
+                t0.record()
+                for i in range(steps):
+                    if graphs:
+                        marks[i][0].record()
+                        graphs[i % nsets].replay()
+                        marks[i][1].record()
+                    else:
+                        w.step(sets[i % nsets], ops, marks[i])
+                t1.record()
+                self.barrier()
+                ms = self.max_over_ranks(t0.elapsed_time(t1))
+                blocks.append(ms)
+                # marks: [0] after the first launch of a step (or before the only one), [1] after the last
+                phases.append((sum(a.elapsed_time(b) for a, b in marks) / steps, t0.elapsed_time(t1) / steps))
+                total += ms
+                if total >= min_seconds * 1e3 or len(blocks) >= 400:
+                    break
+        order = sorted(range(len(blocks)), key=lambda i: blocks[i])
+        mid = order[len(order) // 2]
+        return blocks[mid] / steps, phases[mid][0], blocks, clocks.summary(), bool(graphs)
+
+    def op_record(self, w, ms_per_step, dominant_ms, blocks, clocks, tokens_all_ranks):
+        hbm_peak, tc_peak, kind = measured_peaks()
+        rec = {"workload": w.name, "batch_per_gpu": w.B, "ms_per_step": ms_per_step,
+               "tokens_per_s": tokens_all_ranks / (ms_per_step * 1e-3), "dtype": w.dtype,
+               "blocks": len(blocks), "block_ms_min_med_max": [min(blocks), sorted(blocks)[len(blocks) // 2], max(blocks)],
+               "clocks": clocks}
+        if hasattr(w, "roofline"):
+            rec["roofline"] = w.roofline(dominant_ms)
+            return rec
+        alg = w.algorithmic_bytes()
+        flops = w.algorithmic_flops()
+        step_bytes, step_flops = sum(alg.values()), sum(flops.values())
+        t = ms_per_step * 1e-3
+        # whole step (all launches) against both roofs; the binding roof is the one with the larger floor time
+        hbm_frac = step_bytes / t / 1e9 / hbm_peak
+        tc_frac = step_flops / t / 1e12 / tc_peak
+        dom_bytes = alg[w.dominant]
+        achieved = dom_bytes / (dominant_ms * 1e-3) / 1e9
+        rec["roofline"] = {
+            "bound": "hbm" if step_bytes / hbm_peak / 1e9 >= step_flops / tc_peak / 1e12 else "tensor",
+            "step": {"algorithmic_bytes": step_bytes, "algorithmic_flop": step_flops, "hbm_frac": hbm_frac,
+                     "tensor_frac": tc_frac, "hbm_peak_gbs": hbm_peak, "tensor_peak_tflops": tc_peak},
+            "kernel": w.dominant, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+            "peak_kind": f"of {kind}", "algorithmic_bytes_per_launch": dom_bytes, "ms_per_launch": dominant_ms,
+            "tensor_frac_of_kernel": flops[w.dominant] / (dominant_ms * 1e-3) / 1e12 / tc_peak}
+        return rec
+
+    def run_op(self, cls, batch, steps, warmup, min_seconds, on_device=True):
+        """Times one workload with device-generated inputs and frees everything afterwards."""
+        w = cls(batch=batch)
+        _, sets, in_bytes = self.input_sets(w, on_device)
+        ms, dom_ms, blocks, clocks, graphed = self.time_workload(w, sets, steps, warmup, min_seconds)
+        rec = self.op_record(w, ms, dom_ms, blocks, clocks, self.world * w.tokens())
+        rec["l2"] = f"{len(sets)} input set(s) rotated, {in_bytes * len(sets) / 1e6:.0f} MB of inputs"
+        rec["launch"] = "cuda graph replay" if graphed else "direct"
+        if hasattr(w, "trainer"):
+            w.trainer = None
+        del sets, w
+        torch.cuda.empty_cache()
+        return rec
+
+
+def run_gpu_arm(args):
+    hz = Harness(args)
+    rank, world, dev, ops = hz.rank, hz.world, hz.dev, hz.ops
+    cls = WORKLOADS[args.workload]
+    w = cls(batch=args.batch)
+    host, sets, in_bytes = hz.input_sets(w, on_device=False)
+    nsets = len(sets)
+    ms_per_step, dominant_ms, blocks, clock_summary, graphed = hz.time_workload(w, sets, args.steps, args.warmup,
+                                                                               args.min_seconds)
     value = world * w.tokens() / (ms_per_step * 1e-3)
+    head = hz.op_record(w, ms_per_step, dominant_ms, blocks, clock_summary, world * w.tokens())
 
     # ---- end to end: host buffers in, host results out, through the same calls ----
+    barrier = hz.barrier
     pinned_in = {k: v.pin_memory() for k, v in host.items()}
     e2e_steps = max(3, min(args.steps, 20))
     outs = w.step(to_device(pinned_in, dev), ops)
@@ -614,24 +755,64 @@ def run_gpu_arm(args):
     pipe.join()
     e1.record()
     barrier()
-    e2e_ms = e0.elapsed_time(e1)
-    if dist:
-        t = torch.tensor([e2e_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    e2e_ms = hz.max_over_ranks(e0.elapsed_time(e1))
     e2e_value = world * w.tokens() / (e2e_ms / e2e_steps * 1e-3)
+    ops.check_status(dev)
+
+    # ---- wire floor: the same bytes over PCIe, both directions at once, no kernels ----
+    dev_in = to_device(pinned_in, dev)
+    s_up, s_down = torch.cuda.Stream(), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    s_up.wait_event(f0)
+    s_down.wait_event(f0)
+    for _ in range(e2e_steps):
+        with torch.cuda.stream(s_up):
+            for k, v in pinned_in.items():
+                dev_in[k].copy_(v, non_blocking=True)
+        with torch.cuda.stream(s_down):
+            for dst, src in zip(pinned_out, outs):
+                dst.copy_(src, non_blocking=True)
+    torch.cuda.current_stream().wait_stream(s_up)
+    torch.cuda.current_stream().wait_stream(s_down)
+    f1.record()
+    barrier()
+    wire_ms = hz.max_over_ranks(f0.elapsed_time(f1)) / e2e_steps
+    wire = {"value": world * w.tokens() / (wire_ms * 1e-3), "unit": "tokens/s", "ms_per_step": wire_ms,
+            "h2d_gbs_per_gpu": h2d / wire_ms / 1e6, "d2h_gbs_per_gpu": d2h / wire_ms / 1e6,
+            "what": "same pinned buffers copied in and out concurrently, no kernels: the PCIe bound of e2e"}
+    del dev_in, outs, pipe, sets
+    torch.cuda.empty_cache()
+
+    # ---- every other op of the metric, and the strong-scaling split of the configs ----
+    per_op, strong = {}, {}
+    if args.ops:
+        per_op[args.workload] = {k: head[k] for k in ("workload", "batch_per_gpu", "ms_per_step", "tokens_per_s",
+                                                      "dtype", "blocks", "clocks", "roofline")}
+        for name in ("c1", "c3", "c4", "c5"):
+            if name == args.workload:
+                continue
+            per_op[name] = hz.run_op(WORKLOADS[name], None, args.steps, args.warmup, args.min_seconds)
+        for name in ("c2", "c3", "c4"):
+            full = WORKLOADS[name].B
+            if full % world:
+                continue
+            if world == 1:
+                src = per_op[name]
+                strong[name] = {"batch_per_gpu": full, "ms_per_step": src["ms_per_step"], "tokens_per_s": src["tokens_per_s"],
+                                "note": "one GPU: the strong split is the whole config (same measurement as ops)"}
+                continue
+            rec = hz.run_op(WORKLOADS[name], full // world, args.steps, args.warmup, args.min_seconds)
+            rec["tokens_per_s"] = WORKLOADS[name].B * WORKLOADS[name].T / (rec["ms_per_step"] * 1e-3)
+            strong[name] = {k: rec[k] for k in ("batch_per_gpu", "ms_per_step", "tokens_per_s", "blocks", "clocks")}
+            strong[name]["config_batch"] = full
 
     if rank == 0:
-        if hasattr(w, "roofline"):
-            roof = w.roofline(dominant_ms)
-        else:
-            peak, peak_kind = measured_hbm_peak()
-            alg = w.algorithmic_bytes()[w.dominant]
-            achieved = alg / (dominant_ms * 1e-3) / 1e9
-            roof = {"bound": "hbm", "kernel": w.dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                    "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
-                    "traffic": (w.dominant_traffic_bytes if args.batch is None else None),
-                    "algorithmic_bytes_per_launch": alg, "ms_per_launch": dominant_ms}
+        roof = head["roofline"]
+        if "traffic" not in roof:
+            roof["traffic"] = (w.dominant_traffic_bytes if args.batch is None else None)
         line = {
             "metric": "tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -639,21 +820,28 @@ def run_gpu_arm(args):
             "config": {"workload": w.name, "batch_per_gpu": w.B, "T": w.T, "tokens_per_step_per_gpu": w.tokens(),
                        "l2": f"{nsets} input set(s) rotated, {in_bytes * nsets / 1e6:.0f} MB of inputs > 126 MB L2",
                        "sharding": "independent sequences per rank, no data-path collective",
-                       "launch": "cuda graph replay" if graphs else "direct"},
-            "clocks": clocks.summary(),
+                       "launch": "cuda graph replay" if graphed else "direct",
+                       "timing": f"{len(blocks)} blocks of {args.steps} steps (>= {args.min_seconds} s of device time), "
+                                 "median block reported, max over ranks per block",
+                       "block_ms_min_med_max": head["block_ms_min_med_max"]},
+            "clocks": clock_summary,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": e2e_steps, "batch_slices_in_flight": nslices,
+                    "steps": e2e_steps, "batch_slices_in_flight": nslices, "host_binding": hz.binding,
+                    "wire_floor": wire,
                     "mode": {"stream": "three streams, copy-in of step i+1 overlaps copy-out of step i (two steps in flight)",
                              "graph": "cuda graph replay of the three-stream schedule",
                              "plain": "three streams, step by step"}[mode]},
-            "gpu_launches": w.launches_per_step * args.steps,
+            "gpu_launches": w.launches_per_step * args.steps * len(blocks),
             "roofline": roof,
         }
+        if per_op:
+            line["ops"] = per_op
+            line["strong"] = strong
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(cls)
         print(json.dumps(line))
-    if dist:
-        dist.destroy_process_group()
+    if hz.dist:
+        hz.dist.destroy_process_group()
 
 
 def main():
@@ -662,12 +850,21 @@ def main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=None, help="override sequences per GPU (profiling only)")
     ap.add_argument("--e2e-slices", type=int, default=None, help="override the batch slices of the host pipeline")
     ap.add_argument("--e2e-mode", choices=["stream", "graph", "plain"], default=None, help="host pipeline mode for the e2e figure")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--min-seconds", type=float, default=0.5,
+                    help="repeat the block of --steps steps until this much device time has been measured")
+    ap.add_argument("--ops", dest="ops", action="store_true", default=None,
+                    help="also time every other op of the metric (c1, c3, c4, c5) and the strong-scaling split; "
+                         "default: on when --workload and --batch are not given")
+    ap.add_argument("--no-ops", dest="ops", action="store_false")
     args = ap.parse_args()
+    if args.ops is None:
+        args.ops = args.workload is None and args.batch is None
+    args.workload = args.workload or "c2"
     if args.impl == "reference":
         run_reference_arm(args)
     else:

@@ -12,11 +12,16 @@
  *   - Launch-only: each call validates its arguments on the host, enqueues
  *     kernels on `stream` and returns.  No host synchronisation, no allocation,
  *     no retained pointers.  All buffers, outputs and workspaces included, are
- *     device memory owned by the caller.
+ *     device memory owned by the caller.  The one exception is
+ *     mxk_linrec_c64_bwd_noalloc, which keeps its scratch in the library's own
+ *     device image and remembers that array's address per device (see there).
  *   - Layout: batch-major, time second, features last, C-contiguous --
  *     (B, T, D) or (B, T, H, d); `done` is (B, T) bytes, non-zero = "step t is
  *     the first step of a new episode", i.e. the state before step t is
  *     discarded (memoroid.py:67-85).  `done` may be NULL (no resets).
+ *     Contiguity is part of the contract: there are no stride arguments, a host
+ *     that holds a strided view copies it first (XLA hands custom calls dense
+ *     row-major buffers, so the jax.ffi binding never has to).
  *   - Carries are passed without the reference's singleton time axis:
  *     (B, D) or (B, H, dv, dk).
  *   - Complex tensors are interleaved (re, im) float pairs.  Complex
@@ -51,6 +56,16 @@ enum {
 const char* mxk_status_string(int status);
 /* ABI version of the loaded library (bumped on signature changes). */
 int mxk_abi_version(void);
+
+/* Failure-path self-test.  Every tensor-core kernel below waits for its copies
+ * and MMAs with a bounded poll and, when a wait gives up, sets the caller's
+ * `status` word to 1 and drains instead of spinning or trapping.  This launches
+ * a one-thread kernel that waits, with the same primitive and a limit of
+ * `polls` (1..16, about a millisecond each), on a barrier that nothing ever
+ * completes, so a host can check that the word really gets set and that the
+ * context survives.  It has no counterpart in the reference.
+ *   status  device int, expected to read 1 after the stream has drained */
+int mxk_selftest_bounded_wait(int* status, int polls, mxk_stream_t stream);
 
 /* ---------------------------------------------------------------------------
  * Diagonal linear recurrence  h_t = done_t ? b_t : a_t * h_{t-1} + b_t
@@ -120,7 +135,10 @@ int mxk_linrec_c64_bwd(const float* a, int a_time_invariant, const float* h, con
  *     elements); larger problems return MXK_ERR_SCRATCH_LIMIT and launch nothing.
  *   - The first call on each device looks up the array's device address (one
  *     cudaGetSymbolAddress, no allocation); make that first call before any
- *     stream capture begins.
+ *     stream capture begins.  The address is remembered per device ordinal for
+ *     the life of the process: after cudaDeviceReset (or any teardown of the
+ *     device's primary context) it is stale, so a process that resets a device
+ *     must not call this function on it again.
  *   - All calls on a device share the one array.  Every partial sum is
  *     overwritten before it is read, so nothing has to be cleared between
  *     calls, but two calls whose kernels overlap on the GPU (different streams)
@@ -192,26 +210,36 @@ int mxk_linattn_bf16_bwd(const void* q, const void* k, const void* v, const void
  * i.e. Memoroid.scan_fn (memoroid.py:60-91) over the elements
  * (alpha (I - beta k k^T), beta v k^T) with the operator (M_i M_j, U_i M_j + U_j).
  *
- *   q, k, v   (B,T,H,d) bf16, contiguous, d = 128; k is expected L2-normalised
+ *   q, k, v   (B,T,H,d) bf16, contiguous, d = 128 or 64 (a 64-wide head runs on the
+ *             128-wide tiles with their upper half zero-filled by the tensor maps: half the
+ *             memory traffic, the arithmetic of d = 128); k is expected L2-normalised
  *   alpha     (B,T,H) fp32 in (0, 1];  beta (B,T,H) fp32
  *   s0        (B,H,d_v,d_k) fp32 carried state, NULL = zeros
  *   o         (B,T,H,d) bf16 out;  s_last (B,H,d_v,d_k) fp32 out, optional
  *   chunk_states  optional residual for the backward call,
  *             mxk_gdelta_chunk_states_bytes(...) bytes (per chunk: the bf16 state
  *             entering it and the solved pseudo-values U)
+ *   workspace required scratch of mxk_gdelta_workspace_bytes(...) bytes: a
+ *             chunk-parallel preparation kernel leaves every chunk's
+ *             (I + diag(beta) L)^-1 diag(beta) there (bf16, 8 KiB per chunk) and the
+ *             state-serial kernel reads it back.  Keep it for the backward call on
+ *             the same inputs, which reads it too.
  *   status    optional device int, set non-zero if a bounded wait gave up
  * ------------------------------------------------------------------------- */
 size_t mxk_gdelta_chunk_states_bytes(int B, int T, int H, int d);
+size_t mxk_gdelta_workspace_bytes(int B, int T, int H, int d);
 int mxk_gdelta_bf16_fwd(const void* q, const void* k, const void* v, const float* alpha, const float* beta,
                         const float* s0, const uint8_t* done, void* o, float* s_last, void* chunk_states,
-                        int* status, int B, int T, int H, int d, mxk_stream_t stream);
+                        void* workspace, size_t workspace_bytes, int* status, int B, int T, int H, int d,
+                        mxk_stream_t stream);
 
 /* Reverse mode of mxk_gdelta_bf16_fwd.
  *   d_o (B,T,H,d) bf16 cotangent of o;  ds_last (B,H,d,d) fp32 cotangent of the
  *   next carry, NULL = zeros;  chunk_states from the forward call
  *   dq, dk, dv (B,T,H,d) bf16 out;  dalpha, dbeta (B,T,H) fp32 out (dalpha is 0
  *   where done, whose steps ignore alpha);  ds0 (B,H,d,d) fp32 out, optional.
- * beta must be non-zero wherever its gradient is wanted. */
+ * beta must be non-zero wherever its gradient is wanted (dbeta is written as 0
+ * where beta == 0); alpha must lie in (0, 1] (its logarithm is taken). */
 int mxk_gdelta_bf16_bwd(const void* q, const void* k, const void* v, const float* alpha, const float* beta,
                         const void* d_o, const void* chunk_states, const uint8_t* done, const float* ds_last,
                         void* dq, void* dk, void* dv, float* dalpha, float* dbeta, float* ds0, int* status,
@@ -226,6 +254,13 @@ int mxk_gdelta_bf16_bwd(const void* q, const void* k, const void* v, const float
  * ------------------------------------------------------------------------- */
 int mxk_adam_bf16(void* params, const void* grads, float* m, float* v, long long n, float lr, float beta1,
                   float beta2, float eps, int step, float grad_scale, mxk_stream_t stream);
+/* The same step on fp32 master parameters (optax.adam updates the reference's
+ * fp32 params): `master` (n floats) is read, updated and written back, and
+ * `params` receives its bf16 rounding in the same pass.  master == NULL is
+ * mxk_adam_bf16. */
+int mxk_adam_bf16_master(void* params, float* master, const void* grads, float* m, float* v, long long n,
+                         float lr, float beta1, float beta2, float eps, int step, float grad_scale,
+                         mxk_stream_t stream);
 
 #ifdef __cplusplus
 }

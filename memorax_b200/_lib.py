@@ -20,6 +20,7 @@ _f = ctypes.c_float
 SIGNATURES = {
     "mxk_status_string": (ctypes.c_char_p, [_i]),
     "mxk_abi_version": (_i, []),
+    "mxk_selftest_bounded_wait": (_i, [_p, _i, _p]),
     "mxk_linrec_f32_fwd": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
     "mxk_linrec_c64_fwd": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
     "mxk_linrec_bwd_workspace_bytes": (_z, [_i, _i, _i, _i, _i]),
@@ -33,9 +34,11 @@ SIGNATURES = {
     "mxk_linattn_bf16_fwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p]),
     "mxk_linattn_bf16_bwd": (_i, [_p] * 14 + [_i, _i, _i, _i, _f, _i, _p]),
     "mxk_gdelta_chunk_states_bytes": (_z, [_i, _i, _i, _i]),
-    "mxk_gdelta_bf16_fwd": (_i, [_p] * 11 + [_i, _i, _i, _i, _p]),
+    "mxk_gdelta_workspace_bytes": (_z, [_i, _i, _i, _i]),
+    "mxk_gdelta_bf16_fwd": (_i, [_p] * 11 + [_z, _p, _i, _i, _i, _i, _p]),
     "mxk_gdelta_bf16_bwd": (_i, [_p] * 16 + [_i, _i, _i, _i, _p]),
     "mxk_adam_bf16": (_i, [_p, _p, _p, _p, ctypes.c_longlong, _f, _f, _f, _f, _i, _f, _p]),
+    "mxk_adam_bf16_master": (_i, [_p, _p, _p, _p, _p, ctypes.c_longlong, _f, _f, _f, _f, _i, _f, _p]),
 }
 
 

@@ -62,7 +62,7 @@ class GTrXLStyleValueNet(nn.Module):
     -> Dense(d_model -> 1); the reference's "GTrXL-style" composition
     (README.md:119-124) with the attention block replaced by the delta-rule mixer."""
 
-    def __init__(self, obs_dim=128, d_model=512, num_heads=4, head_dim=128, layers=4):
+    def __init__(self, obs_dim=128, d_model=512, num_heads=8, head_dim=64, layers=4):
         super().__init__()
         self.embed = nn.Linear(obs_dim, d_model)
         blocks = []
@@ -79,9 +79,19 @@ class GTrXLStyleValueNet(nn.Module):
 
 class FlatAdamTrainer:
     """Keeps every parameter (bf16) and gradient as a view into one flat buffer so
-    that the gradient all-reduce is one NCCL call and Adam one kernel launch."""
+    that Adam is one kernel launch and the gradient all-reduce works on contiguous
+    ranges.  The update itself is applied to an fp32 master copy (optax.adam on the
+    reference's fp32 params); the bf16 buffer the model computes with is its rounding,
+    rewritten by the same kernel -- a step of lr = 3e-4 is far below a bf16 ulp at |p| = 1.
 
-    def __init__(self, model, lr=3e-4, betas=(0.9, 0.999), eps=1e-8, process_group=None, world_size=1):
+    With more than one rank the flat gradient is cut into one bucket per top-level block
+    (embedding, each torso block, head).  A bucket's all-reduce is launched from a gradient
+    hook the moment the last gradient of that bucket has been accumulated, so it runs on
+    NCCL's stream underneath the rest of the backward pass; the step waits for all buckets
+    before the Adam kernel."""
+
+    def __init__(self, model, lr=3e-4, betas=(0.9, 0.999), eps=1e-8, process_group=None, world_size=1,
+                 overlap_allreduce=True):
         self.model, self.lr, self.betas, self.eps = model, lr, betas, eps
         self.group, self.world = process_group, world_size
         params = [p for p in model.parameters()]
@@ -91,26 +101,74 @@ class FlatAdamTrainer:
         self.flat = torch.zeros(padded, dtype=torch.bfloat16, device=dev)
         self.flat_grad = torch.zeros(padded, dtype=torch.bfloat16, device=dev)
         off = 0
+        offsets = {}
         for p in params:
             n = p.numel()
             self.flat[off:off + n].copy_(p.data.reshape(-1))
             p.data = self.flat[off:off + n].view_as(p)
             p.grad = self.flat_grad[off:off + n].view_as(p)
+            offsets[p] = (off, off + n)
             off += n
+        self.master = self.flat.float()
         self.m = torch.zeros(padded, dtype=torch.float32, device=dev)
         self.v = torch.zeros(padded, dtype=torch.float32, device=dev)
         self.step_count = 0
+        self.check_every = 16
         self.num_params = total
+        # ---- gradient buckets: contiguous ranges of the flat buffer, one per top-level block
+        self.buckets = []          # (lo, hi, number of parameters)
+        self._pending, self._handles = [], []
+        if world_size > 1 and overlap_allreduce:
+            groups = []
+            for child in self._top_level_blocks(model):
+                ps = [p for p in child.parameters()]
+                if ps:
+                    groups.append(ps)
+            for ps in groups:
+                lo, hi = min(offsets[p][0] for p in ps), max(offsets[p][1] for p in ps)
+                index = len(self.buckets)
+                self.buckets.append((lo, hi, len(ps)))
+                for p in ps:
+                    p.register_post_accumulate_grad_hook(self._make_hook(index))
+            covered = sorted((lo, hi) for lo, hi, _ in self.buckets)
+            assert covered[0][0] == 0 and covered[-1][1] == total and all(
+                a[1] == b[0] for a, b in zip(covered, covered[1:])), "buckets must tile the flat gradient"
+
+    @staticmethod
+    def _top_level_blocks(model):
+        for child in model.children():
+            if isinstance(child, Stack):
+                yield from child.blocks
+            else:
+                yield child
+
+    def _make_hook(self, index):
+        def hook(_param):
+            self._pending[index] -= 1
+            if self._pending[index] == 0:
+                import torch.distributed as dist
+                lo, hi, _ = self.buckets[index]
+                self._handles.append(dist.all_reduce(self.flat_grad[lo:hi], group=self.group, async_op=True))
+        return hook
 
     def step(self, obs, done, target):
         self.flat_grad.zero_()
+        self._pending = [n for _, _, n in self.buckets]
+        self._handles = []
         value = self.model(obs, done)
         loss = 0.5 * (value.float() - target).square().mean()     # VNetwork.loss, heads.py:114-117
         loss.backward()
         if self.world > 1:
-            import torch.distributed as dist
-            dist.all_reduce(self.flat_grad, group=self.group)
+            if self.buckets:
+                for handle in self._handles:
+                    handle.wait()
+                assert len(self._handles) == len(self.buckets), "a gradient bucket was never reduced"
+            else:
+                import torch.distributed as dist
+                dist.all_reduce(self.flat_grad, group=self.group)
         self.step_count += 1
         ops.adam_step(self.flat, self.flat_grad, self.m, self.v, self.step_count, self.lr, self.betas, self.eps,
-                      grad_scale=1.0 / self.world)
+                      grad_scale=1.0 / self.world, master=self.master)
+        if self.step_count % self.check_every == 0:
+            ops.check_status(self.flat.device)   # a bounded wait that gave up inside the mixer kernels
         return loss.detach()

@@ -2,6 +2,12 @@
 // gradients, fp32 moments, bias correction as in optax.adam (the optimiser the
 // reference's algorithms use).  One pass, 16-byte accesses; the gradient is
 // scaled on the fly (1 / world size after a sum all-reduce).
+//
+// With a `master` buffer the update is applied to fp32 parameters (what
+// optax.adam does on the reference's fp32 params) and the bf16 buffer is only
+// the rounded working copy written in the same pass: a step of about lr = 3e-4
+// is below half a bf16 ulp for |p| >= 0.125, so without the master copy such
+// parameters (every normalisation scale at 1.0) would never move.
 #include <cuda_bf16.h>
 
 #include "mxk_common.cuh"
@@ -11,12 +17,19 @@ namespace mxk {
 namespace {
 
 __global__ void __launch_bounds__(256)
-adam_bf16_kernel(uint4* __restrict__ p, const uint4* __restrict__ g, float4* __restrict__ m, float4* __restrict__ v,
-                 long long n8, float lr, float b1, float b2, float eps, float c1, float c2, float gscale) {
+adam_bf16_kernel(uint4* __restrict__ p, float4* __restrict__ master, const uint4* __restrict__ g,
+                 float4* __restrict__ m, float4* __restrict__ v, long long n8, float lr, float b1, float b2, float eps,
+                 float c1, float c2, float gscale) {
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= n8) return;
   float pf[8], gf[8];
-  umma::unpack8_bf16(p[i], pf);
+  if (master) {
+    const float4 lo = master[2 * i], hi = master[2 * i + 1];
+    pf[0] = lo.x; pf[1] = lo.y; pf[2] = lo.z; pf[3] = lo.w;
+    pf[4] = hi.x; pf[5] = hi.y; pf[6] = hi.z; pf[7] = hi.w;
+  } else {
+    umma::unpack8_bf16(p[i], pf);
+  }
   umma::unpack8_bf16(g[i], gf);
   float4 mm[2] = {m[2 * i], m[2 * i + 1]}, vv[2] = {v[2 * i], v[2 * i + 1]};
   float* mf = reinterpret_cast<float*>(mm);
@@ -29,6 +42,10 @@ adam_bf16_kernel(uint4* __restrict__ p, const uint4* __restrict__ g, float4* __r
     pf[e] -= lr * (mf[e] * c1) / (sqrtf(vf[e] * c2) + eps);
   }
   p[i] = umma::pack8_bf16(pf);
+  if (master) {
+    master[2 * i] = make_float4(pf[0], pf[1], pf[2], pf[3]);
+    master[2 * i + 1] = make_float4(pf[4], pf[5], pf[6], pf[7]);
+  }
   m[2 * i] = mm[0]; m[2 * i + 1] = mm[1];
   v[2 * i] = vv[0]; v[2 * i + 1] = vv[1];
 }
@@ -36,18 +53,24 @@ adam_bf16_kernel(uint4* __restrict__ p, const uint4* __restrict__ g, float4* __r
 }  // namespace
 }  // namespace mxk
 
-extern "C" int mxk_adam_bf16(void* params, const void* grads, float* m, float* v, long long n, float lr, float beta1,
-                             float beta2, float eps, int step, float grad_scale, mxk_stream_t stream) {
+extern "C" int mxk_adam_bf16_master(void* params, float* master, const void* grads, float* m, float* v, long long n,
+                                    float lr, float beta1, float beta2, float eps, int step, float grad_scale,
+                                    mxk_stream_t stream) {
   using namespace mxk;
   if (!params || !grads || !m || !v) return MXK_ERR_NULL;
   if (n <= 0 || (n % 8) != 0 || step <= 0) return MXK_ERR_DIMS;
-  for (const void* ptr : {(const void*)params, grads, (const void*)m, (const void*)v})
-    if (!aligned16(ptr)) return MXK_ERR_ALIGN;
+  for (const void* ptr : {(const void*)params, (const void*)master, grads, (const void*)m, (const void*)v})
+    if (ptr && !aligned16(ptr)) return MXK_ERR_ALIGN;
   const float c1 = 1.f / (1.f - powf(beta1, static_cast<float>(step)));
   const float c2 = 1.f / (1.f - powf(beta2, static_cast<float>(step)));
   const long long n8 = n / 8;
   adam_bf16_kernel<<<static_cast<unsigned>((n8 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<uint4*>(params), static_cast<const uint4*>(grads), reinterpret_cast<float4*>(m),
+      static_cast<uint4*>(params), reinterpret_cast<float4*>(master), static_cast<const uint4*>(grads), reinterpret_cast<float4*>(m),
       reinterpret_cast<float4*>(v), n8, lr, beta1, beta2, eps, c1, c2, grad_scale);
   return launch_status();
+}
+
+extern "C" int mxk_adam_bf16(void* params, const void* grads, float* m, float* v, long long n, float lr, float beta1,
+                             float beta2, float eps, int step, float grad_scale, mxk_stream_t stream) {
+  return mxk_adam_bf16_master(params, nullptr, grads, m, v, n, lr, beta1, beta2, eps, step, grad_scale, stream);
 }

@@ -2,14 +2,17 @@
 //
 // One CTA (256 threads, two warpgroups) owns one (batch, head) sequence and walks its
 // 64-token chunks in order with the fp32 state S (128 x 128) resident in tensor memory;
-// K, Q (128-byte-swizzled tiles) and V arrive by TMA one chunk ahead.  Per chunk:
-//   MMAs 1: K K^T, Q K^T (64 x 64), Y^T = S_in K^T (128 x 64)
-//   epilogue 1: row threads build -beta L (fp32, shared) and tril(G o QK^T) (bf16) and
-//               rescale Q, K in place (g Q, gam K); warpgroup 0, thread v, forms its
-//               column of beta (V - g Y) and solves the unit lower-triangular system by
-//               forward substitution in fp32 registers while warpgroup 1 decays S in place
-//   MMAs 2: O^T = S_in (g Q)^T + U^T P^T (128 x 64), S += U^T (gam K) (128 x 128)
-//   epilogue 2: output tile (one TMA store), bf16 operand copy of the new state.
+// K, Q, V (128-byte-swizzled tiles) arrive by TMA one chunk ahead, as does the chunk's
+// T' = (I + diag(beta) L)^-1 diag(beta) from the preparation kernel (gdelta_prep.cu), so the
+// state-serial chain holds no triangular solve, only products:
+//   MMAs 1: Q K^T (64 x 64, two key halves), Y^T = S_in K^T (128 x 64)
+//   epilogue 1: tril(G o QK^T) (bf16), -(g Y)^T (bf16), Q and K rescaled in place (g Q, gam K)
+//   MMAs 2: U^T = V^T T'^T - (g Y)^T T'^T  (128 x 64), i.e. U = T' (V - diag(g) K S_in^T)
+//   epilogue 2: U^T as bf16 operand (and residual for the backward pass); S <- g_last S in place
+//   MMAs 3: O^T = S_in (g Q)^T + U^T P^T (128 x 64), S += U^T (gam K) (128 x 128)
+//   epilogue 3: output tile (one TMA store), bf16 operand copy of the new state.
+#include <cstddef>
+
 #include "gdelta_common.cuh"
 #include "tma.cuh"
 
@@ -30,32 +33,43 @@ struct FwdParams {
   __nv_bfloat16* o;
   float* s_last;
   uint4* chunk_states;
+  const uint4* tprime;        // T' of every chunk, written by the preparation kernel
   int* status;
   int B, T, H;
-  CUtensorMap map_k, map_q;   // 64-token tiles as SW tiles (two 64-column blocks)
-  CUtensorMap map_v, map_o;   // 64-token tiles row-major
+  int d;                      // head dimension in memory: 128, or 64 (the upper half of every tile is then the
+                              // tensor maps' zero fill and the state's rows / columns 64..127 stay zero)
+  CUtensorMap map_k, map_q, map_v;   // 64-token tiles as SW tiles (two 64-column blocks)
+  CUtensorMap map_o;                 // 64-token tiles row-major
+};
+
+// What the kernel needs of a chunk's decay: no alpha / beta (beta is folded into T').
+struct FwdDecay {
+  float cum[kC], g[kC], gam[kC];
 };
 
 struct FwdSmem {
   uint4 s[kStateVecs];        // S_in bf16                      [k/8][v][8]
   uint4 k[kPanD * kC];        // K, after the first MMAs gam K  (SW tiles: two 64-column blocks)
   uint4 q[kPanD * kC];        // Q, after the first MMAs g Q    (SW tiles)
-  uint4 vu[kC * 16];          // V row-major [t][v], then U^T   [j/8][v][8]
+  uint4 v[kPanD * kC];        // V                              (SW tiles)
+  uint4 yu[kPanC * kD];       // -(g Y)^T, then U^T             [t/8][v][8]
+  // p and tp are contiguous: together they stage the bf16 output tile [t][v] once the last MMAs of the
+  // chunk have read them
   uint4 p[kPanC * kC];        // tril(G o QK^T)                 [j/8][t][8]
-  float lt[kC * kC];          // lt[j][t] = -beta_t L_tj, then the bf16 output tile [t][v]
-  uint4 lb[4 * 32];           // bf16 copy of the off-diagonal block, rows t = 32..63, columns j = 0..31: [j/8][t-32][8]
-  ChunkDecay cd;
+  uint4 tp[kAinvVecs];        // T'                             [j/8][t][8]
+  FwdDecay cd;   // cd.gam doubles as the staging of log(alpha) while cum is being built
   uint64_t bar[3];
-  uint64_t bar_load;
+  uint64_t bar_load, bar_tp;
   uint32_t tmem;
 };
-static_assert(sizeof(FwdSmem) <= 112 * 1024, "two CTAs per SM");
+static_assert(sizeof(FwdSmem) <= 113 * 1024, "two CTAs per SM");
+static_assert(offsetof(FwdSmem, tp) == offsetof(FwdSmem, p) + sizeof(uint4) * kPanC * kC, "output staging spans p and tp");
 
 // 256 TMEM columns per CTA (two CTAs per SM):
 //   columns   0..127  S (fp32, all 128 lanes = value rows)
-//   columns 128..191  first K K^T (lanes 0..15 of each warp) and Q K^T (lanes 16..31),
-//                     both M = 64; afterwards O^T (all lanes)
-//   columns 192..255  Y^T = S_in K^T
+//   columns 128..191  Y^T = S_in K^T, afterwards U^T
+//   columns 192..255  Q K^T (keys 0..31 in lanes 0..15 of each warp's quarter, keys 32..63 in lanes 16..31,
+//                     32 columns), afterwards O^T (64 columns)
 #ifdef MXK_TIMING
 }  // namespace
 __device__ unsigned long long g_gdf_phase_cycles[16];
@@ -66,11 +80,10 @@ namespace {
 #endif
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kUpper = 16u << 16;
-constexpr uint32_t kColS = 0, kColKQ = 128, kColO = 128, kColY = 192;
+constexpr uint32_t kColS = 0, kColY = 128, kColU = 128, kColQK = 192, kColO = 192;
 
 // 256 threads: two warpgroups that see the same TMEM lanes (warp w and warp w + 4 share a lane
-// quarter).  They split the columns of every row in the epilogues; around the forward
-// substitution warpgroup 0 solves while warpgroup 1 decays the state.
+// quarter) and split the columns of every row in the epilogues.
 constexpr int kFwdThreads = 256;
 
 __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid_constant__ FwdParams p) {
@@ -90,6 +103,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
     mbar_init(&sm.bar[1], 1);
     mbar_init(&sm.bar[2], 1);
     mbar_init(&sm.bar_load, 1);
+    mbar_init(&sm.bar_tp, 1);
     mbar_init_fence();
   }
   if (warp == 0) tmem_alloc(&sm.tmem, kTmemCols);
@@ -101,7 +115,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
 
   // carried state: thread (v, wg) owns S[v][64 wg .. 64 wg + 63]
   {
-    const float* s0 = p.s0 ? p.s0 + (static_cast<size_t>(bh) * kD + vt) * kD + wg * 64 : nullptr;
+    const float* s0 = (p.s0 && vt < p.d && wg * 64 < p.d) ? p.s0 + (static_cast<size_t>(bh) * p.d + vt) * p.d + wg * 64 : nullptr;
     float vals[64];   // all loads first: the TMEM stores below are compiler memory barriers
 #pragma unroll
     for (int c4 = 0; c4 < 16; ++c4) {
@@ -119,26 +133,40 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
 
   const uint8_t* drow = p.done ? p.done + static_cast<size_t>(b) * p.T : nullptr;
   const size_t bt_base = static_cast<size_t>(b) * p.T;
-  const uint32_t id_64 = idesc_bf16(kC, kC, false, false);
+  const uint32_t id_half = idesc_bf16(kC, 32, false, false);
   const uint32_t id_128x64 = idesc_bf16(kD, kC, false, false);
+  const uint32_t id_vt = idesc_bf16(kD, kC, true, false);
   const uint32_t id_ds = idesc_bf16(kD, kD, false, true);
+  constexpr uint32_t kBlk = kSwBlockVecs * 16;   // bytes between the two 64-column blocks of an SW tile pair
   bool timed_out = false;
 
-  // K, Q (SW tiles) and V (row-major) of a chunk arrive by TMA, issued by one thread
-  // one chunk ahead: as soon as the second MMA group of the previous chunk has released
-  // the buffers, so that the copies overlap that chunk's output epilogue.
+  // K, Q, V (SW tiles) of a chunk arrive by TMA, issued by one thread one chunk ahead: as soon as the last
+  // MMA group of the previous chunk has released the buffers, so that the copies overlap that chunk's
+  // output epilogue.  T' follows at the top of the next iteration (its buffer stages the output tile).
   auto issue_chunk_loads = [&](int cc) {
     fence_smem_to_async();   // earlier generic-proxy accesses to the buffers come first
     tma::expect_bytes(&sm.bar_load, 3 * kPanD * kC * 16);
-    // K, Q as SW tiles: two 64-column blocks of 64 x 128 bytes each
     tma::load_plain_tile(sm.k, &p.map_k, &sm.bar_load, cc * kC, h, b, 0);
     tma::load_plain_tile(sm.k + kSwBlockVecs, &p.map_k, &sm.bar_load, cc * kC, h, b, 64);
     tma::load_plain_tile(sm.q, &p.map_q, &sm.bar_load, cc * kC, h, b, 0);
     tma::load_plain_tile(sm.q + kSwBlockVecs, &p.map_q, &sm.bar_load, cc * kC, h, b, 64);
-    tma::load_plain_tile(sm.vu, &p.map_v, &sm.bar_load, cc * kC, h, b);
+    tma::load_plain_tile(sm.v, &p.map_v, &sm.bar_load, cc * kC, h, b, 0);
+    tma::load_plain_tile(sm.v + kSwBlockVecs, &p.map_v, &sm.bar_load, cc * kC, h, b, 64);
+    if (cc + 1 < nchunks) {   // the chunk after it: into L2 now, so that its loads a chunk from now hit there
+      tma::prefetch_plain_tile(&p.map_k, (cc + 1) * kC, h, b, 0);
+      tma::prefetch_plain_tile(&p.map_q, (cc + 1) * kC, h, b, 0);
+      tma::prefetch_plain_tile(&p.map_v, (cc + 1) * kC, h, b, 0);
+      if (p.d > 64) {
+        tma::prefetch_plain_tile(&p.map_k, (cc + 1) * kC, h, b, 64);
+        tma::prefetch_plain_tile(&p.map_q, (cc + 1) * kC, h, b, 64);
+        tma::prefetch_plain_tile(&p.map_v, (cc + 1) * kC, h, b, 64);
+      }
+      tma::prefetch_bulk(p.tprime + (static_cast<size_t>(bh) * nchunks + cc + 1) * kAinvVecs, kAinvVecs * 16);
+    }
   };
   if (tid == 0) issue_chunk_loads(0);
-  float2 ab_next = fetch_chunk_decay(p.alpha, p.beta, bt_base, p.H, h, 0, p.T, tid);
+  float alpha_next = 1.f;
+  if (tid < kC && tid < p.T) alpha_next = __ldg(p.alpha + (bt_base + tid) * p.H + h);
   linattn::DoneFlags flags_next = linattn::load_done_flags(drow, 0, p.T, lane);
 
 #ifdef MXK_TIMING
@@ -147,17 +175,36 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
   for (int c = 0; c < nchunks; ++c) {
     const int t0 = c * kC;
     const uint64_t dm = linattn::done_mask_from_flags(flags_next);
+    if (tid < kC) sm.cd.gam[tid] = __logf(alpha_next);
     fence_smem_to_async();   // the bf16 state copy written below / above is read by bulk copies and MMAs
     __syncthreads();
-    chunk_decay_from_regs(sm.cd, ab_next, dm, tid);
+    // cum / g / gam of the chunk (same arithmetic as finish_chunk_decay)
+    if (tid < 32) {
+      const float l0 = sm.cd.gam[2 * tid], l1 = sm.cd.gam[2 * tid + 1];
+      float s = l0 + l1;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const float o = __shfl_up_sync(0xffffffffu, s, off);
+        if (tid >= off) s += o;
+      }
+      sm.cd.cum[2 * tid] = s - l1;
+      sm.cd.cum[2 * tid + 1] = s;
+    }
     if (tid == 0) {
       if (p.chunk_states) {
         // residual for the backward pass: the state entering the chunk
         tma::store_bulk(p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * kResidualVecs, sm.s, kStateVecs * 16);
         tma::commit_group();
       }
-      // the previous chunk's output tile (older group) has left `lt` before epilogue 1a rewrites it
+      // the previous chunk's output tile (older group) has left p / tp: T' of this chunk may land there
       if (p.chunk_states) tma::wait_group_read<1>(); else tma::wait_group_read<0>();
+      tma::expect_bytes(&sm.bar_tp, kAinvVecs * 16);
+      tma::load_bulk(sm.tp, p.tprime + (static_cast<size_t>(bh) * nchunks + c) * kAinvVecs, kAinvVecs * 16, &sm.bar_tp);
+    }
+    __syncthreads();
+    if (tid < kC) {
+      sm.cd.g[tid] = row_live(dm, tid) ? __expf(sm.cd.cum[tid]) : 0.f;
+      sm.cd.gam[tid] = row_keep(dm, tid) ? __expf(sm.cd.cum[kC - 1] - sm.cd.cum[tid]) : 0.f;
     }
     MXK_TF(0);
     mbar_wait_flag(&sm.bar_load, c & 1, timed_out);
@@ -168,48 +215,46 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
     if (warp == 0) {
       const bool leader = elect_one();
       fence_after_sync();
-      const Operand ak = sw_operand(smem_u32(sm.k), false, kSwBlockVecs * 16), aq = sw_operand(smem_u32(sm.q), false, kSwBlockVecs * 16);
+      const Operand ak = sw_operand(smem_u32(sm.k), false, kBlk), aq = sw_operand(smem_u32(sm.q), false, kBlk);
+      const Operand bk_hi = sw_operand(smem_u32(sm.k) + 32 * 128, false, kBlk);
       const Operand as{smem_u32(sm.s), kD, false};
-      gemm128(tmem + kColKQ, ak, ak, id_64, false, leader);              // K K^T -> lower lanes
-      gemm128(tmem + kUpper + kColKQ, aq, ak, id_64, false, leader);     // Q K^T -> upper lanes
-      gemm128(tmem + kColY, as, ak, id_128x64, false, leader);           // Y^T = S_in K^T
+      gemm128(tmem + kColQK, aq, ak, id_half, false, leader);               // Q K^T, keys 0..31  -> lanes 0..15
+      gemm128(tmem + kUpper + kColQK, aq, bk_hi, id_half, false, leader);   // Q K^T, keys 32..63 -> lanes 16..31
+      gemm128(tmem + kColY, as, ak, id_128x64, false, leader);              // Y^T = S_in K^T
       if (leader) commit(&sm.bar[0]);
     }
     mbar_wait_flag(&sm.bar[0], c & 1, timed_out);
     fence_after_sync();
     MXK_TF(2);
 
-    // ---- epilogue 1a: lower lanes turn their K K^T row into -beta L (fp32), upper lanes their
-    //      Q K^T row into the masked, decayed bf16 operand, 32 keys per warpgroup; then Q and K are
-    //      rescaled in place (g_t q_t for the inter-chunk output, gam_j k_j for the state update),
-    //      eight 16-byte vectors per thread ----
+    // ---- epilogue 1: every thread turns 16 keys of its Q K^T row into the masked, decayed bf16 operand;
+    //      thread (v, wg) turns 32 tokens of its Y^T row into -(g Y)^T; then Q and K are rescaled in place
+    //      (g_t q_t for the inter-chunk output, gam_j k_j for the state update) ----
     {
       const int lo = row_first_key(dm, row);
-      const float cum_t = sm.cd.cum[row], beta_t = sm.cd.beta[row];
-      {
-        float x[32];
-        tmem_ld_row<32>(lane_base + kColKQ + wg * 32, x);
+      const float cum_t = sm.cd.cum[row];
+      const int j0 = (upper ? 32 : 0) + wg * 16;
+      float qk[16];
+      tmem_ld_row<16>(lane_base + kColQK + wg * 16, qk);
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int j = wg * 32 + e;
+      for (int jq = 0; jq < 2; ++jq) {
+        float pm[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int j = j0 + jq * 8 + e;
           const bool in = (j >= lo && j <= row);
-          x[e] *= in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
+          pm[e] = in ? __expf(cum_t - sm.cd.cum[j]) * qk[jq * 8 + e] : 0.f;
         }
-        if (upper) {
+        sm.p[((j0 >> 3) + jq) * kC + row] = pack8_bf16(pm);
+      }
+      float y[32];
+      tmem_ld_row<32>(lane_base + kColY + wg * 32, y);
 #pragma unroll
-          for (int jq = 0; jq < 4; ++jq) sm.p[(wg * 4 + jq) * kC + row] = pack8_bf16(x + jq * 8);
-        } else {
+      for (int tp8 = 0; tp8 < 4; ++tp8) {
+        float f[8];
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int j = wg * 32 + e;
-            x[e] = (j < row) ? -beta_t * x[e] : 0.f;
-            sm.lt[j * kC + row] = x[e];
-          }
-          if (wg == 0 && row >= 32) {   // rows 32..63 x columns 0..31: operand of the blocked solve's MMA
-#pragma unroll
-            for (int jq = 0; jq < 4; ++jq) sm.lb[jq * 32 + (row - 32)] = pack8_bf16(x + jq * 8);
-          }
-        }
+        for (int e = 0; e < 8; ++e) f[e] = -sm.cd.g[wg * 32 + tp8 * 8 + e] * y[tp8 * 8 + e];
+        sm.yu[(wg * 4 + tp8) * kD + vt] = pack8_bf16(f);
       }
       uint4* tile = upper ? sm.k : sm.q;
       const float sc = upper ? sm.cd.gam[row] : sm.cd.g[row];
@@ -224,70 +269,56 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
       }
     }
     MXK_TF(3);
-    // ---- epilogue 1b.  Warpgroup 0, thread v: right-hand side and forward substitution for its
-    //      column of U.  Warpgroup 1 meanwhile: S <- g_last S in place. ----
-    __align__(8) float r[kC];
-    if (wg == 0) {
-      tmem_ld_row<kC>(lane_base + kColY, r);
-#pragma unroll
-      for (int t = 0; t < kC; ++t) r[t] = sm.cd.beta[t] * (bf16_at(sm.vu, t, vt) - sm.cd.g[t] * r[t]);
-    } else {
+    mbar_wait_flag(&sm.bar_tp, c & 1, timed_out);
+    fence_smem_to_async();
+    fence_before_sync();
+    __syncthreads();
+    MXK_TF(4);
+
+    if (warp == 0) {
+      const bool leader = elect_one();
+      fence_after_sync();
+      const Operand av = sw_operand(smem_u32(sm.v), true, kBlk);     // V^T: contraction over the token rows
+      const Operand ay{smem_u32(sm.yu), kD, false};
+      const Operand bt{smem_u32(sm.tp), kC, false};
+      gemm<kC / 16>(tmem + kColU, av, bt, id_vt, false, leader);          // U^T  = V^T T'^T
+      gemm<kC / 16>(tmem + kColU, ay, bt, id_128x64, true, leader);       // U^T -= (g Y)^T T'^T
+      if (leader) commit(&sm.bar[2]);
+    }
+    // meanwhile: S <- g_last S in place (the last MMAs of the previous chunk are long complete, the next
+    // ones are issued after the barrier below); thread (v, wg) covers state columns 64 wg .. 64 wg + 63
+    {
+      fence_after_sync();
       const float g_last = sm.cd.g[kC - 1];
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
+      for (int q2 = 0; q2 < 2; ++q2) {
         float s[32];
-        tmem_ld_row<32>(lane_base + kColS + q4 * 32, s);
+        tmem_ld_row<32>(lane_base + kColS + wg * 64 + q2 * 32, s);
 #pragma unroll
         for (int e = 0; e < 32; ++e) s[e] *= g_last;
 #pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8) tmem_st8(lane_base + kColS + q4 * 32 + c8 * 8, s + c8 * 8);
+        for (int c8 = 0; c8 < 4; ++c8) tmem_st8(lane_base + kColS + wg * 64 + q2 * 32 + c8 * 8, s + c8 * 8);
       }
       tmem_st_wait();
     }
-    fence_before_sync();
-    __syncthreads();   // -beta L complete; V consumed (U^T reuses its buffer)
-    MXK_TF(4);
-    if (wg == 0) {
-      // Blocked solve: rows 0..31 in fp32 registers; their effect on rows 32..63 (the 32 x 32
-      // off-diagonal block times U_lo, a quarter of the FMAs and half of the dependent chain) on the
-      // tensor core from the bf16 operands U_lo^T and -beta L, fp32 accumulate; then rows 32..63.
+    mbar_wait_flag(&sm.bar[2], c & 1, timed_out);
+    fence_after_sync();
+    MXK_TF(5);
+
+    // ---- epilogue 2: U^T as bf16 operand over -(g Y)^T (dead now) and as the backward pass's residual ----
+    {
       uint4* res = p.chunk_states ? p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * kResidualVecs + kStateVecs : nullptr;
-      forward_substitute_range<0, 31, 32>(reinterpret_cast<float2*>(r), sm.lt);
+      float u[32];
+      tmem_ld_row<32>(lane_base + kColU + wg * 32, u);
 #pragma unroll
-      for (int jp = 0; jp < kPanC / 2; ++jp) {
-        const uint4 u8 = pack8_bf16(r + jp * 8);
-        sm.vu[jp * kD + vt] = u8;
-        if (res) res[jp * kD + vt] = u8;   // the backward pass reuses U instead of solving again
-      }
-      fence_smem_to_async();
-      fence_before_sync();
-      asm volatile("bar.sync 1, 128;" ::: "memory");   // warpgroup 0 only
-      if (warp == 0) {
-        const bool leader = elect_one();
-        fence_after_sync();
-        gemm<2>(tmem + kColKQ, Operand{smem_u32(sm.vu), kD, false}, Operand{smem_u32(sm.lb), 32, false},
-                idesc_bf16(kD, 32, false, false), false, leader);
-        if (leader) commit(&sm.bar[2]);
-      }
-      mbar_wait_flag(&sm.bar[2], c & 1, timed_out);
-      fence_after_sync();
-      {
-        float delta[32];
-        tmem_ld_row<32>(lane_base + kColKQ, delta);
-#pragma unroll
-        for (int e = 0; e < 32; ++e) r[32 + e] += delta[e];
-      }
-      forward_substitute_range<32, kC - 1, kC>(reinterpret_cast<float2*>(r), sm.lt);
-#pragma unroll
-      for (int jp = kPanC / 2; jp < kPanC; ++jp) {
-        const uint4 u8 = pack8_bf16(r + jp * 8);
-        sm.vu[jp * kD + vt] = u8;
-        if (res) res[jp * kD + vt] = u8;
+      for (int jp = 0; jp < 4; ++jp) {
+        const uint4 u8 = pack8_bf16(u + jp * 8);
+        sm.yu[(wg * 4 + jp) * kD + vt] = u8;
+        if (res) res[(wg * 4 + jp) * kD + vt] = u8;
       }
     }
-    MXK_TF(5);
     MXK_TF(6);
-    if (tid == 0) tma::wait_group_read<0>();   // the residual copy has finished reading `s` (rewritten in epilogue 2)
+    if (tid == 0) tma::wait_group_read<0>();   // the residual copy has finished reading `s` (rewritten in epilogue 3)
     fence_smem_to_async();
     fence_before_sync();
     __syncthreads();
@@ -295,9 +326,9 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
     if (warp == 0) {
       const bool leader = elect_one();
       fence_after_sync();
-      const Operand as{smem_u32(sm.s), kD, false}, bgq = sw_operand(smem_u32(sm.q), false, kSwBlockVecs * 16);
-      const Operand au{smem_u32(sm.vu), kD, false}, bp{smem_u32(sm.p), kC, false};
-      const Operand bgk = sw_operand(smem_u32(sm.k), true, kSwBlockVecs * 16);
+      const Operand as{smem_u32(sm.s), kD, false}, bgq = sw_operand(smem_u32(sm.q), false, kBlk);
+      const Operand au{smem_u32(sm.yu), kD, false}, bp{smem_u32(sm.p), kC, false};
+      const Operand bgk = sw_operand(smem_u32(sm.k), true, kBlk);
       gemm128(tmem + kColO, as, bgq, id_128x64, false, leader);         // O^T  = S_in (g Q)^T
       gemm<kC / 16>(tmem + kColO, au, bp, id_128x64, true, leader);     // O^T += U^T P^T
       gemm<kC / 16>(tmem + kColS, au, bgk, id_ds, true, leader);        // S    = g_last S_in + U^T (gam K)
@@ -308,14 +339,15 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
     MXK_TF(7);
     if (c + 1 < nchunks) {
       if (tid == 0) issue_chunk_loads(c + 1);
-      ab_next = fetch_chunk_decay(p.alpha, p.beta, bt_base, p.H, h, t0 + kC, p.T, tid);
+      alpha_next = 1.f;
+      if (tid < kC && t0 + kC + tid < p.T) alpha_next = __ldg(p.alpha + (bt_base + t0 + kC + tid) * p.H + h);
       flags_next = linattn::load_done_flags(drow, t0 + kC, p.T, lane);
     }
 
-    // ---- epilogue 2: output tile (staged row-major for one TMA store), bf16 copy of the new state;
+    // ---- epilogue 3: output tile (staged row-major over p / tp for one TMA store), bf16 copy of the new state;
     //      thread (v, wg) covers tokens 32 wg .. 32 wg + 31 and state columns 64 wg .. 64 wg + 63 ----
     {
-      __nv_bfloat16* otile = reinterpret_cast<__nv_bfloat16*>(sm.lt);
+      __nv_bfloat16* otile = reinterpret_cast<__nv_bfloat16*>(sm.p);
       {
         float o[32];
         tmem_ld_row<32>(lane_base + kColO + wg * 32, o);
@@ -323,7 +355,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
         for (int e = 0; e < 32; ++e) otile[(wg * 32 + e) * kD + vt] = __float2bfloat16(o[e]);
       }
       const bool last = (c == nchunks - 1);
-      float* sl = (last && p.s_last) ? p.s_last + (static_cast<size_t>(bh) * kD + vt) * kD : nullptr;
+      float* sl = (last && p.s_last && vt < p.d) ? p.s_last + (static_cast<size_t>(bh) * p.d + vt) * p.d : nullptr;
 #pragma unroll
       for (int q2 = 0; q2 < 2; ++q2) {
         const int q4 = wg * 2 + q2;
@@ -332,7 +364,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
 #pragma unroll
         for (int c8 = 0; c8 < 4; ++c8) {
           sm.s[(q4 * 4 + c8) * kD + vt] = pack8_bf16(s + c8 * 8);
-          if (sl) {
+          if (sl && q4 * 32 < p.d) {
             *reinterpret_cast<float4*>(sl + q4 * 32 + c8 * 8) = make_float4(s[c8 * 8], s[c8 * 8 + 1], s[c8 * 8 + 2], s[c8 * 8 + 3]);
             *reinterpret_cast<float4*>(sl + q4 * 32 + c8 * 8 + 4) = make_float4(s[c8 * 8 + 4], s[c8 * 8 + 5], s[c8 * 8 + 6], s[c8 * 8 + 7]);
           }
@@ -342,7 +374,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
     fence_smem_to_async();
     __syncthreads();
     if (tid == 0) {
-      tma::store_plain_tile(&p.map_o, sm.lt, t0, h, b);   // rows past the end of the sequence are clipped
+      tma::store_plain_tile(&p.map_o, sm.p, t0, h, b);   // rows past the end of the sequence are clipped
       tma::commit_group();
     }
     MXK_TF(8);
@@ -371,19 +403,28 @@ extern "C" int mxk_debug_gdf_phase_cycles(unsigned long long* out, int reset) {
 extern "C" {
 
 size_t mxk_gdelta_chunk_states_bytes(int B, int T, int H, int d) {
-  if (B <= 0 || T <= 0 || H <= 0 || d != mxk::gdelta::kD) return 0;
+  if (B <= 0 || T <= 0 || H <= 0 || (d != mxk::gdelta::kD && d != 64)) return 0;
   const size_t nchunks = (static_cast<size_t>(T) + mxk::gdelta::kC - 1) / mxk::gdelta::kC;
   return static_cast<size_t>(B) * H * nchunks * mxk::gdelta::kResidualVecs * sizeof(uint4);
 }
 
+size_t mxk_gdelta_workspace_bytes(int B, int T, int H, int d) {
+  if (B <= 0 || T <= 0 || H <= 0 || (d != mxk::gdelta::kD && d != 64)) return 0;
+  const size_t nchunks = (static_cast<size_t>(T) + mxk::gdelta::kC - 1) / mxk::gdelta::kC;
+  return static_cast<size_t>(B) * H * nchunks * mxk::gdelta::kAinvVecs * sizeof(uint4);
+}
+
 int mxk_gdelta_bf16_fwd(const void* q, const void* k, const void* v, const float* alpha, const float* beta,
                         const float* s0, const uint8_t* done, void* o, float* s_last, void* chunk_states,
-                        int* status, int B, int T, int H, int d, mxk_stream_t stream) {
+                        void* workspace, size_t workspace_bytes, int* status, int B, int T, int H, int d,
+                        mxk_stream_t stream) {
   using namespace mxk;
   using namespace mxk::gdelta;
   if (!q || !k || !v || !alpha || !beta || !o) return MXK_ERR_NULL;
+  if (!workspace || workspace_bytes < mxk_gdelta_workspace_bytes(B, T, H, d)) return MXK_ERR_WORKSPACE;
+  if (!aligned16(workspace)) return MXK_ERR_ALIGN;
   if (B <= 0 || T <= 0 || H <= 0 || static_cast<long long>(B) * H > 0x7fffffffLL) return MXK_ERR_DIMS;
-  if (d != kD) return MXK_ERR_UNSUPPORTED;
+  if (d != kD && d != 64) return MXK_ERR_UNSUPPORTED;
   for (const void* ptr : {q, k, v, (const void*)o, (const void*)chunk_states, (const void*)s0, (const void*)s_last})
     if (ptr && !aligned16(ptr)) return MXK_ERR_ALIGN;
   FwdParams prm;
@@ -397,11 +438,14 @@ int mxk_gdelta_bf16_fwd(const void* q, const void* k, const void* v, const float
   prm.o = static_cast<__nv_bfloat16*>(o);
   prm.s_last = s_last;
   prm.chunk_states = static_cast<uint4*>(chunk_states);
+  prm.tprime = static_cast<const uint4*>(workspace);
   prm.status = status;
-  prm.B = B; prm.T = T; prm.H = H;
-  if (!tma::make_sw_map(&prm.map_k, k, B, T, H, kC, kD) || !tma::make_sw_map(&prm.map_q, q, B, T, H, kC, kD) ||
-      !tma::make_plain_map(&prm.map_v, v, B, T, H, kD, kC) || !tma::make_plain_map(&prm.map_o, o, B, T, H, kD, kC))
+  prm.B = B; prm.T = T; prm.H = H; prm.d = d;
+  if (!tma::make_sw_map(&prm.map_k, k, B, T, H, kC, d) || !tma::make_sw_map(&prm.map_q, q, B, T, H, kC, d) ||
+      !tma::make_sw_map(&prm.map_v, v, B, T, H, kC, d) || !tma::make_plain_map(&prm.map_o, o, B, T, H, d, kC, kD))
     return MXK_ERR_UNSUPPORTED;
+  const int st = launch_prep(k, alpha, beta, done, workspace, status, B, T, H, d, static_cast<cudaStream_t>(stream));
+  if (st != MXK_OK) return st;
   cudaError_t e = cudaFuncSetAttribute(gdelta_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(FwdSmem)));
   if (e != cudaSuccess) return static_cast<int>(e);

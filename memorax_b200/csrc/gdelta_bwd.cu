@@ -44,6 +44,7 @@ struct BwdParams {
   float* ds0;
   int* status;
   int B, T, H;
+  int d;                              // head dimension in memory: 128, or 64 (see the forward kernel)
   CUtensorMap map_k, map_q, map_do;   // 64-token tiles as SW tiles (two 64-column blocks)
   CUtensorMap map_dq, map_dk;         // the same for the outputs
   CUtensorMap map_dv;                 // 64-token tiles row-major
@@ -134,6 +135,18 @@ __device__ __forceinline__ void issue_chunk_loads(BwdSmem& sm, const BwdParams& 
   const uint4* src = p.chunk_states + (static_cast<size_t>(b * p.H + h) * nchunks + c) * kResidualVecs;
   tma::load_bulk(sm.s, src, kStateVecs * 16, &sm.bar_load);
   tma::load_bulk(sm.u, src + kStateVecs, kUVecs * 16, &sm.bar_load);
+  if (c > 0) {   // the chunk after it (walking right to left): into L2 now, so that its loads hit there
+    const int tp = t0 - kC;
+    tma::prefetch_plain_tile(&p.map_k, tp, h, b, 0);
+    tma::prefetch_plain_tile(&p.map_q, tp, h, b, 0);
+    tma::prefetch_plain_tile(&p.map_do, tp, h, b, 0);
+    if (p.d > 64) {
+      tma::prefetch_plain_tile(&p.map_k, tp, h, b, 64);
+      tma::prefetch_plain_tile(&p.map_q, tp, h, b, 64);
+      tma::prefetch_plain_tile(&p.map_do, tp, h, b, 64);
+    }
+    tma::prefetch_bulk(src - kResidualVecs, kResidualVecs * 16);
+  }
 }
 
 // 256 threads: two warpgroups that see the same TMEM lanes (warp w and warp w + 4 share a lane
@@ -176,7 +189,7 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
   linattn::DoneFlags flags_next = linattn::load_done_flags(drow, (nchunks - 1) * kC, p.T, lane);
   // cotangent of the next carry: thread (v, wg) owns dS[v][64 wg .. 64 wg + 63]
   {
-    const float* g0 = p.ds_last ? p.ds_last + (static_cast<size_t>(bh) * kD + vt) * kD + wg * 64 : nullptr;
+    const float* g0 = (p.ds_last && vt < p.d && wg * 64 < p.d) ? p.ds_last + (static_cast<size_t>(bh) * p.d + vt) * p.d + wg * 64 : nullptr;
     float vals[64];   // all loads first: the TMEM stores below are compiler memory barriers
 #pragma unroll
     for (int c4 = 0; c4 < 16; ++c4) {
@@ -468,7 +481,7 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
       // dbeta_t = (dUt_t . U_t) / beta_t, once, outside the unrolled loop (a store inside it made every
       // iteration a divergent branch for the warps that hold the diagonal)
       if (row >= j0 && row < j0 + 16 && row < valid)
-        p.dbeta[(static_cast<size_t>(b) * p.T + t0 + row) * p.H + h] = beta_t > 0.f ? wtt / beta_t : 0.f;
+        p.dbeta[(static_cast<size_t>(b) * p.T + t0 + row) * p.H + h] = beta_t != 0.f ? wtt / beta_t : 0.f;
       rs += __shfl_xor_sync(0xffffffffu, rs, 16);
       if (!upper) atomicAdd(&sm.rowsum[row], rs);
       const float gt = sm.cd.g[row];
@@ -574,7 +587,7 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
         }
       }
       const float g_last = sm.cd.g[kC - 1];
-      float* out0 = (c == 0 && p.ds0) ? p.ds0 + (static_cast<size_t>(bh) * kD + vt) * kD : nullptr;
+      float* out0 = (c == 0 && p.ds0 && vt < p.d) ? p.ds0 + (static_cast<size_t>(bh) * p.d + vt) * p.d : nullptr;
 #pragma unroll
       for (int q2 = 0; q2 < 2; ++q2) {
         const int q4 = wg * 2 + q2;
@@ -587,7 +600,7 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
         for (int c8 = 0; c8 < 4; ++c8) {
           tmem_st8(lane_base + kColDS + q4 * 32 + c8 * 8, s + c8 * 8);
           sm.ds[(q4 * 4 + c8) * kD + vt] = pack8_bf16(s + c8 * 8);
-          if (out0) {
+          if (out0 && q4 * 32 < p.d) {
             *reinterpret_cast<float4*>(out0 + q4 * 32 + c8 * 8) = make_float4(s[c8 * 8], s[c8 * 8 + 1], s[c8 * 8 + 2], s[c8 * 8 + 3]);
             *reinterpret_cast<float4*>(out0 + q4 * 32 + c8 * 8 + 4) = make_float4(s[c8 * 8 + 4], s[c8 * 8 + 5], s[c8 * 8 + 6], s[c8 * 8 + 7]);
           }
@@ -600,9 +613,11 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
     __syncthreads();
     if (tid == 0) {
       tma::store_plain_tile(&p.map_dq, sm.r1, t0, h, b, 0);
-      tma::store_plain_tile(&p.map_dq, sm.r1 + kSwBlockVecs, t0, h, b, 64);
       tma::store_plain_tile(&p.map_dk, sm.lt, t0, h, b, 0);
-      tma::store_plain_tile(&p.map_dk, reinterpret_cast<uint4*>(sm.lt) + kSwBlockVecs, t0, h, b, 64);
+      if (p.d > 64) {   // a 64-wide head has no second column block in memory
+        tma::store_plain_tile(&p.map_dq, sm.r1 + kSwBlockVecs, t0, h, b, 64);
+        tma::store_plain_tile(&p.map_dk, reinterpret_cast<uint4*>(sm.lt) + kSwBlockVecs, t0, h, b, 64);
+      }
       tma::commit_group();
     }
   }
@@ -645,7 +660,7 @@ int mxk_gdelta_bf16_bwd(const void* q, const void* k, const void* v, const float
   if (!q || !k || !v || !alpha || !beta || !d_o || !chunk_states || !dq || !dk || !dv || !dalpha || !dbeta)
     return MXK_ERR_NULL;
   if (B <= 0 || T <= 0 || H <= 0 || static_cast<long long>(B) * H > 0x7fffffffLL) return MXK_ERR_DIMS;
-  if (d != kD) return MXK_ERR_UNSUPPORTED;
+  if (d != kD && d != 64) return MXK_ERR_UNSUPPORTED;
   for (const void* ptr : {q, k, v, d_o, chunk_states, (const void*)dq, (const void*)dk, (const void*)dv,
                           (const void*)ds_last, (const void*)ds0})
     if (ptr && !aligned16(ptr)) return MXK_ERR_ALIGN;
@@ -666,15 +681,15 @@ int mxk_gdelta_bf16_bwd(const void* q, const void* k, const void* v, const float
   prm.dbeta = dbeta;
   prm.ds0 = ds0;
   prm.status = status;
-  prm.B = B; prm.T = T; prm.H = H;
+  prm.B = B; prm.T = T; prm.H = H; prm.d = d;
   prm.phase_cycles = nullptr;
   if (g_gd_phase_on) {
     void* sym = nullptr;
     if (cudaGetSymbolAddress(&sym, g_gd_phase_cycles) == cudaSuccess) prm.phase_cycles = static_cast<unsigned long long*>(sym);
   }
-  if (!tma::make_sw_map(&prm.map_k, k, B, T, H, kC, kD) || !tma::make_sw_map(&prm.map_q, q, B, T, H, kC, kD) ||
-      !tma::make_sw_map(&prm.map_do, d_o, B, T, H, kC, kD) || !tma::make_sw_map(&prm.map_dq, dq, B, T, H, kC, kD) ||
-      !tma::make_sw_map(&prm.map_dk, dk, B, T, H, kC, kD) || !tma::make_plain_map(&prm.map_dv, dv, B, T, H, kD, kC))
+  if (!tma::make_sw_map(&prm.map_k, k, B, T, H, kC, d) || !tma::make_sw_map(&prm.map_q, q, B, T, H, kC, d) ||
+      !tma::make_sw_map(&prm.map_do, d_o, B, T, H, kC, d) || !tma::make_sw_map(&prm.map_dq, dq, B, T, H, kC, d) ||
+      !tma::make_sw_map(&prm.map_dk, dk, B, T, H, kC, d) || !tma::make_plain_map(&prm.map_dv, dv, B, T, H, d, kC, kD))
     return MXK_ERR_UNSUPPORTED;
   cudaError_t e = cudaFuncSetAttribute(gdelta_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(sizeof(BwdSmem)));

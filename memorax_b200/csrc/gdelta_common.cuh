@@ -35,6 +35,13 @@ constexpr int kUVecs = kPanC * kD;      // uint4 per bf16 U^T of one chunk (16 K
 // Residual the forward call leaves per (sequence, chunk): the state entering the chunk, then U^T.
 constexpr int kResidualVecs = kStateVecs + kUVecs;
 
+// State-independent part of a chunk, written by the preparation kernel (gdelta_prep.cu) for both the
+// forward and the backward kernel: T' = (I + diag(beta) L)^-1 diag(beta) as bf16, [j/8][t][8] (8 KiB).
+constexpr int kAinvVecs = kPanC * kC;
+// Launches the preparation kernel over all (batch, head, chunk) items; defined in gdelta_prep.cu.
+int launch_prep(const void* k, const float* alpha, const float* beta, const uint8_t* done, void* ainv, int* status,
+                int B, int T, int H, int d, cudaStream_t stream);
+
 // A 64 x 128 bf16 tile as SW tiles (umma.cuh): two 64-column blocks of 64 lines x 128 bytes.
 constexpr int kSwBlockVecs = kC * 8;   // uint4 per block (8 KiB)
 // uint4 index of the 16-byte vector `pn` (0..15) of token row `r`

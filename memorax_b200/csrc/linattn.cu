@@ -111,6 +111,11 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
     tma::load_plain_tile(sm.q, &p.map_q, &sm.bar_load, cc * kC, h, b);
     tma::load_plain_tile(sm.k, &p.map_k, &sm.bar_load, cc * kC, h, b);
     tma::load_panel_tile(sm.v, &p.map_v, &sm.bar_load, cc * kC, h, b);
+    if (cc + 1 < nchunks) {   // the chunk after it: into L2 now, so that its loads a chunk from now hit there
+      tma::prefetch_plain_tile(&p.map_q, (cc + 1) * kC, h, b);
+      tma::prefetch_plain_tile(&p.map_k, (cc + 1) * kC, h, b);
+      tma::prefetch_panel_tile(&p.map_v, (cc + 1) * kC, h, b);
+    }
   };
   if (tid == 0) issue_chunk_loads(0);
 

@@ -152,6 +152,13 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
     tma::load_plain_tile(sm.d_o, &p.map_do, &sm.bar_load, cc * kC, h, b);
     tma::load_bulk(sm.s, p.chunk_states + (static_cast<size_t>(bh) * nchunks + cc) * (kPanelsX * kD),
                    kPanelsX * kD * 16, &sm.bar_load);
+    if (cc > 0) {   // the chunk after it (walking right to left): into L2 now, so that its loads hit there
+      tma::prefetch_plain_tile(&p.map_q, (cc - 1) * kC, h, b);
+      tma::prefetch_plain_tile(&p.map_k, (cc - 1) * kC, h, b);
+      tma::prefetch_plain_tile(&p.map_v, (cc - 1) * kC, h, b);
+      tma::prefetch_plain_tile(&p.map_do, (cc - 1) * kC, h, b);
+      tma::prefetch_bulk(p.chunk_states + (static_cast<size_t>(bh) * nchunks + cc - 1) * (kPanelsX * kD), kPanelsX * kD * 16);
+    }
   };
   if (tid == 0) issue_chunk_loads(nchunks - 1);
 

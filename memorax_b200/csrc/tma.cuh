@@ -53,15 +53,18 @@ inline bool make_panel_map(CUtensorMap* map, const void* base, int B, int T, int
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Map whose loads write `rows` x D tiles row-major, [t][D].  Coordinates: {0, h, t0, b}.
-inline bool make_plain_map(CUtensorMap* map, const void* base, int B, int T, int H, int D, int rows) {
+// Map whose loads write `rows` x box_cols tiles row-major, [t][box_cols].  Coordinates: {0, h, t0, b}.
+// box_cols (default D) may exceed D: the columns past D are zero-filled on loads and clipped on stores,
+// which is how a head of 64 columns is served by a kernel built for 128.
+inline bool make_plain_map(CUtensorMap* map, const void* base, int B, int T, int H, int D, int rows, int box_cols = 0) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return false;
+  if (box_cols <= 0) box_cols = D;
   const cuuint64_t row_bytes = static_cast<cuuint64_t>(H) * D * 2;
   const cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(T),
                               static_cast<cuuint64_t>(B)};
   const cuuint64_t strides[3] = {static_cast<cuuint64_t>(D) * 2, row_bytes, row_bytes * T};
-  const cuuint32_t box[4] = {static_cast<cuuint32_t>(D), 1, static_cast<cuuint32_t>(rows), 1};
+  const cuuint32_t box[4] = {static_cast<cuuint32_t>(box_cols), 1, static_cast<cuuint32_t>(rows), 1};
   const cuuint32_t elem[4] = {1, 1, 1, 1};
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, elem,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -113,6 +116,25 @@ __device__ __forceinline__ void load_bulk(void* dst, const void* src, uint32_t b
                    umma::smem_u32(dst)),
                "l"(src), "r"(bytes), "r"(umma::smem_u32(bar))
                : "memory");
+}
+// ---- global -> L2 only: the tile a later load_*_tile will fetch, requested a chunk ahead so that the
+//      load itself finds it in L2 (no shared memory, no barrier, no completion to wait for).
+//      Coordinates follow the alignment rule of the loads (innermost one a multiple of 16 bytes). ----
+__device__ __forceinline__ void prefetch_plain_tile(const CUtensorMap* map, int t0, int h, int b, int c0 = 0) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(c0), "r"(h), "r"(t0), "r"(b)
+               : "memory");
+}
+__device__ __forceinline__ void prefetch_panel_tile(const CUtensorMap* map, int t0, int h, int b) {
+  asm volatile("cp.async.bulk.prefetch.tensor.5d.L2.global.tile [%0, {%1, %2, %3, %4, %5}];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(0), "r"(t0), "r"(0), "r"(h), "r"(b)
+               : "memory");
+}
+// Contiguous range; `src` 16-byte aligned, `bytes` a multiple of 16.
+__device__ __forceinline__ void prefetch_bulk(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 // ---- shared -> global (bulk groups of the issuing thread) ----
 // Tile store through a plain map; rows past the end of the sequence are clipped.

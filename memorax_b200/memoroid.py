@@ -248,7 +248,8 @@ class DeltaNetCell(MemoroidCellBase):
     ``(alpha (I - beta k k^T), beta v k^T)`` with operator
     ``((M_i, U_i), (M_j, U_j)) -> (M_i M_j, U_i M_j + U_j)``; the carry keeps
     only the state ``S (B,1,H,d_v,d_k)`` (the map leaf is O(d_k^2) per step and
-    no read-out uses it).  ``head_dim`` must be 128."""
+    no read-out uses it).  ``head_dim`` is 128 or 64 (a 64-wide head runs on the
+    128-wide kernels with the upper half of every tile zero-filled by the tensor maps)."""
 
     def __init__(self, features, head_dim, num_heads, in_features=None):
         super().__init__()

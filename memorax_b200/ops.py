@@ -24,6 +24,8 @@ def _stream():
 
 
 def _dev(t, dtype, name):
+    """Device tensor of the given dtype in the dense layout the C-ABI requires.  The ABI has no stride
+    arguments; a strided view (e.g. a time slice ``x[:, :h]``) is copied here, once, before the launch."""
     if t is None:
         return None
     if not t.is_cuda:
@@ -159,14 +161,48 @@ class LogLinRec(torch.autograd.Function):
         return gls, gd, gx0, None, None
 
 
-# ------------------------------------------------------- linear attention
+# ------------------------------------------------------- device status word
+# One int32 per device that every tensor-core launch is handed: a kernel whose bounded wait gave up
+# sets it to 1 and drains.  ``check=True`` on a wrapper reads it right after the launch (one host
+# sync); the autograd Functions never sync -- call :func:`check_status` where a sync is affordable
+# (end of a training step, end of a rollout).
+_STATUS_WORDS = {}
+
+
 def _status_word(device):
-    return torch.zeros(1, dtype=torch.int32, device=device)
+    device = torch.device(device)
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    word = _STATUS_WORDS.get(key)
+    if word is None:
+        word = _STATUS_WORDS[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+    return word
 
 
 def _check_status(word, what):
-    if int(word.item()) != 0:
-        raise _lib.MxkError(what, int(word.item()), "a bounded device-side wait gave up")
+    value = int(word.item())
+    if value != 0:
+        word.zero_()
+        raise _lib.MxkError(what, value, "a bounded device-side wait gave up; the results of launches since "
+                                         "the last check are undefined")
+
+
+def check_status(device=None):
+    """Raise :class:`MxkError` if any launch on ``device`` since the last check reported that a bounded
+    device-side wait gave up (synchronises with the device).  The word is cleared on failure."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    _check_status(_status_word(device), "memorax_b200 kernels")
+
+
+def selftest_bounded_wait(polls=2, device=None):
+    """Launch the library's failure-path self-test: a kernel that waits, bounded, on a barrier nothing
+    completes.  Returns the status word's value afterwards (1 = the wait gave up and reported it)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = torch.zeros(1, dtype=torch.int32, device=device)
+    _lib.call("mxk_selftest_bounded_wait", _ptr(word), int(polls), _stream())
+    return int(word.item())
+
+
+# ------------------------------------------------------- linear attention
 
 
 def linattn_fwd(q, k, v, s0=None, z0=None, done=None, eps=1e-6, feature_map=True, save_states=False,
@@ -184,7 +220,7 @@ def linattn_fwd(q, k, v, s0=None, z0=None, done=None, eps=1e-6, feature_map=True
     if save_states:
         nbytes = _lib.lib.mxk_linattn_chunk_states_bytes(bsz, steps, heads, dim)
         states = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
-    status = _status_word(q.device) if check else None
+    status = _status_word(q.device)
     _lib.call("mxk_linattn_bf16_fwd", _ptr(q), _ptr(k), _ptr(v), _ptr(s0), _ptr(z0), _ptr(_done_bytes(done)),
               _ptr(o), _ptr(s_last), _ptr(z_last), _ptr(states), _ptr(status), bsz, steps, heads, dim,
               float(eps), int(feature_map), _stream())
@@ -202,7 +238,7 @@ def linattn_bwd(q, k, v, d_o, chunk_states, done=None, ds_last=None, dz_last=Non
     dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
     ds0 = torch.empty(bsz, heads, dim, dim, dtype=torch.float32, device=q.device)
     dz0 = torch.empty(bsz, heads, dim, dtype=torch.float32, device=q.device)
-    status = _status_word(q.device) if check else None
+    status = _status_word(q.device)
     _lib.call("mxk_linattn_bf16_bwd", _ptr(q), _ptr(k), _ptr(v), _ptr(d_o), _ptr(chunk_states),
               _ptr(_done_bytes(done)), _ptr(ds_last), _ptr(dz_last), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(ds0),
               _ptr(dz0), _ptr(status), bsz, steps, heads, dim, float(eps), int(feature_map), _stream())
@@ -233,8 +269,9 @@ class LinAttn(torch.autograd.Function):
 
 # --------------------------------------------------------- gated delta rule
 def gdelta_fwd(q, k, v, alpha, beta, s0=None, done=None, save_states=False, check=False):
-    """Gated delta rule; q, k, v (B,T,H,128) bf16, alpha/beta (B,T,H) fp32.
-    Returns ``(o, s_last, chunk_states)``."""
+    """Gated delta rule; q, k, v (B,T,H,d) bf16 with d = 128 or 64, alpha/beta (B,T,H) fp32.
+    Returns ``(o, s_last, chunk_states)``; with ``save_states`` the third item is the pair
+    ``(chunk_states, workspace)`` that :func:`gdelta_bwd` takes."""
     q, k, v = (_dev(t, torch.bfloat16, n) for t, n in ((q, "q"), (k, "k"), (v, "v")))
     alpha, beta = _dev(alpha, torch.float32, "alpha"), _dev(beta, torch.float32, "beta")
     s0 = _dev(s0, torch.float32, "s0")
@@ -246,13 +283,15 @@ def gdelta_fwd(q, k, v, alpha, beta, s0=None, done=None, save_states=False, chec
     if save_states:
         states = torch.empty(_lib.lib.mxk_gdelta_chunk_states_bytes(bsz, steps, heads, dim), dtype=torch.uint8,
                              device=q.device)
-    status = _status_word(q.device) if check else None
+    ws_bytes = _lib.lib.mxk_gdelta_workspace_bytes(bsz, steps, heads, dim)
+    workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    status = _status_word(q.device)
     _lib.call("mxk_gdelta_bf16_fwd", _ptr(q), _ptr(k), _ptr(v), _ptr(alpha), _ptr(beta), _ptr(s0),
-              _ptr(_done_bytes(done)), _ptr(o), _ptr(s_last), _ptr(states), _ptr(status), bsz, steps, heads, dim,
-              _stream())
+              _ptr(_done_bytes(done)), _ptr(o), _ptr(s_last), _ptr(states), _ptr(workspace), ws_bytes, _ptr(status),
+              bsz, steps, heads, dim, _stream())
     if check:
         _check_status(status, "mxk_gdelta_bf16_fwd")
-    return o, s_last, states
+    return o, s_last, ((states, workspace) if save_states else None)
 
 
 def gdelta_bwd(q, k, v, alpha, beta, d_o, chunk_states, done=None, ds_last=None, check=False):
@@ -260,11 +299,12 @@ def gdelta_bwd(q, k, v, alpha, beta, d_o, chunk_states, done=None, ds_last=None,
     q, k, v, d_o = (_dev(t, torch.bfloat16, n) for t, n in ((q, "q"), (k, "k"), (v, "v"), (d_o, "d_o")))
     alpha, beta = _dev(alpha, torch.float32, "alpha"), _dev(beta, torch.float32, "beta")
     ds_last = _dev(ds_last, torch.float32, "ds_last")
+    chunk_states, workspace = chunk_states
     bsz, steps, heads, dim = q.shape
     dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
     dalpha, dbeta = torch.empty_like(alpha), torch.empty_like(beta)
     ds0 = torch.empty(bsz, heads, dim, dim, dtype=torch.float32, device=q.device)
-    status = _status_word(q.device) if check else None
+    status = _status_word(q.device)
     _lib.call("mxk_gdelta_bf16_bwd", _ptr(q), _ptr(k), _ptr(v), _ptr(alpha), _ptr(beta), _ptr(d_o),
               _ptr(chunk_states), _ptr(_done_bytes(done)), _ptr(ds_last), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dalpha),
               _ptr(dbeta), _ptr(ds0), _ptr(status), bsz, steps, heads, dim, _stream())
@@ -278,23 +318,26 @@ class GatedDelta(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, alpha, beta, s0, done):
-        o, s_last, states = gdelta_fwd(q, k, v, alpha, beta, s0, done, save_states=True)
-        ctx.save_for_backward(q, k, v, alpha, beta, states, done)
+        o, s_last, (states, workspace) = gdelta_fwd(q, k, v, alpha, beta, s0, done, save_states=True)
+        ctx.save_for_backward(q, k, v, alpha, beta, states, workspace, done)
         ctx.has_state = s0 is not None
         return o, s_last
 
     @staticmethod
     def backward(ctx, d_o, ds_last):
-        q, k, v, alpha, beta, states, done = ctx.saved_tensors
-        dq, dk, dv, dalpha, dbeta, ds0 = gdelta_bwd(q, k, v, alpha, beta, d_o, states, done, ds_last)
+        q, k, v, alpha, beta, states, workspace, done = ctx.saved_tensors
+        dq, dk, dv, dalpha, dbeta, ds0 = gdelta_bwd(q, k, v, alpha, beta, d_o, (states, workspace), done, ds_last)
         return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dalpha.to(alpha.dtype), dbeta.to(beta.dtype),
                 ds0 if ctx.has_state else None, None)
 
 
 # ------------------------------------------------------------------- Adam
-def adam_step(params, grads, m, v, step, lr=3e-4, betas=(0.9, 0.999), eps=1e-8, grad_scale=1.0):
-    """In-place fused Adam on flat buffers (bf16 params/grads, fp32 moments)."""
+def adam_step(params, grads, m, v, step, lr=3e-4, betas=(0.9, 0.999), eps=1e-8, grad_scale=1.0, master=None):
+    """In-place fused Adam on flat buffers (bf16 params/grads, fp32 moments).  With ``master`` (fp32, same
+    length) the update is applied to the fp32 copy and ``params`` receives its bf16 rounding."""
     assert params.dtype == torch.bfloat16 and grads.dtype == torch.bfloat16
     assert m.dtype == torch.float32 and v.dtype == torch.float32 and params.is_contiguous() and grads.is_contiguous()
-    _lib.call("mxk_adam_bf16", _ptr(params), _ptr(grads), _ptr(m), _ptr(v), params.numel(), float(lr), float(betas[0]),
-              float(betas[1]), float(eps), int(step), float(grad_scale), _stream())
+    if master is not None:
+        assert master.dtype == torch.float32 and master.is_contiguous() and master.numel() == params.numel()
+    _lib.call("mxk_adam_bf16_master", _ptr(params), _ptr(master), _ptr(grads), _ptr(m), _ptr(v), params.numel(),
+              float(lr), float(betas[0]), float(betas[1]), float(eps), int(step), float(grad_scale), _stream())

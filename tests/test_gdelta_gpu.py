@@ -1,6 +1,10 @@
 """GPU parity of the gated delta rule against the fp64 CPU oracle (the
 published recurrence; the reference has no such cell), through the C-ABI.
-bf16 inputs, fp32 state; tolerance 2e-2 max-abs on outputs and gradients."""
+bf16 inputs, fp32 state.  Tolerance: 2e-2 max-abs on the outputs (O(1)); the
+gradients reach O(10..30) and leave as bf16, where half an ulp alone exceeds
+2e-2 absolute, so each gradient tensor is held to 1e-2 of its max-abs
+(measured: <= 5e-3), which is 2e-2 absolute or better wherever the tensor is
+O(1)."""
 import pytest
 import torch
 
@@ -8,6 +12,7 @@ from oracle import memoroid_oracle as mo
 
 pytestmark = pytest.mark.gpu
 ATOL = 2e-2
+GRAD_RTOL = 1e-2
 
 
 def make_case(seed, bsz, steps, heads, p_done, zero_state=True, dim=128):
@@ -77,10 +82,33 @@ def test_gdelta_bwd(shape, p_done, zero_state):
         ref = leaf.grad
         if name == "dalpha":   # steps that start an episode ignore alpha
             assert float(got.cpu()[done[:, :, None].expand_as(got)].abs().max() if done.any() else 0.0) == 0.0
-        # gradients here are O(1..30); 2e-2 max-abs is applied relative to each tensor's scale
-        tol = ATOL * max(1.0, float(ref.abs().max()))
+        tol = GRAD_RTOL * max(1.0, float(ref.abs().max()))
         err = max_abs(got.float(), ref)
         assert err <= tol, f"{name}: {err:.4f} > {tol:.4f} (ref max {float(ref.abs().max()):.3f})"
+
+
+@pytest.mark.parametrize("shape,p_done,zero_state", [((2, 130, 3), 0.03, False), ((1, 64, 8), 0.0, True)])
+def test_gdelta_head_dim_64(shape, p_done, zero_state):
+    """64-wide heads (the training-step configuration: 8 heads of 64), forward and backward."""
+    from memorax_b200 import ops
+    q, k, v, alpha, beta, s0, done = make_case(sum(shape) + 64, *shape, p_done, zero_state, dim=64)
+    gen = torch.Generator().manual_seed(6)
+    d_o = torch.randn(*q.shape, generator=gen).bfloat16()
+    ds_last = torch.randn(*s0.shape, generator=gen) * 0.2
+    leaves = [t.double().requires_grad_() for t in (q, k, v, alpha, beta, s0)]
+    o_ref, s_ref = mo.gdelta_seq(*leaves, done.double())
+    ((o_ref * d_o.double()).sum() + (s_ref * ds_last.double()).sum()).backward()
+    cu = lambda t: t.cuda()
+    o, s_last, states = ops.gdelta_fwd(cu(q), cu(k), cu(v), cu(alpha), cu(beta), cu(s0), cu(done), save_states=True,
+                                       check=True)
+    assert o.shape == q.shape and s_last.shape == s0.shape
+    assert max_abs(o.float(), o_ref) <= ATOL
+    assert max_abs(s_last, s_ref) <= 1e-2 * max(1.0, float(s_ref.abs().max()))
+    outs = ops.gdelta_bwd(cu(q), cu(k), cu(v), cu(alpha), cu(beta), cu(d_o), states, cu(done), cu(ds_last), check=True)
+    for got, leaf, name in zip(outs, leaves, ["dq", "dk", "dv", "dalpha", "dbeta", "ds0"]):
+        assert got.shape == leaf.shape
+        err, tol = max_abs(got.float(), leaf.grad), GRAD_RTOL * max(1.0, float(leaf.grad.abs().max()))
+        assert err <= tol, f"{name}: {err:.4f} > {tol:.4f}"
 
 
 def test_gdelta_autograd_function():
@@ -94,4 +122,4 @@ def test_gdelta_autograd_function():
     o, _ = ops.GatedDelta.apply(*dev, done.cuda())
     (o.float() * w.cuda()).sum().backward()
     for got, leaf in zip(dev, leaves):
-        assert max_abs(got.grad.float(), leaf.grad) <= ATOL * max(1.0, float(leaf.grad.abs().max()))
+        assert max_abs(got.grad.float(), leaf.grad) <= GRAD_RTOL * max(1.0, float(leaf.grad.abs().max()))
