@@ -35,7 +35,7 @@ const char* mxk_status_string(int status) {
   return "unknown mxk status";
 }
 
-int mxk_abi_version(void) { return 2; }
+int mxk_abi_version(void) { return 3; }
 
 int mxk_selftest_bounded_wait(int* status, int polls, mxk_stream_t stream) {
   if (!status) return MXK_ERR_NULL;

@@ -421,12 +421,12 @@ int mxk_gdelta_bf16_fwd(const void* q, const void* k, const void* v, const float
   using namespace mxk;
   using namespace mxk::gdelta;
   if (!q || !k || !v || !alpha || !beta || !o) return MXK_ERR_NULL;
-  if (!workspace || workspace_bytes < mxk_gdelta_workspace_bytes(B, T, H, d)) return MXK_ERR_WORKSPACE;
-  if (!aligned16(workspace)) return MXK_ERR_ALIGN;
   if (B <= 0 || T <= 0 || H <= 0 || static_cast<long long>(B) * H > 0x7fffffffLL) return MXK_ERR_DIMS;
   if (d != kD && d != 64) return MXK_ERR_UNSUPPORTED;
   for (const void* ptr : {q, k, v, (const void*)o, (const void*)chunk_states, (const void*)s0, (const void*)s_last})
     if (ptr && !aligned16(ptr)) return MXK_ERR_ALIGN;
+  if (!workspace || workspace_bytes < mxk_gdelta_workspace_bytes(B, T, H, d)) return MXK_ERR_WORKSPACE;
+  if (!aligned16(workspace)) return MXK_ERR_ALIGN;
   FwdParams prm;
   prm.q = static_cast<const __nv_bfloat16*>(q);
   prm.k = static_cast<const __nv_bfloat16*>(k);

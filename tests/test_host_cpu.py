@@ -31,7 +31,7 @@ def test_library_exports_every_declared_symbol(lib):
 
 
 def test_status_strings_and_validation_without_a_gpu(lib):
-    assert lib.lib.mxk_abi_version() >= 1
+    assert lib.lib.mxk_abi_version() >= 3
     assert lib.status_string(0) == "ok"
     for code in (-1, -2, -3, -4, -5, -6):
         assert lib.status_string(code) != "unknown mxk status"
@@ -41,14 +41,17 @@ def test_status_strings_and_validation_without_a_gpu(lib):
     assert L.mxk_linrec_c64_bwd(None, 1, None, None, None, None, None, None, None, None, None, 0, 1, 1, 1, 0, None) == -1
     assert L.mxk_loglinrec_f32_fwd(None, None, None, None, None, None, None, None, 1, 1, 1, None) == -1
     assert L.mxk_linattn_bf16_fwd(*([None] * 11), 1, 1, 1, 64, 1e-6, 1, None) == -1
-    assert L.mxk_gdelta_bf16_fwd(*([None] * 11), 1, 1, 1, 128, None) == -1
+    assert L.mxk_gdelta_bf16_fwd(*([None] * 11), 0, None, 1, 1, 1, 128, None) == -1
     assert L.mxk_gdelta_bf16_bwd(*([None] * 16), 1, 1, 1, 128, None) == -1
     import ctypes
     buf = (ctypes.c_char * 256)()
     p = ctypes.addressof(buf) & ~15
     assert L.mxk_linattn_bf16_fwd(p, p, p, None, None, None, p, None, None, None, None, 1, 1, 1, 32, 1e-6, 1, None) == -4
     assert L.mxk_linattn_bf16_fwd(p, p, p, None, None, None, p, None, None, None, None, 0, 1, 1, 64, 1e-6, 1, None) == -2
-    assert L.mxk_gdelta_bf16_fwd(p, p, p, p, p, None, None, p + 2, None, None, None, 1, 1, 1, 128, None) == -3
+    assert L.mxk_gdelta_bf16_fwd(p, p, p, p, p, None, None, p + 2, None, None, p, 1 << 20, None, 1, 1, 1, 128, None) == -3
+    assert L.mxk_gdelta_bf16_fwd(p, p, p, p, p, None, None, p, None, None, None, 0, None, 1, 1, 1, 128, None) == -5
+    assert L.mxk_gdelta_bf16_fwd(p, p, p, p, p, None, None, p, None, None, p, 16, None, 1, 1, 1, 128, None) == -5
+    assert L.mxk_gdelta_workspace_bytes(2, 65, 3, 64) == 2 * 3 * 2 * 8192
     assert L.mxk_linrec_c64_bwd_noalloc(p, p, None, None, p, None, p, p, None, 1 << 12, 1, 1 << 12, 0, None) == -6
     assert L.mxk_linattn_chunk_states_bytes(2, 65, 3, 64) == 2 * 3 * 2 * 9 * 64 * 16
     assert L.mxk_gdelta_chunk_states_bytes(2, 65, 3, 128) == 2 * 3 * 2 * (16 + 8) * 128 * 16
