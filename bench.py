@@ -375,13 +375,14 @@ class MambaN2:
     """Mamba selective scan fwd+bwd (the scan of MambaCell, mamba.py:109-122, at the shipped example's
     size, examples/gradient_ppo_craftax.py:70-98: MambaCell(features=512) = 8 heads x 16 x 16 state,
     128 environments per device; T widened from 64 to 256 steps so that the inputs exceed L2): real fp32
-    recurrence over H*N*P = 2048 channels with a per-(b,t,head) decay, materialised as the reference does."""
+    recurrence over H*N*P = 2048 channels with a per-(b,t,head) decay that the kernels read un-expanded
+    (one value per group of N*P = 256 channels) and whose gradient they reduce per head."""
     name = "n2_mamba_scan_fwd_bwd"
     dtype = "f32"
     B, T, H, N, P = 128, 256, 8, 16, 16
     p_done = 0.01
     seed = 1234 + 6
-    dominant = "linrec_bwd_kernel"
+    dominant = "linrec_grouped_bwd_kernel"
     launches_per_step = 2
     dominant_traffic_bytes = None
     cpu_sample_batch = 16
@@ -399,24 +400,24 @@ class MambaN2:
         dt = torch.nn.functional.softplus(rn(self.B, self.T, self.H) - 2.0)
         a_neg = -torch.exp(torch.rand(self.H, generator=g, device=device) * math.log(16.0))
         decay = torch.exp(dt * a_neg)
-        return dict(a=decay[..., None].expand(self.B, self.T, self.H, self.N * self.P).reshape(self.B, self.T, width).contiguous(),
-                    z=rn(self.B, self.T, width) * 0.1, gh=rn(self.B, self.T, width),
+        return dict(a=decay.contiguous(), z=rn(self.B, self.T, width) * 0.1, gh=rn(self.B, self.T, width),
                     done=(torch.rand(self.B, self.T, generator=g, device=device) < self.p_done).to(torch.uint8))
 
     def algorithmic_bytes(self):
         n = self.B * self.T * self.H * self.N * self.P
-        # fwd: read a, z, write h; bwd: read a, h, gh, write gz, ga
-        return {"linrec_fwd_kernel": 12 * n, "linrec_bwd_kernel": 20 * n}
+        # fwd: read z, write h (+ the per-head decay); bwd: read h, gh, write gz (+ decay in, its gradient out)
+        small = 4 * self.B * self.T * self.H
+        return {"linrec_grouped_fwd_kernel": 8 * n + small, "linrec_grouped_bwd_kernel": 12 * n + 2 * small}
 
     def algorithmic_flops(self):
         n = self.B * self.T * self.H * self.N * self.P
-        return {"linrec_fwd_kernel": 2 * n, "linrec_bwd_kernel": 4 * n}
+        return {"linrec_grouped_fwd_kernel": 2 * n, "linrec_grouped_bwd_kernel": 4 * n}
 
     def step(self, x, ops, mark=None):
-        h, _ = ops.linrec_fwd(x["a"], x["z"], None, None, x["done"], want_decay=False)
+        h, _ = ops.linrec_grouped_fwd(x["a"], x["z"], None, None, x["done"], want_decay=False)
         if mark:
             mark[0].record()
-        gb, ga, _ = ops.linrec_bwd(x["a"], h, None, x["done"], x["gh"], None, need_ga=True, need_gh0=False)
+        gb, ga, _ = ops.linrec_grouped_bwd(x["a"], h, None, x["done"], x["gh"], None, need_ga=True, need_gh0=False)
         if mark:
             mark[1].record()
         return (h[:, -1], gb, ga)
@@ -424,7 +425,8 @@ class MambaN2:
     def cpu_step(self, x):
         from oracle import memoroid_oracle as mo
         a, z = x["a"].clone().requires_grad_(), x["z"].clone().requires_grad_()
-        h, _ = mo.linrec_seq(a, z, torch.zeros(z.shape[0], z.shape[2]), x["done"].float())
+        h, _ = mo.linrec_seq(a.repeat_interleave(self.N * self.P, dim=-1), z, torch.zeros(z.shape[0], z.shape[2]),
+                             x["done"].float())
         (h * x["gh"]).sum().backward()
         return h
 

@@ -120,6 +120,20 @@ int mxk_linrec_c64_bwd(const float* a, int a_time_invariant, const float* h, con
                        float* ga, float* gh0, void* workspace, size_t workspace_bytes,
                        int B, int T, int D, int conjugate, mxk_stream_t stream);
 
+/* The real recurrence with one decay per GROUP of channels: a is (B,T,G), D = G * group channels,
+ * channel c uses a[..., c / group].  This is MambaCell's scan (mamba.py:109-122: a scalar decay per
+ * (b, t, head) over a state_dim x head_dim matrix state) without expanding the decay to full width.
+ * group must be a multiple of 128 (MXK_ERR_UNSUPPORTED otherwise: expand the decay and use
+ * mxk_linrec_f32_fwd).  a0 / a_last, the decay leaf of the carry, are (B,G).
+ * Backward: ga (B,T,G) is reduced over each group in the kernel (fixed order, no atomics);
+ * `workspace` of mxk_linrec_grouped_bwd_workspace_bytes(...) bytes is needed when group > 128. */
+size_t mxk_linrec_grouped_bwd_workspace_bytes(int B, int T, int D, int G);
+int mxk_linrec_f32_grouped_fwd(const float* a, const float* b, const float* h0, const float* a0, const uint8_t* done,
+                               float* h, float* a_last, int B, int T, int D, int G, mxk_stream_t stream);
+int mxk_linrec_f32_grouped_bwd(const float* a, const float* h, const float* h0, const uint8_t* done, const float* gh,
+                               const float* gh_last, float* gb, float* ga, float* gh0, void* workspace,
+                               size_t workspace_bytes, int B, int T, int D, int G, mxk_stream_t stream);
+
 /* Allocation-free variant of mxk_linrec_c64_bwd for a time-invariant decay
  * (the LRU / S5 case).  It has no counterpart in the reference; it exists for
  * hosts that cannot hand this library a workspace.  An XLA custom call is
@@ -235,13 +249,15 @@ int mxk_gdelta_bf16_fwd(const void* q, const void* k, const void* v, const float
 
 /* Reverse mode of mxk_gdelta_bf16_fwd.
  *   d_o (B,T,H,d) bf16 cotangent of o;  ds_last (B,H,d,d) fp32 cotangent of the
- *   next carry, NULL = zeros;  chunk_states from the forward call
+ *   next carry, NULL = zeros;  chunk_states and workspace as the forward call on the
+ *   same inputs left them (both are read only here)
  *   dq, dk, dv (B,T,H,d) bf16 out;  dalpha, dbeta (B,T,H) fp32 out (dalpha is 0
  *   where done, whose steps ignore alpha);  ds0 (B,H,d,d) fp32 out, optional.
  * beta must be non-zero wherever its gradient is wanted (dbeta is written as 0
  * where beta == 0); alpha must lie in (0, 1] (its logarithm is taken). */
 int mxk_gdelta_bf16_bwd(const void* q, const void* k, const void* v, const float* alpha, const float* beta,
-                        const void* d_o, const void* chunk_states, const uint8_t* done, const float* ds_last,
+                        const void* d_o, const void* chunk_states, const void* workspace, const uint8_t* done,
+                        const float* ds_last,
                         void* dq, void* dk, void* dv, float* dalpha, float* dbeta, float* ds0, int* status,
                         int B, int T, int H, int d, mxk_stream_t stream);
 

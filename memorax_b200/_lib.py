@@ -26,6 +26,9 @@ SIGNATURES = {
     "mxk_linrec_bwd_workspace_bytes": (_z, [_i, _i, _i, _i, _i]),
     "mxk_linrec_f32_bwd": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _i, _i, _i, _p]),
     "mxk_linrec_c64_bwd": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _i, _i, _i, _i, _p]),
+    "mxk_linrec_grouped_bwd_workspace_bytes": (_z, [_i, _i, _i, _i]),
+    "mxk_linrec_f32_grouped_fwd": (_i, [_p] * 7 + [_i, _i, _i, _i, _p]),
+    "mxk_linrec_f32_grouped_bwd": (_i, [_p] * 10 + [_z, _i, _i, _i, _i, _p]),
     "mxk_linrec_noalloc_max_elements": (_z, []),
     "mxk_linrec_c64_bwd_noalloc": (_i, [_p] * 9 + [_i, _i, _i, _i, _p]),
     "mxk_loglinrec_f32_fwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
@@ -36,7 +39,7 @@ SIGNATURES = {
     "mxk_gdelta_chunk_states_bytes": (_z, [_i, _i, _i, _i]),
     "mxk_gdelta_workspace_bytes": (_z, [_i, _i, _i, _i]),
     "mxk_gdelta_bf16_fwd": (_i, [_p] * 11 + [_z, _p, _i, _i, _i, _i, _p]),
-    "mxk_gdelta_bf16_bwd": (_i, [_p] * 16 + [_i, _i, _i, _i, _p]),
+    "mxk_gdelta_bf16_bwd": (_i, [_p] * 17 + [_i, _i, _i, _i, _p]),
     "mxk_adam_bf16": (_i, [_p, _p, _p, _p, ctypes.c_longlong, _f, _f, _f, _f, _i, _f, _p]),
     "mxk_adam_bf16_master": (_i, [_p, _p, _p, _p, _p, ctypes.c_longlong, _f, _f, _f, _f, _i, _f, _p]),
 }

@@ -5,9 +5,10 @@
 // resident in tensor memory.  S_in and U of every chunk are the forward call's residual.
 // With the chunk quantities of gdelta_common.cuh (A = I + diag(beta) L, P =
 // tril(G o QK^T), R = V - diag(g) K S_in^T, U = A^-1 diag(beta) R):
-//   dU   = P^T dO + diag(gam) K dS^T            dUt = A^-T dU      (back substitution)
-//   dV   = diag(beta) dUt =: dR                  dbeta_t = (dUt_t . U_t) / beta_t
-//   dP   = tril(dO U^T)                          dL = -diag(beta) stril(dUt U^T)
+//   dU   = P^T dO + diag(gam) K dS^T            dR = T'^T dU  with T' = A^-1 diag(beta) from the preparation
+//                                                kernel (gdelta_prep.cu): a product, no back substitution
+//   dV   = dR                                    dbeta_t = (dR_t . U_t) / beta_t^2
+//   dP   = tril(dO U^T)                          dL = -stril(dR U^T)
 //   dQ   = (dP o G) K + diag(g) dO S_in
 //   dK   = (dP o G)^T Q + (dL o G) K + (dL o G)^T K + diag(gam) U dS - diag(g) dR S_in
 //   dS_in = g_last dS + (diag(g) dO)^T Q - (diag(g) dR)^T K
@@ -16,7 +17,8 @@
 //          dcum_t = rowsum_t(E) - colsum_t(E) + dg_t g_t - dgam_t gam_t (+ sum_j dgam_j gam_j at t = last),
 //          dlog(alpha_i) = sum_{t >= i} dcum_t,  dalpha_i = done_i ? 0 : dlog(alpha_i) / alpha_i.
 // Matrices with d_v on their rows are kept transposed ([v][t]) so that thread v
-// owns one value column, as in the forward kernel.
+// owns one value column, as in the forward kernel; dQ and dK are accumulated transposed too
+// ([feature][token], M = 128 products: the full tensor datapath instead of half of it).
 #include "gdelta_common.cuh"
 #include "tma.cuh"
 
@@ -34,6 +36,7 @@ struct BwdParams {
   const float* beta;
   const __nv_bfloat16* d_o;
   const uint4* chunk_states;
+  const uint4* tprime;                // T' of every chunk (the forward call's workspace)
   const uint8_t* done;
   const float* ds_last;
   __nv_bfloat16* dq;
@@ -61,20 +64,19 @@ struct BwdSmem {
   uint4 k[kPanD * kC];      // K                  SW tiles (two 64-column blocks)
   uint4 q[kPanD * kC];      // Q                  SW tiles
   uint4 d_o[kPanD * kC];    // dO, later g dO     SW tiles
-  uint4 r1[kC * 16];        // V [t][v]   -> dUt^T            [t/8][v][8]
+  uint4 r1[kC * 16];        // dU^T -> dR^T                   [t/8][v][8]   -> dq staging (SW tiles)
   uint4 r2[kC * 16];        // -(g dR)^T                      [j/8][v][8]
   uint4 u[kPanC * kD];      // U^T                [j/8][v][8]
   uint4 ug[kPanC * kD];     // (gam U)^T
   uint4 p[kPanC * kC];      // tril(G o QK^T)     [j/8][t][8]
-  float l[kC * kLS];        // l[t][j] = -beta_t L_tj        -> E[t][j]   (row stride kLS)
-  float lt[kC * kC];        // lt[j][t] = -beta_t L_tj       -> dV tile -> (dP o G), (dL o G) panels
-  uint4 lb[4 * 32];         // bf16 copy of -beta L, rows i = 32..63 x columns t = 0..31, as [(i-32)/8][t][8]
+  float l[kC * kLS];        // T' [j/8][t][8] (first 8 KiB, by bulk copy) -> E[t][j] (row stride kLS)
+  float lt[kC * kC];        // dV tile -> (dP o G), (dL o G) panels -> dk staging (SW tiles)
   ChunkDecay cd;
   // per-warp partial sums of the decay cotangents, combined in a fixed order (no floating-point atomics:
   // the results are bit-reproducible)
   float dg_a[4][kC], dg_b[4][kC], dgam_p[4][kC];
   float rowsum[kC], colsum[kC], dcum[kC];
-  float dgl[4];
+  float dgl[8];
   uint64_t bar[3];
   uint64_t bar_load;
   uint32_t tmem;
@@ -93,8 +95,8 @@ namespace {
 #define MXK_TG(i) do { if (p.phase_cycles != nullptr && tid == 0 && (blockIdx.x % 37) == 0) { const long long now_ = clock64(); atomicAdd(&p.phase_cycles[i], (unsigned long long)(now_ - t_prev_)); t_prev_ = now_; } } while (0)
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kUpper = 16u << 16;
-constexpr uint32_t kColDS = 0, kColKK = 128, kColQK = 192, kColY = 256, kColOI = 320, kColX1 = 320, kColW = 320,
-                   kColX2 = 384, kColDP = 448, kColDQ = 128, kColDK = 256, kColDelta = 384;
+constexpr uint32_t kColDS = 0, kColKK = 128, kColQK = 192, kColY = 256, kColOI = 320, kColX1 = 320, kColDR = 320,
+                   kColW = 320, kColX2 = 384, kColDP = 448, kColDQ = 128, kColDK = 192, kColDelta = 384;
 
 // Sums N (32 or 64) per-thread values over the 32 lanes of a warp; on return lane l holds
 // the totals of indices (N / 32) l .. (N / 32) l + N / 32 - 1 in vals[0 .. N / 32 - 1].
@@ -119,7 +121,7 @@ __device__ __forceinline__ void warp_reduce(float* vals, int lane) {
 // loads and two bulk copies issued by ONE thread, completing on sm.bar_load.  The
 // kernel issues them one chunk ahead, right after the last MMAs of the previous chunk
 // have released the buffers, so that they overlap that chunk's last epilogue.
-constexpr uint32_t kChunkLoadBytes = (3 * kPanD * kC + kResidualVecs) * 16;
+constexpr uint32_t kChunkLoadBytes = (3 * kPanD * kC + kResidualVecs + kAinvVecs) * 16;
 __device__ __forceinline__ void issue_chunk_loads(BwdSmem& sm, const BwdParams& p, int b, int h, int c, int nchunks) {
   // earlier generic-proxy accesses to these buffers are ordered before the async-proxy writes
   fence_smem_to_async();
@@ -135,6 +137,8 @@ __device__ __forceinline__ void issue_chunk_loads(BwdSmem& sm, const BwdParams& 
   const uint4* src = p.chunk_states + (static_cast<size_t>(b * p.H + h) * nchunks + c) * kResidualVecs;
   tma::load_bulk(sm.s, src, kStateVecs * 16, &sm.bar_load);
   tma::load_bulk(sm.u, src + kStateVecs, kUVecs * 16, &sm.bar_load);
+  const uint4* tp_src = p.tprime + (static_cast<size_t>(b * p.H + h) * nchunks + c) * kAinvVecs;
+  tma::load_bulk(sm.l, tp_src, kAinvVecs * 16, &sm.bar_load);
   if (c > 0) {   // the chunk after it (walking right to left): into L2 now, so that its loads hit there
     const int tp = t0 - kC;
     tma::prefetch_plain_tile(&p.map_k, tp, h, b, 0);
@@ -146,6 +150,7 @@ __device__ __forceinline__ void issue_chunk_loads(BwdSmem& sm, const BwdParams& 
       tma::prefetch_plain_tile(&p.map_do, tp, h, b, 64);
     }
     tma::prefetch_bulk(src - kResidualVecs, kResidualVecs * 16);
+    tma::prefetch_bulk(tp_src - kAinvVecs, kAinvVecs * 16);
   }
 }
 
@@ -215,7 +220,6 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
     __syncthreads();
     chunk_decay_from_regs(sm.cd, ab_next, dm, tid);
     if (tid < kC) sm.rowsum[tid] = 0.f;   // two contributions per row: order-independent
-    if (tid < 4) sm.dgl[tid] = 0.f;
 
     MXK_TG(0);
     mbar_wait_flag(&sm.bar_load, it & 1, timed_out);
@@ -261,34 +265,21 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
     fence_after_sync();
     MXK_TG(2);
 
-    // ---- epilogue A1: -beta L (fp32, row-major) and tril(G o QK^T) (bf16); every thread owns
-    //      16 keys of its token row ----
+    // ---- epilogue A1: tril(G o QK^T) (bf16); every thread owns 16 keys of its token row ----
     {
       const int lo = row_first_key(dm, row);
-      const float cum_t = sm.cd.cum[row], beta_t = sm.cd.beta[row];
+      const float cum_t = sm.cd.cum[row];
       const int j0 = (upper ? 32 : 0) + wg * 16;
-      float kk[16], qk[16];
-      tmem_ld_row<16>(lane_base + kColKK + wg * 16, kk);
+      float qk[16];
       tmem_ld_row<16>(lane_base + kColQK + wg * 16, qk);
 #pragma unroll
       for (int jq = 0; jq < 2; ++jq) {
-        float pm[8], lv[8];
+        float pm[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int x = jq * 8 + e, j = j0 + x;
           const bool in = (j >= lo && j <= row);
-          const float gtj = in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
-          pm[e] = gtj * qk[x];
-          lv[e] = (j < row) ? -beta_t * gtj * kk[x] : 0.f;
-        }
-        float4* lrow = reinterpret_cast<float4*>(&sm.l[row * kLS + j0 + jq * 8]);
-        lrow[0] = make_float4(lv[0], lv[1], lv[2], lv[3]);
-        lrow[1] = make_float4(lv[4], lv[5], lv[6], lv[7]);
-        if (row >= 32 && !upper) {   // rows 32..63 x columns 0..31: operand of the blocked solve's MMA
-          __nv_bfloat16* lb = reinterpret_cast<__nv_bfloat16*>(sm.lb);
-#pragma unroll
-          for (int e = 0; e < 8; ++e)
-            lb[(((row - 32) >> 3) * 32 + j0 + jq * 8 + e) * 8 + ((row - 32) & 7)] = __float2bfloat16(lv[e]);
+          pm[e] = in ? __expf(cum_t - sm.cd.cum[j]) * qk[x] : 0.f;
         }
         sm.p[((j0 >> 3) + jq) * kC + row] = pack8_bf16(pm);
       }
@@ -322,86 +313,45 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
     fence_after_sync();
     MXK_TG(4);
 
-    // ---- epilogue B.  Warpgroup 0, thread v: dU column, back substitution, dV, second dg term.
-    //      Warpgroup 1 meanwhile: the dgam reduction and <dS, S_in>. ----
-    if (wg == 0) {
-      __align__(8) float r[kC];
-      float ga[kC];
-      tmem_ld_row<kC>(lane_base + kColX2, ga);   // (dS k_j)[v]
-      tmem_ld_row<kC>(lane_base + kColX1, r);
+    // ---- epilogue B1: dU^T = X1^T + gam o X2^T as the bf16 operand of the T' product, and the dgam
+    //      reduction dgam_j = sum_v u_j[v] (dS k_j)[v]; thread (v, wg) covers tokens 32 wg .. 32 wg + 31 ----
+    {
+      float x2[32], x1[32];
+      tmem_ld_row<32>(lane_base + kColX2 + wg * 32, x2);   // (dS k_j)[v]
+      tmem_ld_row<32>(lane_base + kColX1 + wg * 32, x1);
 #pragma unroll
-      for (int j = 0; j < kC; ++j) r[j] = fmaf(sm.cd.gam[j], ga[j], r[j]);   // dU[v][j]
-      MXK_TG(11);
-
-      // Blocked solve (r = dUt[v][.] afterwards): rows 63..32 in fp32 registers; their effect on entries
-      // 0..31 (the 32 x 32 off-diagonal block) on the tensor core from bf16 operands, fp32 accumulate;
-      // then rows 31..1.
-      backward_substitute_range<kLS, kC - 1, 33, 32>(reinterpret_cast<float2*>(r), sm.l);
-#pragma unroll
-      for (int tp = kPanC / 2; tp < kPanC; ++tp) sm.r1[tp * kD + vt] = pack8_bf16(r + tp * 8);
-      fence_smem_to_async();
-      fence_before_sync();
-      asm volatile("bar.sync 1, 128;" ::: "memory");   // warpgroup 0 only
-      if (warp == 0) {
-        const bool leader = elect_one();
-        fence_after_sync();
-        gemm<2>(tmem + kColX1, Operand{smem_u32(sm.r1) + (kPanC / 2) * kD * 16, kD, false},
-                Operand{smem_u32(sm.lb), 32, false}, idesc_bf16(kD, 32, false, false), false, leader);
-        if (leader) commit(&sm.bar[2]);
-      }
-      mbar_wait_flag(&sm.bar[2], it & 1, timed_out);
-      fence_after_sync();
-      {
-        float delta[32];
-        tmem_ld_row<32>(lane_base + kColX1, delta);
-#pragma unroll
-        for (int e = 0; e < 32; ++e) r[e] += delta[e];
-      }
-      backward_substitute_range<kLS, 31, 1, 0>(reinterpret_cast<float2*>(r), sm.l);
-      MXK_TG(12);
-
-      // dR = beta dUt: the dV tile (row-major [t][v], staged in `lt`), -(g dR)^T panels,
-      // dUt^T panels, and dg_t -= dr_t . (S_in k_t)
-      tmem_ld_row<kC>(lane_base + kColY, ga);
-      __nv_bfloat16* dvt = reinterpret_cast<__nv_bfloat16*>(sm.lt);
-#pragma unroll
-      for (int tp = 0; tp < kPanC; ++tp) {
-        float ng[8];
+      for (int tp = 0; tp < 4; ++tp) {
+        float du[8], uf[8];
+        unpack8_bf16(sm.u[(wg * 4 + tp) * kD + vt], uf);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int t = tp * 8 + e;
-          const float dr = sm.cd.beta[t] * r[t];
-          dvt[t * kD + vt] = __float2bfloat16(dr);
-          ng[e] = -sm.cd.g[t] * dr;
-          ga[t] *= -dr;
+          du[e] = fmaf(sm.cd.gam[wg * 32 + t], x2[t], x1[t]);
+          x2[t] *= uf[e];
         }
-        sm.r1[tp * kD + vt] = pack8_bf16(r + tp * 8);
-        sm.r2[tp * kD + vt] = pack8_bf16(ng);
+        sm.r1[(wg * 4 + tp) * kD + vt] = pack8_bf16(du);
       }
-      MXK_TG(13);
-      warp_reduce<64>(ga, lane);
-      sm.dg_b[qw][2 * lane] = ga[0];
-      sm.dg_b[qw][2 * lane + 1] = ga[1];
-      MXK_TG(14);
-    } else {
-      // dgam_j = sum_v u_j[v] (dS k_j)[v]
-      float ga[kC];
-      tmem_ld_row<kC>(lane_base + kColX2, ga);
-#pragma unroll
-      for (int jp = 0; jp < kPanC; ++jp) {
-        float uf[8];
-        unpack8_bf16(sm.u[jp * kD + vt], uf);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) ga[jp * 8 + e] *= uf[e];
-      }
-      warp_reduce<64>(ga, lane);
-      sm.dgam_p[qw][2 * lane] = ga[0];
-      sm.dgam_p[qw][2 * lane + 1] = ga[1];
-
-      // <dS, S_in> for the g_last gradient
+      warp_reduce<32>(x2, lane);
+      sm.dgam_p[qw][wg * 32 + lane] = x2[0];
+    }
+    fence_smem_to_async();
+    fence_before_sync();
+    __syncthreads();
+    MXK_TG(11);
+    // ---- MMA B2: dR^T = dU^T T'  (128 x 64, contraction over the 64 tokens of dU) ----
+    if (warp == 0) {
+      const bool leader = elect_one();
+      fence_after_sync();
+      gemm<kC / 16>(tmem + kColDR, Operand{smem_u32(sm.r1), kD, false}, Operand{smem_u32(sm.l), kC, true},
+                    idesc_bf16(kD, kC, false, true), false, leader);
+      if (leader) commit(&sm.bar[2]);
+    }
+    // meanwhile: <dS, S_in> for the g_last gradient; thread (v, wg) covers state columns 64 wg .. 64 wg + 63
+    {
       float dot = 0.f;
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
+      for (int q2 = 0; q2 < 2; ++q2) {
+        const int q4 = wg * 2 + q2;
         float d32[32];
         tmem_ld_row<32>(lane_base + kColDS + q4 * 32, d32);
 #pragma unroll
@@ -414,7 +364,36 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
       }
 #pragma unroll
       for (int off = 16; off >= 1; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-      if (lane == 0) sm.dgl[qw] = dot;
+      if (lane == 0) sm.dgl[warp] = dot;
+    }
+    mbar_wait_flag(&sm.bar[2], it & 1, timed_out);
+    fence_after_sync();
+    MXK_TG(12);
+
+    // ---- epilogue B2: dR = dV: the dV tile (row-major [t][v], staged in `lt`), -(g dR)^T and dR^T
+    //      panels, and dg_t -= dr_t . (S_in k_t) ----
+    {
+      float dr[32], y[32];
+      tmem_ld_row<32>(lane_base + kColDR + wg * 32, dr);
+      tmem_ld_row<32>(lane_base + kColY + wg * 32, y);
+      __nv_bfloat16* dvt = reinterpret_cast<__nv_bfloat16*>(sm.lt);
+#pragma unroll
+      for (int tp = 0; tp < 4; ++tp) {
+        float ng[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int t = tp * 8 + e;
+          dvt[(wg * 32 + t) * kD + vt] = __float2bfloat16(dr[t]);
+          ng[e] = -sm.cd.g[wg * 32 + t] * dr[t];
+          y[t] *= -dr[t];
+        }
+        sm.r1[(wg * 4 + tp) * kD + vt] = pack8_bf16(dr + tp * 8);
+        sm.r2[(wg * 4 + tp) * kD + vt] = pack8_bf16(ng);
+      }
+      MXK_TG(13);
+      warp_reduce<32>(y, lane);
+      sm.dg_b[qw][wg * 32 + lane] = y[0];
+      MXK_TG(14);
     }
     fence_smem_to_async();
     fence_before_sync();
@@ -425,7 +404,7 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
     }
 
     MXK_TG(5);
-    // ---- MMA C: W = dUt U^T (64 x 64) ----
+    // ---- MMA C: W' = dR U^T (64 x 64) ----
     if (warp == 0) {
       const bool leader = elect_one();
       fence_after_sync();
@@ -463,8 +442,8 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
           const int x = jq * 8 + e, j = j0 + x;
           const bool in = (j >= lo && j <= row);
           const float gtj = in ? __expf(cum_t - sm.cd.cum[j]) : 0.f;
-          const float dl = (j < row) ? -beta_t * w[x] : 0.f;
-          wtt = (j == row) ? w[x] : wtt;   // the diagonal of W, held by exactly one thread per row
+          const float dl = (j < row) ? -w[x] : 0.f;
+          wtt = (j == row) ? w[x] : wtt;   // the diagonal of W', held by exactly one thread per row
           a8[e] = dp[x] * gtj;
           b8[e] = dl * gtj;
           ev[e] = (dp[x] * qk[x] + dl * kk[x]) * gtj;
@@ -478,10 +457,10 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
         dlg[pn * kC + row] = pack8_bf16(b8);
       }
       MXK_TG(17);
-      // dbeta_t = (dUt_t . U_t) / beta_t, once, outside the unrolled loop (a store inside it made every
+      // dbeta_t = (dR_t . U_t) / beta_t^2, once, outside the unrolled loop (a store inside it made every
       // iteration a divergent branch for the warps that hold the diagonal)
       if (row >= j0 && row < j0 + 16 && row < valid)
-        p.dbeta[(static_cast<size_t>(b) * p.T + t0 + row) * p.H + h] = beta_t != 0.f ? wtt / beta_t : 0.f;
+        p.dbeta[(static_cast<size_t>(b) * p.T + t0 + row) * p.H + h] = beta_t != 0.f ? wtt / (beta_t * beta_t) : 0.f;
       rs += __shfl_xor_sync(0xffffffffu, rs, 16);
       if (!upper) atomicAdd(&sm.rowsum[row], rs);
       const float gt = sm.cd.g[row];
@@ -500,28 +479,29 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
     __syncthreads();
 
     MXK_TG(7);
-    // ---- MMAs D: dQ, dK (64 x 128), dS_in increment (128 x 128) ----
+    // ---- MMAs D: dQ^T, dK^T (128 x 64 each: features on the rows), dS_in increment (128 x 128) ----
     if (warp == 0) {
       const bool leader = elect_one();
       fence_after_sync();
       const uint4* dpg_p = reinterpret_cast<const uint4*>(sm.lt);
       const uint32_t dpg = smem_u32(dpg_p), dlg = smem_u32(dpg_p + kPanC * kC);
       constexpr uint32_t kBlk = kSwBlockVecs * 16;
-      const Operand bk = sw_operand(smem_u32(sm.k), true, kBlk), bq = sw_operand(smem_u32(sm.q), true, kBlk);
-      const Operand ado_k = sw_operand(smem_u32(sm.d_o), false, kBlk), ado_t = sw_operand(smem_u32(sm.d_o), true, kBlk);
-      const Operand bs{smem_u32(sm.s), kD, true}, bds{smem_u32(sm.ds), kD, true};
-      const uint32_t id_km = idesc_bf16(kC, kD, false, true), id_mm = idesc_bf16(kC, kD, true, true);
-      // dQ = (dP o G) K + (g dO) S_in
-      gemm<kC / 16>(tmem + kColDQ, Operand{dpg, kC, false}, bk, id_km, false, leader);
-      gemm128(tmem + kColDQ, ado_k, bs, id_km, true, leader);
-      // dK = (dP o G)^T Q + (dL o G) K + (dL o G)^T K + (gam U) dS - (g dR) S_in
-      gemm<kC / 16>(tmem + kColDK, Operand{dpg, kC, true}, bq, id_mm, false, leader);
-      gemm<kC / 16>(tmem + kColDK, Operand{dlg, kC, false}, bk, id_km, true, leader);
-      gemm<kC / 16>(tmem + kColDK, Operand{dlg, kC, true}, bk, id_mm, true, leader);
-      gemm<kD / 16>(tmem + kColDK, Operand{smem_u32(sm.ug), kD, true}, bds, id_mm, true, leader);
-      gemm<kD / 16>(tmem + kColDK, Operand{smem_u32(sm.r2), kD, true}, bs, id_mm, true, leader);
+      const Operand kt = sw_operand(smem_u32(sm.k), true, kBlk), qt = sw_operand(smem_u32(sm.q), true, kBlk);   // K^T, Q^T
+      const Operand bk = kt, bq = qt;
+      const Operand gdo_k = sw_operand(smem_u32(sm.d_o), false, kBlk), gdo_t = sw_operand(smem_u32(sm.d_o), true, kBlk);
+      const Operand st{smem_u32(sm.s), kD, true}, dst{smem_u32(sm.ds), kD, true};                               // S_in^T, dS^T
+      const uint32_t id_mk = idesc_bf16(kD, kC, true, false), id_mm64 = idesc_bf16(kD, kC, true, true);
+      // dQ^T = K^T (dP o G)^T + S_in^T (g dO)^T
+      gemm<kC / 16>(tmem + kColDQ, kt, Operand{dpg, kC, false}, id_mk, false, leader);
+      gemm128(tmem + kColDQ, st, gdo_k, id_mk, true, leader);
+      // dK^T = Q^T (dP o G) + K^T (dL o G)^T + K^T (dL o G) + dS^T (gam U)^T - S_in^T (g dR)^T
+      gemm<kC / 16>(tmem + kColDK, qt, Operand{dpg, kC, true}, id_mm64, false, leader);
+      gemm<kC / 16>(tmem + kColDK, kt, Operand{dlg, kC, false}, id_mk, true, leader);
+      gemm<kC / 16>(tmem + kColDK, kt, Operand{dlg, kC, true}, id_mm64, true, leader);
+      gemm<kD / 16>(tmem + kColDK, dst, Operand{smem_u32(sm.ug), kD, true}, id_mm64, true, leader);
+      gemm<kD / 16>(tmem + kColDK, st, Operand{smem_u32(sm.r2), kD, true}, id_mm64, true, leader);
       // dS_in - g_last dS = (g dO)^T Q - (g dR)^T K
-      gemm<kC / 16>(tmem + kColDelta, ado_t, bq, idesc_bf16(kD, kD, true, true), false, leader);
+      gemm<kC / 16>(tmem + kColDelta, gdo_t, bq, idesc_bf16(kD, kD, true, true), false, leader);
       gemm<kC / 16>(tmem + kColDelta, Operand{smem_u32(sm.r2), kD, false}, bk, idesc_bf16(kD, kD, false, true), true, leader);
       if (leader) commit(&sm.bar[1]);
     }
@@ -542,7 +522,7 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
       float extra = sm.colsum[2 * tid] + sm.colsum[2 * tid + 1];
 #pragma unroll
       for (int off = 16; off >= 1; off >>= 1) extra += __shfl_xor_sync(0xffffffffu, extra, off);
-      extra += (sm.dgl[0] + sm.dgl[1] + sm.dgl[2] + sm.dgl[3]) * sm.cd.g[kC - 1];
+      extra += (((sm.dgl[0] + sm.dgl[1]) + (sm.dgl[2] + sm.dgl[3])) + ((sm.dgl[4] + sm.dgl[5]) + (sm.dgl[6] + sm.dgl[7]))) * sm.cd.g[kC - 1];
       float d0 = sm.dcum[2 * tid], d1 = sm.dcum[2 * tid + 1];
       if (tid == 31) d1 += extra;
       // suffix sums over the chunk
@@ -570,21 +550,23 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
       flags_next = linattn::load_done_flags(drow, t0 - kC, p.T, lane);
     }
 
-    // ---- epilogue D: dq rows (warpgroup 0), dk rows (warpgroup 1); dS = g_last dS + increment,
-    //      64 state columns per warpgroup ----
+    // ---- epilogue D: dq, dk tiles from the transposed accumulators (thread (feature, wg) covers tokens
+    //      32 wg .. 32 wg + 31); dS = g_last dS + increment, 64 state columns per warpgroup ----
     {
       // staged as SW tiles in buffers the finished MMAs no longer need (dq in `r1`, dk in `lt`),
       // stored by TMA after the barrier that ends the chunk
-      uint4* stage = wg == 0 ? sm.r1 : reinterpret_cast<uint4*>(sm.lt);
-      const uint32_t col = wg == 0 ? kColDQ : kColDK;
+      uint4* dq_stage = sm.r1;
+      uint4* dk_stage = reinterpret_cast<uint4*>(sm.lt);
+      {
+        float acc[32];
+        tmem_ld_row<32>(lane_base + kColDQ + wg * 32, acc);
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        float acc[kC];
-        tmem_ld_row<kC>(lane_base + col + half * kC, acc);
-        if (!upper) {
+        for (int e = 0; e < 32; ++e)
+          reinterpret_cast<__nv_bfloat16*>(&dq_stage[sw_slot(wg * 32 + e, vt >> 3)])[vt & 7] = __float2bfloat16(acc[e]);
+        tmem_ld_row<32>(lane_base + kColDK + wg * 32, acc);
 #pragma unroll
-          for (int pn = 0; pn < kPanC; ++pn) stage[sw_slot(row, half * kPanC + pn)] = pack8_bf16(acc + pn * 8);
-        }
+        for (int e = 0; e < 32; ++e)
+          reinterpret_cast<__nv_bfloat16*>(&dk_stage[sw_slot(wg * 32 + e, vt >> 3)])[vt & 7] = __float2bfloat16(acc[e]);
       }
       const float g_last = sm.cd.g[kC - 1];
       float* out0 = (c == 0 && p.ds0 && vt < p.d) ? p.ds0 + (static_cast<size_t>(bh) * p.d + vt) * p.d : nullptr;
@@ -652,16 +634,17 @@ extern "C" int mxk_debug_gd_phase_cycles(unsigned long long* out, int reset) {
 extern "C" {
 
 int mxk_gdelta_bf16_bwd(const void* q, const void* k, const void* v, const float* alpha, const float* beta,
-                        const void* d_o, const void* chunk_states, const uint8_t* done, const float* ds_last,
+                        const void* d_o, const void* chunk_states, const void* workspace, const uint8_t* done,
+                        const float* ds_last,
                         void* dq, void* dk, void* dv, float* dalpha, float* dbeta, float* ds0, int* status,
                         int B, int T, int H, int d, mxk_stream_t stream) {
   using namespace mxk;
   using namespace mxk::gdelta;
-  if (!q || !k || !v || !alpha || !beta || !d_o || !chunk_states || !dq || !dk || !dv || !dalpha || !dbeta)
+  if (!q || !k || !v || !alpha || !beta || !d_o || !chunk_states || !workspace || !dq || !dk || !dv || !dalpha || !dbeta)
     return MXK_ERR_NULL;
   if (B <= 0 || T <= 0 || H <= 0 || static_cast<long long>(B) * H > 0x7fffffffLL) return MXK_ERR_DIMS;
   if (d != kD && d != 64) return MXK_ERR_UNSUPPORTED;
-  for (const void* ptr : {q, k, v, d_o, chunk_states, (const void*)dq, (const void*)dk, (const void*)dv,
+  for (const void* ptr : {q, k, v, d_o, chunk_states, workspace, (const void*)dq, (const void*)dk, (const void*)dv,
                           (const void*)ds_last, (const void*)ds0})
     if (ptr && !aligned16(ptr)) return MXK_ERR_ALIGN;
   BwdParams prm;
@@ -672,6 +655,7 @@ int mxk_gdelta_bf16_bwd(const void* q, const void* k, const void* v, const float
   prm.beta = beta;
   prm.d_o = static_cast<const __nv_bfloat16*>(d_o);
   prm.chunk_states = static_cast<const uint4*>(chunk_states);
+  prm.tprime = static_cast<const uint4*>(workspace);
   prm.done = done;
   prm.ds_last = ds_last;
   prm.dq = static_cast<__nv_bfloat16*>(dq);

@@ -71,6 +71,13 @@ class MemoroidCellBase(nn.Module):
         """-> (next_carry, y)"""
         raise NotImplementedError
 
+    def scan_states(self, z, initial_carry, done):
+        """The time scan without the read-out, -> (h, next_carry) as ``Memoroid.scan_fn``
+        (memoroid.py:60-91).  Cells whose read-out over every state is fused into the kernel
+        (linear attention, delta rule: the per-step states are O(T d^2) and never exist) do not
+        offer it."""
+        raise NotImplementedError(f"{type(self).__name__} never materialises its per-step states; use scan()")
+
 
 class Memoroid(SequenceModel):
     def __init__(self, cell: MemoroidCellBase):
@@ -86,6 +93,14 @@ class Memoroid(SequenceModel):
 
     def initialize_carry(self, key, input_shape):
         return self.cell.initialize_carry(key, input_shape)
+
+    def scan_fn(self, z, initial_carry, done):
+        """``Memoroid.scan_fn(z, initial_carry, done) -> (h, next_carry)`` (memoroid.py:60-91): every
+        prefix of ``[carry, z_1 .. z_T]`` under the cell's operator with the reset rule, and the last one.
+        ``h`` is the cell's ``(state, decay)`` pair with the decay leaf ``None``: of that leaf only the
+        last step is ever read (memoroid.py:89; every ``read`` ignores it), so the kernels return it in
+        ``next_carry`` and never write the (B, T, ...) tensor."""
+        return self.cell.scan_states(z, initial_carry, done)
 
     def propagate_sensitivities(self, decay, jacobians, sensitivity, done):
         """RTRL sensitivities after T steps (``Memoroid._propagate_sensitivities``,
@@ -150,12 +165,15 @@ class LRUCell(MemoroidCellBase):
         return (torch.zeros(*batch, 1, self.hidden_dim, dtype=torch.complex64),
                 torch.ones(*batch, 1, self.hidden_dim, dtype=torch.complex64))
 
-    def scan(self, z, initial_carry, done, inputs):
+    def scan_states(self, z, initial_carry, done):
         state, lam = z
         h0, a0 = _squeeze_carry(initial_carry, 2)
         h, a_last = ops.LinRec.apply(lam, state.contiguous(), h0, a0, done)
-        y = self.read((h, None), inputs)
-        return (h[:, -1:], a_last[:, None]), y
+        return (h, None), (h[:, -1:], a_last[:, None])
+
+    def scan(self, z, initial_carry, done, inputs):
+        h, next_carry = self.scan_states(z, initial_carry, done)
+        return next_carry, self.read(h, inputs)
 
 
 # ------------------------------------------------------------------- MinGRU
@@ -187,6 +205,12 @@ class MinGRUCell(MemoroidCellBase):
     def initialize_carry(self, key, input_shape):
         *batch, _ = input_shape
         return (torch.full((*batch, 1, self.features), -float("inf")), torch.zeros(*batch, 1, self.features))
+
+    def scan_states(self, z, initial_carry, done):
+        log_state, decay = z
+        x0, a0 = _squeeze_carry(initial_carry, 2)
+        x, _, a_last = ops.LogLinRec.apply(log_state.contiguous(), decay.contiguous(), x0, a0, done)
+        return (x, None), (x[:, -1:], a_last[:, None])
 
     def scan(self, z, initial_carry, done, inputs):
         log_state, decay = z
@@ -348,11 +372,15 @@ class S5Cell(MemoroidCellBase):
         return (torch.zeros(*batch, 1, self.state_size, dtype=torch.complex64),
                 torch.ones(*batch, 1, self.state_size, dtype=torch.complex64))
 
-    def scan(self, z, initial_carry, done, inputs):
+    def scan_states(self, z, initial_carry, done):
         state, lambda_bar = z
         h0, a0 = _squeeze_carry(initial_carry, 2)
         h, a_last = ops.LinRec.apply(lambda_bar, state.contiguous(), h0, a0, done)
-        return (h[:, -1:], a_last[:, None]), self.read((h, None), inputs)
+        return (h, None), (h[:, -1:], a_last[:, None])
+
+    def scan(self, z, initial_carry, done, inputs):
+        h, next_carry = self.scan_states(z, initial_carry, done)
+        return next_carry, self.read(h, inputs)
 
 
 # -------------------------------------------------------------------- Mamba
@@ -363,7 +391,9 @@ class MambaCell(MemoroidCellBase):
     ``(decay_j h_i + h_j, decay_j decay_i)`` (:119-122), ``y = C . h + D x`` gated by
     ``silu(z)`` after an RMSNorm (:124-135) -- and, like the reference, the scan runs over the
     materialised (B, T, H, N, P) elements: here as ONE real linear-recurrence launch over
-    H*N*P channels (forward and backward through ``ops.LinRec``) instead of ~2 log2(T) passes."""
+    H*N*P channels instead of ~2 log2(T) passes.  When a head's N*P state elements are a multiple of
+    128 (the default 16 x 16 is) the kernels read the per-head decay (B,T,H) directly and reduce its
+    gradient per head (``ops.LinRecGrouped``); otherwise the decay is expanded (``ops.LinRec``)."""
 
     def __init__(self, features, num_heads=8, head_dim=16, state_dim=16, conv_dim=4, in_features=None):
         super().__init__()
@@ -429,6 +459,16 @@ class MambaCell(MemoroidCellBase):
         ``initialize_carry`` -> (h (B,T,H,N,P), next_carry)."""
         bsz, steps, heads, sdim, hdim = h_elems.shape
         width = heads * sdim * hdim
+        if ops.grouped_decay_supported(width, heads):
+            # one decay per head, read as such by the kernel: the (B,T,H) tensor is never expanded
+            h0 = a0 = None
+            if initial_carry is not None:
+                h0 = initial_carry[0].reshape(bsz, width).contiguous()
+                a0 = initial_carry[1].reshape(bsz, heads).contiguous()
+            h, a_last = ops.LinRecGrouped.apply(decay.reshape(bsz, steps, heads).contiguous(),
+                                                h_elems.reshape(bsz, steps, width).contiguous(), h0, a0, done)
+            h = h.reshape(bsz, steps, heads, sdim, hdim)
+            return h, (h[:, -1:], a_last.reshape(bsz, 1, heads, 1, 1))
         a = decay.expand(bsz, steps, heads, sdim, hdim).reshape(bsz, steps, width).contiguous()
         h0 = a0 = None
         if initial_carry is not None:
@@ -437,6 +477,11 @@ class MambaCell(MemoroidCellBase):
         h, a_last = ops.LinRec.apply(a, h_elems.reshape(bsz, steps, width).contiguous(), h0, a0, done)
         h = h.reshape(bsz, steps, heads, sdim, hdim)
         return h, (h[:, -1:], a_last.reshape(bsz, 1, heads, sdim, hdim)[..., :1, :1])
+
+    def scan_states(self, z, initial_carry, done):
+        h_elems, decay = z[0], z[1]
+        h, next_carry = self.scan_elements(h_elems, decay, initial_carry, done)
+        return (h, None), next_carry
 
     def scan(self, z, initial_carry, done, inputs):
         h_elems, decay, projected = z

@@ -118,6 +118,61 @@ class LinRec(torch.autograd.Function):
         return ga, (gb if need_b else None), gh0, None, None
 
 
+# ------------------------------------------- real recurrence, decay per group
+def grouped_decay_supported(dim, groups):
+    """Whether the grouped-decay kernels take this shape (each group a multiple of 128 channels)."""
+    return groups > 0 and dim % groups == 0 and (dim // groups) % 128 == 0
+
+
+def linrec_grouped_fwd(a, b, h0=None, a0=None, done=None, want_decay=True):
+    """h_t[c] = done_t ? b_t[c] : a_t[c // group] h_{t-1}[c] + b_t[c]; ``a`` is (B,T,G), ``b`` (B,T,D) with
+    D = G * group.  Returns ``(h, a_last)`` with the carry's decay leaf ``a_last`` (B,G)."""
+    a, b = _dev(a, torch.float32, "a"), _dev(b, torch.float32, "b")
+    h0, a0 = _dev(h0, torch.float32, "h0"), _dev(a0, torch.float32, "a0")
+    bsz, steps, dim = b.shape
+    groups = a.shape[-1]
+    assert a.shape == (bsz, steps, groups)
+    h = torch.empty_like(b)
+    a_last = torch.empty(bsz, groups, dtype=torch.float32, device=b.device) if want_decay else None
+    _lib.call("mxk_linrec_f32_grouped_fwd", _ptr(a), _ptr(b), _ptr(h0), _ptr(a0), _ptr(_done_bytes(done)), _ptr(h),
+              _ptr(a_last), bsz, steps, dim, groups, _stream())
+    return h, a_last
+
+
+def linrec_grouped_bwd(a, h, h0, done, gh, gh_last=None, need_ga=True, need_gh0=True):
+    """Cotangents ``(gb, ga, gh0)`` of :func:`linrec_grouped_fwd`; ``ga`` is (B,T,G)."""
+    a, h, gh = _dev(a, torch.float32, "a"), _dev(h, torch.float32, "h"), _dev(gh, torch.float32, "gh")
+    h0, gh_last = _dev(h0, torch.float32, "h0"), _dev(gh_last, torch.float32, "gh_last")
+    bsz, steps, dim = h.shape
+    groups = a.shape[-1]
+    gb = torch.empty_like(h)
+    ga = torch.empty_like(a) if need_ga else None
+    gh0 = torch.empty(bsz, dim, dtype=torch.float32, device=h.device) if need_gh0 else None
+    ws_bytes = _lib.lib.mxk_linrec_grouped_bwd_workspace_bytes(bsz, steps, dim, groups) if need_ga else 0
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=h.device) if ws_bytes else None
+    _lib.call("mxk_linrec_f32_grouped_bwd", _ptr(a), _ptr(h), _ptr(h0), _ptr(_done_bytes(done)), _ptr(gh),
+              _ptr(gh_last), _ptr(gb), _ptr(ga), _ptr(gh0), _ptr(ws), ws_bytes, bsz, steps, dim, groups, _stream())
+    return gb, ga, gh0
+
+
+class LinRecGrouped(torch.autograd.Function):
+    """(a (B,T,G), b (B,T,D), h0, a0 (B,G), done) -> (h, a_last (B,G)); ``a_last`` carries no gradient."""
+
+    @staticmethod
+    def forward(ctx, a, b, h0, a0, done):
+        h, a_last = linrec_grouped_fwd(a, b, h0, a0, done, want_decay=True)
+        ctx.save_for_backward(a, h, h0, done)
+        ctx.mark_non_differentiable(a_last)
+        return h, a_last
+
+    @staticmethod
+    def backward(ctx, gh, _ga_last):
+        a, h, h0, done = ctx.saved_tensors
+        gb, ga, gh0 = linrec_grouped_bwd(a, h, h0, done, gh.contiguous(), None, need_ga=ctx.needs_input_grad[0],
+                                         need_gh0=ctx.needs_input_grad[2] and h0 is not None)
+        return ga, (gb if ctx.needs_input_grad[1] else None), gh0, None, None
+
+
 # --------------------------------------------------------- log-space (MinGRU)
 def loglinrec_fwd(ls, d, x0=None, a0=None, done=None, want_y=True, want_decay=True):
     ls, d = _dev(ls, torch.float32, "ls"), _dev(d, torch.float32, "d")
@@ -306,7 +361,7 @@ def gdelta_bwd(q, k, v, alpha, beta, d_o, chunk_states, done=None, ds_last=None,
     ds0 = torch.empty(bsz, heads, dim, dim, dtype=torch.float32, device=q.device)
     status = _status_word(q.device)
     _lib.call("mxk_gdelta_bf16_bwd", _ptr(q), _ptr(k), _ptr(v), _ptr(alpha), _ptr(beta), _ptr(d_o),
-              _ptr(chunk_states), _ptr(_done_bytes(done)), _ptr(ds_last), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dalpha),
+              _ptr(chunk_states), _ptr(workspace), _ptr(_done_bytes(done)), _ptr(ds_last), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dalpha),
               _ptr(dbeta), _ptr(ds0), _ptr(status), bsz, steps, heads, dim, _stream())
     if check:
         _check_status(status, "mxk_gdelta_bf16_bwd")

@@ -42,7 +42,7 @@ def test_status_strings_and_validation_without_a_gpu(lib):
     assert L.mxk_loglinrec_f32_fwd(None, None, None, None, None, None, None, None, 1, 1, 1, None) == -1
     assert L.mxk_linattn_bf16_fwd(*([None] * 11), 1, 1, 1, 64, 1e-6, 1, None) == -1
     assert L.mxk_gdelta_bf16_fwd(*([None] * 11), 0, None, 1, 1, 1, 128, None) == -1
-    assert L.mxk_gdelta_bf16_bwd(*([None] * 16), 1, 1, 1, 128, None) == -1
+    assert L.mxk_gdelta_bf16_bwd(*([None] * 17), 1, 1, 1, 128, None) == -1
     import ctypes
     buf = (ctypes.c_char * 256)()
     p = ctypes.addressof(buf) & ~15

@@ -205,3 +205,46 @@ def test_golden_vectors_through_cuda(golden):
     h, _ = ops.linrec_fwd(f32(a), f32(g["rt_jac"].reshape(bsz, steps, -1)), f32(g["rt_sens"].reshape(bsz, -1)), None,
                           torch.from_numpy(g["rt_done"]).cuda(), want_decay=False)
     close(h[:, -1], torch.from_numpy(g["rt_next"].reshape(bsz, -1)), what="rtrl")
+
+
+@pytest.mark.parametrize("shape,groups", [((3, 9, 256), 2), ((2, 37, 1024), 4), ((4, 130, 2048), 8), ((2, 5, 128), 1)])
+def test_linrec_grouped_decay_fwd_bwd(shape, groups):
+    """One decay per group of channels (MambaCell's per-head decay, mamba.py:109-122) against the oracle run on
+    the expanded decay: states, the carry's decay leaf per group, and the cotangents with the decay gradient
+    reduced over each group."""
+    from memorax_b200 import ops
+    bsz, steps, dim = shape
+    per = dim // groups
+    gen = torch.Generator().manual_seed(dim + steps)
+    a = torch.rand(bsz, steps, groups, generator=gen, dtype=torch.float64) * 0.6 + 0.4
+    b, h0 = rnd(gen, bsz, steps, dim), rnd(gen, bsz, dim)
+    a0 = torch.rand(bsz, groups, generator=gen, dtype=torch.float64)
+    gh, gh_last = rnd(gen, bsz, steps, dim), rnd(gen, bsz, dim)
+    done = make_done(gen, bsz, steps, 0.08)
+    ar, br, h0r = a.clone().requires_grad_(), b.clone().requires_grad_(), h0.clone().requires_grad_()
+    h_ref, acc_ref = mo.linrec_seq(ar.repeat_interleave(per, dim=-1), br, h0r, done.double(), a0.repeat_interleave(per, dim=-1))
+    ((h_ref * gh).sum() + (h_ref[:, -1] * gh_last).sum()).backward()
+    cu = lambda t: t.float().cuda()
+    assert ops.grouped_decay_supported(dim, groups)
+    h, a_last = ops.linrec_grouped_fwd(cu(a), cu(b), cu(h0), cu(a0), done.cuda())
+    close(h, h_ref, what="h")
+    close(a_last, acc_ref[:, ::per], what="a_last")
+    gb, ga, gh0 = ops.linrec_grouped_bwd(cu(a), h, cu(h0), done.cuda(), cu(gh), cu(gh_last))
+    close(gb, br.grad, what="gb")
+    close(ga, ar.grad, rel=1e-4, what="ga")     # a sum over `per` channels
+    close(gh0, h0r.grad, what="gh0")
+    # default carry and the autograd Function
+    leaves = [cu(a).requires_grad_(), cu(b).requires_grad_()]
+    h2, _ = ops.LinRecGrouped.apply(leaves[0], leaves[1], None, None, done.cuda())
+    h_ref2, _ = mo.linrec_seq(ar.detach().repeat_interleave(per, dim=-1), b, torch.zeros(bsz, dim, dtype=torch.float64), done.double())
+    close(h2, h_ref2, what="h default carry")
+    (h2 * cu(gh)).sum().backward()
+    assert leaves[0].grad.shape == (bsz, steps, groups)
+
+
+def test_linrec_grouped_rejects_narrow_groups():
+    from memorax_b200 import _lib
+    x = torch.zeros(64 * 96, device="cuda")
+    p = x.data_ptr()
+    assert _lib.lib.mxk_linrec_f32_grouped_fwd(p, p, None, None, None, p, None, 1, 1, 96, 2, None) == -4
+    assert _lib.lib.mxk_linrec_f32_grouped_fwd(p, p, None, None, None, p, None, 1, 1, 100, 3, None) == -2

@@ -161,3 +161,34 @@ def test_mamba_model_gradients_match_the_oracle():
         ref = p.grad.detach().double().cpu()
         err = float((got[name] - ref).abs().max())
         assert err <= 2e-4 * max(1.0, float(ref.abs().max())), (name, err)
+
+
+def test_scan_fn_mirror_replays_the_reference_vectors(golden):
+    """``Memoroid.scan_fn(z, initial_carry, done) -> (h, next_carry)`` (memoroid.py:60-91) on the elements
+    the reference's own LRU and MinGRU cells produced: states at every step and the next carry, decay leaf
+    included (returned for the last step only)."""
+    import numpy as np
+    from memorax_b200.memoroid import LRUCell, Memoroid, MinGRUCell, LinearAttentionCell
+    g = golden
+    c64 = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(torch.complex64).cuda()
+    f32 = lambda a: torch.from_numpy(np.ascontiguousarray(a)).float().cuda()
+    done = torch.from_numpy(g["lru_done"]).cuda()
+    model = Memoroid(LRUCell(features=5, hidden_dim=4).cuda())
+    z = (c64(g["lru_z_state"]), c64(g["lru_z_decay"][0, 0]))        # lru.py:86 broadcasts one lambda
+    (h, decay_leaf), (n_state, n_decay) = model.scan_fn(z, (c64(g["lru_c_state"]), c64(g["lru_c_decay"])), done)
+    assert decay_leaf is None
+    ref = torch.from_numpy(g["lru_h_state"])
+    assert float((h.cpu() - ref).abs().max()) <= 1e-5 * float(ref.abs().max())
+    assert n_state.shape == g["lru_n_state"].shape and n_decay.shape == g["lru_n_decay"].shape
+    assert float((n_state.cpu() - torch.from_numpy(g["lru_n_state"])).abs().max()) <= 1e-5 * float(ref.abs().max())
+    assert float((n_decay.cpu() - torch.from_numpy(g["lru_n_decay"])).abs().max()) <= 1e-5
+
+    gru = Memoroid(MinGRUCell(features=6).cuda())
+    (x, _), (nx, nd) = gru.scan_fn((f32(g["gru_z_state"]), f32(g["gru_z_decay"])),
+                                   (f32(g["gru_c1_state"]), f32(g["gru_c1_decay"])), torch.from_numpy(g["gru_done"]).cuda())
+    assert float((x.cpu() - torch.from_numpy(g["gru_h1_state"])).abs().max()) <= 1e-5 * float(np.abs(g["gru_h1_state"]).max())
+    assert float((nx.cpu() - torch.from_numpy(g["gru_n1_state"])).abs().max()) <= 1e-5 * float(np.abs(g["gru_n1_state"]).max())
+    assert float((nd.cpu() - torch.from_numpy(g["gru_n1_decay"])).abs().max()) <= 1e-5 * max(1.0, float(np.abs(g["gru_n1_decay"]).max()))
+
+    with pytest.raises(NotImplementedError):
+        Memoroid(LinearAttentionCell(features=64, head_dim=64, num_heads=1)).scan_fn(None, None, None)
