@@ -431,7 +431,64 @@ class MambaN2:
         return h
 
 
-WORKLOADS = {"c2": LinAttnC2, "c3": GDeltaC3, "c4": LruC4, "c1": LinRecC1, "c5": TrainC5, "n2": MambaN2}
+class MlstmN1:
+    """mLSTM scan + read-out fwd+bwd (mlstm.py:163-240) at the linear-attention configuration's size: B=256,
+    H=4, T=256, head dim 64, fp32; log_i ~ N(0, 0.1^2) (the cell's gate bias init), log_f = -softplus(-N(4.5, 1))
+    (forget-gate bias linspace(3, 6)), q, k, v ~ N(0,1) with k / sqrt(64); done ~ Bernoulli(0.01)."""
+    name = "n1_mlstm_fwd_bwd"
+    dtype = "f32"
+    B, H, T, D = 256, 4, 256, 64
+    p_done = 0.01
+    seed = 1234 + 7
+    dominant = "mlstm_bwd_kernel"
+    launches_per_step = 2
+    dominant_traffic_bytes = None
+    cpu_sample_batch = 4
+
+    def __init__(self, batch=None):
+        self.B = batch or self.B
+
+    def tokens(self):
+        return self.B * self.T
+
+    def host_inputs(self, seed_offset=0, device="cpu"):
+        g = torch.Generator(device=device).manual_seed(self.seed + seed_offset)
+        shp = (self.B, self.T, self.H, self.D)
+        rn = lambda *s: torch.randn(*s, generator=g, device=device)
+        return dict(q=rn(*shp), k=rn(*shp) / math.sqrt(self.D), v=rn(*shp), dh=rn(*shp), log_i=rn(*shp[:3]) * 0.1,
+                    log_f=-torch.nn.functional.softplus(-(rn(*shp[:3]) + 4.5)),
+                    done=(torch.rand(self.B, self.T, generator=g, device=device) < self.p_done).to(torch.uint8))
+
+    def algorithmic_bytes(self):
+        th = self.B * self.T * self.H
+        # q,k,v in, h out (+ gates) | q,k,v,dh in, dq,dk,dv out (+ gates in, their gradients out), fp32
+        return {"mlstm_fwd_kernel": th * (4 * 4 * self.D + 8), "mlstm_bwd_kernel": th * (7 * 4 * self.D + 16)}
+
+    def algorithmic_flops(self):
+        th = self.B * self.T * self.H
+        # per step: update + read of a d x d memory forward (4 d^2), twice that plus the two cotangent copies backward
+        return {"mlstm_fwd_kernel": th * 4 * self.D * self.D, "mlstm_bwd_kernel": th * 14 * self.D * self.D}
+
+    def step(self, x, ops, mark=None):
+        h, c_t, n_t, m_t, _ = ops.mlstm_fwd(x["q"], x["k"], x["v"], x["log_i"], x["log_f"], None, None, None, None, x["done"])
+        if mark:
+            mark[0].record()
+        outs = ops.mlstm_bwd(x["q"], x["k"], x["v"], x["log_i"], x["log_f"], None, None, None, x["done"], x["dh"])
+        if mark:
+            mark[1].record()
+        return (h, c_t) + tuple(outs[:5])
+
+    def cpu_step(self, x):
+        from oracle import memoroid_oracle as mo
+        q, k, v, li, lf = (x[n].clone().requires_grad_() for n in ("q", "k", "v", "log_i", "log_f"))
+        b = q.shape[0]
+        h, _ = mo.mlstm_seq(q, k, v, li, lf, torch.zeros(b, self.H, self.D, self.D), torch.zeros(b, self.H, self.D),
+                            torch.full((b, self.H), -1e9), x["done"].float())
+        (h * x["dh"]).sum().backward()
+        return h
+
+
+WORKLOADS = {"n1": MlstmN1, "c2": LinAttnC2, "c3": GDeltaC3, "c4": LruC4, "c1": LinRecC1, "c5": TrainC5, "n2": MambaN2}
 
 
 # ------------------------------------------------------------ clock sampling

@@ -217,6 +217,38 @@ int mxk_linattn_bf16_bwd(const void* q, const void* k, const void* v, const void
                          int feature_map, mxk_stream_t stream);
 
 /* ---------------------------------------------------------------------------
+ * mLSTM, the matrix-memory LSTM (mlstm.py:163-240 under Memoroid.scan_fn): per head,
+ * with the running-max stabiliser m of the reference's operator (mlstm.py:205-229),
+ *   m_t = max(m_{t-1} + log_f_t, log_i_t)
+ *   C_t = exp(m_{t-1} + log_f_t - m_t) C_{t-1} + exp(log_i_t - m_t) k_t v_t^T   (n_t likewise with k_t)
+ *   h_t = q_t^T C_t / (max(|q_t . n_t|, exp(-m_t)) + eps)                         (mlstm.py:214-218)
+ * and done_t discards (C, n, m) of the past.  The reference materialises every C_t; here the
+ * d x d memory lives in registers and only the carry touches memory.
+ *
+ *   q, k, v   (B,T,H,d) fp32, d = 32, 64 or 128; k as the cell's element holds it (already divided
+ *             by sqrt(d), mlstm.py:196)
+ *   log_i, log_f  (B,T,H) fp32: the input-gate pre-activation and -softplus(-f) (mlstm.py:185-186)
+ *   c0 (B,H,d,d) indexed [key][value], n0 (B,H,d), m0 (B,H), f0 (B,H): the carry (C, n, m, log_f leaf);
+ *             NULL = initialize_carry's zeros / m = -1e9 (mlstm.py:231-240)
+ *   h         (B,T,H,d) out: the read-out before the head-wise norm
+ *   c_last, n_last, m_last, f_last  next carry, each optional
+ * Backward: cotangents dh of h and (dc_last, dn_last, dm_last) of the next carry (NULL = zeros; the
+ * log_f leaf has none, no read-out uses it) -> dq, dk, dv, dlog_i, dlog_f and optionally dc0, dn0,
+ * dm0.  No per-step state is stored: the kernel walks forward once more, then backward.
+ * `workspace`: mxk_mlstm_bwd_workspace_bytes(...) bytes of scratch (six scalars per token and head).
+ * ------------------------------------------------------------------------- */
+size_t mxk_mlstm_bwd_workspace_bytes(int B, int T, int H, int d);
+int mxk_mlstm_f32_fwd(const float* q, const float* k, const float* v, const float* log_i, const float* log_f,
+                      const float* c0, const float* n0, const float* m0, const float* f0, const uint8_t* done,
+                      float* h, float* c_last, float* n_last, float* m_last, float* f_last, int B, int T, int H, int d,
+                      float eps, mxk_stream_t stream);
+int mxk_mlstm_f32_bwd(const float* q, const float* k, const float* v, const float* log_i, const float* log_f,
+                      const float* c0, const float* n0, const float* m0, const uint8_t* done, const float* dh,
+                      const float* dc_last, const float* dn_last, const float* dm_last, float* dq, float* dk, float* dv,
+                      float* dlog_i, float* dlog_f, float* dc0, float* dn0, float* dm0, void* workspace,
+                      size_t workspace_bytes, int B, int T, int H, int d, float eps, mxk_stream_t stream);
+
+/* ---------------------------------------------------------------------------
  * Gated delta rule (DeltaNet with a scalar forget gate).  The reference has no
  * such cell; this is the new MemoroidCellBase-shaped mixer, defined per head
  * (S is d_v x d_k, a_t = done_t ? 0 : alpha_t) by

@@ -36,6 +36,9 @@ SIGNATURES = {
     "mxk_linattn_chunk_states_bytes": (_z, [_i, _i, _i, _i]),
     "mxk_linattn_bf16_fwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p]),
     "mxk_linattn_bf16_bwd": (_i, [_p] * 14 + [_i, _i, _i, _i, _f, _i, _p]),
+    "mxk_mlstm_bwd_workspace_bytes": (_z, [_i, _i, _i, _i]),
+    "mxk_mlstm_f32_fwd": (_i, [_p] * 15 + [_i, _i, _i, _i, _f, _p]),
+    "mxk_mlstm_f32_bwd": (_i, [_p] * 22 + [_z, _i, _i, _i, _i, _f, _p]),
     "mxk_gdelta_chunk_states_bytes": (_z, [_i, _i, _i, _i]),
     "mxk_gdelta_workspace_bytes": (_z, [_i, _i, _i, _i]),
     "mxk_gdelta_bf16_fwd": (_i, [_p] * 11 + [_z, _p, _i, _i, _i, _i, _p]),

@@ -319,6 +319,95 @@ class DeltaNetCell(MemoroidCellBase):
         return (s_last[:, None],), self.output_projection(self.norm(o))
 
 
+# -------------------------------------------------------------------- mLSTM
+class mLSTMCell(MemoroidCellBase):
+    """Matrix-memory LSTM (mlstm.py:31-240): gated linear attention with a per-head scalar forget gate and
+    the running-max stabiliser.  Projections as the reference (up-projection, causal depthwise convolution +
+    SiLU, block-diagonal q / k / v, Dense gates on [q, k, v], head-wise LayerNorm with residual scale,
+    learnable skip, SiLU(z) gate, output projection); the element ``(k (x) v, log_f, k, m = log_i)`` of
+    mlstm.py:198-203 stays factored as ``(k, v, log_i, log_f)`` -- the (B,T,H,d,d) outer products and the
+    per-step memories never exist -- and scan + read-out are one kernel.  ``head_dim`` = hidden_dim /
+    num_heads must be 32, 64 or 128."""
+
+    def __init__(self, features, hidden_dim, num_heads=4, conv_kernel_size=4, in_features=None, eps=1e-6):
+        super().__init__()
+        if hidden_dim % num_heads:
+            raise ValueError(f"hidden_dim ({hidden_dim}) must be divisible by num_heads ({num_heads}).")
+        self.features, self.hidden_dim, self.num_heads, self.eps = features, hidden_dim, num_heads, eps
+        self.head_dim = hidden_dim // num_heads
+        fin = in_features or features
+        self.up_projection = nn.Linear(fin, 2 * hidden_dim, bias=False)
+        self.causal_conv = nn.Conv1d(hidden_dim, hidden_dim, conv_kernel_size, groups=hidden_dim,
+                                     padding=conv_kernel_size - 1)
+        block = lambda: nn.Parameter(torch.randn(num_heads, self.head_dim, self.head_dim) / math.sqrt(self.head_dim))
+        self.query, self.key, self.value = block(), block(), block()     # BlockDiagonalDense kernels [h][out][in]
+        self.i_gate = nn.Linear(3 * hidden_dim, num_heads)
+        self.f_gate = nn.Linear(3 * hidden_dim, num_heads)
+        with torch.no_grad():      # mlstm.py:110-125: zero kernels, bias N(0, 0.1) / linspace(3, 6)
+            self.i_gate.weight.zero_(); self.f_gate.weight.zero_()
+            self.i_gate.bias.normal_(std=0.1)
+            self.f_gate.bias.copy_(torch.linspace(3.0, 6.0, num_heads))
+        self.learnable_skip = nn.Parameter(torch.ones(hidden_dim))
+        self.norm_weight = nn.Parameter(torch.zeros(num_heads, self.head_dim))   # MultiHeadLayerNorm: scale = 1 + weight
+        self.output_projection = nn.Linear(hidden_dim, features, bias=False)
+
+    def _block(self, x, kernel):
+        bsz, steps, _ = x.shape
+        return torch.einsum("bthd,hod->btho", x.view(bsz, steps, self.num_heads, self.head_dim), kernel)
+
+    def _project(self, x):
+        steps = x.shape[1]
+        x_mlstm, z = self.up_projection(x).chunk(2, dim=-1)
+        u = torch.nn.functional.silu(self.causal_conv(x_mlstm.transpose(1, 2))[..., :steps].transpose(1, 2))
+        return self._block(u, self.query), self._block(u, self.key), self._block(x_mlstm, self.value), z, u
+
+    def forward(self, x, **kwargs):
+        """-> factored elements (k / sqrt(d), v, log_i, log_f) plus what the read-out needs."""
+        q, k, v, z, u = self._project(x)
+        gate_in = torch.cat([q, k, v], dim=-1).reshape(*x.shape[:2], -1)
+        log_i = self.i_gate(gate_in)
+        log_f = -torch.nn.functional.softplus(-self.f_gate(gate_in))
+        return k / math.sqrt(self.head_dim), v, log_i, log_f, (q, z, u)
+
+    def binary_operator(self, a, b):
+        c_a, f_a, n_a, m_a = a
+        c_b, f_b, n_b, m_b = b
+        m_dec = m_a + f_b
+        m_new = torch.maximum(m_dec, m_b)
+        s_a, s_b = torch.exp(m_dec - m_new), torch.exp(m_b - m_new)
+        return s_a * c_a + s_b * c_b, f_a + f_b, s_a * n_a + s_b * n_b, m_new
+
+    def read(self, h, x, **kwargs):
+        raise RuntimeError("the read-out over every C_t is fused into scan()")
+
+    def finish(self, h_tilde, z, u):
+        """Everything of ``read`` after the memory read-out (mlstm.py:220-229)."""
+        bsz, steps = h_tilde.shape[:2]
+        y = torch.nn.functional.layer_norm(h_tilde, (self.head_dim,), eps=1e-5) * (1.0 + self.norm_weight)
+        y = y.reshape(bsz, steps, self.hidden_dim) + self.learnable_skip * u
+        return self.output_projection(y * torch.nn.functional.silu(z))
+
+    def initialize_carry(self, key, input_shape):
+        *batch, _ = input_shape
+        hd = self.head_dim
+        return (torch.zeros(*batch, 1, self.num_heads, hd, hd), torch.zeros(*batch, 1, self.num_heads, 1, 1),
+                torch.zeros(*batch, 1, self.num_heads, hd, 1), torch.full((*batch, 1, self.num_heads, 1, 1), -1e9))
+
+    def scan(self, z, initial_carry, done, inputs):
+        k, v, log_i, log_f, (q, zgate, u) = z
+        c0 = f0 = n0 = m0 = None
+        if initial_carry is not None:
+            c0, f0, n0, m0 = initial_carry
+            c0, f0 = c0[:, 0].contiguous(), f0[:, 0, :, 0, 0].contiguous()
+            n0, m0 = n0[:, 0, :, :, 0].contiguous(), m0[:, 0, :, 0, 0].contiguous()
+        h, c_last, n_last, m_last, f_last = ops.MLSTM.apply(q.float().contiguous(), k.float().contiguous(),
+                                                            v.float().contiguous(), log_i.float().contiguous(),
+                                                            log_f.float().contiguous(), c0, n0, m0, f0, done, self.eps)
+        next_carry = (c_last[:, None], f_last[:, None, :, None, None], n_last[:, None, :, :, None],
+                      m_last[:, None, :, None, None])
+        return next_carry, self.finish(h.to(inputs.dtype), zgate, u)
+
+
 # ----------------------------------------------------------------------- S5
 class S5Cell(MemoroidCellBase):
     """Diagonal state-space cell (s5.py:18-149): the same (state, decay) operator

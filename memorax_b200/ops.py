@@ -322,6 +322,69 @@ class LinAttn(torch.autograd.Function):
                 dz0 if ctx.has_state[1] else None, None, None, None)
 
 
+# -------------------------------------------------------------------- mLSTM
+def mlstm_fwd(q, k, v, log_i, log_f, c0=None, n0=None, m0=None, f0=None, done=None, eps=1e-6):
+    """Stabilised mLSTM scan + read-out; q, k, v (B,T,H,d) fp32 (k already divided by sqrt(d)), gates (B,T,H).
+    Returns ``(h, c_last, n_last, m_last, f_last)``."""
+    q, k, v = (_dev(t, torch.float32, n) for t, n in ((q, "q"), (k, "k"), (v, "v")))
+    log_i, log_f = _dev(log_i, torch.float32, "log_i"), _dev(log_f, torch.float32, "log_f")
+    c0, n0, m0, f0 = (_dev(t, torch.float32, n) for t, n in ((c0, "c0"), (n0, "n0"), (m0, "m0"), (f0, "f0")))
+    bsz, steps, heads, dim = q.shape
+    assert log_i.shape == (bsz, steps, heads) and log_f.shape == log_i.shape
+    h = torch.empty_like(q)
+    c_last = torch.empty(bsz, heads, dim, dim, dtype=torch.float32, device=q.device)
+    n_last = torch.empty(bsz, heads, dim, dtype=torch.float32, device=q.device)
+    m_last = torch.empty(bsz, heads, dtype=torch.float32, device=q.device)
+    f_last = torch.empty(bsz, heads, dtype=torch.float32, device=q.device)
+    _lib.call("mxk_mlstm_f32_fwd", _ptr(q), _ptr(k), _ptr(v), _ptr(log_i), _ptr(log_f), _ptr(c0), _ptr(n0), _ptr(m0),
+              _ptr(f0), _ptr(_done_bytes(done)), _ptr(h), _ptr(c_last), _ptr(n_last), _ptr(m_last), _ptr(f_last),
+              bsz, steps, heads, dim, float(eps), _stream())
+    return h, c_last, n_last, m_last, f_last
+
+
+def mlstm_bwd(q, k, v, log_i, log_f, c0, n0, m0, done, dh, dc_last=None, dn_last=None, dm_last=None, eps=1e-6):
+    """Cotangents ``(dq, dk, dv, dlog_i, dlog_f, dc0, dn0, dm0)`` of :func:`mlstm_fwd`."""
+    q, k, v, dh = (_dev(t, torch.float32, n) for t, n in ((q, "q"), (k, "k"), (v, "v"), (dh, "dh")))
+    log_i, log_f = _dev(log_i, torch.float32, "log_i"), _dev(log_f, torch.float32, "log_f")
+    c0, n0, m0 = (_dev(t, torch.float32, n) for t, n in ((c0, "c0"), (n0, "n0"), (m0, "m0")))
+    dc_last, dn_last, dm_last = (_dev(t, torch.float32, n) for t, n in ((dc_last, "dc_last"), (dn_last, "dn_last"),
+                                                                         (dm_last, "dm_last")))
+    bsz, steps, heads, dim = q.shape
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    dli, dlf = torch.empty_like(log_i), torch.empty_like(log_f)
+    dc0 = torch.empty(bsz, heads, dim, dim, dtype=torch.float32, device=q.device)
+    dn0 = torch.empty(bsz, heads, dim, dtype=torch.float32, device=q.device)
+    dm0 = torch.empty(bsz, heads, dtype=torch.float32, device=q.device)
+    ws_bytes = _lib.lib.mxk_mlstm_bwd_workspace_bytes(bsz, steps, heads, dim)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    _lib.call("mxk_mlstm_f32_bwd", _ptr(q), _ptr(k), _ptr(v), _ptr(log_i), _ptr(log_f), _ptr(c0), _ptr(n0), _ptr(m0),
+              _ptr(_done_bytes(done)), _ptr(dh), _ptr(dc_last), _ptr(dn_last), _ptr(dm_last), _ptr(dq), _ptr(dk),
+              _ptr(dv), _ptr(dli), _ptr(dlf), _ptr(dc0), _ptr(dn0), _ptr(dm0), _ptr(ws), ws_bytes, bsz, steps, heads, dim,
+              float(eps), _stream())
+    return dq, dk, dv, dli, dlf, dc0, dn0, dm0
+
+
+class MLSTM(torch.autograd.Function):
+    """(q, k, v, log_i, log_f, c0, n0, m0, f0, done) -> (h, c_last, n_last, m_last, f_last); the log_f leaf of
+    the carry (f0 / f_last) is returned for state parity and carries no gradient."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, log_i, log_f, c0, n0, m0, f0, done, eps):
+        h, c_last, n_last, m_last, f_last = mlstm_fwd(q, k, v, log_i, log_f, c0, n0, m0, f0, done, eps)
+        ctx.save_for_backward(q, k, v, log_i, log_f, c0, n0, m0, done)
+        ctx.eps = eps
+        ctx.mark_non_differentiable(f_last)
+        return h, c_last, n_last, m_last, f_last
+
+    @staticmethod
+    def backward(ctx, dh, dc_last, dn_last, dm_last, _df_last):
+        q, k, v, log_i, log_f, c0, n0, m0, done = ctx.saved_tensors
+        dq, dk, dv, dli, dlf, dc0, dn0, dm0 = mlstm_bwd(q, k, v, log_i, log_f, c0, n0, m0, done, dh.contiguous(),
+                                                        dc_last, dn_last, dm_last, ctx.eps)
+        return (dq, dk, dv, dli, dlf, dc0 if c0 is not None else None, dn0 if n0 is not None else None,
+                dm0 if m0 is not None else None, None, None, None)
+
+
 # --------------------------------------------------------- gated delta rule
 def gdelta_fwd(q, k, v, alpha, beta, s0=None, done=None, save_states=False, check=False):
     """Gated delta rule; q, k, v (B,T,H,d) bf16 with d = 128 or 64, alpha/beta (B,T,H) fp32.

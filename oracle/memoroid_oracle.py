@@ -6,8 +6,8 @@ Two layers, both plain CPU code:
   inclusive prefix over ``[carry, z_1 .. z_T]`` under a reset-aware wrapper of a
   cell's binary operator (memorax/networks/sequence_models/memoroid.py:60-91),
   with the per-cell operators of lru.py:92-95, s5.py:133-136,
-  min_gru.py:67-74, linear_attention.py:82-86 and the multiplicative-reset
-  linear form of memoroid.py:119-123.  NumPy, any bracketing.
+  min_gru.py:67-74, linear_attention.py:82-86, mlstm.py:205-229 and the
+  multiplicative-reset linear form of memoroid.py:119-123.  NumPy, any bracketing.
 * ``*_seq`` functions: the closed-form sequential recurrences those scans
   equal, written in torch so that fp64 autograd gives the gradient oracle.
   ``tests/test_oracle.py`` proves layer 2 == layer 1, and
@@ -143,6 +143,18 @@ def op_gated_delta(lhs, rhs):
     return (m_i @ m_j, u_i @ m_j + u_j)
 
 
+def op_mlstm(lhs, rhs):
+    """mLSTM's operator over (C, log_f, n, m) with the running-max stabiliser (mlstm.py:205-229): the
+    left element is decayed by the right one's forget gate, both are rescaled to the larger log
+    magnitude, and the stabilised memories add."""
+    c_a, f_a, n_a, m_a = lhs
+    c_b, f_b, n_b, m_b = rhs
+    m_dec = m_a + f_b
+    m_new = np.maximum(m_dec, m_b)
+    s_a, s_b = np.exp(m_dec - m_new), np.exp(m_b - m_new)
+    return (s_a * c_a + s_b * c_b, f_a + f_b, s_a * n_a + s_b * n_b, m_new)
+
+
 def elu_plus_one(x):
     """Feature map of linear_attention.py:58-60 (works on numpy and torch)."""
     if isinstance(x, torch.Tensor):
@@ -235,6 +247,35 @@ def gdelta_seq(q, k, v, alpha, beta, s0, done):
         s = s + (bt * (v[:, t] - sk))[..., None] * k[:, t, :, None, :]
         out.append(torch.einsum("bhvk,bhk->bhv", s, q[:, t]))
     return torch.stack(out, dim=1), s
+
+
+def mlstm_seq(q, k, v, log_i, log_f, c0, n0, m0, done, f0=None, eps=1e-6):
+    """Stabilised mLSTM (mlstm.py:163-229 under the reset rule of ``Memoroid.scan_fn``), sequentially:
+      m_t = max(m_{t-1} + log_f_t, log_i_t)
+      C_t = exp(m_{t-1} + log_f_t - m_t) C_{t-1} + exp(log_i_t - m_t) k_t v_t^T      (n_t likewise with k_t)
+      h_t = q_t^T C_t / (max(|q_t . n_t|, exp(-m_t)) + eps)
+    and done_t discards (C, n, m) of the past (the element alone remains: m_t = log_i_t, C_t = k_t v_t^T).
+    ``k`` is the key as the cell's element holds it (already divided by sqrt(head_dim), mlstm.py:196).
+
+    q, k, v (B,T,H,d); log_i, log_f (B,T,H); c0 (B,H,d,d) indexed [key, value]; n0 (B,H,d); m0, f0 (B,H).
+    Returns h (B,T,H,d) and the next carry (C_T, F_T, n_T, m_T) with F the summed log forget gates
+    since the last reset (the carry's log_f leaf)."""
+    c, n, m = c0, n0, m0
+    f = torch.zeros_like(m0) if f0 is None else f0
+    neg_inf = torch.full_like(m0, -float("inf"))
+    out = []
+    for t in range(q.shape[1]):
+        keep = (1.0 - done[:, t]).reshape(-1, 1) > 0
+        m_dec = torch.where(keep, m, neg_inf) + log_f[:, t]
+        m_new = torch.maximum(m_dec, log_i[:, t])
+        s_a, s_b = torch.exp(m_dec - m_new), torch.exp(log_i[:, t] - m_new)
+        c = s_a[..., None, None] * c + s_b[..., None, None] * k[:, t, :, :, None] * v[:, t, :, None, :]
+        n = s_a[..., None] * n + s_b[..., None] * k[:, t]
+        f = torch.where(keep, f + log_f[:, t], log_f[:, t])
+        m = m_new
+        den = torch.maximum((q[:, t] * n).sum(-1).abs(), torch.exp(-m)) + eps
+        out.append(torch.einsum("bhj,bhjk->bhk", q[:, t], c) / den[..., None])
+    return torch.stack(out, dim=1), (c, f, n, m)
 
 
 def mamba_seq(hidden, b_proj, c_proj, dt, a_neg, d_skip, h0, done, a0=None):

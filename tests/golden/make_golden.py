@@ -14,7 +14,7 @@ operators, reset rule, carry layout, read-outs -- not XLA's rounding.
 
 Files executed: memorax/utils/axes.py,
 memorax/networks/sequence_models/{sequence_model,memoroid,lru,min_gru,
-linear_attention,mamba}.py.
+linear_attention,mamba,mlstm}.py.
 
 Run (only where the reference checkout exists):
     python tests/golden/make_golden.py --reference /path/to/memorax
@@ -148,8 +148,11 @@ def install_stand_ins(reference_dir):
     rnd = types.ModuleType("jax.random")
     rnd.key = lambda seed: seed
 
+    jnn = types.ModuleType("jax.nn")
+    jnn.softplus = _softplus
+
     jax = types.ModuleType("jax")
-    jax.numpy, jax.lax, jax.tree, jax.random = jnp, lax, tree, rnd
+    jax.numpy, jax.lax, jax.tree, jax.random, jax.nn = jnp, lax, tree, rnd, jnn
     jax.vmap = _vmap
     jax.Array = np.ndarray
 
@@ -167,14 +170,22 @@ def install_stand_ins(reference_dir):
     inits.lecun_normal = lambda *a, **k: None
     inits.zeros_init = lambda *a, **k: None
     inits.ones = lambda *a, **k: None
+    inits.normal = lambda *a, **k: None
     nn.initializers = inits
+    nn.Conv = nn.Dropout = _Identity
     flax = types.ModuleType("flax")
     flax.linen = nn
     ftyping = types.ModuleType("flax.typing")
     ftyping.Dtype = ftyping.Initializer = object
 
-    mods = {"jax": jax, "jax.numpy": jnp, "jax.lax": lax, "jax.tree": tree, "jax.random": rnd,
+    mods = {"jax": jax, "jax.numpy": jnp, "jax.lax": lax, "jax.tree": tree, "jax.random": rnd, "jax.nn": jnn,
             "flax": flax, "flax.linen": nn, "flax.linen.initializers": inits, "flax.typing": ftyping}
+    # layers / initialisers that mlstm.py imports by name but only uses in setup(), which is bypassed
+    net_inits = types.ModuleType("memorax.networks.initializers")
+    net_inits.wang = lambda *a, **k: None
+    net_layers = types.ModuleType("memorax.networks.layers")
+    net_layers.BlockDiagonalDense = net_layers.MultiHeadLayerNorm = _Identity
+    mods["memorax.networks.initializers"], mods["memorax.networks.layers"] = net_inits, net_layers
 
     # Bare packages whose __path__ points into the checkout, so that the
     # reference's modules import each other without running the package
@@ -315,6 +326,48 @@ def main():
                mb_A_log=cell.A_log, mb_D=cell.D, mb_done=done, mb_c_state=carry[0], mb_c_decay=carry[1],
                mb_z_state=z[0], mb_z_decay=z[1], mb_h_state=h[0], mb_n_state=nxt[0], mb_n_decay=nxt[1],
                mb_y=y, mb_y_pre_gate=(y / gate).reshape(bsz, steps, heads, hdim))
+
+    # ---- mLSTM: the cell's own __call__ (elements with the stabiliser leaf), binary_operator, read and
+    #      initialize_carry under Memoroid.scan_fn; projections, gates' Dense layers, the head-wise norm and the
+    #      output projection are replaced by fixed arrays / identities, so y / silu(z) is the read-out h_tilde ----
+    mlstm = importlib.import_module(sm + "mlstm")
+    bsz, steps, heads, hd = 2, 10, 2, 4
+    cell = object.__new__(mlstm.mLSTMCell)          # no setup(): fields are set by hand below
+    cell.features, cell.hidden_dim, cell.num_heads = heads * hd, heads * hd, heads
+    proj = (rng.normal(size=(bsz, steps, heads, hd)), rng.normal(size=(bsz, steps, heads, hd)),
+            rng.normal(size=(bsz, steps, heads, hd)), rng.normal(size=(bsz, steps, heads * hd)),
+            np.zeros((bsz, steps, heads * hd)))
+    cell._project = lambda x: proj                  # (query, key, value, z, u) of mlstm.py:148-161
+    i_pre = rng.normal(size=(bsz, steps, heads)) * 1.5
+    f_pre = rng.normal(size=(bsz, steps, heads)) * 2.0 + 1.0
+    cell.i_gate = lambda g: i_pre
+    cell.f_gate = lambda g: f_pre
+    cell.norm = _Identity()
+    cell.learnable_skip = np.zeros(heads * hd)
+    cell.output_projection = _Identity()
+    cell.drop = lambda y, deterministic=True: y
+    cell.has_rng = lambda name: False
+    model = memoroid.Memoroid(cell=cell)
+    x = np.zeros((bsz, steps, 1))
+    done = done_patterns(rng, bsz, steps)
+    carry = (rng.normal(size=(bsz, 1, heads, hd, hd)) * 0.5, -np.abs(rng.normal(size=(bsz, 1, heads, 1, 1))),
+             rng.normal(size=(bsz, 1, heads, hd, 1)) * 0.5, rng.normal(size=(bsz, 1, heads, 1, 1)))
+    z = cell(x)
+    h, nxt = model.scan_fn(z, carry, done)
+    nxt2, y = model(x, done, carry)
+    assert all(np.array_equal(p, q) for p, q in zip(nxt, nxt2))
+    silu = proj[3] / (1.0 + np.exp(-proj[3]))
+    out.update(ml_q=proj[0], ml_k=proj[1], ml_v=proj[2], ml_i_pre=i_pre, ml_f_pre=f_pre, ml_done=done,
+               ml_c_C=carry[0], ml_c_logf=carry[1], ml_c_n=carry[2], ml_c_m=carry[3],
+               ml_z_C=z[0], ml_z_logf=z[1], ml_z_n=z[2], ml_z_m=z[3],
+               ml_h_C=h[0], ml_h_logf=h[1], ml_h_n=h[2], ml_h_m=h[3],
+               ml_n_C=nxt[0], ml_n_logf=nxt[1], ml_n_n=nxt[2], ml_n_m=nxt[3],
+               ml_h_tilde=(y / silu).reshape(bsz, steps, heads, hd))
+    # default carry (initialize_carry: zeros with m = -1e9)
+    carry0 = cell.initialize_carry(0, (bsz, heads * hd))
+    nxt0, y0 = model(x, done, None)
+    out.update(ml_default_c_m=carry0[3], ml_default_n_C=nxt0[0], ml_default_n_n=nxt0[2], ml_default_n_m=nxt0[3],
+               ml_default_h_tilde=(y0 / silu).reshape(bsz, steps, heads, hd))
 
     np.savez_compressed(args.out, **out)
     print("wrote", args.out, "with", len(out), "arrays")

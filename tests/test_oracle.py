@@ -193,3 +193,51 @@ def test_carry_split_invariance_and_reset_equivalence():
     # a reset at t=5 == an independent sequence starting at t=5 from a zero state
     h_tail, _ = mo.linrec_seq(a[:, 5:], b[:, 5:], torch.zeros_like(h0), torch.zeros(bsz, steps - 5, dtype=torch.float64))
     np.testing.assert_allclose(h[:, 5:].numpy(), h_tail.numpy(), rtol=1e-12, atol=1e-12)
+
+
+def _mlstm_inputs(g):
+    hd = g["ml_q"].shape[-1]
+    log_f = -np.logaddexp(-g["ml_f_pre"], 0.0)          # -softplus(-f), mlstm.py:185
+    return dict(q=T64(g["ml_q"]), k=T64(g["ml_k"] / np.sqrt(hd)), v=T64(g["ml_v"]), log_i=T64(g["ml_i_pre"]),
+                log_f=T64(log_f), done=T64(g["ml_done"]))
+
+
+def test_golden_mlstm(golden):
+    """The reference's own mlstm.py vectors: elements, every prefix state, the next carry and the read-out,
+    with a non-trivial carry and with initialize_carry's (m = -1e9)."""
+    g = golden
+    x = _mlstm_inputs(g)
+    # elements as the cell builds them (mlstm.py:188-203)
+    np.testing.assert_allclose(np.einsum("bthi,bthj->bthij", x["k"].numpy(), x["v"].numpy()), g["ml_z_C"], **TOL)
+    np.testing.assert_allclose(x["log_f"].numpy()[..., None, None], g["ml_z_logf"], **TOL)
+    np.testing.assert_allclose(x["log_i"].numpy()[..., None, None], g["ml_z_m"], **TOL)
+    carry = (T64(g["ml_c_C"][:, 0]), T64(g["ml_c_n"][:, 0, :, :, 0]), T64(g["ml_c_m"][:, 0, :, 0, 0]))
+    h, (c_t, f_t, n_t, m_t) = mo.mlstm_seq(x["q"], x["k"], x["v"], x["log_i"], x["log_f"], *carry, x["done"],
+                                           T64(g["ml_c_logf"][:, 0, :, 0, 0]))
+    np.testing.assert_allclose(h.numpy(), g["ml_h_tilde"], rtol=1e-9, atol=1e-9)
+    np.testing.assert_allclose(c_t.numpy(), g["ml_n_C"][:, 0], **TOL)
+    np.testing.assert_allclose(n_t.numpy(), g["ml_n_n"][:, 0, :, :, 0], **TOL)
+    np.testing.assert_allclose(m_t.numpy(), g["ml_n_m"][:, 0, :, 0, 0], **TOL)
+    np.testing.assert_allclose(f_t.numpy(), g["ml_n_logf"][:, 0, :, 0, 0], **TOL)
+    # default carry
+    bsz, _, heads, hd = g["ml_q"].shape
+    zeros = lambda *s: torch.zeros(*s, dtype=torch.float64)
+    assert np.all(g["ml_default_c_m"] == -1e9)             # initialize_carry, mlstm.py:238
+    h0, (c_t, _, n_t, m_t) = mo.mlstm_seq(x["q"], x["k"], x["v"], x["log_i"], x["log_f"], zeros(bsz, heads, hd, hd),
+                                          zeros(bsz, heads, hd), T64(g["ml_default_c_m"][:, 0, :, 0, 0]), x["done"])
+    np.testing.assert_allclose(h0.numpy(), g["ml_default_h_tilde"], rtol=1e-9, atol=1e-9)
+    np.testing.assert_allclose(c_t.numpy(), g["ml_default_n_C"][:, 0], **TOL)
+    np.testing.assert_allclose(m_t.numpy(), g["ml_default_n_m"][:, 0, :, 0, 0], **TOL)
+
+
+def test_mlstm_operator_scan_equals_sequential_form(golden):
+    """Layer 1 (prefix scan under the reset wrapper with mlstm.py's operator, any bracketing) against the
+    reference's per-step states and against layer 2."""
+    g = golden
+    z = (g["ml_z_C"], g["ml_z_logf"], g["ml_z_n"], g["ml_z_m"])
+    carry = (g["ml_c_C"], g["ml_c_logf"], g["ml_c_n"], g["ml_c_m"])
+    for bracketing in ("tree", "left"):
+        h, nxt = mo.memoroid_scan(mo.op_mlstm, z, carry, g["ml_done"], bracketing)
+        for got, name in zip(h, ("ml_h_C", "ml_h_logf", "ml_h_n", "ml_h_m")):
+            np.testing.assert_allclose(got, g[name], rtol=1e-9, atol=1e-9)
+        np.testing.assert_allclose(nxt[0], g["ml_n_C"], rtol=1e-9, atol=1e-9)
