@@ -180,6 +180,17 @@ int mxk_loglinrec_f32_bwd(const float* d, const float* x, const float* x0, const
                           const float* gx, const float* gy, const float* gx_last, float* gls,
                           float* gd, float* gx0, int B, int T, int D, mxk_stream_t stream);
 
+/* The same recurrence with MinGRU's gate math fused in (min_gru.py:52-61): the kernels take the two Dense
+ * layers' pre-activations z and h~ (B,T,D) and form the elements on the fly,
+ *   log_state = -softplus(-z) + log g(h~),  decay = -softplus(z),  g(h) = h >= 0 ? h + 0.5 : sigmoid(h),
+ * so the (B,T,D) log_state and decay tensors are never written or read back.  Backward returns the
+ * cotangents of z and h~ (gz, gh).  Other arguments as mxk_loglinrec_f32_fwd / _bwd. */
+int mxk_mingru_f32_fwd(const float* z, const float* h_tilde, const float* x0, const float* a0, const uint8_t* done,
+                       float* x, float* y, float* a_last, int B, int T, int D, mxk_stream_t stream);
+int mxk_mingru_f32_bwd(const float* z, const float* h_tilde, const float* x, const float* x0, const uint8_t* done,
+                       const float* gx, const float* gy, const float* gx_last, float* gz, float* gh, float* gx0,
+                       int B, int T, int D, mxk_stream_t stream);
+
 /* ---------------------------------------------------------------------------
  * Chunked causal linear attention with carried state (linear_attention.py:58-124
  * under Memoroid.scan_fn): per head, S_t = [!done_t] S_{t-1} + v_t phi(k_t)^T,

@@ -33,6 +33,8 @@ SIGNATURES = {
     "mxk_linrec_c64_bwd_noalloc": (_i, [_p] * 9 + [_i, _i, _i, _i, _p]),
     "mxk_loglinrec_f32_fwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
     "mxk_loglinrec_f32_bwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
+    "mxk_mingru_f32_fwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
+    "mxk_mingru_f32_bwd": (_i, [_p] * 11 + [_i, _i, _i, _p]),
     "mxk_linattn_chunk_states_bytes": (_z, [_i, _i, _i, _i]),
     "mxk_linattn_bf16_fwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p]),
     "mxk_linattn_bf16_bwd": (_i, [_p] * 14 + [_i, _i, _i, _i, _f, _i, _p]),

@@ -52,18 +52,15 @@ struct FwdSmem {
   uint4 k[kPanD * kC];        // K, after the first MMAs gam K  (SW tiles: two 64-column blocks)
   uint4 q[kPanD * kC];        // Q, after the first MMAs g Q    (SW tiles)
   uint4 v[kPanD * kC];        // V                              (SW tiles)
-  uint4 yu[kPanC * kD];       // -(g Y)^T, then U^T             [t/8][v][8]
-  // p and tp are contiguous: together they stage the bf16 output tile [t][v] once the last MMAs of the
-  // chunk have read them
+  uint4 yu[kPanC * kD];       // -(g Y)^T, then U^T [t/8][v][8], then the bf16 output tile [t][v] for the TMA store
   uint4 p[kPanC * kC];        // tril(G o QK^T)                 [j/8][t][8]
   uint4 tp[kAinvVecs];        // T'                             [j/8][t][8]
   FwdDecay cd;   // cd.gam doubles as the staging of log(alpha) while cum is being built
   uint64_t bar[3];
-  uint64_t bar_load, bar_tp;
+  uint64_t bar_load;
   uint32_t tmem;
 };
 static_assert(sizeof(FwdSmem) <= 113 * 1024, "two CTAs per SM");
-static_assert(offsetof(FwdSmem, tp) == offsetof(FwdSmem, p) + sizeof(uint4) * kPanC * kC, "output staging spans p and tp");
 
 // 256 TMEM columns per CTA (two CTAs per SM):
 //   columns   0..127  S (fp32, all 128 lanes = value rows)
@@ -103,7 +100,6 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
     mbar_init(&sm.bar[1], 1);
     mbar_init(&sm.bar[2], 1);
     mbar_init(&sm.bar_load, 1);
-    mbar_init(&sm.bar_tp, 1);
     mbar_init_fence();
   }
   if (warp == 0) tmem_alloc(&sm.tmem, kTmemCols);
@@ -140,12 +136,13 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
   constexpr uint32_t kBlk = kSwBlockVecs * 16;   // bytes between the two 64-column blocks of an SW tile pair
   bool timed_out = false;
 
-  // K, Q, V (SW tiles) of a chunk arrive by TMA, issued by one thread one chunk ahead: as soon as the last
-  // MMA group of the previous chunk has released the buffers, so that the copies overlap that chunk's
-  // output epilogue.  T' follows at the top of the next iteration (its buffer stages the output tile).
+  // K, Q, V (SW tiles) and T' of a chunk arrive by TMA / bulk copy, issued by one thread one chunk ahead: as
+  // soon as the last MMA group of the previous chunk has released the buffers, so that the copies overlap
+  // that chunk's output epilogue.
   auto issue_chunk_loads = [&](int cc) {
     fence_smem_to_async();   // earlier generic-proxy accesses to the buffers come first
-    tma::expect_bytes(&sm.bar_load, 3 * kPanD * kC * 16);
+    tma::expect_bytes(&sm.bar_load, (3 * kPanD * kC + kAinvVecs) * 16);
+    tma::load_bulk(sm.tp, p.tprime + (static_cast<size_t>(bh) * nchunks + cc) * kAinvVecs, kAinvVecs * 16, &sm.bar_load);
     tma::load_plain_tile(sm.k, &p.map_k, &sm.bar_load, cc * kC, h, b, 0);
     tma::load_plain_tile(sm.k + kSwBlockVecs, &p.map_k, &sm.bar_load, cc * kC, h, b, 64);
     tma::load_plain_tile(sm.q, &p.map_q, &sm.bar_load, cc * kC, h, b, 0);
@@ -190,16 +187,10 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
       sm.cd.cum[2 * tid] = s - l1;
       sm.cd.cum[2 * tid + 1] = s;
     }
-    if (tid == 0) {
-      if (p.chunk_states) {
-        // residual for the backward pass: the state entering the chunk
-        tma::store_bulk(p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * kResidualVecs, sm.s, kStateVecs * 16);
-        tma::commit_group();
-      }
-      // the previous chunk's output tile (older group) has left p / tp: T' of this chunk may land there
-      if (p.chunk_states) tma::wait_group_read<1>(); else tma::wait_group_read<0>();
-      tma::expect_bytes(&sm.bar_tp, kAinvVecs * 16);
-      tma::load_bulk(sm.tp, p.tprime + (static_cast<size_t>(bh) * nchunks + c) * kAinvVecs, kAinvVecs * 16, &sm.bar_tp);
+    if (tid == 0 && p.chunk_states) {
+      // residual for the backward pass: the state entering the chunk
+      tma::store_bulk(p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * kResidualVecs, sm.s, kStateVecs * 16);
+      tma::commit_group();
     }
     __syncthreads();
     if (tid < kC) {
@@ -208,6 +199,8 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
     }
     MXK_TF(0);
     mbar_wait_flag(&sm.bar_load, c & 1, timed_out);
+    // the previous chunk's output tile (the older bulk group) has left `yu` before epilogue 1 rewrites it
+    if (tid == 0) { if (p.chunk_states) tma::wait_group_read<1>(); else tma::wait_group_read<0>(); }
     fence_before_sync();
     __syncthreads();
     MXK_TF(1);
@@ -231,11 +224,27 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
     //      thread (v, wg) turns 32 tokens of its Y^T row into -(g Y)^T; then Q and K are rescaled in place
     //      (g_t q_t for the inter-chunk output, gam_j k_j for the state update) ----
     {
+      // every load first (TMEM, then the tile vectors and the decay scalars), so that their latencies overlap:
+      // the TMEM accesses are compiler barriers, and stores into a tile would order the later loads from it
+      const int j0 = (upper ? 32 : 0) + wg * 16;
+      float qk[16], y[32];
+      tmem_ld8(lane_base + kColQK + wg * 16, qk);
+      tmem_ld8(lane_base + kColQK + wg * 16 + 8, qk + 8);
+#pragma unroll
+      for (int c8 = 0; c8 < 4; ++c8) tmem_ld8(lane_base + kColY + wg * 32 + c8 * 8, y + c8 * 8);
+      uint4* tile = upper ? sm.k : sm.q;
+      uint4 tv[kPanD / 2];
+#pragma unroll
+      for (int p8 = 0; p8 < kPanD / 2; ++p8) tv[p8] = tile[sw_slot(row, wg * (kPanD / 2) + p8)];
+      const float sc = upper ? sm.cd.gam[row] : sm.cd.g[row];
       const int lo = row_first_key(dm, row);
       const float cum_t = sm.cd.cum[row];
-      const int j0 = (upper ? 32 : 0) + wg * 16;
-      float qk[16];
-      tmem_ld_row<16>(lane_base + kColQK + wg * 16, qk);
+      float cj[16], gt[32];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) cj[e] = sm.cd.cum[j0 + e];
+#pragma unroll
+      for (int e = 0; e < 32; ++e) gt[e] = sm.cd.g[wg * 32 + e];
+      tmem_ld_wait();
 #pragma unroll
       for (int jq = 0; jq < 2; ++jq) {
         float pm[8];
@@ -243,33 +252,27 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
         for (int e = 0; e < 8; ++e) {
           const int j = j0 + jq * 8 + e;
           const bool in = (j >= lo && j <= row);
-          pm[e] = in ? __expf(cum_t - sm.cd.cum[j]) * qk[jq * 8 + e] : 0.f;
+          pm[e] = in ? __expf(cum_t - cj[jq * 8 + e]) * qk[jq * 8 + e] : 0.f;
         }
         sm.p[((j0 >> 3) + jq) * kC + row] = pack8_bf16(pm);
       }
-      float y[32];
-      tmem_ld_row<32>(lane_base + kColY + wg * 32, y);
 #pragma unroll
       for (int tp8 = 0; tp8 < 4; ++tp8) {
         float f[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] = -sm.cd.g[wg * 32 + tp8 * 8 + e] * y[tp8 * 8 + e];
+        for (int e = 0; e < 8; ++e) f[e] = -gt[tp8 * 8 + e] * y[tp8 * 8 + e];
         sm.yu[(wg * 4 + tp8) * kD + vt] = pack8_bf16(f);
       }
-      uint4* tile = upper ? sm.k : sm.q;
-      const float sc = upper ? sm.cd.gam[row] : sm.cd.g[row];
 #pragma unroll
       for (int p8 = 0; p8 < kPanD / 2; ++p8) {
-        const int pn = wg * (kPanD / 2) + p8;
         float f[8];
-        unpack8_bf16(tile[sw_slot(row, pn)], f);
+        unpack8_bf16(tv[p8], f);
 #pragma unroll
         for (int e = 0; e < 8; ++e) f[e] *= sc;
-        tile[sw_slot(row, pn)] = pack8_bf16(f);
+        tile[sw_slot(row, wg * (kPanD / 2) + p8)] = pack8_bf16(f);
       }
     }
     MXK_TF(3);
-    mbar_wait_flag(&sm.bar_tp, c & 1, timed_out);
     fence_smem_to_async();
     fence_before_sync();
     __syncthreads();
@@ -344,37 +347,33 @@ __global__ void __launch_bounds__(kFwdThreads, 2) gdelta_fwd_kernel(const __grid
       flags_next = linattn::load_done_flags(drow, t0 + kC, p.T, lane);
     }
 
-    // ---- epilogue 3: output tile (staged row-major over p / tp for one TMA store), bf16 copy of the new state;
+    // ---- epilogue 3: output tile (staged row-major over U^T, dead now, for one TMA store), bf16 copy of the new state;
     //      thread (v, wg) covers tokens 32 wg .. 32 wg + 31 and state columns 64 wg .. 64 wg + 63 ----
     {
-      __nv_bfloat16* otile = reinterpret_cast<__nv_bfloat16*>(sm.p);
-      {
-        float o[32];
-        tmem_ld_row<32>(lane_base + kColO + wg * 32, o);
+      __nv_bfloat16* otile = reinterpret_cast<__nv_bfloat16*>(sm.yu);
+      float o[32], st[64];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) otile[(wg * 32 + e) * kD + vt] = __float2bfloat16(o[e]);
-      }
+      for (int c8 = 0; c8 < 4; ++c8) tmem_ld8(lane_base + kColO + wg * 32 + c8 * 8, o + c8 * 8);
+#pragma unroll
+      for (int c8 = 0; c8 < 8; ++c8) tmem_ld8(lane_base + kColS + wg * 64 + c8 * 8, st + c8 * 8);
+      tmem_ld_wait();
+#pragma unroll
+      for (int e = 0; e < 32; ++e) otile[(wg * 32 + e) * kD + vt] = __float2bfloat16(o[e]);
       const bool last = (c == nchunks - 1);
-      float* sl = (last && p.s_last && vt < p.d) ? p.s_last + (static_cast<size_t>(bh) * p.d + vt) * p.d : nullptr;
+      float* sl = (last && p.s_last && vt < p.d && wg * 64 < p.d) ? p.s_last + (static_cast<size_t>(bh) * p.d + vt) * p.d + wg * 64 : nullptr;
 #pragma unroll
-      for (int q2 = 0; q2 < 2; ++q2) {
-        const int q4 = wg * 2 + q2;
-        float s[32];
-        tmem_ld_row<32>(lane_base + kColS + q4 * 32, s);
-#pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8) {
-          sm.s[(q4 * 4 + c8) * kD + vt] = pack8_bf16(s + c8 * 8);
-          if (sl && q4 * 32 < p.d) {
-            *reinterpret_cast<float4*>(sl + q4 * 32 + c8 * 8) = make_float4(s[c8 * 8], s[c8 * 8 + 1], s[c8 * 8 + 2], s[c8 * 8 + 3]);
-            *reinterpret_cast<float4*>(sl + q4 * 32 + c8 * 8 + 4) = make_float4(s[c8 * 8 + 4], s[c8 * 8 + 5], s[c8 * 8 + 6], s[c8 * 8 + 7]);
-          }
+      for (int c8 = 0; c8 < 8; ++c8) {
+        sm.s[(wg * 8 + c8) * kD + vt] = pack8_bf16(st + c8 * 8);
+        if (sl) {
+          *reinterpret_cast<float4*>(sl + c8 * 8) = make_float4(st[c8 * 8], st[c8 * 8 + 1], st[c8 * 8 + 2], st[c8 * 8 + 3]);
+          *reinterpret_cast<float4*>(sl + c8 * 8 + 4) = make_float4(st[c8 * 8 + 4], st[c8 * 8 + 5], st[c8 * 8 + 6], st[c8 * 8 + 7]);
         }
       }
     }
     fence_smem_to_async();
     __syncthreads();
     if (tid == 0) {
-      tma::store_plain_tile(&p.map_o, sm.p, t0, h, b);   // rows past the end of the sequence are clipped
+      tma::store_plain_tile(&p.map_o, sm.yu, t0, h, b);   // rows past the end of the sequence are clipped
       tma::commit_group();
     }
     MXK_TF(8);

@@ -506,44 +506,48 @@ __global__ void __launch_bounds__(kBwdThreads) gdelta_bwd_kernel(const __grid_co
       if (leader) commit(&sm.bar[1]);
     }
 
-    // ---- decay gradients (overlaps the MMAs) ----
-    if (tid < kC) {
+    // ---- decay gradients, by warps 2..3 / warp 2 while warp 0 is issuing the MMAs above ----
+    if (tid >= 64 && tid < 128) {
+      const int x = tid - 64;
       float cs = 0.f;
 #pragma unroll 8
-      for (int t = 0; t < kC; ++t) cs += sm.l[t * kLS + tid];
-      const float dg = ((sm.dg_a[0][tid] + sm.dg_a[1][tid]) + (sm.dg_a[2][tid] + sm.dg_a[3][tid])) +
-                       ((sm.dg_b[0][tid] + sm.dg_b[1][tid]) + (sm.dg_b[2][tid] + sm.dg_b[3][tid]));
-      const float dgam = (sm.dgam_p[0][tid] + sm.dgam_p[1][tid]) + (sm.dgam_p[2][tid] + sm.dgam_p[3][tid]);
-      sm.dcum[tid] = sm.rowsum[tid] - cs + dg * sm.cd.g[tid] - dgam * sm.cd.gam[tid];
-      sm.colsum[tid] = dgam * sm.cd.gam[tid];
-    }
-    __syncthreads();
-    if (tid < 32) {
-      float extra = sm.colsum[2 * tid] + sm.colsum[2 * tid + 1];
+      for (int t = 0; t < kC; ++t) cs += sm.l[t * kLS + x];
+      asm volatile("bar.arrive 3, 96;" ::: "memory");   // E has been read: warp 0 may let the next T' land over it
+      const float dg = ((sm.dg_a[0][x] + sm.dg_a[1][x]) + (sm.dg_a[2][x] + sm.dg_a[3][x])) +
+                       ((sm.dg_b[0][x] + sm.dg_b[1][x]) + (sm.dg_b[2][x] + sm.dg_b[3][x]));
+      const float dgam = (sm.dgam_p[0][x] + sm.dgam_p[1][x]) + (sm.dgam_p[2][x] + sm.dgam_p[3][x]);
+      sm.dcum[x] = sm.rowsum[x] - cs + dg * sm.cd.g[x] - dgam * sm.cd.gam[x];
+      sm.colsum[x] = dgam * sm.cd.gam[x];
+      asm volatile("bar.sync 2, 64;" ::: "memory");   // warps 2 and 3 only
+      if (x < 32) {
+        float extra = sm.colsum[2 * x] + sm.colsum[2 * x + 1];
 #pragma unroll
-      for (int off = 16; off >= 1; off >>= 1) extra += __shfl_xor_sync(0xffffffffu, extra, off);
-      extra += (((sm.dgl[0] + sm.dgl[1]) + (sm.dgl[2] + sm.dgl[3])) + ((sm.dgl[4] + sm.dgl[5]) + (sm.dgl[6] + sm.dgl[7]))) * sm.cd.g[kC - 1];
-      float d0 = sm.dcum[2 * tid], d1 = sm.dcum[2 * tid + 1];
-      if (tid == 31) d1 += extra;
-      // suffix sums over the chunk
-      float s = d0 + d1;
+        for (int off = 16; off >= 1; off >>= 1) extra += __shfl_xor_sync(0xffffffffu, extra, off);
+        extra += (((sm.dgl[0] + sm.dgl[1]) + (sm.dgl[2] + sm.dgl[3])) + ((sm.dgl[4] + sm.dgl[5]) + (sm.dgl[6] + sm.dgl[7]))) * sm.cd.g[kC - 1];
+        float d0 = sm.dcum[2 * x], d1 = sm.dcum[2 * x + 1];
+        if (x == 31) d1 += extra;
+        // suffix sums over the chunk
+        float s = d0 + d1;
 #pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const float o = __shfl_down_sync(0xffffffffu, s, off);
-        if (tid + off < 32) s += o;
+        for (int off = 1; off < 32; off <<= 1) {
+          const float o = __shfl_down_sync(0xffffffffu, s, off);
+          if (x + off < 32) s += o;
+        }
+        const float dla0 = s, dla1 = s - d0;
+        const size_t base = (static_cast<size_t>(b) * p.T + t0) * p.H + h;
+        const int i0 = 2 * x, i1 = 2 * x + 1;
+        if (i0 < valid) p.dalpha[base + static_cast<size_t>(i0) * p.H] = ((dm >> i0) & 1ull) ? 0.f : dla0 / sm.cd.alpha[i0];
+        if (i1 < valid) p.dalpha[base + static_cast<size_t>(i1) * p.H] = ((dm >> i1) & 1ull) ? 0.f : dla1 / sm.cd.alpha[i1];
       }
-      const float dla0 = s, dla1 = s - d0;
-      const size_t base = (static_cast<size_t>(b) * p.T + t0) * p.H + h;
-      const int i0 = 2 * tid, i1 = 2 * tid + 1;
-      if (i0 < valid) p.dalpha[base + static_cast<size_t>(i0) * p.H] = ((dm >> i0) & 1ull) ? 0.f : dla0 / sm.cd.alpha[i0];
-      if (i1 < valid) p.dalpha[base + static_cast<size_t>(i1) * p.H] = ((dm >> i1) & 1ull) ? 0.f : dla1 / sm.cd.alpha[i1];
     }
 
     MXK_TG(8);
     mbar_wait_flag(&sm.bar[1], 1, timed_out);
     fence_after_sync();
     MXK_TG(9);
-    // the MMAs above were the last readers of the staged tiles: fetch the next chunk
+    // the MMAs above were the last readers of the staged tiles: fetch the next chunk (its T' lands over E, which
+    // warps 2..3 have finished reading once they have arrived on barrier 3)
+    if (warp == 0) asm volatile("bar.sync 3, 96;" ::: "memory");
     if (c > 0) {
       if (tid == 0) issue_chunk_loads(sm, p, b, h, c - 1, nchunks);
       ab_next = fetch_chunk_decay(p.alpha, p.beta, bt_base, p.H, h, t0 - kC, p.T, tid);

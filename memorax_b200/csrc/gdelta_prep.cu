@@ -10,6 +10,8 @@
 //          (columns 32..63 start at row 32: the upper-left of a unit lower-triangular inverse is zero),
 //   T' = A^-1 diag(beta) leaves as bf16 in tensor-core operand order, [j/8][t][8] with t the row and
 //          j the column.
+// Six CTAs per SM (34 KiB of shared memory, 80 registers) overlap one chunk's copy and substitution latency
+// with the others'.
 // The forward kernel then forms U = T' (V - diag(g) K S_in^T) and the backward kernel dR = T'^T dU as
 // plain tensor-core products.
 #include "gdelta_common.cuh"
@@ -32,19 +34,19 @@ struct PrepParams {
 };
 
 struct PrepSmem {
-  uint4 k[kPanD * kC];      // K, SW tiles (two 64-column blocks)
+  uint4 k[kPanD * kC];      // K, SW tiles (two 64-column blocks); once K K^T is done, its first 8 KiB stage
+                            // the bf16 T', [j/8][t][8]
   float lt[kC * kC];        // lt[j][t] = -beta_t L_tj
-  uint4 out[kAinvVecs];     // bf16 T', [j/8][t][8]
   ChunkDecay cd;
   uint64_t bar_load, bar_mma;
   uint32_t tmem;
 };
-static_assert(sizeof(PrepSmem) <= 44 * 1024, "five CTAs per SM");
+static_assert(sizeof(PrepSmem) <= 36 * 1024, "six CTAs per SM");
 
 constexpr uint32_t kPrepTmemCols = 32;
 constexpr uint32_t kUpper = 16u << 16;
 
-__global__ void __launch_bounds__(kThreads, 4) gdelta_prep_kernel(const __grid_constant__ PrepParams p) {
+__global__ void __launch_bounds__(kThreads, 6) gdelta_prep_kernel(const __grid_constant__ PrepParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   PrepSmem& sm = *reinterpret_cast<PrepSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -115,7 +117,7 @@ __global__ void __launch_bounds__(kThreads, 4) gdelta_prep_kernel(const __grid_c
     for (int t = 0; t < kC; ++t) r[t] = (t == tid) ? 1.f : 0.f;
     if (warp == 0) forward_substitute_range<0, kC - 1, kC>(reinterpret_cast<float2*>(r), sm.lt);
     else forward_substitute_range<32, kC - 1, kC>(reinterpret_cast<float2*>(r), sm.lt);
-    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(sm.out);
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(sm.k);
     const int base = (tid >> 3) * kC * 8 + (tid & 7);   // element (t, j = tid) at [j/8][t][j%8]
     const float beta_j = sm.cd.beta[tid];                // column j of A^-1 times beta_j
 #pragma unroll
@@ -124,7 +126,7 @@ __global__ void __launch_bounds__(kThreads, 4) gdelta_prep_kernel(const __grid_c
   fence_smem_to_async();
   __syncthreads();
   if (tid == 0) {
-    tma::store_bulk(p.ainv + static_cast<size_t>(item) * kAinvVecs, sm.out, kAinvVecs * 16);
+    tma::store_bulk(p.ainv + static_cast<size_t>(item) * kAinvVecs, sm.k, kAinvVecs * 16);
     tma::commit_group();
     tma::wait_group_all();
   }

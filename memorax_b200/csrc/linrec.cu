@@ -374,7 +374,16 @@ __device__ __forceinline__ float log_add_exp(float p, float q) {
   return hi + log1pf(expf(lo - hi));
 }
 
-template <int W>
+// MinGRU's gate math (min_gru.py:52-61), fused into the scan when the kernels are handed the Dense layers'
+// pre-activations instead of the elements:
+//   log_state = -softplus(-z) + log g(h~),  decay = -softplus(z),  g(h) = h >= 0 ? h + 0.5 : sigmoid(h).
+__device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+__device__ __forceinline__ float log_g(float h) { return h >= 0.f ? logf(h + 0.5f) : -softplus_f(-h); }
+__device__ __forceinline__ float dlog_g(float h) { return h >= 0.f ? 1.f / (h + 0.5f) : sigmoid_f(-h); }
+
+// GATES: `ls` / `d` hold the pre-activations z / h~ and the elements are formed on the fly.
+template <int W, bool GATES>
 __global__ void __launch_bounds__(kBlock)
 loglinrec_fwd_kernel(const float* __restrict__ ls, const float* __restrict__ d,
                      const float* __restrict__ x0, const float* __restrict__ a0,
@@ -412,6 +421,11 @@ loglinrec_fwd_kernel(const float* __restrict__ ls, const float* __restrict__ d,
         Pack<W> yo;
 #pragma unroll
         for (int i = 0; i < W; ++i) {
+          if constexpr (GATES) {
+            const float z = lv[u].v[i], ht = dv[u].v[i];
+            lv[u].v[i] = log_g(ht) - softplus_f(-z);
+            dv[u].v[i] = -softplus_f(z);
+          }
           cur.v[i] = rs[u] ? lv[u].v[i] : log_add_exp(dv[u].v[i] + cur.v[i], lv[u].v[i]);
           acc.v[i] = rs[u] ? dv[u].v[i] : dv[u].v[i] + acc.v[i];
           yo.v[i] = expf(cur.v[i]);
@@ -428,9 +442,10 @@ loglinrec_fwd_kernel(const float* __restrict__ ls, const float* __restrict__ d,
   }
 }
 
-template <int W>
+// GATES: `d` holds z, `ht` the second pre-activation; gls / gd receive the cotangents of z / h~.
+template <int W, bool GATES>
 __global__ void __launch_bounds__(kBlock)
-loglinrec_bwd_kernel(const float* __restrict__ d, const float* __restrict__ x,
+loglinrec_bwd_kernel(const float* __restrict__ d, const float* __restrict__ ht, const float* __restrict__ x,
                      const float* __restrict__ x0, const uint8_t* __restrict__ done,
                      const float* __restrict__ gx, const float* __restrict__ gy,
                      const float* __restrict__ gx_last, float* __restrict__ gls,
@@ -448,7 +463,7 @@ loglinrec_bwd_kernel(const float* __restrict__ d, const float* __restrict__ x,
   Pack<W> carry = gx_last ? load_pack_cached<W>(gx_last + crow) : fill_pack<W>(0.f, 0.f, false);
 
   for (int t0 = T - 1; t0 >= 0; t0 -= kUnroll) {
-    Pack<W> dv[kUnroll], xv[kUnroll], xp[kUnroll], gxv[kUnroll], gyv[kUnroll];
+    Pack<W> dv[kUnroll], xv[kUnroll], xp[kUnroll], gxv[kUnroll], gyv[kUnroll], hv[kUnroll];
     bool rs[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
@@ -459,8 +474,12 @@ loglinrec_bwd_kernel(const float* __restrict__ d, const float* __restrict__ x,
         xv[u] = load_pack<W>(x + off);
         gxv[u] = gx ? load_pack<W>(gx + off) : fill_pack<W>(0.f, 0.f, false);
         if (gy) gyv[u] = load_pack<W>(gy + off);
-        if (!rs[u]) {
+        if constexpr (GATES) {
           dv[u] = load_pack<W>(d + off);
+          hv[u] = load_pack<W>(ht + off);
+        }
+        if (!rs[u]) {
+          if constexpr (!GATES) dv[u] = load_pack<W>(d + off);
           if (t > 0) xp[u] = load_pack<W>(x + off - row);
           else xp[u] = x0 ? load_pack_cached<W>(x0 + crow) : fill_pack<W>(-INFINITY, 0.f, false);
         }
@@ -477,12 +496,20 @@ loglinrec_bwd_kernel(const float* __restrict__ d, const float* __restrict__ x,
           if (gy) g = fmaf(gyv[u].v[i], expf(xv[u].v[i]), g);
           float w = 0.f;
           if (!rs[u]) {
-            const float p = dv[u].v[i] + xp[u].v[i];
+            const float dec = GATES ? -softplus_f(dv[u].v[i]) : dv[u].v[i];
+            const float p = dec + xp[u].v[i];
             w = (p == -INFINITY) ? 0.f : expf(p - xv[u].v[i]);
           }
           od.v[i] = w * g;
           ols.v[i] = (1.f - w) * g;
           carry.v[i] = od.v[i];
+          if constexpr (GATES) {
+            // chain rule through the gate math: d(-softplus(-z))/dz = 1 - sigmoid(z), d(-softplus(z))/dz = -sigmoid(z)
+            const float sg = sigmoid_f(dv[u].v[i]);
+            const float g_ls = ols.v[i], g_d = od.v[i];
+            ols.v[i] = g_ls * (1.f - sg) - g_d * sg;
+            od.v[i] = g_ls * dlog_g(hv[u].v[i]);
+          }
         }
         const size_t off = seq + static_cast<size_t>(t) * row;
         store_pack<W>(gls + off, ols);
@@ -690,9 +717,26 @@ int mxk_loglinrec_f32_fwd(const float* ls, const float* d, const float* x0, cons
   const int w = pick_width(total, D, false, {ls, d, x0, a0, x, y, a_last});
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (w == 4)
-    loglinrec_fwd_kernel<4><<<blocks_for(total / 4), kBlock, 0, s>>>(ls, d, x0, a0, done, x, y, a_last, B, T, D);
+    loglinrec_fwd_kernel<4, false><<<blocks_for(total / 4), kBlock, 0, s>>>(ls, d, x0, a0, done, x, y, a_last, B, T, D);
   else
-    loglinrec_fwd_kernel<1><<<blocks_for(total), kBlock, 0, s>>>(ls, d, x0, a0, done, x, y, a_last, B, T, D);
+    loglinrec_fwd_kernel<1, false><<<blocks_for(total), kBlock, 0, s>>>(ls, d, x0, a0, done, x, y, a_last, B, T, D);
+  return launch_status();
+}
+
+int mxk_mingru_f32_fwd(const float* z, const float* h_tilde, const float* x0, const float* a0, const uint8_t* done,
+                       float* x, float* y, float* a_last, int B, int T, int D, mxk_stream_t stream) {
+  using namespace mxk;
+  if (!z || !h_tilde || !x) return MXK_ERR_NULL;
+  if (int st = check_dims(B, T, D)) return st;
+  for (const void* p : {(const void*)z, (const void*)h_tilde, (const void*)x0, (const void*)a0, (const void*)x, (const void*)y, (const void*)a_last})
+    if (p && (reinterpret_cast<uintptr_t>(p) % 4)) return MXK_ERR_ALIGN;
+  const long long total = static_cast<long long>(B) * D;
+  const int w = pick_width(total, D, false, {z, h_tilde, x0, a0, x, y, a_last});
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (w == 4)
+    loglinrec_fwd_kernel<4, true><<<blocks_for(total / 4), kBlock, 0, s>>>(z, h_tilde, x0, a0, done, x, y, a_last, B, T, D);
+  else
+    loglinrec_fwd_kernel<1, true><<<blocks_for(total), kBlock, 0, s>>>(z, h_tilde, x0, a0, done, x, y, a_last, B, T, D);
   return launch_status();
 }
 
@@ -709,9 +753,28 @@ int mxk_loglinrec_f32_bwd(const float* d, const float* x, const float* x0, const
   const int w = pick_width(total, D, false, {d, x, x0, gx, gy, gx_last, gls, gd, gx0});
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (w == 4)
-    loglinrec_bwd_kernel<4><<<blocks_for(total / 4), kBlock, 0, s>>>(d, x, x0, done, gx, gy, gx_last, gls, gd, gx0, B, T, D);
+    loglinrec_bwd_kernel<4, false><<<blocks_for(total / 4), kBlock, 0, s>>>(d, nullptr, x, x0, done, gx, gy, gx_last, gls, gd, gx0, B, T, D);
   else
-    loglinrec_bwd_kernel<1><<<blocks_for(total), kBlock, 0, s>>>(d, x, x0, done, gx, gy, gx_last, gls, gd, gx0, B, T, D);
+    loglinrec_bwd_kernel<1, false><<<blocks_for(total), kBlock, 0, s>>>(d, nullptr, x, x0, done, gx, gy, gx_last, gls, gd, gx0, B, T, D);
+  return launch_status();
+}
+
+int mxk_mingru_f32_bwd(const float* z, const float* h_tilde, const float* x, const float* x0, const uint8_t* done,
+                       const float* gx, const float* gy, const float* gx_last, float* gz, float* gh, float* gx0,
+                       int B, int T, int D, mxk_stream_t stream) {
+  using namespace mxk;
+  if (!z || !h_tilde || !x || !gz || !gh || (!gx && !gy)) return MXK_ERR_NULL;
+  if (int st = check_dims(B, T, D)) return st;
+  for (const void* p : {(const void*)z, (const void*)h_tilde, (const void*)x, (const void*)x0, (const void*)gx, (const void*)gy,
+                        (const void*)gx_last, (const void*)gz, (const void*)gh, (const void*)gx0})
+    if (p && (reinterpret_cast<uintptr_t>(p) % 4)) return MXK_ERR_ALIGN;
+  const long long total = static_cast<long long>(B) * D;
+  const int w = pick_width(total, D, false, {z, h_tilde, x, x0, gx, gy, gx_last, gz, gh, gx0});
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (w == 4)
+    loglinrec_bwd_kernel<4, true><<<blocks_for(total / 4), kBlock, 0, s>>>(z, h_tilde, x, x0, done, gx, gy, gx_last, gz, gh, gx0, B, T, D);
+  else
+    loglinrec_bwd_kernel<1, true><<<blocks_for(total), kBlock, 0, s>>>(z, h_tilde, x, x0, done, gx, gy, gx_last, gz, gh, gx0, B, T, D);
   return launch_status();
 }
 

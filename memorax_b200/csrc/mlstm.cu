@@ -305,8 +305,10 @@ __global__ void __launch_bounds__(D * SPLIT) mlstm_bwd_kernel(const MlstmParams 
 #pragma unroll
         for (int i = 0; i < L; ++i) { col[i] = 0.f; row[i] = 0.f; }
       } else {
-        const float sa_dsa = G - sb_dsb;
-        const float dm_t = dm - G;                     // dm - sa d(sa) - sb d(sb)
+        // sa = 0 (the past is more than e^-100 below this step's input gate, or the carry is initialize_carry's
+        // m = -1e9): nothing flows to the past, exactly
+        const float sa_dsa = sa == 0.f ? 0.f : G - sb_dsb;
+        const float dm_t = dm - sa_dsa - sb_dsb;
         float d_mprev = sa_dsa;
         d_lf = sa_dsa;
         d_li = sb_dsb;

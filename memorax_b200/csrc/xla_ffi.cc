@@ -78,6 +78,55 @@ ffi::Error LinRecBwd(cudaStream_t stream, ffi::Buffer<ffi::F32> a, ffi::Buffer<f
                                     (int)d[0], (int)d[1], (int)d[2], stream));
 }
 
+// ---- Mamba's scan with the per-head decay un-expanded (mamba.py:109-122): a is (B,T,G); `partials` is the
+//      group-gradient scratch (empty when a group is exactly 128 channels) ----
+ffi::Error LinRecGroupedFwd(cudaStream_t stream, ffi::Buffer<ffi::F32> a, ffi::Buffer<ffi::F32> b, ffi::Buffer<ffi::F32> h0,
+                            ffi::Buffer<ffi::F32> a0, ffi::Buffer<ffi::U8> done, ffi::ResultBuffer<ffi::F32> h,
+                            ffi::ResultBuffer<ffi::F32> a_last) {
+  auto d = b.dimensions();
+  return ToError(mxk_linrec_f32_grouped_fwd(a.typed_data(), b.typed_data(), h0.typed_data(), a0.typed_data(), done.typed_data(),
+                                            h->typed_data(), a_last->typed_data(), (int)d[0], (int)d[1], (int)d[2],
+                                            (int)a.dimensions()[2], stream));
+}
+ffi::Error LinRecGroupedBwd(cudaStream_t stream, ffi::Buffer<ffi::F32> a, ffi::Buffer<ffi::F32> h, ffi::Buffer<ffi::F32> h0,
+                            ffi::Buffer<ffi::U8> done, ffi::Buffer<ffi::F32> gh, ffi::Buffer<ffi::F32> gh_last,
+                            ffi::ResultBuffer<ffi::F32> gb, ffi::ResultBuffer<ffi::F32> ga, ffi::ResultBuffer<ffi::F32> gh0,
+                            ffi::ResultBuffer<ffi::F32> partials) {
+  auto d = h.dimensions();
+  return ToError(mxk_linrec_f32_grouped_bwd(a.typed_data(), h.typed_data(), h0.typed_data(), done.typed_data(), gh.typed_data(),
+                                            gh_last.typed_data(), gb->typed_data(), ga->typed_data(), gh0->typed_data(),
+                                            partials->untyped_data(), partials->size_bytes(), (int)d[0], (int)d[1], (int)d[2],
+                                            (int)a.dimensions()[2], stream));
+}
+
+// ---- mLSTM scan + memory read-out (mlstm.py:163-218); `scratch` is the backward call's workspace result ----
+ffi::Error MlstmFwd(cudaStream_t stream, ffi::Buffer<ffi::F32> q, ffi::Buffer<ffi::F32> k, ffi::Buffer<ffi::F32> v,
+                    ffi::Buffer<ffi::F32> log_i, ffi::Buffer<ffi::F32> log_f, ffi::Buffer<ffi::F32> c0, ffi::Buffer<ffi::F32> n0,
+                    ffi::Buffer<ffi::F32> m0, ffi::Buffer<ffi::F32> f0, ffi::Buffer<ffi::U8> done, ffi::ResultBuffer<ffi::F32> h,
+                    ffi::ResultBuffer<ffi::F32> c_last, ffi::ResultBuffer<ffi::F32> n_last, ffi::ResultBuffer<ffi::F32> m_last,
+                    ffi::ResultBuffer<ffi::F32> f_last, float eps) {
+  auto d = q.dimensions();
+  return ToError(mxk_mlstm_f32_fwd(q.typed_data(), k.typed_data(), v.typed_data(), log_i.typed_data(), log_f.typed_data(),
+                                   c0.typed_data(), n0.typed_data(), m0.typed_data(), f0.typed_data(), done.typed_data(),
+                                   h->typed_data(), c_last->typed_data(), n_last->typed_data(), m_last->typed_data(),
+                                   f_last->typed_data(), (int)d[0], (int)d[1], (int)d[2], (int)d[3], eps, stream));
+}
+ffi::Error MlstmBwd(cudaStream_t stream, ffi::Buffer<ffi::F32> q, ffi::Buffer<ffi::F32> k, ffi::Buffer<ffi::F32> v,
+                    ffi::Buffer<ffi::F32> log_i, ffi::Buffer<ffi::F32> log_f, ffi::Buffer<ffi::F32> c0, ffi::Buffer<ffi::F32> n0,
+                    ffi::Buffer<ffi::F32> m0, ffi::Buffer<ffi::U8> done, ffi::Buffer<ffi::F32> dh, ffi::Buffer<ffi::F32> dc_last,
+                    ffi::Buffer<ffi::F32> dn_last, ffi::Buffer<ffi::F32> dm_last, ffi::ResultBuffer<ffi::F32> dq,
+                    ffi::ResultBuffer<ffi::F32> dk, ffi::ResultBuffer<ffi::F32> dv, ffi::ResultBuffer<ffi::F32> dlog_i,
+                    ffi::ResultBuffer<ffi::F32> dlog_f, ffi::ResultBuffer<ffi::F32> dc0, ffi::ResultBuffer<ffi::F32> dn0,
+                    ffi::ResultBuffer<ffi::F32> dm0, ffi::ResultBuffer<ffi::F32> scratch, float eps) {
+  auto d = q.dimensions();
+  return ToError(mxk_mlstm_f32_bwd(q.typed_data(), k.typed_data(), v.typed_data(), log_i.typed_data(), log_f.typed_data(),
+                                   c0.typed_data(), n0.typed_data(), m0.typed_data(), done.typed_data(), dh.typed_data(),
+                                   dc_last.typed_data(), dn_last.typed_data(), dm_last.typed_data(), dq->typed_data(),
+                                   dk->typed_data(), dv->typed_data(), dlog_i->typed_data(), dlog_f->typed_data(),
+                                   dc0->typed_data(), dn0->typed_data(), dm0->typed_data(), scratch->untyped_data(),
+                                   scratch->size_bytes(), (int)d[0], (int)d[1], (int)d[2], (int)d[3], eps, stream));
+}
+
 // ---- MinGRU log-space scan + read-out (min_gru.py:67-78) ----
 ffi::Error MinGruFwd(cudaStream_t stream, ffi::Buffer<ffi::F32> ls, ffi::Buffer<ffi::F32> dec, ffi::Buffer<ffi::F32> x0,
                      ffi::Buffer<ffi::F32> a0, ffi::Buffer<ffi::U8> done, ffi::ResultBuffer<ffi::F32> x,
@@ -171,6 +220,18 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(MxkLinRecFwd, LinRecFwd,
 XLA_FFI_DEFINE_HANDLER_SYMBOL(MxkLinRecBwd, LinRecBwd,
     MXK_BIND_STREAM().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<U8B>().Arg<F32B>().Arg<F32B>()
         .Ret<F32B>().Ret<F32B>().Ret<F32B>());
+XLA_FFI_DEFINE_HANDLER_SYMBOL(MxkLinRecGroupedFwd, LinRecGroupedFwd,
+    MXK_BIND_STREAM().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<U8B>().Ret<F32B>().Ret<F32B>());
+XLA_FFI_DEFINE_HANDLER_SYMBOL(MxkLinRecGroupedBwd, LinRecGroupedBwd,
+    MXK_BIND_STREAM().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<U8B>().Arg<F32B>().Arg<F32B>()
+        .Ret<F32B>().Ret<F32B>().Ret<F32B>().Ret<F32B>());
+XLA_FFI_DEFINE_HANDLER_SYMBOL(MxkMlstmFwd, MlstmFwd,
+    MXK_BIND_STREAM().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>()
+        .Arg<F32B>().Arg<U8B>().Ret<F32B>().Ret<F32B>().Ret<F32B>().Ret<F32B>().Ret<F32B>().Attr<float>("eps"));
+XLA_FFI_DEFINE_HANDLER_SYMBOL(MxkMlstmBwd, MlstmBwd,
+    MXK_BIND_STREAM().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>()
+        .Arg<U8B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Ret<F32B>().Ret<F32B>().Ret<F32B>().Ret<F32B>()
+        .Ret<F32B>().Ret<F32B>().Ret<F32B>().Ret<F32B>().Ret<F32B>().Attr<float>("eps"));
 XLA_FFI_DEFINE_HANDLER_SYMBOL(MxkMinGruFwd, MinGruFwd,
     MXK_BIND_STREAM().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<U8B>().Ret<F32B>().Ret<F32B>().Ret<F32B>());
 XLA_FFI_DEFINE_HANDLER_SYMBOL(MxkMinGruBwd, MinGruBwd,

@@ -177,17 +177,28 @@ class LRUCell(MemoroidCellBase):
 
 
 # ------------------------------------------------------------------- MinGRU
-class MinGRUCell(MemoroidCellBase):
-    """Log-space minimal GRU (min_gru.py:14-90)."""
+class MinGRUPreactivations(tuple):
+    """(z, h_tilde): what ``MinGRUCell`` hands its fused scan instead of the (log_state, decay) elements."""
 
-    def __init__(self, features, in_features=None):
+
+class MinGRUCell(MemoroidCellBase):
+    """Log-space minimal GRU (min_gru.py:14-90).  With ``fused_gates`` (default) the gate math of
+    min_gru.py:52-61 runs inside the scan kernels: ``forward`` returns the two Dense pre-activations and the
+    (B,T,F) log_state / decay tensors are never written; ``elements(x)`` gives the reference's elements."""
+
+    def __init__(self, features, in_features=None, fused_gates=True):
         super().__init__()
-        self.features = features
+        self.features, self.fused_gates = features, fused_gates
         in_features = in_features or features
         self.z = nn.Linear(in_features, features, bias=False)
         self.h = nn.Linear(in_features, features, bias=False)
 
     def forward(self, x, **kwargs):
+        if self.fused_gates:
+            return MinGRUPreactivations((self.z(x), self.h(x)))
+        return self.elements(x)
+
+    def elements(self, x):
         z, h_tilde = self.z(x), self.h(x)
         log_z = -torch.nn.functional.softplus(-z)
         log_h = torch.where(h_tilde >= 0, torch.log(torch.relu(h_tilde) + 0.5),
@@ -213,9 +224,12 @@ class MinGRUCell(MemoroidCellBase):
         return (x, None), (x[:, -1:], a_last[:, None])
 
     def scan(self, z, initial_carry, done, inputs):
-        log_state, decay = z
         x0, a0 = _squeeze_carry(initial_carry, 2)
-        x, y, a_last = ops.LogLinRec.apply(log_state.contiguous(), decay.contiguous(), x0, a0, done)
+        if isinstance(z, MinGRUPreactivations):
+            x, y, a_last = ops.MinGRUFused.apply(z[0].contiguous(), z[1].contiguous(), x0, a0, done)
+        else:
+            log_state, decay = z
+            x, y, a_last = ops.LogLinRec.apply(log_state.contiguous(), decay.contiguous(), x0, a0, done)
         return (x[:, -1:], a_last[:, None]), y
 
 

@@ -216,6 +216,34 @@ class LogLinRec(torch.autograd.Function):
         return gls, gd, gx0, None, None
 
 
+class MinGRUFused(torch.autograd.Function):
+    """(z, h_tilde, x0, a0, done) -> (x, y = exp(x), a_last): MinGRU's gate math (min_gru.py:52-61), scan and
+    read-out in one kernel per direction; ``z`` / ``h_tilde`` are the Dense layers' pre-activations."""
+
+    @staticmethod
+    def forward(ctx, z, h_tilde, x0, a0, done):
+        z, h_tilde = _dev(z, torch.float32, "z"), _dev(h_tilde, torch.float32, "h_tilde")
+        x0, a0 = _dev(x0, torch.float32, "x0"), _dev(a0, torch.float32, "a0")
+        bsz, steps, dim = z.shape
+        x, y = torch.empty_like(z), torch.empty_like(z)
+        a_last = torch.empty(bsz, dim, dtype=torch.float32, device=z.device)
+        _lib.call("mxk_mingru_f32_fwd", _ptr(z), _ptr(h_tilde), _ptr(x0), _ptr(a0), _ptr(_done_bytes(done)), _ptr(x),
+                  _ptr(y), _ptr(a_last), bsz, steps, dim, _stream())
+        ctx.save_for_backward(z, h_tilde, x, x0, done)
+        ctx.mark_non_differentiable(a_last)
+        return x, y, a_last
+
+    @staticmethod
+    def backward(ctx, gx, gy, _ga_last):
+        z, h_tilde, x, x0, done = ctx.saved_tensors
+        bsz, steps, dim = z.shape
+        gz, gh = torch.empty_like(z), torch.empty_like(z)
+        gx0 = torch.empty(bsz, dim, dtype=torch.float32, device=z.device) if (x0 is not None and ctx.needs_input_grad[2]) else None
+        _lib.call("mxk_mingru_f32_bwd", _ptr(z), _ptr(h_tilde), _ptr(x), _ptr(x0), _ptr(_done_bytes(done)),
+                  _ptr(gx.contiguous()), _ptr(gy.contiguous()), None, _ptr(gz), _ptr(gh), _ptr(gx0), bsz, steps, dim, _stream())
+        return gz, gh, gx0, None, None
+
+
 # ------------------------------------------------------- device status word
 # One int32 per device that every tensor-core launch is handed: a kernel whose bounded wait gave up
 # sets it to 1 and drains.  ``check=True`` on a wrapper reads it right after the launch (one host

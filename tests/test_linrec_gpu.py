@@ -248,3 +248,35 @@ def test_linrec_grouped_rejects_narrow_groups():
     p = x.data_ptr()
     assert _lib.lib.mxk_linrec_f32_grouped_fwd(p, p, None, None, None, p, None, 1, 1, 96, 2, None) == -4
     assert _lib.lib.mxk_linrec_f32_grouped_fwd(p, p, None, None, None, p, None, 1, 1, 100, 3, None) == -2
+
+
+@pytest.mark.parametrize("shape", [(3, 9, 6), (8, 65, 256), (64, 40, 1024)])
+def test_mingru_fused_gate_math(shape):
+    """MinGRU's gate math (min_gru.py:52-61) inside the scan kernels: the Dense pre-activations z, h~ in, log
+    states / read-out out, cotangents of z and h~ back -- against fp64 autograd through the same formulas and
+    the oracle's sequential scan."""
+    from memorax_b200 import ops
+    bsz, steps, dim = shape
+    gen = torch.Generator().manual_seed(31 + steps)
+    z, ht = rnd(gen, *shape) * 2.5, rnd(gen, *shape) * 2.0
+    x0, a0 = rnd(gen, bsz, dim), -rnd(gen, bsz, dim).abs()
+    done = make_done(gen, bsz, steps, 0.05)
+    gx, gy = rnd(gen, *shape), rnd(gen, *shape)
+    zr, hr, x0r = z.clone().requires_grad_(), ht.clone().requires_grad_(), x0.clone().requires_grad_()
+    sp = torch.nn.functional.softplus
+    log_state = -sp(-zr) + torch.where(hr >= 0, torch.log(torch.relu(hr) + 0.5), -sp(-hr))
+    x_ref, a_ref = mo.mingru_seq(log_state, -sp(zr), x0r, done.double(), a0)
+    ((gx * x_ref).sum() + (gy * x_ref.exp()).sum()).backward()
+    cu = lambda t: t.float().cuda()
+    leaves = [cu(z).requires_grad_(), cu(ht).requires_grad_(), cu(x0).requires_grad_()]
+    x, y, a_last = ops.MinGRUFused.apply(*leaves, cu(a0), done.cuda())
+    close(x, x_ref, what="x")
+    close(y, x_ref.exp(), what="y")
+    close(a_last, a_ref, what="a_last")
+    ((x * cu(gx)).sum() + (y * cu(gy)).sum()).backward()
+    close(leaves[0].grad, zr.grad, rel=1e-4, what="gz")
+    close(leaves[1].grad, hr.grad, rel=1e-4, what="gh")
+    close(leaves[2].grad, x0r.grad, rel=1e-4, what="gx0")
+    # default (-inf) carry: finite everywhere
+    x2, y2, _ = ops.MinGRUFused.apply(cu(z), cu(ht), None, None, done.cuda())
+    assert torch.isfinite(y2).all() and not torch.isnan(x2).any()
