@@ -109,7 +109,7 @@ __device__ __forceinline__ void gate_step(bool reset, float li, float lf, float&
 template <int D, int SPLIT>
 __global__ void __launch_bounds__(D * SPLIT) mlstm_fwd_kernel(const MlstmParams p) {
   constexpr int L = D / SPLIT, NT = D * SPLIT, NW = NT / 32;
-  __shared__ float rows[3][kTS][D];
+  __shared__ __align__(16) float rows[3][kTS][D];
   __shared__ float sli[kTS], slf[kTS];
   __shared__ uint8_t sdone[kTS];
   __shared__ float red[2][NW];
@@ -137,10 +137,20 @@ __global__ void __launch_bounds__(D * SPLIT) mlstm_fwd_kernel(const MlstmParams 
       fsum = reset ? slf[tt] : fsum + slf[tt];
       const float sbv = sb * rows[2][tt][j];
       float part = 0.f;
+      // broadcast reads of the staged k_t, q_t rows, four values per shared-memory access
+      const float4* k4 = reinterpret_cast<const float4*>(&rows[1][tt][i0]);
+      const float4* q4 = reinterpret_cast<const float4*>(&rows[0][tt][i0]);
 #pragma unroll
-      for (int i = 0; i < L; ++i) {
-        cc[i] = fmaf(sa, cc[i], rows[1][tt][i0 + i] * sbv);
-        part = fmaf(rows[0][tt][i0 + i], cc[i], part);
+      for (int i = 0; i < L / 4; ++i) {
+        const float4 kk = k4[i], qq = q4[i];
+        cc[4 * i] = fmaf(sa, cc[4 * i], kk.x * sbv);
+        cc[4 * i + 1] = fmaf(sa, cc[4 * i + 1], kk.y * sbv);
+        cc[4 * i + 2] = fmaf(sa, cc[4 * i + 2], kk.z * sbv);
+        cc[4 * i + 3] = fmaf(sa, cc[4 * i + 3], kk.w * sbv);
+        part = fmaf(qq.x, cc[4 * i], part);
+        part = fmaf(qq.y, cc[4 * i + 1], part);
+        part = fmaf(qq.z, cc[4 * i + 2], part);
+        part = fmaf(qq.w, cc[4 * i + 3], part);
       }
       if (SPLIT == 2) part += __shfl_xor_sync(0xffffffffu, part, 1);
       nj = fmaf(sa, nj, sb * rows[1][tt][j]);
@@ -164,10 +174,10 @@ __global__ void __launch_bounds__(D * SPLIT) mlstm_fwd_kernel(const MlstmParams 
 template <int D, int SPLIT>
 __global__ void __launch_bounds__(D * SPLIT) mlstm_bwd_kernel(const MlstmParams p) {
   constexpr int L = D / SPLIT, NT = D * SPLIT, NW = NT / 32;
-  __shared__ float rows[4][kTS][D];      // q, k, v, dh of the staged steps
+  __shared__ __align__(16) float rows[4][kTS][D];      // q, k, v, dh of the staged steps
   __shared__ float sli[kTS], slf[kTS];
   __shared__ uint8_t sdone[kTS];
-  __shared__ float sdnum[2][D];          // dnum of the current step (double-buffered by step parity)
+  __shared__ __align__(16) float sdnum[2][D];          // dnum of the current step (double-buffered by step parity)
   __shared__ float red[2][NW];
   __shared__ float2 red2[2][NW];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -200,11 +210,21 @@ __global__ void __launch_bounds__(D * SPLIT) mlstm_bwd_kernel(const MlstmParams 
         const float kj = rows[1][tt][j], vj = rows[2][tt][j];
         const float sbv = sb * vj, sbk = sb * kj;
         float num = 0.f;
+        {
+          const float4* q4 = reinterpret_cast<const float4*>(&rows[0][tt][i0]);
+          const float4* k4 = reinterpret_cast<const float4*>(&rows[1][tt][i0]);
+          const float4* v4 = reinterpret_cast<const float4*>(&rows[2][tt][i0]);
 #pragma unroll
-        for (int i = 0; i < L; ++i) {
-          col[i] = fmaf(sa, col[i], rows[1][tt][i0 + i] * sbv);
-          row[i] = fmaf(sa, row[i], rows[2][tt][i0 + i] * sbk);
-          num = fmaf(rows[0][tt][i0 + i], col[i], num);
+          for (int i = 0; i < L / 4; ++i) {
+            const float4 qq = q4[i], kk = k4[i], vv = v4[i];
+            const float ke[4] = {kk.x, kk.y, kk.z, kk.w}, ve[4] = {vv.x, vv.y, vv.z, vv.w}, qe[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              col[4 * i + e] = fmaf(sa, col[4 * i + e], ke[e] * sbv);
+              row[4 * i + e] = fmaf(sa, row[4 * i + e], ve[e] * sbk);
+              num = fmaf(qe[e], col[4 * i + e], num);
+            }
+          }
         }
         if (SPLIT == 2) num += __shfl_xor_sync(0xffffffffu, num, 1);
         nj = fmaf(sa, nj, sb * kj);
@@ -220,8 +240,17 @@ __global__ void __launch_bounds__(D * SPLIT) mlstm_bwd_kernel(const MlstmParams 
         if (half == 0) sdnum[tt & 1][j] = dhj / den;
         __syncthreads();
         float dqj = 0.f;
+        {
+          const float4* d4 = reinterpret_cast<const float4*>(&sdnum[tt & 1][i0]);
 #pragma unroll
-        for (int i = 0; i < L; ++i) dqj = fmaf(row[i], sdnum[tt & 1][i0 + i], dqj);
+          for (int i = 0; i < L / 4; ++i) {
+            const float4 dd = d4[i];
+            dqj = fmaf(row[4 * i], dd.x, dqj);
+            dqj = fmaf(row[4 * i + 1], dd.y, dqj);
+            dqj = fmaf(row[4 * i + 2], dd.z, dqj);
+            dqj = fmaf(row[4 * i + 3], dd.w, dqj);
+          }
+        }
         if (SPLIT == 2) dqj += __shfl_xor_sync(0xffffffffu, dqj, 1);
         dqj = fmaf(dqn, nj, dqj);
         const size_t tok = (static_cast<size_t>(b) * p.T + t0 + tt) * p.H + h;
@@ -274,12 +303,24 @@ __global__ void __launch_bounds__(D * SPLIT) mlstm_bwd_kernel(const MlstmParams 
       __syncthreads();
       // cotangents of (C_t, n_t, m_t, G_t) including this step's read-out
       float dvj = 0.f, wj = 0.f;
+      {
+        const float4* q4 = reinterpret_cast<const float4*>(&rows[0][tt][i0]);
+        const float4* k4 = reinterpret_cast<const float4*>(&rows[1][tt][i0]);
+        const float4* v4 = reinterpret_cast<const float4*>(&rows[2][tt][i0]);
+        const float4* d4 = reinterpret_cast<const float4*>(&sdnum[tt & 1][i0]);
 #pragma unroll
-      for (int i = 0; i < L; ++i) {
-        col[i] = fmaf(rows[0][tt][i0 + i], dnum_j, col[i]);
-        row[i] = fmaf(qj, sdnum[tt & 1][i0 + i], row[i]);
-        dvj = fmaf(col[i], rows[1][tt][i0 + i], dvj);
-        wj = fmaf(row[i], rows[2][tt][i0 + i], wj);
+        for (int i = 0; i < L / 4; ++i) {
+          const float4 qq = q4[i], kk = k4[i], vv = v4[i], dd = d4[i];
+          const float qe[4] = {qq.x, qq.y, qq.z, qq.w}, ke[4] = {kk.x, kk.y, kk.z, kk.w};
+          const float ve[4] = {vv.x, vv.y, vv.z, vv.w}, de[4] = {dd.x, dd.y, dd.z, dd.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            col[4 * i + e] = fmaf(qe[e], dnum_j, col[4 * i + e]);
+            row[4 * i + e] = fmaf(qj, de[e], row[4 * i + e]);
+            dvj = fmaf(col[4 * i + e], ke[e], dvj);
+            wj = fmaf(row[4 * i + e], ve[e], wj);
+          }
+        }
       }
       if (SPLIT == 2) {
         dvj += __shfl_xor_sync(0xffffffffu, dvj, 1);
