@@ -351,7 +351,7 @@ class TrainC5:
             d, H, hd = 512, 8, 64
             lin = lambda i, o: torch.nn.Linear(i, o)
             self._cpu = dict(embed=lin(self.OBS, d), head=lin(d, 1), layers=[
-                dict(n1=torch.nn.LayerNorm(d), q=lin(d, d), k=lin(d, d), v=lin(d, d), gate=lin(d, 2 * H), rms=torch.nn.RMSNorm(d),
+                dict(n1=torch.nn.LayerNorm(d), q=lin(d, d), k=lin(d, d), v=lin(d, d), gate=lin(d, 2 * H), rms=torch.nn.RMSNorm(d, eps=1e-6),
                      out=lin(d, d), g1=lin(d, d), n2=torch.nn.LayerNorm(d), up=lin(d, 4 * d), down=lin(4 * d, d), g2=lin(d, d))
                 for _ in range(4)])
         P, F = self._cpu, torch.nn.functional

@@ -245,7 +245,7 @@ class LinearAttentionCell(MemoroidCellBase):
         self.key = nn.Linear(in_features, hidden, bias=False)
         self.value = nn.Linear(in_features, hidden, bias=False)
         self.query = nn.Linear(in_features, hidden, bias=False)
-        self.norm = nn.RMSNorm(hidden)
+        self.norm = nn.RMSNorm(hidden, eps=1e-6)   # flax.linen.RMSNorm's default epsilon
         self.output_projection = nn.Linear(hidden, features)
 
     def _heads(self, t):
@@ -298,7 +298,7 @@ class DeltaNetCell(MemoroidCellBase):
         self.key = nn.Linear(in_features, hidden, bias=False)
         self.value = nn.Linear(in_features, hidden, bias=False)
         self.gate = nn.Linear(in_features, 2 * num_heads)   # -> (beta logits, decay logits)
-        self.norm = nn.RMSNorm(hidden)
+        self.norm = nn.RMSNorm(hidden, eps=1e-6)   # flax.linen.RMSNorm's default epsilon
         self.output_projection = nn.Linear(hidden, features)
 
     def _heads(self, t):
@@ -514,7 +514,7 @@ class MambaCell(MemoroidCellBase):
         self.dt = nn.Linear(fin, num_heads, bias=False)
         channels = hidden + 2 * sproj
         self.conv = nn.Conv1d(channels, channels, conv_dim, groups=channels, padding=conv_dim - 1)
-        self.norm = nn.RMSNorm(hidden)
+        self.norm = nn.RMSNorm(hidden, eps=1e-6)   # flax.linen.RMSNorm's default epsilon
         self.output_projection = nn.Linear(hidden, features)
 
     def _project(self, x):

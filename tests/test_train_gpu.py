@@ -113,7 +113,7 @@ def _cpu_restatement(model, obs, done, target):
         b_logit, a_logit = lin(y, c + ".gate").chunk(2, -1)
         o, _ = mo.gdelta_seq(q, k, hv(lin(y, c + ".value")), torch.exp(-F.softplus(a_logit)), torch.sigmoid(b_logit),
                              torch.zeros(B, H, hd, hd), done.float())
-        o = F.rms_norm(o.reshape(B, T, -1), (H * hd,), P[c + ".norm.weight"], torch.finfo(torch.bfloat16).eps if cell.norm.eps is None else cell.norm.eps)   # nn.RMSNorm's default eps is its input dtype's
+        o = F.rms_norm(o.reshape(B, T, -1), (H * hd,), P[c + ".norm.weight"], cell.norm.eps)
         h = h + torch.sigmoid(lin(h, pre + ".gate")) * lin(o, c + ".output_projection")
         pre = f"torso.blocks.{i + 1}"
         y = F.layer_norm(h, h.shape[-1:], P[pre + ".module.norm.weight"], P[pre + ".module.norm.bias"])
