@@ -321,6 +321,33 @@ int mxk_adam_bf16_master(void* params, float* master, const void* grads, float* 
                          float lr, float beta1, float beta2, float eps, int step, float grad_scale,
                          mxk_stream_t stream);
 
+/* ---------------------------------------------------------------------------
+ * Row-wise glue of the blocks around a mixer, each fused into one bandwidth-bound pass
+ * (bf16 in / out, fp32 arithmetic); used by the training-step harness.
+ *
+ * LayerNorm (PreNorm, blocks/normalization.py:10-35) and RMSNorm (the norm in front of the
+ * cells' output projection, linear_attention.py:114): x, y (rows, D) bf16 with D a multiple of
+ * 256 and at most 1024; gamma (and beta for LayerNorm) (D) bf16; mean / rstd (rows) fp32 out
+ * (mean unused when rms != 0).  Backward: dx (rows, D) bf16, dgamma / dbeta (D) fp32, reduced over
+ * the rows in a fixed order through `workspace` (mxk_norm_bwd_workspace_bytes).
+ * Gated residual (blocks/residual.py:53-59): y = x + sigmoid(g) * o over n bf16 elements
+ * (n % 8 == 0); backward gives dg and do (dx = dy).
+ * Per-head L2 normalisation of q / k for the delta-rule cell: `vectors` head vectors of
+ * head_dim (64 or 128) bf16 elements, y = x / max(|x|, eps); with dy != NULL the same call
+ * returns dx instead.
+ * ------------------------------------------------------------------------- */
+size_t mxk_norm_bwd_workspace_bytes(long long rows, int D);
+int mxk_norm_bf16_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                      long long rows, int D, float eps, int rms, mxk_stream_t stream);
+int mxk_norm_bf16_bwd(const void* x, const void* gamma, const float* mean, const float* rstd, const void* dy, void* dx,
+                      float* dgamma, float* dbeta, void* workspace, size_t workspace_bytes, long long rows, int D, int rms,
+                      mxk_stream_t stream);
+int mxk_gated_residual_bf16_fwd(const void* x, const void* g, const void* o, void* y, long long n, mxk_stream_t stream);
+int mxk_gated_residual_bf16_bwd(const void* dy, const void* g, const void* o, void* dg, void* d_o, long long n,
+                                mxk_stream_t stream);
+int mxk_l2norm_heads_bf16(const void* x, const void* dy, void* out, long long vectors, int head_dim, float eps,
+                          mxk_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

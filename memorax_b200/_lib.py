@@ -45,6 +45,12 @@ SIGNATURES = {
     "mxk_gdelta_workspace_bytes": (_z, [_i, _i, _i, _i]),
     "mxk_gdelta_bf16_fwd": (_i, [_p] * 11 + [_z, _p, _i, _i, _i, _i, _p]),
     "mxk_gdelta_bf16_bwd": (_i, [_p] * 17 + [_i, _i, _i, _i, _p]),
+    "mxk_norm_bwd_workspace_bytes": (_z, [ctypes.c_longlong, _i]),
+    "mxk_norm_bf16_fwd": (_i, [_p, _p, _p, _p, _p, _p, ctypes.c_longlong, _i, _f, _i, _p]),
+    "mxk_norm_bf16_bwd": (_i, [_p] * 9 + [_z, ctypes.c_longlong, _i, _i, _p]),
+    "mxk_gated_residual_bf16_fwd": (_i, [_p, _p, _p, _p, ctypes.c_longlong, _p]),
+    "mxk_gated_residual_bf16_bwd": (_i, [_p, _p, _p, _p, _p, ctypes.c_longlong, _p]),
+    "mxk_l2norm_heads_bf16": (_i, [_p, _p, _p, ctypes.c_longlong, _i, _f, _p]),
     "mxk_adam_bf16": (_i, [_p, _p, _p, _p, ctypes.c_longlong, _f, _f, _f, _f, _i, _f, _p]),
     "mxk_adam_bf16_master": (_i, [_p, _p, _p, _p, _p, ctypes.c_longlong, _f, _f, _f, _f, _i, _f, _p]),
 }

@@ -21,7 +21,8 @@ class PreNorm(nn.Module):
         self.module, self.norm = module, nn.LayerNorm(features)
 
     def forward(self, inputs, done=None, initial_carry=None):
-        return self.module(self.norm(inputs), done, initial_carry)
+        normed = ops.layer_norm(inputs, self.norm.weight, self.norm.bias, self.norm.eps)
+        return self.module(normed, done, initial_carry)
 
 
 class GatedResidual(nn.Module):
@@ -31,7 +32,7 @@ class GatedResidual(nn.Module):
 
     def forward(self, inputs, done=None, initial_carry=None):
         carry, out = self.module(inputs, done, initial_carry)
-        return carry, inputs + torch.sigmoid(self.gate(inputs)) * out
+        return carry, ops.gated_residual(inputs, self.gate(inputs), out)
 
 
 class FFN(nn.Module):

@@ -1,0 +1,346 @@
+// Row-wise glue around the mixers, fused into single bandwidth-bound passes (bf16 in / out, fp32 math):
+//   - LayerNorm / RMSNorm forward and backward (PreNorm's LayerNorm, blocks/normalization.py:10-35; the
+//     RMSNorm in front of the cells' output projection, linear_attention.py:114),
+//   - the gated residual y = x + sigmoid(g) * o and its backward (blocks/residual.py:53-59),
+//   - per-head L2 normalisation of q / k and its backward (the delta-rule cell's key / query normalisation).
+// One warp owns one row of D <= 1024 elements (D a multiple of 256): each lane holds D / 32 of them as 16-byte
+// vectors, statistics are warp reductions, nothing goes through shared memory.  The (D,) parameter gradients
+// are accumulated per warp in registers over a grid-stride loop of rows, combined per block in shared memory
+// and written as one partial row per block; a second kernel adds the blocks in index order (no atomics:
+// bit-reproducible).
+#include <cuda_bf16.h>
+
+#include "mxk_common.cuh"
+#include "umma.cuh"
+
+namespace mxk {
+namespace {
+
+constexpr int kRowWarps = 8;   // warps (rows in flight) per block
+
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+  return x;
+}
+
+// V = D / 256 16-byte vectors per lane; lane l owns elements [v * 256 + l * 8, + 8).
+template <int V>
+__device__ __forceinline__ void load_row(const __nv_bfloat16* row, int lane, float (*x)[8]) {
+#pragma unroll
+  for (int v = 0; v < V; ++v) umma::unpack8_bf16(*reinterpret_cast<const uint4*>(row + v * 256 + lane * 8), x[v]);
+}
+template <int V>
+__device__ __forceinline__ void store_row(__nv_bfloat16* row, int lane, const float (*y)[8]) {
+#pragma unroll
+  for (int v = 0; v < V; ++v) *reinterpret_cast<uint4*>(row + v * 256 + lane * 8) = umma::pack8_bf16(y[v]);
+}
+
+template <int V, bool RMS>
+__global__ void __launch_bounds__(kRowWarps * 32)
+norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
+                const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ y, float* __restrict__ mean,
+                float* __restrict__ rstd, long long rows, float eps) {
+  constexpr int D = V * 256;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float g[V][8], b[V][8];
+  load_row<V>(gamma, lane, g);
+  if (!RMS && beta) load_row<V>(beta, lane, b);
+  for (long long r = static_cast<long long>(blockIdx.x) * kRowWarps + warp; r < rows; r += static_cast<long long>(gridDim.x) * kRowWarps) {
+    float xv[V][8];
+    load_row<V>(x + r * D, lane, xv);
+    float s = 0.f;
+    if (!RMS) {
+#pragma unroll
+      for (int v = 0; v < V; ++v)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s += xv[v][e];
+      s = warp_sum(s) * (1.f / D);
+    }
+    float q = 0.f;
+#pragma unroll
+    for (int v = 0; v < V; ++v)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { const float c = xv[v][e] - s; q = fmaf(c, c, q); }
+    const float rs = rsqrtf(warp_sum(q) * (1.f / D) + eps);
+#pragma unroll
+    for (int v = 0; v < V; ++v)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float h = (xv[v][e] - s) * rs * g[v][e];
+        xv[v][e] = (!RMS && beta) ? h + b[v][e] : h;
+      }
+    store_row<V>(y + r * D, lane, xv);
+    if (lane == 0) {
+      if (mean) mean[r] = s;
+      rstd[r] = rs;
+    }
+  }
+}
+
+// dx per row; per-block partial sums of dgamma (and dbeta) into part[block][2][D].
+template <int V, bool RMS>
+__global__ void __launch_bounds__(kRowWarps * 32)
+norm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean,
+                const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dx,
+                float* __restrict__ part, long long rows) {
+  constexpr int D = V * 256;
+  __shared__ float red[kRowWarps][D];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float g[V][8], dg[V][8], db[V][8];
+  load_row<V>(gamma, lane, g);
+#pragma unroll
+  for (int v = 0; v < V; ++v)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dg[v][e] = db[v][e] = 0.f;
+  for (long long r = static_cast<long long>(blockIdx.x) * kRowWarps + warp; r < rows; r += static_cast<long long>(gridDim.x) * kRowWarps) {
+    float xv[V][8], dv[V][8];
+    load_row<V>(x + r * D, lane, xv);
+    load_row<V>(dy + r * D, lane, dv);
+    const float mu = RMS ? 0.f : mean[r], rs = rstd[r];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int v = 0; v < V; ++v)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float xh = (xv[v][e] - mu) * rs, gy = dv[v][e] * g[v][e];
+        dg[v][e] = fmaf(dv[v][e], xh, dg[v][e]);
+        db[v][e] += dv[v][e];
+        xv[v][e] = xh;
+        dv[v][e] = gy;
+        s1 += gy;
+        s2 = fmaf(gy, xh, s2);
+      }
+    s1 = RMS ? 0.f : warp_sum(s1) * (1.f / D);
+    s2 = warp_sum(s2) * (1.f / D);
+#pragma unroll
+    for (int v = 0; v < V; ++v)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) xv[v][e] = rs * (dv[v][e] - s1 - xv[v][e] * s2);
+    store_row<V>(dx + r * D, lane, xv);
+  }
+  // block partials: the eight warps' sums added in warp order
+  for (int pass = 0; pass < (RMS ? 1 : 2); ++pass) {
+    __syncthreads();
+#pragma unroll
+    for (int v = 0; v < V; ++v)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) red[warp][v * 256 + lane * 8 + e] = pass == 0 ? dg[v][e] : db[v][e];
+    __syncthreads();
+    for (int c = threadIdx.x; c < D; c += kRowWarps * 32) {
+      float s = red[0][c];
+#pragma unroll
+      for (int w = 1; w < kRowWarps; ++w) s += red[w][c];
+      part[(static_cast<size_t>(blockIdx.x) * 2 + pass) * D + c] = s;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+norm_bwd_reduce_kernel(const float* __restrict__ part, float* __restrict__ dgamma, float* __restrict__ dbeta, int blocks, int D) {
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= D) return;
+  float sg = 0.f, sb = 0.f;
+  for (int b = 0; b < blocks; ++b) {
+    sg += part[(static_cast<size_t>(b) * 2) * D + c];
+    if (dbeta) sb += part[(static_cast<size_t>(b) * 2 + 1) * D + c];
+  }
+  dgamma[c] = sg;
+  if (dbeta) dbeta[c] = sb;
+}
+
+// y = x + sigmoid(g) * o
+__global__ void __launch_bounds__(256)
+gated_residual_fwd_kernel(const uint4* __restrict__ x, const uint4* __restrict__ g, const uint4* __restrict__ o,
+                          uint4* __restrict__ y, long long n8) {
+  const long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= n8) return;
+  float xf[8], gf[8], of[8];
+  umma::unpack8_bf16(x[i], xf);
+  umma::unpack8_bf16(g[i], gf);
+  umma::unpack8_bf16(o[i], of);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) xf[e] = fmaf(1.f / (1.f + __expf(-gf[e])), of[e], xf[e]);
+  y[i] = umma::pack8_bf16(xf);
+}
+// do = dy * sigmoid(g), dg = dy * o * sigmoid(g) (1 - sigmoid(g)); dx = dy needs no kernel
+__global__ void __launch_bounds__(256)
+gated_residual_bwd_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ g, const uint4* __restrict__ o,
+                          uint4* __restrict__ dg, uint4* __restrict__ d_o, long long n8) {
+  const long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= n8) return;
+  float yf[8], gf[8], of[8];
+  umma::unpack8_bf16(dy[i], yf);
+  umma::unpack8_bf16(g[i], gf);
+  umma::unpack8_bf16(o[i], of);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float s = 1.f / (1.f + __expf(-gf[e]));
+    gf[e] = yf[e] * of[e] * s * (1.f - s);
+    of[e] = yf[e] * s;
+  }
+  dg[i] = umma::pack8_bf16(gf);
+  d_o[i] = umma::pack8_bf16(of);
+}
+
+// Per-head L2 normalisation: LPH = hd / 8 lanes hold one head vector (16 bytes each).
+template <int LPH, bool BWD>
+__global__ void __launch_bounds__(256)
+l2norm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ dy, uint4* __restrict__ out, long long nvec, float eps) {
+  const long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+  const bool in = i < nvec;
+  float xf[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, df[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (in) {
+    umma::unpack8_bf16(x[i], xf);
+    if (BWD) umma::unpack8_bf16(dy[i], df);
+  }
+  float ss = 0.f, sd = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { ss = fmaf(xf[e], xf[e], ss); sd = fmaf(xf[e], df[e], sd); }
+#pragma unroll
+  for (int off = 1; off < LPH; off <<= 1) {
+    ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    if (BWD) sd += __shfl_xor_sync(0xffffffffu, sd, off);
+  }
+  const float inv = 1.f / fmaxf(sqrtf(ss), eps);
+  if (BWD) {
+    // y = x inv;  dx = inv (dy - y (y . dy))
+    const float ydy = sd * inv;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) xf[e] = inv * (df[e] - xf[e] * inv * ydy);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) xf[e] *= inv;
+  }
+  if (in) out[i] = umma::pack8_bf16(xf);
+}
+
+int check_norm(const void* x, const void* gamma, const void* y, long long rows, int D) {
+  if (!x || !gamma || !y) return MXK_ERR_NULL;
+  if (rows <= 0 || D <= 0) return MXK_ERR_DIMS;
+  if (D % 256 != 0 || D > 1024) return MXK_ERR_UNSUPPORTED;
+  for (const void* p : {x, gamma, y})
+    if (!aligned16(p)) return MXK_ERR_ALIGN;
+  return MXK_OK;
+}
+
+int norm_blocks(long long rows) {
+  const long long want = (rows + kRowWarps - 1) / kRowWarps;
+  return static_cast<int>(want < 4LL * kNumSMs ? want : 4LL * kNumSMs);
+}
+
+}  // namespace
+}  // namespace mxk
+
+extern "C" {
+
+size_t mxk_norm_bwd_workspace_bytes(long long rows, int D) {
+  if (rows <= 0 || D <= 0) return 0;
+  return static_cast<size_t>(mxk::norm_blocks(rows)) * 2 * D * sizeof(float);
+}
+
+int mxk_norm_bf16_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                      long long rows, int D, float eps, int rms, mxk_stream_t stream) {
+  using namespace mxk;
+  if (int st = check_norm(x, gamma, y, rows, D)) return st;
+  if (!rstd || (!rms && !mean)) return MXK_ERR_NULL;
+  const auto* xp = static_cast<const __nv_bfloat16*>(x);
+  const auto* gp = static_cast<const __nv_bfloat16*>(gamma);
+  const auto* bp = static_cast<const __nv_bfloat16*>(beta);
+  auto* yp = static_cast<__nv_bfloat16*>(y);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int blocks = norm_blocks(rows), threads = kRowWarps * 32;
+#define MXK_NORM_FWD(V)                                                                                        \
+  if (rms) norm_fwd_kernel<V, true><<<blocks, threads, 0, s>>>(xp, gp, nullptr, yp, nullptr, rstd, rows, eps); \
+  else norm_fwd_kernel<V, false><<<blocks, threads, 0, s>>>(xp, gp, bp, yp, mean, rstd, rows, eps);
+  switch (D / 256) {
+    case 1: MXK_NORM_FWD(1) break;
+    case 2: MXK_NORM_FWD(2) break;
+    case 3: MXK_NORM_FWD(3) break;
+    default: MXK_NORM_FWD(4) break;
+  }
+#undef MXK_NORM_FWD
+  return launch_status();
+}
+
+int mxk_norm_bf16_bwd(const void* x, const void* gamma, const float* mean, const float* rstd, const void* dy, void* dx,
+                      float* dgamma, float* dbeta, void* workspace, size_t workspace_bytes, long long rows, int D, int rms,
+                      mxk_stream_t stream) {
+  using namespace mxk;
+  if (int st = check_norm(x, gamma, dx, rows, D)) return st;
+  if (!rstd || !dy || !dgamma || (!rms && (!mean || !dbeta))) return MXK_ERR_NULL;
+  if (!workspace || workspace_bytes < mxk_norm_bwd_workspace_bytes(rows, D)) return MXK_ERR_WORKSPACE;
+  if (!aligned16(dy) || (reinterpret_cast<uintptr_t>(workspace) & 3u)) return MXK_ERR_ALIGN;
+  const auto* xp = static_cast<const __nv_bfloat16*>(x);
+  const auto* gp = static_cast<const __nv_bfloat16*>(gamma);
+  const auto* dyp = static_cast<const __nv_bfloat16*>(dy);
+  auto* dxp = static_cast<__nv_bfloat16*>(dx);
+  float* part = static_cast<float*>(workspace);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int blocks = norm_blocks(rows), threads = kRowWarps * 32;
+#define MXK_NORM_BWD(V)                                                                                  \
+  if (rms) norm_bwd_kernel<V, true><<<blocks, threads, 0, s>>>(xp, gp, nullptr, rstd, dyp, dxp, part, rows); \
+  else norm_bwd_kernel<V, false><<<blocks, threads, 0, s>>>(xp, gp, mean, rstd, dyp, dxp, part, rows);
+  switch (D / 256) {
+    case 1: MXK_NORM_BWD(1) break;
+    case 2: MXK_NORM_BWD(2) break;
+    case 3: MXK_NORM_BWD(3) break;
+    default: MXK_NORM_BWD(4) break;
+  }
+#undef MXK_NORM_BWD
+  if (int st = launch_status()) return st;
+  norm_bwd_reduce_kernel<<<(D + 255) / 256, 256, 0, s>>>(part, dgamma, rms ? nullptr : dbeta, blocks, D);
+  return launch_status();
+}
+
+int mxk_gated_residual_bf16_fwd(const void* x, const void* g, const void* o, void* y, long long n, mxk_stream_t stream) {
+  using namespace mxk;
+  if (!x || !g || !o || !y) return MXK_ERR_NULL;
+  if (n <= 0 || n % 8) return MXK_ERR_DIMS;
+  for (const void* p : {x, g, o, (const void*)y})
+    if (!aligned16(p)) return MXK_ERR_ALIGN;
+  const long long n8 = n / 8;
+  gated_residual_fwd_kernel<<<static_cast<unsigned>((n8 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), static_cast<const uint4*>(g), static_cast<const uint4*>(o), static_cast<uint4*>(y), n8);
+  return launch_status();
+}
+
+int mxk_gated_residual_bf16_bwd(const void* dy, const void* g, const void* o, void* dg, void* d_o, long long n,
+                                mxk_stream_t stream) {
+  using namespace mxk;
+  if (!dy || !g || !o || !dg || !d_o) return MXK_ERR_NULL;
+  if (n <= 0 || n % 8) return MXK_ERR_DIMS;
+  for (const void* p : {dy, g, o, (const void*)dg, (const void*)d_o})
+    if (!aligned16(p)) return MXK_ERR_ALIGN;
+  const long long n8 = n / 8;
+  gated_residual_bwd_kernel<<<static_cast<unsigned>((n8 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(dy), static_cast<const uint4*>(g), static_cast<const uint4*>(o), static_cast<uint4*>(dg),
+      static_cast<uint4*>(d_o), n8);
+  return launch_status();
+}
+
+int mxk_l2norm_heads_bf16(const void* x, const void* dy, void* out, long long vectors, int head_dim, float eps,
+                          mxk_stream_t stream) {
+  using namespace mxk;
+  if (!x || !out) return MXK_ERR_NULL;
+  if (vectors <= 0) return MXK_ERR_DIMS;
+  if (head_dim != 64 && head_dim != 128) return MXK_ERR_UNSUPPORTED;
+  for (const void* p : {x, dy, (const void*)out})
+    if (p && !aligned16(p)) return MXK_ERR_ALIGN;
+  const long long nvec = vectors * (head_dim / 8);
+  const unsigned blocks = static_cast<unsigned>((nvec + 255) / 256);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const uint4* xp = static_cast<const uint4*>(x);
+  const uint4* dp = static_cast<const uint4*>(dy);
+  uint4* op = static_cast<uint4*>(out);
+  if (head_dim == 64) {
+    if (dy) l2norm_kernel<8, true><<<blocks, 256, 0, s>>>(xp, dp, op, nvec, eps);
+    else l2norm_kernel<8, false><<<blocks, 256, 0, s>>>(xp, nullptr, op, nvec, eps);
+  } else {
+    if (dy) l2norm_kernel<16, true><<<blocks, 256, 0, s>>>(xp, dp, op, nvec, eps);
+    else l2norm_kernel<16, false><<<blocks, 256, 0, s>>>(xp, nullptr, op, nvec, eps);
+  }
+  return launch_status();
+}
+
+}  // extern "C"

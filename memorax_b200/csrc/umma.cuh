@@ -104,7 +104,8 @@ __device__ __forceinline__ bool elect_one() {
 // with warp-uniform arguments; only the `leader` lane (elect_one()) issues.  Keeping the
 // descriptor arithmetic warp-uniform lets it live in uniform registers, and with the K loop
 // unrolled the slices differ by immediates: measured 27-33 cycles per M = 64 instruction
-// against 78 when a single divergent thread builds and issues them.  Only the
+// against 78 when a single divergent thread builds and issues them (and that cost is per instruction:
+// issuing independent accumulators round-robin instead of one product after the other measured the same).  Only the
 // start-address field (low 14 bits, 16-byte units) changes from slice to slice.
 template <int KSTEPS>
 __device__ __forceinline__ void gemm(uint32_t tmem_d, const Operand& a, const Operand& b, uint32_t idesc,

@@ -306,7 +306,7 @@ class DeltaNetCell(MemoroidCellBase):
 
     def forward(self, x, **kwargs):
         """-> factored elements (k, v, alpha, beta); k is L2-normalised per head."""
-        k = torch.nn.functional.normalize(self._heads(self.key(x)).float(), dim=-1)
+        k = ops.l2norm_heads(self.key(x), self.head_dim)
         v = self._heads(self.value(x))
         b_logit, a_logit = self.gate(x).float().chunk(2, dim=-1)
         return k, v, torch.exp(-torch.nn.functional.softplus(a_logit)), torch.sigmoid(b_logit)
@@ -325,12 +325,12 @@ class DeltaNetCell(MemoroidCellBase):
 
     def scan(self, z, initial_carry, done, inputs):
         k, v, alpha, beta = z
-        q = torch.nn.functional.normalize(self._heads(self.query(inputs)).float(), dim=-1)
+        q = ops.l2norm_heads(self.query(inputs), self.head_dim)
         (s0,) = _squeeze_carry(initial_carry, 1)
         bf = torch.bfloat16
         o, s_last = ops.GatedDelta.apply(q.to(bf), k.to(bf), v.to(bf), alpha.contiguous(), beta.contiguous(), s0, done)
         o = o.reshape(*o.shape[:2], -1).to(inputs.dtype)
-        return (s_last[:, None],), self.output_projection(self.norm(o))
+        return (s_last[:, None],), self.output_projection(ops.rms_norm(o, self.norm.weight, self.norm.eps))
 
 
 # -------------------------------------------------------------------- mLSTM

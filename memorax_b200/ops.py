@@ -477,6 +477,113 @@ class GatedDelta(torch.autograd.Function):
                 ds0 if ctx.has_state else None, None)
 
 
+# ------------------------------------------------------ fused row-wise glue
+def _glue_ok(x, dim):
+    return x.is_cuda and x.dtype == torch.bfloat16 and dim % 256 == 0 and dim <= 1024
+
+
+class FusedNorm(torch.autograd.Function):
+    """LayerNorm (``rms=False``) or RMSNorm over the last dimension, bf16, one kernel per direction."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps, rms):
+        x = x.contiguous()
+        dim = x.shape[-1]
+        rows = x.numel() // dim
+        y = torch.empty_like(x)
+        mean = None if rms else torch.empty(rows, dtype=torch.float32, device=x.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        _lib.call("mxk_norm_bf16_fwd", _ptr(x), _ptr(weight), _ptr(bias), _ptr(y), _ptr(mean), _ptr(rstd), rows, dim,
+                  float(eps), int(rms), _stream())
+        ctx.save_for_backward(x, weight, mean, rstd)
+        ctx.rms, ctx.has_bias = rms, bias is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight, mean, rstd = ctx.saved_tensors
+        dim = x.shape[-1]
+        rows = x.numel() // dim
+        dy = dy.contiguous()
+        dx = torch.empty_like(x)
+        dgamma = torch.empty(dim, dtype=torch.float32, device=x.device)
+        dbeta = None if ctx.rms else torch.empty(dim, dtype=torch.float32, device=x.device)
+        ws_bytes = _lib.lib.mxk_norm_bwd_workspace_bytes(rows, dim)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
+        _lib.call("mxk_norm_bf16_bwd", _ptr(x), _ptr(weight), _ptr(mean), _ptr(rstd), _ptr(dy), _ptr(dx), _ptr(dgamma),
+                  _ptr(dbeta), _ptr(ws), ws_bytes, rows, dim, int(ctx.rms), _stream())
+        return (dx, dgamma.to(weight.dtype), dbeta.to(weight.dtype) if (dbeta is not None and ctx.has_bias) else None,
+                None, None)
+
+
+def layer_norm(x, weight, bias, eps=1e-5):
+    """nn.LayerNorm over the last dimension; the fused kernels for bf16 CUDA rows of 256..1024 elements."""
+    if _glue_ok(x, x.shape[-1]) and weight.dtype == torch.bfloat16 and bias is not None:
+        return FusedNorm.apply(x, weight, bias, eps, False)
+    return torch.nn.functional.layer_norm(x, x.shape[-1:], weight, bias, eps)
+
+
+def rms_norm(x, weight, eps=1e-6):
+    if _glue_ok(x, x.shape[-1]) and weight.dtype == torch.bfloat16:
+        return FusedNorm.apply(x, weight, None, eps, True)
+    return torch.nn.functional.rms_norm(x, x.shape[-1:], weight, eps)
+
+
+class GatedResidual(torch.autograd.Function):
+    """y = x + sigmoid(g) * o (blocks/residual.py:53-59), bf16, one kernel per direction."""
+
+    @staticmethod
+    def forward(ctx, x, g, o):
+        x, g, o = x.contiguous(), g.contiguous(), o.contiguous()
+        y = torch.empty_like(x)
+        _lib.call("mxk_gated_residual_bf16_fwd", _ptr(x), _ptr(g), _ptr(o), _ptr(y), x.numel(), _stream())
+        ctx.save_for_backward(g, o)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        g, o = ctx.saved_tensors
+        dy = dy.contiguous()
+        dg, d_o = torch.empty_like(g), torch.empty_like(o)
+        _lib.call("mxk_gated_residual_bf16_bwd", _ptr(dy), _ptr(g), _ptr(o), _ptr(dg), _ptr(d_o), dy.numel(), _stream())
+        return dy, dg, d_o
+
+
+def gated_residual(x, g, o):
+    if x.is_cuda and x.dtype == g.dtype == o.dtype == torch.bfloat16 and x.numel() % 8 == 0 and x.shape == g.shape == o.shape:
+        return GatedResidual.apply(x, g, o)
+    return x + torch.sigmoid(g) * o
+
+
+class L2NormHeads(torch.autograd.Function):
+    """x (..., H * head_dim) bf16 -> each head vector divided by max(its norm, eps), bf16."""
+
+    @staticmethod
+    def forward(ctx, x, head_dim, eps):
+        x = x.contiguous()
+        y = torch.empty_like(x)
+        _lib.call("mxk_l2norm_heads_bf16", _ptr(x), None, _ptr(y), x.numel() // head_dim, head_dim, float(eps), _stream())
+        ctx.save_for_backward(x)
+        ctx.head_dim, ctx.eps = head_dim, eps
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        dx = torch.empty_like(x)
+        _lib.call("mxk_l2norm_heads_bf16", _ptr(x), _ptr(dy.contiguous()), _ptr(dx), x.numel() // ctx.head_dim, ctx.head_dim,
+                  float(ctx.eps), _stream())
+        return dx, None, None
+
+
+def l2norm_heads(x, head_dim, eps=1e-12):
+    """(..., H * head_dim) -> (..., H, head_dim) with every head vector L2-normalised."""
+    heads = x.shape[-1] // head_dim
+    if x.is_cuda and x.dtype == torch.bfloat16 and head_dim in (64, 128):
+        return L2NormHeads.apply(x, head_dim, eps).view(*x.shape[:-1], heads, head_dim)
+    return torch.nn.functional.normalize(x.view(*x.shape[:-1], heads, head_dim).float(), dim=-1, eps=eps)
+
+
 # ------------------------------------------------------------------- Adam
 def adam_step(params, grads, m, v, step, lr=3e-4, betas=(0.9, 0.999), eps=1e-8, grad_scale=1.0, master=None):
     """In-place fused Adam on flat buffers (bf16 params/grads, fp32 moments).  With ``master`` (fp32, same
