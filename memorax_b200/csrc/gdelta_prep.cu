@@ -5,13 +5,15 @@
 // One CTA (128 threads) per (batch, head, 64-token chunk).  With the chunk quantities of
 // gdelta_common.cuh (L = strict_tril(G o K K^T), A = I + diag(beta) L):
 //   K K^T  on the tensor core (two N = 32 halves, so that each thread owns 32 keys of one token row),
-//   -beta L in fp32 in shared memory, transposed,
-//   A^-1   by forward substitution on the identity, one column per thread in fp32 registers
-//          (columns 32..63 start at row 32: the upper-left of a unit lower-triangular inverse is zero),
+//   N = -beta L in fp32 in shared memory, transposed,
+//   A^-1 = (I - N)^-1 in fp32 by block recursion, every step using all four warps and no step longer than a
+//          16-row chain: the four 16 x 16 diagonal blocks by forward substitution (one column per thread),
+//          then  X_pq = X_pp N_pq X_qq  for the two 16 x 16 blocks under the diagonal of each 32 x 32 half,
+//          then the same formula for the lower-left 32 x 32 block (the inverse of a block lower-triangular
+//          matrix [[A11, 0], [A21, A22]] has -A22^-1 A21 A11^-1 there, and A21 = -N21).  A column-per-thread
+//          substitution over all 64 rows would leave three warps idle behind a 63-step dependent chain.
 //   T' = A^-1 diag(beta) leaves as bf16 in tensor-core operand order, [j/8][t][8] with t the row and
 //          j the column.
-// Six CTAs per SM (34 KiB of shared memory, 80 registers) overlap one chunk's copy and substitution latency
-// with the others'.
 // The forward kernel then forms U = T' (V - diag(g) K S_in^T) and the backward kernel dR = T'^T dU as
 // plain tensor-core products.
 #include "gdelta_common.cuh"
@@ -33,20 +35,32 @@ struct PrepParams {
   CUtensorMap map_k;   // 64-token tiles as SW tiles (two 64-column blocks)
 };
 
+constexpr int kXS = kC + 1;   // row stride of the fp32 inverse: odd, so that a column walk is conflict-free
+
 struct PrepSmem {
-  uint4 k[kPanD * kC];      // K, SW tiles (two 64-column blocks); once K K^T is done, its first 8 KiB stage
-                            // the bf16 T', [j/8][t][8]
-  float lt[kC * kC];        // lt[j][t] = -beta_t L_tj
+  // K, SW tiles (two 64-column blocks); once K K^T is done the same 16 KiB hold, in turn, the intermediate
+  // products M = N_pq X_qq (fp32, [row][32]) and the staged bf16 T', [j/8][t][8]
+  uint4 k[kPanD * kC];
+  float lt[kC * kC];        // lt[j][t] = N[t][j] = -beta_t L_tj
+  float x[kC * kXS];        // A^-1, row-major with stride kXS
   ChunkDecay cd;
   uint64_t bar_load, bar_mma;
   uint32_t tmem;
 };
-static_assert(sizeof(PrepSmem) <= 36 * 1024, "six CTAs per SM");
+static_assert(sizeof(PrepSmem) <= 56 * 1024, "four CTAs per SM");
 
+#ifdef MXK_TIMING
+}  // namespace
+__device__ unsigned long long g_gdp_phase_cycles[16];
+namespace {
+#define MXK_TP(i) do { if (tid == 0 && (blockIdx.x % 37) == 0) { const long long now_ = clock64(); atomicAdd(&g_gdp_phase_cycles[i], (unsigned long long)(now_ - t_prev_)); t_prev_ = now_; } } while (0)
+#else
+#define MXK_TP(i) do {} while (0)
+#endif
 constexpr uint32_t kPrepTmemCols = 32;
 constexpr uint32_t kUpper = 16u << 16;
 
-__global__ void __launch_bounds__(kThreads, 6) gdelta_prep_kernel(const __grid_constant__ PrepParams p) {
+__global__ void __launch_bounds__(kThreads, 4) gdelta_prep_kernel(const __grid_constant__ PrepParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   PrepSmem& sm = *reinterpret_cast<PrepSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -56,6 +70,9 @@ __global__ void __launch_bounds__(kThreads, 6) gdelta_prep_kernel(const __grid_c
   const bool upper = lane >= 16;
   const int row = warp * 16 + (lane & 15);   // token row owned in the M = 64 accumulator
 
+#ifdef MXK_TIMING
+  long long t_prev_ = clock64();
+#endif
   if (tid == 0) {
     mbar_init(&sm.bar_load, 1);
     mbar_init(&sm.bar_mma, 1);
@@ -68,6 +85,7 @@ __global__ void __launch_bounds__(kThreads, 6) gdelta_prep_kernel(const __grid_c
   const uint32_t tmem = sm.tmem;
   const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
   bool timed_out = false;
+  MXK_TP(0);
 
   if (tid == 0) {
     tma::expect_bytes(&sm.bar_load, kPanD * kC * 16);
@@ -78,8 +96,10 @@ __global__ void __launch_bounds__(kThreads, 6) gdelta_prep_kernel(const __grid_c
   const uint64_t dm = linattn::done_mask_from_flags(linattn::load_done_flags(drow, t0, p.T, lane));
   const float2 ab = fetch_chunk_decay(p.alpha, p.beta, static_cast<size_t>(b) * p.T, p.H, h, t0, p.T, tid);
   chunk_decay_from_regs(sm.cd, ab, dm, tid);
+  MXK_TP(1);
 
   mbar_wait_flag(&sm.bar_load, 0, timed_out);
+  MXK_TP(2);
   if (warp == 0) {
     const bool leader = elect_one();
     constexpr uint32_t kBlk = kSwBlockVecs * 16;
@@ -93,6 +113,7 @@ __global__ void __launch_bounds__(kThreads, 6) gdelta_prep_kernel(const __grid_c
   }
   mbar_wait_flag(&sm.bar_mma, 0, timed_out);
   fence_after_sync();
+  MXK_TP(3);
 
   // -beta L, transposed: every thread owns 32 keys of its token row
   {
@@ -110,26 +131,108 @@ __global__ void __launch_bounds__(kThreads, 6) gdelta_prep_kernel(const __grid_c
   }
   __syncthreads();
 
-  // A^-1 column by column: thread c < 64 solves A x = e_c
-  if (warp < 2) {
-    __align__(8) float r[kC];
+  MXK_TP(4);
+  // ---- A^-1 = (I - N)^-1 by block recursion (N[t][j] = lt[j * kC + t]) ----
+  float* const xm = sm.x;
+  float* const mm = reinterpret_cast<float*>(sm.k);   // M, [row][32] (K is dead: K K^T has completed)
+  for (int i = tid; i < kC * kXS; i += kThreads) xm[i] = 0.f;
+  __syncthreads();
+  // (1) the four 16 x 16 diagonal blocks: thread (p, c) solves column c of block p
+  if (tid < kC) {
+    const int p0 = (tid >> 4) * 16, c = tid & 15;
+    float xc[16];
 #pragma unroll
-    for (int t = 0; t < kC; ++t) r[t] = (t == tid) ? 1.f : 0.f;
-    if (warp == 0) forward_substitute_range<0, kC - 1, kC>(reinterpret_cast<float2*>(r), sm.lt);
-    else forward_substitute_range<32, kC - 1, kC>(reinterpret_cast<float2*>(r), sm.lt);
-    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(sm.k);
-    const int base = (tid >> 3) * kC * 8 + (tid & 7);   // element (t, j = tid) at [j/8][t][j%8]
-    const float beta_j = sm.cd.beta[tid];                // column j of A^-1 times beta_j
+    for (int t = 0; t < 16; ++t) xc[t] = (t == c) ? 1.f : 0.f;
 #pragma unroll
-    for (int t = 0; t < kC; ++t) out[base + t * 8] = __float2bfloat16(r[t] * beta_j);
+    for (int jj = 0; jj < 15; ++jj) {
+      const float uj = xc[jj];
+#pragma unroll
+      for (int t = jj + 1; t < 16; ++t) xc[t] = fmaf(sm.lt[(p0 + jj) * kC + p0 + t], uj, xc[t]);
+    }
+#pragma unroll
+    for (int t = 0; t < 16; ++t) xm[(p0 + t) * kXS + p0 + c] = xc[t];
+  }
+  __syncthreads();
+  // (2) X_pq = X_pp (N_pq X_qq) for (p, q) = (1, 0) and (3, 2): 64 threads per pair, thread = (row r, 4 columns)
+  {
+    const int pair = tid >> 6, r = tid & 15, c0 = ((tid >> 4) & 3) * 4;
+    const int q0 = pair * 32, p0 = q0 + 16;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      const float a = sm.lt[(q0 + kk) * kC + p0 + r];          // N[p0 + r][q0 + kk]
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[e] = fmaf(a, xm[(q0 + kk) * kXS + q0 + c0 + e], acc[e]);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) mm[(pair * 16 + r) * 32 + c0 + e] = acc[e];
+    __syncthreads();
+    float out[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      const float a = xm[(p0 + r) * kXS + p0 + kk];           // X_pp[r][kk]
+#pragma unroll
+      for (int e = 0; e < 4; ++e) out[e] = fmaf(a, mm[(pair * 16 + kk) * 32 + c0 + e], out[e]);
+    }
+    __syncthreads();   // every read of mm and of the diagonal blocks is done before anything is overwritten
+#pragma unroll
+    for (int e = 0; e < 4; ++e) xm[(p0 + r) * kXS + q0 + c0 + e] = out[e];
+  }
+  __syncthreads();
+  // (3) the lower-left 32 x 32 block: X_PQ = X_PP (N_PQ X_QQ), thread = (row r of 32, 8 columns)
+  {
+    const int r = tid & 31, c0 = (tid >> 5) * 8;
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll 8
+    for (int kk = 0; kk < 32; ++kk) {
+      const float a = sm.lt[kk * kC + 32 + r];                 // N[32 + r][kk]
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = fmaf(a, xm[kk * kXS + c0 + e], acc[e]);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) mm[r * 32 + c0 + e] = acc[e];
+    __syncthreads();
+    float out[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) out[e] = 0.f;
+#pragma unroll 8
+    for (int kk = 0; kk < 32; ++kk) {
+      const float a = xm[(32 + r) * kXS + 32 + kk];            // X_PP[r][kk]
+#pragma unroll
+      for (int e = 0; e < 8; ++e) out[e] = fmaf(a, mm[kk * 32 + c0 + e], out[e]);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int e = 0; e < 8; ++e) xm[(32 + r) * kXS + c0 + e] = out[e];
+  }
+  __syncthreads();
+  MXK_TP(5);
+  // T' = A^-1 diag(beta) as bf16, [j/8][t][8]: thread (t, half) packs four groups of eight columns
+  {
+    uint4* out = sm.k;
+    const int t = tid & 63, g0 = (tid >> 6) * 4;
+#pragma unroll
+    for (int gq = 0; gq < 4; ++gq) {
+      float f[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int jcol = (g0 + gq) * 8 + e;
+        f[e] = xm[t * kXS + jcol] * sm.cd.beta[jcol];
+      }
+      out[(g0 + gq) * kC + t] = pack8_bf16(f);
+    }
   }
   fence_smem_to_async();
   __syncthreads();
+  MXK_TP(6);
   if (tid == 0) {
     tma::store_bulk(p.ainv + static_cast<size_t>(item) * kAinvVecs, sm.k, kAinvVecs * 16);
     tma::commit_group();
     tma::wait_group_all();
   }
+  MXK_TP(7);
   if (timed_out && p.status) atomicExch(p.status, 1);
   fence_before_sync();
   __syncthreads();
@@ -137,6 +240,18 @@ __global__ void __launch_bounds__(kThreads, 6) gdelta_prep_kernel(const __grid_c
 }
 
 }  // namespace
+
+#ifdef MXK_TIMING
+}  // namespace mxk
+extern "C" int mxk_debug_gdp_phase_cycles(unsigned long long* out, int reset) {
+  if (reset) {
+    unsigned long long z[16] = {};
+    return (int)cudaMemcpyToSymbol(mxk::g_gdp_phase_cycles, z, sizeof(z));
+  }
+  return (int)cudaMemcpyFromSymbol(out, mxk::g_gdp_phase_cycles, 16 * sizeof(unsigned long long));
+}
+namespace mxk {
+#endif
 
 namespace gdelta {
 

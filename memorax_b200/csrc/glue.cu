@@ -136,17 +136,30 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   }
 }
 
+// Adds the per-block partial rows in a fixed order: a block owns 32 columns, its eight thread rows each add
+// every eighth partial, then thread row 0 adds the eight sums in order.
 __global__ void __launch_bounds__(256)
 norm_bwd_reduce_kernel(const float* __restrict__ part, float* __restrict__ dgamma, float* __restrict__ dbeta, int blocks, int D) {
-  const int c = blockIdx.x * 256 + threadIdx.x;
-  if (c >= D) return;
+  __shared__ float red[2][8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
   float sg = 0.f, sb = 0.f;
-  for (int b = 0; b < blocks; ++b) {
-    sg += part[(static_cast<size_t>(b) * 2) * D + c];
-    if (dbeta) sb += part[(static_cast<size_t>(b) * 2 + 1) * D + c];
+  if (c < D) {
+    for (int b = ty; b < blocks; b += 8) {
+      sg += part[(static_cast<size_t>(b) * 2) * D + c];
+      if (dbeta) sb += part[(static_cast<size_t>(b) * 2 + 1) * D + c];
+    }
   }
-  dgamma[c] = sg;
-  if (dbeta) dbeta[c] = sb;
+  red[0][ty][tx] = sg;
+  red[1][ty][tx] = sb;
+  __syncthreads();
+  if (ty == 0 && c < D) {
+    float tg = red[0][0][tx], tb = red[1][0][tx];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) { tg += red[0][i][tx]; tb += red[1][i][tx]; }
+    dgamma[c] = tg;
+    if (dbeta) dbeta[c] = tb;
+  }
 }
 
 // y = x + sigmoid(g) * o
@@ -224,9 +237,12 @@ int check_norm(const void* x, const void* gamma, const void* y, long long rows, 
   return MXK_OK;
 }
 
-int norm_blocks(long long rows) {
+// Blocks of the backward row pass: two per SM -- enough rows per warp to amortise the partial row every
+// block writes, few enough partials for the fixed-order reduction.  The forward pass takes eight per SM.
+int norm_blocks(long long rows, int per_sm = 2) {
   const long long want = (rows + kRowWarps - 1) / kRowWarps;
-  return static_cast<int>(want < 4LL * kNumSMs ? want : 4LL * kNumSMs);
+  const long long cap = static_cast<long long>(per_sm) * kNumSMs;
+  return static_cast<int>(want < cap ? want : cap);
 }
 
 }  // namespace
@@ -249,7 +265,7 @@ int mxk_norm_bf16_fwd(const void* x, const void* gamma, const void* beta, void* 
   const auto* bp = static_cast<const __nv_bfloat16*>(beta);
   auto* yp = static_cast<__nv_bfloat16*>(y);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int blocks = norm_blocks(rows), threads = kRowWarps * 32;
+  const int blocks = norm_blocks(rows, 8), threads = kRowWarps * 32;
 #define MXK_NORM_FWD(V)                                                                                        \
   if (rms) norm_fwd_kernel<V, true><<<blocks, threads, 0, s>>>(xp, gp, nullptr, yp, nullptr, rstd, rows, eps); \
   else norm_fwd_kernel<V, false><<<blocks, threads, 0, s>>>(xp, gp, bp, yp, mean, rstd, rows, eps);
@@ -289,7 +305,7 @@ int mxk_norm_bf16_bwd(const void* x, const void* gamma, const float* mean, const
   }
 #undef MXK_NORM_BWD
   if (int st = launch_status()) return st;
-  norm_bwd_reduce_kernel<<<(D + 255) / 256, 256, 0, s>>>(part, dgamma, rms ? nullptr : dbeta, blocks, D);
+  norm_bwd_reduce_kernel<<<(D + 31) / 32, 256, 0, s>>>(part, dgamma, rms ? nullptr : dbeta, blocks, D);
   return launch_status();
 }
 
