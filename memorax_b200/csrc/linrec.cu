@@ -194,53 +194,54 @@ linrec_fwd_kernel(const float* __restrict__ a, int a_tinv, const float* __restri
   }
 }
 
-// ---------------------------------------------- forward, time-split (small B*D)
+// ------------------------------------------------------- time-split (small B*D)
 // When there are too few channels to fill the machine with one thread per
 // channel walking all of T, the time axis is split as well: a block owns
-// 32 x W channels (a warp reads 128 W contiguous bytes per step) x 16 contiguous
-// time segments.  Every thread loads its segment (<= L steps) into registers,
-// folds it into an affine map (P, Q) with h_out = P h_in + Q (a reset makes
-// P = 0), the sixteen maps of a channel are chained through shared memory, and
-// each thread replays its segment from the right incoming state.  One pass over
-// memory, T/16 sequential steps per thread.
+// 32 x W floats of a row (a warp reads 128 W contiguous bytes per step; a complex
+// channel is one (re, im) pair) x 16 contiguous time segments.  Every thread loads
+// its segment (<= L steps) into registers, folds it into an affine map (P, Q) with
+// h_out = P h_in + Q (a reset makes P = 0), the sixteen maps of a channel are
+// chained through shared memory, and each thread replays its segment from the right
+// incoming state.  One pass over memory, T/16 sequential steps per thread.  `row`
+// is the row length in floats (D for real, 2 D for complex).
 constexpr int kSegs = 16;
 
-template <int L, int W>
+template <bool CPLX, int L, int W>
 __global__ void __launch_bounds__(32 * kSegs)
 linrec_fwd_tsplit_kernel(const float* __restrict__ a, int a_tinv, const float* __restrict__ b,
                          const float* __restrict__ h0, const float* __restrict__ a0,
                          const uint8_t* __restrict__ done, float* __restrict__ h, float* __restrict__ a_last,
-                         int B, int T, int D) {
+                         int B, int T, int row) {
   __shared__ float sp[kSegs][32 * W], sq[kSegs][32 * W], sd[kSegs][32 * W];
   __shared__ int sr[kSegs][32];
   const int cx = threadIdx.x & 31, seg = threadIdx.x >> 5;
-  const long long ch = (static_cast<long long>(blockIdx.x) * 32 + cx) * W;   // first channel = b * D + d
-  const bool active = ch < static_cast<long long>(B) * D;
-  const int bi = active ? static_cast<int>(ch / D) : 0, d = active ? static_cast<int>(ch % D) : 0;
+  const long long ch = (static_cast<long long>(blockIdx.x) * 32 + cx) * W;   // first float = b * row + d
+  const bool active = ch < static_cast<long long>(B) * row;
+  const int bi = active ? static_cast<int>(ch / row) : 0, d = active ? static_cast<int>(ch % row) : 0;
   const int len = (T + kSegs - 1) / kSegs;
   const int t_begin = seg * len, t_end = min(T, t_begin + len);
-  const size_t base = static_cast<size_t>(bi) * T * D + d;
+  const size_t base = static_cast<size_t>(bi) * T * row + d;
   const uint8_t* drow = done ? done + static_cast<size_t>(bi) * T : nullptr;
 
   Pack<W> av[L], bv[L];
   bool rs[L];
-  Pack<W> a_fix = fill_pack<W>(0.f, 0.f, false);
+  Pack<W> a_fix = fill_pack<W>(0.f, 0.f, CPLX);
   if (a_tinv && active) a_fix = load_pack_cached<W>(a + d);
 #pragma unroll
   for (int i = 0; i < L; ++i) {
     const int t = t_begin + i;
     const bool in = active && t < t_end;
-    bv[i] = in ? load_pack<W>(b + base + static_cast<size_t>(t) * D) : fill_pack<W>(0.f, 0.f, false);
-    av[i] = in ? (a_tinv ? a_fix : load_pack<W>(a + base + static_cast<size_t>(t) * D)) : fill_pack<W>(1.f, 0.f, false);
+    bv[i] = in ? load_pack<W>(b + base + static_cast<size_t>(t) * row) : fill_pack<W>(0.f, 0.f, CPLX);
+    av[i] = in ? (a_tinv ? a_fix : load_pack<W>(a + base + static_cast<size_t>(t) * row)) : fill_pack<W>(1.f, 0.f, CPLX);
     rs[i] = in && drow && drow[t] != 0;
   }
   // segment summary: state map (P, Q); decay leaf: product since the last reset, and whether there was one
-  Pack<W> P = fill_pack<W>(1.f, 0.f, false), Q = fill_pack<W>(0.f, 0.f, false), dec = fill_pack<W>(1.f, 0.f, false);
+  Pack<W> P = fill_pack<W>(1.f, 0.f, CPLX), Q = fill_pack<W>(0.f, 0.f, CPLX), dec = fill_pack<W>(1.f, 0.f, CPLX);
   int had_reset = 0;
 #pragma unroll
   for (int i = 0; i < L; ++i) {
-    if (rs[i]) { P = fill_pack<W>(0.f, 0.f, false); Q = bv[i]; dec = av[i]; had_reset = 1; }
-    else { P = mul<false, W>(P, av[i]); Q = mul_add<false, W>(av[i], Q, bv[i]); dec = mul<false, W>(dec, av[i]); }
+    if (rs[i]) { P = fill_pack<W>(0.f, 0.f, CPLX); Q = bv[i]; dec = av[i]; had_reset = 1; }
+    else { P = mul<CPLX, W>(P, av[i]); Q = mul_add<CPLX, W>(av[i], Q, bv[i]); dec = mul<CPLX, W>(dec, av[i]); }
   }
 #pragma unroll
   for (int e = 0; e < W; ++e) {
@@ -250,25 +251,128 @@ linrec_fwd_tsplit_kernel(const float* __restrict__ a, int a_tinv, const float* _
   }
   sr[seg][cx] = had_reset;
   __syncthreads();
-  Pack<W> hin = (active && h0) ? load_pack_cached<W>(h0 + static_cast<size_t>(bi) * D + d) : fill_pack<W>(0.f, 0.f, false);
+  Pack<W> hin = (active && h0) ? load_pack_cached<W>(h0 + static_cast<size_t>(bi) * row + d) : fill_pack<W>(0.f, 0.f, CPLX);
   for (int s2 = 0; s2 < seg; ++s2) {
+    Pack<W> p2, q2;
 #pragma unroll
-    for (int e = 0; e < W; ++e) hin.v[e] = fmaf(sp[s2][cx * W + e], hin.v[e], sq[s2][cx * W + e]);
+    for (int e = 0; e < W; ++e) { p2.v[e] = sp[s2][cx * W + e]; q2.v[e] = sq[s2][cx * W + e]; }
+    hin = mul_add<CPLX, W>(p2, hin, q2);
   }
 #pragma unroll
   for (int i = 0; i < L; ++i) {
     const int t = t_begin + i;
-    hin = rs[i] ? bv[i] : mul_add<false, W>(av[i], hin, bv[i]);
-    if (active && t < t_end) store_pack<W>(h + base + static_cast<size_t>(t) * D, hin);
+    hin = rs[i] ? bv[i] : mul_add<CPLX, W>(av[i], hin, bv[i]);
+    if (active && t < t_end) store_pack<W>(h + base + static_cast<size_t>(t) * row, hin);
   }
   if (a_last && seg == kSegs - 1 && active) {
-    Pack<W> acc = a0 ? load_pack_cached<W>(a0 + static_cast<size_t>(bi) * D + d) : fill_pack<W>(1.f, 0.f, false);
+    Pack<W> acc = a0 ? load_pack_cached<W>(a0 + static_cast<size_t>(bi) * row + d) : fill_pack<W>(1.f, 0.f, CPLX);
     for (int s2 = 0; s2 < kSegs; ++s2) {
+      Pack<W> d2;
 #pragma unroll
-      for (int e = 0; e < W; ++e) acc.v[e] = sr[s2][cx] ? sd[s2][cx * W + e] : acc.v[e] * sd[s2][cx * W + e];
+      for (int e = 0; e < W; ++e) d2.v[e] = sd[s2][cx * W + e];
+      acc = sr[s2][cx] ? d2 : mul<CPLX, W>(acc, d2);
     }
 #pragma unroll
-    for (int e = 0; e < W; ++e) a_last[static_cast<size_t>(bi) * D + d + e] = acc.v[e];
+    for (int e = 0; e < W; ++e) a_last[static_cast<size_t>(bi) * row + d + e] = acc.v[e];
+  }
+}
+
+// The backward counterpart.  The carried cotangent c entering step t from the right obeys
+// g_t = gh_t + c, c' = reset_t ? 0 : a_t g_t, so a segment is again an affine map c_out = P c_in + Q
+// (walked right to left); the maps are chained from the last segment down, then every thread
+// replays its segment, writing gb = g and the decay gradient (per step, or summed over its steps
+// and then over the sixteen segments in a fixed order for a time-invariant decay).
+template <bool CPLX, int L, int W>
+__global__ void __launch_bounds__(32 * kSegs)
+linrec_bwd_tsplit_kernel(const float* __restrict__ a, int a_tinv, const float* __restrict__ h,
+                         const float* __restrict__ h0, const uint8_t* __restrict__ done,
+                         const float* __restrict__ gh, const float* __restrict__ gh_last,
+                         float* __restrict__ gb, float* __restrict__ ga, float* __restrict__ ga_partial,
+                         float* __restrict__ gh0, int B, int T, int row, int conj_ops) {
+  __shared__ float sp[kSegs][32 * W], sq[kSegs][32 * W];
+  const int cx = threadIdx.x & 31, seg = threadIdx.x >> 5;
+  const long long ch = (static_cast<long long>(blockIdx.x) * 32 + cx) * W;
+  const bool active = ch < static_cast<long long>(B) * row;
+  const int bi = active ? static_cast<int>(ch / row) : 0, d = active ? static_cast<int>(ch % row) : 0;
+  const int len = (T + kSegs - 1) / kSegs;
+  const int t_begin = seg * len, t_end = min(T, t_begin + len);
+  const size_t base = static_cast<size_t>(bi) * T * row + d;
+  const size_t crow = static_cast<size_t>(bi) * row + d;
+  const uint8_t* drow = done ? done + static_cast<size_t>(bi) * T : nullptr;
+  const bool want_ga = (ga != nullptr) || (ga_partial != nullptr);
+
+  Pack<W> av[L], gv[L];
+  bool rs[L];
+  Pack<W> a_fix = fill_pack<W>(0.f, 0.f, CPLX);
+  if (a_tinv && active) a_fix = conj_if<CPLX, W>(load_pack_cached<W>(a + d), conj_ops);
+#pragma unroll
+  for (int i = 0; i < L; ++i) {
+    const int t = t_begin + i;
+    const bool in = active && t < t_end;
+    gv[i] = in ? load_pack<W>(gh + base + static_cast<size_t>(t) * row) : fill_pack<W>(0.f, 0.f, CPLX);
+    av[i] = in ? (a_tinv ? a_fix : conj_if<CPLX, W>(load_pack<W>(a + base + static_cast<size_t>(t) * row), conj_ops))
+               : fill_pack<W>(1.f, 0.f, CPLX);
+    rs[i] = in && drow && drow[t] != 0;
+  }
+  Pack<W> P = fill_pack<W>(1.f, 0.f, CPLX), Q = fill_pack<W>(0.f, 0.f, CPLX);
+#pragma unroll
+  for (int i = L - 1; i >= 0; --i) {
+    if (rs[i]) { P = fill_pack<W>(0.f, 0.f, CPLX); Q = P; }
+    else { P = mul<CPLX, W>(av[i], P); Q = mul<CPLX, W>(av[i], add<W>(gv[i], Q)); }
+  }
+#pragma unroll
+  for (int e = 0; e < W; ++e) {
+    sp[seg][cx * W + e] = P.v[e];
+    sq[seg][cx * W + e] = Q.v[e];
+  }
+  __syncthreads();
+  Pack<W> carry = (active && gh_last) ? load_pack_cached<W>(gh_last + crow) : fill_pack<W>(0.f, 0.f, CPLX);
+  for (int s2 = kSegs - 1; s2 > seg; --s2) {
+    Pack<W> p2, q2;
+#pragma unroll
+    for (int e = 0; e < W; ++e) { p2.v[e] = sp[s2][cx * W + e]; q2.v[e] = sq[s2][cx * W + e]; }
+    carry = mul_add<CPLX, W>(p2, carry, q2);
+  }
+  __syncthreads();   // sp is reused for the decay-gradient partials
+  Pack<W> ga_acc = fill_pack<W>(0.f, 0.f, CPLX);
+#pragma unroll
+  for (int i = L - 1; i >= 0; --i) {
+    const int t = t_begin + i;
+    const bool in = active && t < t_end;
+    const size_t off = base + static_cast<size_t>(t) * row;
+    const Pack<W> g = add<W>(gv[i], carry);
+    if (in) store_pack<W>(gb + off, g);
+    if (rs[i]) {
+      carry = fill_pack<W>(0.f, 0.f, CPLX);
+      if (want_ga && !a_tinv) store_pack<W>(ga + off, carry);
+    } else if (in) {
+      carry = mul<CPLX, W>(av[i], g);
+      if (want_ga) {
+        Pack<W> hp;
+        if (t > 0) hp = load_pack<W>(h + off - row);
+        else hp = h0 ? load_pack_cached<W>(h0 + crow) : fill_pack<W>(0.f, 0.f, CPLX);
+        hp = conj_if<CPLX, W>(hp, conj_ops);
+        if (a_tinv) ga_acc = mul_add<CPLX, W>(hp, g, ga_acc);
+        else store_pack<W>(ga + off, mul<CPLX, W>(hp, g));
+      }
+    }
+  }
+  if (gh0 && seg == 0 && active) {
+#pragma unroll
+    for (int e = 0; e < W; ++e) gh0[crow + e] = carry.v[e];
+  }
+  if (a_tinv && ga_partial) {
+#pragma unroll
+    for (int e = 0; e < W; ++e) sp[seg][cx * W + e] = ga_acc.v[e];
+    __syncthreads();
+    if (seg == 0 && active) {
+#pragma unroll
+      for (int e = 0; e < W; ++e) {
+        float t = sp[kSegs - 1][cx * W + e];
+        for (int s2 = kSegs - 2; s2 >= 0; --s2) t += sp[s2][cx * W + e];
+        ga_partial[crow + e] = t;
+      }
+    }
   }
 }
 
@@ -535,6 +639,12 @@ inline int pick_width(long long floats_total, int row, bool cplx, std::initializ
   return 4;
 }
 
+// Time-split kernels: narrow packs only (so few channels that wide packs would leave SMs idle),
+// at most four blocks per SM of plain one-thread-per-channel work, and 32 <= T <= 256.
+inline bool use_time_split(int w, long long floats_total, int T, bool cplx) {
+  return w == (cplx ? 2 : 1) && floats_total <= 4LL * kNumSMs * kBlock && T >= 32 && T <= kSegs * 16;
+}
+
 inline unsigned blocks_for(long long threads) {
   return static_cast<unsigned>((threads + kBlock - 1) / kBlock);
 }
@@ -557,24 +667,28 @@ int linrec_fwd(const float* a, int a_tinv, const float* b, const float* h0, cons
   const long long total = static_cast<long long>(B) * row;
   const int w = pick_width(total, row, CPLX, {a, b, h0, a0, h, a_last});
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if constexpr (!CPLX) {
-    // few channels, moderate T: split time too (one launch, T/16 sequential steps per thread)
-    if (w == 1 && total <= 4LL * kNumSMs * kBlock && T >= 32 && T <= kSegs * 16) {
-      const int len = (T + kSegs - 1) / kSegs;
+  // few channels, moderate T: split time too (one launch, T/16 sequential steps per thread)
+  if (use_time_split(w, total, T, CPLX)) {
+    const int len = (T + kSegs - 1) / kSegs;
+    const unsigned threads = 32 * kSegs;
+    if constexpr (CPLX) {
+      const unsigned blocks = static_cast<unsigned>((total / 2 + 31) / 32);
+      if (len <= 8) linrec_fwd_tsplit_kernel<true, 8, 2><<<blocks, threads, 0, s>>>(a, a_tinv, b, h0, a0, done, h, a_last, B, T, row);
+      else linrec_fwd_tsplit_kernel<true, 16, 2><<<blocks, threads, 0, s>>>(a, a_tinv, b, h0, a0, done, h, a_last, B, T, row);
+    } else {
       bool wide = (D % 4 == 0) && len <= 8;   // 16-byte lanes keep 8 steps x (a, b) in registers
       for (const void* ptr : {(const void*)a, (const void*)b, (const void*)h0, (const void*)a0, (const void*)h, (const void*)a_last})
         if (ptr && !aligned16(ptr)) wide = false;
-      const unsigned threads = 32 * kSegs;
       if (wide) {
         const unsigned blocks = static_cast<unsigned>((total / 4 + 31) / 32);
-        linrec_fwd_tsplit_kernel<8, 4><<<blocks, threads, 0, s>>>(a, a_tinv, b, h0, a0, done, h, a_last, B, T, D);
+        linrec_fwd_tsplit_kernel<false, 8, 4><<<blocks, threads, 0, s>>>(a, a_tinv, b, h0, a0, done, h, a_last, B, T, row);
       } else {
         const unsigned blocks = static_cast<unsigned>((total + 31) / 32);
-        if (len <= 8) linrec_fwd_tsplit_kernel<8, 1><<<blocks, threads, 0, s>>>(a, a_tinv, b, h0, a0, done, h, a_last, B, T, D);
-        else linrec_fwd_tsplit_kernel<16, 1><<<blocks, threads, 0, s>>>(a, a_tinv, b, h0, a0, done, h, a_last, B, T, D);
+        if (len <= 8) linrec_fwd_tsplit_kernel<false, 8, 1><<<blocks, threads, 0, s>>>(a, a_tinv, b, h0, a0, done, h, a_last, B, T, row);
+        else linrec_fwd_tsplit_kernel<false, 16, 1><<<blocks, threads, 0, s>>>(a, a_tinv, b, h0, a0, done, h, a_last, B, T, row);
       }
-      return launch_status();
     }
+    return launch_status();
   }
   if (w == 4)
     linrec_fwd_kernel<CPLX, 4><<<blocks_for(total / 4), kBlock, 0, s>>>(a, a_tinv, b, h0, a0, done, h, a_last, B, T, row);
@@ -605,7 +719,14 @@ int linrec_bwd(const float* a, int a_tinv, const float* h, const float* h0, cons
   const int w = pick_width(total, row, CPLX, {a, h, h0, gh, gh_last, gb, ga, gh0, workspace});
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   float* ga_full = a_tinv ? nullptr : ga;
-  if (w == 4)
+  if (use_time_split(w, total, T, CPLX)) {
+    constexpr int kW = CPLX ? 2 : 1;
+    const unsigned blocks = static_cast<unsigned>((total / kW + 31) / 32), threads = 32 * kSegs;
+    if ((T + kSegs - 1) / kSegs <= 8)
+      linrec_bwd_tsplit_kernel<CPLX, 8, kW><<<blocks, threads, 0, s>>>(a, a_tinv, h, h0, done, gh, gh_last, gb, ga_full, partial, gh0, B, T, row, conj_ops);
+    else
+      linrec_bwd_tsplit_kernel<CPLX, 16, kW><<<blocks, threads, 0, s>>>(a, a_tinv, h, h0, done, gh, gh_last, gb, ga_full, partial, gh0, B, T, row, conj_ops);
+  } else if (w == 4)
     linrec_bwd_kernel<CPLX, 4><<<blocks_for(total / 4), kBlock, 0, s>>>(a, a_tinv, h, h0, done, gh, gh_last, gb, ga_full, partial, gh0, B, T, row, conj_ops);
   else
     linrec_bwd_kernel<CPLX, CPLX ? 2 : 1><<<blocks_for(total / (CPLX ? 2 : 1)), kBlock, 0, s>>>(a, a_tinv, h, h0, done, gh, gh_last, gb, ga_full, partial, gh0, B, T, row, conj_ops);

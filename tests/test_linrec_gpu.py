@@ -123,21 +123,36 @@ def test_linrec_split_sequence_is_bit_identical():
     assert torch.equal(acc2, acc)
 
 
+@pytest.mark.parametrize("cplx", [False, True])
 @pytest.mark.parametrize("steps", [32, 33, 40, 128, 255, 256])
 @pytest.mark.parametrize("tinv", [False, True])
-def test_linrec_time_split_kernel(steps, tinv):
-    """Small B*D with moderate T takes the time-split forward kernel."""
+def test_linrec_time_split_kernels(steps, tinv, cplx):
+    """Small B*D with moderate T takes the time-split forward and backward kernels (real and complex)."""
     from memorax_b200 import ops
     gen = torch.Generator().manual_seed(steps)
     bsz, dim = 5, 48
-    a = torch.rand(*((dim,) if tinv else (bsz, steps, dim)), generator=gen, dtype=torch.float64)
-    b, h0, a0 = rnd(gen, bsz, steps, dim), rnd(gen, bsz, dim), rnd(gen, bsz, dim)
+    a = rnd(gen, *((dim,) if tinv else (bsz, steps, dim)), cplx=cplx)
+    a = a / (1.0 + a.abs()) * 1.1
+    b, h0, a0 = rnd(gen, bsz, steps, dim, cplx=cplx), rnd(gen, bsz, dim, cplx=cplx), rnd(gen, bsz, dim, cplx=cplx)
+    gh, gh_last = rnd(gen, bsz, steps, dim, cplx=cplx), rnd(gen, bsz, dim, cplx=cplx)
     done = make_done(gen, bsz, steps, 0.08)
-    h_ref, acc_ref = mo.linrec_seq(a, b, h0, done.double(), a0)
-    cu = lambda t: t.float().cuda()
+    ar, br, h0r = a.clone().requires_grad_(), b.clone().requires_grad_(), h0.clone().requires_grad_()
+    h_ref, acc_ref = mo.linrec_seq(ar, br, h0r, done.double(), a0)
+    loss = (gh * h_ref).sum() + (gh_last * h_ref[:, -1]).sum()
+    (loss.real if cplx else loss).backward()
+    dt = torch.complex64 if cplx else torch.float32
+    cu = lambda t: t.to(dt).cuda()
     h, acc = ops.linrec_fwd(cu(a), cu(b), cu(h0), cu(a0), done.cuda())
     close(h, h_ref, what="h")
     close(acc, acc_ref, what="a_last")
+    gb, ga, gh0 = ops.linrec_bwd(cu(a), h, cu(h0), done.cuda(), cu(gh), cu(gh_last))
+    close(gb, mo.jax_cotangent(br.grad), what="gb")
+    close(ga, mo.jax_cotangent(ar.grad), rel=REL * (10 if tinv else 1), what="ga")
+    close(gh0, mo.jax_cotangent(h0r.grad), what="gh0")
+    # no carried state, no decay gradient wanted, no resets
+    h2, _ = ops.linrec_fwd(cu(a), cu(b), None, None, None)
+    h2_ref, _ = mo.linrec_seq(a, b, torch.zeros_like(h0), torch.zeros(bsz, steps, dtype=torch.float64), None)
+    close(h2, h2_ref, what="h without carry")
 
 
 def test_linrec_rejects_bad_arguments():
