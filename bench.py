@@ -488,7 +488,111 @@ class MlstmN1:
         return h
 
 
-WORKLOADS = {"n1": MlstmN1, "c2": LinAttnC2, "c3": GDeltaC3, "c4": LruC4, "c1": LinRecC1, "c5": TrainC5, "n2": MambaN2}
+class LruLayerN4:
+    """The LRU layer as the reference's Memoroid runs it at inference (lru.py:78-108 around memoroid.py:93-109):
+    input projection B_norm u, the complex scan of configuration 4 (B=1024, T=1024, N=512 states), read-out
+    (C h).real + D u; features F=256, fp32 inputs, forward only, TF32 GEMMs (XLA's default for f32 dots on
+    NVIDIA GPUs).  The measured call is ``Memoroid(LRUCell)``: both projections as ONE real library GEMM each over
+    interleaved (re, im) weights, the scan by this repository's kernel.  ``variants_ms`` times the same layer as the
+    reference formulation writes it (complex matmuls of a complex copy of the inputs, real part taken afterwards)."""
+    name = "n4_lru_layer_inference"
+    dtype = "c64"
+    B, T, F, N = 1024, 1024, 256, 512
+    p_done = 0.002
+    seed = 1234 + 8
+    dominant = "linrec_fwd_kernel"
+    launches_per_step = 1
+    dominant_traffic_bytes = None
+    cpu_sample_batch = 8
+    roofline_of_step = True
+
+    def __init__(self, batch=None):
+        self.B = batch or self.B
+        self.cell = None
+
+    def tokens(self):
+        return self.B * self.T
+
+    def host_inputs(self, seed_offset=0, device="cpu"):
+        g = torch.Generator(device=device).manual_seed(self.seed + seed_offset)
+        return dict(x=torch.randn(self.B, self.T, self.F, generator=g, device=device),
+                    done=(torch.rand(self.B, self.T, generator=g, device=device) < self.p_done).to(torch.uint8))
+
+    def _cell(self, device):
+        if self.cell is None:
+            from memorax_b200.memoroid import LRUCell
+            torch.manual_seed(self.seed)
+            self.cell = LRUCell(self.F, self.N, r_min=0.9, r_max=0.999, max_phase=math.pi / 10).to(device)
+        return self.cell
+
+    def algorithmic_bytes(self):
+        # inputs in and outputs out (fp32), and the (B,T,N) complex64 intermediates between the three launches:
+        # projected inputs written and read, states written and read
+        return 2 * 4 * self.B * self.T * self.F + 4 * 8 * self.B * self.T * self.N
+
+    def roofline(self, step_ms):
+        hbm, tc, kind = measured_peaks()
+        byts = self.algorithmic_bytes()
+        flop = 2 * self.B * self.T * (2 * self.N) * self.F * 2 + 8 * self.B * self.T * self.N
+        return {"bound": "hbm", "achieved": byts / (step_ms * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s",
+                "frac": byts / (step_ms * 1e-3) / 1e9 / hbm, "peak_kind": f"of {kind}",
+                "algorithmic_bytes_per_step": byts, "algorithmic_flop_per_step": flop,
+                "tf32_gemm_tflops": flop / (step_ms * 1e-3) / 1e12,
+                "note": "whole layer, three launches with their intermediates in HBM; the two projections are library "
+                        "GEMMs, the scan is this repository's kernel"}
+
+    def _run(self, fn):
+        prev = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = True
+        try:
+            with torch.no_grad():
+                return fn()
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = prev
+
+    def step(self, x, ops, mark=None):
+        from memorax_b200.memoroid import Memoroid
+        model = Memoroid(self._cell(x["x"].device))
+        if mark:
+            mark[0].record()
+        carry, y = self._run(lambda: model(x["x"], x["done"]))
+        if mark:
+            mark[1].record()
+        return (carry[0][:, 0], y)
+
+    def variants(self, x, ops, reps=3):
+        cell = self._cell(x["x"].device)
+
+        def reference_form():
+            lam = cell.diag_lambda()
+            b_norm = torch.complex(cell.B_real, cell.B_imag) * torch.exp(cell.gamma_log)[:, None]
+            bu = torch.matmul(x["x"].to(torch.complex64), b_norm.t())
+            h, _ = ops.linrec_fwd(lam, bu, None, None, x["done"], want_decay=False)
+            return torch.matmul(h, torch.complex(cell.C_real, cell.C_imag).t()).real + cell.D * x["x"]
+
+        self._run(reference_form)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            self._run(reference_form)
+        e1.record()
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+        return {"complex_matmul_formulation": e0.elapsed_time(e1) / reps}
+
+    def cpu_step(self, x):
+        from oracle import memoroid_oracle as mo
+        cell = self._cell("cpu")
+        with torch.no_grad():
+            lam = cell.diag_lambda()
+            b_norm = torch.complex(cell.B_real, cell.B_imag) * torch.exp(cell.gamma_log)[:, None]
+            bu = torch.matmul(x["x"].to(torch.complex64), b_norm.t())
+            h, _ = mo.linrec_seq(lam, bu, torch.zeros(bu.shape[0], bu.shape[2], dtype=bu.dtype), x["done"].float())
+            return torch.matmul(h, torch.complex(cell.C_real, cell.C_imag).t()).real + cell.D * x["x"]
+
+
+WORKLOADS = {"n4": LruLayerN4, "n1": MlstmN1, "c2": LinAttnC2, "c3": GDeltaC3, "c4": LruC4, "c1": LinRecC1, "c5": TrainC5, "n2": MambaN2}
 
 
 # ------------------------------------------------------------ clock sampling
@@ -741,7 +845,7 @@ class Harness:
                "blocks": len(blocks), "block_ms_min_med_max": [min(blocks), sorted(blocks)[len(blocks) // 2], max(blocks)],
                "clocks": clocks}
         if hasattr(w, "roofline"):
-            rec["roofline"] = w.roofline(dominant_ms)
+            rec["roofline"] = w.roofline(ms_per_step if getattr(w, "roofline_of_step", False) else dominant_ms)
             return rec
         alg = w.algorithmic_bytes()
         flops = w.algorithmic_flops()
@@ -769,6 +873,8 @@ class Harness:
         rec = self.op_record(w, ms, dom_ms, blocks, clocks, self.world * w.tokens())
         rec["l2"] = f"{len(sets)} input set(s) rotated, {in_bytes * len(sets) / 1e6:.0f} MB of inputs"
         rec["launch"] = "cuda graph replay" if graphed else "direct"
+        if hasattr(w, "variants"):
+            rec["variants_ms"] = w.variants(sets[0], self.ops)
         if hasattr(w, "trainer"):
             w.trainer = None
         del sets, w
@@ -850,7 +956,7 @@ def run_gpu_arm(args):
     if args.ops:
         per_op[args.workload] = {k: head[k] for k in ("workload", "batch_per_gpu", "ms_per_step", "tokens_per_s",
                                                       "dtype", "blocks", "clocks", "roofline")}
-        for name in ("c1", "c3", "c4", "c5"):
+        for name in ("c1", "c3", "c4", "c5", "n1", "n2", "n4"):
             if name == args.workload:
                 continue
             per_op[name] = hz.run_op(WORKLOADS[name], None, args.steps, args.warmup, args.min_seconds)

@@ -25,10 +25,17 @@ class PreNorm(nn.Module):
         return self.module(normed, done, initial_carry)
 
 
+class Dense(nn.Linear):
+    """``nn.Linear`` whose bias gradient is this library's fixed-order column sum (``ops.dense``)."""
+
+    def forward(self, x):
+        return ops.dense(x, self.weight, self.bias)
+
+
 class GatedResidual(nn.Module):
     def __init__(self, module, features):
         super().__init__()
-        self.module, self.gate = module, nn.Linear(features, features)
+        self.module, self.gate = module, Dense(features, features)
 
     def forward(self, inputs, done=None, initial_carry=None):
         carry, out = self.module(inputs, done, initial_carry)
@@ -38,7 +45,7 @@ class GatedResidual(nn.Module):
 class FFN(nn.Module):
     def __init__(self, features, expansion_factor=4):
         super().__init__()
-        self.up, self.down = nn.Linear(features, features * expansion_factor), nn.Linear(features * expansion_factor, features)
+        self.up, self.down = Dense(features, features * expansion_factor), Dense(features * expansion_factor, features)
 
     def forward(self, inputs, done=None, initial_carry=None):
         return None, self.down(torch.nn.functional.gelu(self.up(inputs)))
@@ -65,7 +72,7 @@ class GTrXLStyleValueNet(nn.Module):
 
     def __init__(self, obs_dim=128, d_model=512, num_heads=8, head_dim=64, layers=4):
         super().__init__()
-        self.embed = nn.Linear(obs_dim, d_model)
+        self.embed = Dense(obs_dim, d_model)
         blocks = []
         for _ in range(layers):
             mixer = Memoroid(DeltaNetCell(features=d_model, head_dim=head_dim, num_heads=num_heads))

@@ -162,6 +162,62 @@ norm_bwd_reduce_kernel(const float* __restrict__ part, float* __restrict__ dgamm
   }
 }
 
+// Column sums of a (rows, cols) bf16 matrix in fp32 -- the bias gradient of a Dense layer.  Block (cx, ry) owns 256
+// columns x a contiguous range of rows: its thread (tx, ty) adds 8 columns of every eighth row, the eight thread rows
+// are added in a fixed order, and the block's sums go to part[ry][col]; the second kernel adds the row blocks in order.
+__global__ void __launch_bounds__(256)
+colsum_partial_kernel(const uint4* __restrict__ x, float* __restrict__ part, long long rows, int cols8, int rows_per_block) {
+  __shared__ float red[8][32][9];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int v = blockIdx.x * 32 + tx;
+  const long long r0 = static_cast<long long>(blockIdx.y) * rows_per_block;
+  const long long r1 = r0 + rows_per_block < rows ? r0 + rows_per_block : rows;
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  if (v < cols8) {
+    long long r = r0 + ty;
+    for (; r + 24 < r1; r += 32) {   // four independent loads in flight
+      uint4 raw[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) raw[u] = ld_stream(x + (r + 8 * u) * cols8 + v);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float f[8];
+        umma::unpack8_bf16(raw[u], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += f[e];
+      }
+    }
+    for (; r < r1; r += 8) {
+      float f[8];
+      umma::unpack8_bf16(ld_stream(x + r * cols8 + v), f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += f[e];
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) red[ty][tx][e] = acc[e];
+  __syncthreads();
+  // 256 threads = 32 vectors x 8 elements: thread (tx2, e) adds the eight thread rows in order
+  const int e = threadIdx.x & 7, tx2 = threadIdx.x >> 3;
+  const int col = (blockIdx.x * 32 + tx2) * 8 + e;
+  if (col < cols8 * 8) {
+    float t = red[0][tx2][e];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) t += red[i][tx2][e];
+    part[static_cast<size_t>(blockIdx.y) * cols8 * 8 + col] = t;
+  }
+}
+__global__ void __launch_bounds__(256)
+colsum_final_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, int row_blocks, int cols) {
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= cols) return;
+  float t = 0.f;
+  for (int b = 0; b < row_blocks; ++b) t += part[static_cast<size_t>(b) * cols + c];
+  out[c] = __float2bfloat16(t);
+}
+
 // y = x + sigmoid(g) * o
 __global__ void __launch_bounds__(256)
 gated_residual_fwd_kernel(const uint4* __restrict__ x, const uint4* __restrict__ g, const uint4* __restrict__ o,
@@ -245,10 +301,43 @@ int norm_blocks(long long rows, int per_sm = 2) {
   return static_cast<int>(want < cap ? want : cap);
 }
 
+// Row blocks of the column-sum kernels: about four blocks per SM over all column strips, at least 32 rows each.
+int colsum_row_blocks(long long rows, int cols) {
+  const int strips = (cols / 8 + 31) / 32;
+  long long want = (4LL * kNumSMs + strips - 1) / strips;
+  const long long most = (rows + 31) / 32;
+  if (want > most) want = most;
+  if (want > 256) want = 256;
+  return static_cast<int>(want < 1 ? 1 : want);
+}
+
 }  // namespace
 }  // namespace mxk
 
 extern "C" {
+
+size_t mxk_colsum_workspace_bytes(long long rows, int cols) {
+  if (rows <= 0 || cols <= 0) return 0;
+  return static_cast<size_t>(mxk::colsum_row_blocks(rows, cols)) * cols * sizeof(float);
+}
+
+int mxk_colsum_bf16(const void* x, void* out, void* workspace, size_t workspace_bytes, long long rows, int cols,
+                    mxk_stream_t stream) {
+  using namespace mxk;
+  if (!x || !out) return MXK_ERR_NULL;
+  if (rows <= 0 || cols <= 0) return MXK_ERR_DIMS;
+  if (cols % 8) return MXK_ERR_UNSUPPORTED;
+  if (!aligned16(x) || (reinterpret_cast<uintptr_t>(out) % 2) || (workspace && !aligned16(workspace))) return MXK_ERR_ALIGN;
+  if (!workspace || workspace_bytes < mxk_colsum_workspace_bytes(rows, cols)) return MXK_ERR_WORKSPACE;
+  const int nrb = colsum_row_blocks(rows, cols), cols8 = cols / 8;
+  const int rpb = static_cast<int>((rows + nrb - 1) / nrb);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  colsum_partial_kernel<<<dim3((cols8 + 31) / 32, nrb), 256, 0, s>>>(static_cast<const uint4*>(x), static_cast<float*>(workspace),
+                                                                      rows, cols8, rpb);
+  if (int st = launch_status()) return st;
+  colsum_final_kernel<<<(cols + 255) / 256, 256, 0, s>>>(static_cast<const float*>(workspace), static_cast<__nv_bfloat16*>(out), nrb, cols);
+  return launch_status();
+}
 
 size_t mxk_norm_bwd_workspace_bytes(long long rows, int D) {
   if (rows <= 0 || D <= 0) return 0;

@@ -22,6 +22,7 @@ inline int launch_status() {
 __device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p); }
 __device__ __forceinline__ float2 ld_stream(const float2* p) { return __ldcs(p); }
 __device__ __forceinline__ float ld_stream(const float* p) { return __ldcs(p); }
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
 __device__ __forceinline__ void st_stream(float4* p, float4 v) { __stcs(p, v); }
 __device__ __forceinline__ void st_stream(float2* p, float2 v) { __stcs(p, v); }
 __device__ __forceinline__ void st_stream(float* p, float v) { __stcs(p, v); }

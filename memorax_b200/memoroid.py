@@ -26,6 +26,7 @@ import math
 
 import torch
 from torch import nn
+from torch.nn import functional as F
 
 from . import ops
 
@@ -115,15 +116,71 @@ class Memoroid(SequenceModel):
             jac, sens = jacobians[name], sensitivity[name]
             param_shape = tuple(jac.shape[3:])
             psize = math.prod(param_shape)
-            a = decay.float().repeat_interleave(psize, dim=-1)
-            h, _ = ops.linrec_fwd(a, jac.float().reshape(bsz, steps, hid * psize),
-                                  sens.float().reshape(bsz, hid * psize), None, done, want_decay=False)
+            b_flat, s_flat = jac.float().reshape(bsz, steps, hid * psize), sens.float().reshape(bsz, hid * psize)
+            if ops.grouped_decay_supported(hid * psize, hid):
+                # one decay per hidden unit, broadcast over its parameter axes inside the kernel
+                h, _ = ops.linrec_grouped_fwd(decay.float(), b_flat, s_flat, None, done, want_decay=False)
+            else:
+                a = decay.float().repeat_interleave(psize, dim=-1)
+                h, _ = ops.linrec_fwd(a, b_flat, s_flat, None, done, want_decay=False)
             out[name] = h[:, -1:].reshape(bsz, 1, hid, *param_shape)
         return out
 
 
+# ---------------------------------------------------- complex-diagonal cells
+def _project_to_complex(x, w):
+    """``x @ w.T`` for real ``x`` (B,T,F) and complex ``w`` (N,F) as ONE real GEMM: the weight rows are
+    interleaved (re_0, im_0, re_1, ...), so the (B,T,2N) product is the complex64 result in memory."""
+    n, f = w.shape
+    w2 = torch.view_as_real(w).permute(0, 2, 1).reshape(2 * n, f)
+    out = F.linear(x.float(), w2)
+    return torch.view_as_complex(out.view(*out.shape[:-1], n, 2))
+
+
+def _read_real_part(h, c):
+    """``(h @ c.T).real`` for complex ``h`` (B,T,N) and ``c`` (F,N) as ONE real GEMM over the
+    interleaved (re, im) view of ``h``: Re(h c) = h_re c_re - h_im c_im."""
+    f, n = c.shape
+    w2 = torch.stack([c.real, -c.imag], dim=-1).reshape(f, 2 * n)
+    hr = torch.view_as_real(h)
+    return F.linear(hr.reshape(*hr.shape[:-2], 2 * n), w2)
+
+
+class _ComplexDiagonalCell(MemoroidCellBase):
+    """What the LRU and S5 cells share around the scan kernel (lru.py:78-108, s5.py:123-149):
+    the complex projections written as real GEMMs (half the multiply-adds of a complex matmul whose
+    imaginary input or output part is discarded, and no complex copy of the inputs) and the scan."""
+
+    def _weights(self):
+        """-> (decay (N,), input projection (N,F) complex, read-out (F,N) complex, skip (F,))"""
+        raise NotImplementedError
+
+    def forward(self, x, **kwargs):
+        lam, w_in, _, _ = self._weights()
+        return _project_to_complex(x, w_in), lam
+
+    def read(self, h, x, **kwargs):
+        _, _, w_out, skip = self._weights()
+        return _read_real_part(h[0], w_out) + skip * x
+
+    def binary_operator(self, a, b):
+        s_i, a_i = a
+        s_j, a_j = b
+        return a_j * s_i + s_j, a_j * a_i
+
+    def scan_states(self, z, initial_carry, done):
+        state, lam = z
+        h0, a0 = _squeeze_carry(initial_carry, 2)
+        h, a_last = ops.LinRec.apply(lam, state.contiguous(), h0, a0, done)
+        return (h, None), (h[:, -1:], a_last[:, None])
+
+    def scan(self, z, initial_carry, done, inputs):
+        h, next_carry = self.scan_states(z, initial_carry, done)
+        return next_carry, self.read(h, inputs)
+
+
 # ---------------------------------------------------------------------- LRU
-class LRUCell(MemoroidCellBase):
+class LRUCell(_ComplexDiagonalCell):
     """Complex diagonal linear recurrence with time-invariant decay (lru.py:32-108)."""
 
     def __init__(self, features, hidden_dim, r_min=0.0, r_max=1.0, max_phase=6.28):
@@ -143,37 +200,15 @@ class LRUCell(MemoroidCellBase):
     def diag_lambda(self):
         return torch.exp(torch.complex(-torch.exp(self.nu_log), torch.exp(self.theta_log)))
 
-    def forward(self, x, **kwargs):
-        """-> (state (B,T,H) complex64, decay (H,)): the decay is one lambda for
-        every (b, t) (lru.py:86), so it is passed un-broadcast."""
+    def _weights(self):
+        # the decay is one lambda for every (b, t) (lru.py:86), so it is passed un-broadcast
         b_norm = torch.complex(self.B_real, self.B_imag) * torch.exp(self.gamma_log)[:, None]
-        state = torch.matmul(x.to(torch.complex64), b_norm.t())
-        return state, self.diag_lambda()
-
-    def binary_operator(self, a, b):
-        s_i, a_i = a
-        s_j, a_j = b
-        return a_j * s_i + s_j, a_j * a_i
-
-    def read(self, h, x, **kwargs):
-        state, _ = h
-        c = torch.complex(self.C_real, self.C_imag)
-        return torch.matmul(state, c.t()).real + self.D * x
+        return self.diag_lambda(), b_norm, torch.complex(self.C_real, self.C_imag), self.D
 
     def initialize_carry(self, key, input_shape):
         *batch, _ = input_shape
         return (torch.zeros(*batch, 1, self.hidden_dim, dtype=torch.complex64),
                 torch.ones(*batch, 1, self.hidden_dim, dtype=torch.complex64))
-
-    def scan_states(self, z, initial_carry, done):
-        state, lam = z
-        h0, a0 = _squeeze_carry(initial_carry, 2)
-        h, a_last = ops.LinRec.apply(lam, state.contiguous(), h0, a0, done)
-        return (h, None), (h[:, -1:], a_last[:, None])
-
-    def scan(self, z, initial_carry, done, inputs):
-        h, next_carry = self.scan_states(z, initial_carry, done)
-        return next_carry, self.read(h, inputs)
 
 
 # ------------------------------------------------------------------- MinGRU
@@ -275,7 +310,7 @@ class LinearAttentionCell(MemoroidCellBase):
         bf = torch.bfloat16
         o, s_last, z_last = ops.LinAttn.apply(q.to(bf), k.to(bf), v.to(bf), s0, z0, done, self.eps, True)
         o = o.reshape(*o.shape[:2], -1).to(inputs.dtype)
-        y = self.output_projection(self.norm(o))
+        y = ops.dense(self.norm(o), self.output_projection.weight, self.output_projection.bias)
         return (s_last[:, None], z_last[:, None]), y
 
 
@@ -308,7 +343,7 @@ class DeltaNetCell(MemoroidCellBase):
         """-> factored elements (k, v, alpha, beta); k is L2-normalised per head."""
         k = ops.l2norm_heads(self.key(x), self.head_dim)
         v = self._heads(self.value(x))
-        b_logit, a_logit = self.gate(x).float().chunk(2, dim=-1)
+        b_logit, a_logit = ops.dense(x, self.gate.weight, self.gate.bias).float().chunk(2, dim=-1)
         return k, v, torch.exp(-torch.nn.functional.softplus(a_logit)), torch.sigmoid(b_logit)
 
     def binary_operator(self, a, b):
@@ -330,7 +365,8 @@ class DeltaNetCell(MemoroidCellBase):
         bf = torch.bfloat16
         o, s_last = ops.GatedDelta.apply(q.to(bf), k.to(bf), v.to(bf), alpha.contiguous(), beta.contiguous(), s0, done)
         o = o.reshape(*o.shape[:2], -1).to(inputs.dtype)
-        return (s_last[:, None],), self.output_projection(ops.rms_norm(o, self.norm.weight, self.norm.eps))
+        return (s_last[:, None],), ops.dense(ops.rms_norm(o, self.norm.weight, self.norm.eps), self.output_projection.weight,
+                                          self.output_projection.bias)
 
 
 # -------------------------------------------------------------------- mLSTM
@@ -423,7 +459,7 @@ class mLSTMCell(MemoroidCellBase):
 
 
 # ----------------------------------------------------------------------- S5
-class S5Cell(MemoroidCellBase):
+class S5Cell(_ComplexDiagonalCell):
     """Diagonal state-space cell (s5.py:18-149): the same (state, decay) operator
     as the LRU with a discretised, time-invariant ``lambda_bar`` (ZOH or bilinear,
     hippo.py:34-50).  The HiPPO-DPLR initialisation of the reference is
@@ -457,33 +493,14 @@ class S5Cell(MemoroidCellBase):
             raise ValueError(f"Invalid discretization: {self.discretization}")
         return lambda_bar, b_bar
 
-    def forward(self, x, **kwargs):
+    def _weights(self):
         lambda_bar, b_bar = self._discretized()
-        return torch.matmul(x.to(torch.complex64), b_bar.t()), lambda_bar
-
-    def binary_operator(self, a, b):
-        s_i, a_i = a
-        s_j, a_j = b
-        return a_j * s_i + s_j, a_j * a_i
-
-    def read(self, h, x, **kwargs):
-        c_tilde = torch.view_as_complex(self.C.contiguous())
-        return torch.matmul(h[0], c_tilde.t()).real + self.d * x
+        return lambda_bar, b_bar, torch.view_as_complex(self.C.contiguous()), self.d
 
     def initialize_carry(self, key, input_shape):
         *batch, _ = input_shape
         return (torch.zeros(*batch, 1, self.state_size, dtype=torch.complex64),
                 torch.ones(*batch, 1, self.state_size, dtype=torch.complex64))
-
-    def scan_states(self, z, initial_carry, done):
-        state, lambda_bar = z
-        h0, a0 = _squeeze_carry(initial_carry, 2)
-        h, a_last = ops.LinRec.apply(lambda_bar, state.contiguous(), h0, a0, done)
-        return (h, None), (h[:, -1:], a_last[:, None])
-
-    def scan(self, z, initial_carry, done, inputs):
-        h, next_carry = self.scan_states(z, initial_carry, done)
-        return next_carry, self.read(h, inputs)
 
 
 # -------------------------------------------------------------------- Mamba

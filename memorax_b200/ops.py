@@ -10,6 +10,7 @@ from __future__ import annotations
 import ctypes
 
 import torch
+from torch.nn import functional as F
 
 from . import _lib
 
@@ -574,6 +575,48 @@ class L2NormHeads(torch.autograd.Function):
         _lib.call("mxk_l2norm_heads_bf16", _ptr(x), _ptr(dy.contiguous()), _ptr(dx), x.numel() // ctx.head_dim, ctx.head_dim,
                   float(ctx.eps), _stream())
         return dx, None, None
+
+
+def colsum(x):
+    """Sum over the rows of a (rows, cols) bf16 matrix (fp32 accumulation, fixed order), -> (cols,) bf16."""
+    x = x.contiguous()
+    rows, cols = x.shape
+    out = torch.empty(cols, dtype=torch.bfloat16, device=x.device)
+    ws_bytes = _lib.lib.mxk_colsum_workspace_bytes(rows, cols)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
+    _lib.call("mxk_colsum_bf16", _ptr(x), _ptr(out), _ptr(ws), ws_bytes, rows, cols, _stream())
+    return out
+
+
+class DenseBias(torch.autograd.Function):
+    """y = x W^T + b for bf16 CUDA tensors: the two GEMMs of the backward are the library's, the bias gradient
+    (a column sum of dy) is this library's fixed-order kernel."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        ctx.save_for_backward(x, weight)
+        return F.linear(x, weight, bias)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.matmul(dy, weight)
+        if ctx.needs_input_grad[1]:
+            dw = torch.mm(dy2.t(), x.reshape(-1, x.shape[-1]))
+        if ctx.needs_input_grad[2]:
+            db = colsum(dy2)
+        return dx, dw, db
+
+
+def dense(x, weight, bias=None):
+    """``F.linear`` whose bias gradient runs on :func:`colsum` when it can (bf16 CUDA, out features % 8 == 0)."""
+    if (bias is not None and x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and bias.dtype == torch.bfloat16 and weight.shape[0] % 8 == 0 and torch.is_grad_enabled()):
+        return DenseBias.apply(x, weight, bias)
+    return F.linear(x, weight, bias)
 
 
 def l2norm_heads(x, head_dim, eps=1e-12):

@@ -70,3 +70,27 @@ def test_l2norm_heads_matches_torch(head_dim):
     # zero vectors stay zero (norm clamped at eps), no NaN
     z = ops.l2norm_heads(torch.zeros(2, 3, head_dim, dtype=torch.bfloat16, device="cuda"), head_dim)
     assert float(z.abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("shape", [(1, 8), (37, 16), (1000, 512), (16384, 2048), (4099, 520)])
+def test_colsum_and_dense_bias_gradient(shape):
+    """Column sums (bias gradient of a Dense layer) against an fp64 sum of the same bf16 values; bit-reproducible."""
+    from memorax_b200 import ops
+    rows, cols = shape
+    g = torch.Generator(device="cuda").manual_seed(rows + cols)
+    x = torch.randn(rows, cols, device="cuda", generator=g).bfloat16()
+    got = ops.colsum(x)
+    ref = x.double().sum(0)
+    tol = 2 ** -8 * float(ref.abs().max()) + 1e-6      # one bf16 rounding of the result
+    assert float((got.double() - ref).abs().max()) <= tol
+    assert torch.equal(got, ops.colsum(x))
+    # through the autograd function: all three gradients against torch's own Linear
+    if cols <= 520:
+        lin = torch.nn.Linear(24, cols, device="cuda", dtype=torch.bfloat16)
+        inp = torch.randn(3, max(rows // 3, 1), 24, device="cuda", generator=g).bfloat16().requires_grad_()
+        ct = torch.randn(3, max(rows // 3, 1), cols, device="cuda", generator=g).bfloat16()
+        want = torch.autograd.grad(lin(inp), [inp, lin.weight, lin.bias], ct)
+        have = torch.autograd.grad(ops.dense(inp, lin.weight, lin.bias), [inp, lin.weight, lin.bias], ct)
+        assert torch.equal(have[0], want[0]) and torch.equal(have[1], want[1])
+        ref_b = ct.double().sum((0, 1))
+        assert float((have[2].double() - ref_b).abs().max()) <= 2 ** -8 * float(ref_b.abs().max()) + 1e-6

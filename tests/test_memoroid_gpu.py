@@ -105,6 +105,54 @@ def test_propagate_sensitivities_matches_the_reference_vectors():
     assert err <= 1e-5 * max(1.0, float(ref.abs().max())), err
 
 
+def test_propagate_sensitivities_grouped_decay_path():
+    """A parameter leaf of 128 entries per hidden unit takes the grouped-decay kernel (the decay is not
+    expanded); same recurrence as the oracle's real linear recurrence with the decay repeated."""
+    from memorax_b200.memoroid import Memoroid, LRUCell
+    gen = torch.Generator().manual_seed(7)
+    bsz, steps, hid, psize = 3, 21, 4, 128
+    decay = torch.rand(bsz, steps, hid, generator=gen, dtype=torch.float64)
+    jac = torch.randn(bsz, steps, hid, 2, 64, generator=gen, dtype=torch.float64)
+    sens = torch.randn(bsz, 1, hid, 2, 64, generator=gen, dtype=torch.float64)
+    done = torch.rand(bsz, steps, generator=gen) < 0.1
+    model = Memoroid(LRUCell(4, hid))
+    nxt = model.propagate_sensitivities(decay.float().cuda(), {"w": jac.float().cuda()}, {"w": sens.float().cuda()},
+                                        done.cuda())
+    h_ref, _ = mo.linrec_seq(decay.repeat_interleave(psize, dim=-1), jac.reshape(bsz, steps, hid * psize),
+                             sens.reshape(bsz, hid * psize), done.double())
+    ref = h_ref[:, -1:].reshape(bsz, 1, hid, 2, 64)
+    assert nxt["w"].shape == ref.shape
+    err = float((nxt["w"].double().cpu() - ref).abs().max())
+    assert err <= 1e-5 * max(1.0, float(ref.abs().max())), err
+
+
+@pytest.mark.parametrize("kind", ["lru", "s5"])
+def test_real_gemm_projections_equal_the_complex_formulation(kind):
+    """The cells' projections run as real GEMMs over interleaved (re, im) weights; against the reference's
+    complex matmuls (lru.py:82-84,99-102; s5.py:126-128,139-143) on the same weights, values and gradients."""
+    from memorax_b200.memoroid import LRUCell, S5Cell
+    torch.manual_seed(11)
+    cell = (LRUCell(24, 64) if kind == "lru" else S5Cell(24, 64)).cuda()
+    x = torch.randn(3, 17, 24, device="cuda", requires_grad=True)
+    h = torch.randn(3, 17, 64, dtype=torch.complex64, device="cuda", requires_grad=True)
+    _, w_in, w_out, skip = cell._weights()
+    bu, _ = cell(x)
+    y = cell.read((h, None), x)
+    bu_ref = torch.matmul(x.to(torch.complex64), w_in.t())
+    y_ref = torch.matmul(h, w_out.t()).real + skip * x
+    tol = lambda ref: 1e-5 * max(1.0, float(ref.abs().max()))
+    assert float((bu - bu_ref).abs().max()) <= tol(bu_ref) and float((y - y_ref).abs().max()) <= tol(y_ref)
+    ct_bu, ct_y = torch.randn_like(bu), torch.randn_like(y)
+    params = [p for p in cell.parameters()]
+    loss = lambda a, b: (torch.view_as_real(a) * torch.view_as_real(ct_bu)).sum() + (b * ct_y).sum()
+    got = torch.autograd.grad(loss(bu, y), [x, h] + params, allow_unused=True)
+    want = torch.autograd.grad(loss(bu_ref, y_ref), [x, h] + params, allow_unused=True)
+    for g, w in zip(got, want):
+        assert (g is None) == (w is None)
+        if g is not None:
+            assert float((g - w).abs().max()) <= 1e-4 * max(1.0, float(w.abs().max()))
+
+
 def test_mamba_scan_and_read_match_the_reference_vectors():
     """MambaCell.scan_elements / read_state against the vectors produced by the reference's own
     MambaCell source under Memoroid.scan_fn (non-trivial carry, resets)."""
