@@ -209,13 +209,23 @@ colsum_partial_kernel(const uint4* __restrict__ x, float* __restrict__ part, lon
     part[static_cast<size_t>(blockIdx.y) * cols8 * 8 + col] = t;
   }
 }
+// A block owns 32 columns; its eight thread rows each add every eighth row block, then thread row 0 adds the eight sums in order.
 __global__ void __launch_bounds__(256)
 colsum_final_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, int row_blocks, int cols) {
-  const int c = blockIdx.x * 256 + threadIdx.x;
-  if (c >= cols) return;
+  __shared__ float red[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
   float t = 0.f;
-  for (int b = 0; b < row_blocks; ++b) t += part[static_cast<size_t>(b) * cols + c];
-  out[c] = __float2bfloat16(t);
+  if (c < cols)
+    for (int b = ty; b < row_blocks; b += 8) t += part[static_cast<size_t>(b) * cols + c];
+  red[ty][tx] = t;
+  __syncthreads();
+  if (ty == 0 && c < cols) {
+    float u = red[0][tx];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) u += red[i][tx];
+    out[c] = __float2bfloat16(u);
+  }
 }
 
 // y = x + sigmoid(g) * o
@@ -307,7 +317,7 @@ int colsum_row_blocks(long long rows, int cols) {
   long long want = (4LL * kNumSMs + strips - 1) / strips;
   const long long most = (rows + 31) / 32;
   if (want > most) want = most;
-  if (want > 256) want = 256;
+  if (want > 128) want = 128;
   return static_cast<int>(want < 1 ? 1 : want);
 }
 
@@ -335,7 +345,7 @@ int mxk_colsum_bf16(const void* x, void* out, void* workspace, size_t workspace_
   colsum_partial_kernel<<<dim3((cols8 + 31) / 32, nrb), 256, 0, s>>>(static_cast<const uint4*>(x), static_cast<float*>(workspace),
                                                                       rows, cols8, rpb);
   if (int st = launch_status()) return st;
-  colsum_final_kernel<<<(cols + 255) / 256, 256, 0, s>>>(static_cast<const float*>(workspace), static_cast<__nv_bfloat16*>(out), nrb, cols);
+  colsum_final_kernel<<<(cols + 31) / 32, 256, 0, s>>>(static_cast<const float*>(workspace), static_cast<__nv_bfloat16*>(out), nrb, cols);
   return launch_status();
 }
 
