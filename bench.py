@@ -58,7 +58,7 @@ class LinAttnC2:
     e2e_mode = "stream"
     # dram__bytes_read.sum + dram__bytes_write.sum of one linattn_bwd_kernel launch at
     # this size (ncu capture summarised under profiles/)
-    dominant_traffic_bytes = 251.3e6
+    dominant_traffic_bytes = 251.8e6
 
     def __init__(self, batch=None):
         self.B = batch or self.B
@@ -122,7 +122,9 @@ class LruC4:
     seed = 1234 + 4
     dominant = "linrec_bwd_kernel"
     launches_per_step = 3
-    dominant_traffic_bytes = None
+    # one linrec_bwd_kernel launch: 3985.5 MB measured at B=320 (ncu capture summarised under profiles/),
+    # scaled by 1024 / 320 (traffic is proportional to the batch)
+    dominant_traffic_bytes = 3985.5e6 * 1024 / 320
     cpu_sample_batch = 64
 
     def __init__(self, batch=None):
@@ -223,10 +225,11 @@ class GDeltaC3:
     p_done = 0.005
     seed = 1234 + 3
     dominant = "gdelta_bwd_kernel"
-    launches_per_step = 2
+    launches_per_step = 3
     e2e_slices = 4
     e2e_mode = "stream"
-    dominant_traffic_bytes = None
+    # one gdelta_bwd_kernel launch: 304.4 MB measured at B=32 (profiles/), scaled by 128 / 32
+    dominant_traffic_bytes = 304.4e6 * 4
     cpu_sample_batch = 4
 
     def __init__(self, batch=None):
@@ -290,7 +293,10 @@ class TrainC5:
     p_done = 0.005
     seed = 1234 + 5
     dominant = "train_step"
-    launches_per_step = 4 * 2 + 1   # this library's kernels per step: 4 layers x (gdelta fwd, bwd) + Adam
+    # this library's kernels per step: per layer 3 delta-rule launches (prep, fwd, bwd), 9 norm launches (three norms:
+    # fwd, bwd, bwd reduce), 4 gated-residual, 4 L2-normalise, 12 column-sum launches (six biased Dense layers x 2);
+    # plus the embedding's column sum (2) and the Adam step
+    launches_per_step = 4 * (3 + 9 + 4 + 4 + 12) + 2 + 1
     dominant_traffic_bytes = None
     cpu_sample_batch = 2
 
@@ -863,6 +869,8 @@ class Harness:
             "kernel": w.dominant, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
             "peak_kind": f"of {kind}", "algorithmic_bytes_per_launch": dom_bytes, "ms_per_launch": dominant_ms,
             "tensor_frac_of_kernel": flops[w.dominant] / (dominant_ms * 1e-3) / 1e12 / tc_peak}
+        if w.B == type(w).B:
+            rec["roofline"]["traffic"] = w.dominant_traffic_bytes
         return rec
 
     def run_op(self, cls, batch, steps, warmup, min_seconds, on_device=True):

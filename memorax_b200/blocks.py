@@ -92,11 +92,13 @@ class FlatAdamTrainer:
     reference's fp32 params); the bf16 buffer the model computes with is its rounding,
     rewritten by the same kernel -- a step of lr = 3e-4 is far below a bf16 ulp at |p| = 1.
 
-    With more than one rank the flat gradient is cut into one bucket per top-level block
-    (embedding, each torso block, head).  A bucket's all-reduce is launched from a gradient
-    hook the moment the last gradient of that bucket has been accumulated, so it runs on
-    NCCL's stream underneath the rest of the backward pass; the step waits for all buckets
-    before the Adam kernel."""
+    The flat gradient is cut into one bucket per top-level block (embedding, each torso block,
+    head).  Parameters enter the backward pass without a ``.grad``, so autograd hands over each
+    gradient tensor as it is (no add kernel per parameter, no zeroing of the flat buffer); a
+    gradient hook copies a bucket's gradients into the flat buffer with one multi-tensor copy the
+    moment the last of them has arrived and, with more than one rank, launches that bucket's
+    all-reduce, which runs on NCCL's stream underneath the rest of the backward pass; the step
+    waits for all buckets before the Adam kernel."""
 
     def __init__(self, model, lr=3e-4, betas=(0.9, 0.999), eps=1e-8, process_group=None, world_size=1,
                  overlap_allreduce=True):
@@ -114,7 +116,6 @@ class FlatAdamTrainer:
             n = p.numel()
             self.flat[off:off + n].copy_(p.data.reshape(-1))
             p.data = self.flat[off:off + n].view_as(p)
-            p.grad = self.flat_grad[off:off + n].view_as(p)
             offsets[p] = (off, off + n)
             off += n
         self.master = self.flat.float()
@@ -125,22 +126,23 @@ class FlatAdamTrainer:
         self.num_params = total
         # ---- gradient buckets: contiguous ranges of the flat buffer, one per top-level block
         self.buckets = []          # (lo, hi, number of parameters)
+        self._bucket_params = []   # per bucket: (parameters, their views into the flat gradient)
         self._pending, self._handles = [], []
-        if world_size > 1 and overlap_allreduce:
-            groups = []
-            for child in self._top_level_blocks(model):
-                ps = [p for p in child.parameters()]
-                if ps:
-                    groups.append(ps)
-            for ps in groups:
-                lo, hi = min(offsets[p][0] for p in ps), max(offsets[p][1] for p in ps)
-                index = len(self.buckets)
-                self.buckets.append((lo, hi, len(ps)))
-                for p in ps:
-                    p.register_post_accumulate_grad_hook(self._make_hook(index))
-            covered = sorted((lo, hi) for lo, hi, _ in self.buckets)
-            assert covered[0][0] == 0 and covered[-1][1] == total and all(
-                a[1] == b[0] for a, b in zip(covered, covered[1:])), "buckets must tile the flat gradient"
+        self._params = params
+        self._reduce_in_hooks = world_size > 1 and overlap_allreduce
+        for child in self._top_level_blocks(model):
+            ps = [p for p in child.parameters()]
+            if not ps:
+                continue
+            lo, hi = min(offsets[p][0] for p in ps), max(offsets[p][1] for p in ps)
+            index = len(self.buckets)
+            self.buckets.append((lo, hi, len(ps)))
+            self._bucket_params.append((ps, [self.flat_grad[offsets[p][0]:offsets[p][1]].view_as(p) for p in ps]))
+            for p in ps:
+                p.register_post_accumulate_grad_hook(self._make_hook(index))
+        covered = sorted((lo, hi) for lo, hi, _ in self.buckets)
+        assert covered[0][0] == 0 and covered[-1][1] == total and all(
+            a[1] == b[0] for a, b in zip(covered, covered[1:])), "buckets must tile the flat gradient"
 
     @staticmethod
     def _top_level_blocks(model):
@@ -154,20 +156,27 @@ class FlatAdamTrainer:
         def hook(_param):
             self._pending[index] -= 1
             if self._pending[index] == 0:
-                import torch.distributed as dist
-                lo, hi, _ = self.buckets[index]
-                self._handles.append(dist.all_reduce(self.flat_grad[lo:hi], group=self.group, async_op=True))
+                ps, views = self._bucket_params[index]
+                torch._foreach_copy_(views, [p.grad for p in ps])
+                for p in ps:
+                    p.grad = None
+                if self._reduce_in_hooks:
+                    import torch.distributed as dist
+                    lo, hi, _ = self.buckets[index]
+                    self._handles.append(dist.all_reduce(self.flat_grad[lo:hi], group=self.group, async_op=True))
         return hook
 
     def step(self, obs, done, target):
-        self.flat_grad.zero_()
+        for p in self._params:
+            p.grad = None
         self._pending = [n for _, _, n in self.buckets]
         self._handles = []
         value = self.model(obs, done)
         loss = 0.5 * (value.float() - target).square().mean()     # VNetwork.loss, heads.py:114-117
         loss.backward()
+        assert not any(self._pending), "a gradient bucket never filled (a parameter received no gradient)"
         if self.world > 1:
-            if self.buckets:
+            if self._reduce_in_hooks:
                 for handle in self._handles:
                     handle.wait()
                 assert len(self._handles) == len(self.buckets), "a gradient bucket was never reduced"
