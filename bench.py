@@ -371,7 +371,7 @@ class TrainC5:
             o, _ = mo.gdelta_seq(q, k, hv(L["v"](y)), torch.exp(-F.softplus(al)), torch.sigmoid(bl),
                                  torch.zeros(B, 8, 64, 64), x["done"].float())
             h = h + torch.sigmoid(L["g1"](h)) * L["out"](L["rms"](o.reshape(B, T, -1)))
-            h = h + torch.sigmoid(L["g2"](h)) * L["down"](F.gelu(L["up"](L["n2"](h))))
+            h = h + torch.sigmoid(L["g2"](h)) * L["down"](F.gelu(L["up"](L["n2"](h)), approximate="tanh"))
         loss = 0.5 * (P["head"](h).squeeze(-1) - x["target"]).square().mean()
         loss.backward()
         return loss

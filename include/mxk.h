@@ -335,6 +335,8 @@ int mxk_adam_bf16_master(void* params, float* master, const void* grads, float* 
  * Per-head L2 normalisation of q / k for the delta-rule cell: `vectors` head vectors of
  * head_dim (64 or 128) bf16 elements, y = x / max(|x|, eps); with dy != NULL the same call
  * returns dx instead.
+ * GELU in its tanh form (flax's nn.gelu default; the FFN block's activation, blocks/ffn.py:16) over n bf16
+ * elements (n % 8 == 0): out = gelu(x), or with dy != NULL out = dy * gelu'(x).
  * Column sums of x (rows, cols) bf16 -> out (cols) bf16, added in fp32 in a fixed order through
  * `workspace` (mxk_colsum_workspace_bytes): the bias gradient of a Dense layer (the reference's
  * nn.Dense under autodiff); cols % 8 == 0, else MXK_ERR_UNSUPPORTED.
@@ -350,6 +352,7 @@ int mxk_gated_residual_bf16_bwd(const void* dy, const void* g, const void* o, vo
                                 mxk_stream_t stream);
 int mxk_l2norm_heads_bf16(const void* x, const void* dy, void* out, long long vectors, int head_dim, float eps,
                           mxk_stream_t stream);
+int mxk_gelu_bf16(const void* x, const void* dy, void* out, long long n, mxk_stream_t stream);
 size_t mxk_colsum_workspace_bytes(long long rows, int cols);
 int mxk_colsum_bf16(const void* x, void* out, void* workspace, size_t workspace_bytes, long long rows, int cols,
                     mxk_stream_t stream);

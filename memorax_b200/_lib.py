@@ -51,6 +51,7 @@ SIGNATURES = {
     "mxk_gated_residual_bf16_fwd": (_i, [_p, _p, _p, _p, ctypes.c_longlong, _p]),
     "mxk_gated_residual_bf16_bwd": (_i, [_p, _p, _p, _p, _p, ctypes.c_longlong, _p]),
     "mxk_l2norm_heads_bf16": (_i, [_p, _p, _p, ctypes.c_longlong, _i, _f, _p]),
+    "mxk_gelu_bf16": (_i, [_p, _p, _p, ctypes.c_longlong, _p]),
     "mxk_colsum_workspace_bytes": (_z, [ctypes.c_longlong, _i]),
     "mxk_colsum_bf16": (_i, [_p, _p, _p, _z, ctypes.c_longlong, _i, _p]),
     "mxk_adam_bf16": (_i, [_p, _p, _p, _p, ctypes.c_longlong, _f, _f, _f, _f, _i, _f, _p]),

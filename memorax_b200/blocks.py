@@ -48,7 +48,7 @@ class FFN(nn.Module):
         self.up, self.down = Dense(features, features * expansion_factor), Dense(features * expansion_factor, features)
 
     def forward(self, inputs, done=None, initial_carry=None):
-        return None, self.down(torch.nn.functional.gelu(self.up(inputs)))
+        return None, self.down(ops.gelu(self.up(inputs)))
 
 
 class Stack(nn.Module):

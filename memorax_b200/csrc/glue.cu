@@ -228,6 +228,44 @@ colsum_final_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ 
   }
 }
 
+// GELU in its tanh form (flax's nn.gelu default, blocks/ffn.py:16): y = x/2 (1 + tanh(c (x + 0.044715 x^3))), c = sqrt(2/pi).
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__global__ void __launch_bounds__(256)
+gelu_fwd_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, long long n8) {
+  const long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= n8) return;
+  float f[8];
+  umma::unpack8_bf16(ld_stream(x + i), f);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float v = f[e];
+    const float t = tanh_fast(0.7978845608f * fmaf(0.044715f * v, v * v, v));
+    f[e] = 0.5f * v * (1.f + t);
+  }
+  y[i] = umma::pack8_bf16(f);
+}
+// dx = dy * d/dx gelu(x)
+__global__ void __launch_bounds__(256)
+gelu_bwd_kernel(const uint4* __restrict__ x, const uint4* __restrict__ dy, uint4* __restrict__ dx, long long n8) {
+  const long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= n8) return;
+  float f[8], g[8];
+  umma::unpack8_bf16(ld_stream(x + i), f);
+  umma::unpack8_bf16(ld_stream(dy + i), g);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float v = f[e], v2 = v * v;
+    const float t = tanh_fast(0.7978845608f * fmaf(0.044715f * v, v2, v));
+    const float dt = (1.f - t * t) * 0.7978845608f * fmaf(3.f * 0.044715f, v2, 1.f);
+    g[e] *= 0.5f * (1.f + t) + 0.5f * v * dt;
+  }
+  dx[i] = umma::pack8_bf16(g);
+}
+
 // y = x + sigmoid(g) * o
 __global__ void __launch_bounds__(256)
 gated_residual_fwd_kernel(const uint4* __restrict__ x, const uint4* __restrict__ g, const uint4* __restrict__ o,
@@ -405,6 +443,20 @@ int mxk_norm_bf16_bwd(const void* x, const void* gamma, const float* mean, const
 #undef MXK_NORM_BWD
   if (int st = launch_status()) return st;
   norm_bwd_reduce_kernel<<<(D + 31) / 32, 256, 0, s>>>(part, dgamma, rms ? nullptr : dbeta, blocks, D);
+  return launch_status();
+}
+
+int mxk_gelu_bf16(const void* x, const void* dy, void* out, long long n, mxk_stream_t stream) {
+  using namespace mxk;
+  if (!x || !out) return MXK_ERR_NULL;
+  if (n <= 0 || n % 8) return MXK_ERR_DIMS;
+  for (const void* p : {x, dy, (const void*)out})
+    if (p && !aligned16(p)) return MXK_ERR_ALIGN;
+  const long long n8 = n / 8;
+  const unsigned blocks = static_cast<unsigned>((n8 + 255) / 256);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dy) gelu_bwd_kernel<<<blocks, 256, 0, s>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(dy), static_cast<uint4*>(out), n8);
+  else gelu_fwd_kernel<<<blocks, 256, 0, s>>>(static_cast<const uint4*>(x), static_cast<uint4*>(out), n8);
   return launch_status();
 }
 

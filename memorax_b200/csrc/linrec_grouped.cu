@@ -17,9 +17,12 @@ namespace mxk {
 namespace {
 
 constexpr int kBlockG = 256;
-constexpr int kUnrollG = 4;
 
-__global__ void __launch_bounds__(kBlockG, 4)
+// kUnrollG time steps of loads are in flight per thread.  4 steps at four blocks per SM when the grid fills the
+// machine; 8 steps at two blocks per SM (twice the registers) when it does not, so that a small batch still keeps
+// enough bytes in flight per SM to cover the HBM latency.
+template <int kUnrollG, int kMinBlocks>
+__global__ void __launch_bounds__(kBlockG, kMinBlocks)
 linrec_grouped_fwd_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ h0,
                           const float* __restrict__ a0, const uint8_t* __restrict__ done, float* __restrict__ h,
                           float* __restrict__ a_last, int B, int T, int D, int G, int group) {
@@ -67,7 +70,8 @@ linrec_grouped_fwd_kernel(const float* __restrict__ a, const float* __restrict__
 
 // Walks time right to left carrying c = a_{t+1} m_{t+1} g_{t+1}; the decay gradient of step t is the sum of
 // h_{t-1} g_t over the group, of which this warp contributes one partial.
-__global__ void __launch_bounds__(kBlockG, 4)
+template <int kUnrollG, int kMinBlocks>
+__global__ void __launch_bounds__(kBlockG, kMinBlocks)
 linrec_grouped_bwd_kernel(const float* __restrict__ a, const float* __restrict__ h, const float* __restrict__ h0,
                           const uint8_t* __restrict__ done, const float* __restrict__ gh,
                           const float* __restrict__ gh_last, float* __restrict__ gb, float* __restrict__ ga_part,
@@ -164,8 +168,12 @@ int mxk_linrec_f32_grouped_fwd(const float* a, const float* b, const float* h0, 
   for (const void* p : {(const void*)a, (const void*)a0, (const void*)a_last})
     if (p && (reinterpret_cast<uintptr_t>(p) & 3u)) return MXK_ERR_ALIGN;
   const long long threads = static_cast<long long>(B) * (D / 4);
-  linrec_grouped_fwd_kernel<<<static_cast<unsigned>((threads + kBlockG - 1) / kBlockG), kBlockG, 0,
-                              static_cast<cudaStream_t>(stream)>>>(a, b, h0, a0, done, h, a_last, B, T, D, G, D / G);
+  const unsigned blocks = static_cast<unsigned>((threads + kBlockG - 1) / kBlockG);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (blocks <= 3u * kNumSMs)
+    linrec_grouped_fwd_kernel<8, 2><<<blocks, kBlockG, 0, s>>>(a, b, h0, a0, done, h, a_last, B, T, D, G, D / G);
+  else
+    linrec_grouped_fwd_kernel<4, 4><<<blocks, kBlockG, 0, s>>>(a, b, h0, a0, done, h, a_last, B, T, D, G, D / G);
   return launch_status();
 }
 
@@ -187,8 +195,11 @@ int mxk_linrec_f32_grouped_bwd(const float* a, const float* h, const float* h0, 
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const long long threads = static_cast<long long>(B) * (D / 4);
-  linrec_grouped_bwd_kernel<<<static_cast<unsigned>((threads + kBlockG - 1) / kBlockG), kBlockG, 0, s>>>(
-      a, h, h0, done, gh, gh_last, gb, part, gh0, B, T, D, G, D / G);
+  const unsigned blocks = static_cast<unsigned>((threads + kBlockG - 1) / kBlockG);
+  if (blocks <= 3u * kNumSMs)
+    linrec_grouped_bwd_kernel<8, 2><<<blocks, kBlockG, 0, s>>>(a, h, h0, done, gh, gh_last, gb, part, gh0, B, T, D, G, D / G);
+  else
+    linrec_grouped_bwd_kernel<4, 4><<<blocks, kBlockG, 0, s>>>(a, h, h0, done, gh, gh_last, gb, part, gh0, B, T, D, G, D / G);
   if (int st = launch_status()) return st;
   if (ga && wpg > 1) {
     const long long n = static_cast<long long>(B) * T * G;

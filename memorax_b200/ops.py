@@ -577,6 +577,32 @@ class L2NormHeads(torch.autograd.Function):
         return dx, None, None
 
 
+class Gelu(torch.autograd.Function):
+    """tanh-form GELU (flax's ``nn.gelu`` default) of a bf16 CUDA tensor, one streaming pass each way."""
+
+    @staticmethod
+    def forward(ctx, x):
+        x = x.contiguous()
+        y = torch.empty_like(x)
+        _lib.call("mxk_gelu_bf16", _ptr(x), None, _ptr(y), x.numel(), _stream())
+        ctx.save_for_backward(x)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        dx = torch.empty_like(x)
+        _lib.call("mxk_gelu_bf16", _ptr(x), _ptr(dy.contiguous()), _ptr(dx), x.numel(), _stream())
+        return dx
+
+
+def gelu(x):
+    """``flax.linen.gelu`` (tanh form).  bf16 CUDA tensors whose size is a multiple of 8 take the fused kernel."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.numel() % 8 == 0 and x.numel() > 0:
+        return Gelu.apply(x)
+    return F.gelu(x, approximate="tanh")
+
+
 def colsum(x):
     """Sum over the rows of a (rows, cols) bf16 matrix (fp32 accumulation, fixed order), -> (cols,) bf16."""
     x = x.contiguous()

@@ -94,3 +94,20 @@ def test_colsum_and_dense_bias_gradient(shape):
         assert torch.equal(have[0], want[0]) and torch.equal(have[1], want[1])
         ref_b = ct.double().sum((0, 1))
         assert float((have[2].double() - ref_b).abs().max()) <= 2 ** -8 * float(ref_b.abs().max()) + 1e-6
+
+
+@pytest.mark.parametrize("n", [8, 4096, 1000 * 520])
+def test_gelu_tanh_form(n):
+    """Fused GELU (tanh form, flax's default) and its derivative against fp64 on the same bf16 inputs: one bf16
+    rounding of the result plus the approximate tanh."""
+    from memorax_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(n)
+    x = (torch.randn(n, device="cuda", generator=g) * 3).bfloat16().requires_grad_()
+    dy = torch.randn(n, device="cuda", generator=g).bfloat16()
+    y = ops.gelu(x)
+    (dx,) = torch.autograd.grad(y, x, dy)
+    xr = x.detach().double().requires_grad_()
+    yr = torch.nn.functional.gelu(xr, approximate="tanh")
+    (dxr,) = torch.autograd.grad(yr, xr, dy.double())
+    assert float((y.double() - yr).abs().max()) <= 2 ** -8 * float(yr.abs().max()) + 2e-3
+    assert float((dx.double() - dxr).abs().max()) <= 2 ** -8 * float(dxr.abs().max()) + 4e-3

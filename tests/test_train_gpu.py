@@ -117,7 +117,7 @@ def _cpu_restatement(model, obs, done, target):
         h = h + torch.sigmoid(lin(h, pre + ".gate")) * lin(o, c + ".output_projection")
         pre = f"torso.blocks.{i + 1}"
         y = F.layer_norm(h, h.shape[-1:], P[pre + ".module.norm.weight"], P[pre + ".module.norm.bias"])
-        y = lin(F.gelu(lin(y, pre + ".module.module.up")), pre + ".module.module.down")
+        y = lin(F.gelu(lin(y, pre + ".module.module.up"), approximate="tanh"), pre + ".module.module.down")
         h = h + torch.sigmoid(lin(h, pre + ".gate")) * y
     loss = 0.5 * (lin(h, "head").squeeze(-1) - target).square().mean()
     return loss, P
