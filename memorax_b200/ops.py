@@ -314,14 +314,14 @@ def linattn_fwd(q, k, v, s0=None, z0=None, done=None, eps=1e-6, feature_map=True
 
 
 def linattn_bwd(q, k, v, d_o, chunk_states, done=None, ds_last=None, dz_last=None, eps=1e-6, feature_map=True,
-                check=False):
-    """Cotangents ``(dq, dk, dv, ds0, dz0)`` of :func:`linattn_fwd`."""
+                check=False, need_state_grads=True):
+    """Cotangents ``(dq, dk, dv, ds0, dz0)`` of :func:`linattn_fwd` (the last two ``None`` unless wanted)."""
     q, k, v, d_o = (_dev(t, torch.bfloat16, n) for t, n in ((q, "q"), (k, "k"), (v, "v"), (d_o, "d_o")))
     ds_last, dz_last = _dev(ds_last, torch.float32, "ds_last"), _dev(dz_last, torch.float32, "dz_last")
     bsz, steps, heads, dim = q.shape
     dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
-    ds0 = torch.empty(bsz, heads, dim, dim, dtype=torch.float32, device=q.device)
-    dz0 = torch.empty(bsz, heads, dim, dtype=torch.float32, device=q.device)
+    ds0 = torch.empty(bsz, heads, dim, dim, dtype=torch.float32, device=q.device) if need_state_grads else None
+    dz0 = torch.empty(bsz, heads, dim, dtype=torch.float32, device=q.device) if need_state_grads else None
     status = _status_word(q.device)
     _lib.call("mxk_linattn_bf16_bwd", _ptr(q), _ptr(k), _ptr(v), _ptr(d_o), _ptr(chunk_states),
               _ptr(_done_bytes(done)), _ptr(ds_last), _ptr(dz_last), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(ds0),
@@ -341,12 +341,16 @@ class LinAttn(torch.autograd.Function):
         ctx.save_for_backward(q, k, v, states, done)
         ctx.eps, ctx.feature_map = eps, feature_map
         ctx.has_state = (s0 is not None, z0 is not None)
+        ctx.set_materialize_grads(False)     # an unused carry arrives as None, not as a tensor of zeros
         return o, s_last, z_last
 
     @staticmethod
     def backward(ctx, d_o, ds_last, dz_last):
         q, k, v, states, done = ctx.saved_tensors
-        dq, dk, dv, ds0, dz0 = linattn_bwd(q, k, v, d_o, states, done, ds_last, dz_last, ctx.eps, ctx.feature_map)
+        if d_o is None:
+            d_o = torch.zeros_like(q)
+        dq, dk, dv, ds0, dz0 = linattn_bwd(q, k, v, d_o, states, done, ds_last, dz_last, ctx.eps, ctx.feature_map,
+                                           need_state_grads=any(ctx.has_state))
         return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), ds0 if ctx.has_state[0] else None,
                 dz0 if ctx.has_state[1] else None, None, None, None)
 
@@ -441,8 +445,8 @@ def gdelta_fwd(q, k, v, alpha, beta, s0=None, done=None, save_states=False, chec
     return o, s_last, ((states, workspace) if save_states else None)
 
 
-def gdelta_bwd(q, k, v, alpha, beta, d_o, chunk_states, done=None, ds_last=None, check=False):
-    """Cotangents ``(dq, dk, dv, dalpha, dbeta, ds0)`` of :func:`gdelta_fwd`."""
+def gdelta_bwd(q, k, v, alpha, beta, d_o, chunk_states, done=None, ds_last=None, check=False, need_ds0=True):
+    """Cotangents ``(dq, dk, dv, dalpha, dbeta, ds0)`` of :func:`gdelta_fwd` (``ds0`` ``None`` unless wanted)."""
     q, k, v, d_o = (_dev(t, torch.bfloat16, n) for t, n in ((q, "q"), (k, "k"), (v, "v"), (d_o, "d_o")))
     alpha, beta = _dev(alpha, torch.float32, "alpha"), _dev(beta, torch.float32, "beta")
     ds_last = _dev(ds_last, torch.float32, "ds_last")
@@ -450,7 +454,7 @@ def gdelta_bwd(q, k, v, alpha, beta, d_o, chunk_states, done=None, ds_last=None,
     bsz, steps, heads, dim = q.shape
     dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
     dalpha, dbeta = torch.empty_like(alpha), torch.empty_like(beta)
-    ds0 = torch.empty(bsz, heads, dim, dim, dtype=torch.float32, device=q.device)
+    ds0 = torch.empty(bsz, heads, dim, dim, dtype=torch.float32, device=q.device) if need_ds0 else None
     status = _status_word(q.device)
     _lib.call("mxk_gdelta_bf16_bwd", _ptr(q), _ptr(k), _ptr(v), _ptr(alpha), _ptr(beta), _ptr(d_o),
               _ptr(chunk_states), _ptr(workspace), _ptr(_done_bytes(done)), _ptr(ds_last), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dalpha),
@@ -468,12 +472,16 @@ class GatedDelta(torch.autograd.Function):
         o, s_last, (states, workspace) = gdelta_fwd(q, k, v, alpha, beta, s0, done, save_states=True)
         ctx.save_for_backward(q, k, v, alpha, beta, states, workspace, done)
         ctx.has_state = s0 is not None
+        ctx.set_materialize_grads(False)     # an unused carry arrives as None, not as a tensor of zeros
         return o, s_last
 
     @staticmethod
     def backward(ctx, d_o, ds_last):
         q, k, v, alpha, beta, states, workspace, done = ctx.saved_tensors
-        dq, dk, dv, dalpha, dbeta, ds0 = gdelta_bwd(q, k, v, alpha, beta, d_o, (states, workspace), done, ds_last)
+        if d_o is None:
+            d_o = torch.zeros_like(q)
+        dq, dk, dv, dalpha, dbeta, ds0 = gdelta_bwd(q, k, v, alpha, beta, d_o, (states, workspace), done, ds_last,
+                                                    need_ds0=ctx.has_state)
         return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dalpha.to(alpha.dtype), dbeta.to(beta.dtype),
                 ds0 if ctx.has_state else None, None)
 
