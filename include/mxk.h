@@ -199,7 +199,9 @@ int mxk_mingru_f32_bwd(const float* z, const float* h_tilde, const float* x, con
  * The reference materialises every S_t; here the state is carried chunk to
  * chunk (64 tokens) in fp32 and only (B,H,d,d) ever touches memory.
  *
- *   q, k, v   (B,T,H,d) bf16, contiguous;  d = 64
+ *   q, k, v   (B,T,H,d) bf16, contiguous;  d a multiple of 8, at most 64 (else MXK_ERR_UNSUPPORTED).
+ *             The kernels work on 64-column tiles; for d < 64 the tensor maps zero-fill the
+ *             columns past d on loads and clip them on stores.
  *   s0        (B,H,d_v,d_k) fp32 carried S, NULL = zeros;  z0 (B,H,d_k), NULL = zeros
  *   o         (B,T,H,d) bf16 out
  *   s_last, z_last   next carry, optional

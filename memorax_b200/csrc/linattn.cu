@@ -43,6 +43,7 @@ struct FwdParams {
   uint4* chunk_states;  // optional residual: bf16 S^T|z panels entering every chunk
   int* status;
   int B, T, H;
+  int d;                // head dimension: a multiple of 8, at most kD; the tiles are kD wide, the rest zero
   float eps;
   int feature_map;
   CUtensorMap map_q, map_k, map_o;   // 64-token tiles as SW tiles
@@ -79,6 +80,8 @@ namespace {
 constexpr uint32_t kTmemCols = 128;
 constexpr uint32_t kUpper = 16u << 16;
 
+// kFull: head dimension = the tile width (compile-time bounds); otherwise a multiple of 8 below it.
+template <bool kFull>
 __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_constant__ FwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   FwdSmem& sm = *reinterpret_cast<FwdSmem*>(smem_raw);
@@ -88,6 +91,8 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
   const int row = warp * 16 + (lane & 15);   // lower: query row i; upper: state row k
   const int nchunks = (p.T + kC - 1) / kC;
   const uint4 zero4 = make_uint4(0, 0, 0, 0);
+  const int hd = kFull ? kD : p.d;   // head dimension
+  const int dpan = hd >> 3;
 
   if (tid == 0) {
     mbar_init(&sm.bar[0], 1);
@@ -123,14 +128,14 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
   // thread `row` owns S^T[row][.] = S[.][row]; S is (d_v, d_k) row-major in
   // memory, so a fixed v is a coalesced read across threads.
   {
-    const float* s0 = p.s0 ? p.s0 + static_cast<size_t>(bh) * kD * kD : nullptr;
-    const float* z0 = p.z0 ? p.z0 + static_cast<size_t>(bh) * kD : nullptr;
+    const float* s0 = p.s0 ? p.s0 + static_cast<size_t>(bh) * hd * hd : nullptr;
+    const float* z0 = p.z0 ? p.z0 + static_cast<size_t>(bh) * hd : nullptr;
     float vals[kDX];   // all loads first: the TMEM stores below are compiler memory barriers
 #pragma unroll
     for (int vcol = 0; vcol < kDX; ++vcol) {
       float x = 0.f;
-      if (upper) {
-        if (vcol < kD) x = s0 ? s0[vcol * kD + row] : 0.f;
+      if (upper && row < hd) {
+        if (vcol < kD) x = (s0 && vcol < hd) ? s0[vcol * hd + row] : 0.f;
         else if (vcol == kD) x = z0 ? z0[row] : 0.f;
       }
       vals[vcol] = x;
@@ -171,8 +176,11 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
       // Q, K: element-wise, so the physical vector index serves (8 vectors = one token row)
       const int vid = r * kThreads + tid;
       if (p.feature_map && (vid >> 3) < valid) {
-        sm.q[vid] = phi8(sm.q[vid]);
-        sm.k[vid] = phi8(sm.k[vid]);
+        // columns past the head dimension arrive as zeros and must stay zero (phi(0) = 1): the logical
+        // 16-byte chunk of physical chunk `vid & 7` in row `vid >> 3` of a SW tile is (vid ^ (vid >> 3)) & 7
+        const bool inside = kFull || ((vid ^ (vid >> 3)) & 7) < dpan;
+        sm.q[vid] = inside ? phi8(sm.q[vid]) : zero4;
+        sm.k[vid] = inside ? phi8(sm.k[vid]) : zero4;
       }
       if (has_reset) {
         int trow, seg;
@@ -233,13 +241,14 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
         uint4* dst = upper ? &sm.s[cur ^ 1][pn * kD + row] : &sm.k[sw_idx(row, pn & 7)];
         if (pn < kPanels || upper) *dst = pack8_bf16(m);
       }
-      if (upper && c == nchunks - 1) {
+      if (upper && c == nchunks - 1 && row < hd) {
         if (p.s_last) {
-          float* out = p.s_last + static_cast<size_t>(bh) * kD * kD;
+          float* out = p.s_last + static_cast<size_t>(bh) * hd * hd;
 #pragma unroll
-          for (int vcol = 0; vcol < kD; ++vcol) out[vcol * kD + row] = vals[vcol];
+          for (int vcol = 0; vcol < kD; ++vcol)
+            if (vcol < hd) out[vcol * hd + row] = vals[vcol];
         }
-        if (p.z_last) p.z_last[static_cast<size_t>(bh) * kD + row] = vals[kD];
+        if (p.z_last) p.z_last[static_cast<size_t>(bh) * hd + row] = vals[kD];
       }
     }
     if (has_reset) {   // live rows of phi(Q) for the inter-chunk product (the keep copy is dead now)
@@ -324,7 +333,7 @@ extern "C" int mxk_debug_phase_cycles(unsigned long long* out, int reset) {
 extern "C" {
 
 size_t mxk_linattn_chunk_states_bytes(int B, int T, int H, int d) {
-  if (B <= 0 || T <= 0 || H <= 0 || d != mxk::linattn::kD) return 0;
+  if (B <= 0 || T <= 0 || H <= 0 || d < 8 || d > mxk::linattn::kD || d % 8) return 0;
   const size_t nchunks = (static_cast<size_t>(T) + mxk::linattn::kC - 1) / mxk::linattn::kC;
   return static_cast<size_t>(B) * H * nchunks * (mxk::linattn::kPanelsX * mxk::linattn::kD) * sizeof(uint4);
 }
@@ -336,7 +345,7 @@ int mxk_linattn_bf16_fwd(const void* q, const void* k, const void* v, const floa
   using namespace mxk;
   if (!q || !k || !v || !o) return MXK_ERR_NULL;
   if (B <= 0 || T <= 0 || H <= 0 || static_cast<long long>(B) * H > 0x7fffffffLL) return MXK_ERR_DIMS;
-  if (d != kD) return MXK_ERR_UNSUPPORTED;
+  if (d < 8 || d > kD || d % 8) return MXK_ERR_UNSUPPORTED;
   for (const void* ptr : {q, k, v, (const void*)o, (const void*)chunk_states})
     if (ptr && !aligned16(ptr)) return MXK_ERR_ALIGN;
   for (const void* ptr : {(const void*)s0, (const void*)z0, (const void*)s_last, (const void*)z_last})
@@ -354,15 +363,18 @@ int mxk_linattn_bf16_fwd(const void* q, const void* k, const void* v, const floa
   prm.chunk_states = static_cast<uint4*>(chunk_states);
   prm.status = status;
   prm.B = B; prm.T = T; prm.H = H;
+  prm.d = d;
   prm.eps = eps;
   prm.feature_map = feature_map;
-  if (!tma::make_sw_map(&prm.map_q, q, B, T, H, kC) || !tma::make_sw_map(&prm.map_k, k, B, T, H, kC) ||
-      !tma::make_panel_map(&prm.map_v, v, B, T, H, kD, kC) || !tma::make_sw_map(&prm.map_o, o, B, T, H, kC))
+  // maps over the d-column tensors with 64-column boxes: the columns past d are zero-filled on loads and
+  // clipped on stores
+  if (!tma::make_sw_map(&prm.map_q, q, B, T, H, kC, d) || !tma::make_sw_map(&prm.map_k, k, B, T, H, kC, d) ||
+      !tma::make_panel_map(&prm.map_v, v, B, T, H, d, kC, kPanels) || !tma::make_sw_map(&prm.map_o, o, B, T, H, kC, d))
     return MXK_ERR_UNSUPPORTED;
-  cudaError_t e = cudaFuncSetAttribute(linattn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(sizeof(FwdSmem)));
+  auto kernel = d == kD ? linattn_fwd_kernel<true> : linattn_fwd_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FwdSmem)));
   if (e != cudaSuccess) return static_cast<int>(e);
-  linattn_fwd_kernel<<<B * H, kThreads, sizeof(FwdSmem), static_cast<cudaStream_t>(stream)>>>(prm);
+  kernel<<<B * H, kThreads, sizeof(FwdSmem), static_cast<cudaStream_t>(stream)>>>(prm);
   return launch_status();
 }
 

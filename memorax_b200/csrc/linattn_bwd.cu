@@ -53,6 +53,7 @@ struct BwdParams {
   int B, T, H;
   float eps;
   int feature_map;
+  int d;   // head dimension: a multiple of 8, at most kD; the tiles are kD wide, the rest zero
   CUtensorMap map_q, map_k, map_v, map_do;   // 64-token tiles as SW tiles
   CUtensorMap map_dq, map_dk, map_dv;        // the same for the outputs
 };
@@ -105,6 +106,8 @@ constexpr uint32_t kColLo = 0, kColHi = 64, kColP = 0, kColA = 32, kColR = 136;
 
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 
+// kFull: head dimension = the tile width (compile-time bounds); otherwise a multiple of 8 below it.
+template <bool kFull>
 __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __grid_constant__ BwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   BwdSmem& sm = *reinterpret_cast<BwdSmem*>(smem_raw);
@@ -116,6 +119,8 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
   const int row = qw * 16 + (lane & 15);
   const int nchunks = (p.T + kC - 1) / kC;
   const uint4 zero4 = make_uint4(0, 0, 0, 0);
+  const int hd = kFull ? kD : p.d;   // head dimension
+  const int dpan = hd >> 3;
 
   if (tid == 0) {
     mbar_init(&sm.bar[0], 1);
@@ -167,15 +172,15 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
   // 0..31, warpgroup 1 columns 32..63 and gz).
   const int gp0 = wg ? 4 : 0, gpn = wg ? 5 : 4;   // this warpgroup's panels of the 72-column accumulator
   {
-    const float* gs = p.ds_last ? p.ds_last + static_cast<size_t>(bh) * kD * kD : nullptr;
-    const float* gz = p.dz_last ? p.dz_last + static_cast<size_t>(bh) * kD : nullptr;
+    const float* gs = p.ds_last ? p.ds_last + static_cast<size_t>(bh) * hd * hd : nullptr;
+    const float* gz = p.dz_last ? p.dz_last + static_cast<size_t>(bh) * hd : nullptr;
     float vals[40];   // all loads first: the TMEM stores below are compiler memory barriers
 #pragma unroll
     for (int i = 0; i < 40; ++i) {
       const int vcol = gp0 * 8 + i;
       float x = 0.f;
-      if (upper && i < gpn * 8) {
-        if (vcol < kD) x = gs ? gs[vcol * kD + row] : 0.f;
+      if (upper && i < gpn * 8 && row < hd) {
+        if (vcol < kD) x = (gs && vcol < hd) ? gs[vcol * hd + row] : 0.f;
         else if (vcol == kD) x = gz ? gz[row] : 0.f;
       }
       vals[i] = x;
@@ -220,8 +225,11 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
       const int trow = vid >> 3;
       uint4 kv = sm.k[vid];
       if (p.feature_map && trow < valid) {
-        sm.q[vid] = phi8(sm.q[vid]);
-        kv = phi8(kv);
+        // columns past the head dimension arrive as zeros and must stay zero (phi(0) = 1): the logical
+        // 16-byte chunk of physical chunk `vid & 7` in row `trow` of a SW tile is (vid ^ trow) & 7
+        const bool inside = kFull || ((vid ^ trow) & 7) < dpan;
+        sm.q[vid] = inside ? phi8(sm.q[vid]) : zero4;
+        kv = inside ? phi8(kv) : zero4;
         sm.k[vid] = kv;
       }
       if (has_reset) {
@@ -422,16 +430,16 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
 #pragma unroll
           for (int pn = 0; pn < 4; ++pn) sm.pn[sw_idx(row, wg * 4 + pn)] = packed[pn];
         }
-        if (upper && c == 0) {
-          float* out = p.ds0 ? p.ds0 + static_cast<size_t>(bh) * kD * kD : nullptr;
+        if (upper && c == 0 && row < hd) {
+          float* out = p.ds0 ? p.ds0 + static_cast<size_t>(bh) * hd * hd : nullptr;
 #pragma unroll
           for (int i = 0; i < 40; ++i) {
             const int vcol = gp0 * 8 + i;
             if (i < gpn * 8) {
               if (vcol < kD) {
-                if (out) out[vcol * kD + row] = acc[i];
+                if (out && vcol < hd) out[vcol * hd + row] = acc[i];
               } else if (vcol == kD && p.dz0) {
-                p.dz0[static_cast<size_t>(bh) * kD + row] = acc[i];
+                p.dz0[static_cast<size_t>(bh) * hd + row] = acc[i];
               }
             }
           }
@@ -480,7 +488,7 @@ int mxk_linattn_bf16_bwd(const void* q, const void* k, const void* v, const void
   using namespace mxk::linattn;
   if (!q || !k || !v || !d_o || !chunk_states || !dq || !dk || !dv) return MXK_ERR_NULL;
   if (B <= 0 || T <= 0 || H <= 0 || static_cast<long long>(B) * H > 0x7fffffffLL) return MXK_ERR_DIMS;
-  if (d != kD) return MXK_ERR_UNSUPPORTED;
+  if (d < 8 || d > kD || d % 8) return MXK_ERR_UNSUPPORTED;
   for (const void* ptr : {q, k, v, d_o, chunk_states, (const void*)dq, (const void*)dk, (const void*)dv})
     if (!aligned16(ptr)) return MXK_ERR_ALIGN;
   for (const void* ptr : {(const void*)ds_last, (const void*)dz_last, (const void*)ds0, (const void*)dz0})
@@ -503,16 +511,19 @@ int mxk_linattn_bf16_bwd(const void* q, const void* k, const void* v, const void
   prm.B = B; prm.T = T; prm.H = H;
   prm.eps = eps;
   prm.feature_map = feature_map;
-  if (!tma::make_sw_map(&prm.map_q, q, B, T, H, kC) || !tma::make_sw_map(&prm.map_k, k, B, T, H, kC) ||
-      !tma::make_sw_map(&prm.map_v, v, B, T, H, kC) || !tma::make_sw_map(&prm.map_do, d_o, B, T, H, kC))
+  prm.d = d;
+  // maps over the d-column tensors with 64-column boxes: the columns past d are zero-filled on loads and
+  // clipped on stores
+  if (!tma::make_sw_map(&prm.map_q, q, B, T, H, kC, d) || !tma::make_sw_map(&prm.map_k, k, B, T, H, kC, d) ||
+      !tma::make_sw_map(&prm.map_v, v, B, T, H, kC, d) || !tma::make_sw_map(&prm.map_do, d_o, B, T, H, kC, d))
     return MXK_ERR_UNSUPPORTED;
-  if (!tma::make_sw_map(&prm.map_dq, dq, B, T, H, kC) || !tma::make_sw_map(&prm.map_dk, dk, B, T, H, kC) ||
-      !tma::make_sw_map(&prm.map_dv, dv, B, T, H, kC))
+  if (!tma::make_sw_map(&prm.map_dq, dq, B, T, H, kC, d) || !tma::make_sw_map(&prm.map_dk, dk, B, T, H, kC, d) ||
+      !tma::make_sw_map(&prm.map_dv, dv, B, T, H, kC, d))
     return MXK_ERR_UNSUPPORTED;
-  cudaError_t e = cudaFuncSetAttribute(linattn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(sizeof(BwdSmem)));
+  auto kernel = d == kD ? linattn_bwd_kernel<true> : linattn_bwd_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(BwdSmem)));
   if (e != cudaSuccess) return static_cast<int>(e);
-  linattn_bwd_kernel<<<B * H, kBwdThreads, sizeof(BwdSmem), static_cast<cudaStream_t>(stream)>>>(prm);
+  kernel<<<B * H, kBwdThreads, sizeof(BwdSmem), static_cast<cudaStream_t>(stream)>>>(prm);
   return launch_status();
 }
 

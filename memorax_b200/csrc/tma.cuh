@@ -39,14 +39,15 @@ inline EncodeTiledFn encode_tiled_fn() {
 
 // Map whose loads write `rows` x D tiles of one (b, h) sequence in panel order [c/8][t][8].
 // Coordinates of a load: {0, t0, 0, h, b}.
-inline bool make_panel_map(CUtensorMap* map, const void* base, int B, int T, int H, int D, int rows) {
+inline bool make_panel_map(CUtensorMap* map, const void* base, int B, int T, int H, int D, int rows, int box_panels = 0) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return false;
   const cuuint64_t row_bytes = static_cast<cuuint64_t>(H) * D * 2;
   const cuuint64_t dims[5] = {8, static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(D / 8), static_cast<cuuint64_t>(H),
                               static_cast<cuuint64_t>(B)};
   const cuuint64_t strides[4] = {row_bytes, 16, static_cast<cuuint64_t>(D) * 2, row_bytes * T};
-  const cuuint32_t box[5] = {8, static_cast<cuuint32_t>(rows), static_cast<cuuint32_t>(D / 8), 1, 1};
+  // box_panels (default D / 8) may exceed D / 8: the panels past the tensor are zero-filled
+  const cuuint32_t box[5] = {8, static_cast<cuuint32_t>(rows), static_cast<cuuint32_t>(box_panels > 0 ? box_panels : D / 8), 1, 1};
   const cuuint32_t elem[5] = {1, 1, 1, 1, 1};
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims, strides, box, elem,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,

@@ -270,7 +270,7 @@ class MinGRUCell(MemoroidCellBase):
 
 # --------------------------------------------------------- linear attention
 class LinearAttentionCell(MemoroidCellBase):
-    """ELU+1 linear attention (linear_attention.py:14-124).  ``head_dim`` must be 64."""
+    """ELU+1 linear attention (linear_attention.py:14-124).  ``head_dim``: a multiple of 8, at most 64."""
 
     def __init__(self, features, head_dim, num_heads, eps=1e-6, in_features=None):
         super().__init__()

@@ -291,7 +291,7 @@ def selftest_bounded_wait(polls=2, device=None):
 
 def linattn_fwd(q, k, v, s0=None, z0=None, done=None, eps=1e-6, feature_map=True, save_states=False,
                 check=False):
-    """Chunked causal linear attention; q, k, v are (B,T,H,64) bf16.  Returns
+    """Chunked causal linear attention; q, k, v are (B,T,H,d) bf16, d a multiple of 8 up to 64.  Returns
     ``(o, s_last, z_last, chunk_states)`` (chunk_states None unless asked for)."""
     q, k, v = (_dev(t, torch.bfloat16, n) for t, n in ((q, "q"), (k, "k"), (v, "v")))
     s0, z0 = _dev(s0, torch.float32, "s0"), _dev(z0, torch.float32, "z0")

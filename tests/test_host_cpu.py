@@ -46,7 +46,9 @@ def test_status_strings_and_validation_without_a_gpu(lib):
     import ctypes
     buf = (ctypes.c_char * 256)()
     p = ctypes.addressof(buf) & ~15
-    assert L.mxk_linattn_bf16_fwd(p, p, p, None, None, None, p, None, None, None, None, 1, 1, 1, 32, 1e-6, 1, None) == -4
+    assert L.mxk_linattn_bf16_fwd(p, p, p, None, None, None, p, None, None, None, None, 1, 1, 1, 128, 1e-6, 1, None) == -4
+    assert L.mxk_linattn_bf16_fwd(p, p, p, None, None, None, p, None, None, None, None, 1, 1, 1, 12, 1e-6, 1, None) == -4
+    assert L.mxk_linattn_chunk_states_bytes(2, 65, 3, 32) == 2 * 3 * 2 * 9 * 64 * 16 and L.mxk_linattn_chunk_states_bytes(1, 1, 1, 12) == 0
     assert L.mxk_linattn_bf16_fwd(p, p, p, None, None, None, p, None, None, None, None, 0, 1, 1, 64, 1e-6, 1, None) == -2
     assert L.mxk_gdelta_bf16_fwd(p, p, p, p, p, None, None, p + 2, None, None, p, 1 << 20, None, 1, 1, 1, 128, None) == -3
     assert L.mxk_gdelta_bf16_fwd(p, p, p, p, p, None, None, p, None, None, None, 0, None, 1, 1, 1, 128, None) == -5

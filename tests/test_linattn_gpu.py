@@ -33,7 +33,10 @@ def max_abs(a, b):
 @pytest.mark.parametrize("shape,p_done", [((2, 64, 2, 64), 0.0), ((2, 64, 2, 64), 0.05), ((3, 256, 4, 64), 0.01),
                                           ((2, 1, 1, 64), 0.0), ((2, 7, 3, 64), 0.3), ((2, 65, 2, 64), 0.05),
                                           ((1, 200, 2, 64), 0.02), ((2, 128, 1, 64), 1.0),
-                                          ((1, 1100, 1, 64), 0.003)])   # 18 chunks
+                                          ((1, 1100, 1, 64), 0.003),   # 18 chunks
+                                          # head dims below the 64-column tile (columns past d are zero-filled)
+                                          ((2, 130, 2, 32), 0.03), ((2, 70, 3, 16), 0.05), ((3, 64, 2, 8), 0.0),
+                                          ((1, 200, 2, 48), 0.02)])
 def test_linattn_fwd(shape, p_done):
     from memorax_b200 import ops
     q, k, v, s0, z0, done = make_case(sum(shape), *shape, p_done)
@@ -66,6 +69,29 @@ def test_linattn_golden_vectors(golden):
     assert max_abs(z_last[..., :hd], z_ref) <= 1e-2 * float(z_ref.abs().max())
 
 
+def test_linattn_golden_vectors_at_head_dim_8(golden):
+    """The reference-source vectors (head_dim 4) embedded in the smallest native head (8 columns): as in the
+    64-wide replay the host applies the feature map and pads with zeros (a padded raw column would contribute
+    phi(0) = 1), but the call goes through the d = 8 path of the kernels (tensor maps over 8-column tensors,
+    zero-filled tiles, bounded state I/O)."""
+    from memorax_b200 import ops
+    g = golden
+    bsz, steps, heads, hd = g["la_q"].shape
+    pad = lambda x: torch.nn.functional.pad(torch.from_numpy(x).float(), (0, 8 - hd))
+    fq, fk = mo.elu_plus_one(g["la_q"]), mo.elu_plus_one(g["la_k"])
+    s0 = torch.zeros(bsz, heads, 8, 8)
+    s0[:, :, :hd, :hd] = torch.from_numpy(g["la_c_S"][:, 0]).float()
+    z0 = pad(g["la_c_z"][:, 0])
+    done = torch.from_numpy(g["la_done"]).cuda()
+    o, s_last, z_last, _ = ops.linattn_fwd(pad(fq).cuda(), pad(fk).cuda(), pad(g["la_v"]).cuda(), s0.cuda(), z0.cuda(),
+                                           done, feature_map=False, check=True)
+    assert max_abs(o[..., :hd].float(), torch.from_numpy(g["la_y"])) <= ATOL
+    s_ref = torch.from_numpy(g["la_n_S"][:, 0])
+    assert max_abs(s_last[:, :, :hd, :hd], s_ref) <= 1e-2 * float(s_ref.abs().max())
+    z_ref = torch.from_numpy(g["la_n_z"][:, 0])
+    assert max_abs(z_last[..., :hd], z_ref) <= 1e-2 * float(z_ref.abs().max())
+
+
 def test_linattn_split_sequence_matches_single_call():
     from memorax_b200 import ops
     q, k, v, s0, z0, done = make_case(3, 2, 192, 2, 64, 0.02)
@@ -80,7 +106,9 @@ def test_linattn_split_sequence_matches_single_call():
 @pytest.mark.parametrize("shape,p_done", [((2, 64, 2, 64), 0.0), ((2, 64, 2, 64), 0.05), ((2, 256, 4, 64), 0.01),
                                           ((2, 1, 1, 64), 0.0), ((2, 7, 3, 64), 0.3), ((2, 65, 2, 64), 0.05),
                                           ((1, 200, 2, 64), 0.02), ((2, 128, 1, 64), 1.0),
-                                          ((1, 1100, 1, 64), 0.003)])   # 18 chunks
+                                          ((1, 1100, 1, 64), 0.003),   # 18 chunks
+                                          ((2, 130, 2, 32), 0.03), ((2, 70, 3, 16), 0.05), ((3, 64, 2, 8), 0.0),
+                                          ((1, 200, 2, 48), 0.02)])
 def test_linattn_bwd(shape, p_done):
     from memorax_b200 import ops
     q, k, v, s0, z0, done = make_case(sum(shape) + 1, *shape, p_done)
