@@ -72,6 +72,32 @@ class MemoroidCellBase(nn.Module):
         """-> (next_carry, y)"""
         raise NotImplementedError
 
+    # ---- RTRL hooks (memoroid.py:35-54); a cell without local Jacobians returns None ----
+    def local_jacobian(self, carry, z, inputs, **kwargs):
+        return None
+
+    def compute_phantom(self, sensitivity):
+        """sum over the leaves of S . (param - stop_gradient(param)): zero in value, its gradient with respect
+        to the parameters is the sensitivity (memoroid.py:38-47).  Leaves are named by attribute path."""
+        phantom = 0
+        for name, sens in sensitivity.items():
+            param = self
+            for key in name.split("/"):
+                param = getattr(param, key)
+            diff = param - param.detach()
+            term = sens * diff
+            if term.dim() > 3:            # (an empty dim tuple would mean "all axes" to torch)
+                term = term.sum(dim=tuple(range(3, term.dim())))
+            phantom = phantom + term
+        return phantom
+
+    def inject_phantom(self, carry, phantom):
+        state, *rest = carry
+        return (state.detach() + phantom, *rest)
+
+    def initialize_sensitivity(self, key, input_shape):
+        return None
+
     def scan_states(self, z, initial_carry, done):
         """The time scan without the read-out, -> (h, next_carry) as ``Memoroid.scan_fn``
         (memoroid.py:60-91).  Cells whose read-out over every state is fused into the kernel
@@ -108,23 +134,60 @@ class Memoroid(SequenceModel):
         memoroid.py:114-141): for every parameter leaf, S_t = done_t ? J_t : decay_t S_{t-1} + J_t
         with ``decay`` (B,T,H) broadcast over the leaf's parameter axes, ``jacobians[name]``
         (B,T,H,*param_shape), ``sensitivity[name]`` (B,1,H,*param_shape); returns the dict of
-        S_T, shaped like ``sensitivity``.  One real linear-recurrence launch per leaf -- the
-        reference's ``where(done, 0, decay)`` is the kernel's reset rule."""
+        S_T, shaped like ``sensitivity``.  One linear-recurrence launch per leaf -- the reference's
+        ``where(done, 0, decay)`` is the kernel's reset rule.  Real or complex (the LRU's); the decay is
+        never expanded to the leaf's width when it need not be: a decay that is one (H,) vector broadcast
+        over (B,T) (the LRU's lambda, lru.py:118) goes to the kernels as a time-invariant decay, and a
+        real decay whose leaf has a multiple of 128 entries per hidden unit takes the grouped-decay kernel."""
         bsz, steps, hid = decay.shape
+        cplx = decay.is_complex() or any(t.is_complex() for t in jacobians.values()) or \
+            any(t.is_complex() for t in sensitivity.values())
+        dt = torch.complex64 if cplx else torch.float32
+        broadcast = decay.stride(0) == 0 and decay.stride(1) == 0      # lambda.expand(B, T, H)
         out = {}
         for name in sorted(jacobians.keys()):
             jac, sens = jacobians[name], sensitivity[name]
             param_shape = tuple(jac.shape[3:])
             psize = math.prod(param_shape)
-            b_flat, s_flat = jac.float().reshape(bsz, steps, hid * psize), sens.float().reshape(bsz, hid * psize)
-            if ops.grouped_decay_supported(hid * psize, hid):
+            b_flat = jac.to(dt).reshape(bsz, steps, hid * psize)
+            s_flat = sens.to(dt).reshape(bsz, hid * psize)
+            if broadcast:
+                a = decay[0, 0].to(dt).repeat_interleave(psize)
+                h, _ = ops.linrec_fwd(a, b_flat, s_flat, None, done, want_decay=False)
+            elif not cplx and ops.grouped_decay_supported(hid * psize, hid):
                 # one decay per hidden unit, broadcast over its parameter axes inside the kernel
                 h, _ = ops.linrec_grouped_fwd(decay.float(), b_flat, s_flat, None, done, want_decay=False)
             else:
-                a = decay.float().repeat_interleave(psize, dim=-1)
+                a = decay.to(dt).repeat_interleave(psize, dim=-1)
                 h, _ = ops.linrec_fwd(a, b_flat, s_flat, None, done, want_decay=False)
             out[name] = h[:, -1:].reshape(bsz, 1, hid, *param_shape)
         return out
+
+    def local_jacobian(self, inputs, done, carry, sensitivity=None, **kwargs):
+        """One RTRL segment (``Memoroid.local_jacobian``, memoroid.py:143-176), -> (next_carry, y,
+        next_sensitivity): the carried state re-enters through the phantom term (zero in value, it routes the
+        parameters' gradients through the sensitivities), the scan and read-out run as in ``__call__``, and the
+        cell's local Jacobians are propagated from ``sensitivity`` over the segment.  ``carry`` must be given
+        (the cell's ``initialize_carry`` for a fresh start)."""
+        z = self.cell(inputs, **kwargs)
+        if sensitivity is not None:
+            carry = self.cell.inject_phantom(carry, self.cell.compute_phantom(sensitivity))
+        h, next_carry = self.cell.scan_states(z, carry, done)
+        y = self.cell.read(h, inputs, **kwargs)
+        next_sensitivity = None
+        if sensitivity is not None:
+            # the state every step starts from: the carry, then h_1 .. h_{T-1}, zero where the step resets
+            prev_state = torch.cat([carry[0].to(h[0].dtype), h[0][:, :-1]], dim=1)
+            prev_state = torch.where((done != 0)[..., None], torch.zeros_like(prev_state), prev_state)
+            local = self.cell.local_jacobian((prev_state, None), z, inputs)
+            if local is not None and local[1]:
+                next_sensitivity = self.propagate_sensitivities(local[0], local[1], sensitivity, done)
+            else:
+                next_sensitivity = sensitivity
+        return next_carry, y, next_sensitivity
+
+    def initialize_sensitivity(self, key, input_shape):
+        return self.cell.initialize_sensitivity(key, input_shape)
 
 
 # ---------------------------------------------------- complex-diagonal cells
@@ -204,6 +267,31 @@ class LRUCell(_ComplexDiagonalCell):
         # the decay is one lambda for every (b, t) (lru.py:86), so it is passed un-broadcast
         b_norm = torch.complex(self.B_real, self.B_imag) * torch.exp(self.gamma_log)[:, None]
         return self.diag_lambda(), b_norm, torch.complex(self.C_real, self.C_imag), self.D
+
+    def local_jacobian(self, carry, z, inputs, **kwargs):
+        """-> (decay (B,T,H) as a broadcast view of lambda, {leaf: d state_t / d leaf given state_{t-1}})
+        (lru.py:110-125)."""
+        prev_state = carry[0]
+        state_contrib, _ = z
+        lam = self.diag_lambda()
+        gamma_exp = torch.exp(self.gamma_log)
+        bsz, steps = inputs.shape[:2]
+        scaled_inputs = gamma_exp[None, None, :, None] * inputs[:, :, None, :].float()
+        return lam.expand(bsz, steps, self.hidden_dim), {
+            "nu_log": -torch.exp(self.nu_log) * lam * prev_state,
+            "theta_log": 1j * torch.exp(self.theta_log) * lam * prev_state,
+            "gamma_log": state_contrib,
+            "B_real": scaled_inputs,
+            "B_imag": 1j * scaled_inputs,
+        }
+
+    def initialize_sensitivity(self, key, input_shape):
+        *batch, _ = input_shape
+        dev = self.nu_log.device
+        z = lambda *shape: torch.zeros(*batch, 1, *shape, dtype=torch.complex64, device=dev)
+        h = self.hidden_dim
+        return {"nu_log": z(h), "theta_log": z(h), "gamma_log": z(h), "B_real": z(h, self.features),
+                "B_imag": z(h, self.features)}
 
     def initialize_carry(self, key, input_shape):
         *batch, _ = input_shape

@@ -303,6 +303,33 @@ def mamba_seq(hidden, b_proj, c_proj, dt, a_neg, d_skip, h0, done, a0=None):
     return torch.stack(ys, dim=1), h, acc
 
 
+def lru_rtrl_seq(x, done, c_state, nu_log, theta_log, gamma_log, b_mat, c_mat, d_skip, sens):
+    """One RTRL segment of the LRU cell, sequentially in time (Memoroid.local_jacobian, memoroid.py:143-176,
+    with LRUCell.__call__ / read / local_jacobian, lru.py:78-125, and _propagate_sensitivities,
+    memoroid.py:114-141).  ``b_mat`` (H,F), ``c_mat`` (F,H) complex; ``sens`` a dict of (B,1,H,*param) leaves.
+    Returns ``(h_last (B,H), y (B,T,F), next_sens)``.  The phantom term is zero in value and is left out."""
+    lam = torch.exp(torch.complex(-torch.exp(nu_log), torch.exp(theta_log)))
+    gam = torch.exp(gamma_log)
+    bu = x.to(lam.dtype) @ (b_mat * gam[:, None]).t()                      # (B,T,H), lru.py:82-84
+    h = c_state
+    s = {k: v[:, 0].clone() for k, v in sens.items()}
+    ys = []
+    for t in range(x.shape[1]):
+        reset = done[:, t] > 0
+        prev = torch.where(reset[:, None], torch.zeros_like(h), h)         # memoroid.py:158-168
+        jac = {"nu_log": -torch.exp(nu_log) * lam * prev, "theta_log": 1j * torch.exp(theta_log) * lam * prev,
+               "gamma_log": bu[:, t],
+               "B_real": (gam[None, :, None] * x[:, t, None, :]).to(lam.dtype),
+               "B_imag": 1j * (gam[None, :, None] * x[:, t, None, :])}
+        h = torch.where(reset[:, None], bu[:, t], lam * h + bu[:, t])      # memoroid.py:72-85 with lru.py:92-95
+        for name in s:
+            decay = lam.reshape((1, -1) + (1,) * (s[name].dim() - 2))
+            keep = (~reset).reshape((-1,) + (1,) * (s[name].dim() - 1))
+            s[name] = torch.where(keep, decay * s[name], torch.zeros_like(s[name])) + jac[name]
+        ys.append((h @ c_mat.t()).real + d_skip * x[:, t])
+    return h, torch.stack(ys, dim=1), {k: v[:, None] for k, v in s.items()}
+
+
 def jax_cotangent(grad):
     """torch.autograd's gradient of a real loss w.r.t. a complex tensor is the
     conjugate of what JAX's reverse mode (and hence the reference) returns."""

@@ -106,6 +106,10 @@ class _Module:
     def sow(self, *a, **k):
         return None
 
+    @property
+    def variables(self):
+        return {"params": self._params}
+
 
 class _Dense(_Module):
     """Bias-free projection with lazily drawn float64 weights."""
@@ -368,6 +372,31 @@ def main():
     nxt0, y0 = model(x, done, None)
     out.update(ml_default_c_m=carry0[3], ml_default_n_C=nxt0[0], ml_default_n_n=nxt0[2], ml_default_n_m=nxt0[3],
                ml_default_h_tilde=(y0 / silu).reshape(bsz, steps, heads, hd))
+
+    # ---- RTRL through Memoroid.local_jacobian with the LRU cell (memoroid.py:143-176, lru.py:110-139):
+    #      phantom injection, scan, read-out, the cell's local Jacobians and their propagation.  Own generator,
+    #      so that the draws of every case above stay what they were. ----
+    rng2 = np.random.default_rng(20250217)
+    bsz, steps, feat, hid = 3, 9, 5, 4
+    cell = lru.LRUCell(features=feat, hidden_dim=hid)
+    for name, lo, hi in (("nu_log", 0.05, 0.6), ("theta_log", 0.05, 0.6)):
+        cell._params[name] = np.log(rng2.uniform(lo, hi, hid))
+        setattr(cell, name, cell._params[name])
+    model = memoroid.Memoroid(cell=cell)
+    x = rng2.normal(size=(bsz, steps, feat))
+    done = done_patterns(rng2, bsz, steps)
+    cplx = lambda *s: rng2.normal(size=s) + 1j * rng2.normal(size=s)
+    carry = (cplx(bsz, 1, hid), cplx(bsz, 1, hid) * 0.3)
+    sens = {"nu_log": cplx(bsz, 1, hid), "theta_log": cplx(bsz, 1, hid), "gamma_log": cplx(bsz, 1, hid),
+            "B_real": cplx(bsz, 1, hid, feat), "B_imag": cplx(bsz, 1, hid, feat)}
+    nxt, y, nsens = model.local_jacobian(x, done, carry, sens)
+    zero_sens = cell.initialize_sensitivity(0, (bsz, feat))
+    _, _, nsens0 = model.local_jacobian(x, done, carry, zero_sens)
+    out.update(lj_x=x, lj_done=done, lj_c_state=carry[0], lj_c_decay=carry[1], lj_n_state=nxt[0], lj_n_decay=nxt[1],
+               lj_y=y, lj_nu_log=cell.nu_log, lj_theta_log=cell.theta_log, lj_gamma_log=cell.gamma_log,
+               lj_B=cell.B_real + 1j * cell.B_imag, lj_C=cell.C_real + 1j * cell.C_imag, lj_D=cell.D)
+    for name in sens:
+        out["lj_s_" + name], out["lj_ns_" + name], out["lj_ns0_" + name] = sens[name], nsens[name], nsens0[name]
 
     np.savez_compressed(args.out, **out)
     print("wrote", args.out, "with", len(out), "arrays")

@@ -1,6 +1,7 @@
 """The host-side mirror of the reference interface: Memoroid(cell)(inputs, done,
 initial_carry) -> (next_carry, y) with the reference's carry pytrees, carry
 threading across calls (memoroid.py:89) and gradients through the CUDA ops."""
+import numpy as np
 import pytest
 import torch
 
@@ -27,7 +28,7 @@ def test_lru_module_matches_oracle_and_threads_carry():
     state, lam = cell(x)
     h_ref, a_ref = mo.linrec_seq(lam.detach().cpu().to(torch.complex128), state.detach().cpu().to(torch.complex128),
                                  torch.zeros(3, 32, dtype=torch.complex128), done.cpu().double())
-    assert float((h_last[:, 0].cpu() - h_ref[:, -1]).abs().max()) <= 1e-5 * float(h_ref.abs().max())
+    assert float((h_last[:, 0].detach().cpu() - h_ref[:, -1]).abs().max()) <= 1e-5 * float(h_ref.abs().max())
     assert float((a_last[:, 0].cpu() - a_ref).abs().max()) <= 1e-5
     # one call == two calls threading the carry
     c1, y1 = model(x[:, :9], done[:, :9])
@@ -103,6 +104,111 @@ def test_propagate_sensitivities_matches_the_reference_vectors():
     assert nxt["w"].shape == ref.shape
     err = float((nxt["w"].double().cpu() - ref).abs().max())
     assert err <= 1e-5 * max(1.0, float(ref.abs().max())), err
+
+
+def _lru_from_golden(g):
+    from memorax_b200.memoroid import LRUCell
+    feat, hid = g["lj_x"].shape[-1], g["lj_nu_log"].shape[0]
+    cell = LRUCell(feat, hid).cuda()
+    f32 = lambda a: torch.from_numpy(np.asarray(a)).float().cuda()
+    with torch.no_grad():
+        cell.nu_log.copy_(f32(g["lj_nu_log"])); cell.theta_log.copy_(f32(g["lj_theta_log"]))
+        cell.gamma_log.copy_(f32(g["lj_gamma_log"]))
+        cell.B_real.copy_(f32(g["lj_B"].real)); cell.B_imag.copy_(f32(g["lj_B"].imag))
+        cell.C_real.copy_(f32(g["lj_C"].real)); cell.C_imag.copy_(f32(g["lj_C"].imag))
+        cell.D.copy_(f32(g["lj_D"]))
+    return cell
+
+
+def test_local_jacobian_matches_the_reference_vectors():
+    """Memoroid.local_jacobian with the LRU cell (phantom injection, scan, read-out, local Jacobians, propagated
+    sensitivities) against the vectors produced by the reference's own memoroid.py / lru.py."""
+    import os
+    from memorax_b200.memoroid import Memoroid
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "memoroid_golden.npz"))
+    model = Memoroid(_lru_from_golden(g))
+    c64 = lambda a: torch.from_numpy(np.asarray(a)).to(torch.complex64).cuda()
+    names = ["nu_log", "theta_log", "gamma_log", "B_real", "B_imag"]
+    x = torch.from_numpy(g["lj_x"]).float().cuda()
+    done = torch.from_numpy(g["lj_done"]).cuda() > 0
+    carry = (c64(g["lj_c_state"]), c64(g["lj_c_decay"]))
+    close = lambda got, ref, what: float((got.detach().cpu().to(torch.complex128) - torch.from_numpy(np.asarray(ref))).abs().max()) \
+        <= 2e-5 * max(1.0, float(np.abs(ref).max())) or pytest.fail(what)
+    for tag in ("ns", "ns0"):
+        sens = {n: c64(g["lj_s_" + n]) if tag == "ns" else torch.zeros_like(c64(g["lj_s_" + n])) for n in names}
+        (n_state, n_decay), y, nxt = model.local_jacobian(x, done, carry, sens)
+        close(n_state, g["lj_n_state"], "next state")
+        close(n_decay, g["lj_n_decay"], "next decay")
+        close(y, g["lj_y"], "y")
+        for n in names:
+            assert nxt[n].shape == sens[n].shape
+            close(nxt[n], g["lj_" + tag + "_" + n], n)
+    zero = model.initialize_sensitivity(None, (x.shape[0], x.shape[-1]))
+    assert sorted(zero) == sorted(names) and all(zero[n].shape == c64(g["lj_s_" + n]).shape for n in names)
+
+
+def test_rtrl_sensitivities_are_the_state_derivatives():
+    """From a parameter-independent start and zero sensitivity, two chained RTRL segments must give
+    d state_T / d leaf for every leaf: compared with fp64 autograd through the sequential oracle (real and
+    imaginary parts of the state differentiated separately; each hidden unit depends on its own rows only)."""
+    from memorax_b200.memoroid import Memoroid, LRUCell
+    torch.manual_seed(21)
+    feat, hid, bsz, steps = 3, 4, 2, 12
+    cell = LRUCell(feat, hid, r_min=0.5, r_max=0.95, max_phase=1.0).cuda()
+    model = Memoroid(cell)
+    x = torch.randn(bsz, steps, feat, device="cuda")
+    done = torch.zeros(bsz, steps, dtype=torch.bool, device="cuda")
+    done[1, 5] = True
+    carry = cell.initialize_carry(None, (bsz, feat))
+    carry = tuple(c.cuda() for c in carry)
+    sens = model.initialize_sensitivity(None, (bsz, feat))
+    with torch.no_grad():
+        carry, _, sens = model.local_jacobian(x[:, :7], done[:, :7], carry, sens)
+        carry, _, sens = model.local_jacobian(x[:, 7:], done[:, 7:], carry, sens)
+    # oracle: h_T as a function of the leaves, fp64
+    leaves = {n: getattr(cell, n).detach().double().cpu().requires_grad_() for n in
+              ("nu_log", "theta_log", "gamma_log", "B_real", "B_imag")}
+    lam = torch.exp(torch.complex(-torch.exp(leaves["nu_log"]), torch.exp(leaves["theta_log"])))
+    b_norm = torch.complex(leaves["B_real"], leaves["B_imag"]) * torch.exp(leaves["gamma_log"])[:, None]
+    bu = x.double().cpu().to(torch.complex128) @ b_norm.t()
+    h_ref, _ = mo.linrec_seq(lam, bu, torch.zeros(bsz, hid, dtype=torch.complex128), done.double().cpu())
+    h_t = h_ref[:, -1]
+    for name, leaf in leaves.items():
+        for b in range(bsz):
+            for j in range(hid):
+                d_re = torch.autograd.grad(h_t[b, j].real, leaf, retain_graph=True)[0][j]
+                d_im = torch.autograd.grad(h_t[b, j].imag, leaf, retain_graph=True)[0][j]
+                want = torch.complex(d_re, d_im)
+                got = sens[name][b, 0, j].cpu().to(torch.complex128)
+                assert float((got - want).abs().max()) <= 1e-4 * max(1.0, float(want.abs().max())), (name, b, j)
+
+
+def test_rtrl_gradient_equals_backpropagation_through_time():
+    """What the phantom term is for: the gradient of a loss on the second segment's outputs, taken with the
+    carry detached and the first segment's sensitivities injected, equals the gradient of the same loss when
+    both segments are differentiated through in one call."""
+    from memorax_b200.memoroid import Memoroid, LRUCell
+    torch.manual_seed(22)
+    feat, hid, bsz, steps, cut = 4, 8, 3, 20, 9
+    cell = LRUCell(feat, hid, r_min=0.5, r_max=0.95, max_phase=1.0).cuda()
+    model = Memoroid(cell)
+    x = torch.randn(bsz, steps, feat, device="cuda")
+    done = torch.zeros(bsz, steps, dtype=torch.bool, device="cuda")
+    done[2, 3] = True
+    w = torch.randn(bsz, steps - cut, feat, device="cuda")
+    carry0 = tuple(c.cuda() for c in cell.initialize_carry(None, (bsz, feat)))
+    _, y_full = model(x, done, carry0)
+    (y_full[:, cut:] * w).sum().backward()
+    bptt = {n: p.grad.clone() for n, p in cell.named_parameters()}
+    cell.zero_grad()
+    with torch.no_grad():
+        carry, _, sens = model.local_jacobian(x[:, :cut], done[:, :cut], carry0,
+                                              model.initialize_sensitivity(None, (bsz, feat)))
+    _, y2, _ = model.local_jacobian(x[:, cut:], done[:, cut:], carry, sens)
+    (y2 * w).sum().backward()
+    for n, p in cell.named_parameters():
+        err = float((p.grad - bptt[n]).abs().max())
+        assert err <= 2e-4 * max(1.0, float(bptt[n].abs().max())), (n, err)
 
 
 def test_propagate_sensitivities_grouped_decay_path():

@@ -76,6 +76,23 @@ def test_golden_rtrl_multiplicative_reset(golden):
     np.testing.assert_allclose(h[:, -1].numpy().reshape(bsz, 1, hid, psz), g["rt_next"], **TOL)
 
 
+def test_golden_lru_rtrl_segment(golden):
+    """lru_rtrl_seq against the vectors produced by the reference's own Memoroid.local_jacobian with its
+    LRUCell (phantom injection, scan, read-out, local Jacobians, sensitivity propagation)."""
+    g = golden
+    C = lambda a: torch.from_numpy(np.asarray(a))
+    names = ["nu_log", "theta_log", "gamma_log", "B_real", "B_imag"]
+    for tag in ("s", "s0"):
+        sens = {n: (C(g["lj_s_" + n]) if tag == "s" else torch.zeros_like(C(g["lj_s_" + n]))) for n in names}
+        h_last, y, nxt = mo.lru_rtrl_seq(C(g["lj_x"]), C(g["lj_done"]), C(g["lj_c_state"])[:, 0], C(g["lj_nu_log"]),
+                                         C(g["lj_theta_log"]), C(g["lj_gamma_log"]), C(g["lj_B"]), C(g["lj_C"]),
+                                         C(g["lj_D"]), sens)
+        np.testing.assert_allclose(h_last.numpy(), g["lj_n_state"][:, 0], **TOL)
+        np.testing.assert_allclose(y.numpy(), g["lj_y"], **TOL)
+        for n in names:
+            np.testing.assert_allclose(nxt[n].numpy(), g[("lj_ns_" if tag == "s" else "lj_ns0_") + n], **TOL)
+
+
 # ------------------------------------------------- layer 1 == layer 2, any bracketing
 def _done(rng, bsz, steps, p=0.2):
     d = (rng.random((bsz, steps)) < p).astype(np.float64)
