@@ -547,27 +547,47 @@ class mLSTMCell(MemoroidCellBase):
 
 
 # ----------------------------------------------------------------------- S5
-class S5Cell(_ComplexDiagonalCell):
-    """Diagonal state-space cell (s5.py:18-149): the same (state, decay) operator
-    as the LRU with a discretised, time-invariant ``lambda_bar`` (ZOH or bilinear,
-    hippo.py:34-50).  The HiPPO-DPLR initialisation of the reference is
-    initialisation-time CPU work outside this path; ``lambda`` starts at
-    ``-1/2 + i pi n`` here."""
+def make_dplr_hippo(n):
+    """HiPPO-LegS in diagonal-plus-low-rank form (hippo.py:6-32): eigenvalues ``lambda`` (n,) and eigenvectors
+    ``v`` (n,n) of the normal part S = A + p p^T of the HiPPO matrix (real part: the mean of S's diagonal,
+    -1/2; imaginary parts: the eigenvalues of the Hermitian -i S).  Initialisation-time host arithmetic in
+    float64, returned as complex128 tensors."""
+    idx = torch.arange(n, dtype=torch.float64)
+    q = torch.sqrt(1.0 + 2.0 * idx)
+    a = -(torch.tril(q[:, None] * q[None, :]) - torch.diag(idx))
+    p = torch.sqrt(idx + 0.5)
+    s_mat = a + p[:, None] * p[None, :]
+    lambda_real = torch.diagonal(s_mat).mean() * torch.ones(n, dtype=torch.float64)
+    lambda_imag, v = torch.linalg.eigh(s_mat.to(torch.complex128) * (-1j))
+    return torch.complex(lambda_real, lambda_imag), v
 
-    def __init__(self, features, state_size, discretization="zoh", dt_min=0.001, dt_max=0.1, step_rescale=1.0):
+
+class S5Cell(_ComplexDiagonalCell):
+    """Diagonal state-space cell (s5.py:29-149): the same (state, decay) operator as the LRU with a discretised,
+    time-invariant ``lambda_bar`` (ZOH or bilinear, hippo.py:34-50).  Initialised as the reference's ``setup``:
+    ``lambda`` from the HiPPO-DPLR eigenvalues, ``B`` a lecun-normal matrix taken into the eigenbasis
+    (``V^H B``, initializers/hippo.py:19-26), ``C`` a lecun-normal complex matrix times ``V``
+    (initializers/hippo.py:29-37), ``log_step`` uniform in [log dt_min, log dt_max]."""
+
+    def __init__(self, features, state_size, discretization="zoh", dt_min=0.001, dt_max=0.1, step_rescale=1.0,
+                 clip_eigens=False):
         super().__init__()
         self.features, self.state_size = features, state_size
-        self.discretization, self.step_rescale = discretization, step_rescale
-        self.lambda_real = nn.Parameter(torch.full((state_size,), -0.5))
-        self.lambda_imag = nn.Parameter(math.pi * torch.arange(state_size, dtype=torch.float32))
-        self.B = nn.Parameter(torch.randn(state_size, features, 2) / math.sqrt(2 * features))
-        self.C = nn.Parameter(torch.randn(features, state_size, 2) * math.sqrt(0.5))
+        self.discretization, self.step_rescale, self.clip_eigens = discretization, step_rescale, clip_eigens
+        lam, v = make_dplr_hippo(state_size)
+        self.lambda_real = nn.Parameter(lam.real.float())
+        self.lambda_imag = nn.Parameter(lam.imag.float())
+        b = torch.randn(state_size, features, dtype=torch.float64) / math.sqrt(features)          # lecun normal
+        self.B = nn.Parameter(torch.view_as_real(v.conj().t() @ b.to(torch.complex128)).float())
+        c = torch.view_as_complex(torch.randn(features, state_size, 2, dtype=torch.float64) / math.sqrt(state_size))
+        self.C = nn.Parameter(torch.view_as_real(c @ v).float())
         self.d = nn.Parameter(torch.randn(features))
         u = torch.rand(state_size, 1)
         self.log_step = nn.Parameter(u * (math.log(dt_max) - math.log(dt_min)) + math.log(dt_min))
 
     def _discretized(self):
-        lam = torch.complex(self.lambda_real, self.lambda_imag)
+        lam_re = torch.clamp(self.lambda_real, max=-1e-4) if self.clip_eigens else self.lambda_real
+        lam = torch.complex(lam_re, self.lambda_imag)
         b_tilde = torch.view_as_complex(self.B.contiguous())
         step = (self.step_rescale * torch.exp(self.log_step[:, 0])).to(torch.complex64)
         if self.discretization == "zoh":

@@ -330,6 +330,28 @@ def lru_rtrl_seq(x, done, c_state, nu_log, theta_log, gamma_log, b_mat, c_mat, d
     return h, torch.stack(ys, dim=1), {k: v[:, None] for k, v in s.items()}
 
 
+def s5_discretize(lam, b_tilde, step, kind):
+    """(lambda_bar, b_bar) of the diagonal state-space cell (hippo.py:34-50): zero-order hold
+    exp(lambda dt), (lambda_bar - 1) / lambda * B; or bilinear (1 + dt/2 lambda) / (1 - dt/2 lambda), dt / (1 - dt/2 lambda) * B."""
+    step = step.to(lam.dtype)
+    if kind == "zoh":
+        lambda_bar = torch.exp(lam * step)
+        return lambda_bar, ((lambda_bar - 1.0) / lam)[:, None] * b_tilde
+    bl = 1.0 / (1.0 - step / 2.0 * lam)
+    return bl * (1.0 + step / 2.0 * lam), (bl * step)[:, None] * b_tilde
+
+
+def dplr_hippo_lambda(n):
+    """Eigenvalues the S5 cell starts from (hippo.py:6-32): real part mean(diag(A + p p^T)), imaginary parts the
+    eigenvalues of the Hermitian -i (A + p p^T), A the HiPPO-LegS matrix."""
+    idx = np.arange(n, dtype=np.float64)
+    q = np.sqrt(1.0 + 2.0 * idx)
+    a = -(np.tril(q[:, None] * q[None, :]) - np.diag(idx))
+    p = np.sqrt(idx + 0.5)
+    s_mat = a + p[:, None] * p[None, :]
+    return np.mean(np.diag(s_mat)) + 1j * np.linalg.eigvalsh(s_mat * (-1j))
+
+
 def jax_cotangent(grad):
     """torch.autograd's gradient of a real loss w.r.t. a complex tensor is the
     conjugate of what JAX's reverse mode (and hence the reference) returns."""

@@ -137,8 +137,11 @@ class _Identity(_Module):
 def install_stand_ins(reference_dir):
     jnp = types.ModuleType("jax.numpy")
     jnp.__dict__.update({k: getattr(np, k) for k in dir(np) if not k.startswith("_")})
-    jnp.zeros = lambda shape, dtype=None: np.zeros(shape, dtype=np.complex128 if dtype == np.complex64 else F64)
-    jnp.ones = lambda shape, dtype=None: np.ones(shape, dtype=np.complex128 if dtype == np.complex64 else F64)
+    is_cplx = lambda dtype: dtype in (np.complex64, np.complex128)
+    jnp.zeros = lambda shape, dtype=None: np.zeros(shape, dtype=np.complex128 if is_cplx(dtype) else F64)
+    jnp.ones = lambda shape, dtype=None: np.ones(shape, dtype=np.complex128 if is_cplx(dtype) else F64)
+    # everything runs in double precision: the reference's float32 / complex64 casts keep the value
+    jnp.float32, jnp.complex64 = np.float64, np.complex128
     jnp.full = lambda shape, v, dtype=None: np.full(shape, v, dtype=F64)
 
     lax = types.ModuleType("jax.lax")
@@ -154,6 +157,9 @@ def install_stand_ins(reference_dir):
 
     jnn = types.ModuleType("jax.nn")
     jnn.softplus = _softplus
+    jnn_inits = types.ModuleType("jax.nn.initializers")       # names s5.py imports; used only in setup()
+    jnn_inits.lecun_normal = jnn_inits.normal = lambda *a, **k: None
+    jnn.initializers = jnn_inits
 
     jax = types.ModuleType("jax")
     jax.numpy, jax.lax, jax.tree, jax.random, jax.nn = jnp, lax, tree, rnd, jnn
@@ -183,10 +189,13 @@ def install_stand_ins(reference_dir):
     ftyping.Dtype = ftyping.Initializer = object
 
     mods = {"jax": jax, "jax.numpy": jnp, "jax.lax": lax, "jax.tree": tree, "jax.random": rnd, "jax.nn": jnn,
+            "jax.nn.initializers": jnn_inits,
             "flax": flax, "flax.linen": nn, "flax.linen.initializers": inits, "flax.typing": ftyping}
     # layers / initialisers that mlstm.py imports by name but only uses in setup(), which is bypassed
     net_inits = types.ModuleType("memorax.networks.initializers")
     net_inits.wang = lambda *a, **k: None
+    net_inits.init_cv = net_inits.init_v_inv_b = net_inits.log_step = net_inits.truncated_standard_normal = \
+        lambda *a, **k: None
     net_layers = types.ModuleType("memorax.networks.layers")
     net_layers.BlockDiagonalDense = net_layers.MultiHeadLayerNorm = _Identity
     mods["memorax.networks.initializers"], mods["memorax.networks.layers"] = net_inits, net_layers
@@ -397,6 +406,35 @@ def main():
                lj_B=cell.B_real + 1j * cell.B_imag, lj_C=cell.C_real + 1j * cell.C_imag, lj_D=cell.D)
     for name in sens:
         out["lj_s_" + name], out["lj_ns_" + name], out["lj_ns0_" + name] = sens[name], nsens[name], nsens0[name]
+
+    # ---- S5: the reference's own discretisation (hippo.py:34-50), elements, operator and read-out
+    #      (s5.py:97-143) under Memoroid, and the HiPPO-DPLR eigenvalues its setup() starts from
+    #      (hippo.py:20-32).  setup() is bypassed: parameters are set by hand. ----
+    s5 = importlib.import_module(sm + "s5")
+    hippo = importlib.import_module("memorax.networks.hippo")
+    rng3 = np.random.default_rng(20250218)
+    bsz, steps, feat, nstate = 3, 10, 4, 6
+    x = rng3.normal(size=(bsz, steps, feat))
+    done = done_patterns(rng3, bsz, steps)
+    cplx = lambda *s: rng3.normal(size=s) + 1j * rng3.normal(size=s)
+    carry = (cplx(bsz, 1, nstate), cplx(bsz, 1, nstate) * 0.3)
+    params = dict(lambda_real=-np.abs(rng3.normal(size=nstate)) - 0.1, lambda_imag=rng3.normal(size=nstate) * 3.0,
+                  B=rng3.normal(size=(nstate, feat, 2)) * 0.5, C=rng3.normal(size=(feat, nstate, 2)) * 0.5,
+                  d=rng3.normal(size=feat), log_step=np.log(rng3.uniform(0.001, 0.1, size=(nstate, 1))))
+    out.update(s5_x=x, s5_done=done, s5_c_state=carry[0], s5_c_decay=carry[1], **{"s5_p_" + k: v for k, v in params.items()})
+    for disc in ("zoh", "bilinear"):
+        cell = object.__new__(s5.S5Cell)
+        cell.features, cell.state_size, cell.discretization = feat, nstate, disc
+        cell.clip_eigens, cell.step_rescale, cell.dtype = False, 1.0, F64
+        for k, v in params.items():
+            setattr(cell, k, v)
+        model = memoroid.Memoroid(cell=cell)
+        z = cell(x)
+        nxt, y = model(x, done, carry)
+        out.update({f"s5_{disc}_z_state": z[0], f"s5_{disc}_lambda_bar": z[1][0, 0], f"s5_{disc}_n_state": nxt[0],
+                    f"s5_{disc}_n_decay": nxt[1], f"s5_{disc}_y": y})
+    for n in (4, 16):
+        out[f"hippo_lambda_{n}"] = hippo.make_dplr_hippo(n)[0]
 
     np.savez_compressed(args.out, **out)
     print("wrote", args.out, "with", len(out), "arrays")

@@ -89,6 +89,30 @@ def test_s5_module_matches_oracle(disc):
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in cell.parameters())
 
 
+@pytest.mark.parametrize("disc", ["zoh", "bilinear"])
+def test_s5_matches_the_reference_vectors(disc):
+    """S5Cell under Memoroid (discretisation, elements, scan with a non-trivial carry, read-out) against the
+    vectors produced by the reference's own s5.py / hippo.py."""
+    import os
+    from memorax_b200.memoroid import Memoroid, S5Cell
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "memoroid_golden.npz"))
+    nstate, feat = g["s5_p_B"].shape[:2]
+    cell = S5Cell(feat, nstate, discretization=disc).cuda()
+    f32 = lambda a: torch.from_numpy(np.asarray(a)).float().cuda()
+    with torch.no_grad():
+        cell.lambda_real.copy_(f32(g["s5_p_lambda_real"])); cell.lambda_imag.copy_(f32(g["s5_p_lambda_imag"]))
+        cell.B.copy_(f32(g["s5_p_B"])); cell.C.copy_(f32(g["s5_p_C"])); cell.d.copy_(f32(g["s5_p_d"]))
+        cell.log_step.copy_(f32(g["s5_p_log_step"]))
+    c64 = lambda a: torch.from_numpy(np.asarray(a)).to(torch.complex64).cuda()
+    (n_state, n_decay), y = Memoroid(cell)(f32(g["s5_x"]), torch.from_numpy(g["s5_done"]).cuda() > 0,
+                                           (c64(g["s5_c_state"]), c64(g["s5_c_decay"])))
+    close = lambda got, ref, what: float((got.detach().cpu().to(torch.complex128) - torch.from_numpy(np.asarray(ref))).abs().max()) \
+        <= 2e-5 * max(1.0, float(np.abs(ref).max())) or pytest.fail(what)
+    close(n_state, g[f"s5_{disc}_n_state"], "next state")
+    close(n_decay, g[f"s5_{disc}_n_decay"], "next decay")
+    close(y, g[f"s5_{disc}_y"], "y")
+
+
 def test_propagate_sensitivities_matches_the_reference_vectors():
     """Memoroid.propagate_sensitivities against the vectors produced by the reference's own
     ``_propagate_sensitivities`` source (tests/golden/make_golden.py)."""

@@ -93,6 +93,37 @@ def test_golden_lru_rtrl_segment(golden):
             np.testing.assert_allclose(nxt[n].numpy(), g[("lj_ns_" if tag == "s" else "lj_ns0_") + n], **TOL)
 
 
+@pytest.mark.parametrize("disc", ["zoh", "bilinear"])
+def test_golden_s5_discretisation_scan_and_read(golden, disc):
+    """s5_discretize + linrec_seq + the read-out against the vectors produced by the reference's own S5Cell
+    (s5.py:97-143 with hippo.py:34-50) under Memoroid."""
+    g = golden
+    C = lambda a: torch.from_numpy(np.asarray(a))
+    lam = torch.complex(C(g["s5_p_lambda_real"]), C(g["s5_p_lambda_imag"]))
+    b_tilde, c_tilde = torch.view_as_complex(C(g["s5_p_B"])), torch.view_as_complex(C(g["s5_p_C"]))
+    lambda_bar, b_bar = mo.s5_discretize(lam, b_tilde, torch.exp(C(g["s5_p_log_step"])[:, 0]), disc)
+    np.testing.assert_allclose(lambda_bar.numpy(), g[f"s5_{disc}_lambda_bar"], **TOL)
+    x = C(g["s5_x"])
+    z = x.to(torch.complex128) @ b_bar.t()
+    np.testing.assert_allclose(z.numpy(), g[f"s5_{disc}_z_state"], **TOL)
+    h, a_last = mo.linrec_seq(lambda_bar, z, C(g["s5_c_state"])[:, 0], C(g["s5_done"]), C(g["s5_c_decay"])[:, 0])
+    np.testing.assert_allclose(h[:, -1].numpy(), g[f"s5_{disc}_n_state"][:, 0], **TOL)
+    np.testing.assert_allclose(a_last.numpy(), g[f"s5_{disc}_n_decay"][:, 0], **TOL)
+    y = (h @ c_tilde.t()).real + C(g["s5_p_d"]) * x
+    np.testing.assert_allclose(y.numpy(), g[f"s5_{disc}_y"], **TOL)
+
+
+@pytest.mark.parametrize("n", [4, 16])
+def test_golden_hippo_eigenvalues(golden, n):
+    """The oracle's and the host mirror's HiPPO-DPLR eigenvalues against the reference's make_dplr_hippo."""
+    ref = np.sort_complex(golden[f"hippo_lambda_{n}"])
+    np.testing.assert_allclose(np.sort_complex(mo.dplr_hippo_lambda(n)), ref, rtol=1e-9, atol=1e-9)
+    from memorax_b200.memoroid import make_dplr_hippo
+    lam, v = make_dplr_hippo(n)
+    np.testing.assert_allclose(np.sort_complex(lam.numpy()), ref, rtol=1e-9, atol=1e-9)
+    np.testing.assert_allclose((v.conj().t() @ v).numpy(), np.eye(n), atol=1e-9)      # unitary eigenbasis
+
+
 # ------------------------------------------------- layer 1 == layer 2, any bracketing
 def _done(rng, bsz, steps, p=0.2):
     d = (rng.random((bsz, steps)) < p).astype(np.float64)
