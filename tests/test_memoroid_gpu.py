@@ -57,7 +57,9 @@ def test_mingru_module_default_carry_is_neg_inf_and_finite():
 def test_linear_attention_and_deltanet_modules_run_and_thread_carry():
     from memorax_b200.memoroid import DeltaNetCell, LinearAttentionCell, Memoroid
     torch.manual_seed(2)
-    for cell in (LinearAttentionCell(features=32, head_dim=64, num_heads=2), DeltaNetCell(features=32, head_dim=128, num_heads=2)):
+    for cell in (LinearAttentionCell(features=32, head_dim=64, num_heads=2),
+                 LinearAttentionCell(features=32, head_dim=16, num_heads=4),
+                 DeltaNetCell(features=32, head_dim=128, num_heads=2)):
         model = Memoroid(cell).cuda()
         x, done = torch.randn(2, 128, 32, device="cuda"), _done(2, 128, 0.02)
         carry, y = model(x, done)
