@@ -262,6 +262,44 @@ int mxk_mlstm_f32_bwd(const float* q, const float* k, const float* v, const floa
                       size_t workspace_bytes, int B, int T, int H, int d, float eps, mxk_stream_t stream);
 
 /* ---------------------------------------------------------------------------
+ * mLSTM in chunked form on the tensor cores: the same recurrence and reset rule as mxk_mlstm_f32_*
+ * (mlstm.py:163-240 under Memoroid.scan_fn) for bf16 q, k, v and a bf16 read-out, gates and carried
+ * state in fp32 -- the numerical class of mxk_linattn_bf16_* (bf16 operands, fp32 accumulation), about
+ * ten times the throughput of the fp32 kernels.  64-token chunks, one CTA per (batch, head).
+ *
+ *   q, k, v        (B,T,H,d) bf16, contiguous; k already divided by sqrt(d); d a multiple of 8, at most 64
+ *   log_i, log_f   (B,T,H) fp32
+ *   c0 (B,H,d,d) fp32 indexed [key][value], n0 (B,H,d), m0 (B,H), f0 (B,H): carried state, NULL = the
+ *                  cell's initialize_carry (zeros, m = -1e9)
+ *   h              (B,T,H,d) bf16 out;  c_last, n_last, m_last, f_last: next carry, optional
+ *   m_steps        optional (B,T,H) fp32 out: the stabiliser after every step, and
+ *   chunk_states   optional, mxk_mlstm_bf16_chunk_states_bytes(...) bytes: the bf16 state entering every
+ *                  chunk; both are the residuals the backward call needs
+ *   status         optional device int, set non-zero if a bounded device-side wait gave up
+ * ------------------------------------------------------------------------- */
+size_t mxk_mlstm_bf16_chunk_states_bytes(int B, int T, int H, int d);
+int mxk_mlstm_bf16_fwd(const void* q, const void* k, const void* v, const float* log_i, const float* log_f,
+                       const float* c0, const float* n0, const float* m0, const float* f0, const uint8_t* done,
+                       void* h, float* c_last, float* n_last, float* m_last, float* f_last, float* m_steps,
+                       void* chunk_states, int* status, int B, int T, int H, int d, float eps, mxk_stream_t stream);
+
+/* Reverse mode of mxk_mlstm_bf16_fwd.  The stabiliser is a gauge of the recurrence: the decay factors are
+ * differentiated with it held fixed, and its one real effect on the read-out (eps exp(m_t) in the denominator) and
+ * on the stabilised next carry is propagated through m_t = max(m_{t-1} + log_f_t, log_i_t) inside the kernel.
+ *   dh             (B,T,H,d) bf16 cotangent of h
+ *   c_last, n_last the forward call's next carry (required when dc_last / dn_last is given), m_steps and
+ *                  chunk_states its residuals
+ *   dc_last (B,H,d,d) [key][value], dn_last (B,H,d), dm_last (B,H): cotangents of the next carry, NULL = zeros
+ *   dq, dk, dv     (B,T,H,d) bf16 out;  dlog_i, dlog_f (B,T,H) fp32 out;  dc0, dn0, dm0 optional
+ * `done` and the carry's log_f leaf have no cotangent. */
+int mxk_mlstm_bf16_bwd(const void* q, const void* k, const void* v, const float* log_i, const float* log_f,
+                       const float* c0, const float* n0, const float* m0, const uint8_t* done, const void* dh,
+                       const float* c_last, const float* n_last, const float* m_steps, const void* chunk_states,
+                       const float* dc_last, const float* dn_last, const float* dm_last, void* dq, void* dk, void* dv,
+                       float* dlog_i, float* dlog_f, float* dc0, float* dn0, float* dm0, int* status, int B, int T,
+                       int H, int d, float eps, mxk_stream_t stream);
+
+/* ---------------------------------------------------------------------------
  * Gated delta rule (DeltaNet with a scalar forget gate).  The reference has no
  * such cell; this is the new MemoroidCellBase-shaped mixer, defined per head
  * (S is d_v x d_k, a_t = done_t ? 0 : alpha_t) by

@@ -51,6 +51,9 @@ SIGNATURES = {
     "mxk_gated_residual_bf16_fwd": (_i, [_p, _p, _p, _p, ctypes.c_longlong, _p]),
     "mxk_gated_residual_bf16_bwd": (_i, [_p, _p, _p, _p, _p, ctypes.c_longlong, _p]),
     "mxk_l2norm_heads_bf16": (_i, [_p, _p, _p, ctypes.c_longlong, _i, _f, _p]),
+    "mxk_mlstm_bf16_chunk_states_bytes": (_z, [_i, _i, _i, _i]),
+    "mxk_mlstm_bf16_fwd": (_i, [_p] * 18 + [_i, _i, _i, _i, _f, _p]),
+    "mxk_mlstm_bf16_bwd": (_i, [_p] * 26 + [_i, _i, _i, _i, _f, _p]),
     "mxk_gelu_bf16": (_i, [_p, _p, _p, ctypes.c_longlong, _p]),
     "mxk_colsum_workspace_bytes": (_z, [ctypes.c_longlong, _i]),
     "mxk_colsum_bf16": (_i, [_p, _p, _p, _z, ctypes.c_longlong, _i, _p]),

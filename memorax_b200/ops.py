@@ -486,6 +486,91 @@ class GatedDelta(torch.autograd.Function):
                 ds0 if ctx.has_state else None, None)
 
 
+# --------------------------------------------------- mLSTM on the tensor cores
+def mlstm_tc_fwd(q, k, v, log_i, log_f, c0=None, n0=None, m0=None, f0=None, done=None, eps=1e-6, save=False,
+                 check=False):
+    """Chunked mLSTM scan + read-out on the tensor cores; q, k, v (B,T,H,d) bf16 (k already divided by sqrt(d)),
+    d a multiple of 8 up to 64; gates (B,T,H) fp32.  Returns ``(h, c_last, n_last, m_last, f_last, residual)``
+    with ``residual = (m_steps, chunk_states)`` when ``save`` (else None)."""
+    q, k, v = (_dev(t, torch.bfloat16, n) for t, n in ((q, "q"), (k, "k"), (v, "v")))
+    log_i, log_f = _dev(log_i, torch.float32, "log_i"), _dev(log_f, torch.float32, "log_f")
+    c0, n0, m0, f0 = (_dev(t, torch.float32, n) for t, n in ((c0, "c0"), (n0, "n0"), (m0, "m0"), (f0, "f0")))
+    bsz, steps, heads, dim = q.shape
+    assert log_i.shape == (bsz, steps, heads) and log_f.shape == log_i.shape
+    dev = q.device
+    h = torch.empty_like(q)
+    c_last = torch.empty(bsz, heads, dim, dim, dtype=torch.float32, device=dev)
+    n_last = torch.empty(bsz, heads, dim, dtype=torch.float32, device=dev)
+    m_last = torch.empty(bsz, heads, dtype=torch.float32, device=dev)
+    f_last = torch.empty(bsz, heads, dtype=torch.float32, device=dev)
+    m_steps = states = None
+    if save:
+        m_steps = torch.empty(bsz, steps, heads, dtype=torch.float32, device=dev)
+        states = torch.empty(_lib.lib.mxk_mlstm_bf16_chunk_states_bytes(bsz, steps, heads, dim), dtype=torch.uint8, device=dev)
+    status = _status_word(dev)
+    _lib.call("mxk_mlstm_bf16_fwd", _ptr(q), _ptr(k), _ptr(v), _ptr(log_i), _ptr(log_f), _ptr(c0), _ptr(n0), _ptr(m0),
+              _ptr(f0), _ptr(_done_bytes(done)), _ptr(h), _ptr(c_last), _ptr(n_last), _ptr(m_last), _ptr(f_last),
+              _ptr(m_steps), _ptr(states), _ptr(status), bsz, steps, heads, dim, float(eps), _stream())
+    if check:
+        _check_status(status, "mxk_mlstm_bf16_fwd")
+    return h, c_last, n_last, m_last, f_last, ((m_steps, states) if save else None)
+
+
+def mlstm_tc_bwd(q, k, v, log_i, log_f, c0, n0, m0, done, dh, c_last, n_last, residual, dc_last=None, dn_last=None,
+                 dm_last=None, eps=1e-6, need_state_grads=True, check=False):
+    """Cotangents ``(dq, dk, dv, dlog_i, dlog_f, dc0, dn0, dm0)`` of :func:`mlstm_tc_fwd`; ``residual`` is what the
+    forward call returned with ``save``, ``c_last`` / ``n_last`` its next carry."""
+    q, k, v, dh = (_dev(t, torch.bfloat16, n) for t, n in ((q, "q"), (k, "k"), (v, "v"), (dh, "dh")))
+    log_i, log_f = _dev(log_i, torch.float32, "log_i"), _dev(log_f, torch.float32, "log_f")
+    c0, n0, m0 = (_dev(t, torch.float32, n) for t, n in ((c0, "c0"), (n0, "n0"), (m0, "m0")))
+    dc_last, dn_last, dm_last = (_dev(t, torch.float32, n) for t, n in ((dc_last, "dc_last"), (dn_last, "dn_last"),
+                                                                        (dm_last, "dm_last")))
+    m_steps, states = residual
+    bsz, steps, heads, dim = q.shape
+    dev = q.device
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    dli, dlf = torch.empty_like(log_i), torch.empty_like(log_f)
+    dc0 = dn0 = dm0 = None
+    if need_state_grads:
+        dc0 = torch.empty(bsz, heads, dim, dim, dtype=torch.float32, device=dev)
+        dn0 = torch.empty(bsz, heads, dim, dtype=torch.float32, device=dev)
+        dm0 = torch.empty(bsz, heads, dtype=torch.float32, device=dev)
+    status = _status_word(dev)
+    _lib.call("mxk_mlstm_bf16_bwd", _ptr(q), _ptr(k), _ptr(v), _ptr(log_i), _ptr(log_f), _ptr(c0), _ptr(n0), _ptr(m0),
+              _ptr(_done_bytes(done)), _ptr(dh), _ptr(c_last), _ptr(n_last), _ptr(m_steps), _ptr(states), _ptr(dc_last),
+              _ptr(dn_last), _ptr(dm_last), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dli), _ptr(dlf), _ptr(dc0), _ptr(dn0),
+              _ptr(dm0), _ptr(status), bsz, steps, heads, dim, float(eps), _stream())
+    if check:
+        _check_status(status, "mxk_mlstm_bf16_bwd")
+    return dq, dk, dv, dli, dlf, dc0, dn0, dm0
+
+
+class MLSTMTensorCore(torch.autograd.Function):
+    """(q, k, v, log_i, log_f, c0, n0, m0, f0, done) -> (h, c_last, n_last, m_last, f_last) on the tensor cores
+    (bf16 q, k, v, h).  The carry's log_f leaf has no cotangent."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, log_i, log_f, c0, n0, m0, f0, done, eps):
+        h, c_last, n_last, m_last, f_last, residual = mlstm_tc_fwd(q, k, v, log_i, log_f, c0, n0, m0, f0, done, eps, save=True)
+        ctx.save_for_backward(q, k, v, log_i, log_f, c0, n0, m0, done, c_last, n_last, *residual)
+        ctx.eps = eps
+        ctx.has_state = any(t is not None for t in (c0, n0, m0))
+        ctx.set_materialize_grads(False)
+        ctx.mark_non_differentiable(f_last)
+        return h, c_last, n_last, m_last, f_last
+
+    @staticmethod
+    def backward(ctx, dh, dc_last, dn_last, dm_last, _df_last):
+        q, k, v, log_i, log_f, c0, n0, m0, done, c_last, n_last, m_steps, states = ctx.saved_tensors
+        if dh is None:
+            dh = torch.zeros_like(q)
+        dq, dk, dv, dli, dlf, dc0, dn0, dm0 = mlstm_tc_bwd(q, k, v, log_i, log_f, c0, n0, m0, done, dh, c_last, n_last,
+                                                           (m_steps, states), dc_last, dn_last, dm_last, ctx.eps,
+                                                           need_state_grads=ctx.has_state)
+        return (dq, dk, dv, dli, dlf, dc0 if c0 is not None else None, dn0 if n0 is not None else None,
+                dm0 if m0 is not None else None, None, None, None)
+
+
 # ------------------------------------------------------ fused row-wise glue
 def _glue_ok(x, dim):
     return x.is_cuda and x.dtype == torch.bfloat16 and dim % 256 == 0 and dim <= 1024

@@ -249,7 +249,7 @@ def gdelta_seq(q, k, v, alpha, beta, s0, done):
     return torch.stack(out, dim=1), s
 
 
-def mlstm_seq(q, k, v, log_i, log_f, c0, n0, m0, done, f0=None, eps=1e-6):
+def mlstm_seq(q, k, v, log_i, log_f, c0, n0, m0, done, f0=None, eps=1e-6, with_den=False):
     """Stabilised mLSTM (mlstm.py:163-229 under the reset rule of ``Memoroid.scan_fn``), sequentially:
       m_t = max(m_{t-1} + log_f_t, log_i_t)
       C_t = exp(m_{t-1} + log_f_t - m_t) C_{t-1} + exp(log_i_t - m_t) k_t v_t^T      (n_t likewise with k_t)
@@ -259,8 +259,9 @@ def mlstm_seq(q, k, v, log_i, log_f, c0, n0, m0, done, f0=None, eps=1e-6):
 
     q, k, v (B,T,H,d); log_i, log_f (B,T,H); c0 (B,H,d,d) indexed [key, value]; n0 (B,H,d); m0, f0 (B,H).
     Returns h (B,T,H,d) and the next carry (C_T, F_T, n_T, m_T) with F the summed log forget gates
-    since the last reset (the carry's log_f leaf)."""
+    since the last reset (the carry's log_f leaf); with ``with_den`` also the (B,T,H) denominators."""
     c, n, m = c0, n0, m0
+    dens = []
     f = torch.zeros_like(m0) if f0 is None else f0
     neg_inf = torch.full_like(m0, -float("inf"))
     out = []
@@ -275,6 +276,9 @@ def mlstm_seq(q, k, v, log_i, log_f, c0, n0, m0, done, f0=None, eps=1e-6):
         m = m_new
         den = torch.maximum((q[:, t] * n).sum(-1).abs(), torch.exp(-m)) + eps
         out.append(torch.einsum("bhj,bhjk->bhk", q[:, t], c) / den[..., None])
+        dens.append(den)
+    if with_den:
+        return torch.stack(out, dim=1), (c, f, n, m), torch.stack(dens, dim=1)
     return torch.stack(out, dim=1), (c, f, n, m)
 
 

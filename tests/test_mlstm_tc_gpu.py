@@ -1,0 +1,147 @@
+"""GPU parity of the chunked tensor-core mLSTM (bf16 q, k, v, h; fp32 gates and state) against the fp64 CPU
+oracle, through the C-ABI.  Tolerance: 2e-2 max-abs on the read-out and on dq, dk, dv (scaled by the tensor's
+max-abs where that exceeds 1), 1e-2 of the max-abs for the fp32 state, stabiliser and gate cotangents."""
+import pytest
+import torch
+
+from oracle import memoroid_oracle as mo
+
+pytestmark = pytest.mark.gpu
+ATOL = 2e-2
+
+
+def make_case(seed, bsz, steps, heads, dim, p_done, carry=True, gate_shift=0.0):
+    gen = torch.Generator().manual_seed(seed)
+    mk = lambda *s: torch.randn(*s, generator=gen)
+    q = mk(bsz, steps, heads, dim).bfloat16()
+    k = (mk(bsz, steps, heads, dim) / dim ** 0.5).bfloat16()
+    v = mk(bsz, steps, heads, dim).bfloat16()
+    log_i = mk(bsz, steps, heads) * 1.0 + gate_shift
+    log_f = -torch.nn.functional.softplus(-(mk(bsz, steps, heads) * 2.0 + 2.0))
+    done = torch.rand(bsz, steps, generator=gen) < p_done
+    if steps > 3:
+        done[0, 0] = True
+        done[-1, 1:3] = True
+    if carry:
+        c0, n0 = mk(bsz, heads, dim, dim) * 0.3, mk(bsz, heads, dim) * 0.3
+        m0, f0 = mk(bsz, heads) * 0.5, -mk(bsz, heads).abs()
+    else:
+        c0 = n0 = m0 = f0 = None
+    return q, k, v, log_i, log_f, c0, n0, m0, f0, done
+
+
+def err(a, b):
+    return float((a.detach().double().cpu() - b.detach().double().cpu()).abs().max())
+
+
+def tol(ref, rel):
+    return rel * max(1.0, float(ref.abs().max()))
+
+
+def oracle(q, k, v, log_i, log_f, c0, n0, m0, f0, done):
+    bsz, _, heads, dim = q.shape
+    D = lambda t: t.double()
+    zc = torch.zeros(bsz, heads, dim, dim, dtype=torch.float64) if c0 is None else D(c0)
+    zn = torch.zeros(bsz, heads, dim, dtype=torch.float64) if n0 is None else D(n0)
+    zm = torch.full((bsz, heads), -1e9, dtype=torch.float64) if m0 is None else D(m0)
+    return mo.mlstm_seq(D(q), D(k), D(v), D(log_i), D(log_f), zc, zn, zm, done.double(), None if f0 is None else D(f0))
+
+
+SHAPES = [((2, 64, 2, 64), 0.0, True), ((2, 64, 2, 64), 0.05, True), ((3, 256, 4, 64), 0.01, True),
+          ((2, 1, 1, 64), 0.0, True), ((2, 7, 3, 64), 0.3, False), ((2, 65, 2, 64), 0.05, True),
+          ((1, 200, 2, 64), 0.02, False), ((2, 128, 1, 64), 1.0, True), ((1, 700, 1, 64), 0.004, True),
+          ((2, 130, 2, 32), 0.03, True), ((2, 70, 3, 16), 0.05, False)]
+
+
+@pytest.mark.parametrize("shape,p_done,carry", SHAPES)
+def test_mlstm_tc_fwd(shape, p_done, carry):
+    from memorax_b200 import ops
+    case = make_case(sum(shape), *shape, p_done, carry)
+    h_ref, (c_ref, f_ref, n_ref, m_ref) = oracle(*case)
+    cu = lambda t: None if t is None else t.cuda()
+    h, c_last, n_last, m_last, f_last, _ = ops.mlstm_tc_fwd(*[cu(t) for t in case], check=True)
+    assert err(h.float(), h_ref) <= tol(h_ref, ATOL)
+    assert err(c_last, c_ref) <= tol(c_ref, 1e-2) and err(n_last, n_ref) <= tol(n_ref, 1e-2)
+    assert err(m_last, m_ref) <= 1e-4 * max(1.0, float(m_ref.abs().max())) and err(f_last, f_ref) <= 1e-4 * max(1.0, float(f_ref.abs().max()))
+
+
+def test_mlstm_tc_large_input_gates():
+    """Input gates around e^8: the stabiliser carries the scale and the weights stay below one.  The read-out
+    divides by |q . n| wherever that exceeds exp(-m_t) ~ e^-8, so rows whose normaliser nearly cancels are
+    ill-conditioned in any bf16 arithmetic; they are compared through the state and the stabiliser only, the
+    rows with a denominator of at least one element-wise."""
+    from memorax_b200 import ops
+    case = make_case(5, 2, 192, 2, 64, 0.02, True, gate_shift=8.0)
+    q, k, v, log_i, log_f, c0, n0, m0, f0, done = case
+    D = lambda t: t.double()
+    h_ref, (c_ref, _, n_ref, m_ref), den = mo.mlstm_seq(D(q), D(k), D(v), D(log_i), D(log_f), D(c0), D(n0), D(m0),
+                                                        done.double(), D(f0), with_den=True)
+    cu = lambda t: None if t is None else t.cuda()
+    h, c_last, n_last, m_last, _, _ = ops.mlstm_tc_fwd(*[cu(t) for t in case], check=True)
+    assert torch.isfinite(h.float()).all()
+    well = den >= 1.0
+    assert int(well.sum()) > 100
+    diff = (h.float().cpu().double() - h_ref).abs()
+    assert float(diff[well].max()) <= tol(h_ref[well], ATOL)
+    assert err(c_last, c_ref) <= tol(c_ref, 1e-2) and err(n_last, n_ref) <= tol(n_ref, 1e-2)
+    assert err(m_last, m_ref) <= 1e-4 * float(m_ref.abs().max())
+
+
+BWD_SHAPES = [((2, 64, 2, 64), 0.0, True), ((2, 64, 2, 64), 0.05, True), ((2, 256, 4, 64), 0.01, True),
+              ((2, 1, 1, 64), 0.0, True), ((2, 7, 3, 64), 0.3, False), ((2, 65, 2, 64), 0.05, True),
+              ((1, 200, 2, 64), 0.02, False), ((2, 128, 1, 64), 1.0, True), ((1, 700, 1, 64), 0.004, True),
+              ((2, 130, 2, 32), 0.03, True), ((2, 70, 3, 16), 0.05, False)]
+
+
+@pytest.mark.parametrize("shape,p_done,carry", BWD_SHAPES)
+def test_mlstm_tc_bwd(shape, p_done, carry):
+    from memorax_b200 import ops
+    q, k, v, log_i, log_f, c0, n0, m0, f0, done = make_case(sum(shape) + 1, *shape, p_done, carry)
+    bsz, steps, heads, dim = shape
+    gen = torch.Generator().manual_seed(77)
+    dh = torch.randn(*shape, generator=gen).bfloat16()
+    dc_last = torch.randn(bsz, heads, dim, dim, generator=gen) * 0.1
+    dn_last = torch.randn(bsz, heads, dim, generator=gen) * 0.1
+    dm_last = torch.randn(bsz, heads, generator=gen) * 0.1
+    D = lambda t: t.double()
+    zc = torch.zeros(bsz, heads, dim, dim, dtype=torch.float64) if c0 is None else D(c0)
+    zn = torch.zeros(bsz, heads, dim, dtype=torch.float64) if n0 is None else D(n0)
+    zm = torch.full((bsz, heads), -1e9, dtype=torch.float64) if m0 is None else D(m0)
+    leaves = [t.clone().requires_grad_() for t in (D(q), D(k), D(v), D(log_i), D(log_f), zc, zn, zm)]
+    h_ref, (c_ref, _, n_ref, m_ref) = mo.mlstm_seq(*leaves, done.double(), None if f0 is None else D(f0))
+    ((h_ref * D(dh)).sum() + (c_ref * D(dc_last)).sum() + (n_ref * D(dn_last)).sum() + (m_ref * D(dm_last)).sum()).backward()
+    cu = lambda t: None if t is None else t.cuda()
+    h, c_last, n_last, _, _, residual = ops.mlstm_tc_fwd(cu(q), cu(k), cu(v), cu(log_i), cu(log_f), cu(c0), cu(n0), cu(m0), cu(f0),
+                                                         cu(done), save=True, check=True)
+    outs = ops.mlstm_tc_bwd(cu(q), cu(k), cu(v), cu(log_i), cu(log_f), cu(c0), cu(n0), cu(m0), cu(done), cu(dh), c_last, n_last,
+                            residual, cu(dc_last), cu(dn_last), cu(dm_last), check=True)
+    names = ["dq", "dk", "dv", "dlog_i", "dlog_f", "dc0", "dn0", "dm0"]
+    for got, leaf, name in zip(outs, leaves, names):
+        if not carry and name in ("dc0", "dn0", "dm0"):
+            continue          # default carry: the cotangent of the implied (zero, -1e9) state is not meaningful
+        ref = leaf.grad
+        rel = ATOL if name in ("dq", "dk", "dv") else 1e-2
+        bound = tol(ref, rel)
+        if name == "dm0":
+            # dm0 = <dC_0, C_0> + <dn_0, n_0> + (explicit path): a sum of d^2 products that largely cancel, each
+            # carrying the bf16 error of dC_0; the bound is relative to the gross sum
+            gross = (leaves[5].grad.abs() * leaves[5].detach().abs()).sum((-1, -2)) + (leaves[6].grad.abs() * leaves[6].detach().abs()).sum(-1)
+            bound = 1e-2 * max(1.0, float(gross.max()))
+        e = err(got.float(), ref)
+        assert e <= bound, f"{name}: {e:.4f} > {bound:.4f} (ref max {float(ref.abs().max()):.3f})"
+
+
+def test_mlstm_tc_autograd_function():
+    from memorax_b200 import ops
+    q, k, v, log_i, log_f, c0, n0, m0, f0, done = make_case(9, 2, 96, 2, 64, 0.03, True)
+    w = torch.randn(2, 96, 2, 64, generator=torch.Generator().manual_seed(1))
+    D = lambda t: t.double()
+    leaves = [t.clone().requires_grad_() for t in (D(q), D(k), D(v), D(log_i), D(log_f), D(c0), D(n0), D(m0))]
+    h_ref, _ = mo.mlstm_seq(*leaves, done.double(), D(f0))
+    (h_ref * w.double()).sum().backward()
+    dev = [t.cuda().requires_grad_() for t in (q, k, v, log_i, log_f, c0, n0, m0)]
+    h, *_ = ops.MLSTMTensorCore.apply(*dev, f0.cuda(), done.cuda(), 1e-6)
+    (h.float() * w.cuda()).sum().backward()
+    for got, leaf in zip(dev, leaves):
+        rel = ATOL if got.dtype == torch.bfloat16 else 1e-2
+        assert err(got.grad.float(), leaf.grad) <= tol(leaf.grad, rel)
