@@ -494,6 +494,49 @@ class MlstmN1:
         return h
 
 
+class MlstmTcN1(MlstmN1):
+    """The mLSTM workload n1 through the chunked tensor-core kernels: same shapes and gate distributions, q, k, v and
+    the read-out in bf16 (the numerical class of configuration 2), gates and state fp32."""
+    name = "n1_mlstm_tensor_core_fwd_bwd"
+    dtype = "bf16"
+    dominant = "mlstm_tc_bwd_kernel"
+    cpu_sample_batch = 4
+
+    def host_inputs(self, seed_offset=0, device="cpu"):
+        x = super().host_inputs(seed_offset, device)
+        for key in ("q", "k", "v", "dh"):
+            x[key] = x[key].bfloat16()
+        return x
+
+    def algorithmic_bytes(self):
+        n = self.B * self.T * self.H
+        gates = 2 * 4 * n
+        # fwd: q, k, v in, h out (bf16), gates, per-step stabiliser out; bwd: q, k, v, dh in, dq, dk, dv out, gates in, gate gradients out
+        return {"mlstm_tc_fwd_kernel": 4 * 2 * self.D * n + gates + 4 * n,
+                "mlstm_tc_bwd_kernel": 7 * 2 * self.D * n + 2 * gates + 4 * n}
+
+    def algorithmic_flops(self):
+        n = self.B * self.T * self.H
+        c, d = 64, self.D
+        # per token-head: QK^T, P~(V|1), Q S, K^T(V|1) forward; P, dA, R, Y and the four phase-2 groups backward
+        return {"mlstm_tc_fwd_kernel": n * 2 * (c * d + c * (d + 8) + d * (d + 8) + d * (d + 8)),
+                "mlstm_tc_bwd_kernel": n * 2 * (2 * c * d + 2 * d * (d + 8) + 2 * c * d + 2 * d * (d + 16) + 2 * c * d + d * (d + 8))}
+
+    def step(self, x, ops, mark=None):
+        h, c_last, n_last, _, _, res = ops.mlstm_tc_fwd(x["q"], x["k"], x["v"], x["log_i"], x["log_f"], None, None, None, None,
+                                                        x["done"], save=True)
+        if mark:
+            mark[0].record()
+        out = ops.mlstm_tc_bwd(x["q"], x["k"], x["v"], x["log_i"], x["log_f"], None, None, None, x["done"], x["dh"], c_last,
+                               n_last, res, need_state_grads=False)
+        if mark:
+            mark[1].record()
+        return (h, out[0], out[1], out[2], out[3], out[4])
+
+    def cpu_step(self, x):
+        return super().cpu_step({k: (v.float() if v.dtype == torch.bfloat16 else v) for k, v in x.items()})
+
+
 class LruLayerN4:
     """The LRU layer as the reference's Memoroid runs it at inference (lru.py:78-108 around memoroid.py:93-109):
     input projection B_norm u, the complex scan of configuration 4 (B=1024, T=1024, N=512 states), read-out
@@ -598,7 +641,7 @@ class LruLayerN4:
             return torch.matmul(h, torch.complex(cell.C_real, cell.C_imag).t()).real + cell.D * x["x"]
 
 
-WORKLOADS = {"n4": LruLayerN4, "n1": MlstmN1, "c2": LinAttnC2, "c3": GDeltaC3, "c4": LruC4, "c1": LinRecC1, "c5": TrainC5, "n2": MambaN2}
+WORKLOADS = {"n4": LruLayerN4, "n1": MlstmN1, "n1t": MlstmTcN1, "c2": LinAttnC2, "c3": GDeltaC3, "c4": LruC4, "c1": LinRecC1, "c5": TrainC5, "n2": MambaN2}
 
 
 # ------------------------------------------------------------ clock sampling
@@ -964,7 +1007,7 @@ def run_gpu_arm(args):
     if args.ops:
         per_op[args.workload] = {k: head[k] for k in ("workload", "batch_per_gpu", "ms_per_step", "tokens_per_s",
                                                       "dtype", "blocks", "clocks", "roofline")}
-        for name in ("c1", "c3", "c4", "c5", "n1", "n2", "n4"):
+        for name in ("c1", "c3", "c4", "c5", "n1", "n1t", "n2", "n4"):
             if name == args.workload:
                 continue
             per_op[name] = hz.run_op(WORKLOADS[name], None, args.steps, args.warmup, args.min_seconds)

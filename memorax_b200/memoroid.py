@@ -465,10 +465,15 @@ class mLSTMCell(MemoroidCellBase):
     learnable skip, SiLU(z) gate, output projection); the element ``(k (x) v, log_f, k, m = log_i)`` of
     mlstm.py:198-203 stays factored as ``(k, v, log_i, log_f)`` -- the (B,T,H,d,d) outer products and the
     per-step memories never exist -- and scan + read-out are one kernel.  ``head_dim`` = hidden_dim /
-    num_heads must be 32, 64 or 128."""
+    num_heads must be 32, 64 or 128 for the float32 kernels (the reference's arithmetic).  With
+    ``tensor_cores=True`` the scan runs in chunked form on the tensor cores instead: q, k, v and the read-out in
+    bf16, gates and state in fp32 (the numerical class of the linear-attention kernels), head_dim a multiple of 8
+    up to 64, about ten times the throughput."""
 
-    def __init__(self, features, hidden_dim, num_heads=4, conv_kernel_size=4, in_features=None, eps=1e-6):
+    def __init__(self, features, hidden_dim, num_heads=4, conv_kernel_size=4, in_features=None, eps=1e-6,
+                 tensor_cores=False):
         super().__init__()
+        self.tensor_cores = tensor_cores
         if hidden_dim % num_heads:
             raise ValueError(f"hidden_dim ({hidden_dim}) must be divisible by num_heads ({num_heads}).")
         self.features, self.hidden_dim, self.num_heads, self.eps = features, hidden_dim, num_heads, eps
@@ -538,9 +543,15 @@ class mLSTMCell(MemoroidCellBase):
             c0, f0, n0, m0 = initial_carry
             c0, f0 = c0[:, 0].contiguous(), f0[:, 0, :, 0, 0].contiguous()
             n0, m0 = n0[:, 0, :, :, 0].contiguous(), m0[:, 0, :, 0, 0].contiguous()
-        h, c_last, n_last, m_last, f_last = ops.MLSTM.apply(q.float().contiguous(), k.float().contiguous(),
-                                                            v.float().contiguous(), log_i.float().contiguous(),
-                                                            log_f.float().contiguous(), c0, n0, m0, f0, done, self.eps)
+        if self.tensor_cores:
+            bf = lambda t: t.to(torch.bfloat16).contiguous()
+            h, c_last, n_last, m_last, f_last = ops.MLSTMTensorCore.apply(bf(q), bf(k), bf(v), log_i.float().contiguous(),
+                                                                          log_f.float().contiguous(), c0, n0, m0, f0, done,
+                                                                          self.eps)
+        else:
+            h, c_last, n_last, m_last, f_last = ops.MLSTM.apply(q.float().contiguous(), k.float().contiguous(),
+                                                                v.float().contiguous(), log_i.float().contiguous(),
+                                                                log_f.float().contiguous(), c0, n0, m0, f0, done, self.eps)
         next_carry = (c_last[:, None], f_last[:, None, :, None, None], n_last[:, None, :, :, None],
                       m_last[:, None, :, None, None])
         return next_carry, self.finish(h.to(inputs.dtype), zgate, u)
