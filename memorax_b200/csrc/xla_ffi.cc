@@ -127,6 +127,40 @@ ffi::Error MlstmBwd(cudaStream_t stream, ffi::Buffer<ffi::F32> q, ffi::Buffer<ff
                                    scratch->size_bytes(), (int)d[0], (int)d[1], (int)d[2], (int)d[3], eps, stream));
 }
 
+// ---- the same on the tensor cores: bf16 q, k, v, h; `m_steps` and `states` are the residuals the backward call takes ----
+ffi::Error MlstmTcFwd(cudaStream_t stream, ffi::Buffer<ffi::BF16> q, ffi::Buffer<ffi::BF16> k, ffi::Buffer<ffi::BF16> v,
+                      ffi::Buffer<ffi::F32> log_i, ffi::Buffer<ffi::F32> log_f, ffi::Buffer<ffi::F32> c0, ffi::Buffer<ffi::F32> n0,
+                      ffi::Buffer<ffi::F32> m0, ffi::Buffer<ffi::F32> f0, ffi::Buffer<ffi::U8> done, ffi::ResultBuffer<ffi::BF16> h,
+                      ffi::ResultBuffer<ffi::F32> c_last, ffi::ResultBuffer<ffi::F32> n_last, ffi::ResultBuffer<ffi::F32> m_last,
+                      ffi::ResultBuffer<ffi::F32> f_last, ffi::ResultBuffer<ffi::F32> m_steps, ffi::ResultBuffer<ffi::U8> states,
+                      ffi::ResultBuffer<ffi::S32> status, float eps) {
+  auto d = q.dimensions();
+  cudaMemsetAsync(status->typed_data(), 0, sizeof(int), stream);
+  return ToError(mxk_mlstm_bf16_fwd(q.untyped_data(), k.untyped_data(), v.untyped_data(), log_i.typed_data(), log_f.typed_data(),
+                                    c0.typed_data(), n0.typed_data(), m0.typed_data(), f0.typed_data(), done.typed_data(),
+                                    h->untyped_data(), c_last->typed_data(), n_last->typed_data(), m_last->typed_data(),
+                                    f_last->typed_data(), m_steps->typed_data(), states->untyped_data(), status->typed_data(),
+                                    (int)d[0], (int)d[1], (int)d[2], (int)d[3], eps, stream));
+}
+ffi::Error MlstmTcBwd(cudaStream_t stream, ffi::Buffer<ffi::BF16> q, ffi::Buffer<ffi::BF16> k, ffi::Buffer<ffi::BF16> v,
+                      ffi::Buffer<ffi::F32> log_i, ffi::Buffer<ffi::F32> log_f, ffi::Buffer<ffi::F32> c0, ffi::Buffer<ffi::F32> n0,
+                      ffi::Buffer<ffi::F32> m0, ffi::Buffer<ffi::U8> done, ffi::Buffer<ffi::BF16> dh, ffi::Buffer<ffi::F32> c_last,
+                      ffi::Buffer<ffi::F32> n_last, ffi::Buffer<ffi::F32> m_steps, ffi::Buffer<ffi::U8> states,
+                      ffi::Buffer<ffi::F32> dc_last, ffi::Buffer<ffi::F32> dn_last, ffi::Buffer<ffi::F32> dm_last,
+                      ffi::ResultBuffer<ffi::BF16> dq, ffi::ResultBuffer<ffi::BF16> dk, ffi::ResultBuffer<ffi::BF16> dv,
+                      ffi::ResultBuffer<ffi::F32> dlog_i, ffi::ResultBuffer<ffi::F32> dlog_f, ffi::ResultBuffer<ffi::F32> dc0,
+                      ffi::ResultBuffer<ffi::F32> dn0, ffi::ResultBuffer<ffi::F32> dm0, ffi::ResultBuffer<ffi::S32> status, float eps) {
+  auto d = q.dimensions();
+  cudaMemsetAsync(status->typed_data(), 0, sizeof(int), stream);
+  return ToError(mxk_mlstm_bf16_bwd(q.untyped_data(), k.untyped_data(), v.untyped_data(), log_i.typed_data(), log_f.typed_data(),
+                                    c0.typed_data(), n0.typed_data(), m0.typed_data(), done.typed_data(), dh.untyped_data(),
+                                    c_last.typed_data(), n_last.typed_data(), m_steps.typed_data(), states.untyped_data(),
+                                    dc_last.typed_data(), dn_last.typed_data(), dm_last.typed_data(), dq->untyped_data(),
+                                    dk->untyped_data(), dv->untyped_data(), dlog_i->typed_data(), dlog_f->typed_data(),
+                                    dc0->typed_data(), dn0->typed_data(), dm0->typed_data(), status->typed_data(), (int)d[0],
+                                    (int)d[1], (int)d[2], (int)d[3], eps, stream));
+}
+
 // ---- MinGRU log-space scan + read-out (min_gru.py:67-78) ----
 ffi::Error MinGruFwd(cudaStream_t stream, ffi::Buffer<ffi::F32> ls, ffi::Buffer<ffi::F32> dec, ffi::Buffer<ffi::F32> x0,
                      ffi::Buffer<ffi::F32> a0, ffi::Buffer<ffi::U8> done, ffi::ResultBuffer<ffi::F32> x,
@@ -232,6 +266,15 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(MxkMlstmBwd, MlstmBwd,
     MXK_BIND_STREAM().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>()
         .Arg<U8B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Ret<F32B>().Ret<F32B>().Ret<F32B>().Ret<F32B>()
         .Ret<F32B>().Ret<F32B>().Ret<F32B>().Ret<F32B>().Ret<F32B>().Attr<float>("eps"));
+XLA_FFI_DEFINE_HANDLER_SYMBOL(MxkMlstmTcFwd, MlstmTcFwd,
+    MXK_BIND_STREAM().Arg<BF16B>().Arg<BF16B>().Arg<BF16B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>()
+        .Arg<F32B>().Arg<U8B>().Ret<BF16B>().Ret<F32B>().Ret<F32B>().Ret<F32B>().Ret<F32B>().Ret<F32B>().Ret<U8B>().Ret<S32B>()
+        .Attr<float>("eps"));
+XLA_FFI_DEFINE_HANDLER_SYMBOL(MxkMlstmTcBwd, MlstmTcBwd,
+    MXK_BIND_STREAM().Arg<BF16B>().Arg<BF16B>().Arg<BF16B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>()
+        .Arg<U8B>().Arg<BF16B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<U8B>().Arg<F32B>().Arg<F32B>().Arg<F32B>()
+        .Ret<BF16B>().Ret<BF16B>().Ret<BF16B>().Ret<F32B>().Ret<F32B>().Ret<F32B>().Ret<F32B>().Ret<F32B>().Ret<S32B>()
+        .Attr<float>("eps"));
 XLA_FFI_DEFINE_HANDLER_SYMBOL(MxkMinGruFwd, MinGruFwd,
     MXK_BIND_STREAM().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<U8B>().Ret<F32B>().Ret<F32B>().Ret<F32B>());
 XLA_FFI_DEFINE_HANDLER_SYMBOL(MxkMinGruBwd, MinGruBwd,
