@@ -66,6 +66,14 @@ struct FwdSmem {
 static_assert(sizeof(FwdSmem) <= 56 * 1024, "four CTAs per SM");
 static_assert(offsetof(FwdSmem, k) % 1024 == 0 && offsetof(FwdSmem, p) % 1024 == 0, "SW tiles are 1024-byte aligned");
 
+#ifdef MXK_TIMING
+}  // namespace
+__device__ unsigned long long g_mtc_phase_cycles[16];
+namespace {
+#define MXK_TM(i) do { if (tid == 0 && (blockIdx.x % 37) == 0) { const long long now_ = clock64(); atomicAdd(&g_mtc_phase_cycles[i], (unsigned long long)(now_ - t_prev_)); t_prev_ = now_; } } while (0)
+#else
+#define MXK_TM(i) do {} while (0)
+#endif
 constexpr uint32_t kTmemCols = 128;
 constexpr uint32_t kUpper = 16u << 16;
 
@@ -139,8 +147,12 @@ __global__ void __launch_bounds__(kThreads, 4) mlstm_tc_fwd_kernel(const __grid_
   float f_in = p.f0 ? p.f0[bh] : 0.f;
   DoneFlags done_flags = load_done_flags(drow, 0, p.T, lane);
   float2 gate_regs = load_gates(p.log_i, p.log_f, b, h, 0, p.T, p.H, tid);
+#ifdef MXK_TIMING
+  long long t_prev_ = clock64();
+#endif
 
   for (int c = 0; c < nchunks; ++c) {
+    MXK_TM(0);
     const int t0 = c * kC;
     const int valid = min(kC, p.T - t0);
     const uint64_t dm = done_mask_from_flags(done_flags);
@@ -153,11 +165,13 @@ __global__ void __launch_bounds__(kThreads, 4) mlstm_tc_fwd_kernel(const __grid_
     gate_regs = load_gates(p.log_i, p.log_f, b, h, t0 + kC, p.T, p.H, tid);   // the next chunk's, needed a chunk from now
 
     mbar_wait_flag(&sm.bar_load, c & 1, timed_out);
+    MXK_TM(1);
     if (tid < kC) sm.v[kPanels * kC + tid].x = tid < valid ? kOneBf16 : 0u;
     if (tid == 0) tma::wait_group_read<0>();   // the previous output tile has left p
     fence_smem_to_async();
     fence_before_sync();
     __syncthreads();
+    MXK_TM(2);
 
     if (warp == 0) {
       const bool leader = elect_one();
@@ -181,6 +195,7 @@ __global__ void __launch_bounds__(kThreads, 4) mlstm_tc_fwd_kernel(const __grid_
     mbar_wait_flag(&sm.bar[0], c & 1, timed_out);
     fence_after_sync();
     __syncthreads();            // the gate factors of warp 1 are visible
+    MXK_TM(3);
     m_in = sm.gates.m_out;
     f_in = sm.gates.f_out;
     const float delta = sm.gates.delta;
@@ -235,10 +250,12 @@ __global__ void __launch_bounds__(kThreads, 4) mlstm_tc_fwd_kernel(const __grid_
         sm.alt[vid] = pack8_bf16(f);
       }
     }
+    MXK_TM(4);
     if (tid == 0) tma::wait_group_read<0>();   // the residual copy has left s, which epilogue B rewrites
     fence_smem_to_async();
     fence_before_sync();
     __syncthreads();
+    MXK_TM(5);
 
     if (warp == 0) {
       const bool leader = elect_one();
@@ -254,6 +271,7 @@ __global__ void __launch_bounds__(kThreads, 4) mlstm_tc_fwd_kernel(const __grid_
     mbar_wait_flag(&sm.bar[1], c & 1, timed_out);
     fence_after_sync();
     if (tid == 0 && c + 1 < nchunks) issue_chunk_loads(c + 1);
+    MXK_TM(6);
 
     // ---- epilogue B ----
     {
@@ -288,6 +306,7 @@ __global__ void __launch_bounds__(kThreads, 4) mlstm_tc_fwd_kernel(const __grid_
       tma::store_plain_tile(&p.map_o, sm.p, t0, h, b);
       tma::commit_group();
     }
+    MXK_TM(7);
   }
 
   if (tid == 0) {
@@ -303,6 +322,16 @@ __global__ void __launch_bounds__(kThreads, 4) mlstm_tc_fwd_kernel(const __grid_
 
 }  // namespace
 }  // namespace mxk
+
+#ifdef MXK_TIMING
+extern "C" int mxk_debug_mtc_phase_cycles(unsigned long long* out, int reset) {
+  if (reset) {
+    unsigned long long z[16] = {};
+    return (int)cudaMemcpyToSymbol(mxk::g_mtc_phase_cycles, z, sizeof(z));
+  }
+  return (int)cudaMemcpyFromSymbol(out, mxk::g_mtc_phase_cycles, 16 * sizeof(unsigned long long));
+}
+#endif
 
 extern "C" {
 
