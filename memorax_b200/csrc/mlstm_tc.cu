@@ -146,7 +146,22 @@ __global__ void __launch_bounds__(kThreads, 4) mlstm_tc_fwd_kernel(const __grid_
   float m_in = p.m0 ? p.m0[bh] : -1e9f;       // initialize_carry's stabiliser (mlstm.py:231-240)
   float f_in = p.f0 ? p.f0[bh] : 0.f;
   DoneFlags done_flags = load_done_flags(drow, 0, p.T, lane);
-  float2 gate_regs = load_gates(p.log_i, p.log_f, b, h, 0, p.T, p.H, tid);
+  LaneGates lane_gates = load_lane_gates(p.log_i, p.log_f, b, h, 0, p.T, p.H, lane);   // used by warp 1
+  // Warp 1 computes a chunk's gate factors one chunk ahead (for chunk 0 here, afterwards while the second MMA group
+  // of the previous chunk runs), stores the stabilisers and fetches the gates of the chunk after.
+  auto scan_chunk = [&](int cc, uint64_t dmc) {
+    chunk_gate_scan(sm.gates, lane_gates, dmc, m_in, f_in, lane, cc & 1);
+    lane_gates = load_lane_gates(p.log_i, p.log_f, b, h, (cc + 1) * kC, p.T, p.H, lane);
+    m_in = sm.gates.m_out;
+    f_in = sm.gates.f_out;
+    if (p.m_steps) {
+      const int ta = cc * kC + 2 * lane;
+      float* dst = p.m_steps + (static_cast<size_t>(b) * p.T + ta) * p.H + h;
+      if (ta < p.T) dst[0] = sm.gates.m[2 * lane];
+      if (ta + 1 < p.T) dst[p.H] = sm.gates.m[2 * lane + 1];
+    }
+  };
+  if (warp == 1) scan_chunk(0, done_mask_from_flags(done_flags));
 #ifdef MXK_TIMING
   long long t_prev_ = clock64();
 #endif
@@ -158,12 +173,6 @@ __global__ void __launch_bounds__(kThreads, 4) mlstm_tc_fwd_kernel(const __grid_
     const uint64_t dm = done_mask_from_flags(done_flags);
     done_flags = load_done_flags(drow, t0 + kC, p.T, lane);
     const bool has_reset = dm != 0ull;
-    if (tid < kC) {
-      sm.gates.li[tid] = gate_regs.x;
-      sm.gates.lf[tid] = gate_regs.y;
-    }
-    gate_regs = load_gates(p.log_i, p.log_f, b, h, t0 + kC, p.T, p.H, tid);   // the next chunk's, needed a chunk from now
-
     mbar_wait_flag(&sm.bar_load, c & 1, timed_out);
     MXK_TM(1);
     if (tid < kC) sm.v[kPanels * kC + tid].x = tid < valid ? kOneBf16 : 0u;
@@ -183,21 +192,10 @@ __global__ void __launch_bounds__(kThreads, 4) mlstm_tc_fwd_kernel(const __grid_
         tma::store_bulk(p.chunk_states + (static_cast<size_t>(bh) * nchunks + c) * (kPanelsX * kD), sm.s, kPanelsX * kD * 16);
         tma::commit_group();
       }
-    } else if (warp == 1) {
-      chunk_gate_scan(sm.gates, dm, m_in, f_in, lane);
-      if (p.m_steps) {
-        const int ta = t0 + 2 * lane;
-        float* dst = p.m_steps + (static_cast<size_t>(b) * p.T + ta) * p.H + h;
-        if (ta < p.T) dst[0] = sm.gates.m[2 * lane];
-        if (ta + 1 < p.T) dst[p.H] = sm.gates.m[2 * lane + 1];
-      }
     }
     mbar_wait_flag(&sm.bar[0], c & 1, timed_out);
     fence_after_sync();
-    __syncthreads();            // the gate factors of warp 1 are visible
     MXK_TM(3);
-    m_in = sm.gates.m_out;
-    f_in = sm.gates.f_out;
     const float delta = sm.gates.delta;
 
     // ---- epilogue A ----
@@ -205,18 +203,24 @@ __global__ void __launch_bounds__(kThreads, 4) mlstm_tc_fwd_kernel(const __grid_
       float vals[kDX];
       tmem_ld_row<kDX>(lane_base, vals);
       if (!upper) {
+        // P~_tj = P_tj 2^(rowterm2_t + lic2_j) on the keys of row t's segment
         const int lo = row_first_key(dm, row);
-        const float rt = sm.gates.rowterm[row];
+        const float rt = sm.gates.rowterm2[row];
+        const float4* lic4 = reinterpret_cast<const float4*>(sm.gates.lic2);
 #pragma unroll
         for (int pn = 0; pn < kPanels; ++pn) {
+          const float4 c0 = lic4[2 * pn], c1 = lic4[2 * pn + 1];
+          const float cj[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
           float f[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const int j = pn * 8 + e;
-            f[e] = (j >= lo && j <= row) ? vals[j] * __expf(rt + sm.gates.lic[j]) : 0.f;
+            f[e] = (j >= lo && j <= row) ? vals[j] * ex2_fast(rt + cj[e]) : 0.f;
           }
           sm.p[sw_idx(row, pn)] = pack8_bf16(f);
         }
+      } else {
+        // the same-numbered upper thread scales query row `row` by w_t in place and its state row by delta
         const float w = sm.gates.w[row];
 #pragma unroll
         for (int pn = 0; pn < kPanels; ++pn) {
@@ -226,7 +230,6 @@ __global__ void __launch_bounds__(kThreads, 4) mlstm_tc_fwd_kernel(const __grid_
           for (int e = 0; e < 8; ++e) f[e] *= w;
           sm.q[sw_idx(row, pn)] = pack8_bf16(f);
         }
-      } else {
 #pragma unroll
         for (int i = 0; i < kDX; ++i) vals[i] *= delta;
       }
@@ -267,6 +270,8 @@ __global__ void __launch_bounds__(kThreads, 4) mlstm_tc_fwd_kernel(const __grid_
       gemm<kC / 16>(tmem, ap, bv, idesc_o, true, leader);                            // O += P~ (V | 1)
       gemm<kC / 16>(tmem + kUpper, ak, balt, idesc_s, !has_reset, leader);           // S (+)= K^T (kappa o (V | 1))
       if (leader) commit(&sm.bar[1]);
+    } else if (warp == 1 && c + 1 < nchunks) {
+      scan_chunk(c + 1, done_mask_from_flags(done_flags));   // done_flags already holds the next chunk's
     }
     mbar_wait_flag(&sm.bar[1], c & 1, timed_out);
     fence_after_sync();
@@ -278,7 +283,7 @@ __global__ void __launch_bounds__(kThreads, 4) mlstm_tc_fwd_kernel(const __grid_
       float orow[kDX];
       tmem_ld_row<kDX>(lane_base, orow);
       if (!upper) {
-        const float inv = 1.f / (fmaxf(fabsf(orow[kD]), sm.gates.em[row]) + p.eps);
+        const float inv = 1.f / (fmaxf(fabsf(orow[kD]), sm.gates.em[c & 1][row]) + p.eps);
 #pragma unroll
         for (int pn = 0; pn < kPanels; ++pn) {
           float f[8];
@@ -310,8 +315,8 @@ __global__ void __launch_bounds__(kThreads, 4) mlstm_tc_fwd_kernel(const __grid_
   }
 
   if (tid == 0) {
-    if (p.m_last) p.m_last[bh] = m_in;
-    if (p.f_last) p.f_last[bh] = f_in;
+    if (p.m_last) p.m_last[bh] = sm.gates.m_out;
+    if (p.f_last) p.f_last[bh] = sm.gates.f_out;
     tma::wait_group_all();
   }
   if (timed_out && p.status) atomicExch(p.status, 1);

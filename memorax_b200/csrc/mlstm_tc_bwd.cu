@@ -278,13 +278,19 @@ __global__ void __launch_bounds__(kBwdThreads, 2) mlstm_tc_bwd_kernel(const __gr
   const uint32_t id_y = idesc_bf16(kC, kDX, false, true);
   bool timed_out = false;
   DoneFlags done_flags = load_done_flags(drow, (nchunks - 1) * kC, p.T, lane);
-  float2 gate_regs = load_gates(p.log_i, p.log_f, b, h, (nchunks - 1) * kC, p.T, p.H, tid);
+  LaneGates lane_gates = load_lane_gates(p.log_i, p.log_f, b, h, (nchunks - 1) * kC, p.T, p.H, lane);   // used by warp 1
   auto load_m_in = [&](int cc) -> float {   // the stabiliser entering chunk cc
     if (cc <= 0) return p.m0 ? p.m0[bh] : -1e9f;
     return __ldg(p.m_steps + (static_cast<size_t>(b) * p.T + cc * kC - 1) * p.H + h);
   };
   float m_in_next = load_m_in(nchunks - 1);
   float carry = 0.f;   // explicit-path cotangent entering from the right (meaningful in warp 1)
+  // Warp 1 computes a chunk's gate factors one chunk ahead: for the last chunk here, afterwards (behind that chunk's
+  // gate gradients) while the second MMA group of the chunk to the right runs.
+  if (warp == 1) {
+    chunk_gate_scan(sm.gates, lane_gates, done_mask_from_flags(done_flags), m_in_next, 0.f, lane, (nchunks - 1) & 1);
+    lane_gates = load_lane_gates(p.log_i, p.log_f, b, h, (nchunks - 2) * kC, p.T, p.H, lane);
+  }
   float* dli_out = p.dlog_i + static_cast<size_t>(b) * p.T * p.H + h;
   float* dlf_out = p.dlog_f + static_cast<size_t>(b) * p.T * p.H + h;
 
@@ -297,12 +303,6 @@ __global__ void __launch_bounds__(kBwdThreads, 2) mlstm_tc_bwd_kernel(const __gr
     const bool has_reset = dm != 0ull;
     const float m_in = m_in_next;
     m_in_next = load_m_in(c - 1);
-    if (tid < kC) {
-      sm.gates.li[tid] = gate_regs.x;
-      sm.gates.lf[tid] = gate_regs.y;
-    }
-    gate_regs = load_gates(p.log_i, p.log_f, b, h, t0 - kC, p.T, p.H, tid);
-
     mbar_wait_flag(&sm.bar_load, it & 1, timed_out);
     if (tid == 0) tma::wait_group_read<0>();   // the previous chunk's output tiles have left their staging buffers
     fence_smem_to_async();
@@ -327,12 +327,9 @@ __global__ void __launch_bounds__(kBwdThreads, 2) mlstm_tc_bwd_kernel(const __gr
       gemm<kD / 16>(tmem + kUpper + kColR, ado, bs_hi, id_half, false, leader);    // R,  features 32..63
       gemm<kD / 16>(tmem + kColY, sw_operand(smem_u32(sm.k), false), Operand{smem_u32(sm.g), kD, true}, id_y, false, leader);   // Y = K [G | gn]
       if (leader) commit(&sm.bar[0]);
-    } else if (warp == 1) {
-      chunk_gate_scan(sm.gates, dm, m_in, 0.f, lane);
     }
     mbar_wait_flag(&sm.bar[0], it & 1, timed_out);
     fence_after_sync();
-    __syncthreads();            // the gate factors of warp 1 are visible
     const float delta = sm.gates.delta;
 
     // ---- epilogue 1: the four threads of a query row (two half-warps x two warpgroups) each cover 16 keys /
@@ -341,7 +338,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) mlstm_tc_bwd_kernel(const __gr
       const int lo = row_first_key(dm, row);
       const int j0 = (upper ? 32 : 0) + wg * 16;   // first key / feature of this thread
       const int p0 = j0 >> 3;                      // and its first panel
-      const float w = sm.gates.w[row], rt = sm.gates.rowterm[row];
+      const float w = sm.gates.w[row], rt = sm.gates.rowterm2[row];
       float s_dot = 0.f, z_dot = 0.f;
       {
         float rr[16];
@@ -366,7 +363,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) mlstm_tc_bwd_kernel(const __gr
       for (int e = 0; e < 16; ++e) {
         const int j = j0 + e;
         const bool m = (j >= lo && j <= row);
-        dw[e] = m ? __expf(rt + sm.gates.lic[j]) : 0.f;
+        dw[e] = m ? ex2_fast(rt + sm.gates.lic2[j]) : 0.f;
         pv[e] *= dw[e];                     // P~
         av[e] = m ? av[e] : 0.f;
         qn += pv[e];
@@ -389,7 +386,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) mlstm_tc_bwd_kernel(const __gr
       don += sm.xch[wg ^ 1][1][row];
       z_all += sm.gg.colpart[wg ^ 1][row];
       s_all += sm.gg.colpart[2 + (wg ^ 1)][row];
-      const float em = sm.gates.em[row];
+      const float em = sm.gates.em[c & 1][row];
       const float den = fmaxf(fabsf(qn), em) + p.eps;
       const float inv = 1.f / den;
       const float dden = -don * inv * inv;
@@ -543,6 +540,10 @@ __global__ void __launch_bounds__(kBwdThreads, 2) mlstm_tc_bwd_kernel(const __gr
 #pragma unroll
       for (int i = 0; i < 8; ++i) ed += sm.gg.edpart[i];
       chunk_gate_grads(sm.gates, sm.gg, dm, m_in, delta * ed, carry, dli_out, dlf_out, t0, p.T, p.H, lane);
+      if (c > 0) {   // the next (earlier) chunk's factors; done_flags and m_in_next already hold that chunk's
+        chunk_gate_scan(sm.gates, lane_gates, done_mask_from_flags(done_flags), m_in_next, 0.f, lane, (c - 1) & 1);
+        lane_gates = load_lane_gates(p.log_i, p.log_f, b, h, (c - 2) * kC, p.T, p.H, lane);
+      }
     }
     mbar_wait_flag(&sm.bar[1], it & 1, timed_out);
     fence_after_sync();
