@@ -15,7 +15,7 @@
 // (batch, head) with the fp32 state [C | n]^T resident in tensor memory, the same "1" column that makes the
 // normaliser q.n column 64 of the output accumulator.  Per chunk:
 //   MMA 1:       P = Q K^T                                  (lower TMEM lanes)
-//   warp 1:      gate scans (cumulative sum, segmented running maximum) -> D, w, kappa, delta factors
+//   warp 1:      gate scans (cumulative sum, segmented running maximum) -> D, w, kappa, delta factors, under the tile wait
 //   epilogue A:  lower rows P~ = D o P (bf16), q_t <- w_t q_t in place; upper rows scale the state by delta
 //                in tensor memory; all threads kappa o [V | 1]
 //   MMA 2:       O = (w o Q) S_in^T + P~ [V | 1];   S += K^T (kappa o [V | 1])
@@ -147,8 +147,9 @@ __global__ void __launch_bounds__(kThreads, 4) mlstm_tc_fwd_kernel(const __grid_
   float f_in = p.f0 ? p.f0[bh] : 0.f;
   DoneFlags done_flags = load_done_flags(drow, 0, p.T, lane);
   LaneGates lane_gates = load_lane_gates(p.log_i, p.log_f, b, h, 0, p.T, p.H, lane);   // used by warp 1
-  // Warp 1 computes a chunk's gate factors one chunk ahead (for chunk 0 here, afterwards while the second MMA group
-  // of the previous chunk runs), stores the stabilisers and fetches the gates of the chunk after.
+  // Warp 1 computes a chunk's gate factors at the top of the chunk, while the other warps wait for the tiles
+  // (one chunk ahead, under the previous chunk's second MMA group, measured 3 % slower: the scan then delays
+  // the output epilogue), stores the stabilisers and fetches the gates of the chunk after.
   auto scan_chunk = [&](int cc, uint64_t dmc) {
     chunk_gate_scan(sm.gates, lane_gates, dmc, m_in, f_in, lane, cc & 1);
     lane_gates = load_lane_gates(p.log_i, p.log_f, b, h, (cc + 1) * kC, p.T, p.H, lane);
@@ -161,7 +162,6 @@ __global__ void __launch_bounds__(kThreads, 4) mlstm_tc_fwd_kernel(const __grid_
       if (ta + 1 < p.T) dst[p.H] = sm.gates.m[2 * lane + 1];
     }
   };
-  if (warp == 1) scan_chunk(0, done_mask_from_flags(done_flags));
 #ifdef MXK_TIMING
   long long t_prev_ = clock64();
 #endif
@@ -173,6 +173,7 @@ __global__ void __launch_bounds__(kThreads, 4) mlstm_tc_fwd_kernel(const __grid_
     const uint64_t dm = done_mask_from_flags(done_flags);
     done_flags = load_done_flags(drow, t0 + kC, p.T, lane);
     const bool has_reset = dm != 0ull;
+    if (warp == 1) scan_chunk(c, dm);   // while the other warps wait for the tiles
     mbar_wait_flag(&sm.bar_load, c & 1, timed_out);
     MXK_TM(1);
     if (tid < kC) sm.v[kPanels * kC + tid].x = tid < valid ? kOneBf16 : 0u;
@@ -270,8 +271,6 @@ __global__ void __launch_bounds__(kThreads, 4) mlstm_tc_fwd_kernel(const __grid_
       gemm<kC / 16>(tmem, ap, bv, idesc_o, true, leader);                            // O += P~ (V | 1)
       gemm<kC / 16>(tmem + kUpper, ak, balt, idesc_s, !has_reset, leader);           // S (+)= K^T (kappa o (V | 1))
       if (leader) commit(&sm.bar[1]);
-    } else if (warp == 1 && c + 1 < nchunks) {
-      scan_chunk(c + 1, done_mask_from_flags(done_flags));   // done_flags already holds the next chunk's
     }
     mbar_wait_flag(&sm.bar[1], c & 1, timed_out);
     fence_after_sync();
