@@ -46,6 +46,7 @@ struct FwdParams {
   int d;                // head dimension: a multiple of 8, at most kD; the tiles are kD wide, the rest zero
   float eps;
   int feature_map;
+  int state_bulk;       // s0 / z0 are 16-byte aligned: they are staged through shared memory by bulk copies
   CUtensorMap map_q, map_k, map_o;   // 64-token tiles as SW tiles
   CUtensorMap map_v;          // 64-token tiles in panel order
 };
@@ -58,9 +59,11 @@ struct FwdSmem {
   uint4 s[2][kPanelsX * kD];    // bf16 S^T | z entering / leaving the chunk   [v/8][k]
   uint64_t bar[2];
   uint64_t bar_load;
+  uint64_t bar_state;
   uint32_t tmem;
 };
 static_assert(sizeof(FwdSmem) <= 55 * 1024, "four CTAs per SM");
+static_assert(sizeof(FwdSmem::s) >= (kD * kD + kD) * sizeof(float), "the carried state is staged in s");
 static_assert(offsetof(FwdSmem, k) % 1024 == 0 && offsetof(FwdSmem, alt) % 1024 == 0 && offsetof(FwdSmem, s) % 1024 == 0 &&
                   (kPanelsX * kD * 16) % 1024 == 0,
               "SW tiles are 1024-byte aligned");
@@ -93,11 +96,15 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
   const uint4 zero4 = make_uint4(0, 0, 0, 0);
   const int hd = kFull ? kD : p.d;   // head dimension
   const int dpan = hd >> 3;
+#ifdef MXK_TIMING
+  long long t_prev_ = clock64();
+#endif
 
   if (tid == 0) {
     mbar_init(&sm.bar[0], 1);
     mbar_init(&sm.bar[1], 1);
     mbar_init(&sm.bar_load, 1);
+    mbar_init(&sm.bar_state, 1);
     mbar_init_fence();
   }
   if (warp == 0) tmem_alloc(&sm.tmem, kTmemCols);
@@ -106,6 +113,17 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
   fence_after_sync();
   const uint32_t tmem = sm.tmem;
   const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+  bool timed_out = false;
+  MXK_T(11);
+  // The carried state (d x d + d floats, contiguous per (batch, head)) comes in by two bulk copies into the
+  // not-yet-used state buffers: 72 strided global loads per thread cost 7.5 k cycles per sequence here.
+  float* const stage = reinterpret_cast<float*>(sm.s);
+  const bool staged = p.state_bulk && (p.s0 || p.z0);
+  if (staged && tid == 0) {
+    tma::expect_bytes(&sm.bar_state, (p.s0 ? hd * hd * 4 : 0) + (p.z0 ? hd * 4 : 0));
+    if (p.s0) tma::load_bulk(stage, p.s0 + static_cast<size_t>(bh) * hd * hd, hd * hd * 4, &sm.bar_state);
+    if (p.z0) tma::load_bulk(stage + kD * kD, p.z0 + static_cast<size_t>(bh) * hd, hd * 4, &sm.bar_state);
+  }
 
   // The raw Q, K, V tiles of a chunk arrive by TMA straight in operand order, issued by one
   // thread one chunk ahead: as soon as the second MMA group of the previous chunk has released
@@ -131,14 +149,28 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
     const float* s0 = p.s0 ? p.s0 + static_cast<size_t>(bh) * hd * hd : nullptr;
     const float* z0 = p.z0 ? p.z0 + static_cast<size_t>(bh) * hd : nullptr;
     float vals[kDX];   // all loads first: the TMEM stores below are compiler memory barriers
+    if (staged) {
+      mbar_wait_flag(&sm.bar_state, 0, timed_out);
 #pragma unroll
-    for (int vcol = 0; vcol < kDX; ++vcol) {
-      float x = 0.f;
-      if (upper && row < hd) {
-        if (vcol < kD) x = (s0 && vcol < hd) ? s0[vcol * hd + row] : 0.f;
-        else if (vcol == kD) x = z0 ? z0[row] : 0.f;
+      for (int vcol = 0; vcol < kDX; ++vcol) {
+        float x = 0.f;
+        if (upper && row < hd) {
+          if (vcol < kD) x = (s0 && vcol < hd) ? stage[vcol * hd + row] : 0.f;
+          else if (vcol == kD) x = z0 ? stage[kD * kD + row] : 0.f;
+        }
+        vals[vcol] = x;
       }
-      vals[vcol] = x;
+      __syncthreads();   // every thread has taken its values before the bf16 copy overwrites the staging area
+    } else {
+#pragma unroll
+      for (int vcol = 0; vcol < kDX; ++vcol) {
+        float x = 0.f;
+        if (upper && row < hd) {
+          if (vcol < kD) x = (s0 && vcol < hd) ? s0[vcol * hd + row] : 0.f;
+          else if (vcol == kD) x = z0 ? z0[row] : 0.f;
+        }
+        vals[vcol] = x;
+      }
     }
 #pragma unroll
     for (int pn = 0; pn < kPanelsX; ++pn) {
@@ -147,16 +179,14 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
     }
     tmem_st_wait();
   }
+  MXK_T(12);
 
   const uint8_t* drow = p.done ? p.done + static_cast<size_t>(b) * p.T : nullptr;
   const uint32_t idesc_p = idesc_bf16(kC, kC, false, false);
   const uint32_t idesc_o = idesc_bf16(kC, kDX, false, true);
   const uint32_t idesc_s = idesc_bf16(kD, kDX, true, true);
-  bool timed_out = false;
   int cur = 0;
-#ifdef MXK_TIMING
-  long long t_prev_ = clock64();
-#endif
+  MXK_T(9);
   DoneFlags done_flags = load_done_flags(drow, 0, p.T, lane);
 
   for (int c = 0; c < nchunks; ++c) {
@@ -315,6 +345,7 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
   fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+  MXK_T(10);
 }
 
 }  // namespace
@@ -366,6 +397,7 @@ int mxk_linattn_bf16_fwd(const void* q, const void* k, const void* v, const floa
   prm.d = d;
   prm.eps = eps;
   prm.feature_map = feature_map;
+  prm.state_bulk = (!s0 || aligned16(s0)) && (!z0 || aligned16(z0));
   // maps over the d-column tensors with 64-column boxes: the columns past d are zero-filled on loads and
   // clipped on stores
   if (!tma::make_sw_map(&prm.map_q, q, B, T, H, kC, d) || !tma::make_sw_map(&prm.map_k, k, B, T, H, kC, d) ||
