@@ -363,6 +363,109 @@ def jax_cotangent(grad):
 
 
 # --------------------------------------------------------------------------
+# The chunked form of the mLSTM that the tensor-core kernels evaluate (mlstm_tc.cu, mlstm_tc_bwd.cu), restated
+# for one (batch, head) in float64: forward and the hand-derived backward.  tests/test_oracle.py holds it
+# against mlstm_seq and its autograd, which pins the kernels' algebra independently of any GPU.
+# --------------------------------------------------------------------------
+def mlstm_chunked_single(q, k, v, li, lf, done, c0, n0, m0, dh, dc_last, dn_last, dm_last, eps=1e-6, chunk=64):
+    """q, k, v, dh (T,d); li, lf, done (T,); c0 (d,d) [key][value], n0 (d,), m0 scalar; cotangents of the next
+    carry.  Returns ``(h, (c_T, n_T, m_T), grads)`` with ``grads`` keyed q, k, v, li, lf, c0, n0, m0.
+    The stabiliser m is held fixed in every decay factor (it is a gauge of the recurrence) and its one real
+    effect -- eps exp(m_t) in the denominator and the scale of the stabilised next carry -- is propagated
+    through m_t = max(m_{t-1} + lf_t, li_t) separately."""
+    dt = q.dtype
+    T, d = q.shape
+    nch = (T + chunk - 1) // chunk
+    Sx = torch.cat([c0, n0[:, None]], dim=1)
+    m_in = m0.clone()
+    hs, saved = [], []
+    m_all = torch.zeros(T, dtype=dt)
+    for c in range(nch):
+        t0, t1 = c * chunk, min(T, (c + 1) * chunk)
+        L = t1 - t0
+        qc, kc, vc, lic, lfc, dn = q[t0:t1], k[t0:t1], v[t0:t1], li[t0:t1], lf[t0:t1], done[t0:t1]
+        cumf = torch.cumsum(lfc, 0)
+        first = torch.zeros(L, dtype=torch.long)
+        last_reset = -1
+        for t in range(L):
+            if dn[t] > 0:
+                last_reset = t
+            first[t] = max(last_reset, 0)
+        live = torch.tensor([not bool((dn[: t + 1] > 0).any()) for t in range(L)])
+        keep = torch.arange(L) >= max(last_reset, 0)
+        has_reset = last_reset >= 0
+        m = torch.zeros(L, dtype=dt)
+        mp = m_in
+        for t in range(L):
+            m[t] = lic[t] if dn[t] > 0 else torch.maximum(mp + lfc[t], lic[t])
+            mp = m[t]
+        m_all[t0:t1] = m
+        idx = torch.arange(L)
+        mask = (idx[None, :] <= idx[:, None]) & (idx[None, :] >= first[:, None])
+        log_d = lic[None, :] + cumf[:, None] - cumf[None, :] - m[:, None]
+        D = torch.where(mask, torch.exp(log_d), torch.zeros_like(log_d))
+        w = torch.where(live, torch.exp(m_in + cumf - m), torch.zeros_like(cumf))
+        kap = torch.where(keep, torch.exp(lic + cumf[-1] - cumf - m[-1]), torch.zeros_like(cumf))
+        delta = torch.exp(m_in + cumf[-1] - m[-1]) if not has_reset else torch.zeros((), dtype=dt)
+        P = D * (qc @ kc.t())
+        Vx = torch.cat([vc, torch.ones(L, 1, dtype=dt)], 1)
+        inter = (w[:, None] * qc) @ Sx
+        Ox = P @ Vx + inter
+        den = torch.maximum(Ox[:, d].abs(), torch.exp(-m)) + eps
+        hs.append(Ox[:, :d] / den[:, None])
+        saved.append(dict(t0=t0, t1=t1, Sx_in=Sx, m=m, D=D, w=w, kap=kap, delta=delta, P=P, Vx=Vx, inter=inter, Ox=Ox,
+                          den=den, mask=mask))
+        Sx = delta * Sx + kc.t() @ (kap[:, None] * Vx)
+        m_in = m[-1]
+    h = torch.cat(hs, 0)
+    carry_out = (Sx[:, :d].clone(), Sx[:, d].clone(), m_in.clone())
+
+    dSx = torch.cat([dc_last, dn_last[:, None]], 1)
+    g = {n: torch.zeros_like(t) for n, t in (("q", q), ("k", k), ("v", v), ("li", li), ("lf", lf))}
+    dm_exp = torch.zeros(T, dtype=dt)
+    dm_exp[T - 1] += dm_last - (dSx * Sx).sum()       # the stabilised next carry scales with exp(-m_T)
+    for c in reversed(range(nch)):
+        s = saved[c]
+        t0, t1 = s["t0"], s["t1"]
+        qc, kc = q[t0:t1], k[t0:t1]
+        dhc = dh[t0:t1]
+        num, qn, den = s["Ox"][:, :d], s["Ox"][:, d], s["den"]
+        dden = -(dhc * num).sum(1) / den ** 2
+        dqn = torch.where(qn.abs() >= torch.exp(-s["m"]), torch.sign(qn) * dden, torch.zeros_like(dden))
+        dm_exp[t0:t1] += eps * dden
+        dOx = torch.cat([dhc / den[:, None], dqn[:, None]], 1)
+        dP = (dOx @ s["Vx"].t()) * s["mask"]
+        E = dP * s["P"]
+        dA = s["D"] * dP
+        kapVx = s["kap"][:, None] * s["Vx"]
+        y = kc @ dSx
+        g["v"][t0:t1] = (s["P"].t() @ dOx + s["kap"][:, None] * y)[:, :d]
+        e_kap = (kapVx * y).sum(1)
+        g["q"][t0:t1] = dA @ kc + (s["w"][:, None] * dOx) @ s["Sx_in"].t()
+        g["k"][t0:t1] = dA.t() @ qc + kapVx @ dSx.t()
+        e_w = (dOx * s["inter"]).sum(1)
+        e_delta = s["delta"] * (dSx * s["Sx_in"]).sum()
+        dcumf = E.sum(1) - E.sum(0) + e_w - e_kap
+        dcumf[-1] += e_kap.sum() + e_delta
+        g["li"][t0:t1] += E.sum(0) + e_kap
+        g["lf"][t0:t1] += torch.flip(torch.cumsum(torch.flip(dcumf, [0]), 0), [0])
+        dSx = s["delta"] * dSx + (s["w"][:, None] * qc).t() @ dOx
+    carry = torch.zeros((), dtype=dt)
+    for t in reversed(range(T)):
+        gt = dm_exp[t] + carry
+        m_prev = m_all[t - 1] if t > 0 else m0
+        if done[t] > 0 or li[t] > m_prev + lf[t]:
+            g["li"][t] += gt
+            carry = torch.zeros((), dtype=dt)
+        else:
+            g["lf"][t] += gt
+            carry = gt
+    g["c0"], g["n0"] = dSx[:, :d], dSx[:, d]
+    g["m0"] = carry + (dSx * torch.cat([c0, n0[:, None]], 1)).sum()
+    return h, carry_out, g
+
+
+# --------------------------------------------------------------------------
 # fp32 multi-threaded port timed as the CPU baseline of the benchmark
 # --------------------------------------------------------------------------
 

@@ -289,3 +289,32 @@ def test_mlstm_operator_scan_equals_sequential_form(golden):
         for got, name in zip(h, ("ml_h_C", "ml_h_logf", "ml_h_n", "ml_h_m")):
             np.testing.assert_allclose(got, g[name], rtol=1e-9, atol=1e-9)
         np.testing.assert_allclose(nxt[0], g["ml_n_C"], rtol=1e-9, atol=1e-9)
+
+
+@pytest.mark.parametrize("steps,p_done", [(200, 0.02), (64, 0.0), (130, 0.3), (5, 0.0)])
+def test_mlstm_chunked_form_equals_the_sequential_oracle_and_its_autograd(steps, p_done):
+    """The chunked algebra of the tensor-core kernels (decay factors with the stabiliser as a gauge, explicit path
+    through the running maximum) against mlstm_seq and torch autograd, in float64: values and all eight gradients,
+    with a carried state, cotangents on the next carry and resets (also at a chunk boundary)."""
+    gen = torch.Generator().manual_seed(steps)
+    d = 8
+    rn = lambda *s: torch.randn(*s, generator=gen, dtype=torch.float64)
+    q, k, v, dh = rn(steps, d), rn(steps, d) / d ** 0.5, rn(steps, d), rn(steps, d)
+    li = rn(steps) * 1.5 + 2.0
+    lf = -torch.nn.functional.softplus(-(rn(steps) * 2 + 1))
+    done = (torch.rand(steps, generator=gen) < p_done).double()
+    if steps > 70:
+        done[64] = 1.0
+        done[70] = 1.0
+    c0, n0, m0 = rn(d, d) * 0.5, rn(d) * 0.5, torch.tensor(0.3, dtype=torch.float64)
+    dcl, dnl, dml = rn(d, d) * 0.3, rn(d) * 0.3, torch.tensor(0.7, dtype=torch.float64)
+    leaves = [t.clone().requires_grad_() for t in (q, k, v, li, lf, c0, n0, m0)]
+    Q, K, V, LI, LF, C0, N0, M0 = leaves
+    h_ref, (c_t, _, n_t, m_t) = mo.mlstm_seq(Q[None, :, None], K[None, :, None], V[None, :, None], LI[None, :, None],
+                                             LF[None, :, None], C0[None, None], N0[None, None], M0[None, None], done[None])
+    ((h_ref[0, :, 0] * dh).sum() + (c_t[0, 0] * dcl).sum() + (n_t[0, 0] * dnl).sum() + m_t[0, 0] * dml).backward()
+    h, (c_out, n_out, m_out), g = mo.mlstm_chunked_single(q, k, v, li, lf, done, c0, n0, m0, dh, dcl, dnl, dml)
+    close = lambda a, b: float((a - b.detach()).abs().max()) <= 1e-9 * max(1.0, float(b.detach().abs().max()))
+    assert close(h, h_ref[0, :, 0]) and close(c_out, c_t[0, 0]) and close(n_out, n_t[0, 0]) and close(m_out, m_t[0, 0])
+    for name, leaf in zip(["q", "k", "v", "li", "lf", "c0", "n0", "m0"], leaves):
+        assert close(g[name], leaf.grad), name
