@@ -104,6 +104,14 @@ static_assert(sizeof(BwdSmem) <= 113 * 1024, "two CTAs per SM");
 //   columns 136..167   R, state features 0..31 in the lower lanes, 32..63 in the upper lanes
 //   columns 168..239   lower: Y = K [G | gn]
 // Within a half-warp's 32 columns, warpgroup 0 takes the first 16 and warpgroup 1 the rest.
+#ifdef MXK_TIMING
+}  // namespace
+__device__ unsigned long long g_mtcb_phase_cycles[16];
+namespace {
+#define MXK_TMB(i) do { if (tid == 0 && (blockIdx.x % 37) == 0) { const long long now_ = clock64(); atomicAdd(&g_mtcb_phase_cycles[i], (unsigned long long)(now_ - t_prev_)); t_prev_ = now_; } } while (0)
+#else
+#define MXK_TMB(i) do {} while (0)
+#endif
 constexpr uint32_t kBwdTmemCols = 256;
 constexpr uint32_t kUpper = 16u << 16;
 constexpr uint32_t kColLo = 0, kColHi = 64, kColP = 0, kColA = 32, kColR = 136, kColY = 168;
@@ -294,7 +302,11 @@ __global__ void __launch_bounds__(kBwdThreads, 2) mlstm_tc_bwd_kernel(const __gr
   float* dli_out = p.dlog_i + static_cast<size_t>(b) * p.T * p.H + h;
   float* dlf_out = p.dlog_f + static_cast<size_t>(b) * p.T * p.H + h;
 
+#ifdef MXK_TIMING
+  long long t_prev_ = clock64();
+#endif
   for (int it = 0; it < nchunks; ++it) {
+    MXK_TMB(0);
     const int c = nchunks - 1 - it;
     const int t0 = c * kC;
     const int valid = min(kC, p.T - t0);
@@ -304,10 +316,12 @@ __global__ void __launch_bounds__(kBwdThreads, 2) mlstm_tc_bwd_kernel(const __gr
     const float m_in = m_in_next;
     m_in_next = load_m_in(c - 1);
     mbar_wait_flag(&sm.bar_load, it & 1, timed_out);
+    MXK_TMB(1);
     if (tid == 0) tma::wait_group_read<0>();   // the previous chunk's output tiles have left their staging buffers
     fence_smem_to_async();
     fence_before_sync();
     __syncthreads();
+    MXK_TMB(2);
 
     if (warp == 0) {
       const bool leader = elect_one();
@@ -330,6 +344,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) mlstm_tc_bwd_kernel(const __gr
     }
     mbar_wait_flag(&sm.bar[0], it & 1, timed_out);
     fence_after_sync();
+    MXK_TMB(3);
     const float delta = sm.gates.delta;
 
     // ---- epilogue 1: the four threads of a query row (two half-warps x two warpgroups) each cover 16 keys /
@@ -381,7 +396,9 @@ __global__ void __launch_bounds__(kBwdThreads, 2) mlstm_tc_bwd_kernel(const __gr
         sm.gg.colpart[wg][row] = z_all;      // borrowed for the exchange of the inter parts (rewritten below)
         sm.gg.colpart[2 + wg][row] = s_all;
       }
+      MXK_TMB(4);
       __syncthreads();
+      MXK_TMB(5);
       qn += sm.xch[wg ^ 1][0][row];
       don += sm.xch[wg ^ 1][1][row];
       z_all += sm.gg.colpart[wg ^ 1][row];
@@ -406,7 +423,9 @@ __global__ void __launch_bounds__(kBwdThreads, 2) mlstm_tc_bwd_kernel(const __gr
         sm.pn[(p0 + jq) * kC + row] = pack8_bf16(a);
         sm.dp[(p0 + jq) * kC + row] = pack8_bf16(d8);
       }
+      MXK_TMB(6);
       __syncthreads();   // every thread has read the borrowed colpart slots
+      MXK_TMB(7);
       {
         const float tot = half_warp_reduce_scatter(ecol, lane);
         sm.gg.colpart[qw][j0 + (lane & 15)] = tot;
@@ -511,9 +530,11 @@ __global__ void __launch_bounds__(kBwdThreads, 2) mlstm_tc_bwd_kernel(const __gr
         }
       }
     }
+    MXK_TMB(8);
     fence_smem_to_async();
     fence_before_sync();
     __syncthreads();
+    MXK_TMB(9);
 
     if (warp == 0) {
       const bool leader = elect_one();
@@ -548,6 +569,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) mlstm_tc_bwd_kernel(const __gr
     mbar_wait_flag(&sm.bar[1], it & 1, timed_out);
     fence_after_sync();
     if (tid == 0 && c > 0) issue_chunk_loads(c - 1);   // in flight while the output epilogue runs
+    MXK_TMB(10);
 
     // ---- epilogue 2: every thread owns 32 (36, 40) columns of its row ----
     {
@@ -613,6 +635,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) mlstm_tc_bwd_kernel(const __gr
       tma::store_plain_tile(&p.map_dv, sm.pn, t0, h, b);
       tma::commit_group();
     }
+    MXK_TMB(11);
   }
   if (p.dm0 && warp == 1 && lane == 0) {
     float gsum = 0.f;
@@ -630,6 +653,16 @@ __global__ void __launch_bounds__(kBwdThreads, 2) mlstm_tc_bwd_kernel(const __gr
 
 }  // namespace
 }  // namespace mxk
+
+#ifdef MXK_TIMING
+extern "C" int mxk_debug_mtcb_phase_cycles(unsigned long long* out, int reset) {
+  if (reset) {
+    unsigned long long z[16] = {};
+    return (int)cudaMemcpyToSymbol(mxk::g_mtcb_phase_cycles, z, sizeof(z));
+  }
+  return (int)cudaMemcpyFromSymbol(out, mxk::g_mtcb_phase_cycles, 16 * sizeof(unsigned long long));
+}
+#endif
 
 extern "C" {
 
