@@ -146,8 +146,10 @@ __global__ void __launch_bounds__(kThreads, 4) linattn_fwd_kernel(const __grid_c
     tma::load_plain_tile(sm.q, &p.map_q, &sm.bar_load, cc * kC, h, b);
     tma::load_plain_tile(sm.k, &p.map_k, &sm.bar_load, cc * kC, h, b);
     tma::load_panel_tile(sm.v, &p.map_v, &sm.bar_load, cc * kC, h, b);
-    // a chunk kAhead positions on: into L2 now, so that its loads hit there
-    if (cc + kAhead < nchunks) prefetch_chunk(cc + kAhead);
+    // a chunk kAhead positions on: into L2 now, so that its loads hit there -- except at the start of a sequence,
+    // where every resident CTA asks for its first tiles and carried state at once and the prefetch only queues
+    // in front of them (measured: 4 % of the forward)
+    if (cc > 0 && cc + kAhead < nchunks) prefetch_chunk(cc + kAhead);
   };
   if (tid == 0) {
     issue_chunk_loads(0);
