@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(kThreads, 4) mlstm_tc_fwd_kernel(const __grid_
     tma::load_plain_tile(sm.q, &p.map_q, &sm.bar_load, cc * kC, h, b);
     tma::load_plain_tile(sm.k, &p.map_k, &sm.bar_load, cc * kC, h, b);
     tma::load_panel_tile(sm.v, &p.map_v, &sm.bar_load, cc * kC, h, b);
-    if (cc + 1 < nchunks) {
+    if (cc > 0 && cc + 1 < nchunks) {   // not while a sequence starts: the prefetch would queue in front of every CTA's first tiles
       tma::prefetch_plain_tile(&p.map_q, (cc + 1) * kC, h, b);
       tma::prefetch_plain_tile(&p.map_k, (cc + 1) * kC, h, b);
       tma::prefetch_panel_tile(&p.map_v, (cc + 1) * kC, h, b);
