@@ -711,13 +711,13 @@ def time_cpu(workload_cls, steps, warmup, batch=None):
     return w, dt
 
 
-def bounded_cpu_batch(workload_cls, passes, budget_s=90.0):
-    """Largest sample (in sequences) for which `passes` passes fit the budget,
+def bounded_cpu_batch(workload_cls, passes, limit_s=90.0):
+    """Largest sample (in sequences) for which `passes` passes fit the time limit,
     from one calibration pass on a few sequences."""
     probe = min(4, workload_cls.cpu_sample_batch)
     _, dt = time_cpu(workload_cls, steps=1, warmup=1, batch=probe)
     per_seq = dt / probe
-    return int(max(1, min(workload_cls.cpu_sample_batch, budget_s / (per_seq * max(passes, 1)))))
+    return int(max(1, min(workload_cls.cpu_sample_batch, limit_s / (per_seq * max(passes, 1)))))
 
 
 def cpu_baseline(workload_cls):
