@@ -33,8 +33,6 @@ constexpr int kBlock = 256;
 #define MXK_LINREC_MINB_B 4
 #endif
 constexpr int kUnroll = 4;  // log-space kernels
-constexpr int kUnrollF = MXK_LINREC_UNROLL_F;
-constexpr int kUnrollB = MXK_LINREC_UNROLL_B;
 
 template <int W> struct VecOf;
 template <> struct VecOf<4> { using type = float4; };
@@ -142,8 +140,8 @@ __device__ __forceinline__ Pack<W> add(const Pack<W>& x, const Pack<W>& y) {
 // ------------------------------------------------------------------ forward
 // Row stride is `row` floats (D for real, 2D for complex); a thread's W floats
 // start at column `col`.
-template <bool CPLX, int W>
-__global__ void __launch_bounds__(kBlock, MXK_LINREC_MINB_F)
+template <bool CPLX, int W, int kUnrollF = MXK_LINREC_UNROLL_F, int kMinBlocks = MXK_LINREC_MINB_F>
+__global__ void __launch_bounds__(kBlock, kMinBlocks)
 linrec_fwd_kernel(const float* __restrict__ a, int a_tinv, const float* __restrict__ b,
                   const float* __restrict__ h0, const float* __restrict__ a0,
                   const uint8_t* __restrict__ done, float* __restrict__ h,
@@ -164,16 +162,19 @@ linrec_fwd_kernel(const float* __restrict__ a, int a_tinv, const float* __restri
   if (a_tinv) a_fix = load_pack_cached<W>(a + col);
 
   for (int t0 = 0; t0 < T; t0 += kUnrollF) {
+    // Nothing in the first loop touches a loaded value (a thread issues in order and would wait for it there):
+    // the reset bytes stay raw until the second loop.
     Pack<W> av[kUnrollF], bv[kUnrollF];
-    bool rs[kUnrollF];
+    unsigned flag[kUnrollF];
 #pragma unroll
     for (int u = 0; u < kUnrollF; ++u) {
       const int t = t0 + u;
+      flag[u] = 0;
       if (t < T) {
         const size_t off = seq + static_cast<size_t>(t) * row;
         bv[u] = load_pack<W>(b + off);
         if (!a_tinv) av[u] = load_pack<W>(a + off);
-        rs[u] = drow ? (drow[t] != 0) : false;
+        if (drow) flag[u] = drow[t];
       }
     }
 #pragma unroll
@@ -181,8 +182,9 @@ linrec_fwd_kernel(const float* __restrict__ a, int a_tinv, const float* __restri
       const int t = t0 + u;
       if (t < T) {
         const Pack<W>& at = a_tinv ? a_fix : av[u];
-        cur = rs[u] ? bv[u] : mul_add<CPLX, W>(at, cur, bv[u]);
-        if (want_decay) acc = rs[u] ? at : mul<CPLX, W>(at, acc);
+        const bool reset = flag[u] != 0;
+        cur = reset ? bv[u] : mul_add<CPLX, W>(at, cur, bv[u]);
+        if (want_decay) acc = reset ? at : mul<CPLX, W>(at, acc);
         store_pack<W>(h + seq + static_cast<size_t>(t) * row, cur);
       }
     }
@@ -224,7 +226,7 @@ linrec_fwd_tsplit_kernel(const float* __restrict__ a, int a_tinv, const float* _
   const uint8_t* drow = done ? done + static_cast<size_t>(bi) * T : nullptr;
 
   Pack<W> av[L], bv[L];
-  bool rs[L];
+  unsigned flag[L];   // raw reset bytes: the load loop waits for no loaded value
   Pack<W> a_fix = fill_pack<W>(0.f, 0.f, CPLX);
   if (a_tinv && active) a_fix = load_pack_cached<W>(a + d);
 #pragma unroll
@@ -233,8 +235,12 @@ linrec_fwd_tsplit_kernel(const float* __restrict__ a, int a_tinv, const float* _
     const bool in = active && t < t_end;
     bv[i] = in ? load_pack<W>(b + base + static_cast<size_t>(t) * row) : fill_pack<W>(0.f, 0.f, CPLX);
     av[i] = in ? (a_tinv ? a_fix : load_pack<W>(a + base + static_cast<size_t>(t) * row)) : fill_pack<W>(1.f, 0.f, CPLX);
-    rs[i] = in && drow && drow[t] != 0;
+    flag[i] = 0;
+    if (in && drow) flag[i] = drow[t];
   }
+  bool rs[L];
+#pragma unroll
+  for (int i = 0; i < L; ++i) rs[i] = flag[i] != 0;
   // segment summary: state map (P, Q); decay leaf: product since the last reset, and whether there was one
   Pack<W> P = fill_pack<W>(1.f, 0.f, CPLX), Q = fill_pack<W>(0.f, 0.f, CPLX), dec = fill_pack<W>(1.f, 0.f, CPLX);
   int had_reset = 0;
@@ -301,18 +307,32 @@ linrec_bwd_tsplit_kernel(const float* __restrict__ a, int a_tinv, const float* _
   const uint8_t* drow = done ? done + static_cast<size_t>(bi) * T : nullptr;
   const bool want_ga = (ga != nullptr) || (ga_partial != nullptr);
 
-  Pack<W> av[L], gv[L];
-  bool rs[L];
+  // The load loop issues every load of the segment, h_{t-1} for the decay gradient included, and waits for none
+  // (a thread issues in order): conjugation and the reset test follow in a loop of their own.
+  Pack<W> av[L], gv[L], hp[L];
+  unsigned flag[L];
   Pack<W> a_fix = fill_pack<W>(0.f, 0.f, CPLX);
-  if (a_tinv && active) a_fix = conj_if<CPLX, W>(load_pack_cached<W>(a + d), conj_ops);
+  if (a_tinv && active) a_fix = load_pack_cached<W>(a + d);
 #pragma unroll
   for (int i = 0; i < L; ++i) {
     const int t = t_begin + i;
     const bool in = active && t < t_end;
-    gv[i] = in ? load_pack<W>(gh + base + static_cast<size_t>(t) * row) : fill_pack<W>(0.f, 0.f, CPLX);
-    av[i] = in ? (a_tinv ? a_fix : conj_if<CPLX, W>(load_pack<W>(a + base + static_cast<size_t>(t) * row), conj_ops))
-               : fill_pack<W>(1.f, 0.f, CPLX);
-    rs[i] = in && drow && drow[t] != 0;
+    const size_t off = base + static_cast<size_t>(t) * row;
+    gv[i] = in ? load_pack<W>(gh + off) : fill_pack<W>(0.f, 0.f, CPLX);
+    av[i] = in ? (a_tinv ? a_fix : load_pack<W>(a + off)) : fill_pack<W>(1.f, 0.f, CPLX);
+    flag[i] = 0;
+    if (in && drow) flag[i] = drow[t];
+    hp[i] = fill_pack<W>(0.f, 0.f, CPLX);
+    if (in && want_ga) {
+      if (t > 0) hp[i] = load_pack<W>(h + off - row);
+      else if (h0) hp[i] = load_pack_cached<W>(h0 + crow);
+    }
+  }
+  bool rs[L];
+#pragma unroll
+  for (int i = 0; i < L; ++i) {
+    rs[i] = flag[i] != 0;
+    av[i] = conj_if<CPLX, W>(av[i], conj_ops);
   }
   Pack<W> P = fill_pack<W>(1.f, 0.f, CPLX), Q = fill_pack<W>(0.f, 0.f, CPLX);
 #pragma unroll
@@ -348,12 +368,9 @@ linrec_bwd_tsplit_kernel(const float* __restrict__ a, int a_tinv, const float* _
     } else if (in) {
       carry = mul<CPLX, W>(av[i], g);
       if (want_ga) {
-        Pack<W> hp;
-        if (t > 0) hp = load_pack<W>(h + off - row);
-        else hp = h0 ? load_pack_cached<W>(h0 + crow) : fill_pack<W>(0.f, 0.f, CPLX);
-        hp = conj_if<CPLX, W>(hp, conj_ops);
-        if (a_tinv) ga_acc = mul_add<CPLX, W>(hp, g, ga_acc);
-        else store_pack<W>(ga + off, mul<CPLX, W>(hp, g));
+        const Pack<W> hc = conj_if<CPLX, W>(hp[i], conj_ops);
+        if (a_tinv) ga_acc = mul_add<CPLX, W>(hc, g, ga_acc);
+        else store_pack<W>(ga + off, mul<CPLX, W>(hc, g));
       }
     }
   }
@@ -378,8 +395,8 @@ linrec_bwd_tsplit_kernel(const float* __restrict__ a, int a_tinv, const float* _
 
 // ----------------------------------------------------------------- backward
 // Walks time right to left carrying c = a_{t+1} m_{t+1} g_{t+1}.
-template <bool CPLX, int W>
-__global__ void __launch_bounds__(kBlock, MXK_LINREC_MINB_B)
+template <bool CPLX, int W, int kUnrollB = MXK_LINREC_UNROLL_B, int kMinBlocks = MXK_LINREC_MINB_B>
+__global__ void __launch_bounds__(kBlock, kMinBlocks)
 linrec_bwd_kernel(const float* __restrict__ a, int a_tinv, const float* __restrict__ h,
                   const float* __restrict__ h0, const uint8_t* __restrict__ done,
                   const float* __restrict__ gh, const float* __restrict__ gh_last,
@@ -401,20 +418,23 @@ linrec_bwd_kernel(const float* __restrict__ a, int a_tinv, const float* __restri
   const bool want_ga = (ga != nullptr) || (ga_partial != nullptr);
 
   for (int t0 = T - 1; t0 >= 0; t0 -= kUnrollB) {
+    // The first loop only issues loads: a thread issues in order, so a conjugation, a comparison or a branch on
+    // a loaded value there would hold every later load back by one trip to memory per step.  h_{t-1} is therefore
+    // fetched whether or not step t resets, and conjugation and the reset test wait for the second loop.
     Pack<W> av[kUnrollB], gv[kUnrollB], hp[kUnrollB];
-    bool rs[kUnrollB];
+    unsigned flag[kUnrollB];
 #pragma unroll
     for (int u = 0; u < kUnrollB; ++u) {
       const int t = t0 - u;
+      flag[u] = 0;
       if (t >= 0) {
         const size_t off = seq + static_cast<size_t>(t) * row;
         gv[u] = load_pack<W>(gh + off);
-        if (!a_tinv) av[u] = conj_if<CPLX, W>(load_pack<W>(a + off), conj_ops);
-        rs[u] = drow ? (drow[t] != 0) : false;
-        if (want_ga && !rs[u]) {
+        if (!a_tinv) av[u] = load_pack<W>(a + off);
+        if (drow) flag[u] = drow[t];
+        if (want_ga) {
           if (t > 0) hp[u] = load_pack<W>(h + off - row);
           else hp[u] = h0 ? load_pack_cached<W>(h0 + crow) : fill_pack<W>(0.f, 0.f, CPLX);
-          hp[u] = conj_if<CPLX, W>(hp[u], conj_ops);
         }
       }
     }
@@ -422,18 +442,19 @@ linrec_bwd_kernel(const float* __restrict__ a, int a_tinv, const float* __restri
     for (int u = 0; u < kUnrollB; ++u) {
       const int t = t0 - u;
       if (t >= 0) {
-        const Pack<W>& at = a_tinv ? a_fix : av[u];
         const Pack<W> g = add<W>(gv[u], carry);
         const size_t off = seq + static_cast<size_t>(t) * row;
         store_pack<W>(gb + off, g);
-        if (rs[u]) {
+        if (flag[u] != 0) {
           carry = fill_pack<W>(0.f, 0.f, CPLX);
           if (want_ga && !a_tinv) store_pack<W>(ga + off, carry);
         } else {
+          const Pack<W> at = a_tinv ? a_fix : conj_if<CPLX, W>(av[u], conj_ops);
           carry = mul<CPLX, W>(at, g);
           if (want_ga) {
-            if (a_tinv) ga_acc = mul_add<CPLX, W>(hp[u], g, ga_acc);
-            else store_pack<W>(ga + off, mul<CPLX, W>(hp[u], g));
+            const Pack<W> hc = conj_if<CPLX, W>(hp[u], conj_ops);
+            if (a_tinv) ga_acc = mul_add<CPLX, W>(hc, g, ga_acc);
+            else store_pack<W>(ga + off, mul<CPLX, W>(hc, g));
           }
         }
       }
@@ -507,20 +528,23 @@ loglinrec_fwd_kernel(const float* __restrict__ ls, const float* __restrict__ d,
 
   for (int t0 = 0; t0 < T; t0 += kUnroll) {
     Pack<W> lv[kUnroll], dv[kUnroll];
-    bool rs[kUnroll];
+    unsigned flag[kUnroll];   // raw reset bytes: nothing in the load loop may wait for a loaded value
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int t = t0 + u;
+      flag[u] = 0;
       if (t < T) {
         const size_t off = seq + static_cast<size_t>(t) * row;
         lv[u] = load_pack<W>(ls + off);
         dv[u] = load_pack<W>(d + off);
-        rs[u] = drow ? (drow[t] != 0) : false;
+        if (drow) flag[u] = drow[t];
       }
     }
+    bool rs[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int t = t0 + u;
+      rs[u] = flag[u] != 0;
       if (t < T) {
         Pack<W> yo;
 #pragma unroll
@@ -568,30 +592,30 @@ loglinrec_bwd_kernel(const float* __restrict__ d, const float* __restrict__ ht, 
 
   for (int t0 = T - 1; t0 >= 0; t0 -= kUnroll) {
     Pack<W> dv[kUnroll], xv[kUnroll], xp[kUnroll], gxv[kUnroll], gyv[kUnroll], hv[kUnroll];
+    // The load loop issues every load of its steps without waiting for any: the decay and x_{t-1} are fetched
+    // whether or not step t resets (a branch on the reset byte would hold the later loads back).
+    unsigned flag[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int t = t0 - u;
+      flag[u] = 0;
+      if (t >= 0) {
+        const size_t off = seq + static_cast<size_t>(t) * row;
+        if (drow) flag[u] = drow[t];
+        xv[u] = load_pack<W>(x + off);
+        gxv[u] = gx ? load_pack<W>(gx + off) : fill_pack<W>(0.f, 0.f, false);
+        if (gy) gyv[u] = load_pack<W>(gy + off);
+        dv[u] = load_pack<W>(d + off);
+        if constexpr (GATES) hv[u] = load_pack<W>(ht + off);
+        if (t > 0) xp[u] = load_pack<W>(x + off - row);
+        else xp[u] = x0 ? load_pack_cached<W>(x0 + crow) : fill_pack<W>(-INFINITY, 0.f, false);
+      }
+    }
     bool rs[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int t = t0 - u;
-      if (t >= 0) {
-        const size_t off = seq + static_cast<size_t>(t) * row;
-        rs[u] = drow ? (drow[t] != 0) : false;
-        xv[u] = load_pack<W>(x + off);
-        gxv[u] = gx ? load_pack<W>(gx + off) : fill_pack<W>(0.f, 0.f, false);
-        if (gy) gyv[u] = load_pack<W>(gy + off);
-        if constexpr (GATES) {
-          dv[u] = load_pack<W>(d + off);
-          hv[u] = load_pack<W>(ht + off);
-        }
-        if (!rs[u]) {
-          if constexpr (!GATES) dv[u] = load_pack<W>(d + off);
-          if (t > 0) xp[u] = load_pack<W>(x + off - row);
-          else xp[u] = x0 ? load_pack_cached<W>(x0 + crow) : fill_pack<W>(-INFINITY, 0.f, false);
-        }
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int t = t0 - u;
+      rs[u] = flag[u] != 0;
       if (t >= 0) {
         Pack<W> ols, od;
 #pragma unroll
@@ -690,10 +714,18 @@ int linrec_fwd(const float* a, int a_tinv, const float* b, const float* h0, cons
     }
     return launch_status();
   }
-  if (w == 4)
-    linrec_fwd_kernel<CPLX, 4><<<blocks_for(total / 4), kBlock, 0, s>>>(a, a_tinv, b, h0, a0, done, h, a_last, B, T, row);
-  else
-    linrec_fwd_kernel<CPLX, CPLX ? 2 : 1><<<blocks_for(total / (CPLX ? 2 : 1)), kBlock, 0, s>>>(a, a_tinv, b, h0, a0, done, h, a_last, B, T, row);
+  // A grid of at most three blocks per SM cannot cover the HBM latency with the default depth: such launches keep
+  // two (16-byte packs) or four (narrow packs) times as many time steps of loads in flight, at half the occupancy.
+  constexpr int kN = CPLX ? 2 : 1;
+  const unsigned blocks = w == 4 ? blocks_for(total / 4) : blocks_for(total / kN);
+  const bool small = blocks <= 3u * kNumSMs;
+  if (w == 4) {
+    if (small) linrec_fwd_kernel<CPLX, 4, 2 * MXK_LINREC_UNROLL_F, 2><<<blocks, kBlock, 0, s>>>(a, a_tinv, b, h0, a0, done, h, a_last, B, T, row);
+    else linrec_fwd_kernel<CPLX, 4><<<blocks, kBlock, 0, s>>>(a, a_tinv, b, h0, a0, done, h, a_last, B, T, row);
+  } else {
+    if (small) linrec_fwd_kernel<CPLX, kN, 4 * MXK_LINREC_UNROLL_F, 2><<<blocks, kBlock, 0, s>>>(a, a_tinv, b, h0, a0, done, h, a_last, B, T, row);
+    else linrec_fwd_kernel<CPLX, kN><<<blocks, kBlock, 0, s>>>(a, a_tinv, b, h0, a0, done, h, a_last, B, T, row);
+  }
   return launch_status();
 }
 
@@ -726,10 +758,18 @@ int linrec_bwd(const float* a, int a_tinv, const float* h, const float* h0, cons
       linrec_bwd_tsplit_kernel<CPLX, 8, kW><<<blocks, threads, 0, s>>>(a, a_tinv, h, h0, done, gh, gh_last, gb, ga_full, partial, gh0, B, T, row, conj_ops);
     else
       linrec_bwd_tsplit_kernel<CPLX, 16, kW><<<blocks, threads, 0, s>>>(a, a_tinv, h, h0, done, gh, gh_last, gb, ga_full, partial, gh0, B, T, row, conj_ops);
-  } else if (w == 4)
-    linrec_bwd_kernel<CPLX, 4><<<blocks_for(total / 4), kBlock, 0, s>>>(a, a_tinv, h, h0, done, gh, gh_last, gb, ga_full, partial, gh0, B, T, row, conj_ops);
-  else
-    linrec_bwd_kernel<CPLX, CPLX ? 2 : 1><<<blocks_for(total / (CPLX ? 2 : 1)), kBlock, 0, s>>>(a, a_tinv, h, h0, done, gh, gh_last, gb, ga_full, partial, gh0, B, T, row, conj_ops);
+  } else {
+    constexpr int kN = CPLX ? 2 : 1;
+    const unsigned blocks = w == 4 ? blocks_for(total / 4) : blocks_for(total / kN);
+    const bool small = blocks <= 3u * kNumSMs;   // see linrec_fwd
+    if (w == 4) {
+      if (small) linrec_bwd_kernel<CPLX, 4, 2 * MXK_LINREC_UNROLL_B, 2><<<blocks, kBlock, 0, s>>>(a, a_tinv, h, h0, done, gh, gh_last, gb, ga_full, partial, gh0, B, T, row, conj_ops);
+      else linrec_bwd_kernel<CPLX, 4><<<blocks, kBlock, 0, s>>>(a, a_tinv, h, h0, done, gh, gh_last, gb, ga_full, partial, gh0, B, T, row, conj_ops);
+    } else {
+      if (small) linrec_bwd_kernel<CPLX, kN, 4 * MXK_LINREC_UNROLL_B, 2><<<blocks, kBlock, 0, s>>>(a, a_tinv, h, h0, done, gh, gh_last, gb, ga_full, partial, gh0, B, T, row, conj_ops);
+      else linrec_bwd_kernel<CPLX, kN><<<blocks, kBlock, 0, s>>>(a, a_tinv, h, h0, done, gh, gh_last, gb, ga_full, partial, gh0, B, T, row, conj_ops);
+    }
+  }
   if (int st = launch_status()) return st;
   if (partial) {
     reduce_rows_kernel<<<(row + 31) / 32, kBlock, 0, s>>>(partial, ga, B, row);

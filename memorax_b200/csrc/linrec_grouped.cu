@@ -44,23 +44,27 @@ linrec_grouped_fwd_kernel(const float* __restrict__ a, const float* __restrict__
   for (int t0 = 0; t0 < T; t0 += kUnrollG) {
     float4 bv[kUnrollG];
     float av[kUnrollG];
-    bool rs[kUnrollG];
+    // The first loop only issues loads (a thread issues in order and would wait at the first use of a loaded
+    // value): the reset bytes stay raw until the second loop.
+    unsigned flag[kUnrollG];
 #pragma unroll
     for (int u = 0; u < kUnrollG; ++u) {
       const int t = t0 + u;
+      flag[u] = 0;
       if (t < T) {
         bv[u] = ld_stream(reinterpret_cast<const float4*>(b + seq + static_cast<size_t>(t) * D));
         av[u] = __ldg(arow + static_cast<size_t>(t) * G);
-        rs[u] = drow ? (drow[t] != 0) : false;
+        if (drow) flag[u] = drow[t];
       }
     }
 #pragma unroll
     for (int u = 0; u < kUnrollG; ++u) {
       const int t = t0 + u;
       if (t < T) {
-        const float at = rs[u] ? 0.f : av[u];
+        const bool reset = flag[u] != 0;
+        const float at = reset ? 0.f : av[u];
         cur = make_float4(fmaf(at, cur.x, bv[u].x), fmaf(at, cur.y, bv[u].y), fmaf(at, cur.z, bv[u].z), fmaf(at, cur.w, bv[u].w));
-        acc = rs[u] ? av[u] : av[u] * acc;
+        acc = reset ? av[u] : av[u] * acc;
         st_stream(reinterpret_cast<float4*>(h + seq + static_cast<size_t>(t) * D), cur);
       }
     }
@@ -94,17 +98,20 @@ linrec_grouped_bwd_kernel(const float* __restrict__ a, const float* __restrict__
   for (int t0 = T - 1; t0 >= 0; t0 -= kUnrollG) {
     float4 gv[kUnrollG], hp[kUnrollG];
     float av[kUnrollG];
-    bool rs[kUnrollG];
+    // The first loop only issues loads: h_{t-1} is fetched whether or not step t resets, because a branch on the
+    // reset byte would hold every later load back until that byte has arrived.
+    unsigned flag[kUnrollG];
 #pragma unroll
     for (int u = 0; u < kUnrollG; ++u) {
       const int t = t0 - u;
+      flag[u] = 0;
       if (t >= 0) {
         const size_t off = seq + static_cast<size_t>(t) * D;
         gv[u] = ld_stream(reinterpret_cast<const float4*>(gh + off));
         av[u] = __ldg(arow + static_cast<size_t>(t) * G);
-        rs[u] = drow ? (drow[t] != 0) : false;
+        if (drow) flag[u] = drow[t];
         hp[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (ga_part && !rs[u]) {
+        if (ga_part) {
           if (t > 0) hp[u] = ld_stream(reinterpret_cast<const float4*>(h + off - D));
           else if (h0) hp[u] = *reinterpret_cast<const float4*>(h0 + crow);
         }
@@ -114,12 +121,13 @@ linrec_grouped_bwd_kernel(const float* __restrict__ a, const float* __restrict__
     for (int u = 0; u < kUnrollG; ++u) {
       const int t = t0 - u;
       if (t >= 0) {
+        const bool reset = flag[u] != 0;
         const float4 gt = make_float4(gv[u].x + carry.x, gv[u].y + carry.y, gv[u].z + carry.z, gv[u].w + carry.w);
         st_stream(reinterpret_cast<float4*>(gb + seq + static_cast<size_t>(t) * D), gt);
-        const float at = rs[u] ? 0.f : av[u];
+        const float at = reset ? 0.f : av[u];
         carry = make_float4(at * gt.x, at * gt.y, at * gt.z, at * gt.w);
         if (ga_part) {
-          float part = rs[u] ? 0.f : (hp[u].x * gt.x + hp[u].y * gt.y) + (hp[u].z * gt.z + hp[u].w * gt.w);
+          float part = reset ? 0.f : (hp[u].x * gt.x + hp[u].y * gt.y) + (hp[u].z * gt.z + hp[u].w * gt.w);
 #pragma unroll
           for (int off = 16; off >= 1; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
           if (lane == 0) ga_part[((static_cast<size_t>(bi) * T + t) * G + g) * wpg + wi] = part;
