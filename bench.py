@@ -122,9 +122,9 @@ class LruC4:
     seed = 1234 + 4
     dominant = "linrec_bwd_kernel"
     launches_per_step = 3
-    # one linrec_bwd_kernel launch: 3985.5 MB measured at B=320 (ncu capture summarised under profiles/),
-    # scaled by 1024 / 320 (traffic is proportional to the batch)
-    dominant_traffic_bytes = 3985.5e6 * 1024 / 320
+    # one linrec_bwd_kernel launch: 5602.0 MB measured at B=448 (ncu capture summarised under profiles/),
+    # scaled by 1024 / 448 (traffic is proportional to the batch)
+    dominant_traffic_bytes = 5602.0e6 * 1024 / 448
     cpu_sample_batch = 64
 
     def __init__(self, batch=None):
