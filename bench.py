@@ -844,21 +844,21 @@ class Harness:
         for i in range(max(warmup, 3)):
             w.step(sets[i % nsets], ops)
         self.barrier()
-        graphs = None
+        graph = None
         if getattr(w, "use_graph", False):
-            # launch-bound workload: one captured graph per input set (outputs stay alive in the graph's pool)
-            graphs, keep = [], []
+            # launch-bound workload: the `steps` steps of a timed block are captured as ONE graph (rotating over the
+            # input sets as the direct path does; outputs stay alive in the graph's pool), so that a block is one
+            # replay and the host's launch rate is not what gets measured
+            keep = []
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                for x in sets:
-                    g = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(g, stream=side):
-                        keep.append(w.step(x, ops))
-                    graphs.append(g)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for i in range(steps):
+                        keep.append(w.step(sets[i % nsets], ops))
             torch.cuda.current_stream().wait_stream(side)
-            for g in graphs:
-                g.replay()
+            graph.replay()
             self.barrier()
         blocks, phases, total = [], [], 0.0
         with ClockSampler(self.local) as clocks:
@@ -867,25 +867,24 @@ class Harness:
                 t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 self.barrier()
                 t0.record()
-                for i in range(steps):
-                    if graphs:
-                        marks[i][0].record()
-                        graphs[i % nsets].replay()
-                        marks[i][1].record()
-                    else:
+                if graph:
+                    graph.replay()
+                else:
+                    for i in range(steps):
                         w.step(sets[i % nsets], ops, marks[i])
                 t1.record()
                 self.barrier()
                 ms = self.max_over_ranks(t0.elapsed_time(t1))
                 blocks.append(ms)
                 # marks: [0] after the first launch of a step (or before the only one), [1] after the last
-                phases.append((sum(a.elapsed_time(b) for a, b in marks) / steps, t0.elapsed_time(t1) / steps))
+                per_step = t0.elapsed_time(t1) / steps
+                phases.append((per_step if graph else sum(a.elapsed_time(b) for a, b in marks) / steps, per_step))
                 total += ms
                 if total >= min_seconds * 1e3 or len(blocks) >= 400:
                     break
         order = sorted(range(len(blocks)), key=lambda i: blocks[i])
         mid = order[len(order) // 2]
-        return blocks[mid] / steps, phases[mid][0], blocks, clocks.summary(), bool(graphs)
+        return blocks[mid] / steps, phases[mid][0], blocks, clocks.summary(), graph is not None
 
     def op_record(self, w, ms_per_step, dominant_ms, blocks, clocks, tokens_all_ranks):
         hbm_peak, tc_peak, kind = measured_peaks()
@@ -923,7 +922,7 @@ class Harness:
         ms, dom_ms, blocks, clocks, graphed = self.time_workload(w, sets, steps, warmup, min_seconds)
         rec = self.op_record(w, ms, dom_ms, blocks, clocks, self.world * w.tokens())
         rec["l2"] = f"{len(sets)} input set(s) rotated, {in_bytes * len(sets) / 1e6:.0f} MB of inputs"
-        rec["launch"] = "cuda graph replay" if graphed else "direct"
+        rec["launch"] = "one cuda graph replay per block of steps" if graphed else "direct"
         if hasattr(w, "variants"):
             rec["variants_ms"] = w.variants(sets[0], self.ops)
         if hasattr(w, "trainer"):
@@ -1036,7 +1035,7 @@ def run_gpu_arm(args):
             "config": {"workload": w.name, "batch_per_gpu": w.B, "T": w.T, "tokens_per_step_per_gpu": w.tokens(),
                        "l2": f"{nsets} input set(s) rotated, {in_bytes * nsets / 1e6:.0f} MB of inputs > 126 MB L2",
                        "sharding": "independent sequences per rank, no data-path collective",
-                       "launch": "cuda graph replay" if graphed else "direct",
+                       "launch": "one cuda graph replay per block of steps" if graphed else "direct",
                        "timing": f"{len(blocks)} blocks of {args.steps} steps (>= {args.min_seconds} s of device time), "
                                  "median block reported, max over ranks per block",
                        "block_ms_min_med_max": head["block_ms_min_med_max"]},
