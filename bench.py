@@ -846,16 +846,17 @@ class Harness:
         self.barrier()
         graph = None
         if getattr(w, "use_graph", False):
-            # launch-bound workload: the `steps` steps of a timed block are captured as ONE graph (rotating over the
-            # input sets as the direct path does; outputs stay alive in the graph's pool), so that a block is one
-            # replay and the host's launch rate is not what gets measured
+            # launch-bound workload: up to 32 consecutive steps of a timed block are captured as ONE graph (rotating
+            # over the input sets as the direct path does; outputs stay alive in the graph's pool), so that the
+            # host's launch rate is not what gets measured; a block is steps // 32 replays plus the rest directly
             keep = []
+            graph_steps = min(steps, 32)
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph, stream=side):
-                    for i in range(steps):
+                    for i in range(graph_steps):
                         keep.append(w.step(sets[i % nsets], ops))
             torch.cuda.current_stream().wait_stream(side)
             graph.replay()
@@ -868,7 +869,10 @@ class Harness:
                 self.barrier()
                 t0.record()
                 if graph:
-                    graph.replay()
+                    for _ in range(steps // graph_steps):
+                        graph.replay()
+                    for i in range(steps % graph_steps):
+                        w.step(sets[i % nsets], ops)
                 else:
                     for i in range(steps):
                         w.step(sets[i % nsets], ops, marks[i])
@@ -922,7 +926,7 @@ class Harness:
         ms, dom_ms, blocks, clocks, graphed = self.time_workload(w, sets, steps, warmup, min_seconds)
         rec = self.op_record(w, ms, dom_ms, blocks, clocks, self.world * w.tokens())
         rec["l2"] = f"{len(sets)} input set(s) rotated, {in_bytes * len(sets) / 1e6:.0f} MB of inputs"
-        rec["launch"] = "one cuda graph replay per block of steps" if graphed else "direct"
+        rec["launch"] = "cuda graph replays of up to 32 steps each" if graphed else "direct"
         if hasattr(w, "variants"):
             rec["variants_ms"] = w.variants(sets[0], self.ops)
         if hasattr(w, "trainer"):
@@ -1035,7 +1039,7 @@ def run_gpu_arm(args):
             "config": {"workload": w.name, "batch_per_gpu": w.B, "T": w.T, "tokens_per_step_per_gpu": w.tokens(),
                        "l2": f"{nsets} input set(s) rotated, {in_bytes * nsets / 1e6:.0f} MB of inputs > 126 MB L2",
                        "sharding": "independent sequences per rank, no data-path collective",
-                       "launch": "one cuda graph replay per block of steps" if graphed else "direct",
+                       "launch": "cuda graph replays of up to 32 steps each" if graphed else "direct",
                        "timing": f"{len(blocks)} blocks of {args.steps} steps (>= {args.min_seconds} s of device time), "
                                  "median block reported, max over ranks per block",
                        "block_ms_min_med_max": head["block_ms_min_med_max"]},
