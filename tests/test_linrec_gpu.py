@@ -35,7 +35,10 @@ def rnd(gen, *shape, cplx=False):
     return x
 
 
-SHAPES = [(2, 1, 4), (3, 7, 5), (4, 33, 64), (64, 128, 256), (2, 130, 1024)]
+# the last three reach the one-thread-per-channel kernels on grids of at most three blocks per SM (deeper unroll,
+# T not a multiple of it): narrow packs with T beyond the time-split range, and 16-byte packs
+SHAPES = [(2, 1, 4), (3, 7, 5), (4, 33, 64), (64, 128, 256), (2, 130, 1024), (2, 300, 96), (40, 43, 8192),
+          (20, 43, 8192)]
 
 
 @pytest.mark.parametrize("cplx", [False, True])
