@@ -31,9 +31,20 @@ using namespace umma;
 using namespace linattn;
 
 constexpr int kPanelsK = kPanels + 2;  // 80 columns: a K = 80 contraction needs whole K=16 steps
-// 256 threads: two warpgroups that see the same TMEM lanes (warp w and warp w + 4 share a
-// lane quarter) and split the columns of every row between them.
-constexpr int kBwdThreads = 256;
+// kWgs warpgroups that see the same TMEM lanes (warps w, w + 4, ... share a lane quarter) and
+// split the columns of every row between them.  Two is the measured optimum: four (512 threads, 60
+// registers, no spills) gave the same results 7 % slower on the 256 x 4 x 256 x 64 workload -- the
+// chunk time is the chain of barriers and of the MMA-issuing warp, not the threads' column work.
+#ifndef MXK_LINATTN_BWD_THREADS
+#define MXK_LINATTN_BWD_THREADS 256
+#endif
+constexpr int kBwdThreads = MXK_LINATTN_BWD_THREADS;
+constexpr int kWgs = kBwdThreads / 128;
+static_assert(kWgs == 2 || kWgs == 4, "two or four warpgroups");
+constexpr int kKeysPerThread = 32 / kWgs;        // keys / state features of a query row per thread in epilogue 1
+constexpr int kColsPerThread = 64 / kWgs;        // dphiQ / dphiK columns per thread in epilogue 2
+constexpr int kGPanels = 8 / kWgs;               // panels of the 72-column G | gz accumulator per warpgroup
+constexpr int kGPanelsMax = kGPanels + 1;        // the last warpgroup also takes the gz panel
 
 struct BwdParams {
   const __nv_bfloat16* q;
@@ -74,7 +85,7 @@ struct BwdSmem {
   uint4 g[kPanelsK * kD];     // G^T | gz | 0           [v/8][k]
   uint4 pn[kPanels * kC];     // P / D                  [j/8][i]
   uint4 dp[kPanels * kC];     // dP                     [j/8][i]
-  float xch[2][2][kC];        // per warpgroup: partial den and don of every query row
+  float xch[kWgs][2][kC];     // per warpgroup: partial den and don of every query row
   uint64_t bar[2];
   uint64_t bar_load;
   uint64_t bar_free;   // every thread arrives once it has taken its phi(Q) / phi(K) vectors for the epilogue
@@ -182,13 +193,13 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
   // Cotangent of the next carry -> TMEM (upper lanes) and its bf16 operand copy
   // (upper thread `row` owns G^T[row][.] = dS[.][row]; warpgroup 0 takes value columns
   // 0..31, warpgroup 1 columns 32..63 and gz).
-  const int gp0 = wg ? 4 : 0, gpn = wg ? 5 : 4;   // this warpgroup's panels of the 72-column accumulator
+  const int gp0 = wg * kGPanels, gpn = (wg == kWgs - 1) ? kGPanelsMax : kGPanels;   // this warpgroup's panels of the 72-column accumulator
   {
     const float* gs = p.ds_last ? p.ds_last + static_cast<size_t>(bh) * hd * hd : nullptr;
     const float* gz = p.dz_last ? p.dz_last + static_cast<size_t>(bh) * hd : nullptr;
-    float vals[40];   // all loads first: the TMEM stores below are compiler memory barriers
+    float vals[kGPanelsMax * 8];   // all loads first: the TMEM stores below are compiler memory barriers
 #pragma unroll
-    for (int i = 0; i < 40; ++i) {
+    for (int i = 0; i < kGPanelsMax * 8; ++i) {
       const int vcol = gp0 * 8 + i;
       float x = 0.f;
       if (upper && i < gpn * 8 && row < hd) {
@@ -198,7 +209,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
       vals[i] = x;
     }
 #pragma unroll
-    for (int pn = 0; pn < 5; ++pn) {
+    for (int pn = 0; pn < kGPanelsMax; ++pn) {
       if (pn < gpn) {
         tmem_st8(lane_base + kColHi + (gp0 + pn) * 8, vals + pn * 8);
         if (upper) sm.g[(gp0 + pn) * kD + row] = pack8_bf16(vals + pn * 8);
@@ -231,7 +242,7 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
     //      only if the chunk has a reset ----
     mbar_wait_flag(&sm.bar_load, it & 1, timed_out);
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
+    for (int r = 0; r < 512 / kBwdThreads; ++r) {
       // element-wise, so the physical vector index serves (8 vectors = one token row)
       const int vid = r * kBwdThreads + tid;
       const int trow = vid >> 3;
@@ -290,14 +301,15 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
     {
       const bool live = row_live(dm, row);
       const int lo = row_first_key(dm, row);
-      const int j0 = (upper ? 32 : 0) + wg * 16;   // first key / feature of this thread
+      constexpr int KE = kKeysPerThread, PE = KE / 8;
+      const int j0 = (upper ? 32 : 0) + wg * KE;   // first key / feature of this thread
       const int p0 = j0 >> 3;                      // and its first panel
       float s_dot = 0.f, z_dot = 0.f;
       {
-        float rr[16];
-        tmem_ld_row<16>(lane_base + kColR + wg * 16, rr);
+        float rr[KE];
+        tmem_ld_row<KE>(lane_base + kColR + wg * KE, rr);
 #pragma unroll
-        for (int pp = 0; pp < 2; ++pp) {
+        for (int pp = 0; pp < PE; ++pp) {
           float fq[8];
           unpack8_bf16(sm.q[sw_idx(row, p0 + pp)], fq);
 #pragma unroll
@@ -308,12 +320,12 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
           }
         }
       }
-      float pv[16], av[16];
-      tmem_ld_row<16>(lane_base + kColP + wg * 16, pv);
-      tmem_ld_row<16>(lane_base + kColA + wg * 16, av);
+      float pv[KE], av[KE];
+      tmem_ld_row<KE>(lane_base + kColP + wg * KE, pv);
+      tmem_ld_row<KE>(lane_base + kColA + wg * KE, av);
       float den = live ? z_dot : 0.f, don = live ? s_dot : 0.f;
 #pragma unroll
-      for (int e = 0; e < 16; ++e) {
+      for (int e = 0; e < KE; ++e) {
         const int j = j0 + e;
         const bool m = (j >= lo && j <= row);
         pv[e] = m ? pv[e] : 0.f;
@@ -328,13 +340,19 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
         sm.xch[wg][1][row] = don;
       }
       __syncthreads();
-      den += sm.xch[wg ^ 1][0][row];
-      don += sm.xch[wg ^ 1][1][row];
+      // every thread of the row sums the warpgroups' partials in the same order: identical den / don in all of them
+      den = sm.xch[0][0][row];
+      don = sm.xch[0][1][row];
+#pragma unroll
+      for (int w = 1; w < kWgs; ++w) {
+        den += sm.xch[w][0][row];
+        don += sm.xch[w][1][row];
+      }
       const float dcl = fmaxf(den, p.eps);
       const float inv = 1.f / dcl;
       const float dden = den > p.eps ? -don * inv * inv : 0.f;
 #pragma unroll
-      for (int jq = 0; jq < 2; ++jq) {
+      for (int jq = 0; jq < PE; ++jq) {
         float a[8], d8[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
@@ -345,17 +363,17 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
         sm.pn[(p0 + jq) * kC + row] = pack8_bf16(a);
         sm.dp[(p0 + jq) * kC + row] = pack8_bf16(d8);
       }
-      // scaled dO rows: two of the eight panels per thread, the extra column by one of the four
+      // scaled dO rows: this thread's share of the eight panels, the extra column by one thread of the row
       const float sc = live ? inv : 0.f;
 #pragma unroll
-      for (int pp = 0; pp < 2; ++pp) {
+      for (int pp = 0; pp < PE; ++pp) {
         float f[8];
         unpack8_bf16(sm.d_o[sw_idx(row, p0 + pp)], f);
 #pragma unroll
         for (int e = 0; e < 8; ++e) f[e] *= sc;
         sm.dos[(p0 + pp) * kC + row] = pack8_bf16(f);
       }
-      if (upper && wg == 1) sm.dos[kPanels * kC + row] = make_uint4(pack_bf16(live ? dden : 0.f, 0.f), 0, 0, 0);
+      if (upper && wg == kWgs - 1) sm.dos[kPanels * kC + row] = make_uint4(pack_bf16(live ? dden : 0.f, 0.f), 0, 0, 0);
     }
     fence_smem_to_async();
     fence_before_sync();
@@ -386,12 +404,13 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
       if (leader) commit(&sm.bar[1]);
     }
     MXK_TB(10);
-    // phi(Q) (lower) / phi(K) (upper) of this thread's 32 columns, taken while the MMAs run
-    uint4 featv[4];
+    // phi(Q) (lower) / phi(K) (upper) of this thread's columns, taken while the MMAs run
+    constexpr int FE = kColsPerThread / 8;
+    uint4 featv[FE];
     {
       const uint4* feat = upper ? sm.k : sm.q;
 #pragma unroll
-      for (int pn = 0; pn < 4; ++pn) featv[pn] = feat[sw_idx(row, wg * 4 + pn)];
+      for (int pn = 0; pn < FE; ++pn) featv[pn] = feat[sw_idx(row, wg * FE + pn)];
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&sm.bar_free)) : "memory");
     }
     mbar_wait_flag(&sm.bar[1], it & 1, timed_out);
@@ -409,11 +428,11 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
       // end of the sequence are clipped by the tensor map.
       {
         // one stream: lower chains dphiQ through phi'(q) into dq, upper dphiK through phi'(k) into dk
-        float acc[32];
-        tmem_ld_row<32>(lane_base + kColLo + wg * 32, acc);
-        uint4 packed[4];
+        float acc[kColsPerThread];
+        tmem_ld_row<kColsPerThread>(lane_base + kColLo + wg * kColsPerThread, acc);
+        uint4 packed[FE];
 #pragma unroll
-        for (int pn = 0; pn < 4; ++pn) {
+        for (int pn = 0; pn < FE; ++pn) {
           float f[8];
           unpack8_bf16(featv[pn], f);
 #pragma unroll
@@ -422,30 +441,30 @@ __global__ void __launch_bounds__(kBwdThreads, 2) linattn_bwd_kernel(const __gri
         }
         uint4* stage = upper ? sm.dp : sm.dos;
 #pragma unroll
-        for (int pn = 0; pn < 4; ++pn) stage[sw_idx(row, wg * 4 + pn)] = packed[pn];
+        for (int pn = 0; pn < FE; ++pn) stage[sw_idx(row, wg * FE + pn)] = packed[pn];
       }
       // one stream: lower stores dV, upper refreshes the bf16 operand copy of G | gz
       {
-        float acc[40];
-        if (wg == 0) tmem_ld_row<32>(lane_base + kColHi, acc);
-        else tmem_ld_row<40>(lane_base + kColHi + 32, acc);
-        uint4 packed[5];
+        float acc[kGPanelsMax * 8];
+        if (wg < kWgs - 1) tmem_ld_row<kGPanels * 8>(lane_base + kColHi + gp0 * 8, acc);
+        else tmem_ld_row<kGPanelsMax * 8>(lane_base + kColHi + gp0 * 8, acc);
+        uint4 packed[kGPanelsMax];
 #pragma unroll
-        for (int pn = 0; pn < 5; ++pn)
+        for (int pn = 0; pn < kGPanelsMax; ++pn)
           if (pn < gpn) packed[pn] = pack8_bf16(acc + pn * 8);
         if (upper) {
 #pragma unroll
-          for (int pn = 0; pn < 5; ++pn)
+          for (int pn = 0; pn < kGPanelsMax; ++pn)
             if (pn < gpn) sm.g[(gp0 + pn) * kD + row] = packed[pn];
         }
-        if (!upper) {
+        if (!upper) {   // dV: the first eight panels
 #pragma unroll
-          for (int pn = 0; pn < 4; ++pn) sm.pn[sw_idx(row, wg * 4 + pn)] = packed[pn];
+          for (int pn = 0; pn < kGPanels; ++pn) sm.pn[sw_idx(row, gp0 + pn)] = packed[pn];
         }
         if (upper && c == 0 && row < hd) {
           float* out = p.ds0 ? p.ds0 + static_cast<size_t>(bh) * hd * hd : nullptr;
 #pragma unroll
-          for (int i = 0; i < 40; ++i) {
+          for (int i = 0; i < kGPanelsMax * 8; ++i) {
             const int vcol = gp0 * 8 + i;
             if (i < gpn * 8) {
               if (vcol < kD) {
