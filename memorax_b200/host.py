@@ -29,6 +29,11 @@ class HostPipeline:
     copied whole with the first slice.  ``slices=1`` degenerates to copy, run,
     copy on one stream each (for steps that are not separable over the batch).
 
+    In the eager modes the device copies of the inputs live in staging buffers owned by the pipeline (one set per
+    call that may be in flight) and a call's device outputs are kept until its copy-out has completed, so nothing
+    is allocated per call for the inputs and the allocator tracks no cross-stream uses.  The device tensors that
+    ``run`` returns are therefore only valid until ``overlap_calls`` further calls have been issued.
+
     ``graph=True``: ``step`` must then be capturable (no host synchronisation, no
     data-dependent host control flow) and the host tensors must stay alive and in
     place for as long as the pipeline is used with them."""
@@ -41,6 +46,9 @@ class HostPipeline:
         self.graph = graph
         self.overlap_calls = max(1, int(overlap_calls))
         self._finished = []          # completion events of the calls still in flight, oldest first
+        self._pending = []           # (copy-out event, device outputs) of slices whose copy-out may still be running
+        self._in_bufs = {}           # staging set -> {input name: device buffer}
+        self._calls = 0
         self.inputs_consumed = None
         self._graphs = {}
         self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(device=device) for _ in range(3))
@@ -67,6 +75,32 @@ class HostPipeline:
         entry[0].replay()
         return entry[1]
 
+    def _staging(self, slot, host_inputs):
+        """Device copies of the inputs live in staging buffers that belong to the pipeline (one set per call that
+        may be in flight), so that a call allocates nothing for them and the allocator never has to track
+        cross-stream uses; they are (re)allocated when a call brings tensors of another shape."""
+        bufs = self._in_bufs.setdefault(slot, {})
+        fresh = False
+        for name, t in host_inputs.items():
+            b = bufs.get(name)
+            if b is None or b.shape != t.shape or b.dtype != t.dtype:
+                if b is not None:   # still in use by earlier calls on the copy and kernel streams
+                    b.record_stream(self.s_in)
+                    b.record_stream(self.s_run)
+                bufs[name] = torch.empty(t.shape, dtype=t.dtype, device=self.device)
+                fresh = True
+        if fresh:   # the new blocks' earlier life on the caller's stream comes first
+            born = torch.cuda.Event()
+            born.record(torch.cuda.current_stream(self.device))
+            self.s_in.wait_event(born)
+        return bufs
+
+    def _release_finished(self):
+        """Drops the device tensors of calls whose copy-out has completed (they are kept until then instead of
+        being handed to the allocator with cross-stream use records, which makes every later allocation poll events)."""
+        while self._pending and self._pending[0][0].query():
+            self._pending.pop(0)
+
     def _enqueue(self, host_inputs, host_outputs, capturing):
         main = torch.cuda.current_stream(self.device)
         start = torch.cuda.Event()
@@ -80,6 +114,12 @@ class HostPipeline:
         if streaming and len(self._finished) >= self.overlap_calls:
             self.s_in.wait_event(self._finished[-self.overlap_calls])
             del self._finished[:-self.overlap_calls]
+        staged = None
+        if not capturing:
+            self._release_finished()
+            # staging set i % overlap_calls: its previous user is the call the copy-in has just been made to wait for
+            staged = self._staging(self._calls % self.overlap_calls, host_inputs)
+            self._calls += 1
         keep = []
         shared = {}
         for i in range(self.slices):
@@ -89,22 +129,27 @@ class HostPipeline:
             with torch.cuda.stream(self.s_in):
                 x = {}
                 for name, t in host_inputs.items():
-                    if t.dim() > 0 and t.shape[0] == self.batch:
-                        x[name] = t[lo:hi].to(self.device, non_blocking=True)
+                    sliced = t.dim() > 0 and t.shape[0] == self.batch
+                    if capturing:   # a captured schedule owns its tensors (the graph's pool; kept alive in `keep`)
+                        if sliced:
+                            x[name] = t[lo:hi].to(self.device, non_blocking=True)
+                        else:
+                            if name not in shared:
+                                shared[name] = t.to(self.device, non_blocking=True)
+                            x[name] = shared[name]
+                    elif sliced:
+                        x[name] = staged[name][lo:hi]
+                        x[name].copy_(t[lo:hi], non_blocking=True)
                     else:
                         if name not in shared:
-                            shared[name] = t.to(self.device, non_blocking=True)
+                            shared[name] = staged[name]
+                            shared[name].copy_(t, non_blocking=True)
                         x[name] = shared[name]
-                    if not capturing:   # a captured schedule keeps its tensors alive in `keep`
-                        x[name].record_stream(self.s_run)
                 ready = torch.cuda.Event()
                 ready.record(self.s_in)
             self.s_run.wait_event(ready)
             with torch.cuda.stream(self.s_run):
                 outs = self.step(x)
-                if not capturing:
-                    for o in outs:
-                        o.record_stream(self.s_out)
                 done = torch.cuda.Event()
                 done.record(self.s_run)
             self.s_out.wait_event(done)
@@ -114,6 +159,10 @@ class HostPipeline:
                         dst[lo:hi].copy_(src, non_blocking=True)
                     else:
                         dst.copy_(src, non_blocking=True)
+                if not capturing:   # this slice's device outputs go back to the allocator once they have been copied out
+                    copied = torch.cuda.Event()
+                    copied.record(self.s_out)
+                    self._pending.append((copied, outs))
             keep.append((x, outs))
         finished = torch.cuda.Event()
         finished.record(self.s_out)
@@ -138,3 +187,4 @@ class HostPipeline:
             ev.synchronize()
         self._finished.clear()
         torch.cuda.current_stream(self.device).synchronize()
+        self._release_finished()
