@@ -177,12 +177,12 @@ colsum_partial_kernel(const uint4* __restrict__ x, float* __restrict__ part, lon
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
   if (v < cols8) {
     long long r = r0 + ty;
-    for (; r + 24 < r1; r += 32) {   // four independent loads in flight
-      uint4 raw[4];
+    for (; r + 56 < r1; r += 64) {   // eight independent loads in flight
+      uint4 raw[8];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) raw[u] = ld_stream(x + (r + 8 * u) * cols8 + v);
+      for (int u = 0; u < 8; ++u) raw[u] = ld_stream(x + (r + 8 * u) * cols8 + v);
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 8; ++u) {
         float f[8];
         umma::unpack8_bf16(raw[u], f);
 #pragma unroll
@@ -355,7 +355,7 @@ int colsum_row_blocks(long long rows, int cols) {
   long long want = (4LL * kNumSMs + strips - 1) / strips;
   const long long most = (rows + 31) / 32;
   if (want > most) want = most;
-  if (want > 128) want = 128;
+  if (want > 512) want = 512;
   return static_cast<int>(want < 1 ? 1 : want);
 }
 

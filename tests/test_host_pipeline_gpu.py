@@ -97,3 +97,33 @@ def test_host_pipeline_overlapping_calls():
         for got, want in zip(out, ref):
             assert torch.equal(got, want.cpu()), i
     assert pipe.inputs_consumed is not None and pipe.inputs_consumed.query()
+
+
+def test_host_pipeline_restages_on_new_shapes_and_copies_unsliced_inputs_whole():
+    """The pipeline owns the device copies of its inputs: a later call with other shapes gets new staging buffers,
+    and an input whose leading dimension is not the batch (here the time-invariant decay) is copied whole once."""
+    from memorax_b200 import ops
+    from memorax_b200.host import HostPipeline
+    g = torch.Generator().manual_seed(3)
+    B, D = 8, 96
+
+    def make(T):
+        d = dict(lam=(torch.rand(D, generator=g) * 0.9).to(torch.complex64),
+                 bu=torch.complex(torch.randn(B, T, D, generator=g), torch.randn(B, T, D, generator=g)),
+                 done=(torch.rand(B, T, generator=g) < 0.05).to(torch.uint8))
+        return {k: v.pin_memory() for k, v in d.items()}
+
+    def step(x):
+        h, _ = ops.linrec_fwd(x["lam"], x["bu"], None, None, x["done"], want_decay=False)
+        return (h,)
+
+    for overlap in (1, 2):
+        pipe = HostPipeline(step, B, torch.device("cuda", 0), slices=2, overlap_calls=overlap)
+        calls = [make(T) for T in (40, 40, 72, 40)]
+        refs = [step({k: v.cuda() for k, v in c.items()})[0].cpu() for c in calls]
+        outs = [[torch.zeros(r.shape, dtype=r.dtype).pin_memory()] for r in refs]
+        for c, o in zip(calls, outs):
+            pipe.run(c, o)
+        pipe.wait()
+        for i, (ref, out) in enumerate(zip(refs, outs)):
+            assert torch.equal(out[0], ref), (overlap, i)
