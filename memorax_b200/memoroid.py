@@ -224,7 +224,8 @@ class _ComplexDiagonalCell(MemoroidCellBase):
 
     def read(self, h, x, **kwargs):
         _, _, w_out, skip = self._weights()
-        return _read_real_part(h[0], w_out) + skip * x
+        # one pass for the skip term (y + skip * x as a single fused multiply-add over the output)
+        return torch.addcmul(_read_real_part(h[0], w_out), x, skip)
 
     def binary_operator(self, a, b):
         s_i, a_i = a
