@@ -972,11 +972,11 @@ def run_gpu_arm(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     from memorax_b200.host import HostPipeline
     nslices = args.e2e_slices or getattr(w, "e2e_slices", 1)
-    # "stream": consecutive steps overlap (copy-in of step i+1 under the copy-out of step i, at most two
-    # steps in flight); "graph": one CUDA-graph replay per step; "plain": call by call
+    # "stream": consecutive steps overlap (copy-in of step i+1 under the copy-out of step i, at most three
+    # steps in flight: one step of slack between the two copy directions); "graph": one CUDA-graph replay per step; "plain": call by call
     mode = args.e2e_mode or getattr(w, "e2e_mode", "plain")
     pipe = HostPipeline(lambda xs: w.step(xs, ops), w.B, dev, slices=nslices, graph=(mode == "graph"),
-                        overlap_calls=2 if mode == "stream" else 1)
+                        overlap_calls=3 if mode == "stream" else 1)
     pipe.run(pinned_in, pinned_out)          # warm the three streams' allocator pools
     pipe.wait()
     barrier()
@@ -1063,7 +1063,7 @@ def run_gpu_arm(args):
                     "steps": e2e_steps, "batch_slices_in_flight": nslices, "host_enqueue_ms_per_step": host_enqueue_ms,
                     "host_binding": hz.binding,
                     "wire_floor": wire,
-                    "mode": {"stream": "three streams, copy-in of step i+1 overlaps copy-out of step i (two steps in flight)",
+                    "mode": {"stream": "three streams, copy-in of step i+1 overlaps copy-out of step i (three steps in flight)",
                              "graph": "cuda graph replay of the three-stream schedule",
                              "plain": "three streams, step by step"}[mode]},
             "gpu_launches": w.launches_per_step * args.steps * len(blocks),
