@@ -977,7 +977,8 @@ def run_gpu_arm(args):
     mode = args.e2e_mode or getattr(w, "e2e_mode", "plain")
     pipe = HostPipeline(lambda xs: w.step(xs, ops), w.B, dev, slices=nslices, graph=(mode == "graph"),
                         overlap_calls=3 if mode == "stream" else 1)
-    pipe.run(pinned_in, pinned_out)          # warm the three streams' allocator pools
+    for _ in range(pipe.overlap_calls):      # warm the three streams' allocator pools and every staging set
+        pipe.run(pinned_in, pinned_out)
     pipe.wait()
     barrier()
     e0.record()
