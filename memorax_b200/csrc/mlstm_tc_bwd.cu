@@ -342,10 +342,60 @@ __global__ void __launch_bounds__(kBwdThreads, 2) mlstm_tc_bwd_kernel(const __gr
       gemm<kD / 16>(tmem + kColY, sw_operand(smem_u32(sm.k), false), Operand{smem_u32(sm.g), kD, true}, id_y, false, leader);   // Y = K [G | gn]
       if (leader) commit(&sm.bar[0]);
     }
+    const float delta = sm.gates.delta;
+    // ---- while the first MMA group runs: what depends only on the tiles, the gates and the G of the previous
+    //      chunk (none of it on this group's products, none of it in the columns the group writes) ----
+    {
+      // kappa-scaled copies of K and V (SW tiles: physical vector index serves, row = vid >> 3) and of the "1" column
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int vid = r * kBwdThreads + tid;
+        const float kap = sm.gates.kappa[vid >> 3];
+        float f[8];
+        unpack8_bf16(sm.k[vid], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] *= kap;
+        sm.kk[vid] = pack8_bf16(f);
+        unpack8_bf16(sm.v[vid], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] *= kap;
+        sm.vk[vid] = pack8_bf16(f);
+      }
+      if (tid < kC) sm.vkx[tid] = make_uint4(pack_bf16(tid < valid ? sm.gates.kappa[tid] : 0.f, 0.f), 0, 0, 0);
+      // G <- delta G in tensor memory (upper lanes; the lower lanes of the warp-wide store rewrite a dead dV), and
+      // Ed = delta <G, S_in> before that
+      {
+        float acc[40];
+        if (wg == 0) tmem_ld_row<32>(lane_base + kColHi, acc);
+        else tmem_ld_row<40>(lane_base + kColHi + 32, acc);
+        float ed = 0.f;
+        if (upper) {
+#pragma unroll
+          for (int pn = 0; pn < 5; ++pn) {
+            if (pn < gpn) {
+              float f[8];
+              unpack8_bf16(sm.s[(gp0 + pn) * kD + row], f);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) ed = fmaf(acc[pn * 8 + e], f[e], ed);
+            }
+          }
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) ed += __shfl_xor_sync(0xffffffffu, ed, off);
+        if (lane == 0) sm.gg.edpart[warp] = ed;
+        if (!has_reset) {
+#pragma unroll
+          for (int i = 0; i < 40; ++i) acc[i] *= upper ? delta : 1.f;
+#pragma unroll
+          for (int pn = 0; pn < 5; ++pn)
+            if (pn < gpn) tmem_st8(lane_base + kColHi + (gp0 + pn) * 8, acc + pn * 8);
+          tmem_st_wait();
+        }
+      }
+    }
     mbar_wait_flag(&sm.bar[0], it & 1, timed_out);
     fence_after_sync();
     MXK_TMB(3);
-    const float delta = sm.gates.delta;
 
     // ---- epilogue 1: the four threads of a query row (two half-warps x two warpgroups) each cover 16 keys /
     //      state features; qn and don are completed through shared memory ----
@@ -481,52 +531,6 @@ __global__ void __launch_bounds__(kBwdThreads, 2) mlstm_tc_bwd_kernel(const __gr
             acc += (row < valid ? 1.f : 0.f) * y[24];     // the "1" column
           }
           sm.gg.ekpart[wg][row] = sm.gates.kappa[row] * acc;
-        }
-      }
-      // kappa-scaled copies of K and V (SW tiles: physical vector index serves, row = vid >> 3) and of the "1" column
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        const int vid = r * kBwdThreads + tid;
-        const float kap = sm.gates.kappa[vid >> 3];
-        float f[8];
-        unpack8_bf16(sm.k[vid], f);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] *= kap;
-        sm.kk[vid] = pack8_bf16(f);
-        unpack8_bf16(sm.v[vid], f);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] *= kap;
-        sm.vk[vid] = pack8_bf16(f);
-      }
-      if (tid < kC) sm.vkx[tid] = make_uint4(pack_bf16(tid < valid ? sm.gates.kappa[tid] : 0.f, 0.f), 0, 0, 0);
-      // G <- delta G in tensor memory (upper lanes; the lower lanes of the warp-wide store rewrite a dead dV), and
-      // Ed = delta <G, S_in> before that
-      {
-        float acc[40];
-        if (wg == 0) tmem_ld_row<32>(lane_base + kColHi, acc);
-        else tmem_ld_row<40>(lane_base + kColHi + 32, acc);
-        float ed = 0.f;
-        if (upper) {
-#pragma unroll
-          for (int pn = 0; pn < 5; ++pn) {
-            if (pn < gpn) {
-              float f[8];
-              unpack8_bf16(sm.s[(gp0 + pn) * kD + row], f);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) ed = fmaf(acc[pn * 8 + e], f[e], ed);
-            }
-          }
-        }
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) ed += __shfl_xor_sync(0xffffffffu, ed, off);
-        if (lane == 0) sm.gg.edpart[warp] = ed;
-        if (!has_reset) {
-#pragma unroll
-          for (int i = 0; i < 40; ++i) acc[i] *= upper ? delta : 1.f;
-#pragma unroll
-          for (int pn = 0; pn < 5; ++pn)
-            if (pn < gpn) tmem_st8(lane_base + kColHi + (gp0 + pn) * 8, acc + pn * 8);
-          tmem_st_wait();
         }
       }
     }
