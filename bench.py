@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the sequence-mixing hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c1|c5]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c1|c5|a7|n1|n1t|n2|n4]
     python bench.py --impl reference ...      # CPU arm: the oracle port, host cores
 
 A step is one pass of the hot path over one batch of seeded synthetic input:
@@ -441,6 +441,62 @@ class MambaN2:
         return h
 
 
+class MinGruA7:
+    """MinGRU scan with its gate math fused in (min_gru.py:52-78 under the reset wrapper of memoroid.py:60-91),
+    fwd+bwd: the two Dense pre-activations z, h~ in, log-space states and read-out h = exp(x) out, cotangents of the
+    pre-activations back.  B=256, T=256, D=1024, fp32, done ~ Bernoulli(0.01), default (-inf) carry."""
+    name = "a7_mingru_fused_gates_fwd_bwd"
+    dtype = "f32"
+    B, T, D = 256, 256, 1024
+    p_done = 0.01
+    seed = 1234 + 9
+    dominant = "loglinrec_bwd_kernel"
+    launches_per_step = 2
+    dominant_traffic_bytes = None
+    cpu_sample_batch = 32
+
+    def __init__(self, batch=None):
+        self.B = batch or self.B
+
+    def tokens(self):
+        return self.B * self.T
+
+    def host_inputs(self, seed_offset=0, device="cpu"):
+        g = torch.Generator(device=device).manual_seed(self.seed + seed_offset)
+        rn = lambda *s: torch.randn(*s, generator=g, device=device)
+        shp = (self.B, self.T, self.D)
+        return dict(z=rn(*shp) * 2.0, ht=rn(*shp) * 2.0, gy=rn(*shp),
+                    done=(torch.rand(self.B, self.T, generator=g, device=device) < self.p_done).to(torch.uint8))
+
+    def algorithmic_bytes(self):
+        n = self.B * self.T * self.D
+        # fwd: read z, h~; write x, y.  bwd: read z, h~, x, the cotangents of x and y; write the cotangents of z, h~
+        return {"loglinrec_fwd_kernel": 16 * n, "loglinrec_bwd_kernel": 28 * n}
+
+    def algorithmic_flops(self):
+        n = self.B * self.T * self.D
+        return {"loglinrec_fwd_kernel": 20 * n, "loglinrec_bwd_kernel": 30 * n}
+
+    def step(self, x, ops, mark=None):
+        z, ht = x["z"].detach().requires_grad_(), x["ht"].detach().requires_grad_()
+        xs, y, _ = ops.MinGRUFused.apply(z, ht, None, None, x["done"])
+        if mark:
+            mark[0].record()
+        gz, gh = torch.autograd.grad((y,), (z, ht), (x["gy"],))
+        if mark:
+            mark[1].record()
+        return (xs[:, -1], y, gz, gh)
+
+    def cpu_step(self, x):
+        from oracle import memoroid_oracle as mo
+        sp = torch.nn.functional.softplus
+        z, ht = x["z"].clone().requires_grad_(), x["ht"].clone().requires_grad_()
+        log_state = -sp(-z) + torch.where(ht >= 0, torch.log(torch.relu(ht) + 0.5), -sp(-ht))
+        xs, _ = mo.mingru_seq(log_state, -sp(z), torch.full((z.shape[0], z.shape[2]), -float("inf")), x["done"].float())
+        (xs.exp() * x["gy"]).sum().backward()
+        return xs
+
+
 class MlstmN1:
     """mLSTM scan + read-out fwd+bwd (mlstm.py:163-240) at the linear-attention configuration's size: B=256,
     H=4, T=256, head dim 64, fp32; log_i ~ N(0, 0.1^2) (the cell's gate bias init), log_f = -softplus(-N(4.5, 1))
@@ -645,7 +701,7 @@ class LruLayerN4:
             return torch.matmul(h, torch.complex(cell.C_real, cell.C_imag).t()).real + cell.D * x["x"]
 
 
-WORKLOADS = {"n4": LruLayerN4, "n1": MlstmN1, "n1t": MlstmTcN1, "c2": LinAttnC2, "c3": GDeltaC3, "c4": LruC4, "c1": LinRecC1, "c5": TrainC5, "n2": MambaN2}
+WORKLOADS = {"a7": MinGruA7, "n4": LruLayerN4, "n1": MlstmN1, "n1t": MlstmTcN1, "c2": LinAttnC2, "c3": GDeltaC3, "c4": LruC4, "c1": LinRecC1, "c5": TrainC5, "n2": MambaN2}
 
 
 # ------------------------------------------------------------ clock sampling
@@ -1025,7 +1081,7 @@ def run_gpu_arm(args):
     if args.ops:
         per_op[args.workload] = {k: head[k] for k in ("workload", "batch_per_gpu", "ms_per_step", "tokens_per_s",
                                                       "dtype", "blocks", "clocks", "roofline")}
-        for name in ("c1", "c3", "c4", "c5", "n1", "n1t", "n2", "n4"):
+        for name in ("c1", "c3", "c4", "c5", "a7", "n1", "n1t", "n2", "n4"):
             if name == args.workload:
                 continue
             per_op[name] = hz.run_op(WORKLOADS[name], None, args.steps, args.warmup, args.min_seconds)

@@ -550,9 +550,11 @@ loglinrec_fwd_kernel(const float* __restrict__ ls, const float* __restrict__ d,
 #pragma unroll
         for (int i = 0; i < W; ++i) {
           if constexpr (GATES) {
+            // softplus(z) = max(z, 0) + L and softplus(-z) = max(-z, 0) + L share L = log1p(exp(-|z|))
             const float z = lv[u].v[i], ht = dv[u].v[i];
-            lv[u].v[i] = log_g(ht) - softplus_f(-z);
-            dv[u].v[i] = -softplus_f(z);
+            const float lz = log1pf(expf(-fabsf(z)));
+            lv[u].v[i] = log_g(ht) - (fmaxf(-z, 0.f) + lz);
+            dv[u].v[i] = -(fmaxf(z, 0.f) + lz);
           }
           cur.v[i] = rs[u] ? lv[u].v[i] : log_add_exp(dv[u].v[i] + cur.v[i], lv[u].v[i]);
           acc.v[i] = rs[u] ? dv[u].v[i] : dv[u].v[i] + acc.v[i];
@@ -623,8 +625,10 @@ loglinrec_bwd_kernel(const float* __restrict__ d, const float* __restrict__ ht, 
           float g = gxv[u].v[i] + carry.v[i];
           if (gy) g = fmaf(gyv[u].v[i], expf(xv[u].v[i]), g);
           float w = 0.f;
+          float ez = 0.f;   // exp(-|z|): shared by softplus(z) here and sigmoid(z) below
+          if constexpr (GATES) ez = expf(-fabsf(dv[u].v[i]));
           if (!rs[u]) {
-            const float dec = GATES ? -softplus_f(dv[u].v[i]) : dv[u].v[i];
+            const float dec = GATES ? -(fmaxf(dv[u].v[i], 0.f) + log1pf(ez)) : dv[u].v[i];
             const float p = dec + xp[u].v[i];
             w = (p == -INFINITY) ? 0.f : expf(p - xv[u].v[i]);
           }
@@ -633,7 +637,7 @@ loglinrec_bwd_kernel(const float* __restrict__ d, const float* __restrict__ ht, 
           carry.v[i] = od.v[i];
           if constexpr (GATES) {
             // chain rule through the gate math: d(-softplus(-z))/dz = 1 - sigmoid(z), d(-softplus(z))/dz = -sigmoid(z)
-            const float sg = sigmoid_f(dv[u].v[i]);
+            const float sg = (dv[u].v[i] >= 0.f ? 1.f : ez) / (1.f + ez);
             const float g_ls = ols.v[i], g_d = od.v[i];
             ols.v[i] = g_ls * (1.f - sg) - g_d * sg;
             od.v[i] = g_ls * dlog_g(hv[u].v[i]);
