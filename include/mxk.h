@@ -120,6 +120,14 @@ int mxk_linrec_c64_bwd(const float* a, int a_time_invariant, const float* h, con
                        float* ga, float* gh0, void* workspace, size_t workspace_bytes,
                        int B, int T, int D, int conjugate, mxk_stream_t stream);
 
+/* State after the LAST step only, h_T (B,D), of the same recurrences: nothing is stored per step, so the launch is
+ * one read stream.  This is what Memoroid._propagate_sensitivities returns per parameter leaf (memoroid.py:114-141:
+ * the scan's last element, `x[:, -1:]`); the reference materialises all T steps to take it. */
+int mxk_linrec_f32_last(const float* a, int a_time_invariant, const float* b, const float* h0, const uint8_t* done,
+                        float* h_last, int B, int T, int D, mxk_stream_t stream);
+int mxk_linrec_c64_last(const float* a, int a_time_invariant, const float* b, const float* h0, const uint8_t* done,
+                        float* h_last, int B, int T, int D, mxk_stream_t stream);
+
 /* The real recurrence with one decay per GROUP of channels: a is (B,T,G), D = G * group channels,
  * channel c uses a[..., c / group].  This is MambaCell's scan (mamba.py:109-122: a scalar decay per
  * (b, t, head) over a state_dim x head_dim matrix state) without expanding the decay to full width.
@@ -130,6 +138,9 @@ int mxk_linrec_c64_bwd(const float* a, int a_time_invariant, const float* h, con
 size_t mxk_linrec_grouped_bwd_workspace_bytes(int B, int T, int D, int G);
 int mxk_linrec_f32_grouped_fwd(const float* a, const float* b, const float* h0, const float* a0, const uint8_t* done,
                                float* h, float* a_last, int B, int T, int D, int G, mxk_stream_t stream);
+/* h_T (B,D) only, as mxk_linrec_f32_last. */
+int mxk_linrec_f32_grouped_last(const float* a, const float* b, const float* h0, const uint8_t* done, float* h_last,
+                                int B, int T, int D, int G, mxk_stream_t stream);
 int mxk_linrec_f32_grouped_bwd(const float* a, const float* h, const float* h0, const uint8_t* done, const float* gh,
                                const float* gh_last, float* gb, float* ga, float* gh0, void* workspace,
                                size_t workspace_bytes, int B, int T, int D, int G, mxk_stream_t stream);

@@ -27,6 +27,9 @@ SIGNATURES = {
     "mxk_linrec_f32_bwd": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _i, _i, _i, _p]),
     "mxk_linrec_c64_bwd": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _z, _i, _i, _i, _i, _p]),
     "mxk_linrec_grouped_bwd_workspace_bytes": (_z, [_i, _i, _i, _i]),
+    "mxk_linrec_f32_last": (_i, [_p, _i] + [_p] * 4 + [_i, _i, _i, _p]),
+    "mxk_linrec_c64_last": (_i, [_p, _i] + [_p] * 4 + [_i, _i, _i, _p]),
+    "mxk_linrec_f32_grouped_last": (_i, [_p] * 5 + [_i, _i, _i, _i, _p]),
     "mxk_linrec_f32_grouped_fwd": (_i, [_p] * 7 + [_i, _i, _i, _i, _p]),
     "mxk_linrec_f32_grouped_bwd": (_i, [_p] * 10 + [_z, _i, _i, _i, _i, _p]),
     "mxk_linrec_noalloc_max_elements": (_z, []),

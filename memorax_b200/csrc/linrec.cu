@@ -140,7 +140,8 @@ __device__ __forceinline__ Pack<W> add(const Pack<W>& x, const Pack<W>& y) {
 // ------------------------------------------------------------------ forward
 // Row stride is `row` floats (D for real, 2D for complex); a thread's W floats
 // start at column `col`.
-template <bool CPLX, int W, int kUnrollF = MXK_LINREC_UNROLL_F, int kMinBlocks = MXK_LINREC_MINB_F>
+// kLastOnly: `h` is (B, row) and receives the state after the last step only (no per-step stores).
+template <bool CPLX, int W, int kUnrollF = MXK_LINREC_UNROLL_F, int kMinBlocks = MXK_LINREC_MINB_F, bool kLastOnly = false>
 __global__ void __launch_bounds__(kBlock, kMinBlocks)
 linrec_fwd_kernel(const float* __restrict__ a, int a_tinv, const float* __restrict__ b,
                   const float* __restrict__ h0, const float* __restrict__ a0,
@@ -185,9 +186,14 @@ linrec_fwd_kernel(const float* __restrict__ a, int a_tinv, const float* __restri
         const bool reset = flag[u] != 0;
         cur = reset ? bv[u] : mul_add<CPLX, W>(at, cur, bv[u]);
         if (want_decay) acc = reset ? at : mul<CPLX, W>(at, acc);
-        store_pack<W>(h + seq + static_cast<size_t>(t) * row, cur);
+        if constexpr (!kLastOnly) store_pack<W>(h + seq + static_cast<size_t>(t) * row, cur);
       }
     }
+  }
+  if constexpr (kLastOnly) {
+    float* dst = h + static_cast<size_t>(bi) * row + col;
+#pragma unroll
+    for (int i = 0; i < W; ++i) dst[i] = cur.v[i];
   }
   if (want_decay) {
     float* dst = a_last + static_cast<size_t>(bi) * row + col;
@@ -733,6 +739,30 @@ int linrec_fwd(const float* a, int a_tinv, const float* b, const float* h0, cons
   return launch_status();
 }
 
+// State after the last step only: one read stream, nothing stored per step (the deep-unroll variants:
+// with no stores in flight the loads are all there is to overlap).
+template <bool CPLX>
+int linrec_last(const float* a, int a_tinv, const float* b, const float* h0, const uint8_t* done, float* h_last,
+                int B, int T, int D, mxk_stream_t stream) {
+  if (!a || !b || !h_last) return MXK_ERR_NULL;
+  if (int st = check_dims(B, T, D)) return st;
+  const int row = CPLX ? 2 * D : D;
+  const int min_align = CPLX ? 8 : 4;
+  for (const void* p : {(const void*)a, (const void*)b, (const void*)h0, (const void*)h_last})
+    if (p && (reinterpret_cast<uintptr_t>(p) % min_align)) return MXK_ERR_ALIGN;
+  const long long total = static_cast<long long>(B) * row;
+  const int w = pick_width(total, row, CPLX, {a, b, h0, h_last});
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  constexpr int kN = CPLX ? 2 : 1;
+  if (w == 4)
+    linrec_fwd_kernel<CPLX, 4, 2 * MXK_LINREC_UNROLL_F, 2, true><<<blocks_for(total / 4), kBlock, 0, s>>>(
+        a, a_tinv, b, h0, nullptr, done, h_last, nullptr, B, T, row);
+  else
+    linrec_fwd_kernel<CPLX, kN, 4 * MXK_LINREC_UNROLL_F, 2, true><<<blocks_for(total / kN), kBlock, 0, s>>>(
+        a, a_tinv, b, h0, nullptr, done, h_last, nullptr, B, T, row);
+  return launch_status();
+}
+
 template <bool CPLX>
 int linrec_bwd(const float* a, int a_tinv, const float* h, const float* h0, const uint8_t* done,
                const float* gh, const float* gh_last, float* gb, float* ga, float* gh0,
@@ -833,6 +863,16 @@ int mxk_linrec_c64_fwd(const float* a, int a_time_invariant, const float* b, con
                        const float* a0, const uint8_t* done, float* h, float* a_last,
                        int B, int T, int D, mxk_stream_t stream) {
   return mxk::linrec_fwd<true>(a, a_time_invariant, b, h0, a0, done, h, a_last, B, T, D, stream);
+}
+
+int mxk_linrec_f32_last(const float* a, int a_time_invariant, const float* b, const float* h0, const uint8_t* done,
+                        float* h_last, int B, int T, int D, mxk_stream_t stream) {
+  return mxk::linrec_last<false>(a, a_time_invariant, b, h0, done, h_last, B, T, D, stream);
+}
+
+int mxk_linrec_c64_last(const float* a, int a_time_invariant, const float* b, const float* h0, const uint8_t* done,
+                        float* h_last, int B, int T, int D, mxk_stream_t stream) {
+  return mxk::linrec_last<true>(a, a_time_invariant, b, h0, done, h_last, B, T, D, stream);
 }
 
 size_t mxk_linrec_bwd_workspace_bytes(int is_complex, int a_time_invariant, int B, int T, int D) {

@@ -21,7 +21,8 @@ constexpr int kBlockG = 256;
 // kUnrollG time steps of loads are in flight per thread.  4 steps at four blocks per SM when the grid fills the
 // machine; 8 steps at two blocks per SM (twice the registers) when it does not, so that a small batch still keeps
 // enough bytes in flight per SM to cover the HBM latency.
-template <int kUnrollG, int kMinBlocks>
+// kLastOnly: `h` is (B, D) and receives the state after the last step only.
+template <int kUnrollG, int kMinBlocks, bool kLastOnly = false>
 __global__ void __launch_bounds__(kBlockG, kMinBlocks)
 linrec_grouped_fwd_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ h0,
                           const float* __restrict__ a0, const uint8_t* __restrict__ done, float* __restrict__ h,
@@ -65,10 +66,11 @@ linrec_grouped_fwd_kernel(const float* __restrict__ a, const float* __restrict__
         const float at = reset ? 0.f : av[u];
         cur = make_float4(fmaf(at, cur.x, bv[u].x), fmaf(at, cur.y, bv[u].y), fmaf(at, cur.z, bv[u].z), fmaf(at, cur.w, bv[u].w));
         acc = reset ? av[u] : av[u] * acc;
-        st_stream(reinterpret_cast<float4*>(h + seq + static_cast<size_t>(t) * D), cur);
+        if constexpr (!kLastOnly) st_stream(reinterpret_cast<float4*>(h + seq + static_cast<size_t>(t) * D), cur);
       }
     }
   }
+  if constexpr (kLastOnly) *reinterpret_cast<float4*>(h + static_cast<size_t>(bi) * D + col) = cur;
   if (owns_decay) a_last[static_cast<size_t>(bi) * G + g] = acc;
 }
 
@@ -182,6 +184,21 @@ int mxk_linrec_f32_grouped_fwd(const float* a, const float* b, const float* h0, 
     linrec_grouped_fwd_kernel<8, 2><<<blocks, kBlockG, 0, s>>>(a, b, h0, a0, done, h, a_last, B, T, D, G, D / G);
   else
     linrec_grouped_fwd_kernel<4, 4><<<blocks, kBlockG, 0, s>>>(a, b, h0, a0, done, h, a_last, B, T, D, G, D / G);
+  return launch_status();
+}
+
+int mxk_linrec_f32_grouped_last(const float* a, const float* b, const float* h0, const uint8_t* done, float* h_last,
+                                int B, int T, int D, int G, mxk_stream_t stream) {
+  using namespace mxk;
+  if (!a || !b || !h_last) return MXK_ERR_NULL;
+  if (int st = check_grouped(B, T, D, G)) return st;
+  for (const void* p : {(const void*)b, (const void*)h0, (const void*)h_last})
+    if (p && !aligned16(p)) return MXK_ERR_ALIGN;
+  if (reinterpret_cast<uintptr_t>(a) & 3u) return MXK_ERR_ALIGN;
+  const long long threads = static_cast<long long>(B) * (D / 4);
+  const unsigned blocks = static_cast<unsigned>((threads + kBlockG - 1) / kBlockG);
+  linrec_grouped_fwd_kernel<8, 2, true><<<blocks, kBlockG, 0, static_cast<cudaStream_t>(stream)>>>(
+      a, b, h0, nullptr, done, h_last, nullptr, B, T, D, G, D / G);
   return launch_status();
 }
 

@@ -134,7 +134,7 @@ class Memoroid(SequenceModel):
         memoroid.py:114-141): for every parameter leaf, S_t = done_t ? J_t : decay_t S_{t-1} + J_t
         with ``decay`` (B,T,H) broadcast over the leaf's parameter axes, ``jacobians[name]``
         (B,T,H,*param_shape), ``sensitivity[name]`` (B,1,H,*param_shape); returns the dict of
-        S_T, shaped like ``sensitivity``.  One linear-recurrence launch per leaf -- the reference's
+        S_T, shaped like ``sensitivity``.  One last-state-only linear-recurrence launch per leaf -- the reference's
         ``where(done, 0, decay)`` is the kernel's reset rule.  Real or complex (the LRU's); the decay is
         never expanded to the leaf's width when it need not be: a decay that is one (H,) vector broadcast
         over (B,T) (the LRU's lambda, lru.py:118) goes to the kernels as a time-invariant decay, and a
@@ -151,16 +151,17 @@ class Memoroid(SequenceModel):
             psize = math.prod(param_shape)
             b_flat = jac.to(dt).reshape(bsz, steps, hid * psize)
             s_flat = sens.to(dt).reshape(bsz, hid * psize)
+            # only S_T is returned, so the kernels store nothing per step (one read stream over the Jacobians)
             if broadcast:
                 a = decay[0, 0].to(dt).repeat_interleave(psize)
-                h, _ = ops.linrec_fwd(a, b_flat, s_flat, None, done, want_decay=False)
+                last = ops.linrec_last(a, b_flat, s_flat, done)
             elif not cplx and ops.grouped_decay_supported(hid * psize, hid):
                 # one decay per hidden unit, broadcast over its parameter axes inside the kernel
-                h, _ = ops.linrec_grouped_fwd(decay.float(), b_flat, s_flat, None, done, want_decay=False)
+                last = ops.linrec_grouped_last(decay.float(), b_flat, s_flat, done)
             else:
                 a = decay.to(dt).repeat_interleave(psize, dim=-1)
-                h, _ = ops.linrec_fwd(a, b_flat, s_flat, None, done, want_decay=False)
-            out[name] = h[:, -1:].reshape(bsz, 1, hid, *param_shape)
+                last = ops.linrec_last(a, b_flat, s_flat, done)
+            out[name] = last.reshape(bsz, 1, hid, *param_shape)
         return out
 
     def local_jacobian(self, inputs, done, carry, sensitivity=None, **kwargs):

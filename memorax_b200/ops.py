@@ -125,6 +125,32 @@ def grouped_decay_supported(dim, groups):
     return groups > 0 and dim % groups == 0 and (dim // groups) % 128 == 0
 
 
+def linrec_last(a, b, h0=None, done=None):
+    """The state after the last step, h_T (B,D), of :func:`linrec_fwd`'s recurrence, without storing the T states."""
+    cplx = b.is_complex()
+    dt = torch.complex64 if cplx else torch.float32
+    a, b, h0 = _dev(a, dt, "a"), _dev(b, dt, "b"), _dev(h0, dt, "h0")
+    bsz, steps, dim = b.shape
+    tinv = a.dim() == 1
+    assert a.shape == ((dim,) if tinv else b.shape)
+    h_last = torch.empty(bsz, dim, dtype=dt, device=b.device)
+    _lib.call("mxk_linrec_c64_last" if cplx else "mxk_linrec_f32_last", _ptr(a), int(tinv), _ptr(b), _ptr(h0),
+              _ptr(_done_bytes(done)), _ptr(h_last), bsz, steps, dim, _stream())
+    return h_last
+
+
+def linrec_grouped_last(a, b, h0=None, done=None):
+    """h_T (B,D) of :func:`linrec_grouped_fwd`'s recurrence, without storing the T states."""
+    a, b, h0 = _dev(a, torch.float32, "a"), _dev(b, torch.float32, "b"), _dev(h0, torch.float32, "h0")
+    bsz, steps, dim = b.shape
+    groups = a.shape[-1]
+    assert a.shape == (bsz, steps, groups)
+    h_last = torch.empty(bsz, dim, dtype=torch.float32, device=b.device)
+    _lib.call("mxk_linrec_f32_grouped_last", _ptr(a), _ptr(b), _ptr(h0), _ptr(_done_bytes(done)), _ptr(h_last),
+              bsz, steps, dim, groups, _stream())
+    return h_last
+
+
 def linrec_grouped_fwd(a, b, h0=None, a0=None, done=None, want_decay=True):
     """h_t[c] = done_t ? b_t[c] : a_t[c // group] h_{t-1}[c] + b_t[c]; ``a`` is (B,T,G), ``b`` (B,T,D) with
     D = G * group.  Returns ``(h, a_last)`` with the carry's decay leaf ``a_last`` (B,G)."""

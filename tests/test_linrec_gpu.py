@@ -298,3 +298,39 @@ def test_mingru_fused_gate_math(shape):
     # default (-inf) carry: finite everywhere
     x2, y2, _ = ops.MinGRUFused.apply(cu(z), cu(ht), None, None, done.cuda())
     assert torch.isfinite(y2).all() and not torch.isnan(x2).any()
+
+
+@pytest.mark.parametrize("cplx", [False, True])
+@pytest.mark.parametrize("tinv", [False, True])
+@pytest.mark.parametrize("shape", [(2, 1, 4), (3, 7, 5), (5, 70, 48), (40, 43, 8192)])
+def test_linrec_last_state_only(shape, tinv, cplx):
+    """The last-state-only entry points (what the RTRL propagation returns, memoroid.py:114-141) against the
+    fp64 oracle's final state, with resets, a carried state and T not a multiple of the unroll depth."""
+    from memorax_b200 import ops
+    bsz, steps, dim = shape
+    gen = torch.Generator().manual_seed(77 + steps + dim)
+    a = rnd(gen, *((dim,) if tinv else shape), cplx=cplx)
+    a = a / (1.0 + a.abs()) * 1.1
+    b, h0 = rnd(gen, *shape, cplx=cplx), rnd(gen, bsz, dim, cplx=cplx)
+    done = make_done(gen, bsz, steps, 0.05)
+    h_ref, _ = mo.linrec_seq(a, b, h0, done.double())
+    dt = torch.complex64 if cplx else torch.float32
+    last = ops.linrec_last(a.to(dt).cuda(), b.to(dt).cuda(), h0.to(dt).cuda(), done.cuda())
+    close(last, h_ref[:, -1], what="h_T")
+    last0 = ops.linrec_last(a.to(dt).cuda(), b.to(dt).cuda(), None, None)
+    h_ref0, _ = mo.linrec_seq(a, b, torch.zeros_like(h0), torch.zeros(bsz, steps, dtype=torch.float64))
+    close(last0, h_ref0[:, -1], what="h_T without carry and resets")
+
+
+def test_linrec_grouped_last_state_only():
+    from memorax_b200 import ops
+    gen = torch.Generator().manual_seed(5)
+    bsz, steps, groups, group = 6, 37, 3, 256
+    a = torch.rand(bsz, steps, groups, generator=gen, dtype=torch.float64)
+    b, h0 = rnd(gen, bsz, steps, groups * group), rnd(gen, bsz, groups * group)
+    done = make_done(gen, bsz, steps, 0.08)
+    h_ref, _ = mo.linrec_seq(a.repeat_interleave(group, dim=-1), b, h0, done.double())
+    last = ops.linrec_grouped_last(a.float().cuda(), b.float().cuda(), h0.float().cuda(), done.cuda())
+    close(last, h_ref[:, -1], what="h_T")
+    full, _ = ops.linrec_grouped_fwd(a.float().cuda(), b.float().cuda(), h0.float().cuda(), None, done.cuda(), want_decay=False)
+    assert torch.equal(last, full[:, -1])
