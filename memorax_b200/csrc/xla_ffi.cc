@@ -69,6 +69,20 @@ ffi::Error LinRecFwd(cudaStream_t stream, ffi::Buffer<ffi::F32> a, ffi::Buffer<f
                                     a0.typed_data(), done.typed_data(), h->typed_data(), a_last->typed_data(),
                                     (int)d[0], (int)d[1], (int)d[2], stream));
 }
+// RTRL sensitivities after the last step (memoroid.py:114-141 returns x[:, -1:]): nothing is stored per step.
+ffi::Error LinRecLast(cudaStream_t stream, ffi::Buffer<ffi::F32> a, ffi::Buffer<ffi::F32> b, ffi::Buffer<ffi::F32> h0,
+                      ffi::Buffer<ffi::U8> done, ffi::ResultBuffer<ffi::F32> h_last) {
+  auto d = b.dimensions();
+  return ToError(mxk_linrec_f32_last(a.typed_data(), a.dimensions().size() == 1, b.typed_data(), h0.typed_data(),
+                                     done.typed_data(), h_last->typed_data(), (int)d[0], (int)d[1], (int)d[2], stream));
+}
+ffi::Error LruLast(cudaStream_t stream, ffi::Buffer<ffi::C64> lam, ffi::Buffer<ffi::C64> b, ffi::Buffer<ffi::C64> h0,
+                   ffi::Buffer<ffi::U8> done, ffi::ResultBuffer<ffi::C64> h_last) {
+  auto d = b.dimensions();
+  return ToError(mxk_linrec_c64_last((const float*)lam.typed_data(), lam.dimensions().size() == 1,
+                                     (const float*)b.typed_data(), (const float*)h0.typed_data(), done.typed_data(),
+                                     (float*)h_last->typed_data(), (int)d[0], (int)d[1], (int)d[2], stream));
+}
 ffi::Error LinRecBwd(cudaStream_t stream, ffi::Buffer<ffi::F32> a, ffi::Buffer<ffi::F32> h, ffi::Buffer<ffi::F32> h0,
                      ffi::Buffer<ffi::U8> done, ffi::Buffer<ffi::F32> gh, ffi::Buffer<ffi::F32> gh_last,
                      ffi::ResultBuffer<ffi::F32> gb, ffi::ResultBuffer<ffi::F32> ga, ffi::ResultBuffer<ffi::F32> gh0) {
@@ -251,6 +265,10 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(MxkLruBwdNoAlloc, LruBwdNoAlloc,
         .Ret<C64B>().Ret<C64B>().Ret<C64B>());
 XLA_FFI_DEFINE_HANDLER_SYMBOL(MxkLinRecFwd, LinRecFwd,
     MXK_BIND_STREAM().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<U8B>().Ret<F32B>().Ret<F32B>());
+XLA_FFI_DEFINE_HANDLER_SYMBOL(MxkLinRecLast, LinRecLast,
+    MXK_BIND_STREAM().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<U8B>().Ret<F32B>());
+XLA_FFI_DEFINE_HANDLER_SYMBOL(MxkLruLast, LruLast,
+    MXK_BIND_STREAM().Arg<C64B>().Arg<C64B>().Arg<C64B>().Arg<U8B>().Ret<C64B>());
 XLA_FFI_DEFINE_HANDLER_SYMBOL(MxkLinRecBwd, LinRecBwd,
     MXK_BIND_STREAM().Arg<F32B>().Arg<F32B>().Arg<F32B>().Arg<U8B>().Arg<F32B>().Arg<F32B>()
         .Ret<F32B>().Ret<F32B>().Ret<F32B>());
