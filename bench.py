@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the sequence-mixing hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c1|c5|a7|n1|n1t|n2|n4]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c1|c5|a7|n1|n1t|n2|n3|n4]
     python bench.py --impl reference ...      # CPU arm: the oracle port, host cores
 
 A step is one pass of the hot path over one batch of seeded synthetic input:
@@ -497,6 +497,80 @@ class MinGruA7:
         return xs
 
 
+class RtrlN3:
+    """One RTRL segment of the LRU cell (Memoroid.local_jacobian, memoroid.py:143-176 with lru.py:110-139): scan,
+    read-out, the five local Jacobians and their propagation to the sensitivities after the last step.  B=64
+    sequences x T=64 steps, F=64 features, N=128 hidden units, fp32 / complex64, done ~ Bernoulli(0.01)."""
+    name = "n3_rtrl_lru_segment"
+    dtype = "c64"
+    B, T, F, N = 64, 64, 64, 128
+    p_done = 0.01
+    seed = 1234 + 10
+    dominant = "linrec_fwd_kernel"
+    launches_per_step = 6
+    dominant_traffic_bytes = None
+    cpu_sample_batch = 8
+    roofline_of_step = True
+
+    def __init__(self, batch=None):
+        self.B = batch or self.B
+        self.model = None
+
+    def tokens(self):
+        return self.B * self.T
+
+    def host_inputs(self, seed_offset=0, device="cpu"):
+        g = torch.Generator(device=device).manual_seed(self.seed + seed_offset)
+        return dict(x=torch.randn(self.B, self.T, self.F, generator=g, device=device),
+                    done=(torch.rand(self.B, self.T, generator=g, device=device) < self.p_done).to(torch.uint8))
+
+    def _model(self, device):
+        if self.model is None:
+            from memorax_b200.memoroid import LRUCell, Memoroid
+            torch.manual_seed(self.seed)
+            self.model = Memoroid(LRUCell(self.F, self.N, r_min=0.9, r_max=0.999, max_phase=math.pi / 10).to(device))
+            self.carry = tuple(c.to(device) for c in self.model.cell.initialize_carry(None, (self.B, self.F)))
+            self.sens = self.model.initialize_sensitivity(None, (self.B, self.F))
+        return self.model
+
+    def algorithmic_bytes(self):
+        # the formulation's own traffic: the two (B,T,N,F) complex Jacobians of the input matrix written and read once,
+        # the three (B,T,N) ones likewise, inputs in, read-out and sensitivities out
+        big = 2 * 8 * self.B * self.T * self.N * self.F
+        small = 3 * 8 * self.B * self.T * self.N
+        return 2 * (big + small) + 8 * self.B * self.T * self.F + 8 * self.B * self.N * (2 * self.F + 3)
+
+    def roofline(self, step_ms):
+        hbm, _, kind = measured_peaks()
+        byts = self.algorithmic_bytes()
+        return {"bound": "hbm", "achieved": byts / (step_ms * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s",
+                "frac": byts / (step_ms * 1e-3) / 1e9 / hbm, "peak_kind": f"of {kind}", "algorithmic_bytes_per_step": byts,
+                "note": "whole segment: library GEMMs and PyTorch elementwise ops build the Jacobians, this repository's "
+                        "kernels run the scan and the five last-state-only propagations"}
+
+    def step(self, x, ops, mark=None):
+        model = self._model(x["x"].device)
+        if mark:
+            mark[0].record()
+        with torch.no_grad():
+            carry, y, sens = model.local_jacobian(x["x"], x["done"], self.carry, self.sens)
+        if mark:
+            mark[1].record()
+        return (y, carry[0][:, 0]) + tuple(sens[k] for k in sorted(sens))
+
+    def cpu_step(self, x):
+        from oracle import memoroid_oracle as mo
+        cell = self._model("cpu").cell if self.model is None else self.model.cell
+        p = {n: getattr(cell, n).detach().cpu() for n in ("nu_log", "theta_log", "gamma_log", "B_real", "B_imag", "C_real", "C_imag", "D")}
+        nb = x["x"].shape[0]
+        sens = {"nu_log": torch.zeros(nb, 1, self.N, dtype=torch.complex64), "theta_log": torch.zeros(nb, 1, self.N, dtype=torch.complex64),
+                "gamma_log": torch.zeros(nb, 1, self.N, dtype=torch.complex64),
+                "B_real": torch.zeros(nb, 1, self.N, self.F, dtype=torch.complex64), "B_imag": torch.zeros(nb, 1, self.N, self.F, dtype=torch.complex64)}
+        with torch.no_grad():
+            return mo.lru_rtrl_seq(x["x"], x["done"].float(), torch.zeros(nb, self.N, dtype=torch.complex64), p["nu_log"], p["theta_log"],
+                                   p["gamma_log"], torch.complex(p["B_real"], p["B_imag"]), torch.complex(p["C_real"], p["C_imag"]), p["D"], sens)
+
+
 class MlstmN1:
     """mLSTM scan + read-out fwd+bwd (mlstm.py:163-240) at the linear-attention configuration's size: B=256,
     H=4, T=256, head dim 64, fp32; log_i ~ N(0, 0.1^2) (the cell's gate bias init), log_f = -softplus(-N(4.5, 1))
@@ -701,7 +775,7 @@ class LruLayerN4:
             return torch.matmul(h, torch.complex(cell.C_real, cell.C_imag).t()).real + cell.D * x["x"]
 
 
-WORKLOADS = {"a7": MinGruA7, "n4": LruLayerN4, "n1": MlstmN1, "n1t": MlstmTcN1, "c2": LinAttnC2, "c3": GDeltaC3, "c4": LruC4, "c1": LinRecC1, "c5": TrainC5, "n2": MambaN2}
+WORKLOADS = {"n3": RtrlN3, "a7": MinGruA7, "n4": LruLayerN4, "n1": MlstmN1, "n1t": MlstmTcN1, "c2": LinAttnC2, "c3": GDeltaC3, "c4": LruC4, "c1": LinRecC1, "c5": TrainC5, "n2": MambaN2}
 
 
 # ------------------------------------------------------------ clock sampling
@@ -1081,7 +1155,7 @@ def run_gpu_arm(args):
     if args.ops:
         per_op[args.workload] = {k: head[k] for k in ("workload", "batch_per_gpu", "ms_per_step", "tokens_per_s",
                                                       "dtype", "blocks", "clocks", "roofline")}
-        for name in ("c1", "c3", "c4", "c5", "a7", "n1", "n1t", "n2", "n4"):
+        for name in ("c1", "c3", "c4", "c5", "a7", "n1", "n1t", "n2", "n3", "n4"):
             if name == args.workload:
                 continue
             per_op[name] = hz.run_op(WORKLOADS[name], None, args.steps, args.warmup, args.min_seconds)
