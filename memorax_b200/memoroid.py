@@ -278,13 +278,16 @@ class LRUCell(_ComplexDiagonalCell):
         lam = self.diag_lambda()
         gamma_exp = torch.exp(self.gamma_log)
         bsz, steps = inputs.shape[:2]
-        scaled_inputs = gamma_exp[None, None, :, None] * inputs[:, :, None, :].float()
+        # gamma (x) u and i gamma (x) u, each written once in the propagation's complex dtype (a real product, its
+        # complex copy and the multiplication by i would be three passes over the (B,T,H,F) tensors)
+        g_c = gamma_exp.to(torch.complex64)[None, None, :, None]
+        u_c = inputs.float().to(torch.complex64)[:, :, None, :]
         return lam.expand(bsz, steps, self.hidden_dim), {
             "nu_log": -torch.exp(self.nu_log) * lam * prev_state,
             "theta_log": 1j * torch.exp(self.theta_log) * lam * prev_state,
             "gamma_log": state_contrib,
-            "B_real": scaled_inputs,
-            "B_imag": 1j * scaled_inputs,
+            "B_real": g_c * u_c,
+            "B_imag": (1j * g_c) * u_c,
         }
 
     def initialize_sensitivity(self, key, input_shape):
