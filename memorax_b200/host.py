@@ -13,7 +13,9 @@ afterwards, so that a step costs one launch on the host however many slices it h
 
 With ``overlap_calls=N`` (eager mode) consecutive calls stream: the copy-in of call
 i+1 no longer waits for the copy-out of call i (host inputs have no producer on the
-device), so both copy engines stay busy across calls; at most N calls are in flight.
+device), so both copy engines stay busy across calls; at most N calls are in flight on the device and the
+host blocks once it is two calls further ahead (its lead, and with it the device memory held by calls not yet
+copied out, stays bounded).
 The caller then must not rewrite a host input buffer before ``inputs_consumed`` (an
 event recorded after the last copy-in of the latest call) has completed."""
 from __future__ import annotations
@@ -47,6 +49,7 @@ class HostPipeline:
         self.overlap_calls = max(1, int(overlap_calls))
         self._finished = []          # completion events of the calls still in flight, oldest first
         self._pending = []           # (copy-out event, device outputs) of slices whose copy-out may still be running
+        self._issued = []            # completion events of the calls the host has issued and not yet waited for
         self._in_bufs = {}           # staging set -> {input name: device buffer}
         self._calls = 0
         self.inputs_consumed = None
@@ -114,6 +117,11 @@ class HostPipeline:
         if streaming and len(self._finished) >= self.overlap_calls:
             self.s_in.wait_event(self._finished[-self.overlap_calls])
             del self._finished[:-self.overlap_calls]
+        if streaming and len(self._issued) > self.overlap_calls + 2:
+            # the host stays at most two calls ahead of what the device may have in flight: an unbounded lead would
+            # keep every call's device outputs alive at once (the allocator then grows by a cudaMalloc per tensor
+            # and call) without making anything faster
+            self._issued.pop(0).synchronize()
         staged = None
         if not capturing:
             self._release_finished()
@@ -170,6 +178,7 @@ class HostPipeline:
             # the caller's stream is NOT made to wait here (that would serialise the next call's kernels
             # behind this call's copy-out); call wait() before reading the host outputs
             self._finished.append(finished)
+            self._issued.append(finished)
             self.inputs_consumed = ready
         else:
             main.wait_event(finished)
@@ -186,5 +195,6 @@ class HostPipeline:
         for ev in self._finished:
             ev.synchronize()
         self._finished.clear()
+        self._issued.clear()
         torch.cuda.current_stream(self.device).synchronize()
         self._release_finished()
