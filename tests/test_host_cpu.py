@@ -58,6 +58,12 @@ def test_status_strings_and_validation_without_a_gpu(lib):
     assert L.mxk_linattn_chunk_states_bytes(2, 65, 3, 64) == 2 * 3 * 2 * 9 * 64 * 16
     assert L.mxk_gdelta_chunk_states_bytes(2, 65, 3, 128) == 2 * 3 * 2 * (16 + 8) * 128 * 16
     assert L.mxk_linrec_bwd_workspace_bytes(1, 1, 4, 9, 8) == 4 * 8 * 8
+    # the last-state-only recurrences: missing pointers, bad dimensions, misaligned buffers, unsupported group width
+    assert L.mxk_linrec_f32_last(None, 0, None, None, None, None, 1, 1, 1, None) == -1
+    assert L.mxk_linrec_c64_last(p, 1, p, None, None, p, 0, 1, 1, None) == -2
+    assert L.mxk_linrec_c64_last(p, 1, p + 4, None, None, p, 1, 1, 1, None) == -3
+    assert L.mxk_linrec_f32_grouped_last(None, None, None, None, None, 1, 1, 128, 1, None) == -1
+    assert L.mxk_linrec_f32_grouped_last(p, p, None, None, p, 1, 1, 100, 1, None) == -4
 
 
 def test_missing_library_fails_loudly(tmp_path):
